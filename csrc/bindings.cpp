@@ -1,0 +1,530 @@
+// Python bindings of the sm_100a kernels (torch extension `oxb_cuda`).
+// Every function launches on torch's current CUDA stream and allocates nothing unless noted.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <pybind11/stl.h>
+#include <torch/extension.h>
+
+#include <string>
+#include <vector>
+
+#include "common/tma_host.h"
+#include "kernels/attn.cuh"
+#include "kernels/fused_ops.cuh"
+#include "kernels/gemm_bf16.cuh"
+#include "kernels/quant_ops.cuh"
+#include "kernels/sampler.cuh"
+
+namespace py = pybind11;
+using torch::Tensor;
+
+namespace {
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  TORCH_CHECK(e == cudaSuccess, "oxb: launch of ", what, " failed: ", cudaGetErrorString(e));
+}
+
+const __nv_bfloat16* bf16_ptr(const c10::optional<Tensor>& t) {
+  if (!t.has_value() || !t->defined()) return nullptr;
+  TORCH_CHECK(t->scalar_type() == torch::kBFloat16 && t->is_cuda(), "expected a CUDA bf16 tensor");
+  return reinterpret_cast<const __nv_bfloat16*>(t->data_ptr());
+}
+template <typename T>
+T* opt_ptr(const c10::optional<Tensor>& t) {
+  if (!t.has_value() || !t->defined()) return nullptr;
+  return reinterpret_cast<T*>(t->data_ptr());
+}
+
+// ---------------------------------------------------------------------------------------------
+// GEMM
+// ---------------------------------------------------------------------------------------------
+// a: [M, K] or [G, cap, K] bf16 (K contiguous);  w: [N, K] or [G, N, K] bf16.
+void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optional<Tensor>& out,
+               const c10::optional<Tensor>& bias, const std::vector<int64_t>& dst_ptrs,
+               const std::vector<int64_t>& arrive_ptrs, const c10::optional<Tensor>& done_ticket,
+               const c10::optional<Tensor>& reset_on_done, int64_t rows_per_owner,
+               const c10::optional<Tensor>& group_counts, const c10::optional<Tensor>& row_meta,
+               const c10::optional<Tensor>& ag_flags, int64_t ag_expected, int64_t ag_rows_per_src,
+               const c10::optional<Tensor>& ag_ticket, const Tensor& status, int64_t bn,
+               int64_t splits, int64_t act, int64_t m_tiles_override) {
+  TORCH_CHECK(a.is_cuda() && w.is_cuda(), "gemm_bf16: CUDA tensors required");
+  TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16,
+              "gemm_bf16: bf16 operands required");
+  TORCH_CHECK(a.stride(-1) == 1 && w.stride(-1) == 1, "gemm_bf16: K must be contiguous");
+  const bool grouped3d = a.dim() == 3;
+  TORCH_CHECK(w.dim() == a.dim(), "gemm_bf16: a and w must have the same rank");
+  const int64_t G = grouped3d ? a.size(0) : 1;
+  const int64_t M = grouped3d ? a.size(1) : a.size(0);
+  const int64_t K = a.size(-1);
+  const int64_t N = grouped3d ? w.size(1) : w.size(0);
+  TORCH_CHECK(w.size(-1) == K, "gemm_bf16: K mismatch");
+  TORCH_CHECK(K % 8 == 0, "gemm_bf16: K must be a multiple of 8 (16-byte TMA rows)");
+  if (grouped3d) {
+    TORCH_CHECK(w.size(0) == G, "gemm_bf16: group mismatch");
+  }
+
+  const uint64_t a_row = static_cast<uint64_t>(a.stride(-2)) * 2;
+  const uint64_t w_row = static_cast<uint64_t>(w.stride(-2)) * 2;
+  const uint64_t a_grp = grouped3d ? static_cast<uint64_t>(a.stride(0)) * 2 : a_row * M;
+  const uint64_t w_grp = grouped3d ? static_cast<uint64_t>(w.stride(0)) * 2 : w_row * N;
+  const int bn_i = bn == 64 ? 64 : (bn == 256 ? 256 : 128);
+  CUtensorMap tmA = oxb::make_tma_map(a.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, K, M, G,
+                                      a_row, a_grp, 64, 128, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+  CUtensorMap tmB = oxb::make_tma_map(w.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, K, N, G,
+                                      w_row, w_grp, 64, bn_i, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+
+  oxb::GemmParams p{};
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(K);
+  const int total_kb = static_cast<int>((K + 63) / 64);
+  int s = static_cast<int>(splits < 1 ? 1 : splits);
+  if (s > total_kb) s = total_kb;
+  p.kb_per_split = (total_kb + s - 1) / s;
+  s = (total_kb + p.kb_per_split - 1) / p.kb_per_split;
+  p.epi = static_cast<int>(epi);
+  p.act = static_cast<int>(act);
+  if (epi != oxb::kEpiRedF32) {
+    TORCH_CHECK(out.has_value(), "gemm_bf16: out required for store epilogues");
+    TORCH_CHECK(s == 1, "gemm_bf16: split-K needs the fp32 reduction epilogue");
+    TORCH_CHECK(out->stride(-1) == 1, "gemm_bf16: out must be row-major");
+    if (epi == oxb::kEpiStoreF32) {
+      TORCH_CHECK(out->scalar_type() == torch::kFloat32, "gemm_bf16: fp32 out expected");
+    } else {
+      TORCH_CHECK(out->scalar_type() == torch::kBFloat16, "gemm_bf16: bf16 out expected");
+    }
+    p.C = out->data_ptr();
+    p.ldc = out->stride(-2);
+    p.c_group_stride = out->dim() == 3 ? out->stride(0) : 0;
+  } else {
+    TORCH_CHECK(!dst_ptrs.empty() && dst_ptrs.size() <= oxb::kMaxRanks, "gemm_bf16: 1..8 owners");
+    for (size_t i = 0; i < dst_ptrs.size(); ++i) p.dst[i] = reinterpret_cast<float*>(dst_ptrs[i]);
+    for (size_t i = 0; i < arrive_ptrs.size() && i < oxb::kMaxRanks; ++i)
+      p.arrive[i] = reinterpret_cast<uint32_t*>(arrive_ptrs[i]);
+    p.n_owners = static_cast<int>(dst_ptrs.size());
+    p.rows_per_owner = static_cast<int>(rows_per_owner > 0 ? rows_per_owner : M);
+  }
+  if (epi == oxb::kEpiSwigluBf16) {
+    TORCH_CHECK(N % bn_i == 0, "swiglu epilogue: N % BN must be 0");
+  }
+  p.bias = bf16_ptr(bias);
+  p.done_ticket = opt_ptr<uint32_t>(done_ticket);
+  if (reset_on_done.has_value() && reset_on_done->defined()) {
+    p.reset_on_done = reinterpret_cast<uint32_t*>(reset_on_done->data_ptr());
+    p.n_reset = static_cast<int>(reset_on_done->numel());
+  }
+  int m_tiles = static_cast<int>((M + 127) / 128);
+  if (group_counts.has_value() && group_counts->defined()) {
+    p.group_counts = reinterpret_cast<const uint32_t*>(group_counts->data_ptr());
+    p.n_groups = static_cast<int>(G);
+    TORCH_CHECK(m_tiles_override > 0, "gemm_bf16: grouped mode needs the m-tile bound");
+    m_tiles = static_cast<int>(m_tiles_override);
+    if (row_meta.has_value() && row_meta->defined()) {
+      p.row_meta = reinterpret_cast<const oxb::RowMeta*>(row_meta->data_ptr());
+      p.meta_group_stride = M;
+    }
+  } else {
+    TORCH_CHECK(G == 1, "gemm_bf16: 3-D operands need group_counts");
+  }
+  if (ag_flags.has_value() && ag_flags->defined()) {
+    TORCH_CHECK(ag_ticket.has_value(), "gemm_bf16: ag_ticket required with ag_flags");
+    p.ag_flags = reinterpret_cast<const uint32_t*>(ag_flags->data_ptr());
+    p.ag_n_src = static_cast<int>(ag_flags->numel());
+    p.ag_expected = static_cast<uint32_t>(ag_expected);
+    p.ag_rows_per_src = static_cast<int>(ag_rows_per_src > 0 ? ag_rows_per_src : M);
+    p.ag_ticket = reinterpret_cast<uint32_t*>(ag_ticket->data_ptr());
+  }
+  p.status = reinterpret_cast<int*>(status.data_ptr());
+  oxb::launch_gemm_bf16(tmA, tmB, p, bn_i, m_tiles, s, cur_stream());
+  check_launch("gemm_bf16");
+}
+
+// ---------------------------------------------------------------------------------------------
+// attention
+// ---------------------------------------------------------------------------------------------
+void paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
+                  const Tensor& block_tables, const Tensor& seq_lens, const Tensor& pages_per_split,
+                  const Tensor& part_o, const Tensor& part_ml, const Tensor& out, int64_t batch,
+                  int64_t max_splits, int64_t window, double scale) {
+  TORCH_CHECK(q.dim() == 3 && k_cache.dim() == 4, "paged_decode: q [B,Hq,D], cache [blk,Hkv,16,D]");
+  TORCH_CHECK(k_cache.size(2) == 16, "paged_decode: 16-token pages");
+  oxb::DecodeAttnParams p{};
+  const int D = static_cast<int>(q.size(2));
+  TORCH_CHECK(D == 64 || D == 128, "paged_decode: head_dim 64 or 128");
+  p.q = reinterpret_cast<const __nv_bfloat16*>(q.data_ptr());
+  p.q_stride = q.stride(0);
+  TORCH_CHECK(q.stride(1) == D && q.stride(2) == 1, "paged_decode: q heads must be packed");
+  p.k_cache = reinterpret_cast<const __nv_bfloat16*>(k_cache.data_ptr());
+  p.v_cache = reinterpret_cast<const __nv_bfloat16*>(v_cache.data_ptr());
+  p.block_tables = block_tables.data_ptr<int>();
+  p.seq_lens = seq_lens.data_ptr<int>();
+  p.pages_per_split = pages_per_split.data_ptr<int>();
+  p.part_o = part_o.data_ptr<float>();
+  p.part_ml = part_ml.data_ptr<float>();
+  p.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  p.out_stride = out.stride(0);
+  p.max_blocks = static_cast<int>(block_tables.size(1));
+  p.Hq = static_cast<int>(q.size(1));
+  p.Hkv = static_cast<int>(k_cache.size(1));
+  TORCH_CHECK(p.Hq % p.Hkv == 0 && p.Hq / p.Hkv <= 16, "paged_decode: group size must be <= 16");
+  p.max_splits = static_cast<int>(max_splits);
+  TORCH_CHECK(part_o.numel() >= batch * p.Hq * max_splits * D, "paged_decode: part_o too small");
+  TORCH_CHECK(part_ml.numel() >= batch * p.Hq * max_splits * 2, "paged_decode: part_ml too small");
+  p.window = static_cast<int>(window);
+  p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
+  oxb::launch_paged_decode(p, static_cast<int>(batch), D, cur_stream());
+  check_launch("paged_decode");
+}
+
+void paged_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
+                   const Tensor& block_tables, const Tensor& tile_seq, const Tensor& tile_q0,
+                   const Tensor& q_start, const Tensor& q_lens, const Tensor& ctx_lens,
+                   const Tensor& out, int64_t n_tiles, int64_t window, double scale) {
+  TORCH_CHECK(q.dim() == 3 && k_cache.dim() == 4, "paged_prefill: q [T,Hq,D], cache [blk,Hkv,16,D]");
+  oxb::PrefillAttnParams p{};
+  const int D = static_cast<int>(q.size(2));
+  TORCH_CHECK(D == 64 || D == 128, "paged_prefill: head_dim 64 or 128");
+  p.q = reinterpret_cast<const __nv_bfloat16*>(q.data_ptr());
+  p.q_stride = q.stride(0);
+  TORCH_CHECK(q.stride(1) == D && q.stride(2) == 1, "paged_prefill: q heads must be packed");
+  p.k_cache = reinterpret_cast<const __nv_bfloat16*>(k_cache.data_ptr());
+  p.v_cache = reinterpret_cast<const __nv_bfloat16*>(v_cache.data_ptr());
+  p.block_tables = block_tables.data_ptr<int>();
+  p.tile_seq = tile_seq.data_ptr<int>();
+  p.tile_q0 = tile_q0.data_ptr<int>();
+  p.q_start = q_start.data_ptr<int>();
+  p.q_lens = q_lens.data_ptr<int>();
+  p.ctx_lens = ctx_lens.data_ptr<int>();
+  p.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  p.out_stride = out.stride(0);
+  p.max_blocks = static_cast<int>(block_tables.size(1));
+  p.Hq = static_cast<int>(q.size(1));
+  p.Hkv = static_cast<int>(k_cache.size(1));
+  p.window = static_cast<int>(window);
+  p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
+  oxb::launch_paged_prefill(p, static_cast<int>(n_tiles), D, cur_stream());
+  check_launch("paged_prefill");
+}
+
+// ---------------------------------------------------------------------------------------------
+// fused finalize kernels
+// ---------------------------------------------------------------------------------------------
+void finalize_norm(const c10::optional<Tensor>& acc, const c10::optional<Tensor>& arrive,
+                   int64_t expected, const c10::optional<Tensor>& ticket,
+                   const c10::optional<Tensor>& residual_in,
+                   const c10::optional<Tensor>& residual_out, const c10::optional<Tensor>& bias,
+                   const c10::optional<Tensor>& norm_w, double eps, double w_offset,
+                   const std::vector<int64_t>& out_ptrs, const std::vector<int64_t>& out_flag_ptrs,
+                   int64_t out_row_off, int64_t rows, int64_t N, const Tensor& status,
+                   const c10::optional<Tensor>& router_w, int64_t top_k, int64_t experts_per_rank,
+                   double routed_scale, const std::vector<int64_t>& slab_ptrs,
+                   const std::vector<int64_t>& meta_ptrs, const std::vector<int64_t>& cnt_ptrs,
+                   int64_t cap, int64_t my_rank) {
+  TORCH_CHECK(N % 8 == 0, "finalize_norm: N must be a multiple of 8");
+  oxb::FinalizeNormParams p{};
+  p.acc = opt_ptr<float>(acc);
+  p.arrive = opt_ptr<uint32_t>(arrive);
+  p.expected = static_cast<uint32_t>(expected);
+  p.ticket = opt_ptr<uint32_t>(ticket);
+  if (p.arrive != nullptr) {
+    TORCH_CHECK(p.ticket != nullptr, "finalize_norm: ticket required");
+  }
+  p.residual_in = bf16_ptr(residual_in);
+  p.residual_out = const_cast<__nv_bfloat16*>(bf16_ptr(residual_out));
+  p.bias = bf16_ptr(bias);
+  p.norm_w = bf16_ptr(norm_w);
+  p.eps = static_cast<float>(eps);
+  p.w_offset = static_cast<float>(w_offset);
+  TORCH_CHECK(out_ptrs.size() <= oxb::kMaxPeers, "finalize_norm: at most 8 destinations");
+  for (size_t i = 0; i < out_ptrs.size(); ++i)
+    p.out[i] = reinterpret_cast<__nv_bfloat16*>(out_ptrs[i]);
+  for (size_t i = 0; i < out_flag_ptrs.size() && i < oxb::kMaxPeers; ++i)
+    p.out_flag[i] = reinterpret_cast<uint32_t*>(out_flag_ptrs[i]);
+  p.n_dst = static_cast<int>(out_ptrs.size() > 0 ? out_ptrs.size() : out_flag_ptrs.size());
+  p.out_row_off = out_row_off;
+  p.rows = static_cast<int>(rows);
+  p.N = static_cast<int>(N);
+  p.status = reinterpret_cast<int*>(status.data_ptr());
+  if (router_w.has_value() && router_w->defined()) {
+    p.router_w = bf16_ptr(router_w);
+    p.n_experts = static_cast<int>(router_w->size(0));
+    TORCH_CHECK(p.n_experts <= 64 && top_k <= 8, "finalize_norm: <= 64 experts, top_k <= 8");
+    p.top_k = static_cast<int>(top_k);
+    p.experts_per_rank = static_cast<int>(experts_per_rank);
+    p.routed_scale = static_cast<float>(routed_scale);
+    TORCH_CHECK(slab_ptrs.size() == meta_ptrs.size() && slab_ptrs.size() == cnt_ptrs.size() &&
+                    slab_ptrs.size() <= oxb::kMaxPeers,
+                "finalize_norm: slab/meta/cnt tables must match");
+    for (size_t i = 0; i < slab_ptrs.size(); ++i) {
+      p.slab[i] = reinterpret_cast<__nv_bfloat16*>(slab_ptrs[i]);
+      p.meta[i] = reinterpret_cast<oxb::MoeRowMeta*>(meta_ptrs[i]);
+      p.slab_cnt[i] = reinterpret_cast<uint32_t*>(cnt_ptrs[i]);
+    }
+    p.n_dst = static_cast<int>(slab_ptrs.size());
+    p.cap = static_cast<int>(cap);
+    p.my_rank = static_cast<int>(my_rank);
+  }
+  oxb::launch_finalize_norm(p, cur_stream());
+  check_launch("finalize_norm");
+}
+
+void qkv_rope_append(const c10::optional<Tensor>& acc_f32, const c10::optional<Tensor>& qkv_bf16,
+                     const c10::optional<Tensor>& bias, const c10::optional<Tensor>& q_norm_w,
+                     const c10::optional<Tensor>& k_norm_w, double norm_eps, double norm_w_offset,
+                     const Tensor& positions, const Tensor& slot_mapping, const Tensor& inv_freq,
+                     double rope_mscale, const Tensor& q_out, const Tensor& k_cache,
+                     const Tensor& v_cache, int64_t M, int64_t Hq, int64_t Hkv, int64_t D,
+                     const Tensor& status) {
+  oxb::QkvRopeParams p{};
+  p.acc_f32 = opt_ptr<float>(acc_f32);
+  p.qkv_bf16 = bf16_ptr(qkv_bf16);
+  TORCH_CHECK((p.acc_f32 != nullptr) != (p.qkv_bf16 != nullptr), "qkv_rope_append: one input");
+  p.bias = bf16_ptr(bias);
+  p.q_norm_w = bf16_ptr(q_norm_w);
+  p.k_norm_w = bf16_ptr(k_norm_w);
+  p.norm_eps = static_cast<float>(norm_eps);
+  p.norm_w_offset = static_cast<float>(norm_w_offset);
+  TORCH_CHECK(positions.scalar_type() == torch::kInt32 && slot_mapping.scalar_type() == torch::kInt64,
+              "qkv_rope_append: positions int32, slot_mapping int64");
+  p.positions = positions.data_ptr<int>();
+  p.slot_mapping = reinterpret_cast<const long long*>(slot_mapping.data_ptr<int64_t>());
+  p.inv_freq = inv_freq.data_ptr<float>();
+  TORCH_CHECK(inv_freq.numel() == D / 2, "qkv_rope_append: inv_freq must have D/2 entries");
+  p.rope_mscale = static_cast<float>(rope_mscale);
+  p.q_out = reinterpret_cast<__nv_bfloat16*>(q_out.data_ptr());
+  p.k_cache = reinterpret_cast<__nv_bfloat16*>(k_cache.data_ptr());
+  p.v_cache = reinterpret_cast<__nv_bfloat16*>(v_cache.data_ptr());
+  p.M = static_cast<int>(M);
+  p.Hq = static_cast<int>(Hq);
+  p.Hkv = static_cast<int>(Hkv);
+  p.D = static_cast<int>(D);
+  TORCH_CHECK(Hq + Hkv <= 160 && (D % 8) == 0, "qkv_rope_append: unsupported head layout");
+  p.num_slots = k_cache.size(0) * 16;
+  p.status = reinterpret_cast<int*>(status.data_ptr());
+  oxb::launch_qkv_rope_append(p, cur_stream());
+  check_launch("qkv_rope_append");
+}
+
+void swiglu(const c10::optional<Tensor>& acc_f32, const c10::optional<Tensor>& gu_bf16,
+            const Tensor& out, int64_t M, int64_t I, int64_t act) {
+  oxb::SwigluParams p{};
+  p.acc_f32 = opt_ptr<float>(acc_f32);
+  p.gu_bf16 = bf16_ptr(gu_bf16);
+  TORCH_CHECK(I % 4 == 0, "swiglu: I must be a multiple of 4");
+  p.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  p.M = static_cast<int>(M);
+  p.I = static_cast<int>(I);
+  p.act = static_cast<int>(act);
+  oxb::launch_swiglu(p, cur_stream());
+  check_launch("swiglu");
+}
+
+void embed_gather(const Tensor& tokens, const Tensor& table, const Tensor& out, double scale,
+                  int64_t vocab_start) {
+  TORCH_CHECK(tokens.scalar_type() == torch::kInt32, "embed_gather: int32 tokens");
+  TORCH_CHECK(table.size(1) % 8 == 0, "embed_gather: hidden must be a multiple of 8");
+  oxb::launch_embed_gather(tokens.data_ptr<int>(), bf16_ptr(table),
+                           reinterpret_cast<__nv_bfloat16*>(out.data_ptr()),
+                           static_cast<int>(tokens.numel()), static_cast<int>(table.size(1)),
+                           static_cast<int>(table.size(0)), static_cast<float>(scale),
+                           static_cast<int>(vocab_start), cur_stream());
+  check_launch("embed_gather");
+}
+
+void cast_acc_bf16(const Tensor& acc, const c10::optional<Tensor>& bias, const Tensor& out,
+                   int64_t M, int64_t N) {
+  TORCH_CHECK(N % 4 == 0, "cast_acc_bf16: N must be a multiple of 4");
+  oxb::launch_cast_acc_bf16(acc.data_ptr<float>(), bf16_ptr(bias),
+                            reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), static_cast<int>(M),
+                            static_cast<int>(N), out.stride(0), cur_stream());
+  check_launch("cast_acc_bf16");
+}
+
+void fwht128(const Tensor& x) {
+  TORCH_CHECK(x.scalar_type() == torch::kFloat32 && x.numel() % 128 == 0, "fwht128: fp32, 128 | n");
+  oxb::launch_fwht128(x.data_ptr<float>(), x.numel() / 128, cur_stream());
+  check_launch("fwht128");
+}
+
+void kv_block_copy(const Tensor& k_cache, const Tensor& v_cache, const Tensor& src,
+                   const Tensor& dst) {
+  const long long block_elems = k_cache.stride(0);
+  oxb::launch_kv_block_copy(reinterpret_cast<__nv_bfloat16*>(k_cache.data_ptr()),
+                            reinterpret_cast<__nv_bfloat16*>(v_cache.data_ptr()),
+                            src.data_ptr<int>(), dst.data_ptr<int>(),
+                            static_cast<int>(src.numel()), block_elems, cur_stream());
+  check_launch("kv_block_copy");
+}
+
+void softcap(const Tensor& logits, double cap) {
+  oxb::launch_softcap(logits.data_ptr<float>(), logits.numel(), static_cast<float>(cap),
+                      cur_stream());
+  check_launch("softcap");
+}
+
+// ---------------------------------------------------------------------------------------------
+// quantized weights
+// ---------------------------------------------------------------------------------------------
+void mmvq(int64_t qtype, const Tensor& w, const Tensor& x, const c10::optional<Tensor>& bias,
+          const Tensor& out, int64_t N, int64_t K, bool add) {
+  TORCH_CHECK(w.scalar_type() == torch::kUInt8 && w.is_cuda(), "mmvq: packed uint8 weights");
+  TORCH_CHECK(K % 32 == 0, "mmvq: K must be a multiple of 32");
+  oxb::MmvqParams p{};
+  p.w = w.data_ptr<uint8_t>();
+  p.row_bytes = oxb::quant_row_bytes(static_cast<int>(qtype), K);
+  TORCH_CHECK(p.row_bytes > 0 && w.numel() >= p.row_bytes * N, "mmvq: weight buffer too small");
+  p.x = bf16_ptr(x);
+  p.ldx = x.stride(0);
+  p.bias = bf16_ptr(bias);
+  if (out.scalar_type() == torch::kFloat32)
+    p.out_f32 = out.data_ptr<float>();
+  else
+    p.out_bf16 = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  p.ldo = out.stride(0);
+  p.M = static_cast<int>(x.size(0));
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(K);
+  p.add = add ? 1 : 0;
+  TORCH_CHECK(oxb::launch_mmvq(static_cast<int>(qtype), p, cur_stream()),
+              "mmvq: no device decoder for GGUF type ", qtype);
+  check_launch("mmvq");
+}
+
+void dequant_rows(int64_t qtype, const Tensor& w, const c10::optional<Tensor>& row_ids,
+                  const Tensor& out, int64_t n_src_rows, int64_t K, double scale) {
+  TORCH_CHECK(w.scalar_type() == torch::kUInt8 && w.is_cuda(), "dequant_rows: packed weights");
+  TORCH_CHECK(K % 32 == 0, "dequant_rows: K must be a multiple of 32");
+  const long long rb = oxb::quant_row_bytes(static_cast<int>(qtype), K);
+  const int* ids = nullptr;
+  if (row_ids.has_value() && row_ids->defined()) ids = row_ids->data_ptr<int>();
+  TORCH_CHECK(oxb::launch_dequant_rows(static_cast<int>(qtype), w.data_ptr<uint8_t>(), rb, ids,
+                                       static_cast<int>(out.size(0)), static_cast<int>(K),
+                                       reinterpret_cast<__nv_bfloat16*>(out.data_ptr()),
+                                       out.stride(0), static_cast<float>(scale),
+                                       static_cast<int>(n_src_rows), cur_stream()),
+              "dequant_rows: no device decoder for GGUF type ", qtype);
+  check_launch("dequant_rows");
+}
+
+int64_t quant_row_bytes(int64_t qtype, int64_t K) {
+  return oxb::quant_row_bytes(static_cast<int>(qtype), K);
+}
+
+// ---------------------------------------------------------------------------------------------
+// sampler
+// ---------------------------------------------------------------------------------------------
+void sample(const Tensor& logits, const c10::optional<Tensor>& temperature,
+            const c10::optional<Tensor>& top_k, const c10::optional<Tensor>& top_p,
+            const c10::optional<Tensor>& min_p, const c10::optional<Tensor>& seeds,
+            const c10::optional<Tensor>& counters, const c10::optional<Tensor>& allow_mask,
+            const Tensor& out_tokens, const c10::optional<Tensor>& out_logit) {
+  TORCH_CHECK(logits.scalar_type() == torch::kFloat32 && logits.dim() == 2, "sample: fp32 [B,V]");
+  oxb::SampleParams p{};
+  p.logits = logits.data_ptr<float>();
+  p.ld = logits.stride(0);
+  p.V = static_cast<int>(logits.size(1));
+  p.temperature = opt_ptr<float>(temperature);
+  p.top_k = opt_ptr<int>(top_k);
+  p.top_p = opt_ptr<float>(top_p);
+  p.min_p = opt_ptr<float>(min_p);
+  p.seeds = opt_ptr<uint64_t>(seeds);
+  p.counters = opt_ptr<uint64_t>(counters);
+  p.allow_mask = opt_ptr<uint32_t>(allow_mask);
+  p.mask_words = allow_mask.has_value() && allow_mask->defined()
+                     ? static_cast<int>(allow_mask->size(1))
+                     : 0;
+  p.out_tokens = out_tokens.data_ptr<int>();
+  p.out_logit = opt_ptr<float>(out_logit);
+  oxb::launch_sample(p, static_cast<int>(logits.size(0)), cur_stream());
+  check_launch("sample");
+}
+
+void argmax(const Tensor& logits, const Tensor& out, const c10::optional<Tensor>& out_val) {
+  TORCH_CHECK(logits.scalar_type() == torch::kFloat32 && logits.dim() == 2, "argmax: fp32 [B,V]");
+  oxb::launch_argmax(logits.data_ptr<float>(), logits.stride(0), static_cast<int>(logits.size(1)),
+                     static_cast<int>(logits.size(0)), out.data_ptr<int>(), opt_ptr<float>(out_val),
+                     cur_stream());
+  check_launch("argmax");
+}
+
+void argmax_combine(const Tensor& vals, const Tensor& idxs, const Tensor& out) {
+  oxb::launch_argmax_combine(vals.data_ptr<float>(), idxs.data_ptr<int>(),
+                             static_cast<int>(vals.size(0)), static_cast<int>(vals.size(1)),
+                             out.data_ptr<int>(), cur_stream());
+  check_launch("argmax_combine");
+}
+
+// ---------------------------------------------------------------------------------------------
+// peer memory (CUDA IPC): symmetric buffers that kernels address directly over NVLink
+// ---------------------------------------------------------------------------------------------
+int64_t ipc_alloc(int64_t bytes) {  // allocates: raw cudaMalloc so that the handle is exportable
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, static_cast<size_t>(bytes));
+  TORCH_CHECK(e == cudaSuccess, "ipc_alloc: ", cudaGetErrorString(e));
+  e = cudaMemset(p, 0, static_cast<size_t>(bytes));
+  TORCH_CHECK(e == cudaSuccess, "ipc_alloc memset: ", cudaGetErrorString(e));
+  return reinterpret_cast<int64_t>(p);
+}
+void ipc_free(int64_t ptr) { cudaFree(reinterpret_cast<void*>(ptr)); }
+py::bytes ipc_get_handle(int64_t ptr) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(ptr));
+  TORCH_CHECK(e == cudaSuccess, "ipc_get_handle: ", cudaGetErrorString(e));
+  return py::bytes(reinterpret_cast<const char*>(&h), sizeof(h));
+}
+int64_t ipc_open_handle(const std::string& handle) {
+  TORCH_CHECK(handle.size() == sizeof(cudaIpcMemHandle_t), "ipc_open_handle: bad handle size");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle.data(), sizeof(h));
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  TORCH_CHECK(e == cudaSuccess, "ipc_open_handle: ", cudaGetErrorString(e));
+  return reinterpret_cast<int64_t>(p);
+}
+void ipc_close_handle(int64_t ptr) { cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr)); }
+
+Tensor tensor_from_ptr(int64_t ptr, const std::vector<int64_t>& shape, const std::string& dtype,
+                       int64_t device) {
+  auto dt = torch::kUInt8;
+  if (dtype == "bf16") dt = torch::kBFloat16;
+  else if (dtype == "f32") dt = torch::kFloat32;
+  else if (dtype == "i32") dt = torch::kInt32;
+  else if (dtype == "u8") dt = torch::kUInt8;
+  else TORCH_CHECK(false, "tensor_from_ptr: unknown dtype ", dtype);
+  auto opts = torch::TensorOptions().dtype(dt).device(torch::kCUDA, static_cast<int>(device));
+  return torch::from_blob(reinterpret_cast<void*>(ptr), shape, [](void*) {}, opts);
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "sm_100a kernels of the B200-native Oxide engine";
+  m.def("gemm_bf16", &gemm_bf16);
+  m.def("paged_decode", &paged_decode);
+  m.def("paged_prefill", &paged_prefill);
+  m.def("finalize_norm", &finalize_norm);
+  m.def("qkv_rope_append", &qkv_rope_append);
+  m.def("swiglu", &swiglu);
+  m.def("embed_gather", &embed_gather);
+  m.def("cast_acc_bf16", &cast_acc_bf16);
+  m.def("fwht128", &fwht128);
+  m.def("kv_block_copy", &kv_block_copy);
+  m.def("softcap", &softcap);
+  m.def("mmvq", &mmvq);
+  m.def("dequant_rows", &dequant_rows);
+  m.def("quant_row_bytes", &quant_row_bytes);
+  m.def("sample", &sample);
+  m.def("argmax", &argmax);
+  m.def("argmax_combine", &argmax_combine);
+  m.def("ipc_alloc", &ipc_alloc);
+  m.def("ipc_free", &ipc_free);
+  m.def("ipc_get_handle", &ipc_get_handle);
+  m.def("ipc_open_handle", &ipc_open_handle);
+  m.def("ipc_close_handle", &ipc_close_handle);
+  m.def("tensor_from_ptr", &tensor_from_ptr);
+}

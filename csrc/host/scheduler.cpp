@@ -1,0 +1,410 @@
+#include "scheduler.h"
+
+#include <algorithm>
+#include <cmath>
+#include <stdexcept>
+
+namespace oxb {
+
+namespace {
+constexpr int kTileQ = 64;  // query rows per prefill-attention tile
+}
+
+Scheduler::Scheduler(const SchedulerConfig& cfg) : cfg_(cfg), pool_(cfg.num_blocks), radix_(&pool_) {}
+
+void Scheduler::add_request(int64_t id, const std::vector<int32_t>& prompt, int max_new_tokens,
+                            const std::vector<int32_t>& stop_ids, bool ignore_eos) {
+  if (prompt.empty()) throw std::invalid_argument("empty prompt");
+  if (static_cast<int>(prompt.size()) + 1 > cfg_.max_blocks_per_seq * kTokensPerBlock)
+    throw std::invalid_argument("prompt longer than the per-sequence KV capacity");
+  std::unique_ptr<Request> r(new Request());
+  r->id = id;
+  r->tokens = prompt;
+  r->prompt_len = static_cast<int>(prompt.size());
+  r->max_new_tokens = max_new_tokens;
+  r->stop_ids = stop_ids;
+  r->ignore_eos = ignore_eos;
+  r->arrival = arrivals_++;
+  r->table.reset(new SequenceBlockTable(&pool_));
+  waiting_.push_back(std::move(r));
+}
+
+const Request* Scheduler::find(int64_t id) const {
+  for (auto& r : running_)
+    if (r->id == id) return r.get();
+  for (auto& r : waiting_)
+    if (r->id == id) return r.get();
+  return nullptr;
+}
+
+std::vector<int64_t> Scheduler::running_ids() const {
+  std::vector<int64_t> ids;
+  for (auto& r : running_) ids.push_back(r->id);
+  return ids;
+}
+
+bool Scheduler::cancel(int64_t id, std::vector<TokenEvent>* events) {
+  for (auto it = waiting_.begin(); it != waiting_.end(); ++it) {
+    if ((*it)->id == id) {
+      if (events) events->push_back({id, -1, true, "cancelled"});
+      waiting_.erase(it);
+      return true;
+    }
+  }
+  for (auto it = running_.begin(); it != running_.end(); ++it) {
+    if ((*it)->id == id) {
+      if (events) events->push_back({id, -1, true, "cancelled"});
+      (*it)->table->release_all();
+      running_.erase(it);
+      return true;
+    }
+  }
+  return false;
+}
+
+void Scheduler::set_drafts(int64_t id, const std::vector<int32_t>& drafts) {
+  for (auto& r : running_)
+    if (r->id == id && r->phase == Phase::Decode) r->drafts = drafts;
+}
+
+void Scheduler::inject_prefill_error(int64_t id, const std::string& msg) { prefill_faults_[id] = msg; }
+
+int Scheduler::prefill_budget(int active_decodes) const {
+  const int room = cfg_.max_num_batched_tokens - active_decodes;
+  if (room <= 0) return 0;
+  if (!cfg_.sla_budget) return room;
+  const double decode_est = cfg_.base_us + cfg_.decode_us_per_seq * active_decodes;
+  double by_sla = (cfg_.sla_itl_us - decode_est) / cfg_.per_token_us;
+  if (by_sla < 0) by_sla = 0;
+  int b = static_cast<int>(std::min<double>(by_sla, room));
+  b = std::max(b, cfg_.chunk_min);
+  b = std::min(b, cfg_.chunk_max);
+  return std::min(b, room);
+}
+
+void Scheduler::radix_pressure() {
+  if (!cfg_.enable_radix) return;
+  const int total = pool_.num_blocks();
+  const int used = total - pool_.num_free();
+  if (used > static_cast<int>(cfg_.radix_high * total)) {
+    const int target = static_cast<int>(cfg_.radix_low * total);
+    radix_.evict(used - target);
+  }
+}
+
+bool Scheduler::ensure_blocks(Request* r, int n_tokens, StepPlan* plan) {
+  std::vector<std::pair<int, int>> cow;
+  if (r->table->advance(n_tokens, &cow)) {
+    for (auto& c : cow) {
+      plan->cow_src.push_back(c.first);
+      plan->cow_dst.push_back(c.second);
+    }
+    return true;
+  }
+  if (cfg_.enable_radix) {
+    const int need = (n_tokens + kTokensPerBlock - 1) / kTokensPerBlock + 1;
+    radix_.evict(need);
+    cow.clear();
+    if (r->table->advance(n_tokens, &cow)) {
+      for (auto& c : cow) {
+        plan->cow_src.push_back(c.first);
+        plan->cow_dst.push_back(c.second);
+      }
+      return true;
+    }
+  }
+  return false;
+}
+
+void Scheduler::preempt(Request* r) {
+  // recompute-style preemption: drop the KV, keep the tokens, go back to the head of the queue
+  ++preemptions_;
+  ++r->preemptions;
+  r->table->release_all();
+  r->computed = 0;
+  r->cached_blocks = 0;
+  r->drafts.clear();
+  r->phase = Phase::Waiting;
+  for (auto it = running_.begin(); it != running_.end(); ++it) {
+    if (it->get() == r) {
+      std::unique_ptr<Request> owned = std::move(*it);
+      running_.erase(it);
+      waiting_.push_front(std::move(owned));
+      return;
+    }
+  }
+}
+
+void Scheduler::offer_to_radix(Request* r) {
+  if (!cfg_.enable_radix) return;
+  const int n_full = std::min<int>(r->computed, static_cast<int>(r->tokens.size())) / kTokensPerBlock;
+  if (n_full <= r->cached_blocks) return;
+  radix_.insert(r->tokens.data(), r->table->blocks().data(), n_full);
+  r->cached_blocks = n_full;
+}
+
+void Scheduler::finish(Request* r) {
+  offer_to_radix(r);
+  r->table->release_all();
+  r->phase = Phase::Finished;
+  for (auto it = running_.begin(); it != running_.end(); ++it) {
+    if (it->get() == r) {
+      running_.erase(it);
+      return;
+    }
+  }
+}
+
+StepPlan Scheduler::schedule() {
+  StepPlan plan;
+  radix_pressure();
+
+  std::sort(running_.begin(), running_.end(),
+            [](const std::unique_ptr<Request>& a, const std::unique_ptr<Request>& b) {
+              return a->arrival < b->arrival;
+            });
+
+  struct Item {
+    Request* r;
+    int len;
+    int kind;  // 0 decode, 1 prefill chunk, 2 verify chunk
+  };
+  std::vector<Item> decodes, chunks;
+
+  // ---- 1. decode phase sequences (oldest first; the youngest is preempted when KV runs out) ----
+  size_t i = 0;
+  while (i < running_.size()) {
+    Request* r = running_[i].get();
+    if (r->phase != Phase::Decode) {
+      ++i;
+      continue;
+    }
+    const int need = 1 + static_cast<int>(r->drafts.size());
+    const int limit = cfg_.max_blocks_per_seq * kTokensPerBlock;
+    if (r->computed + need > limit) r->drafts.clear();
+    const int n = 1 + static_cast<int>(r->drafts.size());
+    bool ok = ensure_blocks(r, n, &plan);
+    while (!ok) {
+      Request* victim = running_.back().get();
+      if (victim == r) {
+        preempt(r);
+        break;
+      }
+      preempt(victim);
+      ok = ensure_blocks(r, n, &plan);
+    }
+    if (!ok) continue;  // r itself was preempted; running_[i] is now the next request
+    if (n == 1)
+      decodes.push_back({r, 1, 0});
+    else
+      chunks.push_back({r, n, 2});
+    ++i;
+  }
+
+  int n_dec_tokens = 0;
+  for (auto& d : decodes) n_dec_tokens += d.len;
+  for (auto& c : chunks) n_dec_tokens += c.len;
+  int budget = prefill_budget(n_dec_tokens);
+
+  // ---- 2. continuing prefill chunks ----
+  for (size_t k = 0; k < running_.size() && budget > 0; ++k) {
+    Request* r = running_[k].get();
+    if (r->phase != Phase::Prefill) continue;
+    const int remaining = static_cast<int>(r->tokens.size()) - r->computed;
+    const int c = std::min(remaining, budget);
+    if (c <= 0) continue;
+    if (!ensure_blocks(r, c, &plan)) continue;
+    chunks.push_back({r, c, 1});
+    budget -= c;
+  }
+
+  // ---- 3. admission of waiting requests ----
+  while (!waiting_.empty() && budget > 0 &&
+         static_cast<int>(running_.size()) < cfg_.max_num_seqs) {
+    Request* r = waiting_.front().get();
+    if (cfg_.enable_radix && r->computed == 0) {
+      RadixCache::Match m = radix_.match(r->tokens.data(), static_cast<int>(r->tokens.size()), true);
+      if (m.tokens > 0) {
+        r->table->adopt_prefix(m.blocks, m.tokens);
+        r->computed = m.tokens;
+        r->prefix_hit = m.tokens;
+        r->cached_blocks = m.tokens / kTokensPerBlock;
+      }
+    }
+    const int remaining = static_cast<int>(r->tokens.size()) - r->computed;
+    const int c = std::min(remaining, budget);
+    if (!ensure_blocks(r, c, &plan)) {
+      r->table->release_all();
+      r->computed = 0;
+      r->cached_blocks = 0;
+      break;  // no memory: stay queued
+    }
+    r->phase = Phase::Prefill;
+    std::unique_ptr<Request> owned = std::move(waiting_.front());
+    waiting_.pop_front();
+    running_.push_back(std::move(owned));
+    chunks.push_back({r, c, 1});
+    budget -= c;
+  }
+
+  // ---- build the flat arrays: decode rows first, then chunk rows ----
+  int max_blocks = 1;
+  for (auto& d : decodes) max_blocks = std::max<int>(max_blocks, d.r->table->blocks().size());
+  for (auto& c : chunks) max_blocks = std::max<int>(max_blocks, c.r->table->blocks().size());
+  plan.max_blocks = max_blocks;
+  plan.n_decode = static_cast<int>(decodes.size());
+  plan.n_prefill = static_cast<int>(chunks.size());
+
+  auto slot_of = [](const Request* r, int pos) -> int64_t {
+    const auto& b = r->table->blocks();
+    return static_cast<int64_t>(b[pos / kTokensPerBlock]) * kTokensPerBlock + pos % kTokensPerBlock;
+  };
+  auto push_table = [&](std::vector<int32_t>* dst, const Request* r) {
+    const auto& b = r->table->blocks();
+    for (int k = 0; k < max_blocks; ++k)
+      dst->push_back(k < static_cast<int>(b.size()) ? b[k] : 0);
+  };
+
+  for (auto& d : decodes) {
+    Request* r = d.r;
+    const int pos = r->computed;
+    plan.token_ids.push_back(r->tokens.back());
+    plan.positions.push_back(pos);
+    plan.slot_mapping.push_back(slot_of(r, pos));
+    plan.decode_ids.push_back(r->id);
+    plan.decode_seq_lens.push_back(pos + 1);
+    push_table(&plan.decode_block_tables, r);
+    plan.logit_rows.push_back(static_cast<int32_t>(plan.token_ids.size()) - 1);
+    plan.logit_req.push_back(r->id);
+  }
+  int s = 0;
+  for (auto& c : chunks) {
+    Request* r = c.r;
+    const int start = static_cast<int>(plan.token_ids.size());
+    plan.prefill_ids.push_back(r->id);
+    plan.q_start.push_back(start);
+    plan.q_lens.push_back(c.len);
+    plan.ctx_lens.push_back(r->computed + c.len);
+    push_table(&plan.prefill_block_tables, r);
+    for (int q0 = 0; q0 < c.len; q0 += kTileQ) {
+      plan.tile_seq.push_back(s);
+      plan.tile_q0.push_back(q0);
+    }
+    for (int j = 0; j < c.len; ++j) {
+      const int pos = r->computed + j;
+      int32_t tok;
+      if (c.kind == 2)
+        tok = j == 0 ? r->tokens.back() : r->drafts[j - 1];
+      else
+        tok = r->tokens[pos];
+      plan.token_ids.push_back(tok);
+      plan.positions.push_back(pos);
+      plan.slot_mapping.push_back(slot_of(r, pos));
+      const bool last = j == c.len - 1;
+      const bool wants_logits =
+          c.kind == 2 || (last && r->computed + c.len == static_cast<int>(r->tokens.size()));
+      if (wants_logits) {
+        plan.logit_rows.push_back(static_cast<int32_t>(plan.token_ids.size()) - 1);
+        plan.logit_req.push_back(r->id);
+      }
+    }
+    if (c.kind == 1) plan.prefill_tokens += c.len;
+    ++s;
+  }
+  plan.n_tokens = static_cast<int>(plan.token_ids.size());
+  return plan;
+}
+
+std::vector<TokenEvent> Scheduler::update(const StepPlan& plan, const std::vector<int32_t>& sampled) {
+  std::vector<TokenEvent> events;
+  if (sampled.size() != plan.logit_rows.size())
+    throw std::invalid_argument("update: one sampled token per logits row expected");
+
+  auto find_running = [&](int64_t id) -> Request* {
+    for (auto& r : running_)
+      if (r->id == id) return r.get();
+    return nullptr;
+  };
+  auto emit = [&](Request* r, int32_t tok) -> bool {
+    // returns true when the request finished with this token
+    r->tokens.push_back(tok);
+    bool stop = false;
+    if (!r->ignore_eos)
+      for (int32_t sid : r->stop_ids) stop |= sid == tok;
+    std::string reason;
+    if (stop)
+      reason = "stop";
+    else if (r->generated() >= r->max_new_tokens)
+      reason = "length";
+    else if (static_cast<int>(r->tokens.size()) >= cfg_.max_blocks_per_seq * kTokensPerBlock)
+      reason = "length";
+    events.push_back({r->id, tok, !reason.empty(), reason});
+    return !reason.empty();
+  };
+
+  size_t li = 0;  // cursor into logit rows
+  for (int d = 0; d < plan.n_decode; ++d) {
+    Request* r = find_running(plan.decode_ids[d]);
+    const int32_t tok = sampled[li++];
+    if (r == nullptr) continue;  // cancelled meanwhile
+    r->computed += 1;
+    r->table->commit();
+    if (emit(r, tok)) finish(r);
+  }
+  for (int c = 0; c < plan.n_prefill; ++c) {
+    const int64_t id = plan.prefill_ids[c];
+    const int len = plan.q_lens[c];
+    // logits rows that belong to this chunk
+    const int row_lo = plan.q_start[c], row_hi = row_lo + len;
+    size_t first = li;
+    while (li < plan.logit_rows.size() && plan.logit_rows[li] >= row_lo &&
+           plan.logit_rows[li] < row_hi)
+      ++li;
+    const int n_logits = static_cast<int>(li - first);
+    Request* r = find_running(id);
+    if (r == nullptr) continue;
+    auto fault = prefill_faults_.find(id);
+    if (fault != prefill_faults_.end() && r->phase == Phase::Prefill) {
+      events.push_back({id, -1, true, "prefill_error: " + fault->second});
+      prefill_faults_.erase(fault);
+      r->table->release_all();
+      for (auto it = running_.begin(); it != running_.end(); ++it)
+        if (it->get() == r) {
+          running_.erase(it);
+          break;
+        }
+      continue;
+    }
+    if (r->phase == Phase::Prefill) {
+      r->computed += len;
+      r->table->commit();
+      offer_to_radix(r);
+      if (n_logits == 1) {
+        r->phase = Phase::Decode;
+        if (emit(r, sampled[first])) finish(r);
+      }
+    } else {
+      // speculative verify: rows = [last token, draft_0 .. draft_{k-1}]
+      const int k = len - 1;
+      int accepted = 0;
+      while (accepted < k && accepted < static_cast<int>(r->drafts.size()) &&
+             r->drafts[accepted] == sampled[first + accepted])
+        ++accepted;
+      r->drafts.clear();
+      bool done = false;
+      int emitted = 0;
+      for (int j = 0; j <= accepted && !done; ++j) {
+        done = emit(r, sampled[first + j]);
+        ++emitted;
+      }
+      // KV is valid for the input token and for every accepted draft that was emitted
+      r->computed += emitted;
+      r->table->rewind_to(r->computed);
+      r->table->commit();
+      if (done) finish(r);
+    }
+  }
+  return events;
+}
+
+}  // namespace oxb

@@ -1,0 +1,48 @@
+// Parameter blocks of the paged attention kernels.
+// KV cache layout (per layer): [num_blocks, Hkv, 16 tokens, head_dim] bf16 for K and for V.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace oxb {
+
+struct DecodeAttnParams {
+  const __nv_bfloat16* q;  // [B, Hq, D], row stride q_stride (elements)
+  long long q_stride;
+  const __nv_bfloat16* k_cache;
+  const __nv_bfloat16* v_cache;
+  const int* block_tables;     // [B, max_blocks]
+  const int* seq_lens;         // [B] context length including the current token
+  const int* pages_per_split;  // device scalar, >= 1
+  float* part_o;               // [B, Hq, max_splits, D]
+  float* part_ml;              // [B, Hq, max_splits, 2]  (running max in log2 units, sum)
+  __nv_bfloat16* out;          // [B, Hq*D], row stride out_stride
+  long long out_stride;
+  int max_blocks, Hq, Hkv, max_splits, window;
+  float scale_log2;  // softmax scale * log2(e)
+};
+
+void launch_paged_decode(const DecodeAttnParams& p, int batch, int head_dim, cudaStream_t stream);
+
+struct PrefillAttnParams {
+  const __nv_bfloat16* q;  // [T, Hq, D] ragged over sequences, row stride q_stride
+  long long q_stride;
+  const __nv_bfloat16* k_cache;
+  const __nv_bfloat16* v_cache;
+  const int* block_tables;  // [n_seqs, max_blocks]
+  const int* tile_seq;      // [n_tiles] sequence of each 64-row query tile
+  const int* tile_q0;       // [n_tiles] first query index of the tile inside its sequence
+  const int* q_start;       // [n_seqs] first row of the sequence in q
+  const int* q_lens;        // [n_seqs] query tokens of this chunk
+  const int* ctx_lens;      // [n_seqs] context length after this chunk (KV tokens in the cache)
+  __nv_bfloat16* out;       // [T, Hq*D], row stride out_stride
+  long long out_stride;
+  int max_blocks, Hq, Hkv, window;
+  float scale_log2;
+};
+
+void launch_paged_prefill(const PrefillAttnParams& p, int n_tiles, int head_dim,
+                          cudaStream_t stream);
+
+}  // namespace oxb

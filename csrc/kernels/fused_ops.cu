@@ -1,0 +1,555 @@
+// Fused elementwise / normalisation kernels between the GEMMs (sm_100a).
+//
+//  finalize_norm : tail of the fused GEMM->reduce-scatter. Waits (bounded) until every
+//                  contribution has arrived in this rank's fp32 accumulator, then per
+//                  row: h = acc + bias + residual; residual_out = h; y = RMSNorm(h) * w;
+//                  y is stored into the all-gather buffer of EVERY rank (peer stores over
+//                  NVLink) and a per-source counter on each destination is bumped with a
+//                  system-scope release. The accumulator is zeroed for its next use.
+//                  With one rank and no counters it is residual-add + RMSNorm.
+//                  (reference: fused_residual_rmsnorm_q8_1_cuda_kernel, norms_rope.cu:190-280;
+//                   rms_norm_f32_kernel, norms_rope.cu:37-89)
+//  qkv_rope_append: bias + optional per-head QK RMSNorm + half-split RoPE + write of K and V
+//                  into the paged cache through a slot mapping, Q to a dense buffer.
+//                  (reference: rope_continuous_batch_kernel megakernel_ops.cu:359-427,
+//                   fused_qknorm_rope_batch_kernel norms_batch.cu:56-131,
+//                   write_v_cache_continuous_batch_kernel megakernel_ops.cu:429-461,
+//                   fused_paged_kv_write_fp16_kernel vec_ops_activations.cu:181-201)
+//  swiglu        : SiLU(gate) * up or tanh-GELU(gate) * up (vec_ops_activations.cu:118-163).
+//  embed_gather, fwht128 (fwht.cu:10-38), kv_block_copy, softcap.
+#include "fused_ops.cuh"
+
+#include "../common/sm100.cuh"
+
+namespace oxb {
+
+namespace {
+
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add_u32(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  float r = lane < nw ? scratch[lane] : 0.f;
+  r = warp_sum(r);
+  __syncthreads();
+  return r;
+}
+
+constexpr int kNormThreads = 256;
+
+__global__ void __launch_bounds__(kNormThreads) finalize_norm_kernel(const FinalizeNormParams p) {
+  extern __shared__ float s_h[];  // N floats
+  __shared__ float s_red[32];
+  __shared__ int s_ok;
+  const int row = blockIdx.x;
+  const int N = p.N;
+
+  if (p.arrive != nullptr) {
+    if (threadIdx.x == 0) {
+      int ok = 1;
+      uint32_t it = 0;
+      while (ld_acquire_sys_u32(p.arrive) < p.expected) {
+        if (++it > OXB_SPIN_LIMIT) {
+          atomicExch(p.status, kStatusPeerFlagTimeout);
+          ok = 0;
+          break;
+        }
+      }
+      s_ok = ok;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+  }
+
+  float ss = 0.f;
+  const long long roff = static_cast<long long>(row) * N;
+  for (int c = threadIdx.x * 8; c < N; c += kNormThreads * 8) {
+    float h[8];
+    if (p.acc != nullptr) {
+      float4* a = reinterpret_cast<float4*>(p.acc + roff + c);
+      const float4 x0 = __ldcg(a), x1 = __ldcg(a + 1);
+      h[0] = x0.x; h[1] = x0.y; h[2] = x0.z; h[3] = x0.w;
+      h[4] = x1.x; h[5] = x1.y; h[6] = x1.z; h[7] = x1.w;
+      const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+      __stcg(a, z);
+      __stcg(a + 1, z);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) h[j] = 0.f;
+    }
+    if (p.bias != nullptr) {
+      const uint4 b = *reinterpret_cast<const uint4*>(p.bias + c);
+      const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) h[j] += __bfloat162float(bb[j]);
+    }
+    if (p.residual_in != nullptr) {
+      const uint4 r = *reinterpret_cast<const uint4*>(p.residual_in + roff + c);
+      const __nv_bfloat16* rr = reinterpret_cast<const __nv_bfloat16*>(&r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) h[j] += __bfloat162float(rr[j]);
+    }
+    if (p.residual_out != nullptr) {
+      uint4 o;
+      o.x = pack_bf16x2(h[0], h[1]);
+      o.y = pack_bf16x2(h[2], h[3]);
+      o.z = pack_bf16x2(h[4], h[5]);
+      o.w = pack_bf16x2(h[6], h[7]);
+      *reinterpret_cast<uint4*>(p.residual_out + roff + c) = o;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      ss += h[j] * h[j];
+      s_h[c + j] = h[j];
+    }
+  }
+  float inv = 1.f;
+  if (p.norm_w != nullptr) {
+    const float tot = block_sum(ss, s_red);
+    inv = rsqrtf(tot / static_cast<float>(N) + p.eps);
+  }
+  const long long ooff = (p.out_row_off + row) * static_cast<long long>(N);
+  for (int c = threadIdx.x * 8; c < N; c += kNormThreads * 8) {
+    float y[8];
+    if (p.norm_w != nullptr) {
+      const uint4 w = *reinterpret_cast<const uint4*>(p.norm_w + c);
+      const __nv_bfloat16* ww = reinterpret_cast<const __nv_bfloat16*>(&w);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] = s_h[c + j] * inv * (__bfloat162float(ww[j]) + p.w_offset);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] = s_h[c + j];
+    }
+    if (p.router_w != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s_h[c + j] = y[j];  // kept for the router and the dispatch
+      continue;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(y[0], y[1]);
+    o.y = pack_bf16x2(y[2], y[3]);
+    o.z = pack_bf16x2(y[4], y[5]);
+    o.w = pack_bf16x2(y[6], y[7]);
+#pragma unroll
+    for (int d = 0; d < kMaxPeers; ++d)
+      if (d < p.n_dst) *reinterpret_cast<uint4*>(p.out[d] + ooff + c) = o;
+  }
+
+  if (p.router_w != nullptr) {
+    // ---- router: logits over all experts, top-k, softmax over the selected logits ----
+    __shared__ float s_logit[64];
+    __shared__ int s_sel[8];
+    __shared__ float s_wgt[8];
+    __shared__ int s_slot[8];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int e = warp; e < p.n_experts; e += nw) {
+      const __nv_bfloat16* wr = p.router_w + static_cast<long long>(e) * N;
+      float s = 0.f;
+      for (int c = lane * 8; c < N; c += 32 * 8) {
+        const uint4 w = *reinterpret_cast<const uint4*>(wr + c);
+        const __nv_bfloat16* ww = reinterpret_cast<const __nv_bfloat16*>(&w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += s_h[c + j] * __bfloat162float(ww[j]);
+      }
+      s = warp_sum(s);
+      if (lane == 0) s_logit[e] = s;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float mx = -INFINITY;
+      for (int k = 0; k < p.top_k; ++k) {
+        int best = 0;
+        float bv = -INFINITY;
+        for (int e = 0; e < p.n_experts; ++e) {
+          bool taken = false;
+          for (int t = 0; t < k; ++t) taken |= s_sel[t] == e;
+          if (!taken && s_logit[e] > bv) {
+            bv = s_logit[e];
+            best = e;
+          }
+        }
+        s_sel[k] = best;
+        s_wgt[k] = bv;
+        mx = fmaxf(mx, bv);
+      }
+      float sum = 0.f;
+      for (int k = 0; k < p.top_k; ++k) {
+        s_wgt[k] = __expf(s_wgt[k] - mx);
+        sum += s_wgt[k];
+      }
+      for (int k = 0; k < p.top_k; ++k) s_wgt[k] = s_wgt[k] / sum * p.routed_scale;
+    }
+    __syncthreads();
+    // ---- claim a slab row on each selected expert's owner (remote atomic) and record the way home
+    if (threadIdx.x < p.top_k) {
+      const int k = threadIdx.x;
+      const int e = s_sel[k];
+      const int o = e / p.experts_per_rank, el = e - o * p.experts_per_rank;
+      uint32_t* cnt = nullptr;
+      MoeRowMeta* meta = nullptr;
+#pragma unroll
+      for (int d = 0; d < kMaxPeers; ++d)
+        if (d == o) {
+          cnt = p.slab_cnt[d];
+          meta = p.meta[d];
+        }
+      int slot = static_cast<int>(atomicAdd(cnt + el, 1u));
+      if (slot >= p.cap) {
+        atomicExch(p.status, kStatusBadIndex);
+        slot = -1;
+      } else {
+        MoeRowMeta m;
+        m.rank = p.my_rank;
+        m.row = row;
+        m.weight = s_wgt[k];
+        m.pad = 0;
+        meta[static_cast<long long>(el) * p.cap + slot] = m;
+      }
+      s_slot[k] = slot;
+    }
+    __syncthreads();
+    for (int k = 0; k < p.top_k; ++k) {
+      const int slot = s_slot[k];
+      if (slot < 0) continue;
+      const int e = s_sel[k];
+      const int o = e / p.experts_per_rank, el = e - o * p.experts_per_rank;
+      __nv_bfloat16* base = nullptr;
+#pragma unroll
+      for (int d = 0; d < kMaxPeers; ++d)
+        if (d == o) base = p.slab[d];
+      __nv_bfloat16* drow = base + (static_cast<long long>(el) * p.cap + slot) * N;
+      for (int c = threadIdx.x * 8; c < N; c += kNormThreads * 8) {
+        uint4 o4;
+        o4.x = pack_bf16x2(s_h[c], s_h[c + 1]);
+        o4.y = pack_bf16x2(s_h[c + 2], s_h[c + 3]);
+        o4.z = pack_bf16x2(s_h[c + 4], s_h[c + 5]);
+        o4.w = pack_bf16x2(s_h[c + 6], s_h[c + 7]);
+        *reinterpret_cast<uint4*>(drow + c) = o4;
+      }
+    }
+  }
+
+  const bool signal = p.out_flag[0] != nullptr;
+  if (signal || p.arrive != nullptr) {
+    if (signal) __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      if (signal) {
+#pragma unroll
+        for (int d = 0; d < kMaxPeers; ++d)
+          if (d < p.n_dst) red_release_sys_add_u32(p.out_flag[d], 1u);
+      }
+      if (p.arrive != nullptr) {
+        // every CTA has passed its wait once the ticket is full: re-arm the arrival counter
+        const uint32_t old = atomicAdd(p.ticket, 1u);
+        if (old == gridDim.x - 1) {
+          *const_cast<uint32_t*>(p.arrive) = 0;
+          __threadfence();
+          *p.ticket = 0;
+        }
+      }
+    }
+  }
+}
+
+// One CTA per token. Thread i handles rotation pair (d, d + D/2) of some head.
+__global__ void __launch_bounds__(256) qkv_rope_append_kernel(const QkvRopeParams p) {
+  extern __shared__ float s_row[];  // (Hq + 2 Hkv) * D floats
+  __shared__ float s_ssq[160];      // per-head sum of squares (Hq + Hkv <= 160)
+  const int tok = blockIdx.x;
+  const int D = p.D, half = D >> 1;
+  const int W = (p.Hq + 2 * p.Hkv) * D;
+  const long long roff = static_cast<long long>(tok) * W;
+
+  for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+    float v[4];
+    if (p.acc_f32 != nullptr) {
+      float4* a = reinterpret_cast<float4*>(const_cast<float*>(p.acc_f32) + roff + c);
+      const float4 x = __ldcg(a);
+      v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+      __stcg(a, make_float4(0.f, 0.f, 0.f, 0.f));
+    } else {
+      const uint2 x = *reinterpret_cast<const uint2*>(p.qkv_bf16 + roff + c);
+      const __nv_bfloat16* xx = reinterpret_cast<const __nv_bfloat16*>(&x);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = __bfloat162float(xx[j]);
+    }
+    if (p.bias != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] += __bfloat162float(p.bias[c + j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s_row[c + j] = v[j];
+  }
+  __syncthreads();
+
+  const int n_rot_heads = p.Hq + p.Hkv;
+  const bool qk_norm = p.q_norm_w != nullptr;
+  if (qk_norm) {
+    // one warp per head computes the head's mean square
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int h = warp; h < n_rot_heads; h += nw) {
+      float ss = 0.f;
+      for (int d = lane; d < D; d += 32) {
+        const float x = s_row[h * D + d];
+        ss += x * x;
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) s_ssq[h] = rsqrtf(ss / static_cast<float>(D) + p.norm_eps);
+    }
+    __syncthreads();
+  }
+
+  const int pos = p.positions[tok];
+  const long long slot = p.slot_mapping[tok];
+  const bool store_kv = slot >= 0 && slot < p.num_slots;
+  if (slot >= p.num_slots && threadIdx.x == 0) atomicExch(p.status, kStatusBadIndex);
+  const long long blk = slot >> 4;
+  const int off = static_cast<int>(slot & 15);
+
+  // rotate Q and K heads
+  for (int i = threadIdx.x; i < n_rot_heads * half; i += blockDim.x) {
+    const int h = i / half, d = i - h * half;
+    float x0 = s_row[h * D + d], x1 = s_row[h * D + d + half];
+    if (qk_norm) {
+      const __nv_bfloat16* w = h < p.Hq ? p.q_norm_w : p.k_norm_w;
+      const float r = s_ssq[h];
+      x0 = x0 * r * (__bfloat162float(w[d]) + p.norm_w_offset);
+      x1 = x1 * r * (__bfloat162float(w[d + half]) + p.norm_w_offset);
+    }
+    float sn, cs;
+    sincosf(static_cast<float>(pos) * p.inv_freq[d], &sn, &cs);
+    sn *= p.rope_mscale;
+    cs *= p.rope_mscale;
+    const float y0 = x0 * cs - x1 * sn;
+    const float y1 = x1 * cs + x0 * sn;
+    if (h < p.Hq) {
+      __nv_bfloat16* q = p.q_out + static_cast<long long>(tok) * p.Hq * D + h * D;
+      q[d] = __float2bfloat16(y0);
+      q[d + half] = __float2bfloat16(y1);
+    } else if (store_kv) {
+      const int kh = h - p.Hq;
+      __nv_bfloat16* k = p.k_cache + ((blk * p.Hkv + kh) * 16 + off) * D;
+      k[d] = __float2bfloat16(y0);
+      k[d + half] = __float2bfloat16(y1);
+    }
+  }
+  if (store_kv) {
+    const float* vrow = s_row + (p.Hq + p.Hkv) * D;
+    for (int i = threadIdx.x; i < p.Hkv * D; i += blockDim.x) {
+      const int kh = i / D, d = i - kh * D;
+      p.v_cache[((blk * p.Hkv + kh) * 16 + off) * D + d] = __float2bfloat16(vrow[i]);
+    }
+  }
+}
+
+__global__ void swiglu_kernel(const SwigluParams p) {
+  const long long total = static_cast<long long>(p.M) * p.I / 4;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = i * 4;
+    const long long m = e / p.I;
+    const int c = static_cast<int>(e - m * p.I);
+    float gt[4], up[4];
+    if (p.acc_f32 != nullptr) {
+      float4* ga = reinterpret_cast<float4*>(const_cast<float*>(p.acc_f32) + m * 2 * p.I + c);
+      float4* ua = reinterpret_cast<float4*>(const_cast<float*>(p.acc_f32) + m * 2 * p.I + p.I + c);
+      const float4 gv = __ldcg(ga), uv = __ldcg(ua);
+      gt[0] = gv.x; gt[1] = gv.y; gt[2] = gv.z; gt[3] = gv.w;
+      up[0] = uv.x; up[1] = uv.y; up[2] = uv.z; up[3] = uv.w;
+      const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+      __stcg(ga, z);
+      __stcg(ua, z);
+    } else {
+      const uint2 gv = *reinterpret_cast<const uint2*>(p.gu_bf16 + m * 2 * p.I + c);
+      const uint2 uv = *reinterpret_cast<const uint2*>(p.gu_bf16 + m * 2 * p.I + p.I + c);
+      const __nv_bfloat16* gg = reinterpret_cast<const __nv_bfloat16*>(&gv);
+      const __nv_bfloat16* uu = reinterpret_cast<const __nv_bfloat16*>(&uv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        gt[j] = __bfloat162float(gg[j]);
+        up[j] = __bfloat162float(uu[j]);
+      }
+    }
+    float y[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float a;
+      if (p.act == 0) {
+        a = gt[j] / (1.f + __expf(-gt[j]));
+      } else {
+        const float x = gt[j];
+        a = 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+      }
+      y[j] = a * up[j];
+    }
+    uint2 o;
+    o.x = pack_bf16x2(y[0], y[1]);
+    o.y = pack_bf16x2(y[2], y[3]);
+    *reinterpret_cast<uint2*>(p.out + m * p.I + c) = o;
+  }
+}
+
+__global__ void embed_gather_kernel(const int* tokens, const __nv_bfloat16* table,
+                                    __nv_bfloat16* out, int N, int vocab, float scale,
+                                    int vocab_start) {
+  const int row = blockIdx.x;
+  const int tok = tokens[row] - vocab_start;
+  const bool valid = tok >= 0 && tok < vocab;  // vocab-parallel: rows of other shards give zeros
+  const __nv_bfloat16* src = table + static_cast<long long>(valid ? tok : 0) * N;
+  __nv_bfloat16* dst = out + static_cast<long long>(row) * N;
+  for (int c = threadIdx.x * 8; c < N; c += blockDim.x * 8) {
+    uint4 v = valid ? *reinterpret_cast<const uint4*>(src + c) : make_uint4(0, 0, 0, 0);
+    if (scale != 1.f && valid) {
+      __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) e[j] = __float2bfloat16(__bfloat162float(e[j]) * scale);
+    }
+    *reinterpret_cast<uint4*>(dst + c) = v;
+  }
+}
+
+__global__ void cast_acc_bf16_kernel(float* acc, const __nv_bfloat16* bias, __nv_bfloat16* out,
+                                     int M, int N, long long ldo) {
+  const long long total = static_cast<long long>(M) * N / 4;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = i * 4;
+    const long long m = e / N;
+    const int c = static_cast<int>(e - m * N);
+    float4* a = reinterpret_cast<float4*>(acc + e);
+    float4 v = __ldcg(a);
+    __stcg(a, make_float4(0.f, 0.f, 0.f, 0.f));
+    if (bias != nullptr) {
+      v.x += __bfloat162float(bias[c]);
+      v.y += __bfloat162float(bias[c + 1]);
+      v.z += __bfloat162float(bias[c + 2]);
+      v.w += __bfloat162float(bias[c + 3]);
+    }
+    uint2 o;
+    o.x = pack_bf16x2(v.x, v.y);
+    o.y = pack_bf16x2(v.z, v.w);
+    *reinterpret_cast<uint2*>(out + m * ldo + c) = o;
+  }
+}
+
+// 128-point Walsh-Hadamard transform per block of 128 floats, scaled by 1/sqrt(128).
+__global__ void __launch_bounds__(128) fwht128_kernel(float* x, long long n_blocks) {
+  __shared__ float s[128];
+  for (long long b = blockIdx.x; b < n_blocks; b += gridDim.x) {
+    s[threadIdx.x] = x[b * 128 + threadIdx.x];
+    __syncthreads();
+#pragma unroll
+    for (int h = 1; h < 128; h <<= 1) {
+      const int i = threadIdx.x;
+      const float a = s[i & ~h], c = s[i | h];
+      __syncthreads();
+      s[i] = (i & h) ? a - c : a + c;
+      __syncthreads();
+    }
+    x[b * 128 + threadIdx.x] = s[threadIdx.x] * 0.08838834764831845f;
+    __syncthreads();
+  }
+}
+
+// Copies whole KV blocks (copy-on-write of a shared partial block, context-shift compaction).
+__global__ void kv_block_copy_kernel(__nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
+                                     const int* src_blocks, const int* dst_blocks,
+                                     long long block_elems) {
+  const int pair = blockIdx.x;
+  const long long s = static_cast<long long>(src_blocks[pair]) * block_elems;
+  const long long d = static_cast<long long>(dst_blocks[pair]) * block_elems;
+  __nv_bfloat16* base = blockIdx.y == 0 ? k_cache : v_cache;
+  for (long long i = threadIdx.x * 8; i < block_elems; i += blockDim.x * 8)
+    *reinterpret_cast<uint4*>(base + d + i) = *reinterpret_cast<const uint4*>(base + s + i);
+}
+
+__global__ void softcap_kernel(float* x, long long n, float cap) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    x[i] = cap * tanhf(x[i] / cap);
+}
+
+}  // namespace
+
+void launch_finalize_norm(const FinalizeNormParams& p, cudaStream_t stream) {
+  if (p.rows <= 0) return;
+  const size_t smem = static_cast<size_t>(p.N) * sizeof(float);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaFuncSetAttribute(finalize_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         static_cast<int>(smem));
+    configured = smem;
+  }
+  finalize_norm_kernel<<<p.rows, kNormThreads, smem, stream>>>(p);
+}
+
+void launch_qkv_rope_append(const QkvRopeParams& p, cudaStream_t stream) {
+  if (p.M <= 0) return;
+  const size_t smem = static_cast<size_t>(p.Hq + 2 * p.Hkv) * p.D * sizeof(float);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaFuncSetAttribute(qkv_rope_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         static_cast<int>(smem));
+    configured = smem;
+  }
+  qkv_rope_append_kernel<<<p.M, 256, smem, stream>>>(p);
+}
+
+void launch_swiglu(const SwigluParams& p, cudaStream_t stream) {
+  const long long total = static_cast<long long>(p.M) * p.I / 4;
+  if (total <= 0) return;
+  int blocks = static_cast<int>((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  swiglu_kernel<<<blocks, 256, 0, stream>>>(p);
+}
+
+void launch_embed_gather(const int* tokens, const __nv_bfloat16* table, __nv_bfloat16* out, int M,
+                         int N, int vocab, float scale, int vocab_start, cudaStream_t stream) {
+  if (M <= 0) return;
+  embed_gather_kernel<<<M, 256, 0, stream>>>(tokens, table, out, N, vocab, scale, vocab_start);
+}
+
+void launch_cast_acc_bf16(float* acc, const __nv_bfloat16* bias, __nv_bfloat16* out, int M, int N,
+                          long long ldo, cudaStream_t stream) {
+  const long long total = static_cast<long long>(M) * N / 4;
+  if (total <= 0) return;
+  int blocks = static_cast<int>((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  cast_acc_bf16_kernel<<<blocks, 256, 0, stream>>>(acc, bias, out, M, N, ldo);
+}
+
+void launch_fwht128(float* x, long long n_blocks, cudaStream_t stream) {
+  if (n_blocks <= 0) return;
+  int blocks = n_blocks > 148 * 8 ? 148 * 8 : static_cast<int>(n_blocks);
+  fwht128_kernel<<<blocks, 128, 0, stream>>>(x, n_blocks);
+}
+
+void launch_kv_block_copy(__nv_bfloat16* k_cache, __nv_bfloat16* v_cache, const int* src_blocks,
+                          const int* dst_blocks, int n_pairs, long long block_elems,
+                          cudaStream_t stream) {
+  if (n_pairs <= 0) return;
+  kv_block_copy_kernel<<<dim3(n_pairs, 2), 256, 0, stream>>>(k_cache, v_cache, src_blocks,
+                                                            dst_blocks, block_elems);
+}
+
+void launch_softcap(float* logits, long long n, float cap, cudaStream_t stream) {
+  if (n <= 0) return;
+  int blocks = static_cast<int>((n + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  softcap_kernel<<<blocks, 256, 0, stream>>>(logits, n, cap);
+}
+
+}  // namespace oxb

@@ -1,0 +1,62 @@
+// Parameters of the tcgen05 bf16 GEMM  C[g][M,N] (+)= A[g][M,K] * B[g][N,K]^T  (g = group /
+// expert index, 1 for a plain GEMM) and of the routed-reduction epilogue that turns it into a
+// fused GEMM -> reduce-scatter (dense TP) or grouped-GEMM -> combine (MoE EP).
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace oxb {
+
+constexpr int kMaxRanks = 8;
+
+enum GemmEpilogue : int {
+  kEpiStoreBf16 = 0,   // C[row, col] = bf16(acc + bias[col])
+  kEpiRedF32 = 1,      // dst[owner][row', col] += w * acc   (fp32 red; local or peer memory)
+  kEpiStoreF32 = 2,    // C[row, col] = acc + bias[col]      (fp32)
+  kEpiSwigluBf16 = 3,  // C[row, n0/2 + j] = act(acc[j]) * acc[BN/2 + j]; weights interleaved per tile
+};
+
+// Per-row routing record of the MoE combine: which rank / row / weight a slab row goes back to.
+struct RowMeta {
+  int rank;
+  int row;
+  float weight;
+  int pad;
+};
+
+struct GemmParams {
+  int M, N, K;        // M = rows per group when group_counts == nullptr
+  int kb_per_split;   // 64-wide k blocks handled by one CTA along grid.z
+  int epi;
+  int act;            // kEpiSwigluBf16: 0 = SiLU, 1 = tanh-GELU
+  void* C;            // kEpiStoreBf16 / kEpiStoreF32 / kEpiSwigluBf16
+  long long ldc;
+  long long c_group_stride;   // elements between groups of C
+  const __nv_bfloat16* bias;  // optional, length N (per group: bias + g * N)
+  // --- grouped (MoE) mode ---
+  const uint32_t* group_counts;  // [n_groups] rows used in each group (device); nullptr = dense
+  int n_groups;
+  const RowMeta* row_meta;       // [n_groups, meta_group_stride] routing of each slab row
+  long long meta_group_stride;
+  // --- routed fp32 reduction (split-K on one GPU; reduce-scatter / combine across GPUs) ---
+  float* dst[kMaxRanks];        // accumulator of owner o (a peer mapping when o != this rank)
+  uint32_t* arrive[kMaxRanks];  // counter on owner o, bumped once when this whole GEMM has landed
+  uint32_t* done_ticket;        // local ticket that finds the last CTA (nullptr = no signalling)
+  uint32_t* reset_on_done;      // optional local words zeroed by the last CTA before signalling
+  int n_reset;
+  int rows_per_owner;           // dense: row r belongs to owner r / rows_per_owner
+  int n_owners;
+  // --- wait on the A operand (rows written into local memory by peers) ---
+  const uint32_t* ag_flags;  // local counters, one per source rank; nullptr = A is ready
+  uint32_t ag_expected;      // value each needed counter must reach
+  int ag_rows_per_src;
+  int ag_n_src;
+  uint32_t* ag_ticket;       // local ticket used to re-arm the counters after the last CTA passed
+  int* status;               // error word (0 = ok)
+};
+
+void launch_gemm_bf16(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int bn,
+                      int m_tiles, int splits, cudaStream_t stream);
+
+}  // namespace oxb

@@ -1,0 +1,219 @@
+"""Python front-ends of the sm_100a kernels.
+
+Every function here launches a hand-written kernel from ``csrc/kernels``; there is no PyTorch
+fallback on this path. If the CUDA extension cannot be loaded the import error propagates, so a
+GPU box never runs these ops on a silent eager substitute.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from .._build import cuda_ext
+
+EPI_STORE_BF16 = 0
+EPI_RED_F32 = 1
+EPI_STORE_F32 = 2
+EPI_SWIGLU_BF16 = 3
+
+STATUS_NAMES = {
+    0: "ok",
+    1: "mbarrier timeout (TMA producer)",
+    2: "mbarrier timeout (MMA issuer)",
+    3: "mbarrier timeout (epilogue)",
+    4: "peer flag timeout",
+    5: "index out of range",
+}
+
+# number of kernel launches issued through this module (bench.py reports it)
+launch_count = 0
+
+
+def _ext():
+    return cuda_ext()
+
+
+def _bump(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
+
+_status: dict[int, torch.Tensor] = {}
+
+
+def status_word(device: torch.device | int | None = None) -> torch.Tensor:
+    """Per-device int32 error word that kernels set when a bounded wait expires."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return _status[key]
+
+
+def check_status(device=None) -> None:
+    """Host check of the kernel status word (one D2H copy); raises on a recorded timeout."""
+    from ..errors import CollectiveTimeout, EngineError
+
+    code = int(status_word(device).item())
+    if code != 0:
+        status_word(device).zero_()
+        msg = STATUS_NAMES.get(code, f"code {code}")
+        if code == 4:
+            raise CollectiveTimeout(f"device wait expired: {msg}")
+        raise EngineError(f"kernel reported: {msg}")
+
+
+def pick_bn(n: int, m_tiles: int = 1) -> int:
+    """Output-tile width: wide tiles when there are plenty, narrow ones to fill 148 SMs."""
+    if n % 256 == 0 and (n // 256) * m_tiles >= 148:
+        return 256
+    if (n + 127) // 128 * m_tiles >= 100:
+        return 128
+    return 64 if n >= 64 and n % 64 == 0 else 128
+
+
+def pick_splits(m: int, n: int, k: int, bn: int) -> int:
+    """Split-K factor so that small GEMMs still occupy most SMs (needs the fp32 red epilogue)."""
+    tiles = ((m + 127) // 128) * ((n + bn - 1) // bn)
+    kb = (k + 63) // 64
+    if tiles >= 120 or kb < 8:
+        return 1
+    s = min(max(1, 148 // tiles), max(1, kb // 4), 16)
+    return s
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+         epi: int = EPI_STORE_BF16, bias: Optional[torch.Tensor] = None,
+         dst_ptrs: Sequence[int] = (), arrive_ptrs: Sequence[int] = (),
+         done_ticket: Optional[torch.Tensor] = None, reset_on_done: Optional[torch.Tensor] = None,
+         rows_per_owner: int = 0, group_counts: Optional[torch.Tensor] = None,
+         row_meta: Optional[torch.Tensor] = None, ag_flags: Optional[torch.Tensor] = None,
+         ag_expected: int = 0, ag_rows_per_src: int = 0, ag_ticket: Optional[torch.Tensor] = None,
+         bn: int = 0, splits: int = 1, act: int = 0, m_tiles: int = 0) -> Optional[torch.Tensor]:
+    """tcgen05 GEMM  out = a @ w^T  (bf16 in, fp32 accumulate). See csrc/kernels/gemm_bf16.cu."""
+    M = a.shape[-2]
+    N = w.shape[-2]
+    if bn == 0:
+        bn = pick_bn(N, (M + 127) // 128)
+    if out is None and epi != EPI_RED_F32:
+        n_out = N // 2 if epi == EPI_SWIGLU_BF16 else N
+        dt = torch.float32 if epi == EPI_STORE_F32 else torch.bfloat16
+        out = torch.empty(*a.shape[:-1], n_out, dtype=dt, device=a.device)
+    _ext().gemm_bf16(a, w, epi, out, bias, list(dst_ptrs), list(arrive_ptrs), done_ticket,
+                     reset_on_done, rows_per_owner, group_counts, row_meta, ag_flags, ag_expected,
+                     ag_rows_per_src, ag_ticket, status_word(a.device), bn, splits, act, m_tiles)
+    _bump()
+    return out
+
+
+def paged_decode(q, k_cache, v_cache, block_tables, seq_lens, pages_per_split, part_o, part_ml, out,
+                 *, batch: int, max_splits: int, window: int = 0, scale: float) -> None:
+    _ext().paged_decode(q, k_cache, v_cache, block_tables, seq_lens, pages_per_split, part_o, part_ml,
+                        out, batch, max_splits, window, scale)
+    _bump(2)
+
+
+def paged_prefill(q, k_cache, v_cache, block_tables, tile_seq, tile_q0, q_start, q_lens, ctx_lens, out,
+                  *, n_tiles: int, window: int = 0, scale: float) -> None:
+    _ext().paged_prefill(q, k_cache, v_cache, block_tables, tile_seq, tile_q0, q_start, q_lens,
+                         ctx_lens, out, n_tiles, window, scale)
+    _bump()
+
+
+def finalize_norm(*, rows: int, n: int, acc=None, arrive=None, expected: int = 0, ticket=None,
+                  residual_in=None, residual_out=None, bias=None, norm_w=None, eps: float = 1e-5,
+                  w_offset: float = 0.0, out_ptrs: Sequence[int] = (), out_flag_ptrs: Sequence[int] = (),
+                  out_row_off: int = 0, router_w=None, top_k: int = 0, experts_per_rank: int = 0,
+                  routed_scale: float = 1.0, slab_ptrs: Sequence[int] = (), meta_ptrs: Sequence[int] = (),
+                  cnt_ptrs: Sequence[int] = (), cap: int = 0, my_rank: int = 0, device=None) -> None:
+    _ext().finalize_norm(acc, arrive, expected, ticket, residual_in, residual_out, bias, norm_w, eps,
+                         w_offset, list(out_ptrs), list(out_flag_ptrs), out_row_off, rows, n,
+                         status_word(device), router_w, top_k, experts_per_rank, routed_scale,
+                         list(slab_ptrs), list(meta_ptrs), list(cnt_ptrs), cap, my_rank)
+    _bump()
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, *, residual: Optional[torch.Tensor] = None,
+            residual_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+            w_offset: float = 0.0) -> torch.Tensor:
+    """out = RMSNorm(x [+ residual]) * (w + w_offset); optionally writes the sum to residual_out.
+
+    Convenience wrapper over the finalize kernel; with a residual the second operand is passed
+    through the kernel's fp32 accumulator input.
+    """
+    rows, n = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    acc = None if residual is None else x.float()
+    finalize_norm(rows=rows, n=n, acc=acc, residual_in=x if residual is None else residual,
+                  residual_out=residual_out, norm_w=w, eps=eps, w_offset=w_offset,
+                  out_ptrs=[out.data_ptr()], device=x.device)
+    return out
+
+
+def qkv_rope_append(*, acc_f32=None, qkv_bf16=None, bias=None, q_norm_w=None, k_norm_w=None,
+                    norm_eps: float = 1e-6, norm_w_offset: float = 0.0, positions, slot_mapping,
+                    inv_freq, rope_mscale: float = 1.0, q_out, k_cache, v_cache, m: int, hq: int,
+                    hkv: int, d: int) -> None:
+    _ext().qkv_rope_append(acc_f32, qkv_bf16, bias, q_norm_w, k_norm_w, norm_eps, norm_w_offset,
+                           positions, slot_mapping, inv_freq, rope_mscale, q_out, k_cache, v_cache, m,
+                           hq, hkv, d, status_word(q_out.device))
+    _bump()
+
+
+def swiglu(*, acc_f32=None, gu_bf16=None, out, m: int, i: int, act: int = 0) -> None:
+    _ext().swiglu(acc_f32, gu_bf16, out, m, i, act)
+    _bump()
+
+
+def embed_gather(tokens, table, out, scale: float = 1.0, vocab_start: int = 0) -> None:
+    _ext().embed_gather(tokens, table, out, scale, vocab_start)
+    _bump()
+
+
+def cast_acc_bf16(acc, out, m: int, n: int, bias=None) -> None:
+    _ext().cast_acc_bf16(acc, bias, out, m, n)
+    _bump()
+
+
+def fwht128(x) -> None:
+    _ext().fwht128(x)
+    _bump()
+
+
+def kv_block_copy(k_cache, v_cache, src, dst) -> None:
+    _ext().kv_block_copy(k_cache, v_cache, src, dst)
+    _bump()
+
+
+def softcap(logits, cap: float) -> None:
+    _ext().softcap(logits, cap)
+    _bump()
+
+
+def mmvq(qtype: int, w, x, out, *, n: int, k: int, bias=None, add: bool = False) -> None:
+    _ext().mmvq(qtype, w, x, bias, out, n, k, add)
+    _bump()
+
+
+def dequant_rows(qtype: int, w, out, *, n_src_rows: int, k: int, row_ids=None, scale: float = 1.0) -> None:
+    _ext().dequant_rows(qtype, w, row_ids, out, n_src_rows, k, scale)
+    _bump()
+
+
+def sample(logits, out_tokens, *, temperature=None, top_k=None, top_p=None, min_p=None, seeds=None,
+           counters=None, allow_mask=None, out_logit=None) -> None:
+    _ext().sample(logits, temperature, top_k, top_p, min_p, seeds, counters, allow_mask, out_tokens,
+                  out_logit)
+    _bump()
+
+
+def argmax(logits, out, out_val=None) -> None:
+    _ext().argmax(logits, out, out_val)
+    _bump()
+
+
+def argmax_combine(vals, idxs, out) -> None:
+    _ext().argmax_combine(vals, idxs, out)
+    _bump()
