@@ -51,7 +51,7 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
                const c10::optional<Tensor>& group_counts, const c10::optional<Tensor>& row_meta,
                const c10::optional<Tensor>& ag_flags, int64_t ag_expected, int64_t ag_rows_per_src,
                const c10::optional<Tensor>& ag_ticket, const Tensor& status, int64_t bn,
-               int64_t splits, int64_t act, int64_t m_tiles_override) {
+               int64_t splits, int64_t act, int64_t m_tiles_override, int64_t dst_ld) {
   TORCH_CHECK(a.is_cuda() && w.is_cuda(), "gemm_bf16: CUDA tensors required");
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16,
               "gemm_bf16: bf16 operands required");
@@ -108,6 +108,7 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
       p.arrive[i] = reinterpret_cast<uint32_t*>(arrive_ptrs[i]);
     p.n_owners = static_cast<int>(dst_ptrs.size());
     p.rows_per_owner = static_cast<int>(rows_per_owner > 0 ? rows_per_owner : M);
+    p.dst_ld = dst_ld > 0 ? dst_ld : N;
   }
   if (epi == oxb::kEpiSwigluBf16) {
     TORCH_CHECK(N % bn_i == 0, "swiglu epilogue: N % BN must be 0");
@@ -136,7 +137,7 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
     p.ag_flags = reinterpret_cast<const uint32_t*>(ag_flags->data_ptr());
     p.ag_n_src = static_cast<int>(ag_flags->numel());
     p.ag_expected = static_cast<uint32_t>(ag_expected);
-    p.ag_rows_per_src = static_cast<int>(ag_rows_per_src > 0 ? ag_rows_per_src : M);
+    p.ag_rows_per_src = static_cast<int>(ag_rows_per_src);
     p.ag_ticket = reinterpret_cast<uint32_t*>(ag_ticket->data_ptr());
   }
   p.status = reinterpret_cast<int*>(status.data_ptr());
@@ -220,7 +221,8 @@ void finalize_norm(const c10::optional<Tensor>& acc, const c10::optional<Tensor>
                    const c10::optional<Tensor>& residual_out, const c10::optional<Tensor>& bias,
                    const c10::optional<Tensor>& norm_w, double eps, double w_offset,
                    const std::vector<int64_t>& out_ptrs, const std::vector<int64_t>& out_flag_ptrs,
-                   int64_t out_row_off, int64_t rows, int64_t N, const Tensor& status,
+                   int64_t out_row_off, const c10::optional<Tensor>& out_row_map, int64_t rows,
+                   int64_t N, const Tensor& status,
                    const c10::optional<Tensor>& router_w, int64_t top_k, int64_t experts_per_rank,
                    double routed_scale, const std::vector<int64_t>& slab_ptrs,
                    const std::vector<int64_t>& meta_ptrs, const std::vector<int64_t>& cnt_ptrs,
@@ -247,6 +249,7 @@ void finalize_norm(const c10::optional<Tensor>& acc, const c10::optional<Tensor>
     p.out_flag[i] = reinterpret_cast<uint32_t*>(out_flag_ptrs[i]);
   p.n_dst = static_cast<int>(out_ptrs.size() > 0 ? out_ptrs.size() : out_flag_ptrs.size());
   p.out_row_off = out_row_off;
+  p.out_row_map = opt_ptr<int>(out_row_map);
   p.rows = static_cast<int>(rows);
   p.N = static_cast<int>(N);
   p.status = reinterpret_cast<int*>(status.data_ptr());

@@ -119,7 +119,10 @@ __global__ void __launch_bounds__(kNormThreads) finalize_norm_kernel(const Final
     const float tot = block_sum(ss, s_red);
     inv = rsqrtf(tot / static_cast<float>(N) + p.eps);
   }
-  const long long ooff = (p.out_row_off + row) * static_cast<long long>(N);
+  long long orow = p.out_row_off + row;
+  if (p.out_row_map != nullptr) orow = p.out_row_map[row];
+  const bool store_out = orow >= 0;
+  const long long ooff = orow * static_cast<long long>(N);
   for (int c = threadIdx.x * 8; c < N; c += kNormThreads * 8) {
     float y[8];
     if (p.norm_w != nullptr) {
@@ -143,7 +146,7 @@ __global__ void __launch_bounds__(kNormThreads) finalize_norm_kernel(const Final
     o.w = pack_bf16x2(y[6], y[7]);
 #pragma unroll
     for (int d = 0; d < kMaxPeers; ++d)
-      if (d < p.n_dst) *reinterpret_cast<uint4*>(p.out[d] + ooff + c) = o;
+      if (d < p.n_dst && store_out) *reinterpret_cast<uint4*>(p.out[d] + ooff + c) = o;
   }
 
   if (p.router_w != nullptr) {

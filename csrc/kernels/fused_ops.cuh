@@ -33,6 +33,7 @@ struct FinalizeNormParams {
   uint32_t* out_flag[kMaxPeers];   // counter to bump on each destination (nullable entries)
   int n_dst;
   long long out_row_off;
+  const int* out_row_map;   // optional [rows]: destination row (replaces out_row_off + r); < 0 = skip
   int rows, N;
   int* status;
   // --- MoE dispatch mode (router_w != nullptr): the normed row goes only to the ranks that own

@@ -172,11 +172,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       bool ok = true;
       if (p.ag_flags != nullptr && !grouped) {
-        const int m_end = m0 + BM < rows ? m0 + BM : rows;
-        int s_lo = m0 / p.ag_rows_per_src;
-        int s_hi = (m_end - 1) / p.ag_rows_per_src;
-        if (s_hi >= p.ag_n_src) s_hi = p.ag_n_src - 1;
-        if (s_lo > s_hi) s_lo = s_hi;
+        int s_lo = 0, s_hi = p.ag_n_src - 1;  // rows_per_src <= 0: rows are not grouped by source
+        if (p.ag_rows_per_src > 0) {
+          const int m_end = m0 + BM < rows ? m0 + BM : rows;
+          s_lo = m0 / p.ag_rows_per_src;
+          s_hi = (m_end - 1) / p.ag_rows_per_src;
+          if (s_hi >= p.ag_n_src) s_hi = p.ag_n_src - 1;
+          if (s_lo > s_hi) s_lo = s_hi;
+        }
         ok = wait_sources(p, s_lo, s_hi);
       }
       for (int kb = 0; kb < nkb && ok; ++kb) {
@@ -264,7 +267,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tmem_ld_wait();
           const int col0 = n0 + c * 32;
           if (!row_ok || col0 >= p.N || red_base == nullptr) continue;
-          float* d = red_base + static_cast<long long>(row_local) * p.N + col0;
+          float* d = red_base + static_cast<long long>(row_local) * p.dst_ld + col0;
           if (vec_ok && col0 + 32 <= p.N) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4)
@@ -283,8 +286,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll 1
         for (int c = 0; c < BN / 64; ++c) {
           uint32_t gt[32], up[32];
-          tmem_ld_32x32b_x32(lane_addr + c * 32, gt);
-          tmem_ld_32x32b_x32(lane_addr + BN / 2 + c * 32, up);
+          tmem_ld_32x32b_x32(lane_addr + c * 64, gt);
+          tmem_ld_32x32b_x32(lane_addr + c * 64 + 32, up);
           tmem_ld_wait();
           const int col0 = (n0 >> 1) + c * 32;
           if (!row_ok || col0 >= n_out) continue;

@@ -14,7 +14,7 @@ enum GemmEpilogue : int {
   kEpiStoreBf16 = 0,   // C[row, col] = bf16(acc + bias[col])
   kEpiRedF32 = 1,      // dst[owner][row', col] += w * acc   (fp32 red; local or peer memory)
   kEpiStoreF32 = 2,    // C[row, col] = acc + bias[col]      (fp32)
-  kEpiSwigluBf16 = 3,  // C[row, n0/2 + j] = act(acc[j]) * acc[BN/2 + j]; weights interleaved per tile
+  kEpiSwigluBf16 = 3,  // C[row, n/2] = act(gate) * up; weight rows interleaved [32 gate | 32 up]
 };
 
 // Per-row routing record of the MoE combine: which rank / row / weight a slab row goes back to.
@@ -41,6 +41,7 @@ struct GemmParams {
   long long meta_group_stride;
   // --- routed fp32 reduction (split-K on one GPU; reduce-scatter / combine across GPUs) ---
   float* dst[kMaxRanks];        // accumulator of owner o (a peer mapping when o != this rank)
+  long long dst_ld;             // row stride of the accumulators (elements)
   uint32_t* arrive[kMaxRanks];  // counter on owner o, bumped once when this whole GEMM has landed
   uint32_t* done_ticket;        // local ticket that finds the last CTA (nullptr = no signalling)
   uint32_t* reset_on_done;      // optional local words zeroed by the last CTA before signalling
@@ -50,7 +51,7 @@ struct GemmParams {
   // --- wait on the A operand (rows written into local memory by peers) ---
   const uint32_t* ag_flags;  // local counters, one per source rank; nullptr = A is ready
   uint32_t ag_expected;      // value each needed counter must reach
-  int ag_rows_per_src;
+  int ag_rows_per_src;       // rows [s*n, (s+1)*n) come from source s; <= 0: wait for every source
   int ag_n_src;
   uint32_t* ag_ticket;       // local ticket used to re-arm the counters after the last CTA passed
   int* status;               // error word (0 = ok)

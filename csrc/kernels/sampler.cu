@@ -225,14 +225,13 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const SampleParams p) 
       keep = c > 0 ? c : 1;
     }
     if (top_k < keep) keep = top_k;
-    // top-p over the renormalised kept set
+    // top-p: cumulative mass of the candidate softmax (not renormalised after min-p / top-k,
+    // as in the reference pipeline)
     if (top_p < 1.f) {
-      float tot = 0.f;
-      for (int i = 0; i < keep; ++i) tot += s_val[i];
       float cum = 0.f;
       int c = 0;
       while (c < keep) {
-        cum += s_val[c] / tot;
+        cum += s_val[c] / sum;
         ++c;
         if (cum >= top_p) break;
       }

@@ -1,0 +1,452 @@
+"""LLMEngine: continuous-batching serving loop of one rank.
+
+step() = C++ scheduler builds the plan -> one pinned-host -> device copy of the step descriptor
+-> forward (CUDA graph replay for decode-only buckets, eager launches for steps with prefill
+chunks) -> device sampler -> D2H of the sampled ids -> scheduler update -> token events.
+With tp > 1 every rank runs the same deterministic scheduler on the same request stream, so no
+per-step control traffic is needed; rank 0 owns the client-facing side.
+
+Reference parity: ContinuousBatchingEngine::run_loop / step_batch_overlap
+(oxide-engine/src/continuous_batching.rs:303-1395), CudaBackend::dispatch_batch_decode_step with
+one graph per batch bucket (oxide-backend-cuda/src/lib.rs:3326-4114), prefix reuse
+(continuous_batching.rs:406-437), typed errors and per-request failure (`:664-672`).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Iterable, Optional
+
+import numpy as np
+import torch
+
+from .. import ops
+from .._build import host_ext
+from ..config import EngineConfig
+from ..errors import ConfigError, EngineError, OutOfMemory
+from ..models.config import ModelConfig, preset
+from ..models.llama import DeviceModel, StepInputs
+from ..sampling_params import SamplingParams
+
+
+@dataclass
+class RequestState:
+    req_id: int
+    params: SamplingParams
+    prompt_len: int
+    t_arrival: float
+    t_first_token: Optional[float] = None
+    t_last_token: Optional[float] = None
+    n_generated: int = 0
+    host_sampler: object = None
+    grammar: object = None
+    on_token: Optional[Callable] = None
+    output: list = field(default_factory=list)
+    finished: bool = False
+    finish_reason: str = ""
+
+
+class _Staging:
+    """One pinned host buffer and its device mirror holding every per-step array; a step is
+    described to the GPU with a single H2D copy."""
+
+    def __init__(self, fields_: dict[str, tuple[int, np.dtype]], device):
+        off = 0
+        self.off: dict[str, tuple[int, int, np.dtype]] = {}
+        for name, (count, dt) in fields_.items():
+            dt = np.dtype(dt)
+            off = (off + 15) // 16 * 16
+            self.off[name] = (off, count, dt)
+            off += count * dt.itemsize
+        self.nbytes = (off + 15) // 16 * 16
+        pin = torch.cuda.is_available()
+        self.host = torch.zeros(self.nbytes, dtype=torch.uint8, pin_memory=pin)
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(self.nbytes, dtype=torch.uint8, device=device)
+        self._tdt = {np.dtype(np.int32): torch.int32, np.dtype(np.int64): torch.int64,
+                     np.dtype(np.float32): torch.float32}
+
+    def h(self, name: str) -> np.ndarray:
+        o, c, dt = self.off[name]
+        return self.host_np[o:o + c * dt.itemsize].view(dt)
+
+    def d(self, name: str) -> torch.Tensor:
+        o, c, dt = self.off[name]
+        return self.dev[o:o + c * dt.itemsize].view(self._tdt[dt])
+
+    def upload(self, upto: Optional[int] = None) -> int:
+        n = self.nbytes if upto is None else upto
+        self.dev[:n].copy_(self.host[:n], non_blocking=True)
+        return n
+
+
+class LLMEngine:
+    def __init__(self, cfg: EngineConfig, model_cfg: Optional[ModelConfig] = None, *, weights=None,
+                 rank: int = 0, world: int = 1, group=None, device: Optional[torch.device] = None,
+                 random_init: bool = False):
+        self.cfg = cfg
+        self.rank, self.world = rank, world
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        if model_cfg is None:
+            if weights is not None:
+                model_cfg = weights.cfg
+            else:
+                model_cfg = preset(cfg.model)
+        self.model_cfg = model_cfg
+        mc = model_cfg
+        H = host_ext()
+        self.block = H.TOKENS_PER_BLOCK
+        max_blocks_per_seq = (min(cfg.ctx_size, mc.max_ctx) + self.block - 1) // self.block
+        weight_mode = cfg.weight_mode
+        if weight_mode == "auto":
+            packed = weights is not None and any(
+                weights.type_name(n) not in ("F32", "F16", "BF16") for n in ("blk.0.attn_q.weight",)
+                if weights.has(n))
+            weight_mode = "quant" if packed and world == 1 and not mc.is_moe else "bf16"
+        self.max_tokens = max(cfg.max_num_batched_tokens, cfg.max_num_seqs)
+        self.max_tokens = (self.max_tokens + world - 1) // world * world
+        num_blocks = cfg.num_kv_blocks
+        if num_blocks <= 0:
+            num_blocks = self._auto_blocks(mc, weight_mode, random_init or weights is not None)
+        self.model = DeviceModel(mc, rank=rank, world=world, group=group, device=self.device,
+                                 max_tokens=self.max_tokens, max_seqs=cfg.max_num_seqs,
+                                 num_blocks=num_blocks, max_blocks_per_seq=max_blocks_per_seq,
+                                 max_logits=max(cfg.max_num_seqs * (1 + (cfg.draft_tokens if cfg.speculative != "off" else 0)), 64),
+                                 max_splits=cfg.max_splits, weight_mode=weight_mode)
+        if weights is not None:
+            self.model.load(weights)
+        elif random_init:
+            self.model.init_random(cfg.seed)
+        sc = H.SchedulerConfig()
+        sc.num_blocks = num_blocks
+        sc.max_num_seqs = cfg.max_num_seqs
+        sc.max_num_batched_tokens = cfg.max_num_batched_tokens
+        sc.max_blocks_per_seq = max_blocks_per_seq
+        sc.chunk_min, sc.chunk_max = cfg.chunk_min, cfg.chunk_max
+        sc.sla_itl_us, sc.base_us, sc.per_token_us = cfg.sla_itl_us, cfg.base_us, cfg.per_token_us
+        sc.enable_radix = cfg.enable_radix
+        sc.sla_budget = cfg.sla_budget
+        self.sched = H.Scheduler(sc)
+        self.max_blocks_per_seq = max_blocks_per_seq
+        S, M = cfg.max_num_seqs, self.max_tokens
+        n_tiles_max = M // 64 + S + 1
+        i32, i64 = np.int32, np.int64
+        self.st = _Staging({
+            "token_ids": (M, i32), "positions": (M, i32), "logit_map": (M, i32), "slot_mapping": (M, i64),
+            "pages_per_split": (4, i32), "seq_lens": (S, i32), "block_tables": (S * max_blocks_per_seq, i32),
+            "q_start": (S, i32), "q_lens": (S, i32), "ctx_lens": (S, i32), "tile_seq": (n_tiles_max, i32),
+            "tile_q0": (n_tiles_max, i32), "prefill_block_tables": (S * max_blocks_per_seq, i32),
+            "cow_src": (S, i32), "cow_dst": (S, i32),
+            "temperature": (self.model.max_logits, np.float32), "top_k": (self.model.max_logits, i32),
+            "top_p": (self.model.max_logits, np.float32), "min_p": (self.model.max_logits, np.float32),
+            "seeds": (self.model.max_logits, i64), "counters": (self.model.max_logits, i64),
+        }, self.device)
+        # everything up to the prefill arrays is what a decode-only step needs
+        self._decode_bytes = self.st.off["q_start"][0]
+        self.sampled = torch.zeros(self.model.max_logits, dtype=torch.int32, device=self.device)
+        self.sampled_val = torch.zeros(self.model.max_logits, dtype=torch.float32, device=self.device)
+        self.sampled_host = torch.zeros(self.model.max_logits, dtype=torch.int32,
+                                        pin_memory=torch.cuda.is_available())
+        self.requests: dict[int, RequestState] = {}
+        self._next_id = 0
+        self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.stats = {"steps": 0, "decode_tokens": 0, "prefill_tokens": 0, "graph_replays": 0,
+                      "h2d_bytes": 0, "d2h_bytes": 0, "degraded": False}
+        self.stop_ids_default = [mc.eos_id]
+        self._drafter = None
+        if cfg.speculative in ("ngram", "auto"):
+            from .spec_decode import NgramDrafter
+
+            self._drafter = NgramDrafter(cfg.draft_tokens)
+
+    # ------------------------------------------------------------------ sizing
+    def _auto_blocks(self, mc: ModelConfig, weight_mode: str, has_weights: bool) -> int:
+        free, total = torch.cuda.mem_get_info(self.device)
+        tp = self.world
+        w_bytes = 0
+        if has_weights:
+            per = 2.0 if weight_mode == "bf16" else 0.6
+            n = mc.n_params()
+            w_bytes = int((n - mc.vocab_size * mc.d_model) / tp * per + mc.vocab_size * mc.d_model * 2)
+        act = self.max_tokens * (mc.d_model * 16 + (mc.q_dim + 2 * mc.kv_dim) // tp * 8 + mc.ffn_dim // tp * 4)
+        act += self.cfg.max_num_seqs * (mc.vocab_size // tp) * 4 * 2
+        if mc.is_moe:
+            act += (mc.n_experts // tp) * self.max_tokens * (mc.d_model + mc.ffn_dim) * 2
+        budget = int(free * self.cfg.gpu_memory_utilization) - w_bytes - act - (2 << 30)
+        per_block = 2 * mc.n_layers * (mc.n_kv_heads // tp) * 16 * mc.head_dim * 2
+        n = budget // per_block
+        if n < 16:
+            raise OutOfMemory(f"not enough device memory for the KV pool ({budget} bytes left for blocks)")
+        cap = self.cfg.max_num_seqs * ((min(self.cfg.ctx_size, mc.max_ctx) + 15) // 16) + 64
+        return int(min(n, cap))
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt_tokens: Iterable[int], params: Optional[SamplingParams] = None,
+                    on_token: Optional[Callable] = None, req_id: Optional[int] = None) -> int:
+        params = params or SamplingParams()
+        toks = np.asarray(list(prompt_tokens), dtype=np.int32)
+        if toks.size == 0:
+            raise ConfigError("empty prompt")
+        rid = self._next_id if req_id is None else req_id
+        self._next_id = max(self._next_id, rid) + 1
+        stop = list(params.stop_token_ids) or list(self.stop_ids_default)
+        self.sched.add_request(rid, toks, int(params.max_tokens), stop, bool(params.ignore_eos))
+        st = RequestState(rid, params, int(toks.size), time.perf_counter(), on_token=on_token)
+        if not params.is_greedy() and not params.device_ok():
+            from ..sampler import HostSampler
+
+            st.host_sampler = HostSampler(params)
+        if params.grammar:
+            from ..grammar import grammar_from_spec
+
+            st.grammar = grammar_from_spec(params.grammar)
+        self.requests[rid] = st
+        return rid
+
+    def cancel(self, req_id: int) -> bool:
+        ok, events = self.sched.cancel(req_id)
+        for e in events:
+            self._deliver(e)
+        return ok
+
+    def has_work(self) -> bool:
+        return self.sched.has_work()
+
+    # ------------------------------------------------------------------ step
+    def _bucket(self, n: int) -> Optional[int]:
+        for b in self.cfg.graph_buckets:
+            if b >= n and b % self.world == 0 and b <= self.cfg.max_num_seqs:
+                return b
+        return None
+
+    def _fill(self, plan):
+        st = self.st
+        n, nd, npf = plan.n_tokens, plan.n_decode, plan.n_prefill
+        world = self.world
+        decode_only = npf == 0
+        m = n
+        bucket = self._bucket(nd) if (decode_only and self.cfg.cuda_graph) else None
+        if bucket is not None:
+            m = bucket
+        m = (m + world - 1) // world * world
+        h = st.h
+        tok, pos, slot, lmap = h("token_ids"), h("positions"), h("slot_mapping"), h("logit_map")
+        tok[:n] = plan.token_ids
+        pos[:n] = plan.positions
+        slot[:n] = plan.slot_mapping
+        tok[n:m] = 0
+        pos[n:m] = 0
+        slot[n:m] = -1
+        rows = plan.logit_rows
+        if bucket is not None:
+            lmap[:m] = np.arange(m, dtype=np.int32)  # graph buckets compute logits for every row
+        else:
+            lmap[:m] = -1
+            lmap[rows] = np.arange(rows.size, dtype=np.int32)
+        W = self.max_blocks_per_seq
+        w = plan.max_blocks
+        nd_pad = m if decode_only else nd
+        if nd > 0:
+            sl = h("seq_lens")
+            sl[:nd] = plan.decode_seq_lens
+            sl[nd:nd_pad] = 0
+            bt = h("block_tables").reshape(-1, W)
+            bt[:nd, :w] = plan.decode_block_tables.reshape(nd, w)
+            max_len = int(plan.decode_seq_lens.max())
+            pages = (max_len + 15) // 16
+            # enough CTAs to fill 148 SMs a few times over, at least one page per warp
+            want = -(-4 * 148 // max(1, nd * self.model.hkv))
+            splits = max(1, min(self.cfg.max_splits, want))
+            pps = max(4, -(-pages // splits))
+            pps = (pps + 3) // 4 * 4
+            h("pages_per_split")[0] = pps
+        n_tiles = 0
+        if npf > 0:
+            h("q_start")[:npf] = plan.q_start
+            h("q_lens")[:npf] = plan.q_lens
+            h("ctx_lens")[:npf] = plan.ctx_lens
+            n_tiles = plan.tile_seq.size
+            h("tile_seq")[:n_tiles] = plan.tile_seq
+            h("tile_q0")[:n_tiles] = plan.tile_q0
+            pbt = h("prefill_block_tables").reshape(-1, W)
+            pbt[:npf, :w] = plan.prefill_block_tables.reshape(npf, w)
+        n_cow = plan.cow_src.size
+        if n_cow:
+            h("cow_src")[:n_cow] = plan.cow_src
+            h("cow_dst")[:n_cow] = plan.cow_dst
+        nbytes = st.upload(self._decode_bytes if (decode_only and not n_cow) else None)
+        self.stats["h2d_bytes"] += nbytes
+        d = st.d
+        s = StepInputs(m=m, n_decode=nd_pad if decode_only else nd, n_prefill=npf, n_tiles=n_tiles,
+                       n_logits=rows.size if bucket is None else m,
+                       token_ids=d("token_ids"), positions=d("positions"), slot_mapping=d("slot_mapping"),
+                       seq_lens=d("seq_lens"), block_tables=d("block_tables").view(-1, W),
+                       pages_per_split=d("pages_per_split"), tile_seq=d("tile_seq"), tile_q0=d("tile_q0"),
+                       q_start=d("q_start"), q_lens=d("q_lens"), ctx_lens=d("ctx_lens"),
+                       prefill_block_tables=d("prefill_block_tables").view(-1, W), logit_map=d("logit_map"))
+        if n_cow:
+            for li in range(self.model_cfg.n_layers):
+                ops.kv_block_copy(self.model.k_cache[li], self.model.v_cache[li], d("cow_src")[:n_cow],
+                                  d("cow_dst")[:n_cow])
+        return s, bucket
+
+    def _forward(self, s: StepInputs, bucket: Optional[int]) -> torch.Tensor:
+        if bucket is None:
+            return self.model.forward(s)
+        g = self.graphs.get(bucket)
+        if g is None:
+            # warm-up launches outside capture (lazy module init, TMA descriptor cache), then capture
+            self.model.forward(s)
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.model.forward(s)
+            self.graphs[bucket] = g
+            # the capture did not execute; the warm-up run already produced this step's state
+            return self.model.logits[:s.n_logits]
+        g.replay()
+        self.stats["graph_replays"] += 1
+        return self.model.logits[:s.n_logits]
+
+    def step(self) -> list:
+        """One scheduler iteration. Returns the TokenEvents of this step."""
+        t0 = time.perf_counter()
+        plan = self.sched.schedule()
+        if plan.n_tokens == 0:
+            return []
+        if self._drafter is not None:
+            pass  # drafts are attached after update(), see below
+        s, bucket = self._fill(plan)
+        logits = self._forward(s, bucket)
+        n_rows = plan.logit_rows.size
+        tokens = self._sample(plan, logits, n_rows)
+        events = self.sched.update(plan, tokens)
+        self.stats["steps"] += 1
+        self.stats["decode_tokens"] += plan.n_decode
+        self.stats["prefill_tokens"] += plan.prefill_tokens
+        for e in events:
+            self._deliver(e)
+        if self._drafter is not None:
+            self._attach_drafts()
+        if time.perf_counter() - t0 > self.cfg.step_deadline_s:
+            self.stats["degraded"] = True
+        return events
+
+    # ------------------------------------------------------------------ sampling
+    def _sample(self, plan, logits: torch.Tensor, n_rows: int) -> np.ndarray:
+        reqs = [self.requests.get(int(r)) for r in plan.logit_req]
+        all_greedy = all(r is None or (r.params.is_greedy() and r.grammar is None) for r in reqs)
+        n_log = logits.shape[0]
+        if self.world > 1:
+            logits = self._gather_logits(logits, all_greedy, n_log)
+            if logits is None:  # greedy fast path finished on the device
+                return self._fetch(n_rows)
+        if all_greedy:
+            ops.argmax(logits, self.sampled[:n_log], self.sampled_val[:n_log])
+            return self._fetch(n_rows)
+        st = self.st
+        h = st.h
+        need_host = []
+        mask = None
+        for i, r in enumerate(reqs):
+            p = r.params if r is not None else SamplingParams(greedy=True)
+            h("temperature")[i] = 0.0 if p.is_greedy() else p.temperature
+            h("top_k")[i] = p.top_k
+            h("top_p")[i] = p.top_p
+            h("min_p")[i] = p.min_p
+            h("seeds")[i] = p.seed
+            h("counters")[i] = r.n_generated if r is not None else 0
+            if r is not None and (r.host_sampler is not None):
+                need_host.append(i)
+            if r is not None and r.grammar is not None:
+                if mask is None:
+                    words = (self.model_cfg.vocab_size + 31) // 32
+                    mask = np.full((n_log, words), -1, dtype=np.int32)
+                mask[i] = r.grammar.allow_mask(self.model_cfg.vocab_size)
+        for name in ("temperature", "top_k", "top_p", "min_p", "seeds", "counters"):
+            o, c, dt = st.off[name]
+            nb = n_rows * dt.itemsize
+            st.dev[o:o + nb].copy_(st.host[o:o + nb], non_blocking=True)
+        mask_t = torch.from_numpy(mask).to(self.device) if mask is not None else None
+        ops.sample(logits, self.sampled[:n_log], temperature=st.d("temperature")[:n_log],
+                   top_k=st.d("top_k")[:n_log], top_p=st.d("top_p")[:n_log], min_p=st.d("min_p")[:n_log],
+                   seeds=st.d("seeds")[:n_log], counters=st.d("counters")[:n_log], allow_mask=mask_t)
+        toks = self._fetch(n_rows)
+        if need_host:
+            rows = logits[need_host].float().cpu().numpy()
+            for j, i in enumerate(need_host):
+                r = reqs[i]
+                hist = self.sched.request_tokens(r.req_id)
+                toks[i] = r.host_sampler.sample(rows[j], hist if hist is not None else np.zeros(0, np.int32))
+        return toks
+
+    def _gather_logits(self, logits, all_greedy: bool, n_log: int):
+        import torch.distributed as dist
+
+        if all_greedy:
+            ops.argmax(logits, self.sampled[:n_log], self.sampled_val[:n_log])
+            idx = self.sampled[:n_log] + self.rank * self.model.v_l
+            vals = torch.empty(self.world, n_log, dtype=torch.float32, device=self.device)
+            idxs = torch.empty(self.world, n_log, dtype=torch.int32, device=self.device)
+            dist.all_gather_into_tensor(vals, self.sampled_val[:n_log].contiguous())
+            dist.all_gather_into_tensor(idxs, idx.contiguous())
+            ops.argmax_combine(vals, idxs, self.sampled[:n_log])
+            return None
+        full = torch.empty(self.world, n_log, self.model.v_l, dtype=torch.float32, device=self.device)
+        dist.all_gather_into_tensor(full, logits.contiguous())
+        return full.permute(1, 0, 2).reshape(n_log, -1).contiguous()
+
+    def _fetch(self, n_rows: int) -> np.ndarray:
+        self.sampled_host[:n_rows].copy_(self.sampled[:n_rows], non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        self.stats["d2h_bytes"] += 4 * n_rows
+        return self.sampled_host[:n_rows].numpy().copy()
+
+    # ------------------------------------------------------------------ events
+    def _deliver(self, e) -> None:
+        r = self.requests.get(int(e.req_id))
+        if r is None:
+            return
+        now = time.perf_counter()
+        if e.token >= 0:
+            if r.t_first_token is None:
+                r.t_first_token = now
+            r.t_last_token = now
+            r.n_generated += 1
+            r.output.append(int(e.token))
+            if r.grammar is not None:
+                r.grammar.advance(int(e.token))
+        if e.finished:
+            r.finished = True
+            r.finish_reason = e.reason
+        if r.on_token is not None:
+            r.on_token(r, e)
+
+    def _attach_drafts(self) -> None:
+        for rid in self.sched.running_ids():
+            r = self.requests.get(int(rid))
+            if r is None or r.finished or not r.params.is_greedy():
+                continue
+            hist = self.sched.request_tokens(rid)
+            if hist is None:
+                continue
+            d = self._drafter.propose(hist)
+            if d:
+                self.sched.set_drafts(rid, d)
+
+    # ------------------------------------------------------------------ convenience
+    def generate(self, prompts: list, params: Optional[SamplingParams] = None, max_steps: int = 1 << 30):
+        """Runs the given prompts to completion; returns the generated token lists in order."""
+        ids = [self.add_request(p, params) for p in prompts]
+        steps = 0
+        while self.has_work() and steps < max_steps:
+            self.step()
+            steps += 1
+        return [self.requests[i].output for i in ids]
+
+    def check_device_status(self) -> None:
+        ops.check_status(self.device)
+
+    def close(self) -> None:
+        self.graphs.clear()
+        self.model.close()

@@ -1,0 +1,450 @@
+"""Device model: Llama-family dense decoder and Mixtral-style MoE, tensor/expert parallel.
+
+One process per GPU. Every rank holds its shard of the weights (column-parallel QKV / gate-up /
+LM head, row-parallel O / down, KV heads sharded, experts sharded) and a symmetric workspace that
+peers write into directly. Between the RS and the next AG the residual stream is sequence
+parallel: rank r owns rows [r*M/tp, (r+1)*M/tp). Per layer the launch sequence is
+
+    gemm(QKV, A = all-gather buffer, waits on per-source flags)      -> fp32 / bf16
+    qkv_rope_append (bias, QK-norm, RoPE, paged K/V write)           -> q
+    paged_decode / paged_prefill                                     -> attn
+    gemm(O, routed fp32 red into the row owner's accumulator)        == GEMM -> reduce-scatter
+    finalize_norm (wait, + residual, RMSNorm, push to every rank)    == ... + all-gather
+    gemm(gate|up, SwiGLU epilogue)   or   MoE: routed dispatch + grouped GEMMs
+    gemm(down, routed red)  ->  finalize_norm
+
+so no NCCL call sits on the forward path; the same code runs with tp == 1 (all pointers local).
+The reference's equivalent is the single-GPU launch chain of
+oxide-backend-cuda/src/lib.rs:3584-3992 (about 11 kernels per layer, fp32 activations).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..errors import ConfigError
+from ..formats import quants
+from ..parallel.comm import SymmetricWorkspace
+from .config import ModelConfig
+from .rope import inv_freq_table
+from .weights import WeightSource
+
+F_ARRIVE0, F_ARRIVE1, F_AG0, F_AG1, F_LMG, F_MOE = 0, 1, 8, 16, 24, 32
+T_FIN0, T_FIN1, T_AG0, T_AG1, T_LMG, T_MOE, T_DONE_O, T_DONE_D = range(8)
+
+
+def interleave32(g: torch.Tensor, u: torch.Tensor) -> torch.Tensor:
+    """[I, K] gate and up rows -> [2I, K] in units of 32 rows: g0..31 | u0..31 | g32..63 | ..."""
+    i, k = g.shape[-2], g.shape[-1]
+    lead = g.shape[:-2]
+    gg = g.reshape(*lead, i // 32, 1, 32, k)
+    uu = u.reshape(*lead, i // 32, 1, 32, k)
+    return torch.cat([gg, uu], dim=-3).reshape(*lead, 2 * i, k).contiguous()
+
+
+@dataclass
+class StepInputs:
+    """Device-side description of one engine step (static buffers, sliced by the counts)."""
+    m: int                 # tokens in the step, padded to a multiple of tp
+    n_decode: int
+    n_prefill: int
+    n_tiles: int
+    n_logits: int
+    token_ids: torch.Tensor      # [M] int32
+    positions: torch.Tensor      # [M] int32
+    slot_mapping: torch.Tensor   # [M] int64 (-1 = padding row)
+    seq_lens: torch.Tensor       # [n_decode] int32
+    block_tables: torch.Tensor   # [n_decode, max_blocks] int32
+    pages_per_split: torch.Tensor  # [1] int32
+    tile_seq: Optional[torch.Tensor] = None
+    tile_q0: Optional[torch.Tensor] = None
+    q_start: Optional[torch.Tensor] = None
+    q_lens: Optional[torch.Tensor] = None
+    ctx_lens: Optional[torch.Tensor] = None
+    prefill_block_tables: Optional[torch.Tensor] = None
+    logit_map: Optional[torch.Tensor] = None  # [M] int32: logits row of each token row or -1
+
+
+class QuantLinear:
+    """A GGUF-quantized weight kept packed in HBM (tp == 1 path)."""
+
+    def __init__(self, type_name: str, raw: np.ndarray, n: int, k: int, device):
+        self.code = quants.TYPES[type_name].code
+        self.type_name = type_name
+        self.n, self.k = n, k
+        self.packed = type_name not in ("F32", "F16", "BF16")
+        if self.packed:
+            self.w = torch.from_numpy(np.ascontiguousarray(raw).reshape(-1).copy()).to(device)
+        else:
+            f = quants.dequantize(type_name, raw, n * k).reshape(n, k)
+            self.w = torch.from_numpy(f).to(device=device, dtype=torch.bfloat16)
+
+
+class DeviceModel:
+    def __init__(self, cfg: ModelConfig, *, rank: int = 0, world: int = 1, group=None,
+                 device: Optional[torch.device] = None, max_tokens: int = 2048, max_seqs: int = 256,
+                 num_blocks: int = 1024, max_blocks_per_seq: int = 512, max_logits: Optional[int] = None,
+                 max_splits: int = 16, weight_mode: str = "bf16"):
+        self.cfg = cfg
+        self.rank, self.tp, self.group = rank, world, group
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        tp = world
+        if cfg.n_heads % tp or cfg.n_kv_heads % tp or cfg.vocab_size % tp:
+            raise ConfigError(f"heads/kv heads/vocab of {cfg.name} do not divide tp={tp}")
+        if cfg.is_moe and cfg.n_experts % tp:
+            raise ConfigError("n_experts must be a multiple of the expert-parallel size")
+        if not cfg.is_moe and (cfg.ffn_dim % (32 * tp)):
+            raise ConfigError("ffn_dim / tp must be a multiple of 32")
+        if weight_mode == "quant" and tp != 1:
+            raise ConfigError("packed GGUF weights are served at tp=1; use weight_mode='bf16' for tp>1")
+        self.weight_mode = weight_mode
+        self.D = cfg.head_dim
+        self.hq = cfg.n_heads // tp
+        self.hkv = cfg.n_kv_heads // tp
+        self.wqkv = (self.hq + 2 * self.hkv) * self.D
+        self.i_l = cfg.ffn_dim if cfg.is_moe else cfg.ffn_dim // tp
+        self.e_l = cfg.n_experts // tp if cfg.is_moe else 0
+        self.v_l = cfg.vocab_size // tp
+        self.max_tokens = (max_tokens + tp - 1) // tp * tp
+        self.max_seqs = max_seqs
+        self.max_logits = max_logits or max(max_seqs, 64)
+        self.max_splits = max_splits
+        self.num_blocks = num_blocks
+        self.max_blocks_per_seq = max_blocks_per_seq
+        self.scale = 1.0 / math.sqrt(self.D)
+        inv, self.rope_mscale = inv_freq_table(cfg)
+        dev = self.device
+        self.inv_freq = torch.from_numpy(inv).to(dev)
+        d = cfg.d_model
+        M = self.max_tokens
+        rpr = M // tp
+        specs = {
+            "acc0": ((rpr, d), "f32"), "acc1": ((rpr, d), "f32"),
+            "gather0": ((M, d), "bf16"), "gather1": ((M, d), "bf16"),
+            "lmg": ((self.max_logits, d), "bf16"),
+            "flags": ((128,), "i32"),
+        }
+        if cfg.is_moe:
+            self.cap = M
+            specs["slab"] = ((self.e_l, self.cap, d), "bf16")
+            specs["meta"] = ((self.e_l, self.cap, 4), "i32")
+            specs["cnt"] = ((16,), "i32")
+        self.ws = SymmetricWorkspace(specs, rank=rank, world=world, group=group, device=dev)
+        self.tickets = torch.zeros(16, dtype=torch.int32, device=dev)
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        self.residual = torch.zeros(rpr, d, **bf)
+        self.q_buf = torch.zeros(M, self.hq * self.D, **bf)
+        self.attn_out = torch.zeros(M, self.hq * self.D, **bf)
+        self.qkv_acc = torch.zeros(M, self.wqkv, dtype=torch.float32, device=dev)
+        self.qkv_bf16 = torch.zeros(M, self.wqkv, **bf)
+        if cfg.is_moe:
+            self.act_slab = torch.zeros(self.e_l, self.cap, self.i_l, **bf)
+        else:
+            self.act = torch.zeros(M, self.i_l, **bf)
+        self.logits = torch.zeros(self.max_logits, self.v_l, dtype=torch.float32, device=dev)
+        self.part_o = torch.zeros(max_seqs * self.hq * max_splits * self.D, dtype=torch.float32, device=dev)
+        self.part_ml = torch.zeros(max_seqs * self.hq * max_splits * 2, dtype=torch.float32, device=dev)
+        self.k_cache = [torch.zeros(num_blocks, self.hkv, 16, self.D, **bf) for _ in range(cfg.n_layers)]
+        self.v_cache = [torch.zeros(num_blocks, self.hkv, 16, self.D, **bf) for _ in range(cfg.n_layers)]
+        if weight_mode == "quant":
+            self.gu_acc = torch.zeros(M, 2 * self.i_l, dtype=torch.float32, device=dev)
+            self._scratch: Optional[torch.Tensor] = None
+        self.layers: list[dict] = []
+        self.embed = None
+        self.lm_head = None
+        self.out_norm = None
+        self._act_code = 1 if cfg.act == "gelu_tanh" else 0
+
+    # ------------------------------------------------------------------ weights
+    def kv_bytes(self) -> int:
+        return 2 * self.cfg.n_layers * self.num_blocks * self.hkv * 16 * self.D * 2
+
+    def init_random(self, seed: int = 0, std: float = 0.02) -> None:
+        """Random-init shards generated on the device (benchmarks; no host copy of the model)."""
+        cfg, dev = self.cfg, self.device
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed * 1000 + self.rank)
+        gr = torch.Generator(device=dev)
+        gr.manual_seed(seed * 1000 + 999)  # replicated tensors: same stream on every rank
+
+        def rnd(*shape, gen=g, s=std):
+            t = torch.empty(*shape, dtype=torch.bfloat16, device=dev)
+            t.normal_(0.0, s, generator=gen)
+            return t
+
+        d = cfg.d_model
+        ones = lambda n: torch.full((n,), 1.0 - cfg.norm_weight_offset, dtype=torch.bfloat16, device=dev)
+        self.embed = rnd(cfg.vocab_size, d, gen=gr)
+        self.lm_head = rnd(self.v_l, d)
+        self.out_norm = ones(d)
+        self.layers = []
+        for _ in range(cfg.n_layers):
+            L = {"attn_norm": ones(d), "ffn_norm": ones(d), "w_qkv": rnd(self.wqkv, d),
+                 "w_o": rnd(d, self.hq * self.D), "b_qkv": None, "q_norm": None, "k_norm": None}
+            if cfg.is_moe:
+                L["router"] = rnd(cfg.n_experts, d, gen=gr, s=1.0 / math.sqrt(d))
+                L["w_gu"] = rnd(self.e_l, 2 * self.i_l, d)
+                L["w_down"] = rnd(self.e_l, d, self.i_l)
+            else:
+                L["w_gu"] = rnd(2 * self.i_l, d)
+                L["w_down"] = rnd(d, self.i_l)
+            self.layers.append(L)
+
+    def load(self, src: WeightSource) -> None:
+        """Shards and uploads a checkpoint (GGUF / SafeTensors / synthetic source)."""
+        cfg, dev, r, tp, D = self.cfg, self.device, self.rank, self.tp, self.D
+        bf = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device=dev, dtype=torch.bfloat16)
+        hq_lo, hq_hi = r * self.hq * D, (r + 1) * self.hq * D
+        kv_lo, kv_hi = r * self.hkv * D, (r + 1) * self.hkv * D
+        self.out_norm = bf(src.f32("output_norm.weight"))
+        head_name = "output.weight" if src.has("output.weight") else "token_embd.weight"
+        quant = self.weight_mode == "quant"
+        if quant:
+            self.embed_q = QuantLinear(src.type_name("token_embd.weight"), src.raw("token_embd.weight"),
+                                       cfg.vocab_size, cfg.d_model, dev)
+            self.embed = self.embed_q.w if not self.embed_q.packed else None
+            self.lm_head_q = QuantLinear(src.type_name(head_name), src.raw(head_name), cfg.vocab_size,
+                                         cfg.d_model, dev) if head_name != "token_embd.weight" else self.embed_q
+        else:
+            self.embed = bf(src.f32("token_embd.weight"))
+            self.lm_head = bf(src.f32(head_name)[r * self.v_l:(r + 1) * self.v_l])
+        self.layers = []
+        for i in range(cfg.n_layers):
+            p = f"blk.{i}."
+            L: dict = {"attn_norm": bf(src.f32(p + "attn_norm.weight")), "ffn_norm": bf(src.f32(p + "ffn_norm.weight"))}
+            L["q_norm"] = bf(src.f32(p + "attn_q_norm.weight")) if src.has(p + "attn_q_norm.weight") else None
+            L["k_norm"] = bf(src.f32(p + "attn_k_norm.weight")) if src.has(p + "attn_k_norm.weight") else None
+            if src.has(p + "attn_q.bias"):
+                L["b_qkv"] = bf(np.concatenate([src.f32(p + "attn_q.bias")[hq_lo:hq_hi],
+                                                src.f32(p + "attn_k.bias")[kv_lo:kv_hi],
+                                                src.f32(p + "attn_v.bias")[kv_lo:kv_hi]]))
+            else:
+                L["b_qkv"] = None
+            if quant:
+                for key, n, k in (("attn_q", cfg.q_dim, cfg.d_model), ("attn_k", cfg.kv_dim, cfg.d_model),
+                                  ("attn_v", cfg.kv_dim, cfg.d_model), ("attn_output", cfg.d_model, cfg.q_dim),
+                                  ("ffn_gate", cfg.ffn_dim, cfg.d_model), ("ffn_up", cfg.ffn_dim, cfg.d_model),
+                                  ("ffn_down", cfg.d_model, cfg.ffn_dim)):
+                    nm = p + key + ".weight"
+                    L[key] = QuantLinear(src.type_name(nm), src.raw(nm), n, k, dev)
+            else:
+                wq, wk, wv = src.f32(p + "attn_q.weight"), src.f32(p + "attn_k.weight"), src.f32(p + "attn_v.weight")
+                L["w_qkv"] = bf(np.concatenate([wq[hq_lo:hq_hi], wk[kv_lo:kv_hi], wv[kv_lo:kv_hi]], 0))
+                L["w_o"] = bf(src.f32(p + "attn_output.weight")[:, hq_lo:hq_hi])
+                if cfg.is_moe:
+                    e_lo, e_hi = r * self.e_l, (r + 1) * self.e_l
+                    L["router"] = bf(src.f32(p + "ffn_gate_inp.weight"))
+                    g = bf(src.f32(p + "ffn_gate_exps.weight")[e_lo:e_hi])
+                    u = bf(src.f32(p + "ffn_up_exps.weight")[e_lo:e_hi])
+                    L["w_gu"] = interleave32(g, u)
+                    L["w_down"] = bf(src.f32(p + "ffn_down_exps.weight")[e_lo:e_hi])
+                else:
+                    i_lo, i_hi = r * self.i_l, (r + 1) * self.i_l
+                    g = bf(src.f32(p + "ffn_gate.weight")[i_lo:i_hi])
+                    u = bf(src.f32(p + "ffn_up.weight")[i_lo:i_hi])
+                    L["w_gu"] = interleave32(g, u)
+                    L["w_down"] = bf(src.f32(p + "ffn_down.weight")[:, i_lo:i_hi])
+            self.layers.append(L)
+
+    # ------------------------------------------------------------------ helpers
+    def _flag_ptrs(self, index: int) -> list[int]:
+        return self.ws.ptrs("flags", 4 * index)
+
+    def _finalize(self, rows: int, norm_w, *, acc: Optional[int], gather: str, flag_base: int,
+                  r0: int, first: bool = False, row_map=None, layer: Optional[dict] = None,
+                  moe: bool = False) -> None:
+        tp, d = self.tp, self.cfg.d_model
+        multi = tp > 1
+        kw = {}
+        if acc is not None:
+            kw["acc"] = self.ws.local(f"acc{acc}")
+            if multi:
+                kw["arrive"] = self.ws.local("flags")[F_ARRIVE0 + acc:F_ARRIVE0 + acc + 1]
+                kw["expected"] = tp
+                kw["ticket"] = self.tickets[T_FIN0 + acc:T_FIN0 + acc + 1]
+        flag_ptrs = self._flag_ptrs(flag_base + self.rank) if multi else []
+        if moe:
+            ops.finalize_norm(rows=rows, n=d, residual_in=self.residual, residual_out=self.residual,
+                              norm_w=norm_w, eps=self.cfg.rms_eps, w_offset=self.cfg.norm_weight_offset,
+                              out_flag_ptrs=flag_ptrs, router_w=layer["router"], top_k=self.cfg.n_experts_used,
+                              experts_per_rank=self.e_l, routed_scale=self.cfg.routed_scale,
+                              slab_ptrs=self.ws.ptrs("slab"), meta_ptrs=self.ws.ptrs("meta"),
+                              cnt_ptrs=self.ws.ptrs("cnt"), cap=self.cap, my_rank=self.rank,
+                              device=self.device, **kw)
+            return
+        ops.finalize_norm(rows=rows, n=d, residual_in=self.residual,
+                          residual_out=None if first else self.residual, norm_w=norm_w,
+                          eps=self.cfg.rms_eps, w_offset=self.cfg.norm_weight_offset,
+                          out_ptrs=self.ws.ptrs(gather), out_flag_ptrs=flag_ptrs, out_row_off=r0,
+                          out_row_map=row_map, device=self.device, **kw)
+
+    def _ag_kwargs(self, flag_base: int, ticket: int, rows_per_src: int, expected: int) -> dict:
+        if self.tp == 1:
+            return {}
+        return dict(ag_flags=self.ws.local("flags")[flag_base:flag_base + self.tp], ag_expected=expected,
+                    ag_rows_per_src=rows_per_src, ag_ticket=self.tickets[ticket:ticket + 1])
+
+    def _red_kwargs(self, acc: int, ticket: int, rpr: int) -> dict:
+        kw = dict(epi=ops.EPI_RED_F32, dst_ptrs=self.ws.ptrs(f"acc{acc}"), rows_per_owner=rpr)
+        if self.tp > 1:
+            kw["arrive_ptrs"] = self._flag_ptrs(F_ARRIVE0 + acc)
+            kw["done_ticket"] = self.tickets[ticket:ticket + 1]
+        return kw
+
+    def _scratch_for(self, n: int, k: int) -> torch.Tensor:
+        need = n * k
+        if self._scratch is None or self._scratch.numel() < need:
+            self._scratch = torch.empty(need, dtype=torch.bfloat16, device=self.device)
+        return self._scratch[:need].view(n, k)
+
+    def _qlinear(self, lin: QuantLinear, x: torch.Tensor, out_f32: torch.Tensor, ld_out: Optional[int] = None):
+        """out_f32[:, :n] = x @ W^T for a packed weight: MMVQ for small batches, else dequant + tcgen05."""
+        m = x.shape[0]
+        if lin.packed and m <= 8:
+            ops.mmvq(lin.code, lin.w, x, out_f32, n=lin.n, k=lin.k)
+            return
+        w = lin.w
+        if lin.packed:
+            w = self._scratch_for(lin.n, lin.k)
+            ops.dequant_rows(lin.code, lin.w, w, n_src_rows=lin.n, k=lin.k)
+        bn = ops.pick_bn(lin.n, (m + 127) // 128)
+        out_f32[:m].zero_() if out_f32.is_contiguous() else out_f32[:m].fill_(0)
+        ops.gemm(x, w, epi=ops.EPI_RED_F32, dst_ptrs=[out_f32.data_ptr()], bn=bn,
+                 splits=ops.pick_splits(m, lin.n, lin.k, bn), dst_ld=out_f32.stride(0))
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, s: StepInputs) -> torch.Tensor:
+        """Runs one step; returns fp32 logits [n_logits, vocab/tp] (a view of a static buffer)."""
+        if self.weight_mode == "quant":
+            return self._forward_quant(s)
+        cfg, tp, rank = self.cfg, self.tp, self.rank
+        M = s.m
+        rpr = M // tp
+        r0 = rank * rpr
+        d = cfg.d_model
+        ops.embed_gather(s.token_ids[r0:r0 + rpr], self.embed, self.residual[:rpr], cfg.emb_scale)
+        self._finalize(rpr, self.layers[0]["attn_norm"], acc=None, gather="gather0", flag_base=F_AG0, r0=r0,
+                       first=True)
+        g0 = self.ws.local("gather0")[:M]
+        g1 = self.ws.local("gather1")[:M]
+        for li, L in enumerate(self.layers):
+            # ---- attention block ----
+            bn = ops.pick_bn(self.wqkv, (M + 127) // 128)
+            splits = ops.pick_splits(M, self.wqkv, d, bn)
+            ag = self._ag_kwargs(F_AG0, T_AG0, rpr, rpr)
+            if splits > 1:
+                ops.gemm(g0, L["w_qkv"], epi=ops.EPI_RED_F32, dst_ptrs=[self.qkv_acc.data_ptr()], bn=bn,
+                         splits=splits, **ag)
+                qkv_kw = dict(acc_f32=self.qkv_acc)
+            else:
+                ops.gemm(g0, L["w_qkv"], out=self.qkv_bf16[:M], bn=bn, **ag)
+                qkv_kw = dict(qkv_bf16=self.qkv_bf16)
+            ops.qkv_rope_append(bias=L["b_qkv"], q_norm_w=L["q_norm"], k_norm_w=L["k_norm"], norm_eps=1e-6,
+                                norm_w_offset=cfg.norm_weight_offset, positions=s.positions,
+                                slot_mapping=s.slot_mapping, inv_freq=self.inv_freq,
+                                rope_mscale=self.rope_mscale, q_out=self.q_buf, k_cache=self.k_cache[li],
+                                v_cache=self.v_cache[li], m=M, hq=self.hq, hkv=self.hkv, d=self.D, **qkv_kw)
+            self._attention(s, li)
+            bn = ops.pick_bn(d, (M + 127) // 128)
+            ops.gemm(self.attn_out[:M], L["w_o"], bn=bn, splits=ops.pick_splits(M, d, self.hq * self.D, bn),
+                     **self._red_kwargs(0, T_DONE_O, rpr))
+            # ---- feed-forward block ----
+            if cfg.is_moe:
+                self._finalize(rpr, L["ffn_norm"], acc=0, gather="", flag_base=F_MOE, r0=r0, layer=L, moe=True)
+                self._moe(L, M, rpr)
+            else:
+                self._finalize(rpr, L["ffn_norm"], acc=0, gather="gather1", flag_base=F_AG1, r0=r0)
+                n_gu = 2 * self.i_l
+                ops.gemm(g1, L["w_gu"], out=self.act[:M], epi=ops.EPI_SWIGLU_BF16, act=self._act_code,
+                         bn=ops.pick_bn(n_gu, (M + 127) // 128), **self._ag_kwargs(F_AG1, T_AG1, rpr, rpr))
+                bn = ops.pick_bn(d, (M + 127) // 128)
+                ops.gemm(self.act[:M], L["w_down"], bn=bn, splits=ops.pick_splits(M, d, self.i_l, bn),
+                         **self._red_kwargs(1, T_DONE_D, rpr))
+            last = li == cfg.n_layers - 1
+            if not last:
+                self._finalize(rpr, self.layers[li + 1]["attn_norm"], acc=1, gather="gather0", flag_base=F_AG0,
+                               r0=r0)
+        # ---- final norm (logit rows only) + vocab-parallel LM head ----
+        n_log = s.n_logits
+        row_map = s.logit_map[r0:r0 + rpr] if s.logit_map is not None else None
+        self._finalize(rpr, self.out_norm, acc=1, gather="lmg", flag_base=F_LMG, r0=r0 if row_map is None else 0,
+                       row_map=row_map)
+        lmg = self.ws.local("lmg")[:n_log]
+        ops.gemm(lmg, self.lm_head, out=self.logits[:n_log], epi=ops.EPI_STORE_F32,
+                 bn=ops.pick_bn(self.v_l, (n_log + 127) // 128), **self._ag_kwargs(F_LMG, T_LMG, 0, rpr))
+        if cfg.logit_softcap > 0:
+            ops.softcap(self.logits[:n_log], cfg.logit_softcap)
+        return self.logits[:n_log]
+
+    def _attention(self, s: StepInputs, li: int) -> None:
+        nd = s.n_decode
+        win = self.cfg.sliding_window
+        if nd > 0:
+            ops.paged_decode(self.q_buf[:nd].view(nd, self.hq, self.D), self.k_cache[li], self.v_cache[li],
+                             s.block_tables, s.seq_lens, s.pages_per_split, self.part_o, self.part_ml,
+                             self.attn_out[:nd], batch=nd, max_splits=self.max_splits, window=win,
+                             scale=self.scale)
+        if s.n_prefill > 0:
+            ops.paged_prefill(self.q_buf.view(-1, self.hq, self.D), self.k_cache[li], self.v_cache[li],
+                              s.prefill_block_tables, s.tile_seq, s.tile_q0, s.q_start, s.q_lens, s.ctx_lens,
+                              self.attn_out, n_tiles=s.n_tiles, window=win, scale=self.scale)
+
+    def _moe(self, L: dict, M: int, rpr: int) -> None:
+        cfg, tp = self.cfg, self.tp
+        slab, meta = self.ws.local("slab"), self.ws.local("meta")
+        cnt = self.ws.local("cnt")[:self.e_l]
+        m_tiles = (M * cfg.n_experts_used + 127) // 128 + self.e_l
+        ops.gemm(slab, L["w_gu"], out=self.act_slab, epi=ops.EPI_SWIGLU_BF16, act=self._act_code,
+                 group_counts=cnt, m_tiles=m_tiles, bn=128, **self._ag_kwargs(F_MOE, T_MOE, 0, rpr))
+        kw = dict(epi=ops.EPI_RED_F32, dst_ptrs=self.ws.ptrs("acc1"), group_counts=cnt, row_meta=meta,
+                  m_tiles=m_tiles, bn=128, done_ticket=self.tickets[T_DONE_D:T_DONE_D + 1], reset_on_done=cnt)
+        if tp > 1:
+            kw["arrive_ptrs"] = self._flag_ptrs(F_ARRIVE1)
+        ops.gemm(self.act_slab, L["w_down"], **kw)
+
+    def _forward_quant(self, s: StepInputs) -> torch.Tensor:
+        """tp == 1 path over packed GGUF weights (MMVQ for M <= 8, dequant + tcgen05 GEMM above)."""
+        cfg = self.cfg
+        M, d = s.m, cfg.d_model
+        acc0, acc1 = self.ws.local("acc0"), self.ws.local("acc1")
+        g0, g1 = self.ws.local("gather0")[:M], self.ws.local("gather1")[:M]
+        if self.embed_q.packed:
+            ops.dequant_rows(self.embed_q.code, self.embed_q.w, self.residual[:M], n_src_rows=cfg.vocab_size,
+                             k=d, row_ids=s.token_ids[:M], scale=cfg.emb_scale)
+        else:
+            ops.embed_gather(s.token_ids[:M], self.embed_q.w, self.residual[:M], cfg.emb_scale)
+        self._finalize(M, self.layers[0]["attn_norm"], acc=None, gather="gather0", flag_base=F_AG0, r0=0, first=True)
+        qd, kd = cfg.q_dim, cfg.kv_dim
+        for li, L in enumerate(self.layers):
+            self._qlinear(L["attn_q"], g0, self.qkv_acc[:M, :qd])
+            self._qlinear(L["attn_k"], g0, self.qkv_acc[:M, qd:qd + kd])
+            self._qlinear(L["attn_v"], g0, self.qkv_acc[:M, qd + kd:])
+            ops.qkv_rope_append(acc_f32=self.qkv_acc, bias=L["b_qkv"], q_norm_w=L["q_norm"], k_norm_w=L["k_norm"],
+                                norm_eps=1e-6, norm_w_offset=cfg.norm_weight_offset, positions=s.positions,
+                                slot_mapping=s.slot_mapping, inv_freq=self.inv_freq, rope_mscale=self.rope_mscale,
+                                q_out=self.q_buf, k_cache=self.k_cache[li], v_cache=self.v_cache[li], m=M,
+                                hq=self.hq, hkv=self.hkv, d=self.D)
+            self._attention(s, li)
+            self._qlinear(L["attn_output"], self.attn_out[:M], acc0[:M])
+            self._finalize(M, L["ffn_norm"], acc=0, gather="gather1", flag_base=F_AG1, r0=0)
+            self._qlinear(L["ffn_gate"], g1, self.gu_acc[:M, :self.i_l])
+            self._qlinear(L["ffn_up"], g1, self.gu_acc[:M, self.i_l:])
+            ops.swiglu(acc_f32=self.gu_acc, out=self.act, m=M, i=self.i_l, act=self._act_code)
+            self._qlinear(L["ffn_down"], self.act[:M], acc1[:M])
+            if li != cfg.n_layers - 1:
+                self._finalize(M, self.layers[li + 1]["attn_norm"], acc=1, gather="gather0", flag_base=F_AG0, r0=0)
+        n_log = s.n_logits
+        self._finalize(M, self.out_norm, acc=1, gather="lmg", flag_base=F_LMG, r0=0, row_map=s.logit_map[:M])
+        lmg = self.ws.local("lmg")[:n_log]
+        self._qlinear(self.lm_head_q, lmg, self.logits[:n_log])
+        if cfg.logit_softcap > 0:
+            ops.softcap(self.logits[:n_log], cfg.logit_softcap)
+        return self.logits[:n_log]
+
+    def close(self) -> None:
+        self.ws.close()

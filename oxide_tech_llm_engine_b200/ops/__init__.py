@@ -90,7 +90,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
          rows_per_owner: int = 0, group_counts: Optional[torch.Tensor] = None,
          row_meta: Optional[torch.Tensor] = None, ag_flags: Optional[torch.Tensor] = None,
          ag_expected: int = 0, ag_rows_per_src: int = 0, ag_ticket: Optional[torch.Tensor] = None,
-         bn: int = 0, splits: int = 1, act: int = 0, m_tiles: int = 0) -> Optional[torch.Tensor]:
+         bn: int = 0, splits: int = 1, act: int = 0, m_tiles: int = 0,
+         dst_ld: int = 0) -> Optional[torch.Tensor]:
     """tcgen05 GEMM  out = a @ w^T  (bf16 in, fp32 accumulate). See csrc/kernels/gemm_bf16.cu."""
     M = a.shape[-2]
     N = w.shape[-2]
@@ -102,7 +103,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
         out = torch.empty(*a.shape[:-1], n_out, dtype=dt, device=a.device)
     _ext().gemm_bf16(a, w, epi, out, bias, list(dst_ptrs), list(arrive_ptrs), done_ticket,
                      reset_on_done, rows_per_owner, group_counts, row_meta, ag_flags, ag_expected,
-                     ag_rows_per_src, ag_ticket, status_word(a.device), bn, splits, act, m_tiles)
+                     ag_rows_per_src, ag_ticket, status_word(a.device), bn, splits, act, m_tiles, dst_ld)
     _bump()
     return out
 
@@ -124,11 +125,11 @@ def paged_prefill(q, k_cache, v_cache, block_tables, tile_seq, tile_q0, q_start,
 def finalize_norm(*, rows: int, n: int, acc=None, arrive=None, expected: int = 0, ticket=None,
                   residual_in=None, residual_out=None, bias=None, norm_w=None, eps: float = 1e-5,
                   w_offset: float = 0.0, out_ptrs: Sequence[int] = (), out_flag_ptrs: Sequence[int] = (),
-                  out_row_off: int = 0, router_w=None, top_k: int = 0, experts_per_rank: int = 0,
+                  out_row_off: int = 0, out_row_map=None, router_w=None, top_k: int = 0, experts_per_rank: int = 0,
                   routed_scale: float = 1.0, slab_ptrs: Sequence[int] = (), meta_ptrs: Sequence[int] = (),
                   cnt_ptrs: Sequence[int] = (), cap: int = 0, my_rank: int = 0, device=None) -> None:
     _ext().finalize_norm(acc, arrive, expected, ticket, residual_in, residual_out, bias, norm_w, eps,
-                         w_offset, list(out_ptrs), list(out_flag_ptrs), out_row_off, rows, n,
+                         w_offset, list(out_ptrs), list(out_flag_ptrs), out_row_off, out_row_map, rows, n,
                          status_word(device), router_w, top_k, experts_per_rank, routed_scale,
                          list(slab_ptrs), list(meta_ptrs), list(cnt_ptrs), cap, my_rank)
     _bump()

@@ -1,0 +1,143 @@
+"""End-to-end engine checks on a GPU against the fp32 CPU oracle."""
+import os
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk(preset_name, *, seed=3, std=0.08, weights=None, **kw):
+    from oxide_tech_llm_engine_b200.config import EngineConfig
+    from oxide_tech_llm_engine_b200.engine.engine import LLMEngine
+    from oxide_tech_llm_engine_b200.models.config import preset
+    from oxide_tech_llm_engine_b200.models.weights import SyntheticSource
+
+    mc = preset(preset_name) if weights is None else weights.cfg
+    src = weights or SyntheticSource(mc, seed=seed, std=std)
+    base = dict(model=preset_name, max_num_seqs=8, max_num_batched_tokens=256, num_kv_blocks=256,
+                ctx_size=1024, graph_buckets=(1, 2, 4, 8))
+    base.update(kw)
+    return LLMEngine(EngineConfig(**base), mc, weights=src), mc, src
+
+
+def _oracle_tokens(mc, src, prompt, n):
+    from oxide_tech_llm_engine_b200.models.reference import ReferenceModel
+
+    return ReferenceModel(mc, src).generate_greedy(prompt, n)
+
+
+def _agreement(a, b):
+    n = min(len(a), len(b))
+    same = 0
+    for x, y in zip(a[:n], b[:n]):
+        if x != y:
+            break
+        same += 1
+    return same / max(n, 1)
+
+
+@pytest.mark.parametrize("name", ["tiny", "tiny-moe"])
+def test_engine_matches_oracle(name):
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    eng, mc, src = _mk(name)
+    rng = np.random.default_rng(1)
+    prompts = [rng.integers(3, mc.vocab_size, size=n).tolist() for n in (4, 33, 100, 17)]
+    outs = eng.generate(prompts, SamplingParams(greedy=True, max_tokens=12, ignore_eos=True))
+    eng.check_device_status()
+    agree = [_agreement(o, _oracle_tokens(mc, src, p, 12)) for o, p in zip(outs, prompts)]
+    # bf16 activations against an fp32 oracle: allow late divergence on near-ties
+    assert np.mean(agree) >= 0.75 and min(agree) >= 0.25, (agree, outs)
+    eng.close()
+
+
+def test_first_step_logits_close():
+    from oxide_tech_llm_engine_b200.models.reference import ReferenceModel
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    eng, mc, src = _mk("tiny")
+    prompt = np.random.default_rng(2).integers(3, mc.vocab_size, size=50).tolist()
+    eng.add_request(prompt, SamplingParams(greedy=True, max_tokens=2, ignore_eos=True))
+    eng.step()
+    got = eng.model.logits[0].float().cpu()
+    ref = ReferenceModel(mc, src).forward(prompt)[0]
+    cos = torch.nn.functional.cosine_similarity(got, ref, dim=0).item()
+    assert cos > 0.995, cos
+    assert int(got.argmax()) == int(ref.argmax())
+    eng.close()
+
+
+def test_chunked_prefill_graph_and_prefix_cache_are_consistent():
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    sp = SamplingParams(greedy=True, max_tokens=10, ignore_eos=True)
+    rng = np.random.default_rng(4)
+    shared = rng.integers(3, 1000, size=64).tolist()
+    prompts = [shared + rng.integers(3, 1000, size=n).tolist() for n in (9, 21, 40)]
+    eng, mc, src = _mk("tiny")
+    base = eng.generate(prompts, sp)
+    # same prompts again: served from the radix cache
+    again = eng.generate(prompts, sp)
+    st = eng.sched.radix_stats()
+    assert st["hit_tokens"] >= 3 * 64, st
+    assert again == base
+    eng.close()
+    # small chunks, no graphs
+    eng2, _, _ = _mk("tiny", chunk_max=32, chunk_min=16, max_num_batched_tokens=48, cuda_graph=False,
+                     enable_radix=False)
+    small = eng2.generate(prompts, sp)
+    eng2.close()
+    agree = [_agreement(a, b) for a, b in zip(base, small)]
+    assert np.mean(agree) >= 0.9, (agree, base, small)
+
+
+@pytest.mark.parametrize("qtype", ["Q8_0", "Q4_K", "Q4_0"])
+def test_gguf_quantized_serving(qtype):
+    from oxide_tech_llm_engine_b200.models.config import preset
+    from oxide_tech_llm_engine_b200.models.weights import open_weights, write_synthetic_gguf
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    mc = preset("tiny", d_model=256, ffn_dim=512, head_dim=64)
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "m.gguf")
+        write_synthetic_gguf(path, mc, seed=5, weight_type=qtype, embed_type="Q8_0", std=0.08)
+        src = open_weights(path)
+        eng, mc2, _ = _mk("tiny", weights=src)
+        assert eng.model.weight_mode == "quant"
+        rng = np.random.default_rng(6)
+        prompts = [rng.integers(3, mc.vocab_size, size=n).tolist() for n in (6, 40)]
+        outs = eng.generate(prompts, SamplingParams(greedy=True, max_tokens=10, ignore_eos=True))
+        eng.check_device_status()
+        agree = [_agreement(o, _oracle_tokens(mc2, src, p, 10)) for o, p in zip(outs, prompts)]
+        assert np.mean(agree) >= 0.7, (agree, outs)
+        eng.close()
+
+
+def test_sampling_and_cancel_and_speculative():
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    eng, mc, src = _mk("tiny", speculative="ngram")
+    rng = np.random.default_rng(7)
+    p = rng.integers(3, 1000, size=20).tolist()
+    a = eng.generate([p], SamplingParams(temperature=0.9, top_k=20, top_p=0.9, seed=11, max_tokens=8,
+                                         ignore_eos=True))
+    b = eng.generate([p], SamplingParams(temperature=0.9, top_k=20, top_p=0.9, seed=11, max_tokens=8,
+                                         ignore_eos=True))
+    assert a == b and len(a[0]) == 8
+    rid = eng.add_request(p, SamplingParams(greedy=True, max_tokens=50, ignore_eos=True))
+    eng.step()
+    assert eng.cancel(rid)
+    assert not eng.has_work()
+    free0 = eng.sched.num_free_blocks()
+    # repetitive prompt: the n-gram drafter gets tokens accepted, results equal plain greedy
+    rep = (rng.integers(3, 1000, size=8).tolist()) * 6
+    spec = eng.generate([rep], SamplingParams(greedy=True, max_tokens=16, ignore_eos=True))
+    eng.close()
+    eng2, _, _ = _mk("tiny")
+    plain = eng2.generate([rep], SamplingParams(greedy=True, max_tokens=16, ignore_eos=True))
+    eng2.close()
+    assert _agreement(spec[0], plain[0]) >= 0.75, (spec, plain)
+    assert free0 > 0

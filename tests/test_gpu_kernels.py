@@ -84,8 +84,8 @@ def test_gemm_swiglu_epilogue(ops):
     a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16) * 0.5
     wg = torch.randn(i, k, device=DEV, dtype=torch.bfloat16) * 0.05
     wu = torch.randn(i, k, device=DEV, dtype=torch.bfloat16) * 0.05
-    # interleave per output tile: [gate 0..bn/2) | up 0..bn/2) | gate bn/2.. | ...
-    h = bn // 2
+    # gate and up rows interleaved in units of 32: [gate 0..32) | up 0..32) | gate 32..64) | ...
+    h = 32
     w = torch.stack([wg.view(i // h, h, k), wu.view(i // h, h, k)], 1).reshape(2 * i, k).contiguous()
     out = ops.gemm(a, w, epi=ops.EPI_SWIGLU_BF16, bn=bn)
     torch.cuda.synchronize()
@@ -113,7 +113,8 @@ def test_gemm_grouped_combine(ops):
         if c:
             ref = a[g, :c].float() @ w[g].float().T
             assert _rel_err(out[g, :c], ref) < 1.5e-2
-        assert out[g, c:].abs().max().item() == 0.0
+        if c < cap:
+            assert out[g, c:].abs().max().item() == 0.0
     # weighted scatter-add through the row meta table (MoE combine on one rank)
     T = 300
     meta = torch.zeros(G, cap, 4, dtype=torch.int32, device=DEV)
