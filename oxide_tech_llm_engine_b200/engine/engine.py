@@ -150,6 +150,7 @@ class LLMEngine:
         self.requests: dict[int, RequestState] = {}
         self._next_id = 0
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.graph_launches: dict[int, int] = {}
         self.stats = {"steps": 0, "decode_tokens": 0, "prefill_tokens": 0, "graph_replays": 0,
                       "h2d_bytes": 0, "d2h_bytes": 0, "degraded": False}
         self.stop_ids_default = [mc.eos_id]
@@ -299,12 +300,15 @@ class LLMEngine:
             self.model.forward(s)
             torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
+            c0 = ops.launch_count
             with torch.cuda.graph(g):
                 self.model.forward(s)
+            self.graph_launches[bucket] = ops.launch_count - c0
             self.graphs[bucket] = g
             # the capture did not execute; the warm-up run already produced this step's state
             return self.model.logits[:s.n_logits]
         g.replay()
+        ops.launch_count += self.graph_launches[bucket]  # kernels inside the replayed graph
         self.stats["graph_replays"] += 1
         return self.model.logits[:s.n_logits]
 

@@ -370,7 +370,7 @@ class DeviceModel:
                 self._finalize(rpr, self.layers[li + 1]["attn_norm"], acc=1, gather="gather0", flag_base=F_AG0,
                                r0=r0)
         # ---- final norm (logit rows only) + vocab-parallel LM head ----
-        n_log = s.n_logits
+        n_log = max(s.n_logits, 1)  # a step without logit rows still drains the last accumulator
         row_map = s.logit_map[r0:r0 + rpr] if s.logit_map is not None else None
         self._finalize(rpr, self.out_norm, acc=1, gather="lmg", flag_base=F_LMG, r0=r0 if row_map is None else 0,
                        row_map=row_map)
@@ -438,7 +438,7 @@ class DeviceModel:
             self._qlinear(L["ffn_down"], self.act[:M], acc1[:M])
             if li != cfg.n_layers - 1:
                 self._finalize(M, self.layers[li + 1]["attn_norm"], acc=1, gather="gather0", flag_base=F_AG0, r0=0)
-        n_log = s.n_logits
+        n_log = max(s.n_logits, 1)
         self._finalize(M, self.out_norm, acc=1, gather="lmg", flag_base=F_LMG, r0=0, row_map=s.logit_map[:M])
         lmg = self.ws.local("lmg")[:n_log]
         self._qlinear(self.lm_head_q, lmg, self.logits[:n_log])

@@ -1,0 +1,59 @@
+"""Worker of the multi-GPU tests (launched under torchrun, one rank per GPU): runs the tiny dense
+and MoE models tensor/expert parallel through the fused peer-memory path and checks the tokens
+against the fp32 oracle on rank 0."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+
+def main():
+    from _util import assert_consistent
+    from oxide_tech_llm_engine_b200.config import EngineConfig
+    from oxide_tech_llm_engine_b200.engine.engine import LLMEngine
+    from oxide_tech_llm_engine_b200.models.config import preset
+    from oxide_tech_llm_engine_b200.models.weights import SyntheticSource
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    ok = True
+    for name in sys.argv[1:] or ["tiny", "tiny-moe"]:
+        mc = preset(name, n_heads=8, n_kv_heads=8 if world > 2 else 2, d_model=256, ffn_dim=512, head_dim=64) \
+            if world > 2 else preset(name)
+        src = SyntheticSource(mc, seed=3, std=0.08)
+        cfg = EngineConfig(tp=world, max_num_seqs=8, max_num_batched_tokens=256, num_kv_blocks=256,
+                           ctx_size=1024, graph_buckets=(8,), cuda_graph=True)
+        eng = LLMEngine(cfg, mc, weights=src, rank=rank, world=world, device=dev)
+        rng = np.random.default_rng(1)
+        prompts = [rng.integers(3, mc.vocab_size, size=n).tolist() for n in (4, 33, 100, 17)]
+        outs = eng.generate(prompts, SamplingParams(greedy=True, max_tokens=12, ignore_eos=True))
+        torch.cuda.synchronize()
+        eng.check_device_status()
+        gathered = [None] * world
+        dist.all_gather_object(gathered, outs)
+        if rank == 0:
+            same = all(g == outs for g in gathered)
+            try:
+                assert same, "ranks disagree on the generated tokens"
+                assert_consistent(mc, src, prompts, outs)
+                print(f"TP_CHECK {name} world={world} OK replays={eng.stats['graph_replays']}", flush=True)
+            except AssertionError as e:
+                ok = False
+                print(f"TP_CHECK {name} world={world} FAIL {e} {outs}", flush=True)
+        eng.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    if rank == 0 and not ok:
+        sys.exit(1)
+
+
+if __name__ == "__main__":
+    main()

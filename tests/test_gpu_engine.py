@@ -6,6 +6,8 @@ import numpy as np
 import pytest
 import torch
 
+from _util import assert_consistent
+
 pytestmark = pytest.mark.gpu
 
 
@@ -48,9 +50,9 @@ def test_engine_matches_oracle(name):
     prompts = [rng.integers(3, mc.vocab_size, size=n).tolist() for n in (4, 33, 100, 17)]
     outs = eng.generate(prompts, SamplingParams(greedy=True, max_tokens=12, ignore_eos=True))
     eng.check_device_status()
-    agree = [_agreement(o, _oracle_tokens(mc, src, p, 12)) for o, p in zip(outs, prompts)]
-    # bf16 activations against an fp32 oracle: allow late divergence on near-ties
-    assert np.mean(agree) >= 0.75 and min(agree) >= 0.25, (agree, outs)
+    # bf16 activations against an fp32 oracle: near ties may flip, so score each token against
+    # the oracle's logits given the engine's own history
+    assert_consistent(mc, src, prompts, outs)
     eng.close()
 
 
@@ -111,8 +113,7 @@ def test_gguf_quantized_serving(qtype):
         prompts = [rng.integers(3, mc.vocab_size, size=n).tolist() for n in (6, 40)]
         outs = eng.generate(prompts, SamplingParams(greedy=True, max_tokens=10, ignore_eos=True))
         eng.check_device_status()
-        agree = [_agreement(o, _oracle_tokens(mc2, src, p, 10)) for o, p in zip(outs, prompts)]
-        assert np.mean(agree) >= 0.7, (agree, outs)
+        assert_consistent(mc2, src, prompts, outs)
         eng.close()
 
 
