@@ -146,6 +146,47 @@ def load(name: str):
         return mod
 
 
+def _noalloc_sources() -> list[Path]:
+    return [_CSRC / "noalloc" / "paged_decode_noalloc.cu", _CSRC / "kernels" / "attn_decode.cu"]
+
+
+def noalloc_hash() -> str:
+    h = hashlib.sha256()
+    for p in _noalloc_sources() + [_CSRC / "noalloc" / "oxb_noalloc.h", _CSRC / "kernels" / "attn.cuh"]:
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    return h.hexdigest()
+
+
+def build_noalloc() -> Path:
+    """Plain C-ABI shared library (no torch, no Python): `liboxb_noalloc.so`."""
+    import subprocess
+
+    _EXT.mkdir(exist_ok=True)
+    so = _EXT / "liboxb_noalloc.so"
+    cmd = ["nvcc", "-shared", "-Xcompiler", "-fPIC", "-gencode", "arch=compute_100a,code=sm_100a",
+           "-lineinfo", "-O3", "-std=c++17", "-cudart", "shared", "-o", str(so)]
+    cmd += [str(p) for p in _noalloc_sources()]
+    subprocess.run(cmd, check=True, capture_output=True)
+    (_EXT / "liboxb_noalloc.hash").write_text(noalloc_hash())
+    return so
+
+
+def noalloc_lib_path() -> Path:
+    """Path of the allocation-free C library, built on demand when a compiler is present."""
+    import shutil
+
+    so = _EXT / "liboxb_noalloc.so"
+    st = _EXT / "liboxb_noalloc.hash"
+    fresh = so.exists() and st.exists() and st.read_text().strip() == noalloc_hash()
+    if not fresh:
+        if shutil.which("nvcc") is not None and os.environ.get("OXB_NO_BUILD", "0") != "1":
+            build_noalloc()
+        elif not so.exists():
+            raise ImportError("liboxb_noalloc.so is not built and nvcc is not available")
+    return so
+
+
 def cuda_ext():
     return load("oxb_cuda")
 
