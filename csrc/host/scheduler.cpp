@@ -207,15 +207,21 @@ StepPlan Scheduler::schedule() {
   int budget = prefill_budget(n_dec_tokens);
 
   // ---- 2. continuing prefill chunks ----
-  for (size_t k = 0; k < running_.size() && budget > 0; ++k) {
+  // While requests are waiting for a free slot's worth of budget, long prompts already in
+  // flight take at most half of the step so that short newcomers are not stuck behind them.
+  const bool newcomers = !waiting_.empty() && static_cast<int>(running_.size()) < cfg_.max_num_seqs;
+  int continuing_budget = budget;
+  if (newcomers) continuing_budget = std::max(std::min(cfg_.chunk_min, budget), budget / 2);
+  for (size_t k = 0; k < running_.size() && budget > 0 && continuing_budget > 0; ++k) {
     Request* r = running_[k].get();
     if (r->phase != Phase::Prefill) continue;
     const int remaining = static_cast<int>(r->tokens.size()) - r->computed;
-    const int c = std::min(remaining, budget);
+    const int c = std::min(remaining, std::min(budget, continuing_budget));
     if (c <= 0) continue;
     if (!ensure_blocks(r, c, &plan)) continue;
     chunks.push_back({r, c, 1});
     budget -= c;
+    continuing_budget -= c;
   }
 
   // ---- 3. admission of waiting requests ----

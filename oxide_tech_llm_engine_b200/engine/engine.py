@@ -86,6 +86,10 @@ class LLMEngine:
                  random_init: bool = False):
         self.cfg = cfg
         self.rank, self.world = rank, world
+        self.cpu = cfg.backend == "cpu"
+        if self.cpu:
+            self._init_cpu(cfg, model_cfg, weights)
+            return
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         if model_cfg is None:
             if weights is not None:
@@ -160,6 +164,68 @@ class LLMEngine:
 
             self._drafter = NgramDrafter(cfg.draft_tokens)
 
+    def _init_cpu(self, cfg: EngineConfig, model_cfg, weights) -> None:
+        """fp32 torch backend over the same scheduler / block manager (no GPU needed)."""
+        from ..models.cpu_model import CpuPagedModel
+        from ..models.weights import SyntheticSource
+
+        self.device = torch.device("cpu")
+        if model_cfg is None:
+            model_cfg = weights.cfg if weights is not None else preset(cfg.model)
+        if weights is None:
+            weights = SyntheticSource(model_cfg, seed=cfg.seed)
+        self.model_cfg = mc = model_cfg
+        H = host_ext()
+        self.block = H.TOKENS_PER_BLOCK
+        self.max_blocks_per_seq = (min(cfg.ctx_size, mc.max_ctx) + self.block - 1) // self.block
+        num_blocks = cfg.num_kv_blocks if cfg.num_kv_blocks > 0 else min(
+            4096, cfg.max_num_seqs * self.max_blocks_per_seq + 16)
+        self.model = CpuPagedModel(mc, weights, num_blocks)
+        sc = H.SchedulerConfig()
+        sc.num_blocks = num_blocks
+        sc.max_num_seqs = cfg.max_num_seqs
+        sc.max_num_batched_tokens = cfg.max_num_batched_tokens
+        sc.max_blocks_per_seq = self.max_blocks_per_seq
+        sc.chunk_min, sc.chunk_max = cfg.chunk_min, cfg.chunk_max
+        sc.sla_itl_us, sc.base_us, sc.per_token_us = cfg.sla_itl_us, cfg.base_us, cfg.per_token_us
+        sc.enable_radix = cfg.enable_radix
+        sc.sla_budget = cfg.sla_budget
+        self.sched = H.Scheduler(sc)
+        self.requests = {}
+        self._next_id = 0
+        self.graphs, self.graph_launches = {}, {}
+        self.stats = {"steps": 0, "decode_tokens": 0, "prefill_tokens": 0, "graph_replays": 0,
+                      "h2d_bytes": 0, "d2h_bytes": 0, "degraded": False}
+        self.stop_ids_default = [mc.eos_id]
+        self._drafter = None
+        if cfg.speculative in ("ngram", "auto"):
+            from .spec_decode import NgramDrafter
+
+            self._drafter = NgramDrafter(cfg.draft_tokens)
+
+    def _step_cpu(self, plan) -> np.ndarray:
+        if plan.cow_src.size:
+            self.model.copy_blocks(plan.cow_src, plan.cow_dst)
+        logits = self.model.forward_plan(plan).numpy()
+        toks = np.zeros(plan.logit_rows.size, dtype=np.int32)
+        for i, rid in enumerate(plan.logit_req):
+            r = self.requests.get(int(rid))
+            row = logits[i]
+            mask = None
+            if r is not None and r.grammar is not None:
+                mask = r.grammar.allow_mask(self.model_cfg.vocab_size)
+            if r is None or (r.params.is_greedy() and mask is None):
+                toks[i] = int(row.argmax())
+                continue
+            if r.host_sampler is None:
+                from ..sampler import HostSampler
+
+                r.host_sampler = HostSampler(r.params)
+            hist = self.sched.request_tokens(r.req_id)
+            hist = hist[r.prompt_len:] if hist is not None else np.zeros(0, np.int32)
+            toks[i] = r.host_sampler.sample(row, hist, mask)
+        return toks
+
     # ------------------------------------------------------------------ sizing
     def _auto_blocks(self, mc: ModelConfig, weight_mode: str, has_weights: bool) -> int:
         free, total = torch.cuda.mem_get_info(self.device)
@@ -200,9 +266,14 @@ class LLMEngine:
         if params.grammar:
             from ..grammar import grammar_from_spec
 
-            st.grammar = grammar_from_spec(params.grammar)
+            st.grammar = grammar_from_spec(params.grammar, getattr(self, "vocab_bytes", None))
         self.requests[rid] = st
         return rid
+
+    def set_tokenizer(self, tokenizer) -> None:
+        """Gives grammars the byte strings of the vocabulary and the engine the stop ids."""
+        self.vocab_bytes = tokenizer.vocab_bytes()
+        self.stop_ids_default = tokenizer.stop_ids()
 
     def cancel(self, req_id: int) -> bool:
         ok, events = self.sched.cancel(req_id)
@@ -320,10 +391,13 @@ class LLMEngine:
             return []
         if self._drafter is not None:
             pass  # drafts are attached after update(), see below
-        s, bucket = self._fill(plan)
-        logits = self._forward(s, bucket)
-        n_rows = plan.logit_rows.size
-        tokens = self._sample(plan, logits, n_rows)
+        if self.cpu:
+            tokens = self._step_cpu(plan)
+        else:
+            s, bucket = self._fill(plan)
+            logits = self._forward(s, bucket)
+            n_rows = plan.logit_rows.size
+            tokens = self._sample(plan, logits, n_rows)
         events = self.sched.update(plan, tokens)
         self.stats["steps"] += 1
         self.stats["decode_tokens"] += plan.n_decode
@@ -381,7 +455,8 @@ class LLMEngine:
             for j, i in enumerate(need_host):
                 r = reqs[i]
                 hist = self.sched.request_tokens(r.req_id)
-                toks[i] = r.host_sampler.sample(rows[j], hist if hist is not None else np.zeros(0, np.int32))
+                hist = hist[r.prompt_len:] if hist is not None else np.zeros(0, np.int32)
+                toks[i] = r.host_sampler.sample(rows[j], hist)
         return toks
 
     def _gather_logits(self, logits, all_greedy: bool, n_log: int):
@@ -449,8 +524,10 @@ class LLMEngine:
         return [self.requests[i].output for i in ids]
 
     def check_device_status(self) -> None:
-        ops.check_status(self.device)
+        if not self.cpu:
+            ops.check_status(self.device)
 
     def close(self) -> None:
         self.graphs.clear()
-        self.model.close()
+        if not self.cpu:
+            self.model.close()

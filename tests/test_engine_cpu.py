@@ -1,0 +1,173 @@
+"""The whole engine on the CPU backend: scheduler + block manager + radix cache + paged fp32
+model + samplers, against the contiguous-cache oracle (no GPU)."""
+import numpy as np
+import pytest
+
+from oxide_tech_llm_engine_b200.config import EngineConfig
+from oxide_tech_llm_engine_b200.engine.engine import LLMEngine
+from oxide_tech_llm_engine_b200.engine.handle import EngineHandle
+from oxide_tech_llm_engine_b200.models.config import preset
+from oxide_tech_llm_engine_b200.models.reference import ReferenceModel
+from oxide_tech_llm_engine_b200.models.weights import SyntheticSource
+from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+
+def mk(name="tiny", **kw):
+    mc = preset(name)
+    src = SyntheticSource(mc, seed=3, std=0.08)
+    base = dict(backend="cpu", max_num_seqs=4, max_num_batched_tokens=64, chunk_max=32, chunk_min=8,
+                num_kv_blocks=96, ctx_size=512)
+    base.update(kw)
+    return LLMEngine(EngineConfig(**base), mc, weights=src), mc, src
+
+
+GREEDY = SamplingParams(greedy=True, max_tokens=8, ignore_eos=True)
+
+
+@pytest.mark.parametrize("name", ["tiny", "tiny-moe"])
+def test_paged_engine_equals_oracle(name):
+    eng, mc, src = mk(name)
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(3, 1000, size=n).tolist() for n in (5, 40, 70, 17, 33)]  # 5 > max_num_seqs
+    outs = eng.generate(prompts, GREEDY)
+    ref = [ReferenceModel(mc, src).generate_greedy(p, 8) for p in prompts]
+    assert outs == ref
+    assert eng.sched.num_free_blocks() + eng.sched.radix_stats()["cached_blocks"] == 96
+
+
+def test_two_clients_get_exactly_max_tokens_and_prefix_reuse():
+    eng, mc, src = mk()
+    events = {0: [], 1: []}
+    p = list(range(10, 60))
+    a = eng.add_request(p, SamplingParams(greedy=True, max_tokens=6, ignore_eos=True),
+                        on_token=lambda r, e: events[0].append(e))
+    b = eng.add_request(p[:20], SamplingParams(greedy=True, max_tokens=9, ignore_eos=True),
+                        on_token=lambda r, e: events[1].append(e))
+    while eng.has_work():
+        eng.step()
+    assert len(events[0]) == 6 and len(events[1]) == 9
+    assert events[0][-1].finished and events[0][-1].reason == "length" and not events[0][0].finished
+    # multi-turn: prompt + answer + new user turn hits the cache
+    turn2 = p + eng.requests[a].output + [7, 8, 9]
+    eng.generate([turn2], GREEDY)
+    st = eng.sched.radix_stats()
+    assert st["hit_tokens"] >= 48
+    ref = ReferenceModel(mc, src).generate_greedy(turn2, 8)
+    assert eng.requests[max(eng.requests)].output == ref
+
+
+def test_chunked_prefill_interleaves_with_short_request():
+    eng, mc, src = mk(chunk_max=8, chunk_min=4, max_num_batched_tokens=12)
+    long_p = list(range(100, 190))
+    eng.add_request(long_p, GREEDY)
+    eng.step()
+    short = eng.add_request([5, 6, 7], SamplingParams(greedy=True, max_tokens=3, ignore_eos=True))
+    steps = 0
+    while not eng.requests[short].finished:
+        eng.step()
+        steps += 1
+    # the short request finished while the long prompt was still being prefilled in 8-token chunks
+    assert eng.sched.request_info(0)["computed"] < len(long_p)
+    while eng.has_work():
+        eng.step()
+    assert eng.requests[0].output == ReferenceModel(mc, src).generate_greedy(long_p, 8)
+
+
+def test_radix_lru_eviction_under_pressure():
+    eng, mc, src = mk(num_kv_blocks=24, max_num_seqs=2)
+    rng = np.random.default_rng(5)
+    for i in range(8):
+        eng.generate([rng.integers(3, 1000, size=60).tolist()], SamplingParams(greedy=True, max_tokens=2, ignore_eos=True))
+    st = eng.sched.radix_stats()
+    assert st["cached_blocks"] <= 24 and eng.sched.num_free_blocks() >= 0
+    # everything still works and is correct after evictions
+    p = rng.integers(3, 1000, size=50).tolist()
+    assert eng.generate([p], GREEDY)[0] == ReferenceModel(mc, src).generate_greedy(p, 8)
+
+
+def test_preemption_recompute_is_transparent():
+    eng, mc, src = mk(num_kv_blocks=10, enable_radix=False, max_num_seqs=3)
+    rng = np.random.default_rng(6)
+    prompts = [rng.integers(3, 1000, size=40).tolist() for _ in range(3)]
+    sp = SamplingParams(greedy=True, max_tokens=30, ignore_eos=True)
+    outs = eng.generate(prompts, sp)
+    assert eng.sched.preemptions() > 0
+    assert outs == [ReferenceModel(mc, src).generate_greedy(p, 30) for p in prompts]
+
+
+def test_speculative_ngram_equals_plain_greedy():
+    eng, mc, src = mk(speculative="ngram")
+    rep = [11, 12, 13, 14, 15, 16] * 6
+    sp = SamplingParams(greedy=True, max_tokens=20, ignore_eos=True)
+    spec = eng.generate([rep], sp)[0]
+    assert spec == ReferenceModel(mc, src).generate_greedy(rep, 20)
+    assert eng.stats["steps"] > 0
+
+
+def test_sampling_seed_determinism_and_stop_ids():
+    eng, mc, src = mk()
+    p = list(range(20, 40))
+    sp = SamplingParams(temperature=0.9, top_k=30, top_p=0.9, min_p=0.02, seed=7, max_tokens=10, ignore_eos=True)
+    a = eng.generate([p], sp)[0]
+    b = eng.generate([p], sp)[0]
+    c = eng.generate([p], SamplingParams(temperature=0.9, top_k=30, top_p=0.9, min_p=0.02, seed=8, max_tokens=10,
+                                         ignore_eos=True))[0]
+    assert a == b and len(a) == 10 and a != c
+    first = ReferenceModel(mc, src).generate_greedy(p, 1)[0]
+    out = eng.generate([p], SamplingParams(greedy=True, max_tokens=10, stop_token_ids=[first]))[0]
+    assert out == [first] and eng.requests[max(eng.requests)].finish_reason == "stop"
+
+
+def test_cancel_and_prefill_fault_free_everything():
+    eng, mc, src = mk()
+    free0 = eng.sched.num_free_blocks()
+    rid = eng.add_request(list(range(50)), SamplingParams(greedy=True, max_tokens=100, ignore_eos=True))
+    other = eng.add_request(list(range(60, 90)), GREEDY)
+    eng.step()
+    eng.sched.inject_prefill_error(rid, "boom")
+    while eng.has_work():
+        eng.step()
+    assert eng.requests[rid].finish_reason == "prefill_error: boom"
+    assert eng.requests[other].output == ReferenceModel(mc, src).generate_greedy(list(range(60, 90)), 8)
+    rid2 = eng.add_request(list(range(50)), SamplingParams(greedy=True, max_tokens=100, ignore_eos=True))
+    eng.step(); eng.step()
+    assert eng.cancel(rid2) and not eng.has_work()
+    assert eng.sched.num_free_blocks() + eng.sched.radix_stats()["cached_blocks"] == free0
+
+
+def test_engine_handle_threads_and_failure_isolation():
+    eng, mc, src = mk()
+    h = EngineHandle(eng)
+    try:
+        p = list(range(30, 50))
+        out, reason = h.generate(p, GREEDY)
+        assert out == ReferenceModel(mc, src).generate_greedy(p, 8) and reason == "length"
+        # an inadmissible request (empty prompt) fails alone
+        st = h.submit([], GREEDY)
+        ev = st.get(timeout=30)
+        assert ev.finished and ev.reason.startswith("prefill_error")
+        out2, _ = h.generate(p, GREEDY)
+        assert out2 == out and h.active_slots() == 0
+    finally:
+        h.shutdown()
+
+
+def test_grammar_constrained_json_is_valid():
+    import json
+
+    from oxide_tech_llm_engine_b200.tokenizer import Tokenizer
+
+    eng, mc, src = mk()
+    tok = Tokenizer.ascii_fallback(mc.vocab_size)
+    eng.set_tokenizer(tok)
+    sp = SamplingParams(temperature=0.8, top_k=50, seed=3, max_tokens=60, grammar='json_prefix:{"a": "', ignore_eos=True)
+    rid = eng.add_request(tok.encode("give json"), sp)
+    while eng.has_work():
+        eng.step()
+        r = eng.requests[rid]
+        if r.grammar.done():
+            eng.cancel(rid)
+    text = tok.decode(eng.requests[rid].output)
+    assert text.startswith('{"a": "')
+    if eng.requests[rid].grammar.done():
+        json.loads(text)

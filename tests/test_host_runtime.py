@@ -1,0 +1,210 @@
+"""C++ host runtime: block pool, sequence block tables, radix prefix cache, scheduler core (CPU)."""
+import threading
+
+import numpy as np
+import pytest
+
+from oxide_tech_llm_engine_b200._build import host_ext
+
+
+@pytest.fixture(scope="module")
+def H():
+    return host_ext()
+
+
+def test_block_pool_refcounts(H):
+    p = H.BlockPool(4)
+    a, b = p.allocate(), p.allocate()
+    assert p.num_free() == 2 and p.ref_count(a) == 1
+    p.retain(a)
+    assert not p.release(a) and p.ref_count(a) == 1
+    assert p.release(a) and p.num_free() == 3
+    with pytest.raises(RuntimeError):
+        p.release(a)
+    c, d, e = p.allocate(), p.allocate(), p.allocate()
+    assert p.allocate() == -1 and {b, c, d, e} == {0, 1, 2, 3}
+
+
+def test_block_pool_threaded_soak(H):
+    # fork/release storm from 8 threads: every block must come home
+    p = H.BlockPool(64)
+    def work():
+        for _ in range(2000):
+            b = p.allocate()
+            if b >= 0:
+                p.retain(b)
+                p.release(b)
+                p.release(b)
+    ts = [threading.Thread(target=work) for _ in range(8)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert p.num_free() == 64
+
+
+def test_sequence_table_advance_rewind_cow(H):
+    p = H.BlockPool(8)
+    t = H.SequenceBlockTable(p)
+    ok, cow = t.advance(20)
+    assert ok and len(t.blocks()) == 2 and not cow
+    t.commit()
+    ok, _ = t.advance(30)  # speculative growth
+    assert len(t.blocks()) == 4 and t.num_tokens() == 50
+    t.rollback()
+    assert t.num_tokens() == 20 and len(t.blocks()) == 2 and p.num_free() == 6
+    # a second table adopts the (partial) prefix; writing into the shared tail block forks it
+    u = H.SequenceBlockTable(p)
+    u.adopt_prefix(t.blocks(), 20)
+    assert p.ref_count(t.blocks()[1]) == 2
+    ok, cow = u.advance(1)
+    assert ok and cow == [(t.blocks()[1], u.blocks()[1])] and u.blocks()[0] == t.blocks()[0]
+    # exhaustion leaves the table untouched
+    big = H.SequenceBlockTable(p)
+    ok, _ = big.advance(16 * 100)
+    assert not ok and big.num_tokens() == 0
+    u.release_all(); t.release_all()
+    assert p.num_free() == 8
+
+
+def test_h2o_prune_keeps_sinks_heavy_hitters_and_tail(H):
+    p = H.BlockPool(64)
+    t = H.SequenceBlockTable(p)
+    t.advance(16 * 20 - 5)
+    scores = [0.0] * 20
+    scores[7], scores[11] = 9.0, 5.0
+    kept = t.prune_heavy_hitters(scores, sink_blocks=2, rolling_blocks=3, budget_blocks=7)
+    assert kept == [0, 1, 7, 11, 17, 18, 19]
+    assert t.num_tokens() == 16 * 6 + 11 and p.num_free() == 64 - 7
+
+
+def test_radix_match_insert_split_evict(H):
+    p = H.BlockPool(32)
+    r = H.RadixCache(p)
+    toks = np.arange(64, dtype=np.int32)
+    blocks = [p.allocate() for _ in range(4)]
+    assert r.insert(toks, blocks) == 4 and r.cached_blocks() == 4
+    got, n = r.match(toks, True)
+    assert n == 48 and got == blocks[:3]          # never the whole prompt
+    got, n = r.match(np.concatenate([toks, [1, 2]]).astype(np.int32), True)
+    assert n == 64 and got == blocks
+    # diverge inside the second block: only the first block matches; inserting splits the node
+    other = toks.copy(); other[20] = 999
+    got, n = r.match(other, True)
+    assert n == 16 and got == blocks[:1]
+    ob = [blocks[0]] + [p.allocate() for _ in range(3)]
+    assert r.insert(other, ob) == 3 and r.num_nodes() == 3
+    # blocks still referenced by a sequence cannot be evicted
+    assert r.evict(100) == 0
+    for b in blocks + ob[1:]:
+        p.release(b)
+    assert r.evict(3) >= 3
+    freed_total = 7 - r.cached_blocks()
+    assert p.num_free() == 32 - 7 + freed_total
+    r.clear()
+    assert p.num_free() == 32 and r.cached_blocks() == 0
+
+
+def test_prefill_budget_formula(H):
+    c = H.SchedulerConfig()
+    c.num_blocks = 64
+    s = H.Scheduler(c)
+    # clamp(min((25000 - (2000 + 350 B)) / 25, 2048 - B), 32, 512)
+    assert s.prefill_budget(0) == 512
+    assert s.prefill_budget(40) == int((25000 - (2000 + 350 * 40)) / 25)
+    assert s.prefill_budget(64) == 32       # SLA exhausted -> floor
+    assert s.prefill_budget(2048) == 0
+    c.sla_budget = False
+    assert H.Scheduler(c).prefill_budget(10) == 2038
+
+
+def _drain(s, H, answer=lambda rid, row: 7):
+    events = []
+    for _ in range(10000):
+        if not s.has_work():
+            break
+        plan = s.schedule()
+        if plan.n_tokens == 0:
+            break
+        toks = np.array([answer(int(r), i) for i, r in enumerate(plan.logit_req)], dtype=np.int32)
+        events += s.update(plan, toks)
+    return events
+
+
+def test_scheduler_lifecycle_and_stop_rules(H):
+    c = H.SchedulerConfig()
+    c.num_blocks, c.max_num_seqs, c.chunk_max, c.chunk_min = 64, 4, 16, 8
+    s = H.Scheduler(c)
+    s.add_request(1, np.arange(40, dtype=np.int32), 5, [99], False)
+    s.add_request(2, np.arange(3, dtype=np.int32), 50, [7], False)     # stops on token 7 at once
+    plan = s.schedule()
+    assert plan.n_prefill >= 1 and plan.n_decode == 0 and plan.q_lens[0] == 16   # chunked by chunk_max
+    ev = s.update(plan, np.full(plan.logit_rows.size, 7, dtype=np.int32))
+    ev += _drain(s, H)
+    by = {}
+    for e in ev:
+        by.setdefault(e.req_id, []).append(e)
+    assert [e.token for e in by[1]] == [7] * 5 and by[1][-1].finished and by[1][-1].reason == "length"
+    assert len(by[2]) == 1 and by[2][0].reason == "stop"
+    assert s.num_free_blocks() + s.radix_stats()["cached_blocks"] == 64 and not s.has_work()
+
+
+def test_scheduler_prefix_reuse_and_cancel(H):
+    c = H.SchedulerConfig()
+    c.num_blocks, c.max_num_seqs = 64, 4
+    s = H.Scheduler(c)
+    prompt = np.arange(50, dtype=np.int32)
+    s.add_request(1, prompt, 3, [], True)
+    _drain(s, H)
+    s.add_request(2, np.concatenate([prompt, [5, 6, 7]]).astype(np.int32), 3, [], True)
+    plan = s.schedule()
+    info = s.request_info(2)
+    assert info["prefix_hit"] == 48 and plan.q_lens[0] == 5 and plan.ctx_lens[0] == 53
+    ok, ev = s.cancel(2)
+    assert ok and ev[0].reason == "cancelled" and not s.has_work()
+    assert s.radix_stats()["hit_tokens"] == 48
+
+
+def test_scheduler_preempts_youngest_when_kv_runs_out(H):
+    c = H.SchedulerConfig()
+    c.num_blocks, c.max_num_seqs, c.enable_radix = 6, 4, False
+    s = H.Scheduler(c)
+    for rid in (1, 2, 3):
+        s.add_request(rid, np.arange(30, dtype=np.int32), 40, [], True)
+    ev = _drain(s, H)
+    done = {e.req_id for e in ev if e.finished}
+    assert done == {1, 2, 3} and s.preemptions() > 0
+    counts = {rid: sum(1 for e in ev if e.req_id == rid and e.token >= 0) for rid in (1, 2, 3)}
+    assert counts == {1: 40, 2: 40, 3: 40}
+    assert s.num_free_blocks() == 6
+
+
+def test_scheduler_speculative_accept_and_rollback(H):
+    c = H.SchedulerConfig()
+    c.num_blocks, c.enable_radix = 32, False
+    s = H.Scheduler(c)
+    s.add_request(1, np.arange(10, dtype=np.int32), 20, [], True)
+    plan = s.schedule()
+    s.update(plan, np.array([100], dtype=np.int32))
+    s.set_drafts(1, [101, 102, 555, 104])
+    plan = s.schedule()
+    assert plan.n_decode == 0 and plan.n_prefill == 1 and plan.q_lens[0] == 5 and plan.logit_rows.size == 5
+    assert list(plan.token_ids) == [100, 101, 102, 555, 104]
+    ev = s.update(plan, np.array([101, 102, 103, 0, 0], dtype=np.int32))  # accepts 2 drafts + bonus
+    assert [e.token for e in ev] == [101, 102, 103]
+    info = s.request_info(1)
+    assert info["computed"] == 13 and info["generated"] == 4
+    assert len(info["blocks"]) == 1
+
+
+def test_scheduler_fault_injection_isolated(H):
+    c = H.SchedulerConfig()
+    c.num_blocks = 32
+    s = H.Scheduler(c)
+    s.add_request(1, np.arange(20, dtype=np.int32), 4, [], True)
+    s.add_request(2, np.arange(20, 40, dtype=np.int32), 4, [], True)
+    s.inject_prefill_error(1, "injected")
+    ev = _drain(s, H)
+    r1 = [e for e in ev if e.req_id == 1]
+    r2 = [e for e in ev if e.req_id == 2]
+    assert len(r1) == 1 and r1[0].finished and r1[0].reason == "prefill_error: injected"
+    assert len(r2) == 4 and r2[-1].reason == "length"
+    assert s.num_free_blocks() + s.radix_stats()["cached_blocks"] == 32

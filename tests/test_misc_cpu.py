@@ -1,0 +1,100 @@
+"""Tokenizer, chat templates, CLI parsing, mesh / split planning, RoPE tables, roofline, CSKV (CPU)."""
+import numpy as np
+import pytest
+
+from oxide_tech_llm_engine_b200 import chat_template as ct
+from oxide_tech_llm_engine_b200.cli import engine_config_from_args, normalize_argv, parse_args
+from oxide_tech_llm_engine_b200.errors import BenchmarkIntegrityViolation, ConfigError
+from oxide_tech_llm_engine_b200.models.config import preset
+from oxide_tech_llm_engine_b200.models.rope import inv_freq_table
+from oxide_tech_llm_engine_b200.parallel import mesh
+from oxide_tech_llm_engine_b200.tokenizer import Tokenizer
+from oxide_tech_llm_engine_b200.utils.roofline import RooflineReceipt
+
+
+def test_tokenizer_greedy_longest_match_and_specials():
+    vocab = ["<unk>", "<s>", "</s>", "▁hello", "▁he", "llo", "▁world", "▁", "h", "<|im_end|>", "<0x21>", "w"]
+    t = Tokenizer(vocab, bos_id=1, eos_id=2)
+    ids = t.encode("hello world!<|im_end|>")
+    assert ids == [1, 3, 6, 10, 9]
+    assert t.decode(ids) == "hello world!"
+    assert t.is_stop_token(2) and t.is_stop_token(9) and not t.is_stop_token(3)
+    assert set(t.stop_ids()) == {2, 9}
+
+
+def test_ascii_fallback_round_trip():
+    t = Tokenizer.ascii_fallback(1024)
+    s = "Héllo, wörld! 123"
+    assert t.decode(t.encode(s)) == s
+    assert t.vocab_size == 1024 and len(t.vocab_bytes()) == 1024
+
+
+def test_chat_templates():
+    msgs = [{"role": "system", "content": "S"}, {"role": "user", "content": "U"}]
+    assert ct.render_chat(msgs, ct.ChatFormat.CHATML) == \
+        "<|im_start|>system\nS<|im_end|>\n<|im_start|>user\nU<|im_end|>\n<|im_start|>assistant\n"
+    assert ct.render_chat(msgs, ct.ChatFormat.LLAMA3).startswith("<|begin_of_text|><|start_header_id|>system")
+    assert "[INST] S\n\nU [/INST]" in ct.render_chat(msgs, ct.ChatFormat.MISTRAL)
+    assert ct.render_chat(msgs, ct.ChatFormat.GEMMA).endswith("<start_of_turn>model\n")
+    assert "### Response:" in ct.render_chat(msgs, ct.ChatFormat.ALPACA)
+    assert ct.render_chat(msgs, ct.ChatFormat.RAW) == "S\nU"
+    assert ct.detect("llama", "Meta-Llama-3-8B") == ct.ChatFormat.LLAMA3
+    assert ct.detect("qwen2", "") == ct.ChatFormat.CHATML and ct.detect("gemma2", "") == ct.ChatFormat.GEMMA
+    assert ct.detect("", "DeepSeek-R1") == ct.ChatFormat.DEEPSEEK and ct.parse_format("mistral") == ct.ChatFormat.MISTRAL
+    assert "<|eot_id|>" in ct.stop_strings(ct.ChatFormat.LLAMA3)
+
+
+def test_cli_flags_and_normalisation():
+    assert normalize_argv(["-ngl", "33", "-md", "d.gguf", "--cb"]) == ["--n-gpu-layers", "33", "--draft-model", "d.gguf",
+                                                                       "--continuous-batching"]
+    a = parse_args(["-m", "x.gguf", "-ngl", "20", "-c", "4096", "--temp", "0.2", "--top-k", "10", "--greedy",
+                    "--max-slots", "8", "-b", "cpu", "-p", "hi", "-n", "5", "--speculative", "ngram"])
+    assert a.model == "x.gguf" and a.n_gpu_layers == 20 and a.ctx_size == 4096 and a.greedy and a.max_tokens == 5
+    cfg = engine_config_from_args(a)
+    assert cfg.backend == "cpu" and cfg.max_num_seqs == 8 and cfg.speculative == "ngram" and cfg.ctx_size == 4096
+    s = parse_args(["server", "--port", "9000", "-m", "tiny", "-b", "cpu"])
+    assert s.command == "server" and s.port == 9000
+    d = parse_args([])
+    assert d.temp == 0.7 and d.top_p == 0.95 and d.min_p == 0.05 and d.repeat_penalty == 1.1 and d.top_k == 40 \
+        and d.seed == 42 and d.max_tokens == 512 and d.max_slots == 64 and d.draft_tokens == 5
+    with pytest.raises(ConfigError):
+        parse_args(["-b", "rocm"])
+    with pytest.raises(ConfigError):
+        parse_args(["-b", "nonsense"])
+
+
+def test_mesh_coordinates_and_splits():
+    m = mesh.ParallelMeshConfig(tp=2, cp=2, ep=1, dp=2, pp=2)
+    assert m.world_size == 16
+    seen = set()
+    for r in range(16):
+        c = mesh.MeshCoordinate.from_global_rank(r, m)
+        assert c.to_global_rank(m) == r
+        seen.add((c.tp, c.cp, c.ep, c.dp, c.pp))
+    assert len(seen) == 16
+    assert mesh.MeshCoordinate.from_global_rank(1, m).tp == 1 and mesh.MeshCoordinate.from_global_rank(2, m).cp == 1
+    assert mesh.split_sizes(80, 3) == [27, 27, 26] and sum(mesh.split_sizes(28672, 8, multiple=32)) == 28672
+    assert mesh.layer_partition_for_rank(80, 3, 2) == (54, 80)
+    assert mesh.split_sizes(100, 2, weights=[3, 1]) == [75, 25]
+    st = mesh.RingAttentionStep.plan(32768, 8, 0)
+    assert st.chunk_seq_len == 4096 and st.send_peer == 7 and st.recv_peer == 1
+
+
+def test_rope_tables():
+    base, ms = inv_freq_table(preset("tiny"))
+    assert ms == 1.0 and base[0] == 1.0 and np.all(np.diff(base) < 0)
+    lin, _ = inv_freq_table(preset("tiny", rope_scaling="linear", rope_factor=4.0))
+    assert np.allclose(lin, base / 4)
+    l3, _ = inv_freq_table(preset("tiny", rope_scaling="llama3", rope_factor=8.0, rope_orig_ctx=8192))
+    assert np.isclose(l3[0], base[0]) and np.all(l3 <= base + 1e-12) and l3[-1] < base[-1]
+    yarn, yms = inv_freq_table(preset("tiny", rope_scaling="yarn", rope_factor=4.0, rope_orig_ctx=2048))
+    assert yms > 1.0 and np.isclose(yarn[0], base[0]) and yarn[-1] < base[-1]
+
+
+def test_roofline_receipt_rejects_impossible_numbers():
+    mc = preset("llama3-8b")
+    peaks = {"hbm_gbs": 6531.3, "bf16_tflops": 1627.6, "bf16_tflops_sustained": 1387.6}
+    r = RooflineReceipt.from_run(mc, tokens_per_s=200.0, batch=1, peaks=peaks)
+    assert 0.4 < r.mbu < 0.6 and r.mfu < 0.01
+    with pytest.raises(BenchmarkIntegrityViolation):
+        RooflineReceipt.from_run(mc, tokens_per_s=1138.45 * 4, batch=1, peaks=peaks)
