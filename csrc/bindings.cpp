@@ -51,7 +51,8 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
                const c10::optional<Tensor>& group_counts, const c10::optional<Tensor>& row_meta,
                const c10::optional<Tensor>& ag_flags, int64_t ag_expected, int64_t ag_rows_per_src,
                const c10::optional<Tensor>& ag_ticket, const Tensor& status, int64_t bn,
-               int64_t splits, int64_t act, int64_t m_tiles_override, int64_t dst_ld) {
+               int64_t splits, int64_t act, int64_t m_tiles_override, int64_t dst_ld,
+               int64_t my_rank, int64_t k_stagger) {
   TORCH_CHECK(a.is_cuda() && w.is_cuda(), "gemm_bf16: CUDA tensors required");
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16,
               "gemm_bf16: bf16 operands required");
@@ -89,7 +90,10 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
   s = (total_kb + p.kb_per_split - 1) / p.kb_per_split;
   p.epi = static_cast<int>(epi);
   p.act = static_cast<int>(act);
-  if (epi != oxb::kEpiRedF32) {
+  p.k_stagger = static_cast<int>(k_stagger);
+  const bool routed = epi == oxb::kEpiRedF32 || epi == oxb::kEpiSlabBf16;
+  p.my_rank = static_cast<int>(my_rank);
+  if (!routed) {
     TORCH_CHECK(out.has_value(), "gemm_bf16: out required for store epilogues");
     TORCH_CHECK(s == 1, "gemm_bf16: split-K needs the fp32 reduction epilogue");
     TORCH_CHECK(out->stride(-1) == 1, "gemm_bf16: out must be row-major");
@@ -102,6 +106,7 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
     p.ldc = out->stride(-2);
     p.c_group_stride = out->dim() == 3 ? out->stride(0) : 0;
   } else {
+    TORCH_CHECK(epi == oxb::kEpiRedF32 || s == 1, "gemm_bf16: the slab epilogue cannot split K");
     TORCH_CHECK(!dst_ptrs.empty() && dst_ptrs.size() <= oxb::kMaxRanks, "gemm_bf16: 1..8 owners");
     for (size_t i = 0; i < dst_ptrs.size(); ++i) p.dst[i] = reinterpret_cast<float*>(dst_ptrs[i]);
     for (size_t i = 0; i < arrive_ptrs.size() && i < oxb::kMaxRanks; ++i)
@@ -215,7 +220,8 @@ void paged_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache
 // ---------------------------------------------------------------------------------------------
 // fused finalize kernels
 // ---------------------------------------------------------------------------------------------
-void finalize_norm(const c10::optional<Tensor>& acc, const c10::optional<Tensor>& arrive,
+void finalize_norm(const c10::optional<Tensor>& acc, const c10::optional<Tensor>& rs_slab,
+                   int64_t n_slabs, int64_t slab_stride, const c10::optional<Tensor>& arrive,
                    int64_t expected, const c10::optional<Tensor>& ticket,
                    const c10::optional<Tensor>& residual_in,
                    const c10::optional<Tensor>& residual_out, const c10::optional<Tensor>& bias,
@@ -227,9 +233,12 @@ void finalize_norm(const c10::optional<Tensor>& acc, const c10::optional<Tensor>
                    double routed_scale, const std::vector<int64_t>& slab_ptrs,
                    const std::vector<int64_t>& meta_ptrs, const std::vector<int64_t>& cnt_ptrs,
                    int64_t cap, int64_t my_rank) {
-  TORCH_CHECK(N % 8 == 0, "finalize_norm: N must be a multiple of 8");
+  TORCH_CHECK(N % 8 == 0 && N <= 1024 * 8 * 4, "finalize_norm: N must be a multiple of 8 and <= 32768");
   oxb::FinalizeNormParams p{};
   p.acc = opt_ptr<float>(acc);
+  p.rs_slab = bf16_ptr(rs_slab);
+  p.n_slabs = static_cast<int>(n_slabs);
+  p.slab_stride = slab_stride;
   p.arrive = opt_ptr<uint32_t>(arrive);
   p.expected = static_cast<uint32_t>(expected);
   p.ticket = opt_ptr<uint32_t>(ticket);

@@ -46,14 +46,19 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return r;
 }
 
-constexpr int kNormThreads = 256;
+constexpr int kNormMaxThreads = 1024;
+constexpr int kNormMaxChunks = 4;  // 8-element chunks per thread: N <= 1024 * 8 * 4
 
-__global__ void __launch_bounds__(kNormThreads) finalize_norm_kernel(const FinalizeNormParams p) {
-  extern __shared__ float s_h[];  // N floats
+// One CTA per row; every thread owns up to kNormMaxChunks 8-element chunks, kept in registers.
+// All global loads of a row are issued before the first dependent instruction, so a row costs
+// about one memory round trip however few rows (CTAs) there are.
+__global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const FinalizeNormParams p) {
+  extern __shared__ float s_h[];  // N floats, used only by the MoE router path
   __shared__ float s_red[32];
   __shared__ int s_ok;
   const int row = blockIdx.x;
   const int N = p.N;
+  const int nthr = blockDim.x;
 
   if (p.arrive != nullptr) {
     if (threadIdx.x == 0) {
@@ -72,46 +77,72 @@ __global__ void __launch_bounds__(kNormThreads) finalize_norm_kernel(const Final
     if (!s_ok) return;
   }
 
-  float ss = 0.f;
   const long long roff = static_cast<long long>(row) * N;
-  for (int c = threadIdx.x * 8; c < N; c += kNormThreads * 8) {
-    float h[8];
+  float h[kNormMaxChunks][8];
+  uint4 res[kNormMaxChunks], bia[kNormMaxChunks];
+  // ---- phase 1: issue every load ----
+#pragma unroll
+  for (int ci = 0; ci < kNormMaxChunks; ++ci) {
+    const int c = (ci * nthr + threadIdx.x) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) h[ci][j] = 0.f;
+    res[ci] = make_uint4(0, 0, 0, 0);
+    bia[ci] = make_uint4(0, 0, 0, 0);
+    if (c >= N) continue;
+    if (p.acc != nullptr) {
+      const float4* a = reinterpret_cast<const float4*>(p.acc + roff + c);
+      const float4 x0 = __ldcg(a), x1 = __ldcg(a + 1);
+      h[ci][0] = x0.x; h[ci][1] = x0.y; h[ci][2] = x0.z; h[ci][3] = x0.w;
+      h[ci][4] = x1.x; h[ci][5] = x1.y; h[ci][6] = x1.z; h[ci][7] = x1.w;
+    }
+    if (p.residual_in != nullptr) res[ci] = *reinterpret_cast<const uint4*>(p.residual_in + roff + c);
+    if (p.bias != nullptr) bia[ci] = *reinterpret_cast<const uint4*>(p.bias + c);
+  }
+  if (p.rs_slab != nullptr) {
+    // bf16 partial tiles from every source rank (written by peers): L2-coherent loads
+    for (int sidx = 0; sidx < p.n_slabs; ++sidx) {
+      uint4 v[kNormMaxChunks];
+#pragma unroll
+      for (int ci = 0; ci < kNormMaxChunks; ++ci) {
+        const int c = (ci * nthr + threadIdx.x) * 8;
+        v[ci] = make_uint4(0, 0, 0, 0);
+        if (c < N)
+          v[ci] = __ldcg(reinterpret_cast<const uint4*>(p.rs_slab + sidx * p.slab_stride + roff + c));
+      }
+#pragma unroll
+      for (int ci = 0; ci < kNormMaxChunks; ++ci) {
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v[ci]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) h[ci][j] += __bfloat162float(e[j]);
+      }
+    }
+  }
+  // ---- phase 2: combine, re-arm the accumulator, residual out, sum of squares ----
+  float ss = 0.f;
+#pragma unroll
+  for (int ci = 0; ci < kNormMaxChunks; ++ci) {
+    const int c = (ci * nthr + threadIdx.x) * 8;
+    if (c >= N) continue;
     if (p.acc != nullptr) {
       float4* a = reinterpret_cast<float4*>(p.acc + roff + c);
-      const float4 x0 = __ldcg(a), x1 = __ldcg(a + 1);
-      h[0] = x0.x; h[1] = x0.y; h[2] = x0.z; h[3] = x0.w;
-      h[4] = x1.x; h[5] = x1.y; h[6] = x1.z; h[7] = x1.w;
       const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
       __stcg(a, z);
       __stcg(a + 1, z);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) h[j] = 0.f;
     }
-    if (p.bias != nullptr) {
-      const uint4 b = *reinterpret_cast<const uint4*>(p.bias + c);
-      const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&b);
+    const __nv_bfloat16* rr = reinterpret_cast<const __nv_bfloat16*>(&res[ci]);
+    const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&bia[ci]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) h[j] += __bfloat162float(bb[j]);
-    }
-    if (p.residual_in != nullptr) {
-      const uint4 r = *reinterpret_cast<const uint4*>(p.residual_in + roff + c);
-      const __nv_bfloat16* rr = reinterpret_cast<const __nv_bfloat16*>(&r);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) h[j] += __bfloat162float(rr[j]);
+    for (int j = 0; j < 8; ++j) {
+      h[ci][j] += __bfloat162float(rr[j]) + __bfloat162float(bb[j]);
+      ss += h[ci][j] * h[ci][j];
     }
     if (p.residual_out != nullptr) {
       uint4 o;
-      o.x = pack_bf16x2(h[0], h[1]);
-      o.y = pack_bf16x2(h[2], h[3]);
-      o.z = pack_bf16x2(h[4], h[5]);
-      o.w = pack_bf16x2(h[6], h[7]);
+      o.x = pack_bf16x2(h[ci][0], h[ci][1]);
+      o.y = pack_bf16x2(h[ci][2], h[ci][3]);
+      o.z = pack_bf16x2(h[ci][4], h[ci][5]);
+      o.w = pack_bf16x2(h[ci][6], h[ci][7]);
       *reinterpret_cast<uint4*>(p.residual_out + roff + c) = o;
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      ss += h[j] * h[j];
-      s_h[c + j] = h[j];
     }
   }
   float inv = 1.f;
@@ -123,16 +154,19 @@ __global__ void __launch_bounds__(kNormThreads) finalize_norm_kernel(const Final
   if (p.out_row_map != nullptr) orow = p.out_row_map[row];
   const bool store_out = orow >= 0;
   const long long ooff = orow * static_cast<long long>(N);
-  for (int c = threadIdx.x * 8; c < N; c += kNormThreads * 8) {
+#pragma unroll
+  for (int ci = 0; ci < kNormMaxChunks; ++ci) {
+    const int c = (ci * nthr + threadIdx.x) * 8;
+    if (c >= N) continue;
     float y[8];
     if (p.norm_w != nullptr) {
       const uint4 w = *reinterpret_cast<const uint4*>(p.norm_w + c);
       const __nv_bfloat16* ww = reinterpret_cast<const __nv_bfloat16*>(&w);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) y[j] = s_h[c + j] * inv * (__bfloat162float(ww[j]) + p.w_offset);
+      for (int j = 0; j < 8; ++j) y[j] = h[ci][j] * inv * (__bfloat162float(ww[j]) + p.w_offset);
     } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) y[j] = s_h[c + j];
+      for (int j = 0; j < 8; ++j) y[j] = h[ci][j];
     }
     if (p.router_w != nullptr) {
 #pragma unroll
@@ -233,7 +267,7 @@ __global__ void __launch_bounds__(kNormThreads) finalize_norm_kernel(const Final
       for (int d = 0; d < kMaxPeers; ++d)
         if (d == o) base = p.slab[d];
       __nv_bfloat16* drow = base + (static_cast<long long>(el) * p.cap + slot) * N;
-      for (int c = threadIdx.x * 8; c < N; c += kNormThreads * 8) {
+      for (int c = threadIdx.x * 8; c < N; c += blockDim.x * 8) {
         uint4 o4;
         o4.x = pack_bf16x2(s_h[c], s_h[c + 1]);
         o4.y = pack_bf16x2(s_h[c + 2], s_h[c + 3]);
@@ -489,14 +523,18 @@ __global__ void softcap_kernel(float* x, long long n, float cap) {
 
 void launch_finalize_norm(const FinalizeNormParams& p, cudaStream_t stream) {
   if (p.rows <= 0) return;
-  const size_t smem = static_cast<size_t>(p.N) * sizeof(float);
+  // threads: one 8-element chunk per thread up to 1024 threads, then several chunks per thread
+  int threads = (p.N / 8 + 31) / 32 * 32;
+  if (threads > kNormMaxThreads) threads = kNormMaxThreads;
+  if (threads < 32) threads = 32;
+  const size_t smem = p.router_w != nullptr ? static_cast<size_t>(p.N) * sizeof(float) : 0;
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
     cudaFuncSetAttribute(finalize_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          static_cast<int>(smem));
     configured = smem;
   }
-  finalize_norm_kernel<<<p.rows, kNormThreads, smem, stream>>>(p);
+  finalize_norm_kernel<<<p.rows, threads, smem, stream>>>(p);
 }
 
 void launch_qkv_rope_append(const QkvRopeParams& p, cudaStream_t stream) {

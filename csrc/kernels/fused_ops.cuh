@@ -20,6 +20,9 @@ struct MoeRowMeta {
 
 struct FinalizeNormParams {
   float* acc;               // [rows, N] fp32 accumulator owned by this rank (nullable); zeroed here
+  const __nv_bfloat16* rs_slab; // [n_slabs, slab rows, N] bf16 partials, one slab per source rank (nullable)
+  int n_slabs;
+  long long slab_stride;    // elements between slabs
   const uint32_t* arrive;   // local arrival counter the accumulator's writers bump (nullable)
   uint32_t expected;        // arrivals to wait for
   uint32_t* ticket;         // local ticket; the last CTA re-arms `arrive`

@@ -110,6 +110,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   int nkb = total_kb - kb0;
   if (nkb > p.kb_per_split) nkb = p.kb_per_split;
   const bool grouped = p.group_counts != nullptr;
+  // Each CTA walks its k-blocks from a different starting point: the CTAs of one wave would
+  // otherwise all ask L2 for the same activation tile at the same moment.
+  const int k_rot = (p.k_stagger && nkb > 1) ? static_cast<int>((blockIdx.x * 5u + blockIdx.y * 3u) % static_cast<unsigned>(nkb)) : 0;
 
   constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
 
@@ -168,7 +171,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // Weights do not depend on any peer: start them before waiting for the gathered rows.
       for (int kb = 0; kb < pre; ++kb) {
         mbar_arrive_expect_tx(&full[kb], L::kABytes + L::kBBytes);
-        tma_load_3d(sB + kb * L::kBBytes, &tmB, &full[kb], (kb0 + kb) * BK, n0, group);
+        tma_load_3d(sB + kb * L::kBBytes, &tmB, &full[kb], (kb0 + (kb + k_rot) % nkb) * BK, n0, group);
       }
       bool ok = true;
       if (p.ag_flags != nullptr && !grouped) {
@@ -192,9 +195,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             break;
           }
           mbar_arrive_expect_tx(&full[s], L::kABytes + L::kBBytes);
-          tma_load_3d(sB + s * L::kBBytes, &tmB, &full[s], (kb0 + kb) * BK, n0, group);
+          tma_load_3d(sB + s * L::kBBytes, &tmB, &full[s], (kb0 + (kb + k_rot) % nkb) * BK, n0, group);
         }
-        tma_load_3d(sA + s * L::kABytes, &tmA, &full[s], (kb0 + kb) * BK, m0, group);
+        tma_load_3d(sA + s * L::kABytes, &tmA, &full[s], (kb0 + (kb + k_rot) % nkb) * BK, m0, group);
       }
     }
   } else if (warp == 1) {
@@ -278,20 +281,58 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               atomicAdd(d + j, wgt * __uint_as_float(r[j]));
           }
         }
-      } else if (p.epi == kEpiSwigluBf16) {
-        __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) +
-                              static_cast<long long>(group) * p.c_group_stride +
-                              static_cast<long long>(row) * p.ldc;
-        const int n_out = p.N >> 1;
+      } else if (p.epi == kEpiStoreF32) {
 #pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
-          uint32_t gt[32], up[32];
-          tmem_ld_32x32b_x32(lane_addr + c * 64, gt);
-          tmem_ld_32x32b_x32(lane_addr + c * 64 + 32, up);
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(lane_addr + c * 32, r);
           tmem_ld_wait();
-          const int col0 = (n0 >> 1) + c * 32;
-          if (!row_ok || col0 >= n_out) continue;
-          if ((p.ldc & 7) == 0 && col0 + 32 <= n_out) {
+          const int col0 = n0 + c * 32;
+          if (!row_ok || col0 >= p.N) continue;
+          float* d = reinterpret_cast<float*>(p.C) + static_cast<long long>(group) * p.c_group_stride +
+                     static_cast<long long>(row) * p.ldc + col0;
+          if ((p.ldc & 3) == 0 && vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o4;
+              o4.x = __uint_as_float(r[j]);
+              o4.y = __uint_as_float(r[j + 1]);
+              o4.z = __uint_as_float(r[j + 2]);
+              o4.w = __uint_as_float(r[j + 3]);
+              if (bias) {
+                o4.x += __bfloat162float(bias[col0 + j]);
+                o4.y += __bfloat162float(bias[col0 + j + 1]);
+                o4.z += __bfloat162float(bias[col0 + j + 2]);
+                o4.w += __bfloat162float(bias[col0 + j + 3]);
+              }
+              *reinterpret_cast<float4*>(d + j) = o4;
+            }
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+              float v = __uint_as_float(r[j]);
+              if (bias) v += __bfloat162float(bias[col0 + j]);
+              d[j] = v;
+            }
+          }
+        }
+      } else {
+        // ---- bf16 outputs (plain store, SwiGLU, routed slab store): TMEM -> registers -> a
+        // padded shared-memory tile (the operand ring is free once tmem_full has fired) ->
+        // row-contiguous 16-byte stores, so local HBM and NVLink both see full lines. Each
+        // warp stages and writes only its own 32 rows, a __syncwarp is all it needs.
+        const bool swiglu = p.epi == kEpiSwigluBf16;
+        constexpr int kOutColsMax = BN;
+        constexpr int kPitch = kOutColsMax * 2 + 16;  // bytes; 16-byte skew keeps stores conflict-free
+        uint8_t* stage = smem + static_cast<size_t>(q) * 32 * kPitch;
+        uint8_t* my_row = stage + static_cast<size_t>(lane) * kPitch;
+        const int out_cols = swiglu ? BN / 2 : BN;  // columns of this tile in the output
+        if (swiglu) {
+#pragma unroll 1
+          for (int c = 0; c < BN / 64; ++c) {
+            uint32_t gt[32], up[32];
+            tmem_ld_32x32b_x32(lane_addr + c * 64, gt);
+            tmem_ld_32x32b_x32(lane_addr + c * 64 + 32, up);
+            tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               float v[8];
@@ -303,75 +344,67 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               o4.y = pack_bf16x2(v[2], v[3]);
               o4.z = pack_bf16x2(v[4], v[5]);
               o4.w = pack_bf16x2(v[6], v[7]);
-              *reinterpret_cast<uint4*>(crow + col0 + j) = o4;
+              *reinterpret_cast<uint4*>(my_row + (c * 32 + j) * 2) = o4;
             }
-          } else {
-            for (int j = 0; j < 32 && col0 + j < n_out; ++j)
-              crow[col0 + j] = __float2bfloat16(act_fn(__uint_as_float(gt[j]), p.act) *
-                                                __uint_as_float(up[j]));
+          }
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(lane_addr + c * 32, r);
+            tmem_ld_wait();
+            const int col0 = n0 + c * 32;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float v[8];
+#pragma unroll
+              for (int t = 0; t < 8; ++t) {
+                v[t] = __uint_as_float(r[j + t]);
+                if (bias != nullptr && col0 + j + t < p.N) v[t] += __bfloat162float(bias[col0 + j + t]);
+              }
+              uint4 o4;
+              o4.x = pack_bf16x2(v[0], v[1]);
+              o4.y = pack_bf16x2(v[2], v[3]);
+              o4.z = pack_bf16x2(v[4], v[5]);
+              o4.w = pack_bf16x2(v[6], v[7]);
+              *reinterpret_cast<uint4*>(my_row + (c * 32 + j) * 2) = o4;
+            }
           }
         }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(lane_addr + c * 32, r);
-          tmem_ld_wait();
-          const int col0 = n0 + c * 32;
-          if (!row_ok || col0 >= p.N) continue;
-          if (p.epi == kEpiStoreBf16) {
-            __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.C) +
-                               static_cast<long long>(group) * p.c_group_stride +
-                               static_cast<long long>(row) * p.ldc + col0;
-            if (vec_ok && (p.ldc & 7) == 0 && col0 + 32 <= p.N) {
+        __syncwarp();
+        // copy-out: lanes sweep the row's 16-byte chunks; several rows per instruction
+        const int n_total = swiglu ? (p.N >> 1) : p.N;       // output row length
+        const int oc0 = swiglu ? (n0 >> 1) : n0;             // first output column of this tile
+        const int chunks = out_cols / 8;                     // 16-byte chunks per staged row
+        const int rows_per_it = 32 / chunks > 0 ? 32 / chunks : 1;
+        const bool out_vec = (n_total & 7) == 0;
+        for (int r0 = 0; r0 < 32; r0 += rows_per_it) {
+          for (int ch0 = 0; ch0 < chunks; ch0 += 32) {
+            const int rr = r0 + (chunks >= 32 ? 0 : lane / chunks);
+            const int ch = chunks >= 32 ? ch0 + lane : lane % chunks;
+            const int grow = m0 + q * 32 + rr;
+            const int gcol = oc0 + ch * 8;
+            if (rr >= 32 || ch >= chunks || grow >= rows || gcol >= n_total) continue;
+            __nv_bfloat16* drow;
+            if (p.epi == kEpiSlabBf16) {
+              int owner = grow / p.rows_per_owner;
+              if (owner >= p.n_owners) owner = p.n_owners - 1;
+              const int row_local = grow - owner * p.rows_per_owner;
+              __nv_bfloat16* base = nullptr;
 #pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                float v[8];
-#pragma unroll
-                for (int t = 0; t < 8; ++t) {
-                  v[t] = __uint_as_float(r[j + t]);
-                  if (bias) v[t] += __bfloat162float(bias[col0 + j + t]);
-                }
-                uint4 o4;
-                o4.x = pack_bf16x2(v[0], v[1]);
-                o4.y = pack_bf16x2(v[2], v[3]);
-                o4.z = pack_bf16x2(v[4], v[5]);
-                o4.w = pack_bf16x2(v[6], v[7]);
-                *reinterpret_cast<uint4*>(d + j) = o4;
-              }
+              for (int o = 0; o < kMaxRanks; ++o)
+                if (o == owner) base = reinterpret_cast<__nv_bfloat16*>(p.dst[o]);
+              drow = base + (static_cast<long long>(p.my_rank) * p.rows_per_owner + row_local) * p.dst_ld;
             } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
-                float v = __uint_as_float(r[j]);
-                if (bias) v += __bfloat162float(bias[col0 + j]);
-                d[j] = __float2bfloat16(v);
-              }
+              drow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(group) * p.c_group_stride +
+                     static_cast<long long>(grow) * p.ldc;
             }
-          } else {
-            float* d = reinterpret_cast<float*>(p.C) +
-                       static_cast<long long>(group) * p.c_group_stride +
-                       static_cast<long long>(row) * p.ldc + col0;
-            if ((p.ldc & 3) == 0 && vec_ok && col0 + 32 <= p.N) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 o4;
-                o4.x = __uint_as_float(r[j]);
-                o4.y = __uint_as_float(r[j + 1]);
-                o4.z = __uint_as_float(r[j + 2]);
-                o4.w = __uint_as_float(r[j + 3]);
-                if (bias) {
-                  o4.x += __bfloat162float(bias[col0 + j]);
-                  o4.y += __bfloat162float(bias[col0 + j + 1]);
-                  o4.z += __bfloat162float(bias[col0 + j + 2]);
-                  o4.w += __bfloat162float(bias[col0 + j + 3]);
-                }
-                *reinterpret_cast<float4*>(d + j) = o4;
-              }
+            const uint8_t* src = stage + static_cast<size_t>(rr) * kPitch + ch * 16;
+            if (out_vec && gcol + 8 <= n_total && ((p.epi == kEpiSlabBf16 ? p.dst_ld : p.ldc) & 7) == 0) {
+              *reinterpret_cast<uint4*>(drow + gcol) = *reinterpret_cast<const uint4*>(src);
             } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
-                float v = __uint_as_float(r[j]);
-                if (bias) v += __bfloat162float(bias[col0 + j]);
-                d[j] = v;
-              }
+              const __nv_bfloat16* sv = reinterpret_cast<const __nv_bfloat16*>(src);
+              for (int t = 0; t < 8 && gcol + t < n_total; ++t) drow[gcol + t] = sv[t];
             }
           }
         }

@@ -15,6 +15,8 @@ enum GemmEpilogue : int {
   kEpiRedF32 = 1,      // dst[owner][row', col] += w * acc   (fp32 red; local or peer memory)
   kEpiStoreF32 = 2,    // C[row, col] = acc + bias[col]      (fp32)
   kEpiSwigluBf16 = 3,  // C[row, n/2] = act(gate) * up; weight rows interleaved [32 gate | 32 up]
+  kEpiSlabBf16 = 4,    // dst[owner][my_rank, row', col] = bf16(acc): partial tiles stored into the
+                       // row owner's receive slab (peer stores); the owner sums the slabs
 };
 
 // Per-row routing record of the MoE combine: which rank / row / weight a slab row goes back to.
@@ -30,6 +32,7 @@ struct GemmParams {
   int kb_per_split;   // 64-wide k blocks handled by one CTA along grid.z
   int epi;
   int act;            // kEpiSwigluBf16: 0 = SiLU, 1 = tanh-GELU
+  int k_stagger;      // 1: each CTA starts its k loop at a different block (spreads L2 requests)
   void* C;            // kEpiStoreBf16 / kEpiStoreF32 / kEpiSwigluBf16
   long long ldc;
   long long c_group_stride;   // elements between groups of C
@@ -46,6 +49,7 @@ struct GemmParams {
   uint32_t* done_ticket;        // local ticket that finds the last CTA (nullptr = no signalling)
   uint32_t* reset_on_done;      // optional local words zeroed by the last CTA before signalling
   int n_reset;
+  int my_rank;                  // kEpiSlabBf16: slab index this rank writes into
   int rows_per_owner;           // dense: row r belongs to owner r / rows_per_owner
   int n_owners;
   // --- wait on the A operand (rows written into local memory by peers) ---

@@ -1,0 +1,80 @@
+"""Micro-benchmark of the tcgen05 GEMM over tile / split / epilogue choices.
+
+    python -m oxide_tech_llm_engine_b200.bench_gemm --m 256 --n 7168 --k 8192 --epi 3
+
+Each configuration is timed with CUDA events over `--iters` launches, with a buffer larger than
+L2 written between launches so that weights come from HBM, and reported as microseconds,
+weight-stream GB/s and TFLOP/s next to the measured peaks of this machine.
+"""
+from __future__ import annotations
+
+import argparse
+import itertools
+import json
+
+import torch
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--m", type=int, default=256)
+    ap.add_argument("--n", type=int, default=7168)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--epi", type=int, default=0)
+    ap.add_argument("--bn", default="64,128,256")
+    ap.add_argument("--splits", default="1")
+    ap.add_argument("--stagger", default="0,1")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--no-flush", action="store_true")
+    args = ap.parse_args()
+    from . import ops
+    from .utils.roofline import load_measured_peaks
+
+    peaks = load_measured_peaks()
+    dev = torch.device("cuda", 0)
+    a = torch.randn(args.m, args.k, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(args.n, args.k, device=dev, dtype=torch.bfloat16) * 0.02
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    n_out = args.n // 2 if args.epi == ops.EPI_SWIGLU_BF16 else args.n
+    out_bf = torch.empty(args.m, n_out, device=dev, dtype=torch.bfloat16)
+    out_f32 = torch.zeros(args.m, args.n, device=dev, dtype=torch.float32)
+    flops = 2.0 * args.m * args.n * args.k
+    wbytes = 2.0 * args.n * args.k
+    for bn, sp, stag in itertools.product([int(x) for x in args.bn.split(",")], [int(x) for x in args.splits.split(",")],
+                                           [int(x) for x in args.stagger.split(",")]):
+        if sp > 1 and args.epi != ops.EPI_RED_F32:
+            continue
+        if args.epi == ops.EPI_SWIGLU_BF16 and args.n % bn:
+            continue
+        kw = dict(bn=bn, splits=sp, k_stagger=bool(stag))
+        if args.epi == ops.EPI_RED_F32:
+            kw.update(epi=ops.EPI_RED_F32, dst_ptrs=[out_f32.data_ptr()])
+        elif args.epi == ops.EPI_STORE_F32:
+            kw.update(epi=ops.EPI_STORE_F32, out=out_f32)
+        else:
+            kw.update(epi=args.epi, out=out_bf)
+        for _ in range(3):
+            ops.gemm(a, w, **kw)
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(args.iters):
+            if not args.no_flush:
+                flush.fill_(1)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            ops.gemm(a, w, **kw)
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e) * 1e3)
+        ops.check_status()
+        ts.sort()
+        us = ts[len(ts) // 2]
+        print(json.dumps({"m": args.m, "n": args.n, "k": args.k, "epi": args.epi, "bn": bn, "splits": sp,
+                          "stagger": stag, "us": round(us, 2), "weights_gb_s": round(wbytes / us / 1e3, 1),
+                          "tflops": round(flops / us / 1e6, 1),
+                          "frac_hbm_of_measured": round(wbytes / us / 1e3 / peaks["hbm_gbs"], 3),
+                          "frac_tflops_of_measured": round(flops / us / 1e6 / peaks["bf16_tflops"], 3)}), flush=True)
+
+
+if __name__ == "__main__":
+    main()

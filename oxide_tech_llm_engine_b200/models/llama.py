@@ -129,6 +129,11 @@ class DeviceModel:
             "lmg": ((self.max_logits, d), "bf16"),
             "flags": ((128,), "i32"),
         }
+        if tp > 1:
+            # receive slabs of the bf16 reduce-scatter: [source rank, rows of this rank, d]
+            specs["slab0"] = ((tp, rpr, d), "bf16")
+            specs["slab1"] = ((tp, rpr, d), "bf16")
+        self._rs_slab = [False, False]
         if cfg.is_moe:
             self.cap = M
             specs["slab"] = ((self.e_l, self.cap, d), "bf16")
@@ -257,12 +262,17 @@ class DeviceModel:
 
     def _finalize(self, rows: int, norm_w, *, acc: Optional[int], gather: str, flag_base: int,
                   r0: int, first: bool = False, row_map=None, layer: Optional[dict] = None,
-                  moe: bool = False) -> None:
+                  moe: bool = False, moe_acc: bool = False) -> None:
         tp, d = self.tp, self.cfg.d_model
         multi = tp > 1
         kw = {}
         if acc is not None:
-            kw["acc"] = self.ws.local(f"acc{acc}")
+            if self._rs_slab[acc] and not moe_acc:
+                kw["rs_slab"] = self.ws.local(f"slab{acc}")
+                kw["n_slabs"] = tp
+                kw["slab_stride"] = rows * d
+            else:
+                kw["acc"] = self.ws.local(f"acc{acc}")
             if multi:
                 kw["arrive"] = self.ws.local("flags")[F_ARRIVE0 + acc:F_ARRIVE0 + acc + 1]
                 kw["expected"] = tp
@@ -289,8 +299,16 @@ class DeviceModel:
         return dict(ag_flags=self.ws.local("flags")[flag_base:flag_base + self.tp], ag_expected=expected,
                     ag_rows_per_src=rows_per_src, ag_ticket=self.tickets[ticket:ticket + 1])
 
-    def _red_kwargs(self, acc: int, ticket: int, rpr: int) -> dict:
-        kw = dict(epi=ops.EPI_RED_F32, dst_ptrs=self.ws.ptrs(f"acc{acc}"), rows_per_owner=rpr)
+    def _red_kwargs(self, acc: int, ticket: int, rpr: int, splits: int = 1) -> dict:
+        """Epilogue routing of a row-parallel GEMM. Across GPUs without split-K the partial tiles
+        travel as bf16 row-contiguous stores into the owner's receive slab (half the NVLink bytes
+        of fp32 and full-line packets); otherwise they are added into the fp32 accumulator."""
+        self._rs_slab[acc] = self.tp > 1 and splits == 1
+        if self._rs_slab[acc]:
+            kw = dict(epi=ops.EPI_SLAB_BF16, dst_ptrs=self.ws.ptrs(f"slab{acc}"), rows_per_owner=rpr,
+                      my_rank=self.rank, dst_ld=self.cfg.d_model)
+        else:
+            kw = dict(epi=ops.EPI_RED_F32, dst_ptrs=self.ws.ptrs(f"acc{acc}"), rows_per_owner=rpr)
         if self.tp > 1:
             kw["arrive_ptrs"] = self._flag_ptrs(F_ARRIVE0 + acc)
             kw["done_ticket"] = self.tickets[ticket:ticket + 1]
@@ -312,7 +330,7 @@ class DeviceModel:
         if lin.packed:
             w = self._scratch_for(lin.n, lin.k)
             ops.dequant_rows(lin.code, lin.w, w, n_src_rows=lin.n, k=lin.k)
-        bn = ops.pick_bn(lin.n, (m + 127) // 128)
+        bn = ops.pick_bn(lin.n, (m + 127) // 128, can_split=True)
         out_f32[:m].zero_() if out_f32.is_contiguous() else out_f32[:m].fill_(0)
         ops.gemm(x, w, epi=ops.EPI_RED_F32, dst_ptrs=[out_f32.data_ptr()], bn=bn,
                  splits=ops.pick_splits(m, lin.n, lin.k, bn), dst_ld=out_f32.stride(0))
@@ -334,7 +352,7 @@ class DeviceModel:
         g1 = self.ws.local("gather1")[:M]
         for li, L in enumerate(self.layers):
             # ---- attention block ----
-            bn = ops.pick_bn(self.wqkv, (M + 127) // 128)
+            bn = ops.pick_bn(self.wqkv, (M + 127) // 128, can_split=True)
             splits = ops.pick_splits(M, self.wqkv, d, bn)
             ag = self._ag_kwargs(F_AG0, T_AG0, rpr, rpr)
             if splits > 1:
@@ -350,9 +368,9 @@ class DeviceModel:
                                 rope_mscale=self.rope_mscale, q_out=self.q_buf, k_cache=self.k_cache[li],
                                 v_cache=self.v_cache[li], m=M, hq=self.hq, hkv=self.hkv, d=self.D, **qkv_kw)
             self._attention(s, li)
-            bn = ops.pick_bn(d, (M + 127) // 128)
-            ops.gemm(self.attn_out[:M], L["w_o"], bn=bn, splits=ops.pick_splits(M, d, self.hq * self.D, bn),
-                     **self._red_kwargs(0, T_DONE_O, rpr))
+            bn = ops.pick_bn(d, (M + 127) // 128, can_split=True)
+            sp = ops.pick_splits(M, d, self.hq * self.D, bn)
+            ops.gemm(self.attn_out[:M], L["w_o"], bn=bn, splits=sp, **self._red_kwargs(0, T_DONE_O, rpr, sp))
             # ---- feed-forward block ----
             if cfg.is_moe:
                 self._finalize(rpr, L["ffn_norm"], acc=0, gather="", flag_base=F_MOE, r0=r0, layer=L, moe=True)
@@ -362,18 +380,18 @@ class DeviceModel:
                 n_gu = 2 * self.i_l
                 ops.gemm(g1, L["w_gu"], out=self.act[:M], epi=ops.EPI_SWIGLU_BF16, act=self._act_code,
                          bn=ops.pick_bn(n_gu, (M + 127) // 128), **self._ag_kwargs(F_AG1, T_AG1, rpr, rpr))
-                bn = ops.pick_bn(d, (M + 127) // 128)
-                ops.gemm(self.act[:M], L["w_down"], bn=bn, splits=ops.pick_splits(M, d, self.i_l, bn),
-                         **self._red_kwargs(1, T_DONE_D, rpr))
+                bn = ops.pick_bn(d, (M + 127) // 128, can_split=True)
+                sp = ops.pick_splits(M, d, self.i_l, bn)
+                ops.gemm(self.act[:M], L["w_down"], bn=bn, splits=sp, **self._red_kwargs(1, T_DONE_D, rpr, sp))
             last = li == cfg.n_layers - 1
             if not last:
                 self._finalize(rpr, self.layers[li + 1]["attn_norm"], acc=1, gather="gather0", flag_base=F_AG0,
-                               r0=r0)
+                               r0=r0, moe_acc=cfg.is_moe)
         # ---- final norm (logit rows only) + vocab-parallel LM head ----
         n_log = max(s.n_logits, 1)  # a step without logit rows still drains the last accumulator
         row_map = s.logit_map[r0:r0 + rpr] if s.logit_map is not None else None
         self._finalize(rpr, self.out_norm, acc=1, gather="lmg", flag_base=F_LMG, r0=r0 if row_map is None else 0,
-                       row_map=row_map)
+                       row_map=row_map, moe_acc=cfg.is_moe)
         lmg = self.ws.local("lmg")[:n_log]
         ops.gemm(lmg, self.lm_head, out=self.logits[:n_log], epi=ops.EPI_STORE_F32,
                  bn=ops.pick_bn(self.v_l, (n_log + 127) // 128), **self._ag_kwargs(F_LMG, T_LMG, 0, rpr))

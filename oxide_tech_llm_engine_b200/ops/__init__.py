@@ -6,6 +6,7 @@ GPU box never runs these ops on a silent eager substitute.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Sequence
 
 import torch
@@ -16,6 +17,7 @@ EPI_STORE_BF16 = 0
 EPI_RED_F32 = 1
 EPI_STORE_F32 = 2
 EPI_SWIGLU_BF16 = 3
+EPI_SLAB_BF16 = 4
 
 STATUS_NAMES = {
     0: "ok",
@@ -25,6 +27,8 @@ STATUS_NAMES = {
     4: "peer flag timeout",
     5: "index out of range",
 }
+
+K_STAGGER_DEFAULT = os.environ.get("OXB_K_STAGGER", "0") != "0"
 
 # number of kernel launches issued through this module (bench.py reports it)
 launch_count = 0
@@ -64,23 +68,25 @@ def check_status(device=None) -> None:
         raise EngineError(f"kernel reported: {msg}")
 
 
-def pick_bn(n: int, m_tiles: int = 1) -> int:
-    """Output-tile width: wide tiles when there are plenty, narrow ones to fill 148 SMs."""
-    if n % 256 == 0 and (n // 256) * m_tiles >= 148:
+def pick_bn(n: int, m_tiles: int = 1, can_split: bool = False) -> int:
+    """Output-tile width. Wide tiles move fewer operand bytes per FLOP through the 64 B/clk
+    SM<->L2 port, so take the widest tile that still gives about one CTA per SM; GEMMs that can
+    split K keep 128-wide tiles and fill the machine with splits instead."""
+    if n % 256 == 0 and (n // 256) * m_tiles >= 120:
         return 256
-    if (n + 127) // 128 * m_tiles >= 100:
+    t128 = (n + 127) // 128 * m_tiles
+    if t128 >= 60 or can_split or n % 64 != 0 or n < 64:
         return 128
-    return 64 if n >= 64 and n % 64 == 0 else 128
+    return 64
 
 
 def pick_splits(m: int, n: int, k: int, bn: int) -> int:
     """Split-K factor so that small GEMMs still occupy most SMs (needs the fp32 red epilogue)."""
     tiles = ((m + 127) // 128) * ((n + bn - 1) // bn)
     kb = (k + 63) // 64
-    if tiles >= 120 or kb < 8:
+    if tiles >= 100 or kb < 8:
         return 1
-    s = min(max(1, 148 // tiles), max(1, kb // 4), 16)
-    return s
+    return min(max(1, 148 // tiles), max(1, kb // 4), 16)
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
@@ -91,19 +97,22 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
          row_meta: Optional[torch.Tensor] = None, ag_flags: Optional[torch.Tensor] = None,
          ag_expected: int = 0, ag_rows_per_src: int = 0, ag_ticket: Optional[torch.Tensor] = None,
          bn: int = 0, splits: int = 1, act: int = 0, m_tiles: int = 0,
-         dst_ld: int = 0) -> Optional[torch.Tensor]:
+         dst_ld: int = 0, my_rank: int = 0, k_stagger: Optional[bool] = None) -> Optional[torch.Tensor]:
     """tcgen05 GEMM  out = a @ w^T  (bf16 in, fp32 accumulate). See csrc/kernels/gemm_bf16.cu."""
     M = a.shape[-2]
     N = w.shape[-2]
     if bn == 0:
         bn = pick_bn(N, (M + 127) // 128)
-    if out is None and epi != EPI_RED_F32:
+    if k_stagger is None:
+        k_stagger = K_STAGGER_DEFAULT
+    if out is None and epi not in (EPI_RED_F32, EPI_SLAB_BF16):
         n_out = N // 2 if epi == EPI_SWIGLU_BF16 else N
         dt = torch.float32 if epi == EPI_STORE_F32 else torch.bfloat16
         out = torch.empty(*a.shape[:-1], n_out, dtype=dt, device=a.device)
     _ext().gemm_bf16(a, w, epi, out, bias, list(dst_ptrs), list(arrive_ptrs), done_ticket,
                      reset_on_done, rows_per_owner, group_counts, row_meta, ag_flags, ag_expected,
-                     ag_rows_per_src, ag_ticket, status_word(a.device), bn, splits, act, m_tiles, dst_ld)
+                     ag_rows_per_src, ag_ticket, status_word(a.device), bn, splits, act, m_tiles, dst_ld,
+                     my_rank, 1 if k_stagger else 0)
     _bump()
     return out
 
@@ -122,13 +131,14 @@ def paged_prefill(q, k_cache, v_cache, block_tables, tile_seq, tile_q0, q_start,
     _bump()
 
 
-def finalize_norm(*, rows: int, n: int, acc=None, arrive=None, expected: int = 0, ticket=None,
+def finalize_norm(*, rows: int, n: int, acc=None, rs_slab=None, n_slabs: int = 0, slab_stride: int = 0,
+                  arrive=None, expected: int = 0, ticket=None,
                   residual_in=None, residual_out=None, bias=None, norm_w=None, eps: float = 1e-5,
                   w_offset: float = 0.0, out_ptrs: Sequence[int] = (), out_flag_ptrs: Sequence[int] = (),
                   out_row_off: int = 0, out_row_map=None, router_w=None, top_k: int = 0, experts_per_rank: int = 0,
                   routed_scale: float = 1.0, slab_ptrs: Sequence[int] = (), meta_ptrs: Sequence[int] = (),
                   cnt_ptrs: Sequence[int] = (), cap: int = 0, my_rank: int = 0, device=None) -> None:
-    _ext().finalize_norm(acc, arrive, expected, ticket, residual_in, residual_out, bias, norm_w, eps,
+    _ext().finalize_norm(acc, rs_slab, n_slabs, slab_stride, arrive, expected, ticket, residual_in, residual_out, bias, norm_w, eps,
                          w_offset, list(out_ptrs), list(out_flag_ptrs), out_row_off, out_row_map, rows, n,
                          status_word(device), router_w, top_k, experts_per_rank, routed_scale,
                          list(slab_ptrs), list(meta_ptrs), list(cnt_ptrs), cap, my_rank)

@@ -78,6 +78,40 @@ def test_gemm_splitk_red(ops, m, n, k, splits, bn):
     assert acc.abs().max().item() == 0.0  # the accumulator is re-armed
 
 
+def test_gemm_slab_reduce_scatter_emulated(ops):
+    """Four owners emulated on one GPU: each gets its rows of the partial product in its slab,
+    then finalize_norm sums the slabs of all sources."""
+    torch.manual_seed(13)
+    tp, rpo, n, k = 4, 64, 512, 256
+    m = tp * rpo
+    a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=DEV, dtype=torch.bfloat16)
+    slabs = [torch.zeros(tp, rpo, n, device=DEV, dtype=torch.bfloat16) for _ in range(tp)]
+    my = 2
+    ops.gemm(a, w, epi=ops.EPI_SLAB_BF16, dst_ptrs=[s.data_ptr() for s in slabs], rows_per_owner=rpo,
+             my_rank=my, dst_ld=n, bn=128)
+    torch.cuda.synchronize()
+    ops.check_status()
+    ref = a.float() @ w.float().T
+    for o in range(tp):
+        assert _rel_err(slabs[o][my], ref[o * rpo:(o + 1) * rpo]) < 1.5e-2
+        assert slabs[o][my - 1].abs().max().item() == 0
+    # owner 1 sums its slabs (pretend every source wrote the same partial)
+    own = slabs[1]
+    for src in range(tp):
+        own[src] = own[my]
+    res = torch.randn(rpo, n, device=DEV, dtype=torch.bfloat16)
+    wn = torch.rand(n, device=DEV, dtype=torch.bfloat16) + 0.5
+    out = torch.empty(rpo, n, device=DEV, dtype=torch.bfloat16)
+    res_out = torch.empty_like(res)
+    ops.finalize_norm(rows=rpo, n=n, rs_slab=own, n_slabs=tp, slab_stride=rpo * n, residual_in=res,
+                      residual_out=res_out, norm_w=wn, eps=1e-5, out_ptrs=[out.data_ptr()])
+    torch.cuda.synchronize()
+    h = own[my].float() * tp + res.float()
+    assert _rel_err(res_out, h) < 1.5e-2
+    assert _rel_err(out, _rms(h, wn, 1e-5)) < 2e-2
+
+
 def test_gemm_swiglu_epilogue(ops):
     torch.manual_seed(3)
     m, i, k, bn = 200, 512, 768, 128
@@ -252,7 +286,7 @@ def _rms(x, w, eps, off=0.0):
     return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * (w.float() + off)
 
 
-@pytest.mark.parametrize("rows,n", [(1, 2048), (37, 4096), (256, 8192), (3, 1024)])
+@pytest.mark.parametrize("rows,n", [(1, 2048), (37, 4096), (256, 8192), (3, 1024), (5, 128), (2, 14336), (4, 6152)])
 def test_finalize_norm(ops, rows, n):
     torch.manual_seed(7)
     acc = torch.randn(rows, n, device=DEV)
