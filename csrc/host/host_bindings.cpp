@@ -196,6 +196,30 @@ PYBIND11_MODULE(oxb_host, m) {
              d["nodes"] = s.radix().num_nodes();
              return d;
            })
+      .def("alloc_blocks",
+           [](Scheduler& s, int n) -> py::object {
+             std::vector<int> out;
+             for (int i = 0; i < n; ++i) {
+               int b = s.pool().allocate();
+               if (b < 0) {
+                 for (int x : out) s.pool().release(x);
+                 return py::none();
+               }
+               out.push_back(b);
+             }
+             return py::cast(out);
+           })
+      .def("release_blocks",
+           [](Scheduler& s, const std::vector<int>& blocks) {
+             for (int b : blocks) s.pool().release(b);
+           })
+      .def("radix_insert",
+           [](Scheduler& s, const py::array_t<int32_t, py::array::c_style | py::array::forcecast>& t,
+              const std::vector<int>& blocks) {
+             const int n_blocks = std::min<int>(static_cast<int>(blocks.size()),
+                                                static_cast<int>(t.size()) / kTokensPerBlock);
+             return s.radix().insert(t.data(), blocks.data(), n_blocks);
+           })
       .def("radix_evict", [](Scheduler& s, int want) { return s.radix().evict(want); })
       .def("radix_clear", [](Scheduler& s) { s.radix().clear(); });
 }
