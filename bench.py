@@ -103,6 +103,8 @@ def main() -> None:
     ap.add_argument("--mem-util", type=float, default=0.94)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
+                    help="nccl: comparison path with library GEMMs and NCCL all-reduces")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
@@ -138,7 +140,7 @@ def main() -> None:
     cfg = EngineConfig(model=args.model, tp=world, ctx_size=ctx, max_num_seqs=args.requests,
                        max_num_batched_tokens=args.max_batched_tokens, gpu_memory_utilization=args.mem_util,
                        sla_budget=False, chunk_max=args.max_batched_tokens, enable_radix=False,
-                       cuda_graph=not args.no_graph,
+                       cuda_graph=not args.no_graph, comm=args.comm, gemm="library" if args.comm == "nccl" else "tcgen05",
                        graph_buckets=tuple(b for b in (8, 16, 32, 64, 128, 192, 256) if b <= args.requests) or (args.requests,))
     t_build = time.perf_counter()
     eng = LLMEngine(cfg, mc, rank=rank, world=world, device=dev, random_init=True)
@@ -204,7 +206,7 @@ def main() -> None:
             "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic random-token prompts, random-init N(0,0.02) weights",
-            "impl": "ours", "valid": valid,
+            "impl": "ours" if args.comm == "fused" else "ours-baseline-path", "valid": valid,
             "config": {
                 "model": f"{mc.name} ({mc.n_layers}L d{mc.d_model} {mc.n_heads}q/{mc.n_kv_heads}kv ffn{mc.ffn_dim} v{mc.vocab_size})",
                 "parallelism": f"tp{world}", "requests_submitted": args.requests,
@@ -213,7 +215,8 @@ def main() -> None:
                 "prompt_len": f"uniform[{args.prompt_min},{args.prompt_max}]", "output_len": args.output_len,
                 "seq_len": ctx, "kv_blocks": eng.model.num_blocks, "kv_block_tokens": 16,
                 "cache_note": "per-step inputs (weights + KV, >= 17 GB per GPU) exceed the 126 MB L2",
-                "cuda_graph": cfg.cuda_graph, "comm": "fused peer-memory kernels" if world > 1 else "single GPU",
+                "cuda_graph": cfg.cuda_graph, "comm": ("nccl all-reduce + library GEMMs (baseline path)" if args.comm == "nccl" else
+                         "fused peer-memory kernels" if world > 1 else "single GPU"),
                 "prefill_tokens": int(prefill_tokens), "prefill_seconds": round(prefill_s, 2),
                 "prefill_tok_per_s": round(prefill_tokens / max(prefill_s, 1e-9), 1),
                 "build_seconds": round(t_prefill - t_build, 2),

@@ -146,7 +146,9 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
     p.ag_ticket = reinterpret_cast<uint32_t*>(ag_ticket->data_ptr());
   }
   p.status = reinterpret_cast<int*>(status.data_ptr());
-  oxb::launch_gemm_bf16(tmA, tmB, p, bn_i, m_tiles, s, cur_stream());
+  p.m_tiles = m_tiles;
+  p.splits = s;
+  oxb::launch_gemm_bf16(tmA, tmB, p, bn_i, cur_stream());
   check_launch("gemm_bf16");
 }
 
@@ -215,6 +217,51 @@ void paged_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache
   p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
   oxb::launch_paged_prefill(p, static_cast<int>(n_tiles), D, cur_stream());
   check_launch("paged_prefill");
+}
+
+void paged_prefill_tc(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
+                      const Tensor& block_tables, const Tensor& tile_seq, const Tensor& tile_q0,
+                      const Tensor& q_start, const Tensor& q_lens, const Tensor& ctx_lens,
+                      const Tensor& out, int64_t n_tiles, int64_t window, double scale,
+                      const Tensor& status) {
+  TORCH_CHECK(q.dim() == 3 && k_cache.dim() == 4, "paged_prefill_tc: q [T,Hq,D], cache [blk,Hkv,16,D]");
+  TORCH_CHECK(k_cache.is_contiguous() && v_cache.is_contiguous(), "paged_prefill_tc: contiguous caches");
+  oxb::PrefillAttnParams p{};
+  const int D = static_cast<int>(q.size(2));
+  TORCH_CHECK(D == 64 || D == 128, "paged_prefill_tc: head_dim 64 or 128");
+  TORCH_CHECK(q.stride(1) == D && q.stride(2) == 1, "paged_prefill_tc: q heads must be packed");
+  p.q = reinterpret_cast<const __nv_bfloat16*>(q.data_ptr());
+  p.q_stride = q.stride(0);
+  p.k_cache = reinterpret_cast<const __nv_bfloat16*>(k_cache.data_ptr());
+  p.v_cache = reinterpret_cast<const __nv_bfloat16*>(v_cache.data_ptr());
+  p.block_tables = block_tables.data_ptr<int>();
+  p.tile_seq = tile_seq.data_ptr<int>();
+  p.tile_q0 = tile_q0.data_ptr<int>();
+  p.q_start = q_start.data_ptr<int>();
+  p.q_lens = q_lens.data_ptr<int>();
+  p.ctx_lens = ctx_lens.data_ptr<int>();
+  p.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  p.out_stride = out.stride(0);
+  p.max_blocks = static_cast<int>(block_tables.size(1));
+  p.Hq = static_cast<int>(q.size(1));
+  p.Hkv = static_cast<int>(k_cache.size(1));
+  p.window = static_cast<int>(window);
+  p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
+  const uint64_t T = q.size(0);
+  const uint64_t kv_rows = static_cast<uint64_t>(k_cache.size(0)) * p.Hkv * 16;
+  CUtensorMap tmQ = oxb::make_tma_map(q.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2,
+                                      static_cast<uint64_t>(p.Hq) * D, T, 1,
+                                      static_cast<uint64_t>(q.stride(0)) * 2, 0, 64, 128, 1,
+                                      CU_TENSOR_MAP_SWIZZLE_128B);
+  CUtensorMap tmK = oxb::make_tma_map(k_cache.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, D,
+                                      kv_rows, 1, static_cast<uint64_t>(D) * 2, 0, 64, 16, 1,
+                                      CU_TENSOR_MAP_SWIZZLE_128B);
+  CUtensorMap tmV = oxb::make_tma_map(v_cache.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, D,
+                                      kv_rows, 1, static_cast<uint64_t>(D) * 2, 0, 64, 16, 1,
+                                      CU_TENSOR_MAP_SWIZZLE_128B);
+  oxb::launch_paged_prefill_tc(tmQ, tmK, tmV, p, static_cast<int>(n_tiles), D,
+                               reinterpret_cast<int*>(status.data_ptr()), cur_stream());
+  check_launch("paged_prefill_tc");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -519,6 +566,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_bf16", &gemm_bf16);
   m.def("paged_decode", &paged_decode);
   m.def("paged_prefill", &paged_prefill);
+  m.def("paged_prefill_tc", &paged_prefill_tc);
   m.def("finalize_norm", &finalize_norm);
   m.def("qkv_rope_append", &qkv_rope_append);
   m.def("swiglu", &swiglu);

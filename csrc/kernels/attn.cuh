@@ -1,6 +1,7 @@
 // Parameter blocks of the paged attention kernels.
 // KV cache layout (per layer): [num_blocks, Hkv, 16 tokens, head_dim] bf16 for K and for V.
 #pragma once
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -44,5 +45,9 @@ struct PrefillAttnParams {
 
 void launch_paged_prefill(const PrefillAttnParams& p, int n_tiles, int head_dim,
                           cudaStream_t stream);
+
+void launch_paged_prefill_tc(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
+                             const PrefillAttnParams& p, int n_tiles, int head_dim, int* status,
+                             cudaStream_t stream);
 
 }  // namespace oxb

@@ -29,7 +29,9 @@ struct RowMeta {
 
 struct GemmParams {
   int M, N, K;        // M = rows per group when group_counts == nullptr
-  int kb_per_split;   // 64-wide k blocks handled by one CTA along grid.z
+  int kb_per_split;   // 64-wide k blocks per split
+  int splits;         // number of K slices
+  int m_tiles;        // 128-row tiles along M (grouped mode: upper bound over all groups)
   int epi;
   int act;            // kEpiSwigluBf16: 0 = SiLU, 1 = tanh-GELU
   int k_stagger;      // 1: each CTA starts its k loop at a different block (spreads L2 requests)
@@ -62,6 +64,6 @@ struct GemmParams {
 };
 
 void launch_gemm_bf16(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int bn,
-                      int m_tiles, int splits, cudaStream_t stream);
+                      cudaStream_t stream);
 
 }  // namespace oxb

@@ -52,14 +52,26 @@ def main() -> None:
     ap.add_argument("--trace", action="store_true", help="kernel table from torch.profiler (CUPTI) over the timed steps")
     ap.add_argument("--max-splits", type=int, default=16)
     ap.add_argument("--pps", type=int, default=0, help="pages per KV split (0 = engine heuristic)")
+    ap.add_argument("--no-attn", action="store_true",
+                    help="skip the attention kernels: times the GEMM / collective / norm chain only")
     args = ap.parse_args()
 
     from . import ops
     from .models.config import preset
     from .models.llama import DeviceModel, StepInputs
 
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
+    import os
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
     mc = shard_config(preset(args.model), args.shard_of)
     if args.layers:
         mc = replace(mc, n_layers=args.layers)
@@ -76,9 +88,12 @@ def main() -> None:
     blocks_per_seq = [(c + 15) // 16 for c in ctx]
     num_blocks = sum(blocks_per_seq) + 8
     W = max(blocks_per_seq)
-    model = DeviceModel(mc, device=dev, max_tokens=max(M, 64), max_seqs=max(len(ctx), 8), num_blocks=num_blocks,
-                        max_blocks_per_seq=W, max_logits=max(len(ctx), 64), max_splits=args.max_splits)
+    model = DeviceModel(mc, rank=rank, world=world, device=dev, max_tokens=max(M, 64), max_seqs=max(len(ctx), 8),
+                        num_blocks=num_blocks, max_blocks_per_seq=W, max_logits=max(len(ctx), 64),
+                        max_splits=args.max_splits)
     model.init_random(0)
+    if args.no_attn:
+        model._attention = lambda s, li: None
     for li in range(mc.n_layers):
         model.k_cache[li].normal_()
         model.v_cache[li].normal_()
@@ -183,10 +198,39 @@ def main() -> None:
     ops.check_status()
     ms = sorted(a.elapsed_time(b) for a, b in ev)
     med = ms[len(ms) // 2]
-    out = {"model": mc.name, "shard_of": args.shard_of, "layers": mc.n_layers, "rows": M,
+    if world > 1:
+        t = torch.tensor([med, ms[0]], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)  # every multi-GPU number is the max over ranks
+        med, ms[0] = float(t[0]), float(t[1])
+    out = {"model": mc.name, "shard_of": args.shard_of, "tp": world, "layers": mc.n_layers, "rows": M,
            "mean_ctx": float(np.mean(ctx)), "ms_per_step_median": round(med, 4), "ms_min": round(ms[0], 4),
-           "graph": bool(args.graph)}
-    print(json.dumps(out))
+           "graph": bool(args.graph), "attention": not args.no_attn}
+    if args.no_attn and not mc.is_moe:
+        # roofline of the fused GEMM + collective chain: per GEMM the slower of FLOPs / measured
+        # sustained GEMM peak and NVLink bytes / measured 770 GB/s per direction
+        from .utils.roofline import load_measured_peaks
+
+        pk = load_measured_peaks()
+        peak = pk.get("bf16_tflops_sustained", pk["bf16_tflops"]) * 1e12
+        link = 770e9
+        tp, d = world, mc.d_model
+        qd, kvd, ff = mc.q_dim // tp, mc.kv_dim // tp, mc.ffn_dim // tp
+        frac = (tp - 1) / tp
+        terms = {
+            "ag_gemm_qkv": (2.0 * M * (qd + 2 * kvd) * d / peak, M * d * 2 * frac / link),
+            "gemm_rs_o": (2.0 * M * d * qd / peak, M * d * 2 * frac / link),
+            "ag_gemm_gate_up": (2.0 * M * 2 * ff * d / peak, M * d * 2 * frac / link),
+            "gemm_rs_down": (2.0 * M * d * ff / peak, M * d * 2 * frac / link),
+        }
+        ideal_ms = mc.n_layers * sum(max(c, l) for c, l in terms.values()) * 1e3
+        out["roofline"] = {"ideal_ms": round(ideal_ms, 4), "achieved_over_roofline": round(ideal_ms / med, 3),
+                           "peaks": f"{peak / 1e12:.0f} TFLOP/s sustained ({pk.get('source', 'measured')}), 770 GB/s NVLink per direction",
+                           "per_layer_us": {k: {"compute": round(c * 1e6, 2), "link": round(l * 1e6, 2)}
+                                            for k, (c, l) in terms.items()}}
+    if rank == 0:
+        print(json.dumps(out))
+    if rank != 0:
+        args.breakdown = args.trace = False
     if args.breakdown and graph is None:
         rows = []
         for k, v in times.items():
@@ -197,7 +241,12 @@ def main() -> None:
         for t, c, k in sorted(rows, reverse=True):
             print(f"{t:10.4f} {c:6d} {100 * t / total:6.1f}%  {k}")
         print(f"{total:10.4f} total of event-timed kernels")
+    model.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
     main()
+

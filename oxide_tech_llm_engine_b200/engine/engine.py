@@ -363,6 +363,9 @@ class LLMEngine:
         return s, bucket
 
     def _forward(self, s: StepInputs, bucket: Optional[int]) -> torch.Tensor:
+        if self.cfg.comm == "nccl" or self.cfg.gemm == "library":
+            # baseline path: eager library GEMMs + NCCL collectives (torch allocates, so no graphs)
+            return self.model.forward_baseline(s)
         if bucket is None:
             return self.model.forward(s)
         g = self.graphs.get(bucket)

@@ -48,7 +48,9 @@ class CpuPagedModel(ReferenceModel):
         return torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), vv)
 
     @torch.no_grad()
-    def forward_plan(self, plan) -> torch.Tensor:
+    def forward_plan(self, plan, layer_range=None, x_in=None, return_hidden: bool = False) -> torch.Tensor:
+        """Runs the step; with `layer_range` only those layers (pipeline stage): `x_in` is the hidden
+        state received from the previous stage, `return_hidden` skips the head."""
         cfg = self.cfg
         tok = torch.as_tensor(plan.token_ids.astype(np.int64))
         pos = torch.as_tensor(plan.positions.astype(np.int64))
@@ -59,8 +61,10 @@ class CpuPagedModel(ReferenceModel):
         pbt = plan.prefill_block_tables.reshape(npf, W) if npf else None
         blk = torch.as_tensor(slots // 16)
         off = torch.as_tensor(slots % 16)
-        x = self.embed[tok] * cfg.emb_scale
-        for li, L in enumerate(self.layers):
+        x = self.embed[tok] * cfg.emb_scale if x_in is None else x_in
+        lo, hi = layer_range if layer_range is not None else (0, cfg.n_layers)
+        for li in range(lo, hi):
+            L = self.layers[li]
             h = self._norm(x, L["attn_norm"])
             q, k, v = h @ L["attn_q"].T, h @ L["attn_k"].T, h @ L["attn_v"].T
             if L["attn_q.bias"] is not None:
@@ -86,6 +90,8 @@ class CpuPagedModel(ReferenceModel):
                 a[r0:r0 + ql] = self._attend(q[r0:r0 + ql], kk, vv, pos[r0:r0 + ql])
             x = x + a.reshape(T, cfg.q_dim) @ L["attn_output"].T
             x = x + self._ffn(L, self._norm(x, L["ffn_norm"]))
+        if return_hidden:
+            return x
         rows = torch.as_tensor(plan.logit_rows.astype(np.int64))
         logits = self._norm(x[rows], self.out_norm) @ self.lm_head.T
         if cfg.logit_softcap > 0:

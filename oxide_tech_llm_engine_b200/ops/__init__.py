@@ -124,10 +124,19 @@ def paged_decode(q, k_cache, v_cache, block_tables, seq_lens, pages_per_split, p
     _bump(2)
 
 
+PREFILL_IMPL = os.environ.get("OXB_PREFILL", "tc")  # tc = tcgen05 kernel, mma = mma.sync kernel
+
+
 def paged_prefill(q, k_cache, v_cache, block_tables, tile_seq, tile_q0, q_start, q_lens, ctx_lens, out,
-                  *, n_tiles: int, window: int = 0, scale: float) -> None:
-    _ext().paged_prefill(q, k_cache, v_cache, block_tables, tile_seq, tile_q0, q_start, q_lens,
-                         ctx_lens, out, n_tiles, window, scale)
+                  *, n_tiles: int, window: int = 0, scale: float, impl: Optional[str] = None) -> None:
+    """Causal paged attention over ragged prefill chunks. `tc`: tcgen05 / TMEM kernel on 128-row
+    query tiles (attn_prefill_tc.cu); `mma`: the mma.sync kernel on 64-row tiles (attn_prefill.cu)."""
+    if (impl or PREFILL_IMPL) == "tc":
+        _ext().paged_prefill_tc(q, k_cache, v_cache, block_tables, tile_seq, tile_q0, q_start, q_lens,
+                                ctx_lens, out, n_tiles, window, scale, status_word(q.device))
+    else:
+        _ext().paged_prefill(q, k_cache, v_cache, block_tables, tile_seq, tile_q0, q_start, q_lens,
+                             ctx_lens, out, n_tiles, window, scale)
     _bump()
 
 

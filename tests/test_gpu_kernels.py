@@ -30,7 +30,7 @@ def _cos(got, ref):
 @pytest.mark.parametrize("m,n,k,bn", [
     (128, 128, 64, 128), (128, 128, 256, 128), (256, 512, 1024, 128), (100, 200, 136, 128),
     (1, 1280, 2048, 64), (17, 256, 512, 64), (300, 1024, 512, 256), (129, 4096, 4096, 128),
-    (64, 96, 64, 128),
+    (64, 96, 64, 128), (1024, 4096, 512, 128), (2048, 2048, 192, 64), (640, 8192, 256, 256),
 ])
 def test_gemm_store_bf16(ops, m, n, k, bn):
     torch.manual_seed(0)
@@ -60,7 +60,7 @@ def test_gemm_bias_and_f32(ops):
 
 
 @pytest.mark.parametrize("m,n,k,splits,bn", [(256, 1280, 8192, 7, 128), (32, 512, 4096, 16, 64),
-                                             (130, 256, 1024, 4, 128)])
+                                             (130, 256, 1024, 4, 128), (1500, 2048, 1024, 3, 128)])
 def test_gemm_splitk_red(ops, m, n, k, splits, bn):
     torch.manual_seed(2)
     a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
@@ -114,7 +114,7 @@ def test_gemm_slab_reduce_scatter_emulated(ops):
 
 def test_gemm_swiglu_epilogue(ops):
     torch.manual_seed(3)
-    m, i, k, bn = 200, 512, 768, 128
+    m, i, k, bn = 2100, 1536, 768, 128  # more work items than SMs: exercises the TMEM double buffer
     a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16) * 0.5
     wg = torch.randn(i, k, device=DEV, dtype=torch.bfloat16) * 0.05
     wu = torch.randn(i, k, device=DEV, dtype=torch.bfloat16) * 0.05
@@ -249,8 +249,11 @@ def test_paged_decode(ops, hq, hkv, d, seq_lens, pps, window):
     (4, 4, 64, [(100, 100), (33, 200)], 0),
     (16, 2, 128, [(130, 400)], 0),
     (8, 1, 128, [(90, 300), (20, 20)], 48),
+    (2, 1, 128, [(300, 700), (128, 128), (257, 257)], 0),
+    (4, 2, 64, [(200, 500)], 100),
 ])
-def test_paged_prefill(ops, hq, hkv, d, chunks, window):
+@pytest.mark.parametrize("impl", ["tc", "mma"])
+def test_paged_prefill(ops, hq, hkv, d, chunks, window, impl):
     torch.manual_seed(6)
     q_lens = [c[0] for c in chunks]
     ctx_lens = [c[1] for c in chunks]
@@ -269,8 +272,9 @@ def test_paged_prefill(ops, hq, hkv, d, chunks, window):
     out = torch.zeros(T, hq * d, device=DEV, dtype=torch.bfloat16)
     scale = 1.0 / math.sqrt(d)
     ops.paged_prefill(q, k_cache, v_cache, bt, ti(tile_seq), ti(tile_q0), ti(q_start), ti(q_lens),
-                      ti(ctx_lens), out, n_tiles=len(tile_seq), window=window, scale=scale)
+                      ti(ctx_lens), out, n_tiles=len(tile_seq), window=window, scale=scale, impl=impl)
     torch.cuda.synchronize()
+    ops.check_status()
     for s, (ql, cl) in enumerate(chunks):
         k = _gather_kv(k_cache, bt[s], cl)
         v = _gather_kv(v_cache, bt[s], cl)
