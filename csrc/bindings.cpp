@@ -14,6 +14,7 @@
 #include "kernels/attn.cuh"
 #include "kernels/fused_ops.cuh"
 #include "kernels/gemm_bf16.cuh"
+#include "kernels/gemm_fp8_block.cuh"
 #include "kernels/quant_ops.cuh"
 #include "kernels/sampler.cuh"
 
@@ -150,6 +151,62 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
   p.splits = s;
   oxb::launch_gemm_bf16(tmA, tmB, p, bn_i, cur_stream());
   check_launch("gemm_bf16");
+}
+
+// a8: [M, K] e4m3 bytes; sa_t: [ceil(K/128), >= M] fp32; w8: [N, K] e4m3 bytes; sw: [ceil(N/128), ceil(K/128)].
+void gemm_fp8_block(const Tensor& a8, const Tensor& sa_t, const Tensor& w8, const Tensor& sw,
+                    const Tensor& out, const c10::optional<Tensor>& bias, const Tensor& status) {
+  TORCH_CHECK(a8.is_cuda() && w8.is_cuda() && a8.element_size() == 1 && w8.element_size() == 1,
+              "gemm_fp8_block: CUDA fp8 operands required");
+  TORCH_CHECK(a8.dim() == 2 && w8.dim() == 2 && a8.stride(1) == 1 && w8.stride(1) == 1,
+              "gemm_fp8_block: row-major 2-D operands required");
+  const int64_t M = a8.size(0), K = a8.size(1), N = w8.size(0);
+  TORCH_CHECK(w8.size(1) == K && K % 16 == 0, "gemm_fp8_block: K mismatch or K % 16 != 0");
+  const int64_t n_kb = (K + 127) / 128;
+  TORCH_CHECK(sa_t.scalar_type() == torch::kFloat32 && sa_t.dim() == 2 && sa_t.size(0) == n_kb &&
+                  sa_t.size(1) >= M && sa_t.stride(1) == 1,
+              "gemm_fp8_block: sa_t must be [K/128, >=M] fp32");
+  TORCH_CHECK(sw.scalar_type() == torch::kFloat32 && sw.is_contiguous() &&
+                  sw.size(0) == (N + 127) / 128 && sw.size(1) == n_kb,
+              "gemm_fp8_block: sw must be [N/128, K/128] fp32");
+  TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && out.size(0) == M && out.size(1) == N &&
+                  out.stride(1) == 1,
+              "gemm_fp8_block: out must be [M, N] bf16");
+  CUtensorMap tmA = oxb::make_tma_map(a8.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, 2, K, M, 1,
+                                      static_cast<uint64_t>(a8.stride(0)), 0, 128, 128, 1,
+                                      CU_TENSOR_MAP_SWIZZLE_128B);
+  CUtensorMap tmB = oxb::make_tma_map(w8.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, 2, K, N, 1,
+                                      static_cast<uint64_t>(w8.stride(0)), 0, 128, 128, 1,
+                                      CU_TENSOR_MAP_SWIZZLE_128B);
+  oxb::Fp8GemmParams p{};
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(K);
+  p.sa_t = sa_t.data_ptr<float>();
+  p.sa_ld = static_cast<int>(sa_t.stride(0));
+  p.sw = sw.data_ptr<float>();
+  p.C = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  p.ldc = out.stride(0);
+  p.bias = bf16_ptr(bias);
+  p.status = reinterpret_cast<int*>(status.data_ptr());
+  oxb::launch_gemm_fp8_block(tmA, tmB, p, cur_stream());
+  check_launch("gemm_fp8_block");
+}
+
+void quant_act_fp8(const Tensor& x, const Tensor& q, const Tensor& sa_t) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.dim() == 2 && x.stride(1) == 1,
+              "quant_act_fp8: [M, K] bf16 input required");
+  TORCH_CHECK(q.element_size() == 1 && q.size(0) == x.size(0) && q.size(1) == x.size(1) &&
+                  q.stride(1) == 1,
+              "quant_act_fp8: q must be [M, K] bytes");
+  TORCH_CHECK(sa_t.scalar_type() == torch::kFloat32 && sa_t.size(0) == (x.size(1) + 127) / 128 &&
+                  sa_t.size(1) >= x.size(0) && sa_t.stride(1) == 1,
+              "quant_act_fp8: sa_t must be [K/128, >=M] fp32");
+  oxb::launch_quant_act_fp8(reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), x.stride(0),
+                            reinterpret_cast<uint8_t*>(q.data_ptr()), q.stride(0),
+                            sa_t.data_ptr<float>(), static_cast<int>(sa_t.stride(0)),
+                            static_cast<int>(x.size(0)), static_cast<int>(x.size(1)), cur_stream());
+  check_launch("quant_act_fp8");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -564,6 +621,8 @@ Tensor tensor_from_ptr(int64_t ptr, const std::vector<int64_t>& shape, const std
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "sm_100a kernels of the B200-native Oxide engine";
   m.def("gemm_bf16", &gemm_bf16);
+  m.def("gemm_fp8_block", &gemm_fp8_block);
+  m.def("quant_act_fp8", &quant_act_fp8);
   m.def("paged_decode", &paged_decode);
   m.def("paged_prefill", &paged_prefill);
   m.def("paged_prefill_tc", &paged_prefill_tc);

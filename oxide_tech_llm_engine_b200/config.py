@@ -19,7 +19,7 @@ class EngineConfig:
     model: str = "tiny"                 # preset name or path to a .gguf / safetensors checkpoint
     alias: Optional[str] = None
     models_dir: Optional[str] = None
-    weight_mode: str = "auto"           # auto | bf16 | quant  (quant keeps GGUF blocks packed in HBM)
+    weight_mode: str = "auto"           # auto | bf16 | quant | fp8  (quant: GGUF blocks packed in HBM; fp8: 128x128 block-scaled e4m3)
     tp: int = 1
     pp: int = 1
     dp: int = 1

@@ -232,7 +232,7 @@ class LLMEngine:
         tp = self.world
         w_bytes = 0
         if has_weights:
-            per = 2.0 if weight_mode == "bf16" else 0.6
+            per = {"bf16": 2.0, "fp8": 1.02}.get(weight_mode, 0.6)
             n = mc.n_params()
             w_bytes = int((n - mc.vocab_size * mc.d_model) / tp * per + mc.vocab_size * mc.d_model * 2)
         act = self.max_tokens * (mc.d_model * 16 + (mc.q_dim + 2 * mc.kv_dim) // tp * 8 + mc.ffn_dim // tp * 4)

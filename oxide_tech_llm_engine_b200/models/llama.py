@@ -102,6 +102,8 @@ class DeviceModel:
             raise ConfigError("ffn_dim / tp must be a multiple of 32")
         if weight_mode == "quant" and tp != 1:
             raise ConfigError("packed GGUF weights are served at tp=1; use weight_mode='bf16' for tp>1")
+        if weight_mode == "fp8" and (tp != 1 or cfg.is_moe):
+            raise ConfigError("block-scaled fp8 weights are served at tp=1 on dense models")
         self.weight_mode = weight_mode
         self.D = cfg.head_dim
         self.hq = cfg.n_heads // tp
@@ -159,6 +161,12 @@ class DeviceModel:
         if weight_mode == "quant":
             self.gu_acc = torch.zeros(M, 2 * self.i_l, dtype=torch.float32, device=dev)
             self._scratch: Optional[torch.Tensor] = None
+        if weight_mode == "fp8":
+            k_max = max(d, self.hq * self.D, self.i_l)
+            self.a8_flat = torch.zeros(M * k_max, dtype=torch.float8_e4m3fn, device=dev)
+            self.sa_flat = torch.zeros((k_max + 127) // 128 * M, dtype=torch.float32, device=dev)
+            self.gu_bf16 = torch.zeros(M, 2 * self.i_l, **bf)
+            self.proj_bf16 = torch.zeros(M, d, **bf)
         self.layers: list[dict] = []
         self.embed = None
         self.lm_head = None
@@ -198,6 +206,8 @@ class DeviceModel:
             else:
                 L["w_gu"] = rnd(2 * self.i_l, d)
                 L["w_down"] = rnd(d, self.i_l)
+            if self.weight_mode == "fp8":
+                self._to_fp8(L)
             self.layers.append(L)
 
     def load(self, src: WeightSource) -> None:
@@ -252,9 +262,16 @@ class DeviceModel:
                     i_lo, i_hi = r * self.i_l, (r + 1) * self.i_l
                     g = bf(src.f32(p + "ffn_gate.weight")[i_lo:i_hi])
                     u = bf(src.f32(p + "ffn_up.weight")[i_lo:i_hi])
-                    L["w_gu"] = interleave32(g, u)
+                    L["w_gu"] = torch.cat([g, u], 0) if self.weight_mode == "fp8" else interleave32(g, u)
                     L["w_down"] = bf(src.f32(p + "ffn_down.weight")[:, i_lo:i_hi])
+                if self.weight_mode == "fp8":
+                    self._to_fp8(L)
             self.layers.append(L)
+
+    def _to_fp8(self, L: dict) -> None:
+        """Replaces the bf16 projections of a layer by (e4m3 values, 128 x 128 block scales)."""
+        for key in ("w_qkv", "w_o", "w_gu", "w_down"):
+            L[key] = ops.quant_weight_fp8_block(L[key])
 
     # ------------------------------------------------------------------ helpers
     def _flag_ptrs(self, index: int) -> list[int]:
@@ -340,6 +357,8 @@ class DeviceModel:
         """Runs one step; returns fp32 logits [n_logits, vocab/tp] (a view of a static buffer)."""
         if self.weight_mode == "quant":
             return self._forward_quant(s)
+        if self.weight_mode == "fp8":
+            return self._forward_fp8(s)
         cfg, tp, rank = self.cfg, self.tp, self.rank
         M = s.m
         rpr = M // tp
@@ -460,6 +479,54 @@ class DeviceModel:
         self._finalize(M, self.out_norm, acc=1, gather="lmg", flag_base=F_LMG, r0=0, row_map=s.logit_map[:M])
         lmg = self.ws.local("lmg")[:n_log]
         self._qlinear(self.lm_head_q, lmg, self.logits[:n_log])
+        if cfg.logit_softcap > 0:
+            ops.softcap(self.logits[:n_log], cfg.logit_softcap)
+        return self.logits[:n_log]
+
+    def _fp8_linear(self, w, x: torch.Tensor, out: torch.Tensor, bias=None) -> None:
+        """out = x @ W^T with W in block-scaled fp8: quantise the activation rows (1 x 128 scales),
+        then the tcgen05 f8 GEMM with per-block promotion."""
+        m, k = x.shape
+        a8 = self.a8_flat[:m * k].view(m, k)
+        sa = self.sa_flat[:(k + 127) // 128 * m].view(-1, m)
+        ops.quant_act_fp8(x, a8, sa)
+        ops.gemm_fp8_block(a8, sa, w[0], w[1], out=out, bias=bias)
+
+    def _forward_fp8(self, s: StepInputs) -> torch.Tensor:
+        """tp == 1 path over block-scaled fp8 projections (embedding, norms and LM head stay bf16)."""
+        cfg = self.cfg
+        M, d = s.m, cfg.d_model
+        g0, g1 = self.ws.local("gather0")[:M], self.ws.local("gather1")[:M]
+        ops.embed_gather(s.token_ids[:M], self.embed, self.residual[:M], cfg.emb_scale)
+        self._finalize(M, self.layers[0]["attn_norm"], acc=None, gather="gather0", flag_base=F_AG0, r0=0, first=True)
+        proj = self.proj_bf16[:M]
+
+        def fin(norm_w, gather, flag_base, **kw):
+            ops.finalize_norm(rows=M, n=d, rs_slab=proj, n_slabs=1, slab_stride=M * d, residual_in=self.residual,
+                              residual_out=self.residual, norm_w=norm_w, eps=cfg.rms_eps,
+                              w_offset=cfg.norm_weight_offset, out_ptrs=self.ws.ptrs(gather), out_flag_ptrs=[],
+                              out_row_off=0, device=self.device, **kw)
+
+        for li, L in enumerate(self.layers):
+            self._fp8_linear(L["w_qkv"], g0, self.qkv_bf16[:M])
+            ops.qkv_rope_append(qkv_bf16=self.qkv_bf16, bias=L["b_qkv"], q_norm_w=L["q_norm"], k_norm_w=L["k_norm"],
+                                norm_eps=1e-6, norm_w_offset=cfg.norm_weight_offset, positions=s.positions,
+                                slot_mapping=s.slot_mapping, inv_freq=self.inv_freq, rope_mscale=self.rope_mscale,
+                                q_out=self.q_buf, k_cache=self.k_cache[li], v_cache=self.v_cache[li], m=M,
+                                hq=self.hq, hkv=self.hkv, d=self.D)
+            self._attention(s, li)
+            self._fp8_linear(L["w_o"], self.attn_out[:M], proj)
+            fin(L["ffn_norm"], "gather1", F_AG1)
+            self._fp8_linear(L["w_gu"], g1, self.gu_bf16[:M])
+            ops.swiglu(gu_bf16=self.gu_bf16, out=self.act, m=M, i=self.i_l, act=self._act_code)
+            self._fp8_linear(L["w_down"], self.act[:M], proj)
+            if li != cfg.n_layers - 1:
+                fin(self.layers[li + 1]["attn_norm"], "gather0", F_AG0)
+        n_log = max(s.n_logits, 1)
+        fin(self.out_norm, "lmg", F_LMG, out_row_map=s.logit_map[:M])
+        lmg = self.ws.local("lmg")[:n_log]
+        ops.gemm(lmg, self.lm_head, out=self.logits[:n_log], epi=ops.EPI_STORE_F32,
+                 bn=ops.pick_bn(self.v_l, (n_log + 127) // 128))
         if cfg.logit_softcap > 0:
             ops.softcap(self.logits[:n_log], cfg.logit_softcap)
         return self.logits[:n_log]

@@ -117,6 +117,42 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     return out
 
 
+def quant_weight_fp8_block(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """[N, K] float weight -> (e4m3 [N, K], fp32 scales [ceil(N/128), ceil(K/128)]), one scale per
+    128 x 128 block (amax / 448). Runs wherever `w` lives; a load-time transform."""
+    N, K = w.shape
+    nb, kb = (N + 127) // 128, (K + 127) // 128
+    wp = torch.zeros(nb * 128, kb * 128, dtype=torch.float32, device=w.device)
+    wp[:N, :K] = w.float()
+    blk = wp.view(nb, 128, kb, 128)
+    scale = blk.abs().amax(dim=(1, 3)).clamp_min(1e-10) / 448.0
+    q = (blk / scale[:, None, :, None]).view(nb * 128, kb * 128)[:N, :K]
+    return q.to(torch.float8_e4m3fn).contiguous(), scale.contiguous()
+
+
+def quant_act_fp8(x: torch.Tensor, q: Optional[torch.Tensor] = None,
+                  sa_t: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16 [M, K] -> (e4m3 [M, K], transposed 1 x 128 scales [ceil(K/128), M])."""
+    M, K = x.shape
+    if q is None:
+        q = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=x.device)
+    if sa_t is None:
+        sa_t = torch.empty((K + 127) // 128, M, dtype=torch.float32, device=x.device)
+    _ext().quant_act_fp8(x, q, sa_t)
+    _bump()
+    return q, sa_t
+
+
+def gemm_fp8_block(a8: torch.Tensor, sa_t: torch.Tensor, w8: torch.Tensor, sw: torch.Tensor, *,
+                   out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Block-scaled fp8 GEMM on the tcgen05 f8 path. See csrc/kernels/gemm_fp8_block.cu."""
+    if out is None:
+        out = torch.empty(a8.shape[0], w8.shape[0], dtype=torch.bfloat16, device=a8.device)
+    _ext().gemm_fp8_block(a8, sa_t, w8, sw, out, bias, status_word(a8.device))
+    _bump()
+    return out
+
+
 def paged_decode(q, k_cache, v_cache, block_tables, seq_lens, pages_per_split, part_o, part_ml, out,
                  *, batch: int, max_splits: int, window: int = 0, scale: float) -> None:
     _ext().paged_decode(q, k_cache, v_cache, block_tables, seq_lens, pages_per_split, part_o, part_ml,

@@ -117,6 +117,25 @@ def test_gguf_quantized_serving(qtype):
         eng.close()
 
 
+def test_fp8_block_scaled_serving():
+    """Block-scaled fp8 projections: tokens stay consistent with the fp32 oracle's logits."""
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    from oxide_tech_llm_engine_b200.models.config import preset
+    from oxide_tech_llm_engine_b200.models.weights import SyntheticSource
+
+    mc = preset("tiny", d_model=256, ffn_dim=512, head_dim=64)
+    src = SyntheticSource(mc, seed=7, std=0.08)
+    eng, mc, src = _mk("tiny", weights=src, weight_mode="fp8")
+    assert eng.model.weight_mode == "fp8" and eng.model.layers[0]["w_qkv"][0].dtype == torch.float8_e4m3fn
+    rng = np.random.default_rng(8)
+    prompts = [rng.integers(3, mc.vocab_size, size=n).tolist() for n in (5, 70, 150)]
+    outs = eng.generate(prompts, SamplingParams(greedy=True, max_tokens=10, ignore_eos=True))
+    eng.check_device_status()
+    assert_consistent(mc, src, prompts, outs, tol=0.6, min_exact=0.5)
+    eng.close()
+
+
 def test_sampling_and_cancel_and_speculative():
     from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
 

@@ -531,3 +531,31 @@ def test_argmax_and_sampling(ops):
     ops.sample(lg, toks, temperature=temp, top_k=torch.zeros_like(tk), top_p=tp, min_p=mp2, seeds=seeds,
                counters=ctr)
     assert (toks == top4.indices[0]).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(128, 256, 512), (200, 384, 1024), (8, 1024, 4096), (640, 1152, 2048), (130, 200, 272)])
+def test_gemm_fp8_block_scaled(ops, M, N, K):
+    """Block-scaled fp8 GEMM against the fp32 product of the dequantised operands."""
+    torch.manual_seed(M + N + K)
+    x = (torch.randn(M, K, device="cuda") * torch.rand(M, 1, device="cuda") * 3).bfloat16()
+    w = torch.randn(N, K, device="cuda") * 0.05
+    w8, sw = ops.quant_weight_fp8_block(w)
+    a8, sa_t = ops.quant_act_fp8(x)
+    # activation quantiser: scales are amax/448 per 1x128 block, values round-trip within e4m3 error
+    kb = (K + 127) // 128
+    xp = torch.zeros(M, kb * 128, device="cuda")
+    xp[:, :K] = x.float()
+    amax = xp.view(M, kb, 128).abs().amax(-1)
+    torch.testing.assert_close(sa_t.t().contiguous(), amax.clamp_min(1e-10) / 448.0, rtol=1e-5, atol=1e-12)
+    a_deq = (a8.float().view(torch.float32) if False else a8.to(torch.float32))
+    a_deq = a_deq * sa_t.t().repeat_interleave(128, 1)[:, :K]
+    assert (a_deq - x.float()).abs().max() <= 0.07 * x.float().abs().max()
+    w_deq = w8.to(torch.float32) * sw.repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)[:, :K]
+    ref = a_deq @ w_deq.t()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    out = ops.gemm_fp8_block(a8, sa_t, w8, sw, bias=bias)
+    ops.check_status(out.device)
+    ref = ref + bias.float()
+    err = (out.float() - ref).abs().max().item()
+    assert err <= 2e-2 * ref.abs().max().item() + 1e-3, err
