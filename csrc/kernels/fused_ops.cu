@@ -30,8 +30,9 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void red_release_sys_add_u32(uint32_t* p, uint32_t v) {
-  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// Relaxed: callers fence once at system scope, then signal all peers back to back.
+__device__ __forceinline__ void red_relaxed_sys_add_u32(uint32_t* p, uint32_t v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ float block_sum(float v, float* scratch) {
@@ -280,13 +281,14 @@ __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const Fi
 
   const bool signal = p.out_flag[0] != nullptr;
   if (signal || p.arrive != nullptr) {
-    if (signal) __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
       if (signal) {
+        // one system-scope fence per CTA, after the barrier that orders every thread's stores
+        __threadfence_system();
 #pragma unroll
         for (int d = 0; d < kMaxPeers; ++d)
-          if (d < p.n_dst) red_release_sys_add_u32(p.out_flag[d], 1u);
+          if (d < p.n_dst) red_relaxed_sys_add_u32(p.out_flag[d], 1u);
       }
       if (p.arrive != nullptr) {
         // every CTA has passed its wait once the ticket is full: re-arm the arrival counter

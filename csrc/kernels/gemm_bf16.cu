@@ -16,7 +16,7 @@
 //  * kEpiSlabBf16 stores bf16 partial tiles row-contiguously into the row owner's receive slab
 //    (half the NVLink bytes of fp32, full-line packets); the owner's finalize kernel sums them.
 //    In both cases the last CTA to finish (ticket) bumps an arrival counter on every owner with
-//    a system-scope release, so the consumer kernel on each owner needs one bounded wait.
+//    one system-scope fence and relaxed signals, so the consumer kernel on each owner needs one bounded wait.
 //  * The A operand may be an all-gather / dispatch buffer that peers fill: the producer waits
 //    (bounded) on per-source counters before its first A load of a tile; weight tiles are
 //    requested before that wait.
@@ -47,8 +47,10 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
-  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// Relaxed on purpose: the caller issues ONE system-scope fence and then signals every peer; a
+// release on each signal would wait a full NVLink round trip per peer, one after the other.
+__device__ __forceinline__ void red_relaxed_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ void red_add_v4_f32(float* p, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c),
@@ -466,9 +468,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_before_sync();
     // When the whole grid has landed its contributions, tell every owner once.
     if (p.done_ticket != nullptr) {
-      __threadfence_system();
+      // One system-scope fence per CTA: the barrier orders the other epilogue threads' stores
+      // before it (cumulativity), and a fence per thread would serialise 128 of them.
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (warp == 2 && lane == 0) {
+        __threadfence_system();
         const uint32_t old = atomicAdd(p.done_ticket, 1u);
         if (old == gridDim.x - 1) {
           for (int i = 0; i < p.n_reset; ++i) p.reset_on_done[i] = 0;
@@ -476,7 +480,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           __threadfence_system();
 #pragma unroll
           for (int o = 0; o < kMaxRanks; ++o)
-            if (o < p.n_owners && p.arrive[o] != nullptr) red_release_sys_add(p.arrive[o], 1u);
+            if (o < p.n_owners && p.arrive[o] != nullptr) red_relaxed_sys_add(p.arrive[o], 1u);
         }
       }
     }

@@ -26,6 +26,7 @@ def main() -> None:
     ap.add_argument("--stagger", default="0,1")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--fp8", action="store_true", help="time the block-scaled fp8 GEMM (and its activation quantiser)")
     args = ap.parse_args()
     from . import ops
     from .utils.roofline import load_measured_peaks
@@ -40,6 +41,37 @@ def main() -> None:
     out_f32 = torch.zeros(args.m, args.n, device=dev, dtype=torch.float32)
     flops = 2.0 * args.m * args.n * args.k
     wbytes = 2.0 * args.n * args.k
+    if args.fp8:
+        w8, sw = ops.quant_weight_fp8_block(w)
+        a8, sa = ops.quant_act_fp8(a)
+        out8 = torch.empty(args.m, args.n, device=dev, dtype=torch.bfloat16)
+
+        def timed(fn):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(args.iters):
+                if not args.no_flush:
+                    flush.fill_(1)
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                fn()
+                e.record()
+                torch.cuda.synchronize()
+                ts.append(s.elapsed_time(e) * 1e3)
+            ts.sort()
+            return ts[len(ts) // 2]
+
+        us = timed(lambda: ops.gemm_fp8_block(a8, sa, w8, sw, out=out8))
+        uq = timed(lambda: ops.quant_act_fp8(a, a8, sa))
+        ops.check_status()
+        print(json.dumps({"kernel": "gemm_fp8_block", "m": args.m, "n": args.n, "k": args.k, "us": round(us, 2),
+                          "weights_gb_s": round(wbytes / 2 / us / 1e3, 1), "tflops": round(flops / us / 1e6, 1),
+                          "frac_hbm_of_measured": round(wbytes / 2 / us / 1e3 / peaks["hbm_gbs"], 3),
+                          "x_bf16_peak_of_measured": round(flops / us / 1e6 / peaks["bf16_tflops"], 3),
+                          "quant_act_us": round(uq, 2)}), flush=True)
+        return
     for bn, sp, stag in itertools.product([int(x) for x in args.bn.split(",")], [int(x) for x in args.splits.split(",")],
                                            [int(x) for x in args.stagger.split(",")]):
         if sp > 1 and args.epi != ops.EPI_RED_F32:

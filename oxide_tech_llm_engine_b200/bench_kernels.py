@@ -178,6 +178,7 @@ def main() -> None:
     torch.cuda.synchronize()
     if prof is not None:
         prof.__exit__(None, None, None)
+    if prof is not None and rank == 0:
         agg = defaultdict(lambda: [0.0, 0])
         for e in prof.events():
             if e.device_type is not None and str(e.device_type).endswith("CUDA") and e.name and "Memcpy" not in e.name:
