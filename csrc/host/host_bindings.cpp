@@ -2,11 +2,13 @@
 // tables, radix prefix cache and the continuous-batching scheduler core.
 #include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
+#include <pybind11/functional.h>
 #include <pybind11/stl.h>
 
 #include "block_manager.h"
 #include "radix_cache.h"
 #include "scheduler.h"
+#include "worker.h"
 
 namespace py = pybind11;
 using namespace oxb;
@@ -222,4 +224,80 @@ PYBIND11_MODULE(oxb_host, m) {
            })
       .def("radix_evict", [](Scheduler& s, int want) { return s.radix().evict(want); })
       .def("radix_clear", [](Scheduler& s) { s.radix().clear(); });
+
+  // Step worker: the handler is a Python callable (kind, arg0, arg1) -> int | (int, int); it runs on
+  // the worker thread with the GIL held, the waits of the caller release it.
+  struct WorkerDeleter {
+    void operator()(StepWorker* w) const {
+      py::gil_scoped_release rel;  // the worker thread may need the GIL to finish its command
+      delete w;
+    }
+  };
+  py::class_<StepWorker, std::unique_ptr<StepWorker, WorkerDeleter>>(m, "StepWorker")
+      .def(py::init([](py::function fn, int capacity, int pin_core, int spin_limit, int yield_limit,
+                       int park_us) {
+             // the callable is reference-counted only under the GIL, wherever the last copy dies
+             std::shared_ptr<py::function> fp(new py::function(std::move(fn)), [](py::function* f) {
+               py::gil_scoped_acquire gil;
+               delete f;
+             });
+             auto handler = [fp](const StepCommand& c, int* value) -> int {
+               py::gil_scoped_acquire gil;
+               try {
+                 py::object r = (*fp)(c.kind, c.arg0, c.arg1);
+                 if (py::isinstance<py::tuple>(r)) {
+                   py::tuple t = r.cast<py::tuple>();
+                   *value = t[1].cast<int>();
+                   return t[0].cast<int>();
+                 }
+                 return r.is_none() ? 0 : r.cast<int>();
+               } catch (py::error_already_set& e) {
+                 e.discard_as_unraisable("StepWorker handler");
+                 return -1;
+               }
+             };
+             return new StepWorker(handler, capacity, pin_core, spin_limit, yield_limit, park_us);
+           }),
+           py::arg("handler"), py::arg("capacity") = 64, py::arg("pin_core") = -1,
+           py::arg("spin_limit") = 200, py::arg("yield_limit") = 2000, py::arg("park_us") = 50)
+      .def("submit",
+           [](StepWorker& w, uint64_t seq, int kind, int arg0, int64_t arg1) {
+             StepCommand c;
+             c.seq = seq;
+             c.kind = kind;
+             c.arg0 = arg0;
+             c.arg1 = arg1;
+             return w.submit(c);
+           },
+           py::arg("seq"), py::arg("kind") = 0, py::arg("arg0") = 0, py::arg("arg1") = 0)
+      .def("wait",
+           [](StepWorker& w, int timeout_ms) -> py::object {
+             StepCompletion c;
+             bool ok;
+             {
+               py::gil_scoped_release rel;
+               ok = w.wait(&c, timeout_ms);
+             }
+             if (!ok) return py::none();
+             return py::make_tuple(c.seq, c.status, c.value, c.busy_us);
+           },
+           py::arg("timeout_ms") = 1000)
+      .def("stop",
+           [](StepWorker& w) {
+             py::gil_scoped_release rel;
+             w.stop();
+           })
+      .def("heartbeat", &StepWorker::heartbeat)
+      .def("pinned", &StepWorker::pinned)
+      .def("idle_stats", [](const StepWorker& w) {
+        WorkerIdleStats s = w.idle_stats();
+        py::dict d;
+        d["spins"] = s.spins;
+        d["yields"] = s.yields;
+        d["parks"] = s.parks;
+        d["commands"] = s.commands;
+        return d;
+      });
+  m.attr("STEP_COMMAND_BYTES") = sizeof(StepCommand);
+  m.attr("STEP_COMPLETION_BYTES") = sizeof(StepCompletion);
 }

@@ -386,9 +386,32 @@ class LLMEngine:
         self.stats["graph_replays"] += 1
         return self.model.logits[:s.n_logits]
 
+    def attach_monitor(self, monitor) -> None:
+        """`monitor.check()` (parallel.watchdog.RankMonitor) runs before every step: a peer that
+        stopped answering is found on the host, before any kernel waits on it."""
+        self.monitor = monitor
+
+    def fail_all(self, reason: str) -> list:
+        """Ends every request with `reason` and returns the KV blocks (used when the job degrades)."""
+        events = []
+        for rid in list(self.requests.keys()):
+            ok, ev = self.sched.cancel(rid)
+            for e in ev:
+                self._deliver(e)
+                events.append(e)
+        self.degraded = reason
+        return events
+
     def step(self) -> list:
         """One scheduler iteration. Returns the TokenEvents of this step."""
         t0 = time.perf_counter()
+        mon = getattr(self, "monitor", None)
+        if mon is not None:
+            try:
+                mon.check()
+            except Exception as e:
+                self.fail_all(f"rank_failure: {e}")
+                raise
         plan = self.sched.schedule()
         if plan.n_tokens == 0:
             return []

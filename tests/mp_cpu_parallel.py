@@ -75,8 +75,68 @@ def run_ring(rank, world):
         print("RING_OK", flush=True)
 
 
+def run_rank_exit(rank, world):
+    """Rank `world-1` leaves between steps; the others learn of it on the host before their next
+    collective, fail their in-flight requests with a typed error and return every KV block."""
+    import time
+    from datetime import timedelta
+
+    from oxide_tech_llm_engine_b200._build import host_ext
+    from oxide_tech_llm_engine_b200.parallel.watchdog import Heartbeat, RankFailure, RankMonitor
+
+    store = dist.TCPStore("127.0.0.1", int(os.environ["MASTER_PORT"]) + 1, world, rank == 0,
+                          timeout=timedelta(seconds=30))
+    hb = Heartbeat(store, rank, period_s=0.02).start()
+    mon = RankMonitor(store, rank, world, timeout_s=0.5)
+    H = host_ext()
+    sc = H.SchedulerConfig()
+    sc.num_blocks, sc.max_num_seqs, sc.enable_radix = 64, 4, False
+    sched = H.Scheduler(sc)
+    free0 = sched.num_free_blocks()
+    sched.add_request(0, np.arange(3, 40, dtype=np.int32), 50, [], True)
+    victim = world - 1
+    steps, failure = 0, None
+    x = torch.ones(4)
+    t0 = time.monotonic()
+    while sched.has_work() and time.monotonic() - t0 < 20:
+        if rank == victim and steps == 3:
+            hb.leave()          # between steps, nothing in flight
+            break
+        try:
+            mon.check()         # host-side check BEFORE the collective
+        except RankFailure as e:
+            failure = e
+            break
+        plan = sched.schedule()
+        if rank != victim or steps < 3:
+            # the "collective" of the step among ranks that are still in the job
+            dist.all_reduce(x) if steps < 3 else None
+        toks = np.full(plan.logit_rows.size, 7, dtype=np.int32)
+        sched.update(plan, toks)
+        steps += 1
+        time.sleep(0.05)
+    if rank != victim:
+        assert failure is not None and failure.rank == victim, (rank, failure, steps)
+        ok, ev = sched.cancel(0)
+        assert ok and ev and ev[0].finished
+        assert sched.num_free_blocks() == free0
+        hb.stop()
+        print(f"RANK_EXIT_OK rank={rank} steps={steps} reason={failure.reason}", flush=True)
+        store.set(f"done/{rank}", "1")
+    else:
+        # keep the store's client alive until the survivors have finished reading it
+        for r in range(world - 1):
+            store.wait([f"done/{r}"], timedelta(seconds=20))
+    if rank == 0:
+        time.sleep(0.3)
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    if sys.argv[1] == "rank_exit":
+        dist.init_process_group("gloo")
+        run_rank_exit(rank, world)
+        os._exit(0)  # survivors do not run a collective teardown with a rank that is gone
     dist.init_process_group("gloo")
     {"pipeline": run_pipeline, "ring": run_ring}[sys.argv[1]](rank, world)
     dist.barrier()

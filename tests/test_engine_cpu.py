@@ -171,3 +171,34 @@ def test_grammar_constrained_json_is_valid():
     assert text.startswith('{"a": "')
     if eng.requests[rid].grammar.done():
         json.loads(text)
+
+
+def test_monitor_failure_fails_requests_and_returns_blocks():
+    """A peer that stops answering is found before the step: requests end with a typed reason and
+    every KV block goes back to the pool."""
+    from oxide_tech_llm_engine_b200.config import EngineConfig
+    from oxide_tech_llm_engine_b200.engine.engine import LLMEngine
+    from oxide_tech_llm_engine_b200.models.config import preset
+    from oxide_tech_llm_engine_b200.models.weights import SyntheticSource
+    from oxide_tech_llm_engine_b200.parallel.watchdog import RankFailure
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    mc = preset("tiny")
+    eng = LLMEngine(EngineConfig(model="tiny", backend="cpu", max_num_seqs=4, num_kv_blocks=64, ctx_size=256),
+                    mc, weights=SyntheticSource(mc, seed=1, std=0.08))
+    free0 = eng.sched.num_free_blocks()
+    eng.add_request(list(range(3, 30)), SamplingParams(greedy=True, max_tokens=20, ignore_eos=True))
+    eng.step()
+    assert eng.sched.num_free_blocks() < free0
+
+    class Mon:
+        def check(self):
+            raise RankFailure(1, "missed heartbeats for 1.00s")
+    eng.attach_monitor(Mon())
+    import pytest as _pt
+    with _pt.raises(RankFailure):
+        eng.step()
+    cached = eng.sched.radix_stats()["cached_blocks"]   # full prompt blocks stay in the prefix cache
+    assert eng.sched.num_free_blocks() + cached == free0 and not eng.has_work()
+    assert "rank_failure" in eng.degraded
+    eng.close()

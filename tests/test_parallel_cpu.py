@@ -61,3 +61,75 @@ def test_dp_router_prefix_affinity_and_balance():
     assert max(rep.n for rep in reps) - min(rep.n for rep in reps) <= 5
     spill = r.pick(a)
     assert spill != ia                                  # the hot replica is too far ahead: spill over
+
+
+def test_rank_exit_is_detected_on_the_host_and_resources_return():
+    r = _torchrun(3, "rank_exit", 29630)
+    assert r.returncode == 0 and r.stdout.count("RANK_EXIT_OK") == 2, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+def test_rank_monitor_with_fake_store_and_clock():
+    from oxide_tech_llm_engine_b200.parallel.watchdog import Heartbeat, RankFailure, RankMonitor
+
+    class Store(dict):
+        def set(self, k, v): self[k] = v
+        def get(self, k): return self[k]
+        def check(self, ks): return all(k in self for k in ks)
+    st, now = Store(), [0.0]
+    hb1 = Heartbeat(st, 1)
+    mon = RankMonitor(st, 0, 3, timeout_s=1.0, clock=lambda: now[0])
+    now[0] = 0.5
+    assert mon.poll() == {}
+    hb1.beat()
+    now[0] = 1.2
+    gone = mon.poll()                      # rank 2 never wrote a heartbeat: it never joined
+    assert list(gone) == [2] and "missed" in gone[2]
+    now[0] = 1.9
+    assert 1 not in mon.poll()             # rank 1 beat at 0.5..1.2
+    now[0] = 3.0
+    with pytest.raises(RankFailure) as ei:
+        mon.check()
+    assert ei.value.rank == 1
+    hb1.leave()
+    mon2 = RankMonitor(st, 0, 2, timeout_s=10.0, clock=lambda: now[0])
+    assert mon2.poll() == {1: "left the job"}
+
+
+@pytest.mark.filterwarnings("ignore::pytest.PytestUnraisableExceptionWarning")
+def test_step_worker_runs_commands_in_order_and_idles_in_three_phases():
+    import time
+
+    from oxide_tech_llm_engine_b200._build import host_ext
+
+    H = host_ext()
+    assert H.STEP_COMMAND_BYTES == 64 and H.STEP_COMPLETION_BYTES == 64
+    seen = []
+
+    def handler(kind, a0, a1):
+        seen.append((kind, a0, a1))
+        if a0 == 13:
+            raise RuntimeError("boom")
+        return 0, a0 * 2
+    w = H.StepWorker(handler, capacity=8, pin_core=-1, spin_limit=50, yield_limit=200, park_us=50)
+    hb0 = w.heartbeat()
+    for i in range(20):
+        while not w.submit(i, 0, i, 1000 + i):
+            c = w.wait(1000)
+            assert c is not None
+        if i == 5:
+            time.sleep(0.02)               # let the worker reach the park phase
+    got = []
+    while len(got) + 0 < 20:
+        c = w.wait(2000)
+        if c is None:
+            break
+        got.append(c)
+    # completions drained inside the submit loop are not in `got`; order is still monotonic
+    seqs = [c[0] for c in got]
+    assert seqs == sorted(seqs) and seqs[-1] == 19
+    assert [s[1] for s in seen] == list(range(20))
+    assert any(c[1] == -1 for c in got if c[0] == 13) or 13 not in seqs   # handler exception -> status -1
+    st = w.idle_stats()
+    assert st["commands"] == 20 and st["spins"] > 0 and st["yields"] > 0 and st["parks"] > 0, st
+    assert w.heartbeat() > hb0
+    w.stop()
