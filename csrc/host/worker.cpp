@@ -33,7 +33,9 @@ void StepWorker::stop() {
 
 bool StepWorker::submit(const StepCommand& cmd) {
   const uint64_t head = cmd_head_.load(std::memory_order_relaxed);
-  if (head - cmd_tail_.load(std::memory_order_acquire) > mask_) return false;
+  // Every command produces one completion: bounding the commands that were submitted but whose
+  // completion has not been taken yet bounds both rings.
+  if (head - done_tail_.load(std::memory_order_acquire) > mask_) return false;
   cmds_[head & mask_] = cmd;
   cmd_head_.store(head + 1, std::memory_order_release);
   cv_.notify_one();  // only matters when the worker is parked
@@ -90,8 +92,7 @@ void StepWorker::run() {
       c.status = cmd.kind == 1 ? 0 : handler_(cmd, &value);
       c.value = value;
       c.busy_us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count();
-      // the completion ring has the capacity of the command ring and the consumer must have
-      // drained a slot before it could submit the command that fills it again
+      // submit() admits a command only while its completion slot is free
       const uint64_t dh = done_head_.load(std::memory_order_relaxed);
       done_[dh & mask_] = c;
       done_head_.store(dh + 1, std::memory_order_release);
