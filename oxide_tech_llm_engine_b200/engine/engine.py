@@ -83,7 +83,7 @@ class _Staging:
 class LLMEngine:
     def __init__(self, cfg: EngineConfig, model_cfg: Optional[ModelConfig] = None, *, weights=None,
                  rank: int = 0, world: int = 1, group=None, device: Optional[torch.device] = None,
-                 random_init: bool = False):
+                 random_init: bool = False, random_quant_type: Optional[str] = None):
         self.cfg = cfg
         self.rank, self.world = rank, world
         self.cpu = cfg.backend == "cpu"
@@ -119,6 +119,8 @@ class LLMEngine:
                                  max_splits=cfg.max_splits, weight_mode=weight_mode)
         if weights is not None:
             self.model.load(weights)
+        elif random_init and weight_mode == "quant":
+            self.model.init_random_quant(random_quant_type or "Q4_K", cfg.seed)
         elif random_init:
             self.model.init_random(cfg.seed)
         sc = H.SchedulerConfig()

@@ -85,6 +85,28 @@ class QuantLinear:
             self.w = torch.from_numpy(f).to(device=device, dtype=torch.bfloat16)
 
 
+_RANDOM_BLOCK_HEADERS = {
+    # type -> fp16 header values that make uniformly random payload bytes decode to roughly N(0, 0.02)
+    "Q8_0": (2.7e-4,), "Q4_0": (4.3e-3,), "Q4_K": (1.4e-4, 1.05e-3),
+}
+
+
+def random_quant_linear(type_name: str, n: int, k: int, device, gen: torch.Generator) -> QuantLinear:
+    """A packed weight with random payload bytes generated on the device (benchmarks: no host copy,
+    no quantiser pass). Supported block types: Q8_0, Q4_0, Q4_K."""
+    info = quants.TYPES[type_name]
+    if type_name not in _RANDOM_BLOCK_HEADERS or k % info.block:
+        raise ConfigError(f"random packed weights: unsupported type {type_name} or K % {info.block} != 0")
+    n_blocks = n * k // info.block
+    raw = torch.randint(0, 256, (n_blocks, info.nbytes), dtype=torch.uint8, device=device, generator=gen)
+    hdr = torch.tensor(_RANDOM_BLOCK_HEADERS[type_name], dtype=torch.float16).view(torch.uint8).to(device)
+    raw[:, :hdr.numel()] = hdr
+    lin = QuantLinear.__new__(QuantLinear)
+    lin.code, lin.type_name, lin.n, lin.k, lin.packed = info.code, type_name, n, k, True
+    lin.w = raw.view(-1)
+    return lin
+
+
 class DeviceModel:
     def __init__(self, cfg: ModelConfig, *, rank: int = 0, world: int = 1, group=None,
                  device: Optional[torch.device] = None, max_tokens: int = 2048, max_seqs: int = 256,
@@ -208,6 +230,26 @@ class DeviceModel:
                 L["w_down"] = rnd(d, self.i_l)
             if self.weight_mode == "fp8":
                 self._to_fp8(L)
+            self.layers.append(L)
+
+    def init_random_quant(self, type_name: str = "Q4_K", seed: int = 0, embed_type: str = "Q8_0") -> None:
+        """Random packed GGUF-format weights generated on the device (weight_mode == 'quant')."""
+        cfg, dev = self.cfg, self.device
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed * 1000 + 17)
+        d = cfg.d_model
+        ones = lambda n: torch.full((n,), 1.0 - cfg.norm_weight_offset, dtype=torch.bfloat16, device=dev)
+        self.out_norm = ones(d)
+        self.embed_q = random_quant_linear(embed_type, cfg.vocab_size, d, dev, g)
+        self.embed = None
+        self.lm_head_q = random_quant_linear(embed_type, cfg.vocab_size, d, dev, g)
+        self.layers = []
+        for _ in range(cfg.n_layers):
+            L = {"attn_norm": ones(d), "ffn_norm": ones(d), "b_qkv": None, "q_norm": None, "k_norm": None}
+            for key, n, k in (("attn_q", cfg.q_dim, d), ("attn_k", cfg.kv_dim, d), ("attn_v", cfg.kv_dim, d),
+                              ("attn_output", d, cfg.q_dim), ("ffn_gate", cfg.ffn_dim, d), ("ffn_up", cfg.ffn_dim, d),
+                              ("ffn_down", d, cfg.ffn_dim)):
+                L[key] = random_quant_linear(type_name, n, k, dev, g)
             self.layers.append(L)
 
     def load(self, src: WeightSource) -> None:
