@@ -53,32 +53,44 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
                const c10::optional<Tensor>& ag_flags, int64_t ag_expected, int64_t ag_rows_per_src,
                const c10::optional<Tensor>& ag_ticket, const Tensor& status, int64_t bn,
                int64_t splits, int64_t act, int64_t m_tiles_override, int64_t dst_ld,
-               int64_t my_rank, int64_t k_stagger) {
+               int64_t my_rank, int64_t b_tiled) {
   TORCH_CHECK(a.is_cuda() && w.is_cuda(), "gemm_bf16: CUDA tensors required");
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16,
               "gemm_bf16: bf16 operands required");
   TORCH_CHECK(a.stride(-1) == 1 && w.stride(-1) == 1, "gemm_bf16: K must be contiguous");
+  TORCH_CHECK(b_tiled == 0 || !(group_counts.has_value() && group_counts->defined()),
+              "gemm_bf16: grouped GEMMs take row-major weights");
   const bool grouped3d = a.dim() == 3;
-  TORCH_CHECK(w.dim() == a.dim(), "gemm_bf16: a and w must have the same rank");
+  const bool tiled = b_tiled != 0;
+  if (tiled) {
+    TORCH_CHECK(a.dim() == 2 && w.dim() == 4 && w.size(2) == 128 && w.size(3) == 64 && w.is_contiguous(),
+                "gemm_bf16: tile-major weights are [N/128, K/64, 128, 64] contiguous, 2-D activations");
+  } else {
+    TORCH_CHECK(w.dim() == a.dim(), "gemm_bf16: a and w must have the same rank");
+  }
   const int64_t G = grouped3d ? a.size(0) : 1;
   const int64_t M = grouped3d ? a.size(1) : a.size(0);
   const int64_t K = a.size(-1);
-  const int64_t N = grouped3d ? w.size(1) : w.size(0);
-  TORCH_CHECK(w.size(-1) == K, "gemm_bf16: K mismatch");
+  const int64_t N = tiled ? w.size(0) * 128 : (grouped3d ? w.size(1) : w.size(0));
+  TORCH_CHECK(tiled ? w.size(1) * 64 == K : w.size(-1) == K, "gemm_bf16: K mismatch");
   TORCH_CHECK(K % 8 == 0, "gemm_bf16: K must be a multiple of 8 (16-byte TMA rows)");
   if (grouped3d) {
     TORCH_CHECK(w.size(0) == G, "gemm_bf16: group mismatch");
   }
 
   const uint64_t a_row = static_cast<uint64_t>(a.stride(-2)) * 2;
-  const uint64_t w_row = static_cast<uint64_t>(w.stride(-2)) * 2;
+  const uint64_t w_row = tiled ? 128 : static_cast<uint64_t>(w.stride(-2)) * 2;
   const uint64_t a_grp = grouped3d ? static_cast<uint64_t>(a.stride(0)) * 2 : a_row * M;
-  const uint64_t w_grp = grouped3d ? static_cast<uint64_t>(w.stride(0)) * 2 : w_row * N;
+  const uint64_t w_grp = tiled ? 16384 : (grouped3d ? static_cast<uint64_t>(w.stride(0)) * 2 : w_row * N);
   const int bn_i = bn == 64 ? 64 : (bn == 256 ? 256 : 128);
   CUtensorMap tmA = oxb::make_tma_map(a.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, K, M, G,
                                       a_row, a_grp, 64, 128, 1, CU_TENSOR_MAP_SWIZZLE_128B);
-  CUtensorMap tmB = oxb::make_tma_map(w.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, K, N, G,
-                                      w_row, w_grp, 64, bn_i, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+  CUtensorMap tmB =
+      tiled ? oxb::make_tma_map(w.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, 64, 128,
+                                static_cast<uint64_t>(w.size(0) * w.size(1)), 128, 16384, 64,
+                                bn_i < 128 ? bn_i : 128, 1, CU_TENSOR_MAP_SWIZZLE_128B)
+            : oxb::make_tma_map(w.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, K, N, G, w_row,
+                                w_grp, 64, bn_i, 1, CU_TENSOR_MAP_SWIZZLE_128B);
 
   oxb::GemmParams p{};
   p.M = static_cast<int>(M);
@@ -91,7 +103,7 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
   s = (total_kb + p.kb_per_split - 1) / p.kb_per_split;
   p.epi = static_cast<int>(epi);
   p.act = static_cast<int>(act);
-  p.k_stagger = static_cast<int>(k_stagger);
+  p.b_tiled = static_cast<int>(b_tiled);
   const bool routed = epi == oxb::kEpiRedF32 || epi == oxb::kEpiSlabBf16;
   p.my_rank = static_cast<int>(my_rank);
   if (!routed) {

@@ -20,6 +20,8 @@
 //  * The A operand may be an all-gather / dispatch buffer that peers fill: the producer waits
 //    (bounded) on per-source counters before its first A load of a tile; weight tiles are
 //    requested before that wait.
+//  * Dense weights may be stored tile-major ([N/128][K/64][128][64]) so that each TMA box of the
+//    weight stream is one contiguous 16 KB run of HBM instead of 128 row segments 2K bytes apart.
 //  * Grouped mode walks a device-side table of per-expert row counts, so the grid is static
 //    (CUDA-graph friendly) while the work is data dependent.
 //
@@ -219,7 +221,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           mbar_arrive_expect_tx(&full[s], L::kABytes + L::kBBytes);
           // weights first: they do not depend on any peer
-          tma_load_3d(sB + s * L::kBBytes, &tmB, &full[s], (it.kb0 + kb) * BK, it.n0, it.group);
+          if (p.b_tiled) {
+            // tile-major weights: tile index = (n / 128) * total_kb + kb, box = 128 x 64 (or the
+            // 64-row half of a tile for BN = 64)
+            constexpr int kRowsPerLoad = BN < 128 ? BN : 128;
+#pragma unroll
+            for (int j = 0; j < (BN + 127) / 128; ++j)
+              tma_load_3d(sB + s * L::kBBytes + j * 16384, &tmB, &full[s], 0, BN < 128 ? (it.n0 & 127) : 0,
+                          ((it.n0 >> 7) + j) * total_kb + it.kb0 + kb);
+            (void)kRowsPerLoad;
+          } else {
+            tma_load_3d(sB + s * L::kBBytes, &tmB, &full[s], (it.kb0 + kb) * BK, it.n0, it.group);
+          }
           if (need_wait) {
             int s_lo = 0, s_hi = p.ag_n_src - 1;  // rows_per_src <= 0: rows are not grouped by source
             if (p.ag_rows_per_src > 0) {

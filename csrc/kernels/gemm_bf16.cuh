@@ -34,7 +34,7 @@ struct GemmParams {
   int m_tiles;        // 128-row tiles along M (grouped mode: upper bound over all groups)
   int epi;
   int act;            // kEpiSwigluBf16: 0 = SiLU, 1 = tanh-GELU
-  int k_stagger;      // 1: each CTA starts its k loop at a different block (spreads L2 requests)
+  int b_tiled;        // 1: B is stored tile-major [N/128][K/64][128][64]: every TMA box is one contiguous 16 KB
   void* C;            // kEpiStoreBf16 / kEpiStoreF32 / kEpiSwigluBf16
   long long ldc;
   long long c_group_stride;   // elements between groups of C

@@ -26,6 +26,7 @@ def main() -> None:
     ap.add_argument("--stagger", default="0,1")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--tiled", default="0", help="comma list of 0/1: weights stored tile-major")
     ap.add_argument("--fp8", action="store_true", help="time the block-scaled fp8 GEMM (and its activation quantiser)")
     args = ap.parse_args()
     from . import ops
@@ -41,6 +42,7 @@ def main() -> None:
     out_f32 = torch.zeros(args.m, args.n, device=dev, dtype=torch.float32)
     flops = 2.0 * args.m * args.n * args.k
     wbytes = 2.0 * args.n * args.k
+    w_tiled = ops.tile_weight(w)
     if args.fp8:
         w8, sw = ops.quant_weight_fp8_block(w)
         a8, sa = ops.quant_act_fp8(a)
@@ -73,12 +75,13 @@ def main() -> None:
                           "quant_act_us": round(uq, 2)}), flush=True)
         return
     for bn, sp, stag in itertools.product([int(x) for x in args.bn.split(",")], [int(x) for x in args.splits.split(",")],
-                                           [int(x) for x in args.stagger.split(",")]):
+                                           [int(x) for x in args.tiled.split(",")]):
         if sp > 1 and args.epi != ops.EPI_RED_F32:
             continue
         if args.epi == ops.EPI_SWIGLU_BF16 and args.n % bn:
             continue
-        kw = dict(bn=bn, splits=sp, k_stagger=bool(stag))
+        kw = dict(bn=bn, splits=sp)
+        ww = w_tiled if stag else w
         if args.epi == ops.EPI_RED_F32:
             kw.update(epi=ops.EPI_RED_F32, dst_ptrs=[out_f32.data_ptr()])
         elif args.epi == ops.EPI_STORE_F32:
@@ -86,7 +89,7 @@ def main() -> None:
         else:
             kw.update(epi=args.epi, out=out_bf)
         for _ in range(3):
-            ops.gemm(a, w, **kw)
+            ops.gemm(a, ww, **kw)
         torch.cuda.synchronize()
         ts = []
         for _ in range(args.iters):
@@ -94,7 +97,7 @@ def main() -> None:
                 flush.fill_(1)
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
-            ops.gemm(a, w, **kw)
+            ops.gemm(a, ww, **kw)
             e.record()
             torch.cuda.synchronize()
             ts.append(s.elapsed_time(e) * 1e3)
@@ -102,7 +105,7 @@ def main() -> None:
         ts.sort()
         us = ts[len(ts) // 2]
         print(json.dumps({"m": args.m, "n": args.n, "k": args.k, "epi": args.epi, "bn": bn, "splits": sp,
-                          "stagger": stag, "us": round(us, 2), "weights_gb_s": round(wbytes / us / 1e3, 1),
+                          "tiled": stag, "us": round(us, 2), "weights_gb_s": round(wbytes / us / 1e3, 1),
                           "tflops": round(flops / us / 1e6, 1),
                           "frac_hbm_of_measured": round(wbytes / us / 1e3 / peaks["hbm_gbs"], 3),
                           "frac_tflops_of_measured": round(flops / us / 1e6 / peaks["bf16_tflops"], 3)}), flush=True)

@@ -116,7 +116,8 @@ class LLMEngine:
                                  max_tokens=self.max_tokens, max_seqs=cfg.max_num_seqs,
                                  num_blocks=num_blocks, max_blocks_per_seq=max_blocks_per_seq,
                                  max_logits=max(cfg.max_num_seqs * (1 + (cfg.draft_tokens if cfg.speculative != "off" else 0)), 64),
-                                 max_splits=cfg.max_splits, weight_mode=weight_mode)
+                                 max_splits=cfg.max_splits, weight_mode=weight_mode,
+                                 tile_weights=False if (cfg.comm == "nccl" or cfg.gemm == "library") else None)
         if weights is not None:
             self.model.load(weights)
         elif random_init and weight_mode == "quant":

@@ -20,6 +20,7 @@ oxide-backend-cuda/src/lib.rs:3584-3992 (about 11 kernels per layer, fp32 activa
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -111,7 +112,7 @@ class DeviceModel:
     def __init__(self, cfg: ModelConfig, *, rank: int = 0, world: int = 1, group=None,
                  device: Optional[torch.device] = None, max_tokens: int = 2048, max_seqs: int = 256,
                  num_blocks: int = 1024, max_blocks_per_seq: int = 512, max_logits: Optional[int] = None,
-                 max_splits: int = 16, weight_mode: str = "bf16"):
+                 max_splits: int = 16, weight_mode: str = "bf16", tile_weights: Optional[bool] = None):
         self.cfg = cfg
         self.rank, self.tp, self.group = rank, world, group
         self.device = device or torch.device("cuda", torch.cuda.current_device())
@@ -127,6 +128,9 @@ class DeviceModel:
         if weight_mode == "fp8" and (tp != 1 or cfg.is_moe):
             raise ConfigError("block-scaled fp8 weights are served at tp=1 on dense models")
         self.weight_mode = weight_mode
+        # dense bf16 projections are kept tile-major in HBM (see ops.tile_weight) unless a library
+        # GEMM has to read them
+        self.tile_weights = (os.environ.get("OXB_TILE_WEIGHTS", "1") != "0") if tile_weights is None else tile_weights
         self.D = cfg.head_dim
         self.hq = cfg.n_heads // tp
         self.hkv = cfg.n_kv_heads // tp
@@ -230,7 +234,19 @@ class DeviceModel:
                 L["w_down"] = rnd(d, self.i_l)
             if self.weight_mode == "fp8":
                 self._to_fp8(L)
+            self._tile_layer(L)
             self.layers.append(L)
+        self._tile_head()
+
+    def _tile_layer(self, L: dict) -> None:
+        if self.weight_mode != "bf16" or not self.tile_weights:
+            return
+        for key in ("w_qkv", "w_o") + (() if self.cfg.is_moe else ("w_gu", "w_down")):
+            L[key] = ops.tile_weight(L[key])
+
+    def _tile_head(self) -> None:
+        if self.weight_mode == "bf16" and self.tile_weights and self.lm_head is not None:
+            self.lm_head = ops.tile_weight(self.lm_head)
 
     def init_random_quant(self, type_name: str = "Q4_K", seed: int = 0, embed_type: str = "Q8_0") -> None:
         """Random packed GGUF-format weights generated on the device (weight_mode == 'quant')."""
@@ -308,7 +324,9 @@ class DeviceModel:
                     L["w_down"] = bf(src.f32(p + "ffn_down.weight")[:, i_lo:i_hi])
                 if self.weight_mode == "fp8":
                     self._to_fp8(L)
+                self._tile_layer(L)
             self.layers.append(L)
+        self._tile_head()
 
     def _to_fp8(self, L: dict) -> None:
         """Replaces the bf16 projections of a layer by (e4m3 values, 128 x 128 block scales)."""

@@ -97,14 +97,13 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
          row_meta: Optional[torch.Tensor] = None, ag_flags: Optional[torch.Tensor] = None,
          ag_expected: int = 0, ag_rows_per_src: int = 0, ag_ticket: Optional[torch.Tensor] = None,
          bn: int = 0, splits: int = 1, act: int = 0, m_tiles: int = 0,
-         dst_ld: int = 0, my_rank: int = 0, k_stagger: Optional[bool] = None) -> Optional[torch.Tensor]:
+         dst_ld: int = 0, my_rank: int = 0, k_stagger: Optional[bool] = None) -> Optional[torch.Tensor]:  # noqa: E501
     """tcgen05 GEMM  out = a @ w^T  (bf16 in, fp32 accumulate). See csrc/kernels/gemm_bf16.cu."""
     M = a.shape[-2]
-    N = w.shape[-2]
+    tiled = w.dim() == 4  # tile-major weight from tile_weight()
+    N = w.shape[0] * 128 if tiled else w.shape[-2]
     if bn == 0:
         bn = pick_bn(N, (M + 127) // 128)
-    if k_stagger is None:
-        k_stagger = K_STAGGER_DEFAULT
     if out is None and epi not in (EPI_RED_F32, EPI_SLAB_BF16):
         n_out = N // 2 if epi == EPI_SWIGLU_BF16 else N
         dt = torch.float32 if epi == EPI_STORE_F32 else torch.bfloat16
@@ -112,7 +111,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     _ext().gemm_bf16(a, w, epi, out, bias, list(dst_ptrs), list(arrive_ptrs), done_ticket,
                      reset_on_done, rows_per_owner, group_counts, row_meta, ag_flags, ag_expected,
                      ag_rows_per_src, ag_ticket, status_word(a.device), bn, splits, act, m_tiles, dst_ld,
-                     my_rank, 1 if k_stagger else 0)
+                     my_rank, 1 if tiled else 0)
     _bump()
     return out
 
@@ -151,6 +150,23 @@ def gemm_fp8_block(a8: torch.Tensor, sa_t: torch.Tensor, w8: torch.Tensor, sw: t
     _ext().gemm_fp8_block(a8, sa_t, w8, sw, out, bias, status_word(a8.device))
     _bump()
     return out
+
+
+def tile_weight(w: torch.Tensor) -> torch.Tensor:
+    """[N, K] row-major -> tile-major [N/128, K/64, 128, 64] (a load-time transform): each TMA box of
+    the weight stream becomes one contiguous 16 KB run. Needs N % 128 == 0 and K % 64 == 0; other
+    shapes stay row-major (the GEMM takes either)."""
+    N, K = w.shape
+    if N % 128 or K % 64:
+        return w
+    return w.view(N // 128, 128, K // 64, 64).permute(0, 2, 1, 3).contiguous()
+
+
+def untile_weight(w: torch.Tensor) -> torch.Tensor:
+    if w.dim() != 4:
+        return w
+    nt, kt = w.shape[0], w.shape[1]
+    return w.permute(0, 2, 1, 3).reshape(nt * 128, kt * 64)
 
 
 def paged_decode(q, k_cache, v_cache, block_tables, seq_lens, pages_per_split, part_o, part_ml, out,

@@ -559,3 +559,24 @@ def test_gemm_fp8_block_scaled(ops, M, N, K):
     ref = ref + bias.float()
     err = (out.float() - ref).abs().max().item()
     assert err <= 2e-2 * ref.abs().max().item() + 1e-3, err
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("m,n,k", [(200, 512, 256), (256, 1280, 1024), (8, 768, 192)])
+def test_gemm_tile_major_weights(ops, m, n, k, bn):
+    """Weights stored tile-major ([N/128, K/64, 128, 64]) give the same product as row-major."""
+    torch.manual_seed(m + n + k + bn)
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.1).bfloat16()
+    wt = ops.tile_weight(w)
+    assert wt.dim() == 4 and torch.equal(ops.untile_weight(wt), w)
+    ref = a.float() @ w.float().t()
+    out = ops.gemm(a, wt, bn=bn)
+    ops.check_status(out.device)
+    assert _rel_err(out.float(), ref) < 2e-2
+    acc = torch.zeros(m, n, device="cuda")
+    ops.gemm(a, wt, epi=ops.EPI_RED_F32, dst_ptrs=[acc.data_ptr()], bn=bn, splits=2)
+    ops.check_status(out.device)
+    assert _rel_err(acc, ref) < 1e-2
+    assert ops.tile_weight(w[:100]).dim() == 2   # shapes that do not tile stay row-major
