@@ -83,8 +83,10 @@ class _Staging:
 class LLMEngine:
     def __init__(self, cfg: EngineConfig, model_cfg: Optional[ModelConfig] = None, *, weights=None,
                  rank: int = 0, world: int = 1, group=None, device: Optional[torch.device] = None,
-                 random_init: bool = False, random_quant_type: Optional[str] = None):
+                 random_init: bool = False, random_quant_type: Optional[str] = None, pp=None):
         self.cfg = cfg
+        self.group = group
+        self.pp = pp  # parallel.pipeline.PpContext or None; rank/world/group describe the TP group of this stage
         self.rank, self.world = rank, world
         self.cpu = cfg.backend == "cpu"
         if self.cpu:
@@ -117,7 +119,12 @@ class LLMEngine:
                                  num_blocks=num_blocks, max_blocks_per_seq=max_blocks_per_seq,
                                  max_logits=max(cfg.max_num_seqs * (1 + (cfg.draft_tokens if cfg.speculative != "off" else 0)), 64),
                                  max_splits=cfg.max_splits, weight_mode=weight_mode,
-                                 tile_weights=False if (cfg.comm == "nccl" or cfg.gemm == "library") else None)
+                                 tile_weights=False if (cfg.comm == "nccl" or cfg.gemm == "library") else None,
+                                 layer_range=pp.layers(mc.n_layers) if pp is not None else None)
+        if pp is not None:
+            self.pp_recv = torch.zeros(self.max_tokens // world, mc.d_model, dtype=torch.bfloat16, device=self.device)
+            self.pp_tokens = torch.zeros(max(cfg.max_num_seqs * (1 + cfg.draft_tokens), 64), dtype=torch.int32,
+                                         device=self.device)
         if weights is not None:
             self.model.load(weights)
         elif random_init and weight_mode == "quant":
@@ -389,6 +396,29 @@ class LLMEngine:
         self.stats["graph_replays"] += 1
         return self.model.logits[:s.n_logits]
 
+    def _step_pp(self, plan, s: StepInputs, n_rows: int) -> np.ndarray:
+        """One step of a pipeline stage: receive the residual rows from the previous stage (NCCL
+        recv), run this stage's layers, send them on or sample; the sampled ids are broadcast down
+        the pipeline column so that every stage's scheduler replica applies the same update."""
+        import torch.distributed as dist
+
+        ctx = self.pp
+        rpr = s.m // self.world
+        hidden = None
+        if not ctx.first:
+            hidden = self.pp_recv[:rpr]
+            dist.recv(hidden, src=ctx.prev_rank)
+        out = self.model.forward(s, hidden)
+        tok = self.pp_tokens[:max(n_rows, 1)]
+        if ctx.last:
+            toks = self._sample(plan, out, n_rows)
+            if n_rows:
+                tok[:n_rows].copy_(torch.from_numpy(np.ascontiguousarray(toks, dtype=np.int32)))
+        else:
+            dist.send(out.contiguous(), dst=ctx.next_rank)
+        dist.broadcast(tok, src=ctx.column_src, group=ctx.column_group)
+        return tok[:n_rows].cpu().numpy()
+
     def attach_monitor(self, monitor) -> None:
         """`monitor.check()` (parallel.watchdog.RankMonitor) runs before every step: a peer that
         stopped answering is found on the host, before any kernel waits on it."""
@@ -424,9 +454,12 @@ class LLMEngine:
             tokens = self._step_cpu(plan)
         else:
             s, bucket = self._fill(plan)
-            logits = self._forward(s, bucket)
             n_rows = plan.logit_rows.size
-            tokens = self._sample(plan, logits, n_rows)
+            if self.pp is not None:
+                tokens = self._step_pp(plan, s, n_rows)
+            else:
+                logits = self._forward(s, bucket)
+                tokens = self._sample(plan, logits, n_rows)
         events = self.sched.update(plan, tokens)
         self.stats["steps"] += 1
         self.stats["decode_tokens"] += plan.n_decode
@@ -496,12 +529,12 @@ class LLMEngine:
             idx = self.sampled[:n_log] + self.rank * self.model.v_l
             vals = torch.empty(self.world, n_log, dtype=torch.float32, device=self.device)
             idxs = torch.empty(self.world, n_log, dtype=torch.int32, device=self.device)
-            dist.all_gather_into_tensor(vals, self.sampled_val[:n_log].contiguous())
-            dist.all_gather_into_tensor(idxs, idx.contiguous())
+            dist.all_gather_into_tensor(vals, self.sampled_val[:n_log].contiguous(), group=self.group)
+            dist.all_gather_into_tensor(idxs, idx.contiguous(), group=self.group)
             ops.argmax_combine(vals, idxs, self.sampled[:n_log])
             return None
         full = torch.empty(self.world, n_log, self.model.v_l, dtype=torch.float32, device=self.device)
-        dist.all_gather_into_tensor(full, logits.contiguous())
+        dist.all_gather_into_tensor(full, logits.contiguous(), group=self.group)
         return full.permute(1, 0, 2).reshape(n_log, -1).contiguous()
 
     def _fetch(self, n_rows: int) -> np.ndarray:

@@ -112,7 +112,8 @@ class DeviceModel:
     def __init__(self, cfg: ModelConfig, *, rank: int = 0, world: int = 1, group=None,
                  device: Optional[torch.device] = None, max_tokens: int = 2048, max_seqs: int = 256,
                  num_blocks: int = 1024, max_blocks_per_seq: int = 512, max_logits: Optional[int] = None,
-                 max_splits: int = 16, weight_mode: str = "bf16", tile_weights: Optional[bool] = None):
+                 max_splits: int = 16, weight_mode: str = "bf16", tile_weights: Optional[bool] = None,
+                 layer_range: Optional[tuple] = None):
         self.cfg = cfg
         self.rank, self.tp, self.group = rank, world, group
         self.device = device or torch.device("cuda", torch.cuda.current_device())
@@ -127,6 +128,12 @@ class DeviceModel:
             raise ConfigError("packed GGUF weights are served at tp=1; use weight_mode='bf16' for tp>1")
         if weight_mode == "fp8" and (tp != 1 or cfg.is_moe):
             raise ConfigError("block-scaled fp8 weights are served at tp=1 on dense models")
+        # pipeline stage: this model owns layers [lo, hi); the first stage embeds, the last one
+        # runs the final norm and the LM head, the others hand the residual stream on
+        self.layer_lo, self.layer_hi = layer_range if layer_range is not None else (0, cfg.n_layers)
+        self.pp_first, self.pp_last = self.layer_lo == 0, self.layer_hi == cfg.n_layers
+        if layer_range is not None and weight_mode != "bf16":
+            raise ConfigError("pipeline stages are served with bf16 weights")
         self.weight_mode = weight_mode
         # dense bf16 projections are kept tile-major in HBM (see ops.tile_weight) unless a library
         # GEMM has to read them
@@ -182,8 +189,10 @@ class DeviceModel:
         self.logits = torch.zeros(self.max_logits, self.v_l, dtype=torch.float32, device=dev)
         self.part_o = torch.zeros(max_seqs * self.hq * max_splits * self.D, dtype=torch.float32, device=dev)
         self.part_ml = torch.zeros(max_seqs * self.hq * max_splits * 2, dtype=torch.float32, device=dev)
-        self.k_cache = [torch.zeros(num_blocks, self.hkv, 16, self.D, **bf) for _ in range(cfg.n_layers)]
-        self.v_cache = [torch.zeros(num_blocks, self.hkv, 16, self.D, **bf) for _ in range(cfg.n_layers)]
+        n_local = self.layer_hi - self.layer_lo
+        self.k_cache = [torch.zeros(num_blocks, self.hkv, 16, self.D, **bf) for _ in range(n_local)]
+        self.v_cache = [torch.zeros(num_blocks, self.hkv, 16, self.D, **bf) for _ in range(n_local)]
+        self.pp_out = torch.zeros(rpr, d, **bf) if not self.pp_last else None
         if weight_mode == "quant":
             self.gu_acc = torch.zeros(M, 2 * self.i_l, dtype=torch.float32, device=dev)
             self._scratch: Optional[torch.Tensor] = None
@@ -201,7 +210,7 @@ class DeviceModel:
 
     # ------------------------------------------------------------------ weights
     def kv_bytes(self) -> int:
-        return 2 * self.cfg.n_layers * self.num_blocks * self.hkv * 16 * self.D * 2
+        return 2 * (self.layer_hi - self.layer_lo) * self.num_blocks * self.hkv * 16 * self.D * 2
 
     def init_random(self, seed: int = 0, std: float = 0.02) -> None:
         """Random-init shards generated on the device (benchmarks; no host copy of the model)."""
@@ -222,7 +231,7 @@ class DeviceModel:
         self.lm_head = rnd(self.v_l, d)
         self.out_norm = ones(d)
         self.layers = []
-        for _ in range(cfg.n_layers):
+        for _ in range(self.layer_lo, self.layer_hi):
             L = {"attn_norm": ones(d), "ffn_norm": ones(d), "w_qkv": rnd(self.wqkv, d),
                  "w_o": rnd(d, self.hq * self.D), "b_qkv": None, "q_norm": None, "k_norm": None}
             if cfg.is_moe:
@@ -287,7 +296,7 @@ class DeviceModel:
             self.embed = bf(src.f32("token_embd.weight"))
             self.lm_head = bf(src.f32(head_name)[r * self.v_l:(r + 1) * self.v_l])
         self.layers = []
-        for i in range(cfg.n_layers):
+        for i in range(self.layer_lo, self.layer_hi):
             p = f"blk.{i}."
             L: dict = {"attn_norm": bf(src.f32(p + "attn_norm.weight")), "ffn_norm": bf(src.f32(p + "ffn_norm.weight"))}
             L["q_norm"] = bf(src.f32(p + "attn_q_norm.weight")) if src.has(p + "attn_q_norm.weight") else None
@@ -339,7 +348,7 @@ class DeviceModel:
 
     def _finalize(self, rows: int, norm_w, *, acc: Optional[int], gather: str, flag_base: int,
                   r0: int, first: bool = False, row_map=None, layer: Optional[dict] = None,
-                  moe: bool = False, moe_acc: bool = False) -> None:
+                  moe: bool = False, moe_acc: bool = False, out_local: Optional[torch.Tensor] = None) -> None:
         tp, d = self.tp, self.cfg.d_model
         multi = tp > 1
         kw = {}
@@ -355,6 +364,13 @@ class DeviceModel:
                 kw["expected"] = tp
                 kw["ticket"] = self.tickets[T_FIN0 + acc:T_FIN0 + acc + 1]
         flag_ptrs = self._flag_ptrs(flag_base + self.rank) if multi else []
+        if out_local is not None:
+            # stage boundary: fold the pending accumulator into the residual stream, no norm, rows
+            # stay on this rank (they travel to the next stage by NCCL send)
+            ops.finalize_norm(rows=rows, n=d, residual_in=self.residual, residual_out=self.residual, norm_w=None,
+                              eps=self.cfg.rms_eps, out_ptrs=[out_local.data_ptr()], out_flag_ptrs=[],
+                              out_row_off=0, device=self.device, **kw)
+            return
         if moe:
             ops.finalize_norm(rows=rows, n=d, residual_in=self.residual, residual_out=self.residual,
                               norm_w=norm_w, eps=self.cfg.rms_eps, w_offset=self.cfg.norm_weight_offset,
@@ -413,8 +429,10 @@ class DeviceModel:
                  splits=ops.pick_splits(m, lin.n, lin.k, bn), dst_ld=out_f32.stride(0))
 
     # ------------------------------------------------------------------ forward
-    def forward(self, s: StepInputs) -> torch.Tensor:
-        """Runs one step; returns fp32 logits [n_logits, vocab/tp] (a view of a static buffer)."""
+    def forward(self, s: StepInputs, hidden_in: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Runs one step; returns fp32 logits [n_logits, vocab/tp] (a view of a static buffer). A
+        pipeline stage that is not the first takes the residual rows of this rank from the previous
+        stage in `hidden_in`; one that is not the last returns its residual rows [M/tp, d] instead."""
         if self.weight_mode == "quant":
             return self._forward_quant(s)
         if self.weight_mode == "fp8":
@@ -424,7 +442,10 @@ class DeviceModel:
         rpr = M // tp
         r0 = rank * rpr
         d = cfg.d_model
-        ops.embed_gather(s.token_ids[r0:r0 + rpr], self.embed, self.residual[:rpr], cfg.emb_scale)
+        if self.pp_first:
+            ops.embed_gather(s.token_ids[r0:r0 + rpr], self.embed, self.residual[:rpr], cfg.emb_scale)
+        else:
+            self.residual[:rpr].copy_(hidden_in[:rpr])
         self._finalize(rpr, self.layers[0]["attn_norm"], acc=None, gather="gather0", flag_base=F_AG0, r0=r0,
                        first=True)
         g0 = self.ws.local("gather0")[:M]
@@ -462,10 +483,14 @@ class DeviceModel:
                 bn = ops.pick_bn(d, (M + 127) // 128, can_split=True)
                 sp = ops.pick_splits(M, d, self.i_l, bn)
                 ops.gemm(self.act[:M], L["w_down"], bn=bn, splits=sp, **self._red_kwargs(1, T_DONE_D, rpr, sp))
-            last = li == cfg.n_layers - 1
+            last = li == len(self.layers) - 1
             if not last:
                 self._finalize(rpr, self.layers[li + 1]["attn_norm"], acc=1, gather="gather0", flag_base=F_AG0,
                                r0=r0, moe_acc=cfg.is_moe)
+        if not self.pp_last:
+            self._finalize(rpr, None, acc=1, gather="", flag_base=0, r0=r0, moe_acc=cfg.is_moe,
+                           out_local=self.pp_out)
+            return self.pp_out[:rpr]
         # ---- final norm (logit rows only) + vocab-parallel LM head ----
         n_log = max(s.n_logits, 1)  # a step without logit rows still drains the last accumulator
         row_map = s.logit_map[r0:r0 + rpr] if s.logit_map is not None else None

@@ -100,3 +100,54 @@ def broadcast_tokens(tokens: torch.Tensor, src: int, group=None) -> torch.Tensor
     """The last stage's sampled ids reach every replica of the scheduler."""
     dist.broadcast(tokens, src, group=group)
     return tokens
+
+
+@dataclass
+class PpContext:
+    """Where one rank sits in a (pp x tp) grid: global rank = stage * tp + tp_rank."""
+    pp: int
+    tp: int
+    stage: int
+    tp_rank: int
+    tp_group: object = None       # ranks of this stage (the fused TP kernels' peers)
+    column_group: object = None   # the ranks with the same tp_rank in every stage
+    column_src: int = 0           # global rank of the last stage in this column (token source)
+
+    @property
+    def first(self) -> bool:
+        return self.stage == 0
+
+    @property
+    def last(self) -> bool:
+        return self.stage == self.pp - 1
+
+    @property
+    def prev_rank(self) -> int:
+        return (self.stage - 1) * self.tp + self.tp_rank
+
+    @property
+    def next_rank(self) -> int:
+        return (self.stage + 1) * self.tp + self.tp_rank
+
+    def layers(self, n_layers: int) -> tuple[int, int]:
+        return layer_partition_for_rank(n_layers, self.pp, self.stage)
+
+
+def build_pp_context(rank: int, world: int, pp: int) -> PpContext:
+    """Creates the process groups of a pp x tp grid. Every rank of the job must call this (group
+    creation is collective), after `init_process_group`."""
+    if world % pp:
+        raise ValueError(f"world {world} is not a multiple of pp {pp}")
+    tp = world // pp
+    stage, tp_rank = divmod(rank, tp)
+    tp_group = column_group = None
+    for st in range(pp):
+        g = dist.new_group(list(range(st * tp, (st + 1) * tp)))
+        if st == stage:
+            tp_group = g
+    for c in range(tp):
+        g = dist.new_group([st * tp + c for st in range(pp)])
+        if c == tp_rank:
+            column_group = g
+    return PpContext(pp=pp, tp=tp, stage=stage, tp_rank=tp_rank, tp_group=tp_group, column_group=column_group,
+                     column_src=(pp - 1) * tp + tp_rank)
