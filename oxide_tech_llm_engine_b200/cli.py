@@ -54,7 +54,7 @@ def add_common(p: argparse.ArgumentParser) -> None:
     p.add_argument("-c", "--ctx-size", type=int, default=8192)
     p.add_argument("--n-gpu-layers", type=int, default=-1)
     p.add_argument("-b", "--backend", default="auto")
-    p.add_argument("--weights", default="auto", choices=["auto", "bf16", "quant"])
+    p.add_argument("--weights", default="auto", choices=["auto", "bf16", "quant", "fp8"])
     p.add_argument("--max-slots", type=int, default=64)
     p.add_argument("--gpu", type=int, default=0)
     p.add_argument("-p", "--prompt")
