@@ -98,3 +98,41 @@ def test_roofline_receipt_rejects_impossible_numbers():
     assert 0.4 < r.mbu < 0.6 and r.mfu < 0.01
     with pytest.raises(BenchmarkIntegrityViolation):
         RooflineReceipt.from_run(mc, tokens_per_s=1138.45 * 4, batch=1, peaks=peaks)
+
+
+def test_energy_sampler_against_fake_nvml():
+    from oxide_tech_llm_engine_b200.utils.energy import EnergySampler
+
+    class FakeNvml:
+        def __init__(self, counter=True):
+            self.counter, self.mj, self.mw = counter, 5_000_000, 700_000
+        def nvmlInit(self): pass
+        def nvmlDeviceGetHandleByIndex(self, i): return i
+        def nvmlDeviceGetTotalEnergyConsumption(self, h):
+            if not self.counter:
+                raise RuntimeError("not supported")
+            return self.mj
+        def nvmlDeviceGetPowerUsage(self, h): return self.mw
+    now = [10.0]
+    nv = FakeNvml(counter=True)
+    s = EnergySampler(0, nvml=nv, clock=lambda: now[0]).start()
+    nv.mj += 1_400_000
+    now[0] += 2.0
+    r = s.stop(tokens=2800)
+    assert r.source == "counter" and abs(r.joules - 1400.0) < 1e-6 and abs(r.watts - 700.0) < 1e-6
+    assert abs(r.tokens_per_joule - 2.0) < 1e-9 and r.to_dict()["tokens"] == 2800
+    nv2 = FakeNvml(counter=False)
+    s2 = EnergySampler(0, nvml=nv2, clock=lambda: now[0], period_s=3600)
+    assert s2.source == "integrated"
+    s2.start()
+    s2.sample_once(0.5)
+    nv2.mw = 900_000
+    s2.sample_once(0.5)
+    now[0] += 1.0
+    r2 = s2.stop(tokens=10)
+    assert abs(r2.joules - 800.0) < 1e-6 and abs(r2.watts - 800.0) < 1e-6
+
+    class Broken:
+        def nvmlInit(self): raise RuntimeError("no driver")
+    r3 = EnergySampler(0, nvml=Broken()).start().stop(5)
+    assert r3.source == "unavailable" and r3.joules == 0 and r3.tokens_per_joule == 0
