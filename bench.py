@@ -190,6 +190,10 @@ def main() -> None:
     wall = time.perf_counter() - t0
     clocks = sampler.stop() if sampler else {}
     eng.check_device_status()
+    # latency view of the same run: time to first token of every admitted request (all arrive at
+    # t=0, so it includes queueing behind the other prompts) and time per output token
+    reqs = [r for r in eng.requests.values() if r.t_first_token is not None]
+    ttft = sorted((r.t_first_token - r.t_arrival) * 1e3 for r in reqs)
     dev_ms = sum(a.elapsed_time(b) for a, b in ev)
     tokens = sum(batch_sizes)
     t = torch.tensor([dev_ms, wall * 1e3], dtype=torch.float64, device=dev)
@@ -220,6 +224,9 @@ def main() -> None:
                 "prefill_tokens": int(prefill_tokens), "prefill_seconds": round(prefill_s, 2),
                 "prefill_tok_per_s": round(prefill_tokens / max(prefill_s, 1e-9), 1),
                 "build_seconds": round(t_prefill - t_build, 2),
+                "ttft_p50_ms": round(ttft[len(ttft) // 2], 1) if ttft else None,
+                "ttft_p99_ms": round(ttft[min(len(ttft) - 1, int(len(ttft) * 0.99))], 1) if ttft else None,
+                "tpot_p50_ms": round(statistics.median(a.elapsed_time(b) for a, b in ev), 3),
             },
             "clocks": clocks,
             "e2e": {"value": round(e2e, 2), "unit": "tokens/s", "ms_per_step": round(wall_ms / args.steps, 4),

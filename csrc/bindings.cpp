@@ -227,7 +227,8 @@ void quant_act_fp8(const Tensor& x, const Tensor& q, const Tensor& sa_t) {
 void paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
                   const Tensor& block_tables, const Tensor& seq_lens, const Tensor& pages_per_split,
                   const Tensor& part_o, const Tensor& part_ml, const Tensor& out, int64_t batch,
-                  int64_t max_splits, int64_t window, double scale) {
+                  int64_t max_splits, int64_t window, double scale,
+                  const c10::optional<Tensor>& status) {
   TORCH_CHECK(q.dim() == 3 && k_cache.dim() == 4, "paged_decode: q [B,Hq,D], cache [blk,Hkv,16,D]");
   TORCH_CHECK(k_cache.size(2) == 16, "paged_decode: 16-token pages");
   oxb::DecodeAttnParams p{};
@@ -254,6 +255,8 @@ void paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
   TORCH_CHECK(part_ml.numel() >= batch * p.Hq * max_splits * 2, "paged_decode: part_ml too small");
   p.window = static_cast<int>(window);
   p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
+  p.num_blocks = static_cast<int>(k_cache.size(0));
+  p.status = opt_ptr<int>(status);
   oxb::launch_paged_decode(p, static_cast<int>(batch), D, cur_stream());
   check_launch("paged_decode");
 }
@@ -261,7 +264,8 @@ void paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
 void paged_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
                    const Tensor& block_tables, const Tensor& tile_seq, const Tensor& tile_q0,
                    const Tensor& q_start, const Tensor& q_lens, const Tensor& ctx_lens,
-                   const Tensor& out, int64_t n_tiles, int64_t window, double scale) {
+                   const Tensor& out, int64_t n_tiles, int64_t window, double scale,
+                   const c10::optional<Tensor>& status) {
   TORCH_CHECK(q.dim() == 3 && k_cache.dim() == 4, "paged_prefill: q [T,Hq,D], cache [blk,Hkv,16,D]");
   oxb::PrefillAttnParams p{};
   const int D = static_cast<int>(q.size(2));
@@ -284,6 +288,8 @@ void paged_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache
   p.Hkv = static_cast<int>(k_cache.size(1));
   p.window = static_cast<int>(window);
   p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
+  p.num_blocks = static_cast<int>(k_cache.size(0));
+  p.status = opt_ptr<int>(status);
   oxb::launch_paged_prefill(p, static_cast<int>(n_tiles), D, cur_stream());
   check_launch("paged_prefill");
 }
@@ -328,6 +334,7 @@ void paged_prefill_tc(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   CUtensorMap tmV = oxb::make_tma_map(v_cache.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, D,
                                       kv_rows, 1, static_cast<uint64_t>(D) * 2, 0, 64, 16, 1,
                                       CU_TENSOR_MAP_SWIZZLE_128B);
+  p.num_blocks = static_cast<int>(k_cache.size(0));
   oxb::launch_paged_prefill_tc(tmQ, tmK, tmV, p, static_cast<int>(n_tiles), D,
                                reinterpret_cast<int*>(status.data_ptr()), cur_stream());
   check_launch("paged_prefill_tc");

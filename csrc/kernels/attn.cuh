@@ -22,6 +22,10 @@ struct DecodeAttnParams {
   long long out_stride;
   int max_blocks, Hq, Hkv, max_splits, window;
   float scale_log2;  // softmax scale * log2(e)
+  // Bounds check of block-table entries: an id outside [0, num_blocks) is recorded in *status
+  // (kStatusBadIndex) and page 0 is read instead. num_blocks <= 0 or status == nullptr: no check.
+  int num_blocks;
+  int* status;
 };
 
 void launch_paged_decode(const DecodeAttnParams& p, int batch, int head_dim, cudaStream_t stream);
@@ -41,6 +45,8 @@ struct PrefillAttnParams {
   long long out_stride;
   int max_blocks, Hq, Hkv, window;
   float scale_log2;
+  int num_blocks;  // bound for block-table entries (<= 0: unchecked), violations go to *status
+  int* status;
 };
 
 void launch_paged_prefill(const PrefillAttnParams& p, int n_tiles, int head_dim,

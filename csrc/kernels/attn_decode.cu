@@ -127,11 +127,19 @@ paged_decode_kernel(const DecodeAttnParams p) {
   const long long page_stride = static_cast<long long>(p.Hkv) * kPage * D;  // elements per block
   const long long head_off = static_cast<long long>(kvh) * kPage * D;
 
+  // a block id outside the pool is recorded and replaced by block 0 (never dereferenced)
+  auto checked = [&](int b) -> int {
+    if (p.num_blocks > 0 && static_cast<unsigned>(b) >= static_cast<unsigned>(p.num_blocks)) {
+      if (p.status != nullptr && lane == 0) atomicExch(p.status, 5 /* kStatusBadIndex */);
+      return 0;
+    }
+    return b;
+  };
   int page = pg_lo + warp;
-  int blk = page < pg_hi ? bt[page] : 0;
+  int blk = page < pg_hi ? checked(bt[page]) : 0;
   for (; page < pg_hi; page += kWarps) {
     const int next_page = page + kWarps;
-    const int next_blk = next_page < pg_hi ? bt[next_page] : 0;
+    const int next_blk = next_page < pg_hi ? checked(bt[next_page]) : 0;
     const __nv_bfloat16* kp = p.k_cache + static_cast<long long>(blk) * page_stride + head_off;
     const __nv_bfloat16* vp = p.v_cache + static_cast<long long>(blk) * page_stride + head_off;
 

@@ -111,9 +111,16 @@ __global__ void __launch_bounds__(kWarps * 32) paged_prefill_kernel(const Prefil
   const long long page_stride = static_cast<long long>(p.Hkv) * kPage * D;
   const long long head_off = static_cast<long long>(kvh) * kPage * D;
 
-  int blk = first_page < n_pages ? bt[first_page] : 0;
+  auto checked = [&](int b) -> int {
+    if (p.num_blocks > 0 && static_cast<unsigned>(b) >= static_cast<unsigned>(p.num_blocks)) {
+      if (p.status != nullptr && (threadIdx.x & 31) == 0) atomicExch(p.status, 5 /* kStatusBadIndex */);
+      return 0;
+    }
+    return b;
+  };
+  int blk = first_page < n_pages ? checked(bt[first_page]) : 0;
   for (int page = first_page; page < n_pages; ++page) {
-    const int next_blk = page + 1 < n_pages ? bt[page + 1] : 0;
+    const int next_blk = page + 1 < n_pages ? checked(bt[page + 1]) : 0;
     const __nv_bfloat16* kp = p.k_cache + static_cast<long long>(blk) * page_stride + head_off;
     const __nv_bfloat16* vp = p.v_cache + static_cast<long long>(blk) * page_stride + head_off;
 

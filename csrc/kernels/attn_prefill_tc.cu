@@ -144,7 +144,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         mbar_arrive_expect_tx(&k_full[s], DH * kHalfBytes);
         for (int pg = 0; pg < BKV / 16; ++pg) {
           const int pi = page0 + pg;
-          const int blk = pi < p.max_blocks ? bt[pi] : 0;
+          int blk = pi < p.max_blocks ? bt[pi] : 0;
+          if (p.num_blocks > 0 && static_cast<unsigned>(blk) >= static_cast<unsigned>(p.num_blocks)) {
+            atomicExch(status, kStatusBadIndex);
+            blk = 0;
+          }
           const int row = (blk * p.Hkv + kvh) * 16;
           for (int hf = 0; hf < DH; ++hf)
             tma_load_2d(sK + (s * DH + hf) * kHalfBytes + pg * 2048, &tmK, &k_full[s], hf * 64, row);
@@ -152,7 +156,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         mbar_arrive_expect_tx(&v_full[s], DH * kHalfBytes);
         for (int pg = 0; pg < BKV / 16; ++pg) {
           const int pi = page0 + pg;
-          const int blk = pi < p.max_blocks ? bt[pi] : 0;
+          int blk = pi < p.max_blocks ? bt[pi] : 0;
+          if (p.num_blocks > 0 && static_cast<unsigned>(blk) >= static_cast<unsigned>(p.num_blocks)) {
+            atomicExch(status, kStatusBadIndex);
+            blk = 0;
+          }
           const int row = (blk * p.Hkv + kvh) * 16;
           for (int hf = 0; hf < DH; ++hf)
             tma_load_2d(sV + (s * DH + hf) * kHalfBytes + pg * 2048, &tmV, &v_full[s], hf * 64, row);

@@ -172,7 +172,7 @@ def untile_weight(w: torch.Tensor) -> torch.Tensor:
 def paged_decode(q, k_cache, v_cache, block_tables, seq_lens, pages_per_split, part_o, part_ml, out,
                  *, batch: int, max_splits: int, window: int = 0, scale: float) -> None:
     _ext().paged_decode(q, k_cache, v_cache, block_tables, seq_lens, pages_per_split, part_o, part_ml,
-                        out, batch, max_splits, window, scale)
+                        out, batch, max_splits, window, scale, status_word(q.device))
     _bump(2)
 
 
@@ -188,7 +188,7 @@ def paged_prefill(q, k_cache, v_cache, block_tables, tile_seq, tile_q0, q_start,
                                 ctx_lens, out, n_tiles, window, scale, status_word(q.device))
     else:
         _ext().paged_prefill(q, k_cache, v_cache, block_tables, tile_seq, tile_q0, q_start, q_lens,
-                             ctx_lens, out, n_tiles, window, scale)
+                             ctx_lens, out, n_tiles, window, scale, status_word(q.device))
     _bump()
 
 

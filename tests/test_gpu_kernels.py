@@ -580,3 +580,30 @@ def test_gemm_tile_major_weights(ops, m, n, k, bn):
     ops.check_status(out.device)
     assert _rel_err(acc, ref) < 1e-2
     assert ops.tile_weight(w[:100]).dim() == 2   # shapes that do not tile stay row-major
+
+
+@pytest.mark.gpu
+def test_block_table_bounds_are_checked_without_touching_memory(ops):
+    """A block id beyond the pool that the kernel was told about is recorded in the status word and
+    page 0 is read instead. The 'pool' passed here is a view of the first 8 blocks of a 32-block
+    allocation, so even an unchecked read would stay inside allocated memory."""
+    torch.manual_seed(0)
+    D, hq, hkv, B = 128, 8, 1, 2
+    full_k = torch.randn(32, hkv, 16, D, device="cuda").bfloat16()
+    full_v = torch.randn(32, hkv, 16, D, device="cuda").bfloat16()
+    k, v = full_k[:8], full_v[:8]
+    q = torch.randn(B, hq, D, device="cuda").bfloat16()
+    bt = torch.tensor([[0, 1, 2, 3], [4, 20, 5, 6]], dtype=torch.int32, device="cuda")   # 20 >= 8
+    lens = torch.tensor([40, 50], dtype=torch.int32, device="cuda")
+    pps = torch.tensor([4], dtype=torch.int32, device="cuda")
+    part_o = torch.zeros(B * hq * 4 * D, device="cuda")
+    part_ml = torch.zeros(B * hq * 4 * 2, device="cuda")
+    out = torch.zeros(B, hq * D, device="cuda", dtype=torch.bfloat16)
+    ops.check_status(q.device)
+    ops.paged_decode(q, k, v, bt, lens, pps, part_o, part_ml, out, batch=B, max_splits=4, scale=D ** -0.5)
+    torch.cuda.synchronize()
+    from oxide_tech_llm_engine_b200.errors import EngineError
+    with pytest.raises(EngineError):
+        ops.check_status(q.device)
+    ops.check_status(q.device)   # the status word was cleared by the failed check
+    assert torch.isfinite(out.float()).all()
