@@ -53,7 +53,8 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
                const c10::optional<Tensor>& ag_flags, int64_t ag_expected, int64_t ag_rows_per_src,
                const c10::optional<Tensor>& ag_ticket, const Tensor& status, int64_t bn,
                int64_t splits, int64_t act, int64_t m_tiles_override, int64_t dst_ld,
-               int64_t my_rank, int64_t b_tiled) {
+               int64_t my_rank, int64_t b_tiled,
+               const c10::optional<Tensor>& prefetch) {
   TORCH_CHECK(a.is_cuda() && w.is_cuda(), "gemm_bf16: CUDA tensors required");
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16,
               "gemm_bf16: bf16 operands required");
@@ -104,6 +105,11 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
   p.epi = static_cast<int>(epi);
   p.act = static_cast<int>(act);
   p.b_tiled = static_cast<int>(b_tiled);
+  if (prefetch.has_value() && prefetch->defined()) {
+    TORCH_CHECK(prefetch->is_contiguous() && prefetch->is_cuda(), "gemm_bf16: prefetch range must be contiguous");
+    p.prefetch_ptr = prefetch->data_ptr();
+    p.prefetch_bytes = static_cast<long long>(prefetch->numel() * prefetch->element_size()) & ~15LL;
+  }
   const bool routed = epi == oxb::kEpiRedF32 || epi == oxb::kEpiSlabBf16;
   p.my_rank = static_cast<int>(my_rank);
   if (!routed) {
@@ -255,8 +261,8 @@ void paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
   TORCH_CHECK(part_ml.numel() >= batch * p.Hq * max_splits * 2, "paged_decode: part_ml too small");
   p.window = static_cast<int>(window);
   p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
-  p.num_blocks = static_cast<int>(k_cache.size(0));
-  p.status = opt_ptr<int>(status);
+  p.status = opt_ptr<int>(status);  // given only when bounds checking is on
+  p.num_blocks = p.status != nullptr ? static_cast<int>(k_cache.size(0)) : 0;
   oxb::launch_paged_decode(p, static_cast<int>(batch), D, cur_stream());
   check_launch("paged_decode");
 }
@@ -288,8 +294,8 @@ void paged_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache
   p.Hkv = static_cast<int>(k_cache.size(1));
   p.window = static_cast<int>(window);
   p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
-  p.num_blocks = static_cast<int>(k_cache.size(0));
   p.status = opt_ptr<int>(status);
+  p.num_blocks = p.status != nullptr ? static_cast<int>(k_cache.size(0)) : 0;
   oxb::launch_paged_prefill(p, static_cast<int>(n_tiles), D, cur_stream());
   check_launch("paged_prefill");
 }

@@ -139,7 +139,7 @@ paged_decode_kernel(const DecodeAttnParams p) {
   int blk = page < pg_hi ? checked(bt[page]) : 0;
   for (; page < pg_hi; page += kWarps) {
     const int next_page = page + kWarps;
-    const int next_blk = next_page < pg_hi ? checked(bt[next_page]) : 0;
+    const int next_blk = next_page < pg_hi ? bt[next_page] : 0;  // checked when it is consumed
     const __nv_bfloat16* kp = p.k_cache + static_cast<long long>(blk) * page_stride + head_off;
     const __nv_bfloat16* vp = p.v_cache + static_cast<long long>(blk) * page_stride + head_off;
 
@@ -229,7 +229,7 @@ paged_decode_kernel(const DecodeAttnParams p) {
           mma_bf16_16816(o_acc[nt][4 * c + e], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
       }
     }
-    blk = next_blk;
+    blk = checked(next_blk);
   }
 
   // ---- merge the 4 warps through shared memory ----

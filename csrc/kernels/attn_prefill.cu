@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(kWarps * 32) paged_prefill_kernel(const Prefil
   };
   int blk = first_page < n_pages ? checked(bt[first_page]) : 0;
   for (int page = first_page; page < n_pages; ++page) {
-    const int next_blk = page + 1 < n_pages ? checked(bt[page + 1]) : 0;
+    const int next_blk = page + 1 < n_pages ? bt[page + 1] : 0;  // checked when it is consumed
     const __nv_bfloat16* kp = p.k_cache + static_cast<long long>(blk) * page_stride + head_off;
     const __nv_bfloat16* vp = p.v_cache + static_cast<long long>(blk) * page_stride + head_off;
 
@@ -214,7 +214,7 @@ __global__ void __launch_bounds__(kWarps * 32) paged_prefill_kernel(const Prefil
         mma16816(o_acc[8 * c + e], pa, b0, b1);
       }
     }
-    blk = next_blk;
+    blk = checked(next_blk);
   }
 
   // ---- finalize: divide by the row sums, stage in smem, write coalesced ----

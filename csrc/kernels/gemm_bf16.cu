@@ -293,6 +293,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     // ------------------------------ epilogue ----------------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    if (p.prefetch_bytes > 0 && warp == 5) {
+      // this CTA's slice of the range, in 4 KB requests spread over the lanes
+      constexpr long long kChunk = 4096;
+      const long long n_chunks = (p.prefetch_bytes + kChunk - 1) / kChunk;
+      const char* base = static_cast<const char*>(p.prefetch_ptr);
+      for (long long c = static_cast<long long>(blockIdx.x) * 32 + lane; c < n_chunks;
+           c += static_cast<long long>(gridDim.x) * 32) {
+        const long long off = c * kChunk;
+        const long long left = p.prefetch_bytes - off;
+        const uint32_t sz = static_cast<uint32_t>(left < kChunk ? left : kChunk);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"(sz) : "memory");
+      }
+    }
     uint8_t* stage = sStage + static_cast<size_t>(q) * 32 * kStagePitch;
     uint8_t* my_row = stage + static_cast<size_t>(lane) * kStagePitch;
     const bool vec_ok = (p.N & 7) == 0;

@@ -34,6 +34,10 @@ struct GemmParams {
   int m_tiles;        // 128-row tiles along M (grouped mode: upper bound over all groups)
   int epi;
   int act;            // kEpiSwigluBf16: 0 = SiLU, 1 = tanh-GELU
+  // L2 prefetch of the NEXT kernel's weights, issued by an otherwise idle epilogue warp while this
+  // GEMM streams its own (decode GEMMs are latency bound and leave HBM bandwidth unused).
+  const void* prefetch_ptr;
+  long long prefetch_bytes;  // multiple of 16; 0 = none
   int b_tiled;        // 1: B is stored tile-major [N/128][K/64][128][64]: every TMA box is one contiguous 16 KB
   void* C;            // kEpiStoreBf16 / kEpiStoreF32 / kEpiSwigluBf16
   long long ldc;

@@ -137,6 +137,8 @@ class DeviceModel:
         self.weight_mode = weight_mode
         # dense bf16 projections are kept tile-major in HBM (see ops.tile_weight) unless a library
         # GEMM has to read them
+        self.prefetch_mask = int(os.environ.get("OXB_PREFETCH", "0"))
+        self.prefetch_head = int(os.environ.get("OXB_PREFETCH_HEAD_MB", "48")) << 19  # bf16 elements
         self.tile_weights = (os.environ.get("OXB_TILE_WEIGHTS", "1") != "0") if tile_weights is None else tile_weights
         self.D = cfg.head_dim
         self.hq = cfg.n_heads // tp
@@ -450,6 +452,10 @@ class DeviceModel:
                        first=True)
         g0 = self.ws.local("gather0")[:M]
         g1 = self.ws.local("gather1")[:M]
+        # Decode-sized GEMMs are latency bound and leave HBM bandwidth idle: each one pulls the next
+        # kernel's weights into L2 meanwhile (bit 0: gate/up -> down, 1: down -> next QKV,
+        # 2: QKV -> O, 3: O -> head of gate/up).
+        pf = self.prefetch_mask if M <= 512 and not cfg.is_moe else 0
         for li, L in enumerate(self.layers):
             # ---- attention block ----
             bn = ops.pick_bn(self.wqkv, (M + 127) // 128, can_split=True)
@@ -457,10 +463,10 @@ class DeviceModel:
             ag = self._ag_kwargs(F_AG0, T_AG0, rpr, rpr)
             if splits > 1:
                 ops.gemm(g0, L["w_qkv"], epi=ops.EPI_RED_F32, dst_ptrs=[self.qkv_acc.data_ptr()], bn=bn,
-                         splits=splits, **ag)
+                         splits=splits, prefetch=L["w_o"] if pf & 4 else None, **ag)
                 qkv_kw = dict(acc_f32=self.qkv_acc)
             else:
-                ops.gemm(g0, L["w_qkv"], out=self.qkv_bf16[:M], bn=bn, **ag)
+                ops.gemm(g0, L["w_qkv"], out=self.qkv_bf16[:M], bn=bn, prefetch=L["w_o"] if pf & 4 else None, **ag)
                 qkv_kw = dict(qkv_bf16=self.qkv_bf16)
             ops.qkv_rope_append(bias=L["b_qkv"], q_norm_w=L["q_norm"], k_norm_w=L["k_norm"], norm_eps=1e-6,
                                 norm_w_offset=cfg.norm_weight_offset, positions=s.positions,
@@ -470,7 +476,9 @@ class DeviceModel:
             self._attention(s, li)
             bn = ops.pick_bn(d, (M + 127) // 128, can_split=True)
             sp = ops.pick_splits(M, d, self.hq * self.D, bn)
-            ops.gemm(self.attn_out[:M], L["w_o"], bn=bn, splits=sp, **self._red_kwargs(0, T_DONE_O, rpr, sp))
+            ops.gemm(self.attn_out[:M], L["w_o"], bn=bn, splits=sp,
+                     prefetch=L["w_gu"].view(-1)[:self.prefetch_head] if pf & 8 else None,
+                     **self._red_kwargs(0, T_DONE_O, rpr, sp))
             # ---- feed-forward block ----
             if cfg.is_moe:
                 self._finalize(rpr, L["ffn_norm"], acc=0, gather="", flag_base=F_MOE, r0=r0, layer=L, moe=True)
@@ -479,10 +487,13 @@ class DeviceModel:
                 self._finalize(rpr, L["ffn_norm"], acc=0, gather="gather1", flag_base=F_AG1, r0=r0)
                 n_gu = 2 * self.i_l
                 ops.gemm(g1, L["w_gu"], out=self.act[:M], epi=ops.EPI_SWIGLU_BF16, act=self._act_code,
-                         bn=ops.pick_bn(n_gu, (M + 127) // 128), **self._ag_kwargs(F_AG1, T_AG1, rpr, rpr))
+                         bn=ops.pick_bn(n_gu, (M + 127) // 128), prefetch=L["w_down"] if pf & 1 else None,
+                         **self._ag_kwargs(F_AG1, T_AG1, rpr, rpr))
                 bn = ops.pick_bn(d, (M + 127) // 128, can_split=True)
                 sp = ops.pick_splits(M, d, self.i_l, bn)
-                ops.gemm(self.act[:M], L["w_down"], bn=bn, splits=sp, **self._red_kwargs(1, T_DONE_D, rpr, sp))
+                nxt = self.layers[li + 1]["w_qkv"] if li + 1 < len(self.layers) else None
+                ops.gemm(self.act[:M], L["w_down"], bn=bn, splits=sp, prefetch=nxt if pf & 2 else None,
+                         **self._red_kwargs(1, T_DONE_D, rpr, sp))
             last = li == len(self.layers) - 1
             if not last:
                 self._finalize(rpr, self.layers[li + 1]["attn_norm"], acc=1, gather="gather0", flag_base=F_AG0,

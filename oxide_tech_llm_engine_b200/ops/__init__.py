@@ -28,7 +28,6 @@ STATUS_NAMES = {
     5: "index out of range",
 }
 
-K_STAGGER_DEFAULT = os.environ.get("OXB_K_STAGGER", "0") != "0"
 
 # number of kernel launches issued through this module (bench.py reports it)
 launch_count = 0
@@ -97,8 +96,9 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
          row_meta: Optional[torch.Tensor] = None, ag_flags: Optional[torch.Tensor] = None,
          ag_expected: int = 0, ag_rows_per_src: int = 0, ag_ticket: Optional[torch.Tensor] = None,
          bn: int = 0, splits: int = 1, act: int = 0, m_tiles: int = 0,
-         dst_ld: int = 0, my_rank: int = 0, k_stagger: Optional[bool] = None) -> Optional[torch.Tensor]:  # noqa: E501
-    """tcgen05 GEMM  out = a @ w^T  (bf16 in, fp32 accumulate). See csrc/kernels/gemm_bf16.cu."""
+         dst_ld: int = 0, my_rank: int = 0, prefetch: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """tcgen05 GEMM  out = a @ w^T  (bf16 in, fp32 accumulate). See csrc/kernels/gemm_bf16.cu.
+    `prefetch`: a contiguous tensor (the next kernel's weights) pulled into L2 while this GEMM runs."""
     M = a.shape[-2]
     tiled = w.dim() == 4  # tile-major weight from tile_weight()
     N = w.shape[0] * 128 if tiled else w.shape[-2]
@@ -111,7 +111,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     _ext().gemm_bf16(a, w, epi, out, bias, list(dst_ptrs), list(arrive_ptrs), done_ticket,
                      reset_on_done, rows_per_owner, group_counts, row_meta, ag_flags, ag_expected,
                      ag_rows_per_src, ag_ticket, status_word(a.device), bn, splits, act, m_tiles, dst_ld,
-                     my_rank, 1 if tiled else 0)
+                     my_rank, 1 if tiled else 0, prefetch)
     _bump()
     return out
 
@@ -172,10 +172,13 @@ def untile_weight(w: torch.Tensor) -> torch.Tensor:
 def paged_decode(q, k_cache, v_cache, block_tables, seq_lens, pages_per_split, part_o, part_ml, out,
                  *, batch: int, max_splits: int, window: int = 0, scale: float) -> None:
     _ext().paged_decode(q, k_cache, v_cache, block_tables, seq_lens, pages_per_split, part_o, part_ml,
-                        out, batch, max_splits, window, scale, status_word(q.device))
+                        out, batch, max_splits, window, scale, status_word(q.device) if CHECK_BOUNDS else None)
     _bump(2)
 
 
+# OXB_CHECKS=1: the attention kernels verify every block-table id against the pool size (a bad id is
+# recorded in the status word and page 0 is read instead); costs ~4 % of the decode attention kernel.
+CHECK_BOUNDS = os.environ.get("OXB_CHECKS", "0") != "0"
 PREFILL_IMPL = os.environ.get("OXB_PREFILL", "tc")  # tc = tcgen05 kernel, mma = mma.sync kernel
 
 
@@ -188,7 +191,7 @@ def paged_prefill(q, k_cache, v_cache, block_tables, tile_seq, tile_q0, q_start,
                                 ctx_lens, out, n_tiles, window, scale, status_word(q.device))
     else:
         _ext().paged_prefill(q, k_cache, v_cache, block_tables, tile_seq, tile_q0, q_start, q_lens,
-                             ctx_lens, out, n_tiles, window, scale, status_word(q.device))
+                             ctx_lens, out, n_tiles, window, scale, status_word(q.device) if CHECK_BOUNDS else None)
     _bump()
 
 

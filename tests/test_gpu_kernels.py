@@ -600,7 +600,12 @@ def test_block_table_bounds_are_checked_without_touching_memory(ops):
     part_ml = torch.zeros(B * hq * 4 * 2, device="cuda")
     out = torch.zeros(B, hq * D, device="cuda", dtype=torch.bfloat16)
     ops.check_status(q.device)
-    ops.paged_decode(q, k, v, bt, lens, pps, part_o, part_ml, out, batch=B, max_splits=4, scale=D ** -0.5)
+    old = ops.CHECK_BOUNDS
+    ops.CHECK_BOUNDS = True
+    try:
+        ops.paged_decode(q, k, v, bt, lens, pps, part_o, part_ml, out, batch=B, max_splits=4, scale=D ** -0.5)
+    finally:
+        ops.CHECK_BOUNDS = old
     torch.cuda.synchronize()
     from oxide_tech_llm_engine_b200.errors import EngineError
     with pytest.raises(EngineError):
