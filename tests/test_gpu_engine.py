@@ -161,3 +161,27 @@ def test_sampling_and_cancel_and_speculative():
     eng2.close()
     assert _agreement(spec[0], plain[0]) >= 0.75, (spec, plain)
     assert free0 > 0
+
+
+def test_steady_state_decode_allocates_no_device_memory():
+    """After warm-up, decode steps (CUDA-graph replays, staging upload, device sampler, D2H of the
+    ids) run out of buffers made at construction: the caching allocator hands out nothing."""
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+    from oxide_tech_llm_engine_b200.utils.alloc_guard import AllocGuard
+
+    eng, mc, src = _mk("tiny")
+    rng = np.random.default_rng(11)
+    for n in (5, 19, 40):
+        eng.add_request(rng.integers(3, mc.vocab_size, size=n).tolist(),
+                        SamplingParams(greedy=True, max_tokens=64, ignore_eos=True))
+    for _ in range(8):          # prefill + graph capture + a few replays
+        eng.step()
+    torch.cuda.synchronize()
+    replays0 = eng.stats["graph_replays"]
+    with AllocGuard(device=eng.device) as g:
+        for _ in range(16):
+            eng.step()
+        torch.cuda.synchronize()
+    assert eng.stats["graph_replays"] - replays0 == 16
+    assert g.delta.blocks == 0 and g.delta.segments == 0, g.delta
+    eng.close()

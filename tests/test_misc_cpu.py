@@ -136,3 +136,24 @@ def test_energy_sampler_against_fake_nvml():
         def nvmlInit(self): raise RuntimeError("no driver")
     r3 = EnergySampler(0, nvml=Broken()).start().stop(5)
     assert r3.source == "unavailable" and r3.joules == 0 and r3.tokens_per_joule == 0
+
+
+def test_alloc_guard_with_fake_counters():
+    import pytest as _pt
+
+    from oxide_tech_llm_engine_b200.utils.alloc_guard import AllocGuard
+
+    class Src:
+        def __init__(self): self.s = {"allocation.all.allocated": 10, "segment.all.allocated": 2,
+                                      "allocated_bytes.all.peak": 100}
+        def memory_stats(self): return dict(self.s)
+    src = Src()
+    with AllocGuard(stats_source=src) as g:
+        pass
+    assert g.delta.blocks == 0 and g.delta.segments == 0
+    with _pt.raises(AssertionError):
+        with AllocGuard(stats_source=src):
+            src.s["allocation.all.allocated"] += 3
+    with AllocGuard(stats_source=src, max_blocks=5) as g2:
+        src.s["allocation.all.allocated"] += 3
+    assert g2.delta.blocks == 3
