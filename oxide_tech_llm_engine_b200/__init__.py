@@ -7,3 +7,11 @@ batching scheduler) is C++ (``oxb_host``).
 __version__ = "0.1.0"
 
 from . import _build  # noqa: F401
+
+
+def __getattr__(name):  # lazy: importing the package must not import torch-heavy modules
+    if name in ("Engine", "EngineBuilder"):
+        from . import facade
+
+        return getattr(facade, name)
+    raise AttributeError(name)

@@ -88,6 +88,15 @@ _WS = b" \t\n\r"
 _DIGITS = b"0123456789"
 
 
+def ascii_first_byte_mask(allowed: bytes, vocab_bytes: list) -> np.ndarray:
+    """Allow-mask over the vocabulary by the FIRST byte of each token (the reference's small
+    `GrammarMask`, oxide-core/src/grammar_mask.rs:18-66): token i is allowed iff it is non-empty and its
+    first byte is in `allowed`."""
+    ok = np.zeros(256, dtype=bool)
+    ok[np.frombuffer(bytes(allowed), dtype=np.uint8)] = True
+    return np.fromiter((len(t) > 0 and ok[t[0]] for t in vocab_bytes), dtype=bool, count=len(vocab_bytes))
+
+
 def json_object_dfa() -> Dfa:
     """Flat JSON object: { "key": value, ... } with string / number / true / false / null values."""
     d = Dfa(32)

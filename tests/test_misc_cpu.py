@@ -157,3 +157,45 @@ def test_alloc_guard_with_fake_counters():
     with AllocGuard(stats_source=src, max_blocks=5) as g2:
         src.s["allocation.all.allocated"] += 3
     assert g2.delta.blocks == 3
+
+
+def test_facade_builder_transaction_and_ascii_mask():
+    import numpy as np
+    import pytest as _pt
+
+    import oxide_tech_llm_engine_b200 as oxb
+    from oxide_tech_llm_engine_b200._build import host_ext
+    from oxide_tech_llm_engine_b200.engine.transactional import KvTransaction
+    from oxide_tech_llm_engine_b200.errors import OutOfMemory, TransactionAborted
+    from oxide_tech_llm_engine_b200.grammar import ascii_first_byte_mask
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    eng = (oxb.Engine.builder().model("tiny").backend("cpu").context_size(256).max_slots(2)
+           .option(num_kv_blocks=32).build())
+    out = eng.generate([[5, 6, 7, 8]], SamplingParams(greedy=True, max_tokens=4, ignore_eos=True))
+    assert len(out[0]) == 4
+    eng.close()
+    with _pt.raises(ValueError):
+        oxb.Engine.builder().backend("rocm")
+
+    H = host_ext()
+    pool = H.BlockPool(4)
+    t = H.SequenceBlockTable(pool)
+    with KvTransaction(t, 20) as tx:
+        tx.commit()
+    assert t.num_tokens() == 20 and pool.num_free() == 2
+    with _pt.raises(RuntimeError):
+        with KvTransaction(t, 20):
+            assert pool.num_free() == 1
+            raise RuntimeError("step failed")
+    assert t.num_tokens() == 20 and pool.num_free() == 2      # rolled back
+    with _pt.raises(OutOfMemory):
+        with KvTransaction(t, 200):
+            pass
+    with _pt.raises(TransactionAborted):
+        with KvTransaction(t, 5) as tx:
+            tx.abort("verify rejected")
+    assert t.num_tokens() == 20
+
+    m = ascii_first_byte_mask(b'{["', [b"{a", b"x", b"", b"[1", b'"k'])
+    assert m.tolist() == [True, False, False, True, True]
