@@ -23,7 +23,6 @@ def main() -> None:
     ap.add_argument("--epi", type=int, default=0)
     ap.add_argument("--bn", default="64,128,256")
     ap.add_argument("--splits", default="1")
-    ap.add_argument("--stagger", default="0,1")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--tiled", default="0", help="comma list of 0/1: weights stored tile-major")
