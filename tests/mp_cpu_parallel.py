@@ -59,8 +59,9 @@ def run_ring(rank, world):
 
     torch.manual_seed(0)
     T, H, Hkv, D = 64 * world, 4, 2, 16
-    q, k, v = torch.randn(T, H, D), torch.randn(T, Hkv, D), torch.randn(T, Hkv, D)
-    pos = torch.arange(T)
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if os.environ.get("OXB_RING_GPU") else "cpu"
+    q, k, v = (torch.randn(T, H, D).to(dev), torch.randn(T, Hkv, D).to(dev), torch.randn(T, Hkv, D).to(dev))
+    pos = torch.arange(T, device=dev)
     chunk = T // (2 * world)
     a, b = zigzag_chunks(world, rank)
     idx = torch.cat([pos[a * chunk:(a + 1) * chunk], pos[b * chunk:(b + 1) * chunk]])
@@ -133,6 +134,13 @@ def run_rank_exit(rank, world):
 
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    if os.environ.get("OXB_RING_GPU"):
+        torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+        run_ring(rank, world)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     if sys.argv[1] == "rank_exit":
         dist.init_process_group("gloo")
         run_rank_exit(rank, world)
