@@ -258,6 +258,8 @@ class DeviceModel:
     def _tile_head(self) -> None:
         if self.weight_mode == "bf16" and self.tile_weights and self.lm_head is not None:
             self.lm_head = ops.tile_weight(self.lm_head)
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()  # the row-major originals of the re-laid-out weights
 
     def init_random_quant(self, type_name: str = "Q4_K", seed: int = 0, embed_type: str = "Q8_0") -> None:
         """Random packed GGUF-format weights generated on the device (weight_mode == 'quant')."""
