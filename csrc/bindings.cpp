@@ -173,7 +173,10 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
 
 // a8: [M, K] e4m3 bytes; sa_t: [ceil(K/128), >= M] fp32; w8: [N, K] e4m3 bytes; sw: [ceil(N/128), ceil(K/128)].
 void gemm_fp8_block(const Tensor& a8, const Tensor& sa_t, const Tensor& w8, const Tensor& sw,
-                    const Tensor& out, const c10::optional<Tensor>& bias, const Tensor& status) {
+                    const c10::optional<Tensor>& out_opt, const c10::optional<Tensor>& bias,
+                    const Tensor& status, const std::vector<int64_t>& slab_ptrs,
+                    const std::vector<int64_t>& arrive_ptrs, const c10::optional<Tensor>& done_ticket,
+                    int64_t rows_per_owner, int64_t my_rank, int64_t slab_ld) {
   TORCH_CHECK(a8.is_cuda() && w8.is_cuda() && a8.element_size() == 1 && w8.element_size() == 1,
               "gemm_fp8_block: CUDA fp8 operands required");
   TORCH_CHECK(a8.dim() == 2 && w8.dim() == 2 && a8.stride(1) == 1 && w8.stride(1) == 1,
@@ -187,9 +190,17 @@ void gemm_fp8_block(const Tensor& a8, const Tensor& sa_t, const Tensor& w8, cons
   TORCH_CHECK(sw.scalar_type() == torch::kFloat32 && sw.is_contiguous() &&
                   sw.size(0) == (N + 127) / 128 && sw.size(1) == n_kb,
               "gemm_fp8_block: sw must be [N/128, K/128] fp32");
-  TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && out.size(0) == M && out.size(1) == N &&
-                  out.stride(1) == 1,
-              "gemm_fp8_block: out must be [M, N] bf16");
+  const bool routed = !slab_ptrs.empty();
+  if (!routed) {
+    TORCH_CHECK(out_opt.has_value(), "gemm_fp8_block: out required");
+    const Tensor& out = *out_opt;
+    TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && out.size(0) == M && out.size(1) == N &&
+                    out.stride(1) == 1,
+                "gemm_fp8_block: out must be [M, N] bf16");
+  } else {
+    TORCH_CHECK(slab_ptrs.size() <= 8 && rows_per_owner > 0 && slab_ld >= N,
+                "gemm_fp8_block: 1..8 owners, rows_per_owner > 0, slab_ld >= N");
+  }
   CUtensorMap tmA = oxb::make_tma_map(a8.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, 2, K, M, 1,
                                       static_cast<uint64_t>(a8.stride(0)), 0, 128, 128, 1,
                                       CU_TENSOR_MAP_SWIZZLE_128B);
@@ -203,15 +214,28 @@ void gemm_fp8_block(const Tensor& a8, const Tensor& sa_t, const Tensor& w8, cons
   p.sa_t = sa_t.data_ptr<float>();
   p.sa_ld = static_cast<int>(sa_t.stride(0));
   p.sw = sw.data_ptr<float>();
-  p.C = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
-  p.ldc = out.stride(0);
+  if (!routed) {
+    p.C = reinterpret_cast<__nv_bfloat16*>(out_opt->data_ptr());
+    p.ldc = out_opt->stride(0);
+  } else {
+    for (size_t i = 0; i < slab_ptrs.size(); ++i) p.slab[i] = reinterpret_cast<__nv_bfloat16*>(slab_ptrs[i]);
+    for (size_t i = 0; i < arrive_ptrs.size() && i < 8; ++i)
+      p.arrive[i] = reinterpret_cast<uint32_t*>(arrive_ptrs[i]);
+    p.n_owners = static_cast<int>(slab_ptrs.size());
+    p.rows_per_owner = static_cast<int>(rows_per_owner);
+    p.my_rank = static_cast<int>(my_rank);
+    p.slab_ld = slab_ld;
+    p.done_ticket = opt_ptr<uint32_t>(done_ticket);
+  }
   p.bias = bf16_ptr(bias);
   p.status = reinterpret_cast<int*>(status.data_ptr());
   oxb::launch_gemm_fp8_block(tmA, tmB, p, cur_stream());
   check_launch("gemm_fp8_block");
 }
 
-void quant_act_fp8(const Tensor& x, const Tensor& q, const Tensor& sa_t) {
+void quant_act_fp8(const Tensor& x, const Tensor& q, const Tensor& sa_t,
+                   const c10::optional<Tensor>& ag_flags, int64_t ag_expected, int64_t ag_rows_per_src,
+                   const c10::optional<Tensor>& ag_ticket, const Tensor& status) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.dim() == 2 && x.stride(1) == 1,
               "quant_act_fp8: [M, K] bf16 input required");
   TORCH_CHECK(q.element_size() == 1 && q.size(0) == x.size(0) && q.size(1) == x.size(1) &&
@@ -220,10 +244,20 @@ void quant_act_fp8(const Tensor& x, const Tensor& q, const Tensor& sa_t) {
   TORCH_CHECK(sa_t.scalar_type() == torch::kFloat32 && sa_t.size(0) == (x.size(1) + 127) / 128 &&
                   sa_t.size(1) >= x.size(0) && sa_t.stride(1) == 1,
               "quant_act_fp8: sa_t must be [K/128, >=M] fp32");
+  oxb::QuantActWait wait{};
+  if (ag_flags.has_value() && ag_flags->defined()) {
+    TORCH_CHECK(ag_ticket.has_value(), "quant_act_fp8: ag_ticket required with ag_flags");
+    wait.flags = reinterpret_cast<const uint32_t*>(ag_flags->data_ptr());
+    wait.n_src = static_cast<int>(ag_flags->numel());
+    wait.expected = static_cast<uint32_t>(ag_expected);
+    wait.rows_per_src = static_cast<int>(ag_rows_per_src);
+    wait.ticket = reinterpret_cast<uint32_t*>(ag_ticket->data_ptr());
+    wait.status = reinterpret_cast<int*>(status.data_ptr());
+  }
   oxb::launch_quant_act_fp8(reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), x.stride(0),
                             reinterpret_cast<uint8_t*>(q.data_ptr()), q.stride(0),
                             sa_t.data_ptr<float>(), static_cast<int>(sa_t.stride(0)),
-                            static_cast<int>(x.size(0)), static_cast<int>(x.size(1)), cur_stream());
+                            static_cast<int>(x.size(0)), static_cast<int>(x.size(1)), wait, cur_stream());
   check_launch("quant_act_fp8");
 }
 

@@ -142,7 +142,18 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     }
     if (ok && row_ok) {
       __nv_bfloat16* d = p.C + static_cast<long long>(row) * p.ldc + n0;
-      const bool vec = (p.ldc & 7) == 0 && n0 + BN <= p.N;
+      long long ld = p.ldc;
+      if (p.n_owners > 0) {
+        int owner = row / p.rows_per_owner;
+        if (owner >= p.n_owners) owner = p.n_owners - 1;
+        __nv_bfloat16* base = nullptr;
+#pragma unroll
+        for (int o = 0; o < 8; ++o)
+          if (o == owner) base = p.slab[o];
+        d = base + (static_cast<long long>(p.my_rank) * p.rows_per_owner + (row - owner * p.rows_per_owner)) * p.slab_ld + n0;
+        ld = p.slab_ld;
+      }
+      const bool vec = (ld & 7) == 0 && n0 + BN <= p.N;
 #pragma unroll
       for (int j = 0; j < BN; j += 8) {
         float v[8];
@@ -166,6 +177,24 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       }
     }
     tc_fence_before_sync();
+    if (p.done_ticket != nullptr) {
+      // one system-scope fence per CTA after the barrier, then the grid-wide ticket; the last CTA
+      // signals every owner with relaxed adds (see the bf16 GEMM for the reasoning)
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        __threadfence_system();
+        const uint32_t total = gridDim.x * gridDim.y;
+        const uint32_t old = atomicAdd(p.done_ticket, 1u);
+        if (old == total - 1) {
+          *p.done_ticket = 0;
+          __threadfence_system();
+#pragma unroll
+          for (int o = 0; o < 8; ++o)
+            if (o < p.n_owners && p.arrive[o] != nullptr)
+              asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.arrive[o]), "r"(1u) : "memory");
+        }
+      }
+    }
   }
 
   __syncthreads();
@@ -176,19 +205,69 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 }
 
 // One warp per (row, 128-wide block).
-__global__ void quant_act_fp8_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld,
-                                     uint8_t* __restrict__ q, long long q_ld, float* __restrict__ sa_t,
-                                     int sa_ld, int M, int K) {
+__global__ void quant_act_fp8_kernel(const __nv_bfloat16* x, long long x_ld, uint8_t* __restrict__ q,
+                                     long long q_ld, float* __restrict__ sa_t, int sa_ld, int M, int K,
+                                     const QuantActWait w) {
   const int n_kb = (K + 127) / 128;
   const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
+  if (w.flags != nullptr) {
+    // The input rows are pushed by peers (all-gather): wait, bounded, for the sources of the rows
+    // this CTA touches, then pass the grid-wide gate whose last passer re-arms the flags.
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) {
+      const long long w0 = (static_cast<long long>(blockIdx.x) * blockDim.x) >> 5;
+      long long w1 = w0 + (blockDim.x >> 5) - 1;
+      const long long w_max = static_cast<long long>(M) * n_kb - 1;
+      if (w1 > w_max) w1 = w_max;
+      int s_lo = 0, s_hi = w.n_src - 1;
+      if (w.rows_per_src > 0 && w0 <= w_max) {
+        s_lo = static_cast<int>(w0 / n_kb) / w.rows_per_src;
+        s_hi = static_cast<int>(w1 / n_kb) / w.rows_per_src;
+        if (s_hi >= w.n_src) s_hi = w.n_src - 1;
+        if (s_lo > s_hi) s_lo = s_hi;
+      }
+      int ok = 1;
+      for (int s = s_lo; s <= s_hi && ok; ++s) {
+        uint32_t it = 0, v;
+        do {
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(w.flags + s) : "memory");
+          if (v >= w.expected) break;
+        } while (++it <= OXB_SPIN_LIMIT);
+        if (v < w.expected) {
+          atomicExch(w.status, kStatusPeerFlagTimeout);
+          ok = 0;
+        }
+      }
+      const uint32_t old = atomicAdd(w.ticket, 1u);
+      if (old == gridDim.x - 1) {
+        for (int s = 0; s < w.n_src; ++s) const_cast<uint32_t*>(w.flags)[s] = 0;
+        __threadfence();
+        *w.ticket = 0;
+      }
+      s_ok = ok;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+  }
   if (wid >= static_cast<long long>(M) * n_kb) return;
   const int row = static_cast<int>(wid / n_kb), kb = static_cast<int>(wid % n_kb);
   const int k0 = kb * 128 + lane * 4;
   float v[4];
+  const __nv_bfloat16* xr = x + static_cast<long long>(row) * x_ld + k0;
+  if (k0 + 3 < K && (reinterpret_cast<uintptr_t>(xr) & 7) == 0) {
+    // L2 load: the rows may have been written by a peer GPU moments ago
+    const uint2 raw = __ldcg(reinterpret_cast<const uint2*>(xr));
+    const __nv_bfloat16* e4 = reinterpret_cast<const __nv_bfloat16*>(&raw);
 #pragma unroll
-  for (int e = 0; e < 4; ++e)
-    v[e] = k0 + e < K ? __bfloat162float(x[static_cast<long long>(row) * x_ld + k0 + e]) : 0.f;
+    for (int e = 0; e < 4; ++e) v[e] = __bfloat162float(e4[e]);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      v[e] = k0 + e < K
+                 ? __bfloat162float(__ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(xr + e))))
+                 : 0.f;
+  }
   float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
   amax = warp_max(amax);
   const float scale = fmaxf(amax, 1e-10f) / 448.f;
@@ -215,12 +294,13 @@ void launch_gemm_fp8_block(const CUtensorMap& tmA, const CUtensorMap& tmB, const
 }
 
 void launch_quant_act_fp8(const __nv_bfloat16* x, long long x_ld, uint8_t* q, long long q_ld,
-                          float* sa_t, int sa_ld, int M, int K, cudaStream_t stream) {
+                          float* sa_t, int sa_ld, int M, int K, const QuantActWait& wait,
+                          cudaStream_t stream) {
   const long long warps = static_cast<long long>(M) * ((K + 127) / 128);
   const int threads = 256;
   const long long blocks = (warps * 32 + threads - 1) / threads;
   quant_act_fp8_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(x, x_ld, q, q_ld, sa_t,
-                                                                             sa_ld, M, K);
+                                                                             sa_ld, M, K, wait);
 }
 
 }  // namespace oxb

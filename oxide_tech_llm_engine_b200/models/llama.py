@@ -126,8 +126,8 @@ class DeviceModel:
             raise ConfigError("ffn_dim / tp must be a multiple of 32")
         if weight_mode == "quant" and tp != 1:
             raise ConfigError("packed GGUF weights are served at tp=1; use weight_mode='bf16' for tp>1")
-        if weight_mode == "fp8" and (tp != 1 or cfg.is_moe):
-            raise ConfigError("block-scaled fp8 weights are served at tp=1 on dense models")
+        if weight_mode == "fp8" and cfg.is_moe:
+            raise ConfigError("block-scaled fp8 weights are served on dense models")
         # pipeline stage: this model owns layers [lo, hi); the first stage embeds, the last one
         # runs the final norm and the LM head, the others hand the residual stream on
         self.layer_lo, self.layer_hi = layer_range if layer_range is not None else (0, cfg.n_layers)
@@ -581,50 +581,81 @@ class DeviceModel:
             ops.softcap(self.logits[:n_log], cfg.logit_softcap)
         return self.logits[:n_log]
 
-    def _fp8_linear(self, w, x: torch.Tensor, out: torch.Tensor, bias=None) -> None:
-        """out = x @ W^T with W in block-scaled fp8: quantise the activation rows (1 x 128 scales),
-        then the tcgen05 f8 GEMM with per-block promotion."""
+    def _fp8_linear(self, w, x: torch.Tensor, out: Optional[torch.Tensor], *, ag: Optional[dict] = None,
+                    rs_acc: Optional[int] = None, rs_ticket: int = 0, rpr: int = 0) -> None:
+        """x @ W^T with W in block-scaled fp8: quantise the activation rows (1 x 128 scales; waits on
+        the all-gather flags when the rows come from peers), then the tcgen05 f8 GEMM with per-block
+        promotion. `rs_acc`: row-parallel projection whose epilogue scatters bf16 partial rows into
+        the row owners' receive slabs (GEMM -> reduce-scatter)."""
         m, k = x.shape
         a8 = self.a8_flat[:m * k].view(m, k)
         sa = self.sa_flat[:(k + 127) // 128 * m].view(-1, m)
-        ops.quant_act_fp8(x, a8, sa)
-        ops.gemm_fp8_block(a8, sa, w[0], w[1], out=out, bias=bias)
+        ops.quant_act_fp8(x, a8, sa, **(ag or {}))
+        if rs_acc is None:
+            ops.gemm_fp8_block(a8, sa, w[0], w[1], out=out)
+            return
+        self._rs_slab[rs_acc] = True
+        ops.gemm_fp8_block(a8, sa, w[0], w[1], slab_ptrs=self.ws.ptrs(f"slab{rs_acc}"),
+                           arrive_ptrs=self._flag_ptrs(F_ARRIVE0 + rs_acc),
+                           done_ticket=self.tickets[rs_ticket:rs_ticket + 1], rows_per_owner=rpr,
+                           my_rank=self.rank, slab_ld=self.cfg.d_model)
 
     def _forward_fp8(self, s: StepInputs) -> torch.Tensor:
-        """tp == 1 path over block-scaled fp8 projections (embedding, norms and LM head stay bf16)."""
-        cfg = self.cfg
+        """Block-scaled fp8 projections (embedding, norms and LM head stay bf16). Tensor parallel with
+        the same hand-offs as the bf16 path: the activation quantiser is the consumer of the
+        all-gather buffers, the fp8 GEMM's epilogue is the reduce-scatter of O and down."""
+        cfg, tp, rank = self.cfg, self.tp, self.rank
         M, d = s.m, cfg.d_model
+        rpr = M // tp
+        r0 = rank * rpr
         g0, g1 = self.ws.local("gather0")[:M], self.ws.local("gather1")[:M]
-        ops.embed_gather(s.token_ids[:M], self.embed, self.residual[:M], cfg.emb_scale)
-        self._finalize(M, self.layers[0]["attn_norm"], acc=None, gather="gather0", flag_base=F_AG0, r0=0, first=True)
-        proj = self.proj_bf16[:M]
+        ops.embed_gather(s.token_ids[r0:r0 + rpr], self.embed, self.residual[:rpr], cfg.emb_scale)
+        self._finalize(rpr, self.layers[0]["attn_norm"], acc=None, gather="gather0", flag_base=F_AG0, r0=r0,
+                       first=True)
+        proj = self.proj_bf16[:M] if tp == 1 else None
 
-        def fin(norm_w, gather, flag_base, **kw):
+        def ag(flag_base, ticket):
+            if tp == 1:
+                return None
+            return dict(ag_flags=self.ws.local("flags")[flag_base:flag_base + tp], ag_expected=rpr,
+                        ag_rows_per_src=rpr, ag_ticket=self.tickets[ticket:ticket + 1])
+
+        def fin(norm_w, gather, flag_base, acc, **kw):
+            if tp > 1:
+                self._finalize(rpr, norm_w, acc=acc, gather=gather, flag_base=flag_base, r0=kw.pop("r0", r0), **kw)
+                return
             ops.finalize_norm(rows=M, n=d, rs_slab=proj, n_slabs=1, slab_stride=M * d, residual_in=self.residual,
                               residual_out=self.residual, norm_w=norm_w, eps=cfg.rms_eps,
                               w_offset=cfg.norm_weight_offset, out_ptrs=self.ws.ptrs(gather), out_flag_ptrs=[],
-                              out_row_off=0, device=self.device, **kw)
+                              out_row_off=0, device=self.device, out_row_map=kw.get("row_map"))
 
         for li, L in enumerate(self.layers):
-            self._fp8_linear(L["w_qkv"], g0, self.qkv_bf16[:M])
+            self._fp8_linear(L["w_qkv"], g0, self.qkv_bf16[:M], ag=ag(F_AG0, T_AG0))
             ops.qkv_rope_append(qkv_bf16=self.qkv_bf16, bias=L["b_qkv"], q_norm_w=L["q_norm"], k_norm_w=L["k_norm"],
                                 norm_eps=1e-6, norm_w_offset=cfg.norm_weight_offset, positions=s.positions,
                                 slot_mapping=s.slot_mapping, inv_freq=self.inv_freq, rope_mscale=self.rope_mscale,
                                 q_out=self.q_buf, k_cache=self.k_cache[li], v_cache=self.v_cache[li], m=M,
                                 hq=self.hq, hkv=self.hkv, d=self.D)
             self._attention(s, li)
-            self._fp8_linear(L["w_o"], self.attn_out[:M], proj)
-            fin(L["ffn_norm"], "gather1", F_AG1)
-            self._fp8_linear(L["w_gu"], g1, self.gu_bf16[:M])
+            if tp == 1:
+                self._fp8_linear(L["w_o"], self.attn_out[:M], proj)
+            else:
+                self._fp8_linear(L["w_o"], self.attn_out[:M], None, rs_acc=0, rs_ticket=T_DONE_O, rpr=rpr)
+            fin(L["ffn_norm"], "gather1", F_AG1, 0)
+            self._fp8_linear(L["w_gu"], g1, self.gu_bf16[:M], ag=ag(F_AG1, T_AG1))
             ops.swiglu(gu_bf16=self.gu_bf16, out=self.act, m=M, i=self.i_l, act=self._act_code)
-            self._fp8_linear(L["w_down"], self.act[:M], proj)
+            if tp == 1:
+                self._fp8_linear(L["w_down"], self.act[:M], proj)
+            else:
+                self._fp8_linear(L["w_down"], self.act[:M], None, rs_acc=1, rs_ticket=T_DONE_D, rpr=rpr)
             if li != cfg.n_layers - 1:
-                fin(self.layers[li + 1]["attn_norm"], "gather0", F_AG0)
+                fin(self.layers[li + 1]["attn_norm"], "gather0", F_AG0, 1)
         n_log = max(s.n_logits, 1)
-        fin(self.out_norm, "lmg", F_LMG, out_row_map=s.logit_map[:M])
+        row_map = s.logit_map[r0:r0 + rpr] if s.logit_map is not None else None
+        fin(self.out_norm, "lmg", F_LMG, 1, row_map=row_map, r0=r0 if row_map is None else 0)
         lmg = self.ws.local("lmg")[:n_log]
         ops.gemm(lmg, self.lm_head, out=self.logits[:n_log], epi=ops.EPI_STORE_F32,
-                 bn=ops.pick_bn(self.v_l, (n_log + 127) // 128))
+                 bn=ops.pick_bn(self.v_l, (n_log + 127) // 128), **self._ag_kwargs(F_LMG, T_LMG, 0, rpr))
         if cfg.logit_softcap > 0:
             ops.softcap(self.logits[:n_log], cfg.logit_softcap)
         return self.logits[:n_log]

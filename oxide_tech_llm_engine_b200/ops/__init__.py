@@ -129,25 +129,33 @@ def quant_weight_fp8_block(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]
     return q.to(torch.float8_e4m3fn).contiguous(), scale.contiguous()
 
 
-def quant_act_fp8(x: torch.Tensor, q: Optional[torch.Tensor] = None,
-                  sa_t: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, torch.Tensor]:
-    """bf16 [M, K] -> (e4m3 [M, K], transposed 1 x 128 scales [ceil(K/128), M])."""
+def quant_act_fp8(x: torch.Tensor, q: Optional[torch.Tensor] = None, sa_t: Optional[torch.Tensor] = None, *,
+                  ag_flags: Optional[torch.Tensor] = None, ag_expected: int = 0, ag_rows_per_src: int = 0,
+                  ag_ticket: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16 [M, K] -> (e4m3 [M, K], transposed 1 x 128 scales [ceil(K/128), M]). With `ag_flags` the
+    kernel first waits (bounded) until the peers have pushed the rows it reads (all-gather consumer)."""
     M, K = x.shape
     if q is None:
         q = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=x.device)
     if sa_t is None:
         sa_t = torch.empty((K + 127) // 128, M, dtype=torch.float32, device=x.device)
-    _ext().quant_act_fp8(x, q, sa_t)
+    _ext().quant_act_fp8(x, q, sa_t, ag_flags, ag_expected, ag_rows_per_src, ag_ticket, status_word(x.device))
     _bump()
     return q, sa_t
 
 
 def gemm_fp8_block(a8: torch.Tensor, sa_t: torch.Tensor, w8: torch.Tensor, sw: torch.Tensor, *,
-                   out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Block-scaled fp8 GEMM on the tcgen05 f8 path. See csrc/kernels/gemm_fp8_block.cu."""
-    if out is None:
+                   out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                   slab_ptrs: Sequence[int] = (), arrive_ptrs: Sequence[int] = (),
+                   done_ticket: Optional[torch.Tensor] = None, rows_per_owner: int = 0, my_rank: int = 0,
+                   slab_ld: int = 0) -> Optional[torch.Tensor]:
+    """Block-scaled fp8 GEMM on the tcgen05 f8 path. See csrc/kernels/gemm_fp8_block.cu. With
+    `slab_ptrs` the epilogue is the reduce-scatter of a row-parallel projection (bf16 partial rows go
+    to the row owner's receive slab, the last CTA signals the owners)."""
+    if out is None and not slab_ptrs:
         out = torch.empty(a8.shape[0], w8.shape[0], dtype=torch.bfloat16, device=a8.device)
-    _ext().gemm_fp8_block(a8, sa_t, w8, sw, out, bias, status_word(a8.device))
+    _ext().gemm_fp8_block(a8, sa_t, w8, sw, out, bias, status_word(a8.device), list(slab_ptrs), list(arrive_ptrs),
+                          done_ticket, rows_per_owner, my_rank, slab_ld)
     _bump()
     return out
 

@@ -25,12 +25,19 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     ok = True
-    for name in sys.argv[1:] or ["tiny", "tiny-moe"]:
-        mc = preset(name, n_heads=8, n_kv_heads=8 if world > 2 else 2, d_model=256, ffn_dim=512, head_dim=64) \
-            if world > 2 else preset(name)
+    for name in sys.argv[1:] or ["tiny", "tiny-moe", "tiny-fp8"]:
+        fp8 = name.endswith("-fp8")
+        base = name[:-4] if fp8 else name
+        if world > 2:
+            mc = preset(base, n_heads=8, n_kv_heads=8, d_model=256, ffn_dim=512, head_dim=64)
+        elif fp8:
+            mc = preset(base, d_model=256, ffn_dim=512, head_dim=64)
+        else:
+            mc = preset(base)
         src = SyntheticSource(mc, seed=3, std=0.08)
         cfg = EngineConfig(tp=world, max_num_seqs=8, max_num_batched_tokens=256, num_kv_blocks=256,
-                           ctx_size=1024, graph_buckets=(8,), cuda_graph=True)
+                           ctx_size=1024, graph_buckets=(8,), cuda_graph=True,
+                           weight_mode="fp8" if fp8 else "auto")
         eng = LLMEngine(cfg, mc, weights=src, rank=rank, world=world, device=dev)
         rng = np.random.default_rng(1)
         prompts = [rng.integers(3, mc.vocab_size, size=n).tolist() for n in (4, 33, 100, 17)]
@@ -43,7 +50,7 @@ def main():
             same = all(g == outs for g in gathered)
             try:
                 assert same, "ranks disagree on the generated tokens"
-                assert_consistent(mc, src, prompts, outs)
+                assert_consistent(mc, src, prompts, outs, **(dict(tol=0.6, min_exact=0.5) if fp8 else {}))
                 print(f"TP_CHECK {name} world={world} OK replays={eng.stats['graph_replays']}", flush=True)
             except AssertionError as e:
                 ok = False

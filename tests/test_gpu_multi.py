@@ -20,6 +20,7 @@ def test_tp_and_ep_match_oracle():
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "TP_CHECK tiny world=%d OK" % n in r.stdout
     assert "TP_CHECK tiny-moe world=%d OK" % n in r.stdout
+    assert "TP_CHECK tiny-fp8 world=%d OK" % n in r.stdout
 
 
 def test_pipeline_parallel_stages_match_oracle():
