@@ -50,14 +50,14 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 constexpr int kNormMaxThreads = 1024;
 constexpr int kNormMaxChunks = 4;  // 8-element chunks per thread: N <= 1024 * 8 * 4
 
-// One CTA per row; every thread owns up to kNormMaxChunks 8-element chunks, kept in registers.
+// One CTA per row (looping when there are more rows than resident CTAs); every thread owns up to
+// kNormMaxChunks 8-element chunks, kept in registers.
 // All global loads of a row are issued before the first dependent instruction, so a row costs
 // about one memory round trip however few rows (CTAs) there are.
 __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const FinalizeNormParams p) {
   extern __shared__ float s_h[];  // N floats, used only by the MoE router path
   __shared__ float s_red[32];
   __shared__ int s_ok;
-  const int row = blockIdx.x;
   const int N = p.N;
   const int nthr = blockDim.x;
 
@@ -78,6 +78,10 @@ __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const Fi
     if (!s_ok) return;
   }
 
+  // A CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ...: with many rows (prefill) the wait
+  // above, the system fence and the signals below are paid once per CTA, not once per row.
+  uint32_t rows_done = 0;
+  for (int row = blockIdx.x; row < p.rows; row += gridDim.x, ++rows_done) {
   const long long roff = static_cast<long long>(row) * N;
   float h[kNormMaxChunks][8];
   uint4 res[kNormMaxChunks], bia[kNormMaxChunks];
@@ -279,16 +283,20 @@ __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const Fi
     }
   }
 
+  __syncthreads();  // shared scratch (s_red, router state) is reused by the next row
+  }                 // row loop
+
   const bool signal = p.out_flag[0] != nullptr;
   if (signal || p.arrive != nullptr) {
     __syncthreads();
     if (threadIdx.x == 0) {
       if (signal) {
-        // one system-scope fence per CTA, after the barrier that orders every thread's stores
+        // one system-scope fence per CTA, after the barrier that orders every thread's stores;
+        // the flags count rows, so this CTA adds the number of rows it pushed
         __threadfence_system();
 #pragma unroll
         for (int d = 0; d < kMaxPeers; ++d)
-          if (d < p.n_dst) red_relaxed_sys_add_u32(p.out_flag[d], 1u);
+          if (d < p.n_dst) red_relaxed_sys_add_u32(p.out_flag[d], rows_done);
       }
       if (p.arrive != nullptr) {
         // every CTA has passed its wait once the ticket is full: re-arm the arrival counter
@@ -536,7 +544,15 @@ void launch_finalize_norm(const FinalizeNormParams& p, cudaStream_t stream) {
                          static_cast<int>(smem));
     configured = smem;
   }
-  finalize_norm_kernel<<<p.rows, threads, smem, stream>>>(p);
+  static int max_ctas = 0;
+  if (max_ctas == 0) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    max_ctas = 2 * sms;  // two 1024-thread CTAs are resident per SM
+  }
+  const int grid = p.rows < max_ctas ? p.rows : max_ctas;
+  finalize_norm_kernel<<<grid, threads, smem, stream>>>(p);
 }
 
 void launch_qkv_rope_append(const QkvRopeParams& p, cudaStream_t stream) {
