@@ -45,3 +45,52 @@ class DpRouter:
     def submit(self, prompt_tokens, params, **kw):
         i = self.pick(prompt_tokens)
         return i, self.replicas[i].submit(prompt_tokens, params, **kw)
+
+
+class DpHandle:
+    """Several engine replicas behind the `EngineHandle` interface the HTTP server uses: `submit`
+    routes by prefix affinity and load, `cancel` goes to the replica that owns the request, health and
+    slot counts aggregate. Each replica is a full engine (its own GPU or TP group, its own thread)."""
+
+    def __init__(self, handles: Sequence, **router_kw):
+        if not handles:
+            raise ValueError("DpHandle needs at least one replica")
+        self.handles = list(handles)
+        self.router = DpRouter(self.handles, **router_kw)
+        self._owner: dict = {}
+        self._lock = threading.Lock()
+
+    # the server reads these
+    @property
+    def engine(self):
+        return self.handles[0].engine
+
+    @property
+    def max_slots(self) -> int:
+        return sum(h.max_slots for h in self.handles)
+
+    @property
+    def healthy(self) -> bool:
+        return all(h.healthy for h in self.handles)
+
+    def active_slots(self) -> int:
+        return sum(h.active_slots() for h in self.handles)
+
+    def submit(self, prompt_tokens, params, **kw):
+        i = self.router.pick(prompt_tokens)
+        st = self.handles[i].submit(prompt_tokens, params, **kw)
+        with self._lock:
+            self._owner[(i, st.req_id)] = i
+        st.replica = i
+        return st
+
+    def cancel(self, req_id: int, replica: int = 0) -> None:
+        self.handles[replica].cancel(req_id)
+
+    def generate(self, prompt_tokens, params, timeout: float = 600.0):
+        i = self.router.pick(prompt_tokens)
+        return self.handles[i].generate(prompt_tokens, params, timeout=timeout)
+
+    def shutdown(self, timeout: float = 10.0) -> None:
+        for h in self.handles:
+            h.shutdown(timeout)

@@ -133,3 +133,46 @@ def test_step_worker_runs_commands_in_order_and_idles_in_three_phases():
     assert st["commands"] == 20 and st["spins"] > 0 and st["yields"] > 0 and st["parks"] > 0, st
     assert w.heartbeat() > hb0
     w.stop()
+
+
+def test_dp_handle_serves_over_two_cpu_replicas():
+    """Two complete CPU engines behind one handle: same tokens as a single engine, both replicas used,
+    repeated prompts stick to their replica (prefix affinity)."""
+    from oxide_tech_llm_engine_b200.config import EngineConfig
+    from oxide_tech_llm_engine_b200.engine.engine import LLMEngine
+    from oxide_tech_llm_engine_b200.engine.handle import EngineHandle
+    from oxide_tech_llm_engine_b200.models.config import preset
+    from oxide_tech_llm_engine_b200.models.weights import SyntheticSource
+    from oxide_tech_llm_engine_b200.parallel.dp_router import DpHandle
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    mc = preset("tiny")
+    src = SyntheticSource(mc, seed=2, std=0.08)
+    mk = lambda: EngineHandle(LLMEngine(EngineConfig(model="tiny", backend="cpu", max_num_seqs=4, num_kv_blocks=64,
+                                                     ctx_size=256), mc, weights=src))
+    dp = DpHandle([mk(), mk()], affinity_tokens=8)
+    single = mk()
+    sp = SamplingParams(greedy=True, max_tokens=6, ignore_eos=True)
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(3, 900, size=n).tolist() for n in (12, 20, 33, 15)]
+    try:
+        streams = [dp.submit(p, sp) for p in prompts]
+        outs = []
+        for st in streams:
+            toks = []
+            while True:
+                ev = st.get(timeout=60)
+                if ev.token >= 0:
+                    toks.append(ev.token)
+                if ev.finished:
+                    break
+            outs.append(toks)
+        ref = [single.generate(p, sp)[0] for p in prompts]
+        assert outs == ref
+        assert min(dp.router.routed) >= 1 and sum(dp.router.routed) == 4
+        first = streams[0].replica
+        assert dp.submit(prompts[0], sp).replica == first
+        assert dp.max_slots == 8 and dp.healthy
+    finally:
+        dp.shutdown()
+        single.shutdown()
