@@ -132,12 +132,32 @@ def run_rank_exit(rank, world):
         time.sleep(0.3)
 
 
+def run_ulysses(rank, world):
+    from oxide_tech_llm_engine_b200.parallel.ring_attention import partial_attention
+    from oxide_tech_llm_engine_b200.parallel.ulysses import ulysses_attention
+
+    torch.manual_seed(0)
+    T, H, Hkv, D = 48 * world, 4 * world, 2 * world, 16
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if os.environ.get("OXB_RING_GPU") else "cpu"
+    q, k, v = (torch.randn(T, H, D).to(dev), torch.randn(T, Hkv, D).to(dev), torch.randn(T, Hkv, D).to(dev))
+    tl = T // world
+    sl = slice(rank * tl, (rank + 1) * tl)
+    o = ulysses_attention(q[sl], k[sl], v[sl], rank=rank, cp=world)
+    pos = torch.arange(T, device=dev)
+    full, _ = partial_attention(q, k, v, pos, pos, 1.0 / D ** 0.5)
+    err = (o - full[sl]).abs().max().item()
+    assert o.shape == (tl, H, D) and err < 1e-4, err
+    dist.barrier()
+    if rank == 0:
+        print("ULYSSES_OK", flush=True)
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     if os.environ.get("OXB_RING_GPU"):
         torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
         dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
-        run_ring(rank, world)
+        {"ring": run_ring, "ulysses": run_ulysses}[sys.argv[1]](rank, world)
         dist.barrier()
         dist.destroy_process_group()
         return
@@ -146,7 +166,7 @@ def main():
         run_rank_exit(rank, world)
         os._exit(0)  # survivors do not run a collective teardown with a rank that is gone
     dist.init_process_group("gloo")
-    {"pipeline": run_pipeline, "ring": run_ring}[sys.argv[1]](rank, world)
+    {"pipeline": run_pipeline, "ring": run_ring, "ulysses": run_ulysses}[sys.argv[1]](rank, world)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -34,12 +34,13 @@ def test_pipeline_parallel_stages_match_oracle():
     assert r.returncode == 0 and "PP_CHECK pp=2 tp=1 OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 
-def test_ring_attention_over_nccl_matches_full_attention():
+@pytest.mark.parametrize("what,token", [("ring", "RING_OK"), ("ulysses", "ULYSSES_OK")])
+def test_context_parallel_attention_over_nccl_matches_full_attention(what, token):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs (one context-parallel rank per GPU)")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", OXB_RING_GPU="1")
     here = os.path.dirname(os.path.abspath(__file__))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-           "--master-addr", "127.0.0.1", "--master-port", "29513", os.path.join(here, "mp_cpu_parallel.py"), "ring"]
+           "--master-addr", "127.0.0.1", "--master-port", "29513", os.path.join(here, "mp_cpu_parallel.py"), what]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert r.returncode == 0 and "RING_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0 and token in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

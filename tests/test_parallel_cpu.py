@@ -28,6 +28,11 @@ def test_ring_attention_matches_full_attention():
     assert r.returncode == 0 and "RING_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
+def test_ulysses_attention_matches_full_attention():
+    r = _torchrun(2, "ulysses", 29625)
+    assert r.returncode == 0 and "ULYSSES_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
 def test_stage_plans_and_ngl():
     from oxide_tech_llm_engine_b200.parallel.pipeline import StagePlan, plan_n_gpu_layers
 
