@@ -154,6 +154,8 @@ PYBIND11_MODULE(oxb_host, m) {
              return py::make_tuple(ok, ev);
            })
       .def("set_drafts", &Scheduler::set_drafts)
+      .def("prune_request", &Scheduler::prune_request, py::arg("id"), py::arg("block_scores"),
+           py::arg("sink_blocks") = 1, py::arg("rolling_blocks") = 16, py::arg("budget_blocks") = 128)
       .def("inject_prefill_error", &Scheduler::inject_prefill_error)
       .def("schedule", &Scheduler::schedule)
       .def("update",
@@ -180,6 +182,7 @@ PYBIND11_MODULE(oxb_host, m) {
              if (r == nullptr) return py::none();
              py::dict d;
              d["computed"] = r->computed;
+             d["dropped"] = r->dropped;
              d["prompt_len"] = r->prompt_len;
              d["generated"] = r->generated();
              d["prefix_hit"] = r->prefix_hit;

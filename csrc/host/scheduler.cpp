@@ -63,8 +63,24 @@ bool Scheduler::cancel(int64_t id, std::vector<TokenEvent>* events) {
 }
 
 void Scheduler::set_drafts(int64_t id, const std::vector<int32_t>& drafts) {
+  // a pruned sequence decodes one token at a time (its KV is no longer a contiguous prefix)
   for (auto& r : running_)
-    if (r->id == id && r->phase == Phase::Decode) r->drafts = drafts;
+    if (r->id == id && r->phase == Phase::Decode && r->dropped == 0) r->drafts = drafts;
+}
+
+std::vector<int> Scheduler::prune_request(int64_t id, const std::vector<float>& block_scores,
+                                          int sink_blocks, int rolling_blocks, int budget_blocks) {
+  for (auto& r : running_) {
+    if (r->id != id || r->phase != Phase::Decode) continue;
+    const int before = static_cast<int>(r->table->blocks().size());
+    if (before <= budget_blocks) return {};
+    std::vector<int> keep =
+        r->table->prune_heavy_hitters(block_scores, sink_blocks, rolling_blocks, budget_blocks);
+    r->dropped += (before - static_cast<int>(keep.size())) * kTokensPerBlock;
+    r->drafts.clear();
+    return keep;
+  }
+  return {};
 }
 
 void Scheduler::inject_prefill_error(int64_t id, const std::string& msg) { prefill_faults_[id] = msg; }
@@ -122,6 +138,7 @@ void Scheduler::preempt(Request* r) {
   ++r->preemptions;
   r->table->release_all();
   r->computed = 0;
+  r->dropped = 0;
   r->cached_blocks = 0;
   r->drafts.clear();
   r->phase = Phase::Waiting;
@@ -136,7 +153,7 @@ void Scheduler::preempt(Request* r) {
 }
 
 void Scheduler::offer_to_radix(Request* r) {
-  if (!cfg_.enable_radix) return;
+  if (!cfg_.enable_radix || r->dropped > 0) return;  // pruned KV is not a reusable prefix
   const int n_full = std::min<int>(r->computed, static_cast<int>(r->tokens.size())) / kTokensPerBlock;
   if (n_full <= r->cached_blocks) return;
   radix_.insert(r->tokens.data(), r->table->blocks().data(), n_full);
@@ -261,9 +278,11 @@ StepPlan Scheduler::schedule() {
   plan.n_decode = static_cast<int>(decodes.size());
   plan.n_prefill = static_cast<int>(chunks.size());
 
+  // `pos` is the absolute position; the KV index skips what pruning removed from the middle
   auto slot_of = [](const Request* r, int pos) -> int64_t {
     const auto& b = r->table->blocks();
-    return static_cast<int64_t>(b[pos / kTokensPerBlock]) * kTokensPerBlock + pos % kTokensPerBlock;
+    const int kv = pos - r->dropped;
+    return static_cast<int64_t>(b[kv / kTokensPerBlock]) * kTokensPerBlock + kv % kTokensPerBlock;
   };
   auto push_table = [&](std::vector<int32_t>* dst, const Request* r) {
     const auto& b = r->table->blocks();
@@ -278,7 +297,7 @@ StepPlan Scheduler::schedule() {
     plan.positions.push_back(pos);
     plan.slot_mapping.push_back(slot_of(r, pos));
     plan.decode_ids.push_back(r->id);
-    plan.decode_seq_lens.push_back(pos + 1);
+    plan.decode_seq_lens.push_back(pos + 1 - r->dropped);
     push_table(&plan.decode_block_tables, r);
     plan.logit_rows.push_back(static_cast<int32_t>(plan.token_ids.size()) - 1);
     plan.logit_req.push_back(r->id);
@@ -290,7 +309,7 @@ StepPlan Scheduler::schedule() {
     plan.prefill_ids.push_back(r->id);
     plan.q_start.push_back(start);
     plan.q_lens.push_back(c.len);
-    plan.ctx_lens.push_back(r->computed + c.len);
+    plan.ctx_lens.push_back(r->computed - r->dropped + c.len);
     push_table(&plan.prefill_block_tables, r);
     for (int q0 = 0; q0 < c.len; q0 += kTileQ) {
       plan.tile_seq.push_back(s);
@@ -405,7 +424,7 @@ std::vector<TokenEvent> Scheduler::update(const StepPlan& plan, const std::vecto
       }
       // KV is valid for the input token and for every accepted draft that was emitted
       r->computed += emitted;
-      r->table->rewind_to(r->computed);
+      r->table->rewind_to(r->computed - r->dropped);
       r->table->commit();
       if (done) finish(r);
     }

@@ -54,6 +54,7 @@ struct Request {
   std::vector<int32_t> stop_ids;
   bool ignore_eos = false;
   int computed = 0;             // tokens whose KV is in the cache
+  int dropped = 0;              // of those, tokens removed from the middle by heavy-hitter pruning
   int prefix_hit = 0;           // tokens served by the radix cache at admission
   int cached_blocks = 0;        // full blocks already offered to the radix cache
   Phase phase = Phase::Waiting;
@@ -96,6 +97,11 @@ class Scheduler {
                    const std::vector<int32_t>& stop_ids, bool ignore_eos);
   bool cancel(int64_t id, std::vector<TokenEvent>* events);
   void set_drafts(int64_t id, const std::vector<int32_t>& drafts);
+  // Heavy-hitter (H2O) pruning of a decoding request between steps: keeps the sink blocks, the
+  // rolling window and the best-scored middle blocks within `budget_blocks`; the dropped blocks go
+  // back to the pool, positions stay absolute. Returns the kept block indices (empty: not pruned).
+  std::vector<int> prune_request(int64_t id, const std::vector<float>& block_scores, int sink_blocks,
+                                 int rolling_blocks, int budget_blocks);
   // Fault hook: the next prefill chunk of this request fails (host-side fault injection).
   void inject_prefill_error(int64_t id, const std::string& msg);
 

@@ -45,7 +45,9 @@ class EngineConfig:
     speculative: str = "off"            # off | ngram | auto
     draft_tokens: int = 5
     h2o_pruning: bool = False
-    h2o_budget_blocks: int = 128
+    h2o_budget_blocks: int = 128        # blocks a sequence may keep (sink + rolling window + heavy hitters)
+    h2o_sink_blocks: int = 1
+    h2o_rolling_blocks: int = 16
     seed: int = 42
     backend: str = "cuda"               # cuda | cpu
     step_deadline_s: float = 30.0       # watchdog: a step that takes longer marks the engine degraded

@@ -419,6 +419,45 @@ class LLMEngine:
         dist.broadcast(tok, src=ctx.column_src, group=ctx.column_group)
         return tok[:n_rows].cpu().numpy()
 
+    # ------------------------------------------------------------------ heavy-hitter pruning
+    def _block_scores(self, row: int, blocks: list, kv_tokens: int) -> list:
+        """Attention mass per KV block of one decoding sequence: softmax of the last layer's query of
+        this step against the sequence's keys, summed over heads and the 16 tokens of each block
+        (all-reduced over the tensor-parallel ranks, which hold different heads)."""
+        nb = len(blocks)
+        if self.cpu:
+            return [0.0] * nb
+        m = self.model
+        bt = torch.as_tensor(blocks, dtype=torch.long, device=self.device)
+        k = m.k_cache[-1].index_select(0, bt).float()                      # [nb, hkv, 16, D]
+        q = m.q_buf[row].view(m.hkv, m.hq // m.hkv, m.D).float()
+        s = torch.einsum("hgd,bhtd->hgbt", q, k) * m.scale
+        valid = (torch.arange(nb * 16, device=self.device) < kv_tokens).view(nb, 16)
+        s = s.masked_fill(~valid[None, None], float("-inf"))
+        p = torch.softmax(s.flatten(2), dim=-1).view_as(s)
+        score = p.sum(dim=(0, 1, 3))
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(score, group=self.group)
+        return score.cpu().tolist()
+
+    def _h2o_prune(self, plan) -> None:
+        """Sequences that outgrew `h2o_budget_blocks` give their least attended middle blocks back to
+        the pool (sink and rolling-window blocks always stay). Same decision on every rank: the scores
+        are all-reduced and the scheduler replicas prune identically."""
+        cfg = self.cfg
+        for row, rid in enumerate(plan.decode_ids):
+            info = self.sched.request_info(int(rid))
+            if info is None or info["phase"] != 2 or len(info["blocks"]) <= cfg.h2o_budget_blocks:
+                continue
+            blocks = info["blocks"]
+            scores = self._block_scores(row, blocks, info["computed"] - info["dropped"])
+            keep = self.sched.prune_request(int(rid), scores, cfg.h2o_sink_blocks, cfg.h2o_rolling_blocks,
+                                            cfg.h2o_budget_blocks)
+            if keep:
+                self.stats["h2o_pruned_blocks"] = self.stats.get("h2o_pruned_blocks", 0) + len(blocks) - len(keep)
+
     def attach_monitor(self, monitor) -> None:
         """`monitor.check()` (parallel.watchdog.RankMonitor) runs before every step: a peer that
         stopped answering is found on the host, before any kernel waits on it."""
@@ -466,6 +505,8 @@ class LLMEngine:
         self.stats["prefill_tokens"] += plan.prefill_tokens
         for e in events:
             self._deliver(e)
+        if self.cfg.h2o_pruning and plan.n_decode:
+            self._h2o_prune(plan)
         if self._drafter is not None:
             self._attach_drafts()
         if time.perf_counter() - t0 > self.cfg.step_deadline_s:

@@ -202,3 +202,31 @@ def test_monitor_failure_fails_requests_and_returns_blocks():
     assert eng.sched.num_free_blocks() + cached == free0 and not eng.has_work()
     assert "rank_failure" in eng.degraded
     eng.close()
+
+
+def test_h2o_pruning_bounds_the_kv_of_a_long_sequence_on_cpu():
+    """With heavy-hitter pruning on, a sequence never holds more than the block budget (+1 for the
+    block being filled), the pool gets the rest back and decoding continues to the requested length."""
+    from oxide_tech_llm_engine_b200.config import EngineConfig
+    from oxide_tech_llm_engine_b200.engine.engine import LLMEngine
+    from oxide_tech_llm_engine_b200.models.config import preset
+    from oxide_tech_llm_engine_b200.models.weights import SyntheticSource
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    mc = preset("tiny")
+    eng = LLMEngine(EngineConfig(model="tiny", backend="cpu", max_num_seqs=2, num_kv_blocks=64, ctx_size=512,
+                                 enable_radix=False, h2o_pruning=True, h2o_budget_blocks=6, h2o_sink_blocks=1,
+                                 h2o_rolling_blocks=2), mc, weights=SyntheticSource(mc, seed=4, std=0.08))
+    rid = eng.add_request(list(range(3, 3 + 150)), SamplingParams(greedy=True, max_tokens=40, ignore_eos=True))
+    most = 0
+    while eng.has_work():
+        eng.step()
+        info = eng.sched.request_info(rid)
+        if info is not None:
+            most = max(most, len(info["blocks"])) if info["dropped"] else most
+            if info["dropped"]:
+                assert len(info["blocks"]) <= 7
+    assert eng.stats.get("h2o_pruned_blocks", 0) >= 4 and 0 < most <= 7
+    assert len(eng.requests[rid].output) == 40
+    assert eng.sched.num_free_blocks() == 64
+    eng.close()

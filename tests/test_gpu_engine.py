@@ -185,3 +185,34 @@ def test_steady_state_decode_allocates_no_device_memory():
     assert eng.stats["graph_replays"] - replays0 == 16
     assert g.delta.blocks == 0 and g.delta.segments == 0, g.delta
     eng.close()
+
+
+def test_h2o_pruning_on_device_scores():
+    """Heavy-hitter pruning with block scores from the device (last layer's query against the
+    sequence's keys): the KV of a long sequence stays within the budget, the tokens before the
+    first pruning equal the unpruned run, decoding reaches the requested length, all blocks return."""
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    sp = SamplingParams(greedy=True, max_tokens=48, ignore_eos=True)
+    prompt = np.random.default_rng(12).integers(3, 1000, size=90).tolist()
+    base, mc, src = _mk("tiny", enable_radix=False)
+    ref = base.generate([prompt], sp)[0]
+    base.close()
+    eng, _, _ = _mk("tiny", enable_radix=False, h2o_pruning=True, h2o_budget_blocks=6, h2o_sink_blocks=1,
+                    h2o_rolling_blocks=2)
+    free0 = eng.sched.num_free_blocks()
+    rid = eng.add_request(prompt, sp)
+    first_pruned_at = None
+    while eng.has_work():
+        eng.step()
+        info = eng.sched.request_info(rid)
+        if info is not None and info["dropped"]:
+            assert len(info["blocks"]) <= 7
+            if first_pruned_at is None:
+                first_pruned_at = len(eng.requests[rid].output)
+    eng.check_device_status()
+    out = eng.requests[rid].output
+    assert first_pruned_at is not None and eng.stats["h2o_pruned_blocks"] >= 1
+    assert len(out) == 48 and out[:first_pruned_at] == ref[:first_pruned_at]
+    assert eng.sched.num_free_blocks() == free0
+    eng.close()

@@ -208,3 +208,44 @@ def test_scheduler_fault_injection_isolated(H):
     assert len(r1) == 1 and r1[0].finished and r1[0].reason == "prefill_error: injected"
     assert len(r2) == 4 and r2[-1].reason == "length"
     assert s.num_free_blocks() + s.radix_stats()["cached_blocks"] == 32
+
+
+def test_scheduler_heavy_hitter_pruning_keeps_positions_absolute():
+    """Pruning a decoding request returns its low-score middle blocks, later tokens keep their
+    absolute positions while the KV index and the context length shrink by what was dropped."""
+    import numpy as np
+
+    from oxide_tech_llm_engine_b200._build import host_ext
+
+    H = host_ext()
+    sc = H.SchedulerConfig()
+    sc.num_blocks, sc.max_num_seqs, sc.enable_radix, sc.max_num_batched_tokens = 64, 2, True, 512
+    sc.sla_budget = False
+    sc.chunk_max = 512
+    s = H.Scheduler(sc)
+    free0 = s.num_free_blocks()
+    s.add_request(7, np.arange(3, 3 + 200, dtype=np.int32), 40, [], True)   # 200 tokens -> 13 blocks
+    plan = s.schedule()
+    s.update(plan, np.asarray([5], dtype=np.int32))
+    info = s.request_info(7)
+    assert info["phase"] == 2 and len(info["blocks"]) == 13 and info["dropped"] == 0
+    before = list(info["blocks"])
+    scores = [0.0] * 13
+    scores[5], scores[8] = 9.0, 7.0                                         # the heavy hitters
+    keep = s.prune_request(7, scores, 1, 2, 6)                              # sink 1 + rolling 2 + 3 best
+    assert keep == [0, 1, 5, 8, 11, 12]                                      # stable: the tie goes to the earliest block
+    info = s.request_info(7)
+    assert info["blocks"] == [before[i] for i in keep] and info["dropped"] == 7 * 16
+    assert s.num_free_blocks() >= free0 - 6 - 13      # 7 blocks went back (the radix cache may still pin shared ones)
+    plan = s.schedule()
+    assert plan.n_decode == 1
+    assert plan.positions[0] == 200                                          # absolute position
+    assert plan.decode_seq_lens[0] == 201 - 112                              # keys that are left
+    kv = 200 - 112
+    assert plan.slot_mapping[0] == info["blocks"][kv // 16] * 16 + kv % 16
+    s.update(plan, np.asarray([6], dtype=np.int32))
+    s.set_drafts(7, [1, 2, 3])                                               # ignored for a pruned request
+    assert s.schedule().n_prefill == 0
+    ok, ev = s.cancel(7)
+    assert ok
+    assert s.prune_request(7, scores, 1, 2, 6) == []
