@@ -25,9 +25,10 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     ok = True
-    for name in sys.argv[1:] or ["tiny", "tiny-moe", "tiny-fp8"]:
+    for name in sys.argv[1:] or ["tiny", "tiny-moe", "tiny-fp8", "tiny-h2o"]:
         fp8 = name.endswith("-fp8")
-        base = name[:-4] if fp8 else name
+        h2o = name.endswith("-h2o")
+        base = name[:-4] if (fp8 or h2o) else name
         if world > 2:
             mc = preset(base, n_heads=8, n_kv_heads=8, d_model=256, ffn_dim=512, head_dim=64)
         elif fp8:
@@ -37,7 +38,9 @@ def main():
         src = SyntheticSource(mc, seed=3, std=0.08)
         cfg = EngineConfig(tp=world, max_num_seqs=8, max_num_batched_tokens=256, num_kv_blocks=256,
                            ctx_size=1024, graph_buckets=(8,), cuda_graph=True,
-                           weight_mode="fp8" if fp8 else "auto")
+                           weight_mode="fp8" if fp8 else "auto",
+                           **(dict(h2o_pruning=True, h2o_budget_blocks=5, h2o_sink_blocks=1, h2o_rolling_blocks=2,
+                                   enable_radix=False) if h2o else {}))
         eng = LLMEngine(cfg, mc, weights=src, rank=rank, world=world, device=dev)
         rng = np.random.default_rng(1)
         prompts = [rng.integers(3, mc.vocab_size, size=n).tolist() for n in (4, 33, 100, 17)]
@@ -50,7 +53,10 @@ def main():
             same = all(g == outs for g in gathered)
             try:
                 assert same, "ranks disagree on the generated tokens"
-                assert_consistent(mc, src, prompts, outs, **(dict(tol=0.6, min_exact=0.5) if fp8 else {}))
+                if h2o:   # pruned KV: only agreement between ranks, completion and the pruning itself are checked
+                    assert all(len(o) == 12 for o in outs) and eng.stats.get("h2o_pruned_blocks", 0) > 0
+                else:
+                    assert_consistent(mc, src, prompts, outs, **(dict(tol=0.6, min_exact=0.5) if fp8 else {}))
                 print(f"TP_CHECK {name} world={world} OK replays={eng.stats['graph_replays']}", flush=True)
             except AssertionError as e:
                 ok = False
