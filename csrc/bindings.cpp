@@ -546,7 +546,8 @@ void softcap(const Tensor& logits, double cap) {
 // quantized weights
 // ---------------------------------------------------------------------------------------------
 void mmvq(int64_t qtype, const Tensor& w, const Tensor& x, const c10::optional<Tensor>& bias,
-          const Tensor& out, int64_t N, int64_t K, bool add) {
+          const Tensor& out, int64_t N, int64_t K, bool add, const c10::optional<Tensor>& xq,
+          const c10::optional<Tensor>& xd, const c10::optional<Tensor>& xs) {
   TORCH_CHECK(w.scalar_type() == torch::kUInt8 && w.is_cuda(), "mmvq: packed uint8 weights");
   TORCH_CHECK(K % 32 == 0, "mmvq: K must be a multiple of 32");
   oxb::MmvqParams p{};
@@ -565,9 +566,34 @@ void mmvq(int64_t qtype, const Tensor& w, const Tensor& x, const c10::optional<T
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(K);
   p.add = add ? 1 : 0;
+  if (xq.has_value() && xq->defined()) {
+    TORCH_CHECK(xd.has_value() && xs.has_value() && xq->element_size() == 1 && xq->is_contiguous() &&
+                    xq->size(0) >= x.size(0) && xq->size(1) == K && xd->is_contiguous() &&
+                    xs->is_contiguous() && xd->size(1) == K / 32 && xs->size(1) == K / 32,
+                "mmvq: xq [M, K] int8 with xd / xs [M, K/32] fp32 expected");
+    p.xq = reinterpret_cast<const int8_t*>(xq->data_ptr());
+    p.xd = xd->data_ptr<float>();
+    p.xs = xs->data_ptr<float>();
+  }
   TORCH_CHECK(oxb::launch_mmvq(static_cast<int>(qtype), p, cur_stream()),
               "mmvq: no device decoder for GGUF type ", qtype);
   check_launch("mmvq");
+}
+
+void quant_q8_1(const Tensor& x, const Tensor& xq, const Tensor& xd, const Tensor& xs) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 &&
+                  x.size(1) % 32 == 0,
+              "quant_q8_1: [M, K] bf16 input with K % 32 == 0");
+  const int64_t M = x.size(0), K = x.size(1);
+  TORCH_CHECK(xq.element_size() == 1 && xq.is_contiguous() && xq.size(0) >= M && xq.size(1) == K &&
+                  xd.scalar_type() == torch::kFloat32 && xd.is_contiguous() && xd.size(0) >= M &&
+                  xd.size(1) == K / 32 && xs.scalar_type() == torch::kFloat32 && xs.is_contiguous() &&
+                  xs.size(0) >= M && xs.size(1) == K / 32,
+              "quant_q8_1: xq [M, K] int8, xd / xs [M, K/32] fp32");
+  oxb::launch_quant_q8_1(reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), x.stride(0),
+                         reinterpret_cast<int8_t*>(xq.data_ptr()), xd.data_ptr<float>(),
+                         xs.data_ptr<float>(), static_cast<int>(M), static_cast<int>(K), cur_stream());
+  check_launch("quant_q8_1");
 }
 
 void dequant_rows(int64_t qtype, const Tensor& w, const c10::optional<Tensor>& row_ids,
@@ -694,6 +720,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("kv_block_copy", &kv_block_copy);
   m.def("softcap", &softcap);
   m.def("mmvq", &mmvq);
+  m.def("quant_q8_1", &quant_q8_1);
   m.def("dequant_rows", &dequant_rows);
   m.def("quant_row_bytes", &quant_row_bytes);
   m.def("sample", &sample);

@@ -98,8 +98,328 @@ __global__ void __launch_bounds__(256) dequant_rows_kernel(const uint8_t* w, lon
   }
 }
 
+// ---- vectorised fast paths for the two block types of a usual Q4_K checkpoint -------------------
+// The generic kernel above expands a block byte by byte (it exists for every GGUF type); these two
+// read a block with 16-byte / 2-byte vector loads and never materialise the weights: a block's
+// contribution is  d * sc * sum(q * x) - dmin * mn * sum(x).
+
+__device__ __forceinline__ void mmvq_store(const MmvqParams& p, int n, int m, float v) {
+  float r = v;
+  if (p.bias != nullptr) r += __bfloat162float(p.bias[n]);
+  const long long o = static_cast<long long>(m) * p.ldo + n;
+  if (p.out_f32 != nullptr) {
+    p.out_f32[o] = p.add ? p.out_f32[o] + r : r;
+  } else {
+    if (p.add) r += __bfloat162float(p.out_bf16[o]);
+    p.out_bf16[o] = __float2bfloat16(r);
+  }
+}
+
+__device__ __forceinline__ uint32_t byte_of3(uint32_t s0, uint32_t s1, uint32_t s2, int k) {
+  const uint32_t w = k < 4 ? s0 : (k < 8 ? s1 : s2);
+  return (w >> (8 * (k & 3))) & 0xFFu;
+}
+
+__device__ __forceinline__ float nib_to_float(uint32_t bytes, uint32_t sel) {
+  // byte `sel & 3` of `bytes` (a value 0..15) placed in the mantissa of 2^23, minus 2^23: exact, and
+  // two full-rate instructions instead of a quarter-rate integer-to-float conversion
+  return __uint_as_float(__byte_perm(bytes, 0x4B000000u, sel)) - 8388608.f;
+}
+
+// One warp per weight row, one Q4_K super-block (256 weights, 128 bytes of nibbles) per iteration.
+// Lane l owns 32-bit word l of those bytes: 4 low-nibble weights of sub-block 2j and 4 high-nibble
+// weights of sub-block 2j+1 (j = l / 8). The weight load is one coalesced 128-byte access per warp
+// and the activation loads are 8-byte accesses that are contiguous across lanes (a lane-strided
+// mapping costs one L1 wavefront per lane and made this kernel L1-bound at 1.5 T weights/s).
+template <int MB>
+__global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q4k_kernel(const MmvqParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * kRowsPerCta + warp;
+  if (n >= p.N) return;
+  const int m0 = blockIdx.y * MB;
+  const uint8_t* wrow = p.w + static_cast<long long>(n) * p.row_bytes;
+  const int n_sb = p.K >> 8;
+  const int j = lane >> 3, cw = lane & 7;
+  float acc[MB];
+#pragma unroll
+  for (int m = 0; m < MB; ++m) acc[m] = 0.f;
+
+#pragma unroll 4
+  for (int sb = 0; sb < n_sb; ++sb) {
+    const uint8_t* b = wrow + static_cast<long long>(sb) * 144;
+    const uint32_t qw = __ldg(reinterpret_cast<const uint32_t*>(b + 16) + lane);
+    const uint32_t dm = __ldg(reinterpret_cast<const uint32_t*>(b));
+    const uint32_t s0 = __ldg(reinterpret_cast<const uint32_t*>(b + 4));
+    const uint32_t s1 = __ldg(reinterpret_cast<const uint32_t*>(b + 8));
+    const uint32_t s2 = __ldg(reinterpret_cast<const uint32_t*>(b + 12));
+    const float d = __half2float(__ushort_as_half(static_cast<uint16_t>(dm & 0xFFFFu)));
+    const float dmin = __half2float(__ushort_as_half(static_cast<uint16_t>(dm >> 16)));
+    int sc[2], mn[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int sub = 2 * j + h;
+      if (sub < 4) {
+        sc[h] = byte_of3(s0, s1, s2, sub) & 63;
+        mn[h] = byte_of3(s0, s1, s2, sub + 4) & 63;
+      } else {
+        sc[h] = (byte_of3(s0, s1, s2, sub + 4) & 0xF) | ((byte_of3(s0, s1, s2, sub - 4) >> 6) << 4);
+        mn[h] = (byte_of3(s0, s1, s2, sub + 4) >> 4) | ((byte_of3(s0, s1, s2, sub) >> 6) << 4);
+      }
+    }
+    const uint32_t lo = qw & 0x0F0F0F0Fu, hi = (qw >> 4) & 0x0F0F0F0Fu;
+    const float l0 = nib_to_float(lo, 0x7650), l1 = nib_to_float(lo, 0x7651), l2 = nib_to_float(lo, 0x7652),
+                l3 = nib_to_float(lo, 0x7653);
+    const float h0 = nib_to_float(hi, 0x7650), h1 = nib_to_float(hi, 0x7651), h2 = nib_to_float(hi, 0x7652),
+                h3 = nib_to_float(hi, 0x7653);
+    const float dl0 = d * sc[0], dl1 = d * sc[1], ml0 = dmin * mn[0], ml1 = dmin * mn[1];
+    const int e0 = sb * 256 + j * 64 + cw * 4;
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+      if (m0 + m >= p.M) continue;
+      const __nv_bfloat16* xr = p.x + static_cast<long long>(m0 + m) * p.ldx + e0;
+      const uint2 xl = __ldg(reinterpret_cast<const uint2*>(xr));
+      const uint2 xh = __ldg(reinterpret_cast<const uint2*>(xr + 32));
+      const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xl.x));
+      const float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xl.y));
+      const float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xh.x));
+      const float2 b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xh.y));
+      const float ql = l0 * a0.x + l1 * a0.y + l2 * a1.x + l3 * a1.y;
+      const float qh = h0 * b0.x + h1 * b0.y + h2 * b1.x + h3 * b1.y;
+      const float sl = (a0.x + a0.y) + (a1.x + a1.y), sh = (b0.x + b0.y) + (b1.x + b1.y);
+      acc[m] += dl0 * ql - ml0 * sl + dl1 * qh - ml1 * sh;
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MB; ++m) {
+    const float v = warp_sum(acc[m]);
+    if (lane == 0 && m0 + m < p.M) mmvq_store(p, n, m0 + m, v);
+  }
+}
+
+// ---- integer dot-product path (activations pre-quantised to int8 blocks of 32) -------------------
+// The fp32 kernels above spend 6-9 instructions per weight and top out near 0.8 TB/s; the HBM
+// roofline leaves about 3. With int8 activations a lane multiplies 4 weights per `dp4a`.
+__device__ __forceinline__ float int_to_float(int v) {  // |v| < 2^22, two full-rate instructions
+  return __int_as_float(0x4B400000 + v) - 12582912.f;
+}
+
+__global__ void quant_q8_1_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int8_t* __restrict__ xq,
+                                  float* __restrict__ xd, float* __restrict__ xs, int M, int K) {
+  const int n_blk = K >> 5;
+  const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= static_cast<long long>(M) * n_blk) return;
+  const int row = static_cast<int>(wid / n_blk), blk = static_cast<int>(wid % n_blk);
+  const float v = __bfloat162float(x[static_cast<long long>(row) * ldx + blk * 32 + lane]);
+  const float amax = warp_max(fabsf(v));
+  const float d = amax / 127.f;
+  const int q = amax > 0.f ? __float2int_rn(v / d) : 0;
+  xq[static_cast<long long>(row) * K + blk * 32 + lane] = static_cast<int8_t>(q);
+  const float sum = warp_sum(static_cast<float>(q));
+  if (lane == 0) {
+    xd[static_cast<long long>(row) * n_blk + blk] = d;
+    xs[static_cast<long long>(row) * n_blk + blk] = d * sum;
+  }
+}
+
+// Q4_K x int8: one warp per weight row, four super-blocks per iteration. Lane l: super-block l / 8
+// of the four, 16-byte chunk r = l % 8 of its 128 nibble bytes = 16 low-nibble weights of sub-block
+// 2j and 16 high-nibble weights of sub-block 2j+1 (j = r / 2). The loop is unrolled so that a warp
+// keeps 2 KB of weights in flight; all loads are contiguous across lanes.
+template <int MB>
+__global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q4k_dp4a_kernel(const MmvqParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * kRowsPerCta + warp;
+  if (n >= p.N) return;
+  const int m0 = blockIdx.y * MB;
+  const uint8_t* wrow = p.w + static_cast<long long>(n) * p.row_bytes;
+  const int n_sb = p.K >> 8, n_blk = p.K >> 5;
+  const int r = lane & 7, j = r >> 1, c2 = r & 1;
+  float acc[MB];
+#pragma unroll
+  for (int m = 0; m < MB; ++m) acc[m] = 0.f;
+
+#pragma unroll 4
+  for (int sb = lane >> 3; sb < n_sb; sb += 4) {
+    const uint8_t* b = wrow + static_cast<long long>(sb) * 144;
+    const uint4 q = __ldg(reinterpret_cast<const uint4*>(b + 16) + r);
+    const uint32_t dm = __ldg(reinterpret_cast<const uint32_t*>(b));
+    const uint32_t s0 = __ldg(reinterpret_cast<const uint32_t*>(b + 4));
+    const uint32_t s1 = __ldg(reinterpret_cast<const uint32_t*>(b + 8));
+    const uint32_t s2 = __ldg(reinterpret_cast<const uint32_t*>(b + 12));
+    const float d = __half2float(__ushort_as_half(static_cast<uint16_t>(dm & 0xFFFFu)));
+    const float dmin = __half2float(__ushort_as_half(static_cast<uint16_t>(dm >> 16)));
+    int sc[2], mn[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int sub = 2 * j + h;
+      if (sub < 4) {
+        sc[h] = byte_of3(s0, s1, s2, sub) & 63;
+        mn[h] = byte_of3(s0, s1, s2, sub + 4) & 63;
+      } else {
+        sc[h] = (byte_of3(s0, s1, s2, sub + 4) & 0xF) | ((byte_of3(s0, s1, s2, sub - 4) >> 6) << 4);
+        mn[h] = (byte_of3(s0, s1, s2, sub + 4) >> 4) | ((byte_of3(s0, s1, s2, sub) >> 6) << 4);
+      }
+    }
+    const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+    const float dl0 = d * sc[0], dl1 = d * sc[1];
+    // the `- dmin * mn * sum(x)` term of a sub-block is added once, by the lane that owns its first half
+    const float ml0 = c2 == 0 ? dmin * mn[0] : 0.f, ml1 = c2 == 0 ? dmin * mn[1] : 0.f;
+    const int e0 = sb * 256 + j * 64 + c2 * 16;
+    const int blk = sb * 8 + 2 * j;
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+      if (m0 + m >= p.M) continue;
+      const int8_t* xr = p.xq + static_cast<long long>(m0 + m) * p.K + e0;
+      const int4 xl = __ldg(reinterpret_cast<const int4*>(xr));
+      const int4 xh = __ldg(reinterpret_cast<const int4*>(xr + 32));
+      const float2 dd = __ldg(reinterpret_cast<const float2*>(p.xd + static_cast<long long>(m0 + m) * n_blk + blk));
+      const float2 ss = __ldg(reinterpret_cast<const float2*>(p.xs + static_cast<long long>(m0 + m) * n_blk + blk));
+      const int xlw[4] = {xl.x, xl.y, xl.z, xl.w}, xhw[4] = {xh.x, xh.y, xh.z, xh.w};
+      int il = 0, ih = 0;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        il = __dp4a(static_cast<int>(qw[t] & 0x0F0F0F0Fu), xlw[t], il);
+        ih = __dp4a(static_cast<int>((qw[t] >> 4) & 0x0F0F0F0Fu), xhw[t], ih);
+      }
+      acc[m] += dl0 * dd.x * int_to_float(il) + dl1 * dd.y * int_to_float(ih) - ml0 * ss.x - ml1 * ss.y;
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MB; ++m) {
+    const float v = warp_sum(acc[m]);
+    if (lane == 0 && m0 + m < p.M) mmvq_store(p, n, m0 + m, v);
+  }
+}
+
+// Q8_0 x int8: a lane takes one 34-byte block (2-byte aligned: 16-bit loads, repacked into words).
+template <int MB>
+__global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q8_0_dp4a_kernel(const MmvqParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * kRowsPerCta + warp;
+  if (n >= p.N) return;
+  const int m0 = blockIdx.y * MB;
+  const uint8_t* wrow = p.w + static_cast<long long>(n) * p.row_bytes;
+  const int groups = p.K >> 5;
+  float acc[MB];
+#pragma unroll
+  for (int m = 0; m < MB; ++m) acc[m] = 0.f;
+#pragma unroll 2
+  for (int grp = lane; grp < groups; grp += 32) {
+    const uint16_t* b = reinterpret_cast<const uint16_t*>(wrow + static_cast<long long>(grp) * 34);
+    const float d = __half2float(__ushort_as_half(__ldg(b)));
+    int w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      w[i] = static_cast<int>(static_cast<uint32_t>(__ldg(b + 1 + 2 * i)) |
+                              (static_cast<uint32_t>(__ldg(b + 2 + 2 * i)) << 16));
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+      if (m0 + m >= p.M) continue;
+      const int4* xr = reinterpret_cast<const int4*>(p.xq + static_cast<long long>(m0 + m) * p.K + grp * 32);
+      const int4 a = __ldg(xr), c = __ldg(xr + 1);
+      int s = __dp4a(w[0], a.x, 0);
+      s = __dp4a(w[1], a.y, s);
+      s = __dp4a(w[2], a.z, s);
+      s = __dp4a(w[3], a.w, s);
+      s = __dp4a(w[4], c.x, s);
+      s = __dp4a(w[5], c.y, s);
+      s = __dp4a(w[6], c.z, s);
+      s = __dp4a(w[7], c.w, s);
+      acc[m] += d * __ldg(p.xd + static_cast<long long>(m0 + m) * groups + grp) * int_to_float(s);
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MB; ++m) {
+    const float v = warp_sum(acc[m]);
+    if (lane == 0 && m0 + m < p.M) mmvq_store(p, n, m0 + m, v);
+  }
+}
+
+// Q8_0: 34-byte blocks (fp16 scale + 32 int8) are only 2-byte aligned: seventeen 16-bit loads.
+template <int MB>
+__global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q8_0_kernel(const MmvqParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * kRowsPerCta + warp;
+  if (n >= p.N) return;
+  const int m0 = blockIdx.y * MB;
+  const uint8_t* wrow = p.w + static_cast<long long>(n) * p.row_bytes;
+  const int groups = p.K >> 5;
+  float acc[MB];
+#pragma unroll
+  for (int m = 0; m < MB; ++m) acc[m] = 0.f;
+
+#pragma unroll 2
+  for (int grp = lane; grp < groups; grp += 32) {
+    const uint16_t* b = reinterpret_cast<const uint16_t*>(wrow + static_cast<long long>(grp) * 34);
+    uint16_t q[17];
+#pragma unroll
+    for (int i = 0; i < 17; ++i) q[i] = __ldg(b + i);
+    const float d = __half2float(__ushort_as_half(q[0]));
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+      if (m0 + m >= p.M) continue;
+      const uint4* xp =
+          reinterpret_cast<const uint4*>(p.x + static_cast<long long>(m0 + m) * p.ldx + grp * 32);
+      float s = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint4 v = __ldg(xp + c);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint16_t w = q[1 + 4 * c + e];
+          const float2 f = __bfloat1622float2(h[e]);
+          s += static_cast<float>(static_cast<int8_t>(w & 0xFF)) * f.x +
+               static_cast<float>(static_cast<int8_t>(w >> 8)) * f.y;
+        }
+      }
+      acc[m] += d * s;
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MB; ++m) {
+    const float v = warp_sum(acc[m]);
+    if (lane == 0 && m0 + m < p.M) mmvq_store(p, n, m0 + m, v);
+  }
+}
+
+#define OXB_MMVQ_FAST(KERNEL)                                                                  \
+  do {                                                                                         \
+    const int gx = (p.N + kRowsPerCta - 1) / kRowsPerCta;                                      \
+    if (p.M == 1) KERNEL<1><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);                       \
+    else if (p.M == 2) KERNEL<2><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);                  \
+    else if (p.M <= 4) KERNEL<4><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);                  \
+    else KERNEL<8><<<dim3(gx, (p.M + 7) / 8), kRowsPerCta * 32, 0, s>>>(p);                    \
+  } while (0)
+
 template <int T>
 void mmvq_dispatch(const MmvqParams& p, cudaStream_t s) {
+  // vector-load fast paths need 16-byte aligned rows (weights and activations)
+  const bool aligned = (reinterpret_cast<uintptr_t>(p.w) & 15) == 0 && (p.row_bytes & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(p.x) & 15) == 0 && (p.ldx & 7) == 0;
+  if constexpr (T == kQ_Q4_K) {
+    if (p.xq != nullptr && aligned && (p.K & 255) == 0 && (reinterpret_cast<uintptr_t>(p.xq) & 15) == 0) {
+      OXB_MMVQ_FAST(mmvq_q4k_dp4a_kernel);
+      return;
+    }
+    if (aligned && (p.K & 255) == 0) {
+      OXB_MMVQ_FAST(mmvq_q4k_kernel);
+      return;
+    }
+  }
+  if constexpr (T == kQ_Q8_0) {
+    if (p.xq != nullptr && (reinterpret_cast<uintptr_t>(p.w) & 1) == 0 && (p.row_bytes & 1) == 0 &&
+        (reinterpret_cast<uintptr_t>(p.xq) & 15) == 0) {
+      OXB_MMVQ_FAST(mmvq_q8_0_dp4a_kernel);
+      return;
+    }
+    if ((reinterpret_cast<uintptr_t>(p.w) & 1) == 0 && (p.row_bytes & 1) == 0 &&
+        (reinterpret_cast<uintptr_t>(p.x) & 15) == 0 && (p.ldx & 7) == 0) {
+      OXB_MMVQ_FAST(mmvq_q8_0_kernel);
+      return;
+    }
+  }
   const int gx = (p.N + kRowsPerCta - 1) / kRowsPerCta;
   if (p.M == 1) {
     mmvq_kernel<T, 1><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);
@@ -141,6 +461,15 @@ void dequant_dispatch(const uint8_t* w, long long row_bytes, const int* row_ids,
     case kQ_NVFP4: CALL(kQ_NVFP4); break;                           \
     default: return false;                                          \
   }
+
+void launch_quant_q8_1(const __nv_bfloat16* x, long long ldx, int8_t* xq, float* xd, float* xs, int M,
+                       int K, cudaStream_t stream) {
+  const long long warps = static_cast<long long>(M) * (K >> 5);
+  if (warps <= 0) return;
+  const int threads = 256;
+  quant_q8_1_kernel<<<static_cast<unsigned>((warps * 32 + threads - 1) / threads), threads, 0, stream>>>(
+      x, ldx, xq, xd, xs, M, K);
+}
 
 bool launch_mmvq(int qtype, const MmvqParams& p, cudaStream_t stream) {
   if (p.M <= 0 || p.N <= 0) return true;

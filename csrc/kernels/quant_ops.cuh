@@ -16,7 +16,16 @@ struct MmvqParams {
   long long ldo;
   int M, N, K;
   int add;  // 1: out += result (fused residual)
+  // Optional int8 view of x (Q8_1-style, from launch_quant_q8_1): when set, Q4_K and Q8_0 weights take
+  // the integer dot-product path (dp4a) instead of expanding weights to fp32.
+  const int8_t* xq;   // [M, K], row stride K
+  const float* xd;    // [M, K / 32] block scales
+  const float* xs;    // [M, K / 32] block sums (scale * sum of the int8 values)
 };
+
+// x [M, K] bf16 -> int8 blocks of 32 with an fp32 scale (amax / 127) and the block sum.
+void launch_quant_q8_1(const __nv_bfloat16* x, long long ldx, int8_t* xq, float* xd, float* xs, int M,
+                       int K, cudaStream_t stream);
 
 // Return false when the type has no device decoder.
 bool launch_mmvq(int qtype, const MmvqParams& p, cudaStream_t stream);

@@ -108,6 +108,19 @@ def random_quant_linear(type_name: str, n: int, k: int, device, gen: torch.Gener
     return lin
 
 
+def fuse_quant_rows(parts: list) -> Optional[QuantLinear]:
+    """Stacks packed weights that share the block type and K into one matrix (rows are independent
+    byte ranges, so this is a concatenation): Q|K|V and gate|up then take one GEMV launch instead of
+    three / two. Returns None when the parts cannot be stacked."""
+    if any((not q.packed) or q.type_name != parts[0].type_name or q.k != parts[0].k for q in parts):
+        return None
+    lin = QuantLinear.__new__(QuantLinear)
+    lin.code, lin.type_name, lin.k, lin.packed = parts[0].code, parts[0].type_name, parts[0].k, True
+    lin.n = sum(q.n for q in parts)
+    lin.w = torch.cat([q.w.view(-1) for q in parts])
+    return lin
+
+
 class DeviceModel:
     def __init__(self, cfg: ModelConfig, *, rank: int = 0, world: int = 1, group=None,
                  device: Optional[torch.device] = None, max_tokens: int = 2048, max_seqs: int = 256,
@@ -198,6 +211,10 @@ class DeviceModel:
         if weight_mode == "quant":
             self.gu_acc = torch.zeros(M, 2 * self.i_l, dtype=torch.float32, device=dev)
             self._scratch: Optional[torch.Tensor] = None
+            k_max = max(d, cfg.q_dim, cfg.ffn_dim)
+            self._q8_bufs = (torch.zeros(8 * k_max, dtype=torch.int8, device=dev),
+                             torch.zeros(8 * k_max // 32, dtype=torch.float32, device=dev),
+                             torch.zeros(8 * k_max // 32, dtype=torch.float32, device=dev))
         if weight_mode == "fp8":
             k_max = max(d, self.hq * self.D, self.i_l)
             self.a8_flat = torch.zeros(M * k_max, dtype=torch.float8_e4m3fn, device=dev)
@@ -249,6 +266,17 @@ class DeviceModel:
             self.layers.append(L)
         self._tile_head()
 
+    @staticmethod
+    def _fuse_quant_layer(L: dict) -> None:
+        qkv = fuse_quant_rows([L["attn_q"], L["attn_k"], L["attn_v"]])
+        if qkv is not None:
+            L["attn_qkv"] = qkv
+            del L["attn_q"], L["attn_k"], L["attn_v"]
+        gu = fuse_quant_rows([L["ffn_gate"], L["ffn_up"]])
+        if gu is not None:
+            L["ffn_gate_up"] = gu
+            del L["ffn_gate"], L["ffn_up"]
+
     def _tile_layer(self, L: dict) -> None:
         if self.weight_mode != "bf16" or not self.tile_weights:
             return
@@ -279,6 +307,7 @@ class DeviceModel:
                               ("attn_output", d, cfg.q_dim), ("ffn_gate", cfg.ffn_dim, d), ("ffn_up", cfg.ffn_dim, d),
                               ("ffn_down", d, cfg.ffn_dim)):
                 L[key] = random_quant_linear(type_name, n, k, dev, g)
+            self._fuse_quant_layer(L)
             self.layers.append(L)
 
     def load(self, src: WeightSource) -> None:
@@ -318,6 +347,7 @@ class DeviceModel:
                                   ("ffn_down", cfg.d_model, cfg.ffn_dim)):
                     nm = p + key + ".weight"
                     L[key] = QuantLinear(src.type_name(nm), src.raw(nm), n, k, dev)
+                self._fuse_quant_layer(L)
             else:
                 wq, wk, wv = src.f32(p + "attn_q.weight"), src.f32(p + "attn_k.weight"), src.f32(p + "attn_v.weight")
                 L["w_qkv"] = bf(np.concatenate([wq[hq_lo:hq_hi], wk[kv_lo:kv_hi], wv[kv_lo:kv_hi]], 0))
@@ -417,11 +447,19 @@ class DeviceModel:
             self._scratch = torch.empty(need, dtype=torch.bfloat16, device=self.device)
         return self._scratch[:need].view(n, k)
 
-    def _qlinear(self, lin: QuantLinear, x: torch.Tensor, out_f32: torch.Tensor, ld_out: Optional[int] = None):
+    def _q8(self, x: torch.Tensor):
+        """int8 view of the activation rows for the integer dot-product GEMV (small batches only)."""
+        if x.shape[0] > 8 or x.shape[1] % 256:
+            return None
+        return ops.quant_q8_1(x, self._q8_bufs)
+
+    def _qlinear(self, lin: QuantLinear, x: torch.Tensor, out_f32: torch.Tensor, ld_out: Optional[int] = None,
+                 xq=None):
         """out_f32[:, :n] = x @ W^T for a packed weight: MMVQ for small batches, else dequant + tcgen05."""
         m = x.shape[0]
         if lin.packed and m <= 8:
-            ops.mmvq(lin.code, lin.w, x, out_f32, n=lin.n, k=lin.k)
+            ops.mmvq(lin.code, lin.w, x, out_f32, n=lin.n, k=lin.k,
+                     xq=xq if lin.type_name in ("Q4_K", "Q8_0") else None)
             return
         w = lin.w
         if lin.packed:
@@ -556,27 +594,35 @@ class DeviceModel:
         self._finalize(M, self.layers[0]["attn_norm"], acc=None, gather="gather0", flag_base=F_AG0, r0=0, first=True)
         qd, kd = cfg.q_dim, cfg.kv_dim
         for li, L in enumerate(self.layers):
-            self._qlinear(L["attn_q"], g0, self.qkv_acc[:M, :qd])
-            self._qlinear(L["attn_k"], g0, self.qkv_acc[:M, qd:qd + kd])
-            self._qlinear(L["attn_v"], g0, self.qkv_acc[:M, qd + kd:])
+            xq = self._q8(g0)
+            if "attn_qkv" in L:
+                self._qlinear(L["attn_qkv"], g0, self.qkv_acc[:M], xq=xq)
+            else:
+                self._qlinear(L["attn_q"], g0, self.qkv_acc[:M, :qd], xq=xq)
+                self._qlinear(L["attn_k"], g0, self.qkv_acc[:M, qd:qd + kd], xq=xq)
+                self._qlinear(L["attn_v"], g0, self.qkv_acc[:M, qd + kd:], xq=xq)
             ops.qkv_rope_append(acc_f32=self.qkv_acc, bias=L["b_qkv"], q_norm_w=L["q_norm"], k_norm_w=L["k_norm"],
                                 norm_eps=1e-6, norm_w_offset=cfg.norm_weight_offset, positions=s.positions,
                                 slot_mapping=s.slot_mapping, inv_freq=self.inv_freq, rope_mscale=self.rope_mscale,
                                 q_out=self.q_buf, k_cache=self.k_cache[li], v_cache=self.v_cache[li], m=M,
                                 hq=self.hq, hkv=self.hkv, d=self.D)
             self._attention(s, li)
-            self._qlinear(L["attn_output"], self.attn_out[:M], acc0[:M])
+            self._qlinear(L["attn_output"], self.attn_out[:M], acc0[:M], xq=self._q8(self.attn_out[:M]))
             self._finalize(M, L["ffn_norm"], acc=0, gather="gather1", flag_base=F_AG1, r0=0)
-            self._qlinear(L["ffn_gate"], g1, self.gu_acc[:M, :self.i_l])
-            self._qlinear(L["ffn_up"], g1, self.gu_acc[:M, self.i_l:])
+            xq = self._q8(g1)
+            if "ffn_gate_up" in L:
+                self._qlinear(L["ffn_gate_up"], g1, self.gu_acc[:M], xq=xq)
+            else:
+                self._qlinear(L["ffn_gate"], g1, self.gu_acc[:M, :self.i_l], xq=xq)
+                self._qlinear(L["ffn_up"], g1, self.gu_acc[:M, self.i_l:], xq=xq)
             ops.swiglu(acc_f32=self.gu_acc, out=self.act, m=M, i=self.i_l, act=self._act_code)
-            self._qlinear(L["ffn_down"], self.act[:M], acc1[:M])
+            self._qlinear(L["ffn_down"], self.act[:M], acc1[:M], xq=self._q8(self.act[:M]))
             if li != cfg.n_layers - 1:
                 self._finalize(M, self.layers[li + 1]["attn_norm"], acc=1, gather="gather0", flag_base=F_AG0, r0=0)
         n_log = max(s.n_logits, 1)
         self._finalize(M, self.out_norm, acc=1, gather="lmg", flag_base=F_LMG, r0=0, row_map=s.logit_map[:M])
         lmg = self.ws.local("lmg")[:n_log]
-        self._qlinear(self.lm_head_q, lmg, self.logits[:n_log])
+        self._qlinear(self.lm_head_q, lmg, self.logits[:n_log], xq=self._q8(lmg) if n_log <= 8 else None)
         if cfg.logit_softcap > 0:
             ops.softcap(self.logits[:n_log], cfg.logit_softcap)
         return self.logits[:n_log]

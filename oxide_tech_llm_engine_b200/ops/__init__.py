@@ -275,9 +275,29 @@ def softcap(logits, cap: float) -> None:
     _bump()
 
 
-def mmvq(qtype: int, w, x, out, *, n: int, k: int, bias=None, add: bool = False) -> None:
-    _ext().mmvq(qtype, w, x, bias, out, n, k, add)
+def mmvq(qtype: int, w, x, out, *, n: int, k: int, bias=None, add: bool = False, xq=None) -> None:
+    """Small-batch quantised GEMV. `xq` = (int8 [M, K], scales [M, K/32], sums [M, K/32]) from
+    `quant_q8_1(x)`: Q4_K and Q8_0 weights then take the integer dot-product (dp4a) path."""
+    q8, xd, xs = xq if xq is not None else (None, None, None)
+    _ext().mmvq(qtype, w, x, bias, out, n, k, add, q8, xd, xs)
     _bump()
+
+
+def quant_q8_1(x: torch.Tensor, bufs=None):
+    """bf16 [M, K] -> (int8 [M, K], fp32 scales [M, K/32], fp32 block sums [M, K/32]); `bufs` are
+    preallocated flat buffers (int8, fp32, fp32) to view into (CUDA-graph friendly)."""
+    M, K = x.shape
+    if bufs is None:
+        q8 = torch.empty(M, K, dtype=torch.int8, device=x.device)
+        xd = torch.empty(M, K // 32, dtype=torch.float32, device=x.device)
+        xs = torch.empty(M, K // 32, dtype=torch.float32, device=x.device)
+    else:
+        q8 = bufs[0][:M * K].view(M, K)
+        xd = bufs[1][:M * (K // 32)].view(M, K // 32)
+        xs = bufs[2][:M * (K // 32)].view(M, K // 32)
+    _ext().quant_q8_1(x, q8, xd, xs)
+    _bump()
+    return q8, xd, xs
 
 
 def dequant_rows(qtype: int, w, out, *, n_src_rows: int, k: int, row_ids=None, scale: float = 1.0) -> None:

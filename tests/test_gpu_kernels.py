@@ -473,6 +473,22 @@ def test_dequant_and_mmvq(ops, qname):
         torch.cuda.synchronize()
         yref = x.float() @ ref.T
         assert _rel_err(y, yref) < 2e-3, (qname, M, _rel_err(y, yref))
+    if qname in ("Q4_K", "Q8_0"):
+        # integer dot-product path: activations quantised to int8 blocks of 32 (Q8_1 style)
+        for M in (1, 2, 3, 8):
+            x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+            q8, xd, xs = ops.quant_q8_1(x)
+            xb = x.float().view(M, K // 32, 32)
+            torch.testing.assert_close(xd, xb.abs().amax(-1) / 127.0, rtol=1e-5, atol=1e-12)
+            deq = q8.float().view(M, K // 32, 32) * xd[..., None]
+            assert (deq - xb).abs().max() <= xd.max() * 0.51
+            torch.testing.assert_close(xs, deq.sum(-1), rtol=1e-4, atol=1e-4)
+            y = torch.empty(M, N, device=DEV, dtype=torch.float32)
+            ops.mmvq(code, w_dev, x, y, n=N, k=K, xq=(q8, xd, xs))
+            torch.cuda.synchronize()
+            exact = deq.view(M, K) @ ref.T            # exact product of the quantised activations
+            assert _rel_err(y, exact) < 2e-3, (qname, M, _rel_err(y, exact))
+            assert _rel_err(y, x.float() @ ref.T) < 3e-2
     bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
     x = torch.randn(4, K, device=DEV, dtype=torch.bfloat16)
     yb = torch.randn(4, N, device=DEV).to(torch.bfloat16)
