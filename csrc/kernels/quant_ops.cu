@@ -226,70 +226,90 @@ __global__ void quant_q8_1_kernel(const __nv_bfloat16* __restrict__ x, long long
 // of the four, 16-byte chunk r = l % 8 of its 128 nibble bytes = 16 low-nibble weights of sub-block
 // 2j and 16 high-nibble weights of sub-block 2j+1 (j = r / 2). The loop is unrolled so that a warp
 // keeps 2 KB of weights in flight; all loads are contiguous across lanes.
-template <int MB>
+// R weight rows per warp: their loads are issued together (more bytes in flight per warp, the
+// activation loads are shared).
+template <int MB, int R>
 __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q4k_dp4a_kernel(const MmvqParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x * kRowsPerCta + warp;
-  if (n >= p.N) return;
+  const int n_base = (blockIdx.x * kRowsPerCta + warp) * R;
+  if (n_base >= p.N) return;
   const int m0 = blockIdx.y * MB;
-  const uint8_t* wrow = p.w + static_cast<long long>(n) * p.row_bytes;
   const int n_sb = p.K >> 8, n_blk = p.K >> 5;
   const int r = lane & 7, j = r >> 1, c2 = r & 1;
-  float acc[MB];
+  float acc[R][MB];
 #pragma unroll
-  for (int m = 0; m < MB; ++m) acc[m] = 0.f;
+  for (int t = 0; t < R; ++t)
+#pragma unroll
+    for (int m = 0; m < MB; ++m) acc[t][m] = 0.f;
 
 #pragma unroll 4
   for (int sb = lane >> 3; sb < n_sb; sb += 4) {
-    const uint8_t* b = wrow + static_cast<long long>(sb) * 144;
-    const uint4 q = __ldg(reinterpret_cast<const uint4*>(b + 16) + r);
-    const uint32_t dm = __ldg(reinterpret_cast<const uint32_t*>(b));
-    const uint32_t s0 = __ldg(reinterpret_cast<const uint32_t*>(b + 4));
-    const uint32_t s1 = __ldg(reinterpret_cast<const uint32_t*>(b + 8));
-    const uint32_t s2 = __ldg(reinterpret_cast<const uint32_t*>(b + 12));
-    const float d = __half2float(__ushort_as_half(static_cast<uint16_t>(dm & 0xFFFFu)));
-    const float dmin = __half2float(__ushort_as_half(static_cast<uint16_t>(dm >> 16)));
-    int sc[2], mn[2];
+    uint4 q[R];
+    uint32_t dm[R], s0[R], s1[R], s2[R];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int sub = 2 * j + h;
-      if (sub < 4) {
-        sc[h] = byte_of3(s0, s1, s2, sub) & 63;
-        mn[h] = byte_of3(s0, s1, s2, sub + 4) & 63;
-      } else {
-        sc[h] = (byte_of3(s0, s1, s2, sub + 4) & 0xF) | ((byte_of3(s0, s1, s2, sub - 4) >> 6) << 4);
-        mn[h] = (byte_of3(s0, s1, s2, sub + 4) >> 4) | ((byte_of3(s0, s1, s2, sub) >> 6) << 4);
-      }
+    for (int t = 0; t < R; ++t) {
+      const int n = n_base + t < p.N ? n_base + t : p.N - 1;  // a clamped duplicate row is not stored
+      const uint8_t* b = p.w + static_cast<long long>(n) * p.row_bytes + static_cast<long long>(sb) * 144;
+      q[t] = __ldg(reinterpret_cast<const uint4*>(b + 16) + r);
+      dm[t] = __ldg(reinterpret_cast<const uint32_t*>(b));
+      s0[t] = __ldg(reinterpret_cast<const uint32_t*>(b + 4));
+      s1[t] = __ldg(reinterpret_cast<const uint32_t*>(b + 8));
+      s2[t] = __ldg(reinterpret_cast<const uint32_t*>(b + 12));
     }
-    const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
-    const float dl0 = d * sc[0], dl1 = d * sc[1];
-    // the `- dmin * mn * sum(x)` term of a sub-block is added once, by the lane that owns its first half
-    const float ml0 = c2 == 0 ? dmin * mn[0] : 0.f, ml1 = c2 == 0 ? dmin * mn[1] : 0.f;
     const int e0 = sb * 256 + j * 64 + c2 * 16;
     const int blk = sb * 8 + 2 * j;
+    int4 xl[MB], xh[MB];
+    float2 dd[MB], ss[MB];
 #pragma unroll
     for (int m = 0; m < MB; ++m) {
-      if (m0 + m >= p.M) continue;
-      const int8_t* xr = p.xq + static_cast<long long>(m0 + m) * p.K + e0;
-      const int4 xl = __ldg(reinterpret_cast<const int4*>(xr));
-      const int4 xh = __ldg(reinterpret_cast<const int4*>(xr + 32));
-      const float2 dd = __ldg(reinterpret_cast<const float2*>(p.xd + static_cast<long long>(m0 + m) * n_blk + blk));
-      const float2 ss = __ldg(reinterpret_cast<const float2*>(p.xs + static_cast<long long>(m0 + m) * n_blk + blk));
-      const int xlw[4] = {xl.x, xl.y, xl.z, xl.w}, xhw[4] = {xh.x, xh.y, xh.z, xh.w};
-      int il = 0, ih = 0;
+      const int mm = m0 + m < p.M ? m0 + m : p.M - 1;
+      const int8_t* xr = p.xq + static_cast<long long>(mm) * p.K + e0;
+      xl[m] = __ldg(reinterpret_cast<const int4*>(xr));
+      xh[m] = __ldg(reinterpret_cast<const int4*>(xr + 32));
+      dd[m] = __ldg(reinterpret_cast<const float2*>(p.xd + static_cast<long long>(mm) * n_blk + blk));
+      ss[m] = __ldg(reinterpret_cast<const float2*>(p.xs + static_cast<long long>(mm) * n_blk + blk));
+    }
 #pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        il = __dp4a(static_cast<int>(qw[t] & 0x0F0F0F0Fu), xlw[t], il);
-        ih = __dp4a(static_cast<int>((qw[t] >> 4) & 0x0F0F0F0Fu), xhw[t], ih);
+    for (int t = 0; t < R; ++t) {
+      const float d = __half2float(__ushort_as_half(static_cast<uint16_t>(dm[t] & 0xFFFFu)));
+      const float dmin = __half2float(__ushort_as_half(static_cast<uint16_t>(dm[t] >> 16)));
+      int sc[2], mn[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int sub = 2 * j + h;
+        if (sub < 4) {
+          sc[h] = byte_of3(s0[t], s1[t], s2[t], sub) & 63;
+          mn[h] = byte_of3(s0[t], s1[t], s2[t], sub + 4) & 63;
+        } else {
+          sc[h] = (byte_of3(s0[t], s1[t], s2[t], sub + 4) & 0xF) | ((byte_of3(s0[t], s1[t], s2[t], sub - 4) >> 6) << 4);
+          mn[h] = (byte_of3(s0[t], s1[t], s2[t], sub + 4) >> 4) | ((byte_of3(s0[t], s1[t], s2[t], sub) >> 6) << 4);
+        }
       }
-      acc[m] += dl0 * dd.x * int_to_float(il) + dl1 * dd.y * int_to_float(ih) - ml0 * ss.x - ml1 * ss.y;
+      const uint32_t qw[4] = {q[t].x, q[t].y, q[t].z, q[t].w};
+      const float dl0 = d * sc[0], dl1 = d * sc[1];
+      // the `- dmin * mn * sum(x)` term of a sub-block is added once, by the lane that owns its first half
+      const float ml0 = c2 == 0 ? dmin * mn[0] : 0.f, ml1 = c2 == 0 ? dmin * mn[1] : 0.f;
+#pragma unroll
+      for (int m = 0; m < MB; ++m) {
+        const int xlw[4] = {xl[m].x, xl[m].y, xl[m].z, xl[m].w}, xhw[4] = {xh[m].x, xh[m].y, xh[m].z, xh[m].w};
+        int il = 0, ih = 0;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          il = __dp4a(static_cast<int>(qw[u] & 0x0F0F0F0Fu), xlw[u], il);
+          ih = __dp4a(static_cast<int>((qw[u] >> 4) & 0x0F0F0F0Fu), xhw[u], ih);
+        }
+        acc[t][m] += dl0 * dd[m].x * int_to_float(il) + dl1 * dd[m].y * int_to_float(ih) - ml0 * ss[m].x -
+                     ml1 * ss[m].y;
+      }
     }
   }
 #pragma unroll
-  for (int m = 0; m < MB; ++m) {
-    const float v = warp_sum(acc[m]);
-    if (lane == 0 && m0 + m < p.M) mmvq_store(p, n, m0 + m, v);
-  }
+  for (int t = 0; t < R; ++t)
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+      const float v = warp_sum(acc[t][m]);
+      if (lane == 0 && m0 + m < p.M && n_base + t < p.N) mmvq_store(p, n_base + t, m0 + m, v);
+    }
 }
 
 // Q8_0 x int8: a lane takes one 34-byte block (2-byte aligned: 16-bit loads, repacked into words).
@@ -400,7 +420,15 @@ void mmvq_dispatch(const MmvqParams& p, cudaStream_t s) {
                        (reinterpret_cast<uintptr_t>(p.x) & 15) == 0 && (p.ldx & 7) == 0;
   if constexpr (T == kQ_Q4_K) {
     if (p.xq != nullptr && aligned && (p.K & 255) == 0 && (reinterpret_cast<uintptr_t>(p.xq) & 15) == 0) {
-      OXB_MMVQ_FAST(mmvq_q4k_dp4a_kernel);
+      if (p.M == 1) {
+        const int gx = (p.N + 2 * kRowsPerCta - 1) / (2 * kRowsPerCta);
+        mmvq_q4k_dp4a_kernel<1, 2><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);
+      } else {
+        const int gx = (p.N + kRowsPerCta - 1) / kRowsPerCta;
+        if (p.M == 2) mmvq_q4k_dp4a_kernel<2, 1><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);
+        else if (p.M <= 4) mmvq_q4k_dp4a_kernel<4, 1><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);
+        else mmvq_q4k_dp4a_kernel<8, 1><<<dim3(gx, (p.M + 7) / 8), kRowsPerCta * 32, 0, s>>>(p);
+      }
       return;
     }
     if (aligned && (p.K & 255) == 0) {
