@@ -15,6 +15,7 @@
 #include "kernels/fused_ops.cuh"
 #include "kernels/gemm_bf16.cuh"
 #include "kernels/gemm_fp8_block.cuh"
+#include "kernels/gemv_bf16.cuh"
 #include "kernels/quant_ops.cuh"
 #include "kernels/sampler.cuh"
 
@@ -580,6 +581,44 @@ void mmvq(int64_t qtype, const Tensor& w, const Tensor& x, const c10::optional<T
   check_launch("mmvq");
 }
 
+// x: [M <= 8, K] bf16; w: [N, K] bf16 or tile-major [N/128, K/64, 128, 64]; out: [M, N] (or [M, N/2] with swiglu).
+void gemv_bf16(const Tensor& x, const Tensor& w, const Tensor& out, const c10::optional<Tensor>& bias,
+               bool swiglu, int64_t act) {
+  TORCH_CHECK(x.is_cuda() && w.is_cuda() && x.scalar_type() == torch::kBFloat16 &&
+                  w.scalar_type() == torch::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 && w.is_contiguous(),
+              "gemv_bf16: bf16 CUDA operands, contiguous weights");
+  const bool tiled = w.dim() == 4;
+  const int64_t M = x.size(0), K = x.size(1);
+  const int64_t N = tiled ? w.size(0) * 128 : w.size(0);
+  TORCH_CHECK(M >= 1 && M <= 8, "gemv_bf16: 1..8 rows");
+  TORCH_CHECK((tiled ? w.size(1) * 64 : w.size(1)) == K && K % 64 == 0 && N % 2 == 0,
+              "gemv_bf16: K mismatch, K % 64 != 0 or odd N");
+  TORCH_CHECK(x.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0,
+              "gemv_bf16: activation rows must be 16-byte aligned");
+  TORCH_CHECK(!swiglu || N % 64 == 0, "gemv_bf16: the SwiGLU form needs N % 64 == 0");
+  const int64_t n_out = swiglu ? N / 2 : N;
+  TORCH_CHECK(out.dim() == 2 && out.size(0) >= M && out.size(1) >= n_out && out.stride(1) == 1,
+              "gemv_bf16: out too small");
+  oxb::GemvParams p{};
+  p.w = reinterpret_cast<const __nv_bfloat16*>(w.data_ptr());
+  p.x = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr());
+  p.ldx = x.stride(0);
+  p.bias = bf16_ptr(bias);
+  if (out.scalar_type() == torch::kFloat32)
+    p.out_f32 = out.data_ptr<float>();
+  else
+    p.out_bf16 = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  p.ldo = out.stride(0);
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(K);
+  p.tiled = tiled ? 1 : 0;
+  p.swiglu = swiglu ? 1 : 0;
+  p.act = static_cast<int>(act);
+  oxb::launch_gemv_bf16(p, cur_stream());
+  check_launch("gemv_bf16");
+}
+
 void quant_q8_1(const Tensor& x, const Tensor& xq, const Tensor& xd, const Tensor& xs) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 &&
                   x.size(1) % 32 == 0,
@@ -720,6 +759,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("kv_block_copy", &kv_block_copy);
   m.def("softcap", &softcap);
   m.def("mmvq", &mmvq);
+  m.def("gemv_bf16", &gemv_bf16);
   m.def("quant_q8_1", &quant_q8_1);
   m.def("dequant_rows", &dequant_rows);
   m.def("quant_row_bytes", &quant_row_bytes);

@@ -150,6 +150,8 @@ class DeviceModel:
         self.weight_mode = weight_mode
         # dense bf16 projections are kept tile-major in HBM (see ops.tile_weight) unless a library
         # GEMM has to read them
+        self.gemv_small = os.environ.get("OXB_GEMV", "1") != "0"
+        self.gemv_max_rows = int(os.environ.get("OXB_GEMV_MAX", "2"))
         self.prefetch_mask = int(os.environ.get("OXB_PREFETCH", "0"))
         self.prefetch_head = int(os.environ.get("OXB_PREFETCH_HEAD_MB", "48")) << 19  # bf16 elements
         self.tile_weights = (os.environ.get("OXB_TILE_WEIGHTS", "1") != "0") if tile_weights is None else tile_weights
@@ -496,7 +498,30 @@ class DeviceModel:
         # kernel's weights into L2 meanwhile (bit 0: gate/up -> down, 1: down -> next QKV,
         # 2: QKV -> O, 3: O -> head of gate/up).
         pf = self.prefetch_mask if M <= 512 and not cfg.is_moe else 0
+        # single GPU, a handful of rows (latency-mode decoding): weight-streaming GEMVs instead of
+        # 128-row MMA tiles
+        gemv = (tp == 1 and M <= self.gemv_max_rows and not cfg.is_moe and self.gemv_small and d % 64 == 0
+                and (self.hq * self.D) % 64 == 0 and self.i_l % 64 == 0 and self.wqkv % 2 == 0)
         for li, L in enumerate(self.layers):
+            if gemv:
+                acc0, acc1 = self.ws.local("acc0"), self.ws.local("acc1")
+                ops.gemv(g0, L["w_qkv"], self.qkv_bf16[:M])
+                ops.qkv_rope_append(bias=L["b_qkv"], q_norm_w=L["q_norm"], k_norm_w=L["k_norm"], norm_eps=1e-6,
+                                    norm_w_offset=cfg.norm_weight_offset, positions=s.positions,
+                                    slot_mapping=s.slot_mapping, inv_freq=self.inv_freq,
+                                    rope_mscale=self.rope_mscale, q_out=self.q_buf, k_cache=self.k_cache[li],
+                                    v_cache=self.v_cache[li], m=M, hq=self.hq, hkv=self.hkv, d=self.D,
+                                    qkv_bf16=self.qkv_bf16)
+                self._attention(s, li)
+                self._rs_slab[0] = self._rs_slab[1] = False
+                ops.gemv(self.attn_out[:M], L["w_o"], acc0[:M])
+                self._finalize(rpr, L["ffn_norm"], acc=0, gather="gather1", flag_base=F_AG1, r0=r0)
+                ops.gemv(g1, L["w_gu"], self.act[:M], swiglu=True, act=self._act_code)
+                ops.gemv(self.act[:M], L["w_down"], acc1[:M])
+                if li != len(self.layers) - 1:
+                    self._finalize(rpr, self.layers[li + 1]["attn_norm"], acc=1, gather="gather0", flag_base=F_AG0,
+                                   r0=r0)
+                continue
             # ---- attention block ----
             bn = ops.pick_bn(self.wqkv, (M + 127) // 128, can_split=True)
             splits = ops.pick_splits(M, self.wqkv, d, bn)
@@ -548,8 +573,11 @@ class DeviceModel:
         self._finalize(rpr, self.out_norm, acc=1, gather="lmg", flag_base=F_LMG, r0=r0 if row_map is None else 0,
                        row_map=row_map, moe_acc=cfg.is_moe)
         lmg = self.ws.local("lmg")[:n_log]
-        ops.gemm(lmg, self.lm_head, out=self.logits[:n_log], epi=ops.EPI_STORE_F32,
-                 bn=ops.pick_bn(self.v_l, (n_log + 127) // 128), **self._ag_kwargs(F_LMG, T_LMG, 0, rpr))
+        if gemv and n_log <= 8 and self.v_l % 2 == 0:
+            ops.gemv(lmg, self.lm_head, self.logits[:n_log])
+        else:
+            ops.gemm(lmg, self.lm_head, out=self.logits[:n_log], epi=ops.EPI_STORE_F32,
+                     bn=ops.pick_bn(self.v_l, (n_log + 127) // 128), **self._ag_kwargs(F_LMG, T_LMG, 0, rpr))
         if cfg.logit_softcap > 0:
             ops.softcap(self.logits[:n_log], cfg.logit_softcap)
         return self.logits[:n_log]

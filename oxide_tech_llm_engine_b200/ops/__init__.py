@@ -283,6 +283,13 @@ def mmvq(qtype: int, w, x, out, *, n: int, k: int, bias=None, add: bool = False,
     _bump()
 
 
+def gemv(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias=None, swiglu: bool = False, act: int = 0) -> None:
+    """out[:M] = x @ w^T for M <= 8 rows (single-GPU latency-mode decoding); `w` row-major or
+    tile-major. `swiglu`: w holds gate|up interleaved by 32 rows and out gets act(gate) * up."""
+    _ext().gemv_bf16(x, w, out, bias, swiglu, act)
+    _bump()
+
+
 def quant_q8_1(x: torch.Tensor, bufs=None):
     """bf16 [M, K] -> (int8 [M, K], fp32 scales [M, K/32], fp32 block sums [M, K/32]); `bufs` are
     preallocated flat buffers (int8, fp32, fp32) to view into (CUDA-graph friendly)."""

@@ -628,3 +628,33 @@ def test_block_table_bounds_are_checked_without_touching_memory(ops):
         ops.check_status(q.device)
     ops.check_status(q.device)   # the status word was cleared by the failed check
     assert torch.isfinite(out.float()).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tiled", [False, True])
+@pytest.mark.parametrize("m,n,k", [(1, 512, 1024), (3, 256, 192), (8, 1280, 4096)])
+def test_gemv_bf16_small_batch(ops, m, n, k, tiled):
+    torch.manual_seed(m * n + k)
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
+    bias = torch.randn(n, device="cuda").bfloat16()
+    ww = ops.tile_weight(w) if tiled else w
+    if tiled and ww.dim() != 4:
+        pytest.skip("shape does not tile")
+    ref = x.float() @ w.float().t()
+    out = torch.zeros(m, n, device="cuda")
+    ops.gemv(x, ww, out, bias=bias)
+    assert _rel_err(out, ref + bias.float()) < 2e-3
+    outb = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+    ops.gemv(x, ww, outb)
+    assert _rel_err(outb, ref) < 1e-2
+    if n % 64 == 0:
+        # gate|up interleaved in units of 32 rows, as the fused SwiGLU GEMM epilogue stores them
+        from oxide_tech_llm_engine_b200.models.llama import interleave32
+        g, u = w[: n // 2], w[n // 2:]
+        wi = interleave32(g, u)
+        wi = ops.tile_weight(wi) if tiled else wi
+        y = torch.zeros(m, n // 2, device="cuda", dtype=torch.bfloat16)
+        ops.gemv(x, wi, y, swiglu=True)
+        gr, ur = x.float() @ g.float().t(), x.float() @ u.float().t()
+        assert _rel_err(y, torch.nn.functional.silu(gr) * ur) < 1.5e-2
