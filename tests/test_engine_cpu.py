@@ -230,3 +230,28 @@ def test_h2o_pruning_bounds_the_kv_of_a_long_sequence_on_cpu():
     assert len(eng.requests[rid].output) == 40
     assert eng.sched.num_free_blocks() == 64
     eng.close()
+
+
+def test_nvfp4_moe_gguf_round_trip_on_cpu():
+    import os
+    import tempfile
+
+    from oxide_tech_llm_engine_b200.config import EngineConfig
+    from oxide_tech_llm_engine_b200.engine.engine import LLMEngine
+    from oxide_tech_llm_engine_b200.models.config import preset
+    from oxide_tech_llm_engine_b200.models.reference import ReferenceModel
+    from oxide_tech_llm_engine_b200.models.weights import open_weights, write_synthetic_gguf
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    mc = preset("tiny-moe")
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "m.gguf")
+        write_synthetic_gguf(path, mc, seed=5, weight_type="NVFP4", embed_type="Q8_0", std=0.08)
+        src = open_weights(path)
+        assert src.type_name("blk.0.ffn_down_exps.weight") == "NVFP4" and src.cfg.n_experts == mc.n_experts
+        eng = LLMEngine(EngineConfig(model=path, backend="cpu", max_num_seqs=2, num_kv_blocks=32, ctx_size=128),
+                        src.cfg, weights=src)
+        p = list(range(5, 25))
+        out = eng.generate([p], SamplingParams(greedy=True, max_tokens=6, ignore_eos=True))[0]
+        assert out == ReferenceModel(src.cfg, src).generate_greedy(p, 6)
+        eng.close()

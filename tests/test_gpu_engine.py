@@ -117,6 +117,29 @@ def test_gguf_quantized_serving(qtype):
         eng.close()
 
 
+def test_nvfp4_moe_checkpoint_is_served_through_the_fused_expert_path():
+    """A Mixtral-style GGUF whose matrices are NVFP4 blocks: the expert weights are expanded to bf16 at
+    load (packed serving is for dense models) and run through the router / grouped GEMM / combine."""
+    from oxide_tech_llm_engine_b200.models.config import preset
+    from oxide_tech_llm_engine_b200.models.weights import open_weights, write_synthetic_gguf
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    mc = preset("tiny-moe")
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "m.gguf")
+        write_synthetic_gguf(path, mc, seed=5, weight_type="NVFP4", embed_type="Q8_0", std=0.08)
+        src = open_weights(path)
+        assert src.type_name("blk.0.ffn_gate_exps.weight") == "NVFP4"
+        eng, mc2, _ = _mk("tiny-moe", weights=src)
+        assert eng.model.weight_mode == "bf16" and mc2.is_moe
+        rng = np.random.default_rng(9)
+        prompts = [rng.integers(3, mc.vocab_size, size=n).tolist() for n in (6, 40)]
+        outs = eng.generate(prompts, SamplingParams(greedy=True, max_tokens=10, ignore_eos=True))
+        eng.check_device_status()
+        assert_consistent(mc2, src, prompts, outs)
+        eng.close()
+
+
 def test_fp8_block_scaled_serving():
     """Block-scaled fp8 projections: tokens stay consistent with the fp32 oracle's logits."""
     from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
