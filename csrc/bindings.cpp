@@ -460,6 +460,7 @@ void qkv_rope_append(const c10::optional<Tensor>& acc_f32, const c10::optional<T
   p.acc_f32 = opt_ptr<float>(acc_f32);
   p.qkv_bf16 = bf16_ptr(qkv_bf16);
   TORCH_CHECK((p.acc_f32 != nullptr) != (p.qkv_bf16 != nullptr), "qkv_rope_append: one input");
+  TORCH_CHECK(D >= 2 && D <= 256 && D % 2 == 0, "qkv_rope_append: head_dim must be even and <= 256");
   p.bias = bf16_ptr(bias);
   p.q_norm_w = bf16_ptr(q_norm_w);
   p.k_norm_w = bf16_ptr(k_norm_w);

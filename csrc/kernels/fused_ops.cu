@@ -315,10 +315,19 @@ __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const Fi
 __global__ void __launch_bounds__(256) qkv_rope_append_kernel(const QkvRopeParams p) {
   extern __shared__ float s_row[];  // (Hq + 2 Hkv) * D floats
   __shared__ float s_ssq[160];      // per-head sum of squares (Hq + Hkv <= 160)
+  __shared__ float s_sin[128], s_cos[128];  // the token's rotation, shared by every head (D <= 256)
   const int tok = blockIdx.x;
   const int D = p.D, half = D >> 1;
   const int W = (p.Hq + 2 * p.Hkv) * D;
   const long long roff = static_cast<long long>(tok) * W;
+  const int pos = p.positions[tok];
+  // one precise sincos per frequency and token instead of one per (head, frequency)
+  for (int d = threadIdx.x; d < half; d += blockDim.x) {
+    float sn, cs;
+    sincosf(static_cast<float>(pos) * p.inv_freq[d], &sn, &cs);
+    s_sin[d] = sn * p.rope_mscale;
+    s_cos[d] = cs * p.rope_mscale;
+  }
 
   for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
     float v[4];
@@ -359,7 +368,6 @@ __global__ void __launch_bounds__(256) qkv_rope_append_kernel(const QkvRopeParam
     __syncthreads();
   }
 
-  const int pos = p.positions[tok];
   const long long slot = p.slot_mapping[tok];
   const bool store_kv = slot >= 0 && slot < p.num_slots;
   if (slot >= p.num_slots && threadIdx.x == 0) atomicExch(p.status, kStatusBadIndex);
@@ -376,10 +384,7 @@ __global__ void __launch_bounds__(256) qkv_rope_append_kernel(const QkvRopeParam
       x0 = x0 * r * (__bfloat162float(w[d]) + p.norm_w_offset);
       x1 = x1 * r * (__bfloat162float(w[d + half]) + p.norm_w_offset);
     }
-    float sn, cs;
-    sincosf(static_cast<float>(pos) * p.inv_freq[d], &sn, &cs);
-    sn *= p.rope_mscale;
-    cs *= p.rope_mscale;
+    const float sn = s_sin[d], cs = s_cos[d];
     const float y0 = x0 * cs - x1 * sn;
     const float y1 = x1 * cs + x0 * sn;
     if (h < p.Hq) {
