@@ -251,10 +251,11 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q4k_dp4a_kernel(const M
       const int n = n_base + t < p.N ? n_base + t : p.N - 1;  // a clamped duplicate row is not stored
       const uint8_t* b = p.w + static_cast<long long>(n) * p.row_bytes + static_cast<long long>(sb) * 144;
       q[t] = __ldg(reinterpret_cast<const uint4*>(b + 16) + r);
-      dm[t] = __ldg(reinterpret_cast<const uint32_t*>(b));
-      s0[t] = __ldg(reinterpret_cast<const uint32_t*>(b + 4));
-      s1[t] = __ldg(reinterpret_cast<const uint32_t*>(b + 8));
-      s2[t] = __ldg(reinterpret_cast<const uint32_t*>(b + 12));
+      const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(b));  // d | dmin | 12 scale bytes
+      dm[t] = hdr.x;
+      s0[t] = hdr.y;
+      s1[t] = hdr.z;
+      s2[t] = hdr.w;
     }
     const int e0 = sb * 256 + j * 64 + c2 * 16;
     const int blk = sb * 8 + 2 * j;
