@@ -111,6 +111,14 @@ class LLMEngine:
             weight_mode = "quant" if packed and world == 1 and not mc.is_moe else "bf16"
         self.max_tokens = max(cfg.max_num_batched_tokens, cfg.max_num_seqs)
         self.max_tokens = (self.max_tokens + world - 1) // world * world
+        # packed GGUF weights may be doubled by a bf16 copy for batched steps (decided before the KV
+        # pool is sized): by default when that copy is under a quarter of the free memory
+        self._dense_bytes = 0
+        if weight_mode == "quant" and cfg.quant_dense_copy != "off" and (weights is not None or random_init):
+            need = 2 * mc.n_params()
+            free_now, _ = torch.cuda.mem_get_info(self.device)
+            if cfg.quant_dense_copy == "on" or need < free_now // 4:
+                self._dense_bytes = need
         num_blocks = cfg.num_kv_blocks
         if num_blocks <= 0:
             num_blocks = self._auto_blocks(mc, weight_mode, random_init or weights is not None)
@@ -131,6 +139,10 @@ class LLMEngine:
             self.model.init_random_quant(random_quant_type or "Q4_K", cfg.seed)
         elif random_init:
             self.model.init_random(cfg.seed)
+        if weight_mode == "quant" and (weights is not None or random_init) and cfg.quant_dense_copy != "off":
+            # batched steps then run at bf16-GEMM speed, small batches keep streaming the packed blocks
+            if self._dense_bytes:
+                self.stats_dense_copy_bytes = self.model.make_dense_copies()
         sc = H.SchedulerConfig()
         sc.num_blocks = num_blocks
         sc.max_num_seqs = cfg.max_num_seqs
@@ -249,7 +261,7 @@ class LLMEngine:
         act += self.cfg.max_num_seqs * (mc.vocab_size // tp) * 4 * 2
         if mc.is_moe:
             act += (mc.n_experts // tp) * self.max_tokens * (mc.d_model + mc.ffn_dim) * 2
-        budget = int(free * self.cfg.gpu_memory_utilization) - w_bytes - act - (2 << 30)
+        budget = int(free * self.cfg.gpu_memory_utilization) - w_bytes - act - (2 << 30) - getattr(self, "_dense_bytes", 0)
         per_block = 2 * mc.n_layers * (mc.n_kv_heads // tp) * 16 * mc.head_dim * 2
         n = budget // per_block
         if n < 16:

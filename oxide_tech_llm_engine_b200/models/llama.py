@@ -443,6 +443,24 @@ class DeviceModel:
             kw["done_ticket"] = self.tickets[ticket:ticket + 1]
         return kw
 
+    def make_dense_copies(self) -> int:
+        """Keeps a bf16 (tile-major) copy of every packed projection next to its GGUF blocks: steps
+        with more than 8 rows (prefill, batched decode) then run the tcgen05 GEMM on it directly instead
+        of expanding the blocks on every call, while small batches keep streaming the packed weights.
+        Returns the bytes added."""
+        added = 0
+        lins = [self.lm_head_q] + [v for L in self.layers for v in L.values() if isinstance(v, QuantLinear)]
+        for lin in lins:
+            if not lin.packed or getattr(lin, "dense", None) is not None:
+                continue
+            w = torch.empty(lin.n, lin.k, dtype=torch.bfloat16, device=self.device)
+            ops.dequant_rows(lin.code, lin.w, w, n_src_rows=lin.n, k=lin.k)
+            lin.dense = ops.tile_weight(w) if self.tile_weights else w
+            added += lin.n * lin.k * 2
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+        return added
+
     def _scratch_for(self, n: int, k: int) -> torch.Tensor:
         need = n * k
         if self._scratch is None or self._scratch.numel() < need:
@@ -464,7 +482,9 @@ class DeviceModel:
                      xq=xq if lin.type_name in ("Q4_K", "Q8_0") else None)
             return
         w = lin.w
-        if lin.packed:
+        if lin.packed and getattr(lin, "dense", None) is not None:
+            w = lin.dense
+        elif lin.packed:
             w = self._scratch_for(lin.n, lin.k)
             ops.dequant_rows(lin.code, lin.w, w, n_src_rows=lin.n, k=lin.k)
         bn = ops.pick_bn(lin.n, (m + 127) // 128, can_split=True)
