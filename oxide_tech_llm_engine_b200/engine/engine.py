@@ -13,6 +13,7 @@ one graph per batch bucket (oxide-backend-cuda/src/lib.rs:3326-4114), prefix reu
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Callable, Iterable, Optional
@@ -86,6 +87,7 @@ class LLMEngine:
                  random_init: bool = False, random_quant_type: Optional[str] = None, pp=None):
         self.cfg = cfg
         self.group = group
+        self._decode_ctas_per_sm = int(os.environ.get("OXB_DECODE_CTAS_PER_SM", "0"))
         self.pp = pp  # parallel.pipeline.PpContext or None; rank/world/group describe the TP group of this stage
         self.rank, self.world = rank, world
         self.cpu = cfg.backend == "cpu"
@@ -348,8 +350,11 @@ class LLMEngine:
             bt[:nd, :w] = plan.decode_block_tables.reshape(nd, w)
             max_len = int(plan.decode_seq_lens.max())
             pages = (max_len + 15) // 16
-            # enough CTAs to fill 148 SMs a few times over, at least one page per warp
-            want = -(-4 * 148 // max(1, nd * self.model.hkv))
+            # enough CTAs to fill 148 SMs a few times over, at least one page per warp. With several KV
+            # heads per rank (single GPU, low TP) shorter page chains balance ragged lengths better:
+            # measured best near 12 CTAs per SM there, near 4 with one KV head per rank (TP = 8).
+            per_sm = self._decode_ctas_per_sm or (12 if self.model.hkv >= 4 else 4)
+            want = -(-per_sm * 148 // max(1, nd * self.model.hkv))
             splits = max(1, min(self.cfg.max_splits, want))
             pps = max(4, -(-pages // splits))
             pps = (pps + 3) // 4 * 4
