@@ -199,3 +199,24 @@ def test_facade_builder_transaction_and_ascii_mask():
 
     m = ascii_first_byte_mask(b'{["', [b"{a", b"x", b"", b"[1", b'"k'])
     assert m.tolist() == [True, False, False, True, True]
+
+
+def test_fuse_quant_rows_stacks_packed_matrices():
+    import numpy as np
+    import torch
+
+    from oxide_tech_llm_engine_b200.formats import quants
+    from oxide_tech_llm_engine_b200.models.llama import QuantLinear, fuse_quant_rows
+
+    rng = np.random.default_rng(3)
+    K = 256
+    mats = [(rng.standard_normal((n, K)) * 0.05).astype(np.float32) for n in (8, 4, 4)]
+    lins = [QuantLinear("Q4_K", quants.quantize_2d("Q4_K", m), m.shape[0], K, torch.device("cpu")) for m in mats]
+    fused = fuse_quant_rows(lins)
+    assert fused is not None and fused.n == 16 and fused.k == K and fused.type_name == "Q4_K"
+    raw = fused.w.numpy().reshape(16, -1)
+    got = quants.dequantize_2d("Q4_K", raw, 16, K)
+    want = np.concatenate([quants.dequantize_2d("Q4_K", quants.quantize_2d("Q4_K", m), m.shape[0], K) for m in mats])
+    np.testing.assert_array_equal(got, want)
+    other = QuantLinear("Q8_0", quants.quantize_2d("Q8_0", mats[0]), 8, K, torch.device("cpu"))
+    assert fuse_quant_rows([lins[0], other]) is None          # different block types are not stacked
