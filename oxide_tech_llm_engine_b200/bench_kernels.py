@@ -126,7 +126,8 @@ def main() -> None:
         if args.pps:
             pps = args.pps
         else:
-            want = -(-4 * 148 // max(1, B * model.hkv))
+            per_sm = 12 if model.hkv >= 4 else 4   # the engine's rule (engine/engine.py, _fill)
+            want = -(-per_sm * 148 // max(1, B * model.hkv))
             splits = max(1, min(args.max_splits, want))
             pps = (max(4, -(-pages // splits)) + 3) // 4 * 4
         s_in = StepInputs(m=M, n_decode=B, n_prefill=0, n_tiles=0, n_logits=B,
