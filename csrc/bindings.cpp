@@ -10,6 +10,7 @@
 #include <string>
 #include <vector>
 
+#include "common/device_info.h"
 #include "common/tma_host.h"
 #include "kernels/attn.cuh"
 #include "kernels/fused_ops.cuh"
@@ -54,8 +55,9 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
                const c10::optional<Tensor>& ag_flags, int64_t ag_expected, int64_t ag_rows_per_src,
                const c10::optional<Tensor>& ag_ticket, const Tensor& status, int64_t bn,
                int64_t splits, int64_t act, int64_t m_tiles_override, int64_t dst_ld,
-               int64_t my_rank, int64_t b_tiled,
-               const c10::optional<Tensor>& prefetch) {
+               int64_t my_rank, int64_t b_tiled, int64_t mt, const c10::optional<Tensor>& ws,
+               const c10::optional<Tensor>& ws_tickets, int64_t spin_limit,
+               const c10::optional<Tensor>& trace) {
   TORCH_CHECK(a.is_cuda() && w.is_cuda(), "gemm_bf16: CUDA tensors required");
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16,
               "gemm_bf16: bf16 operands required");
@@ -106,16 +108,19 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
   p.epi = static_cast<int>(epi);
   p.act = static_cast<int>(act);
   p.b_tiled = static_cast<int>(b_tiled);
-  if (prefetch.has_value() && prefetch->defined()) {
-    TORCH_CHECK(prefetch->is_contiguous() && prefetch->is_cuda(), "gemm_bf16: prefetch range must be contiguous");
-    p.prefetch_ptr = prefetch->data_ptr();
-    p.prefetch_bytes = static_cast<long long>(prefetch->numel() * prefetch->element_size()) & ~15LL;
+  p.spin_limit = static_cast<uint32_t>(spin_limit > 0 ? spin_limit : 0);
+  if (trace.has_value() && trace->defined()) {
+    TORCH_CHECK(trace->scalar_type() == torch::kInt64 && trace->numel() >= 8 * oxb::sm_count(),
+                "gemm_bf16: trace must hold 8 int64 per SM");
+    p.trace = reinterpret_cast<unsigned long long*>(trace->data_ptr());
   }
+  const int mt_i = mt == 2 ? 2 : 1;
+  const bool fixup = s > 1 && ws.has_value() && ws->defined() && epi != oxb::kEpiRedF32;
   const bool routed = epi == oxb::kEpiRedF32 || epi == oxb::kEpiSlabBf16;
   p.my_rank = static_cast<int>(my_rank);
   if (!routed) {
     TORCH_CHECK(out.has_value(), "gemm_bf16: out required for store epilogues");
-    TORCH_CHECK(s == 1, "gemm_bf16: split-K needs the fp32 reduction epilogue");
+    TORCH_CHECK(s == 1 || fixup, "gemm_bf16: split-K needs the fp32 reduction epilogue or a workspace");
     TORCH_CHECK(out->stride(-1) == 1, "gemm_bf16: out must be row-major");
     if (epi == oxb::kEpiStoreF32) {
       TORCH_CHECK(out->scalar_type() == torch::kFloat32, "gemm_bf16: fp32 out expected");
@@ -126,7 +131,8 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
     p.ldc = out->stride(-2);
     p.c_group_stride = out->dim() == 3 ? out->stride(0) : 0;
   } else {
-    TORCH_CHECK(epi == oxb::kEpiRedF32 || s == 1, "gemm_bf16: the slab epilogue cannot split K");
+    TORCH_CHECK(epi == oxb::kEpiRedF32 || s == 1 || fixup,
+                "gemm_bf16: the slab epilogue splits K only with a workspace");
     TORCH_CHECK(!dst_ptrs.empty() && dst_ptrs.size() <= oxb::kMaxRanks, "gemm_bf16: 1..8 owners");
     for (size_t i = 0; i < dst_ptrs.size(); ++i) p.dst[i] = reinterpret_cast<float*>(dst_ptrs[i]);
     for (size_t i = 0; i < arrive_ptrs.size() && i < oxb::kMaxRanks; ++i)
@@ -144,8 +150,9 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
     p.reset_on_done = reinterpret_cast<uint32_t*>(reset_on_done->data_ptr());
     p.n_reset = static_cast<int>(reset_on_done->numel());
   }
-  int m_tiles = static_cast<int>((M + 127) / 128);
+  int m_tiles = static_cast<int>((M + 128 * mt_i - 1) / (128 * mt_i));
   if (group_counts.has_value() && group_counts->defined()) {
+    TORCH_CHECK(mt_i == 1 && !fixup, "gemm_bf16: grouped GEMMs use 128-row tiles without the split-K fix-up");
     p.group_counts = reinterpret_cast<const uint32_t*>(group_counts->data_ptr());
     p.n_groups = static_cast<int>(G);
     TORCH_CHECK(m_tiles_override > 0, "gemm_bf16: grouped mode needs the m-tile bound");
@@ -168,7 +175,21 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
   p.status = reinterpret_cast<int*>(status.data_ptr());
   p.m_tiles = m_tiles;
   p.splits = s;
-  oxb::launch_gemm_bf16(tmA, tmB, p, bn_i, cur_stream());
+  if (fixup) {
+    TORCH_CHECK(ws_tickets.has_value() && ws_tickets->defined(), "gemm_bf16: ws_tickets required with ws");
+    const int n_work = static_cast<int>((N + bn_i - 1) / bn_i) * m_tiles * s;
+    TORCH_CHECK(n_work <= oxb::sm_count(),
+                "gemm_bf16: split-K with the in-kernel fix-up needs one work item per SM at most (", n_work, ")");
+    TORCH_CHECK(ws->is_cuda() && ws->is_contiguous() &&
+                    static_cast<size_t>(ws->numel() * ws->element_size()) >=
+                        oxb::gemm_ws_bytes(static_cast<int>(M), static_cast<int>(N), bn_i, mt_i, s),
+                "gemm_bf16: split-K workspace too small");
+    TORCH_CHECK(ws_tickets->numel() >= oxb::gemm_ws_tickets(static_cast<int>(M), static_cast<int>(N), bn_i, mt_i),
+                "gemm_bf16: too few split-K tickets");
+    p.ws = reinterpret_cast<__nv_bfloat16*>(ws->data_ptr());
+    p.ws_tickets = reinterpret_cast<uint32_t*>(ws_tickets->data_ptr());
+  }
+  oxb::launch_gemm_bf16(tmA, tmB, p, bn_i, mt_i, cur_stream());
   check_launch("gemm_bf16");
 }
 
@@ -302,39 +323,6 @@ void paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
   check_launch("paged_decode");
 }
 
-void paged_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
-                   const Tensor& block_tables, const Tensor& tile_seq, const Tensor& tile_q0,
-                   const Tensor& q_start, const Tensor& q_lens, const Tensor& ctx_lens,
-                   const Tensor& out, int64_t n_tiles, int64_t window, double scale,
-                   const c10::optional<Tensor>& status) {
-  TORCH_CHECK(q.dim() == 3 && k_cache.dim() == 4, "paged_prefill: q [T,Hq,D], cache [blk,Hkv,16,D]");
-  oxb::PrefillAttnParams p{};
-  const int D = static_cast<int>(q.size(2));
-  TORCH_CHECK(D == 64 || D == 128, "paged_prefill: head_dim 64 or 128");
-  p.q = reinterpret_cast<const __nv_bfloat16*>(q.data_ptr());
-  p.q_stride = q.stride(0);
-  TORCH_CHECK(q.stride(1) == D && q.stride(2) == 1, "paged_prefill: q heads must be packed");
-  p.k_cache = reinterpret_cast<const __nv_bfloat16*>(k_cache.data_ptr());
-  p.v_cache = reinterpret_cast<const __nv_bfloat16*>(v_cache.data_ptr());
-  p.block_tables = block_tables.data_ptr<int>();
-  p.tile_seq = tile_seq.data_ptr<int>();
-  p.tile_q0 = tile_q0.data_ptr<int>();
-  p.q_start = q_start.data_ptr<int>();
-  p.q_lens = q_lens.data_ptr<int>();
-  p.ctx_lens = ctx_lens.data_ptr<int>();
-  p.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
-  p.out_stride = out.stride(0);
-  p.max_blocks = static_cast<int>(block_tables.size(1));
-  p.Hq = static_cast<int>(q.size(1));
-  p.Hkv = static_cast<int>(k_cache.size(1));
-  p.window = static_cast<int>(window);
-  p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
-  p.status = opt_ptr<int>(status);
-  p.num_blocks = p.status != nullptr ? static_cast<int>(k_cache.size(0)) : 0;
-  oxb::launch_paged_prefill(p, static_cast<int>(n_tiles), D, cur_stream());
-  check_launch("paged_prefill");
-}
-
 void paged_prefill_tc(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
                       const Tensor& block_tables, const Tensor& tile_seq, const Tensor& tile_q0,
                       const Tensor& q_start, const Tensor& q_lens, const Tensor& ctx_lens,
@@ -396,7 +384,7 @@ void finalize_norm(const c10::optional<Tensor>& acc, const c10::optional<Tensor>
                    const c10::optional<Tensor>& router_w, int64_t top_k, int64_t experts_per_rank,
                    double routed_scale, const std::vector<int64_t>& slab_ptrs,
                    const std::vector<int64_t>& meta_ptrs, const std::vector<int64_t>& cnt_ptrs,
-                   int64_t cap, int64_t my_rank) {
+                   int64_t cap, int64_t my_rank, int64_t spin_limit) {
   TORCH_CHECK(N % 8 == 0 && N <= 1024 * 8 * 4, "finalize_norm: N must be a multiple of 8 and <= 32768");
   oxb::FinalizeNormParams p{};
   p.acc = opt_ptr<float>(acc);
@@ -426,6 +414,7 @@ void finalize_norm(const c10::optional<Tensor>& acc, const c10::optional<Tensor>
   p.rows = static_cast<int>(rows);
   p.N = static_cast<int>(N);
   p.status = reinterpret_cast<int*>(status.data_ptr());
+  p.spin_limit = static_cast<uint32_t>(spin_limit > 0 ? spin_limit : 0);
   if (router_w.has_value() && router_w->defined()) {
     p.router_w = bf16_ptr(router_w);
     p.n_experts = static_cast<int>(router_w->size(0));
@@ -749,7 +738,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_fp8_block", &gemm_fp8_block);
   m.def("quant_act_fp8", &quant_act_fp8);
   m.def("paged_decode", &paged_decode);
-  m.def("paged_prefill", &paged_prefill);
   m.def("paged_prefill_tc", &paged_prefill_tc);
   m.def("finalize_norm", &finalize_norm);
   m.def("qkv_rope_append", &qkv_rope_append);

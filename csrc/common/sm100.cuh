@@ -81,12 +81,24 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
       : "memory");
   return ok;
 }
-// Bounded wait: true when the phase completed, false when the budget ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < OXB_SPIN_LIMIT; ++i) {
+// Bounded wait: true when the phase completed, false when the budget (`limit` tries) ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
+                                          uint32_t limit = OXB_SPIN_LIMIT) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }
   return false;
+}
+// Records an error code in the status word unless one is there already: the first failure of a
+// launch (for instance the peer-flag wait of the producer) is the one the host reports, not the
+// follow-up time-outs of the warps that depended on it.
+__device__ __forceinline__ void set_status_once(int* status, int code) {
+  if (status != nullptr) atomicCAS(status, 0, code);
+}
+// The spin budget a kernel uses: the value in its parameter block, or the compile-time default
+// when that is 0.
+__device__ __forceinline__ uint32_t spin_budget(uint32_t from_params) {
+  return from_params != 0 ? from_params : OXB_SPIN_LIMIT;
 }
 
 // ---------------------------------------------------------------------------

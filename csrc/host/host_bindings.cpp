@@ -157,6 +157,8 @@ PYBIND11_MODULE(oxb_host, m) {
       .def("prune_request", &Scheduler::prune_request, py::arg("id"), py::arg("block_scores"),
            py::arg("sink_blocks") = 1, py::arg("rolling_blocks") = 16, py::arg("budget_blocks") = 128)
       .def("inject_prefill_error", &Scheduler::inject_prefill_error)
+      .def("append_forced", &Scheduler::append_forced)
+      .def("take_events", &Scheduler::take_events)
       .def("schedule", &Scheduler::schedule)
       .def("update",
            [](Scheduler& s, const StepPlan& plan,

@@ -7,7 +7,7 @@
 namespace oxb {
 
 namespace {
-constexpr int kTileQ = 64;  // query rows per prefill-attention tile
+constexpr int kTileQ = 128;  // query rows per prefill-attention tile (one tcgen05 M tile)
 }
 
 Scheduler::Scheduler(const SchedulerConfig& cfg) : cfg_(cfg), pool_(cfg.num_blocks), radix_(&pool_) {}
@@ -110,11 +110,15 @@ void Scheduler::radix_pressure() {
 
 bool Scheduler::ensure_blocks(Request* r, int n_tokens, StepPlan* plan) {
   std::vector<std::pair<int, int>> cow;
-  if (r->table->advance(n_tokens, &cow)) {
+  auto record = [&]() {
     for (auto& c : cow) {
       plan->cow_src.push_back(c.first);
       plan->cow_dst.push_back(c.second);
+      cow_owner_.push_back(r->id);
     }
+  };
+  if (r->table->advance(n_tokens, &cow)) {
+    record();
     return true;
   }
   if (cfg_.enable_radix) {
@@ -122,10 +126,7 @@ bool Scheduler::ensure_blocks(Request* r, int n_tokens, StepPlan* plan) {
     radix_.evict(need);
     cow.clear();
     if (r->table->advance(n_tokens, &cow)) {
-      for (auto& c : cow) {
-        plan->cow_src.push_back(c.first);
-        plan->cow_dst.push_back(c.second);
-      }
+      record();
       return true;
     }
   }
@@ -152,6 +153,57 @@ void Scheduler::preempt(Request* r) {
   }
 }
 
+void Scheduler::abort(Request* r, const std::string& reason) {
+  deferred_.push_back({r->id, -1, true, reason});
+  r->table->release_all();
+  r->phase = Phase::Finished;
+  for (auto it = running_.begin(); it != running_.end(); ++it) {
+    if (it->get() == r) {
+      running_.erase(it);
+      return;
+    }
+  }
+}
+
+std::vector<TokenEvent> Scheduler::take_events() {
+  std::vector<TokenEvent> out;
+  out.swap(deferred_);
+  return out;
+}
+
+std::vector<TokenEvent> Scheduler::append_forced(int64_t id, const std::vector<int32_t>& forced) {
+  std::vector<TokenEvent> events;
+  for (auto& up : running_) {
+    Request* r = up.get();
+    if (r->id != id) continue;
+    if (r->phase != Phase::Decode || r->dropped != 0 || forced.empty()) return events;
+    r->drafts.clear();
+    const int cap = cfg_.max_blocks_per_seq * kTokensPerBlock;
+    for (int32_t tok : forced) {
+      if (r->generated() >= r->max_new_tokens || static_cast<int>(r->tokens.size()) + 1 >= cap) break;
+      r->tokens.push_back(tok);
+      bool stop = false;
+      if (!r->ignore_eos)
+        for (int32_t sid : r->stop_ids) stop |= sid == tok;
+      std::string reason;
+      if (stop)
+        reason = "stop";
+      else if (r->generated() >= r->max_new_tokens)
+        reason = "length";
+      events.push_back({r->id, tok, !reason.empty(), reason});
+      if (!reason.empty()) {
+        finish(r);
+        return events;
+      }
+    }
+    // the tokens after `computed` (the last sampled one and the forced ones) are prefilled as one
+    // chunk; its last row yields the logits of the next free choice
+    if (static_cast<int>(r->tokens.size()) - r->computed > 1) r->phase = Phase::Prefill;
+    return events;
+  }
+  return events;
+}
+
 void Scheduler::offer_to_radix(Request* r) {
   if (!cfg_.enable_radix || r->dropped > 0) return;  // pruned KV is not a reusable prefix
   const int n_full = std::min<int>(r->computed, static_cast<int>(r->tokens.size())) / kTokensPerBlock;
@@ -174,6 +226,7 @@ void Scheduler::finish(Request* r) {
 
 StepPlan Scheduler::schedule() {
   StepPlan plan;
+  cow_owner_.clear();
   radix_pressure();
 
   std::sort(running_.begin(), running_.end(),
@@ -187,6 +240,45 @@ StepPlan Scheduler::schedule() {
     int kind;  // 0 decode, 1 prefill chunk, 2 verify chunk
   };
   std::vector<Item> decodes, chunks;
+  // A preempted request may already sit in this step's lists (it was given blocks earlier in the
+  // pass): take it out again.
+  auto drop_item = [&](Request* v) {
+    auto gone = [v](const Item& it) { return it.r == v; };
+    decodes.erase(std::remove_if(decodes.begin(), decodes.end(), gone), decodes.end());
+    chunks.erase(std::remove_if(chunks.begin(), chunks.end(), gone), chunks.end());
+    // its copy-on-write pairs too: the destination blocks are free again and may be handed out
+    size_t w = 0;
+    for (size_t k = 0; k < cow_owner_.size(); ++k) {
+      if (cow_owner_[k] == v->id) continue;
+      plan.cow_src[w] = plan.cow_src[k];
+      plan.cow_dst[w] = plan.cow_dst[k];
+      cow_owner_[w++] = cow_owner_[k];
+    }
+    plan.cow_src.resize(w);
+    plan.cow_dst.resize(w);
+    cow_owner_.resize(w);
+  };
+  // Gets `n` more token slots for `r`, preempting younger requests (recompute style) while the
+  // pool is short. Returns false when r itself had to give way: it is then back in the waiting
+  // queue, or, when it was the only request left and still does not fit, aborted with `why`.
+  auto blocks_or_preempt = [&](Request* r, int n, const char* why) -> bool {
+    bool ok = ensure_blocks(r, n, &plan);
+    while (!ok) {
+      Request* victim = running_.back().get();
+      if (victim == r) {
+        drop_item(r);
+        if (running_.size() == 1)
+          abort(r, why);  // it has the whole pool to itself and still cannot grow
+        else
+          preempt(r);
+        return false;
+      }
+      drop_item(victim);
+      preempt(victim);
+      ok = ensure_blocks(r, n, &plan);
+    }
+    return true;
+  };
 
   // ---- 1. decode phase sequences (oldest first; the youngest is preempted when KV runs out) ----
   size_t i = 0;
@@ -200,17 +292,7 @@ StepPlan Scheduler::schedule() {
     const int limit = cfg_.max_blocks_per_seq * kTokensPerBlock;
     if (r->computed + need > limit) r->drafts.clear();
     const int n = 1 + static_cast<int>(r->drafts.size());
-    bool ok = ensure_blocks(r, n, &plan);
-    while (!ok) {
-      Request* victim = running_.back().get();
-      if (victim == r) {
-        preempt(r);
-        break;
-      }
-      preempt(victim);
-      ok = ensure_blocks(r, n, &plan);
-    }
-    if (!ok) continue;  // r itself was preempted; running_[i] is now the next request
+    if (!blocks_or_preempt(r, n, "length")) continue;  // running_[i] is now the next request
     if (n == 1)
       decodes.push_back({r, 1, 0});
     else
@@ -226,19 +308,29 @@ StepPlan Scheduler::schedule() {
   // ---- 2. continuing prefill chunks ----
   // While requests are waiting for a free slot's worth of budget, long prompts already in
   // flight take at most half of the step so that short newcomers are not stuck behind them.
+  // A chunk that finds no free block preempts younger requests like a decode row does:
+  // otherwise two half-prefilled prompts that together fill the pool would wait on each other
+  // for ever.
   const bool newcomers = !waiting_.empty() && static_cast<int>(running_.size()) < cfg_.max_num_seqs;
   int continuing_budget = budget;
   if (newcomers) continuing_budget = std::max(std::min(cfg_.chunk_min, budget), budget / 2);
-  for (size_t k = 0; k < running_.size() && budget > 0 && continuing_budget > 0; ++k) {
+  for (size_t k = 0; k < running_.size() && budget > 0 && continuing_budget > 0;) {
     Request* r = running_[k].get();
-    if (r->phase != Phase::Prefill) continue;
+    if (r->phase != Phase::Prefill) {
+      ++k;
+      continue;
+    }
     const int remaining = static_cast<int>(r->tokens.size()) - r->computed;
     const int c = std::min(remaining, std::min(budget, continuing_budget));
-    if (c <= 0) continue;
-    if (!ensure_blocks(r, c, &plan)) continue;
+    if (c <= 0) {
+      ++k;
+      continue;
+    }
+    if (!blocks_or_preempt(r, c, "prefill_error: prompt does not fit the KV pool")) continue;
     chunks.push_back({r, c, 1});
     budget -= c;
     continuing_budget -= c;
+    ++k;
   }
 
   // ---- 3. admission of waiting requests ----
@@ -260,6 +352,13 @@ StepPlan Scheduler::schedule() {
       r->table->release_all();
       r->computed = 0;
       r->cached_blocks = 0;
+      if (running_.empty()) {
+        // the whole pool is free and the first chunk still does not fit
+        std::unique_ptr<Request> owned = std::move(waiting_.front());
+        waiting_.pop_front();
+        deferred_.push_back({owned->id, -1, true, "prefill_error: prompt does not fit the KV pool"});
+        continue;
+      }
       break;  // no memory: stay queued
     }
     r->phase = Phase::Prefill;

@@ -102,6 +102,13 @@ class Scheduler {
   // back to the pool, positions stay absolute. Returns the kept block indices (empty: not pruned).
   std::vector<int> prune_request(int64_t id, const std::vector<float>& block_scores, int sink_blocks,
                                  int rolling_blocks, int budget_blocks);
+  // Grammar jump-forward: tokens that the grammar leaves no choice about are appended to a decoding
+  // request without sampling; they are computed as one prefill chunk in the next step, whose last
+  // row gives the logits of the next free choice (continuous_batching.rs:475,807,1328). Returns one
+  // event per appended token (the request may finish on a stop id or its length limit).
+  std::vector<TokenEvent> append_forced(int64_t id, const std::vector<int32_t>& forced);
+  // Events that schedule() produced (requests it had to end because they can never fit the pool).
+  std::vector<TokenEvent> take_events();
   // Fault hook: the next prefill chunk of this request fails (host-side fault injection).
   void inject_prefill_error(int64_t id, const std::string& msg);
 
@@ -124,6 +131,7 @@ class Scheduler {
  private:
   bool ensure_blocks(Request* r, int n_tokens, StepPlan* plan);
   void preempt(Request* r);
+  void abort(Request* r, const std::string& reason);
   void finish(Request* r);
   void offer_to_radix(Request* r);
   void radix_pressure();
@@ -134,6 +142,8 @@ class Scheduler {
   std::deque<std::unique_ptr<Request>> waiting_;
   std::vector<std::unique_ptr<Request>> running_;
   std::unordered_map<int64_t, std::string> prefill_faults_;
+  std::vector<TokenEvent> deferred_;
+  std::vector<int64_t> cow_owner_;  // request id of each copy-on-write pair of the plan being built
   uint64_t arrivals_ = 0;
   uint64_t preemptions_ = 0;
 };

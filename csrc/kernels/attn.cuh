@@ -49,9 +49,6 @@ struct PrefillAttnParams {
   int* status;
 };
 
-void launch_paged_prefill(const PrefillAttnParams& p, int n_tiles, int head_dim,
-                          cudaStream_t stream);
-
 void launch_paged_prefill_tc(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
                              const PrefillAttnParams& p, int n_tiles, int head_dim, int* status,
                              cudaStream_t stream);

@@ -21,6 +21,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "../common/device_info.h"
 #include "../common/sm100.cuh"
 #include "attn.cuh"
 
@@ -77,7 +78,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   const int tile = blockIdx.x;
   const int head = blockIdx.y;
   const int q0 = p.tile_q0[tile];
-  if (q0 % BQ != 0) return;  // the tile list is 64-row granular; this kernel works on 128-row tiles
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int seq = p.tile_seq[tile];
@@ -136,7 +136,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j & 1;
         if (j >= 2 && !mbar_wait(&kv_empty[s], ((j >> 1) - 1) & 1)) {
-          atomicExch(status, kStatusMbarTimeoutProducer);
+          set_status_once(status, kStatusMbarTimeoutProducer);
           ok = false;
           break;
         }
@@ -146,7 +146,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           const int pi = page0 + pg;
           int blk = pi < p.max_blocks ? bt[pi] : 0;
           if (p.num_blocks > 0 && static_cast<unsigned>(blk) >= static_cast<unsigned>(p.num_blocks)) {
-            atomicExch(status, kStatusBadIndex);
+            set_status_once(status, kStatusBadIndex);
             blk = 0;
           }
           const int row = (blk * p.Hkv + kvh) * 16;
@@ -158,7 +158,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           const int pi = page0 + pg;
           int blk = pi < p.max_blocks ? bt[pi] : 0;
           if (p.num_blocks > 0 && static_cast<unsigned>(blk) >= static_cast<unsigned>(p.num_blocks)) {
-            atomicExch(status, kStatusBadIndex);
+            set_status_once(status, kStatusBadIndex);
             blk = 0;
           }
           const int row = (blk * p.Hkv + kvh) * 16;
@@ -173,7 +173,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       constexpr uint32_t idesc_s = make_idesc(kFmtBF16, kFmtBF16, BQ, BKV);
       constexpr uint32_t idesc_o = make_idesc(kFmtBF16, kFmtBF16, BQ, D, 0, 1);  // V is MN-major
       bool ok = mbar_wait(q_full, 0);
-      if (!ok) atomicExch(status, kStatusMbarTimeoutMma);
+      if (!ok) set_status_once(status, kStatusMbarTimeoutMma);
       auto issue_s = [&](int j) -> bool {
         const int s = j & 1;
         if (!mbar_wait(&k_full[s], (j >> 1) & 1)) return false;
@@ -212,7 +212,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tc_commit(&kv_empty[s]);
         tc_commit(pv_done);
       }
-      if (!ok) atomicExch(status, kStatusMbarTimeoutMma);
+      if (!ok) set_status_once(status, kStatusMbarTimeoutMma);
     }
   } else {
     // ------------------------------ softmax + epilogue ------------------------
@@ -316,7 +316,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       if (!mbar_wait(pv_done, (n_tiles - 1) & 1)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
     }
-    if (!ok && lane == 0) atomicExch(status, kStatusMbarTimeoutEpilogue);
+    if (!ok && lane == 0) set_status_once(status, kStatusMbarTimeoutEpilogue);
     if (ok && n_tiles > 0) {
       tc_fence_after_sync();
       const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
@@ -353,12 +353,8 @@ template <int D>
 void launch_tc(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
                const PrefillAttnParams& p, int n_tiles, int* status, cudaStream_t stream) {
   using L = Smem<D>;
-  static bool configured = false;
   auto kern = prefill_tc_kernel<D>;
-  if (!configured) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
-    configured = true;
-  }
+  ensure_dynamic_smem(kern, L::kTotal);
   dim3 grid(n_tiles, p.Hq);
   kern<<<grid, kThreads, L::kTotal, stream>>>(tmQ, tmK, tmV, p, status);
 }

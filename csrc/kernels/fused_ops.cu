@@ -19,6 +19,7 @@
 //  embed_gather, fwht128 (fwht.cu:10-38), kv_block_copy, softcap.
 #include "fused_ops.cuh"
 
+#include "../common/device_info.h"
 #include "../common/sm100.cuh"
 
 namespace oxb {
@@ -65,9 +66,10 @@ __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const Fi
     if (threadIdx.x == 0) {
       int ok = 1;
       uint32_t it = 0;
+      const uint32_t limit = spin_budget(p.spin_limit);
       while (ld_acquire_sys_u32(p.arrive) < p.expected) {
-        if (++it > OXB_SPIN_LIMIT) {
-          atomicExch(p.status, kStatusPeerFlagTimeout);
+        if (++it > limit) {
+          set_status_once(p.status, kStatusPeerFlagTimeout);
           ok = 0;
           break;
         }
@@ -249,7 +251,7 @@ __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const Fi
         }
       int slot = static_cast<int>(atomicAdd(cnt + el, 1u));
       if (slot >= p.cap) {
-        atomicExch(p.status, kStatusBadIndex);
+        set_status_once(p.status, kStatusBadIndex);
         slot = -1;
       } else {
         MoeRowMeta m;
@@ -370,7 +372,7 @@ __global__ void __launch_bounds__(256) qkv_rope_append_kernel(const QkvRopeParam
 
   const long long slot = p.slot_mapping[tok];
   const bool store_kv = slot >= 0 && slot < p.num_slots;
-  if (slot >= p.num_slots && threadIdx.x == 0) atomicExch(p.status, kStatusBadIndex);
+  if (slot >= p.num_slots && threadIdx.x == 0) set_status_once(p.status, kStatusBadIndex);
   const long long blk = slot >> 4;
   const int off = static_cast<int>(slot & 15);
 
@@ -543,19 +545,10 @@ void launch_finalize_norm(const FinalizeNormParams& p, cudaStream_t stream) {
   if (threads > kNormMaxThreads) threads = kNormMaxThreads;
   if (threads < 32) threads = 32;
   const size_t smem = p.router_w != nullptr ? static_cast<size_t>(p.N) * sizeof(float) : 0;
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
-    cudaFuncSetAttribute(finalize_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         static_cast<int>(smem));
-    configured = smem;
-  }
-  static int max_ctas = 0;
-  if (max_ctas == 0) {
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    max_ctas = 2 * sms;  // two 1024-thread CTAs are resident per SM
-  }
+  ensure_dynamic_smem(finalize_norm_kernel, smem);
+  // a CTA loops over rows, so any grid is correct; two CTAs per SM keep a second row's loads in
+  // flight where registers allow two resident CTAs, and cost nothing where they do not
+  const int max_ctas = 2 * sm_count();
   const int grid = p.rows < max_ctas ? p.rows : max_ctas;
   finalize_norm_kernel<<<grid, threads, smem, stream>>>(p);
 }
@@ -563,12 +556,7 @@ void launch_finalize_norm(const FinalizeNormParams& p, cudaStream_t stream) {
 void launch_qkv_rope_append(const QkvRopeParams& p, cudaStream_t stream) {
   if (p.M <= 0) return;
   const size_t smem = static_cast<size_t>(p.Hq + 2 * p.Hkv) * p.D * sizeof(float);
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
-    cudaFuncSetAttribute(qkv_rope_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         static_cast<int>(smem));
-    configured = smem;
-  }
+  ensure_dynamic_smem(qkv_rope_append_kernel, smem);
   qkv_rope_append_kernel<<<p.M, 256, smem, stream>>>(p);
 }
 
@@ -576,7 +564,7 @@ void launch_swiglu(const SwigluParams& p, cudaStream_t stream) {
   const long long total = static_cast<long long>(p.M) * p.I / 4;
   if (total <= 0) return;
   int blocks = static_cast<int>((total + 255) / 256);
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   swiglu_kernel<<<blocks, 256, 0, stream>>>(p);
 }
 
@@ -591,13 +579,13 @@ void launch_cast_acc_bf16(float* acc, const __nv_bfloat16* bias, __nv_bfloat16* 
   const long long total = static_cast<long long>(M) * N / 4;
   if (total <= 0) return;
   int blocks = static_cast<int>((total + 255) / 256);
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   cast_acc_bf16_kernel<<<blocks, 256, 0, stream>>>(acc, bias, out, M, N, ldo);
 }
 
 void launch_fwht128(float* x, long long n_blocks, cudaStream_t stream) {
   if (n_blocks <= 0) return;
-  int blocks = n_blocks > 148 * 8 ? 148 * 8 : static_cast<int>(n_blocks);
+  int blocks = n_blocks > sm_count() * 8 ? sm_count() * 8 : static_cast<int>(n_blocks);
   fwht128_kernel<<<blocks, 128, 0, stream>>>(x, n_blocks);
 }
 
@@ -612,7 +600,7 @@ void launch_kv_block_copy(__nv_bfloat16* k_cache, __nv_bfloat16* v_cache, const 
 void launch_softcap(float* logits, long long n, float cap, cudaStream_t stream) {
   if (n <= 0) return;
   int blocks = static_cast<int>((n + 255) / 256);
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   softcap_kernel<<<blocks, 256, 0, stream>>>(logits, n, cap);
 }
 

@@ -39,6 +39,7 @@ struct FinalizeNormParams {
   const int* out_row_map;   // optional [rows]: destination row (replaces out_row_off + r); < 0 = skip
   int rows, N;
   int* status;
+  uint32_t spin_limit;      // iterations of the bounded arrival wait (0 = OXB_SPIN_LIMIT)
   // --- MoE dispatch mode (router_w != nullptr): the normed row goes only to the ranks that own
   //     its top-k experts, into that expert's receive slab, instead of to out[] ---
   const __nv_bfloat16* router_w;  // [n_experts, N]

@@ -1,12 +1,22 @@
 // tcgen05 bf16 GEMM for sm_100a:  C[g][M,N] (+)= A[g][M,K] * B[g][N,K]^T, fp32 accumulation in TMEM.
 //
-// Persistent kernel, one CTA per SM. A work item is one 128 x BN output tile over a slice of K
-// (split-K); CTA c takes items c, c + grid, c + 2 grid, ... Warp roles: warp 0 = TMA producer,
-// warp 1 = TMEM owner + MMA issuer, warps 2..5 = epilogue (one TMEM lane quarter each). Operands
-// are staged by TMA into a ring of 128B-swizzled shared-memory tiles; the accumulator is double
-// buffered in TMEM (2 x BN columns), so the epilogue of item i drains one buffer while the MMAs
-// of item i+1 fill the other. Completion is tracked by mbarriers and every wait is bounded (a
-// spin that runs out writes a status code and unwinds).
+// Persistent kernel, one CTA per SM. A work item is one (128 * MT) x BN output tile over a slice
+// of K (split-K); CTA c takes items c, c + grid, c + 2 grid, ... Warp roles: warp 0 = TMA
+// producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 = epilogue (one TMEM lane quarter each).
+// Operands are staged by TMA into a ring of 128B-swizzled shared-memory tiles. With MT = 1 the
+// accumulator is double buffered in TMEM (2 x BN columns), so the epilogue of item i drains one
+// buffer while the MMAs of item i+1 fill the other. Completion is tracked by mbarriers and every
+// wait is bounded (a spin that runs out writes a status code and unwinds).
+//
+// Decode shapes (M <= 256 rows against a large weight matrix) are bound by how many *distinct*
+// weight bytes every SM keeps in flight, not by FLOPs: a CTA that shares its weight tile with a
+// neighbour (two 128-row M tiles) streams the same bytes twice through the machine. MT = 2 keeps
+// both row halves with the CTA that loads the weight tile (two accumulators fed from one B stage,
+// up to 512 TMEM columns), and split-K spreads the tiles over all SMs. Split partial tiles of the
+// store / SwiGLU / slab epilogues are combined inside the kernel: every split stores its partial
+// as bf16 into its own slab of a workspace, the splits of a tile meet at a ticket, and each of
+// them sums a share of the tile's columns over all slabs and runs the epilogue on that share
+// (the launch is cooperative, so the CTAs that wait for each other are co-resident).
 //
 // Fused collectives, all issued by this kernel over NVLink peer mappings:
 //  * kEpiRedF32 routes each output row to the fp32 accumulator of the rank that owns it
@@ -31,6 +41,7 @@
 // (oxide-backend-cuda/src/nccl.rs:18-29) is a no-op.
 #include "gemm_bf16.cuh"
 
+#include "../common/device_info.h"
 #include "../common/sm100.cuh"
 
 namespace oxb {
@@ -49,6 +60,11 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 // Relaxed on purpose: the caller issues ONE system-scope fence and then signals every peer; a
 // release on each signal would wait a full NVLink round trip per peer, one after the other.
 __device__ __forceinline__ void red_relaxed_sys_add(uint32_t* p, uint32_t v) {
@@ -59,20 +75,68 @@ __device__ __forceinline__ void red_add_v4_f32(float* p, float a, float b, float
                "f"(d)
                : "memory");
 }
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void stamp(const GemmParams& p, int slot) {
+  if (p.trace != nullptr) p.trace[static_cast<size_t>(blockIdx.x) * 8 + slot] = global_ns();
+}
+// SiLU / tanh-GELU on the special-function unit (approximate reciprocal and tanh: the result is
+// rounded to bf16 anyway); a full-precision divide and tanhf cost tens of instructions per value in
+// an epilogue that only one warp per scheduler runs.
 __device__ __forceinline__ float act_fn(float x, int act) {
-  if (act == 0) return x / (1.f + __expf(-x));
-  return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+  if (act == 0) return __fdividef(x, 1.f + __expf(-x));
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+  return 0.5f * x * (1.f + t);
+}
+
+// NG groups of 32 accumulator columns of this thread's TMEM lane: all loads are issued before the
+// one wait (a load-wait pair costs a few hundred cycles).
+template <int NG>
+__device__ __forceinline__ void tmem_load_cols(uint32_t taddr, float (&a)[NG * 32]) {
+  uint32_t r[NG][32];
+#pragma unroll
+  for (int g = 0; g < NG; ++g) tmem_ld_32x32b_x32(taddr + g * 32, r[g]);
+  tmem_ld_wait();
+#pragma unroll
+  for (int g = 0; g < NG; ++g)
+#pragma unroll
+    for (int j = 0; j < 32; ++j) a[g * 32 + j] = __uint_as_float(r[g][j]);
+}
+// The same columns summed over the bf16 slabs of every split: `src` = this thread's row in the
+// first 8-column group of the first split ([col / 8][128 rows][8] layout, 1024 elements per group).
+template <int NG>
+__device__ __forceinline__ void ws_load_cols(const __nv_bfloat16* src, int splits, size_t split_stride,
+                                             float (&a)[NG * 32]) {
+#pragma unroll
+  for (int j = 0; j < NG * 32; ++j) a[j] = 0.f;
+#pragma unroll 2
+  for (int s = 0; s < splits; ++s, src += split_stride) {
+    uint4 x[NG * 4];
+#pragma unroll
+    for (int g = 0; g < NG * 4; ++g) x[g] = __ldcg(reinterpret_cast<const uint4*>(src + g * 1024));
+#pragma unroll
+    for (int g = 0; g < NG * 4; ++g) {
+      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&x[g]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[g * 8 + j] += __bfloat162float(e[j]);
+    }
+  }
 }
 
 // Waits until the source counters [s_lo, s_hi] reach the expected value; `waiters` is the number
 // of such waits the whole grid performs, the last of them re-arms the counters.
 __device__ bool wait_sources(const GemmParams& p, int s_lo, int s_hi, uint32_t waiters) {
   bool ok = true;
+  const uint32_t limit = spin_budget(p.spin_limit);
   for (int s = s_lo; s <= s_hi && ok; ++s) {
     uint32_t it = 0;
     while (ld_acquire_sys(p.ag_flags + s) < p.ag_expected) {
-      if (++it > OXB_SPIN_LIMIT) {
-        atomicExch(p.status, kStatusPeerFlagTimeout);
+      if (++it > limit) {
+        set_status_once(p.status, kStatusPeerFlagTimeout);
         ok = false;
         break;
       }
@@ -89,9 +153,9 @@ __device__ bool wait_sources(const GemmParams& p, int s_lo, int s_hi, uint32_t w
   return ok;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MT>
 struct SmemLayout {
-  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kABytes = MT * BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageOffset = STAGES * (kABytes + kBBytes);
   static constexpr int kBarOffset = kStageOffset + kStageBytes;
@@ -99,15 +163,15 @@ struct SmemLayout {
 };
 
 struct WorkItem {
-  int group, m0, rows, n0, kb0, nkb;
+  int group, m0, rows, n0, kb0, nkb, tile, z;
   bool valid;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmParams p) {
-  using L = SmemLayout<BN, STAGES>;
+  using L = SmemLayout<BN, STAGES, MT>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem =
       reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -119,7 +183,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tmem_full = empty + STAGES;  // [2]
   uint64_t* tmem_empty = tmem_full + 2;  // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
-  int* s_counts = reinterpret_cast<int*>(tmem_slot + 2);  // [0] ok flag, [1..] first m tile per group
+  int* s_misc = reinterpret_cast<int*>(tmem_slot + 2);  // [0] start-up ok, [1] tile barrier ok
+  int* s_counts = s_misc + 2;                           // first m tile per group, grouped mode
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -128,11 +193,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int n_tiles = (p.N + BN - 1) / BN;
   const int m_tiles = p.m_tiles;
   const int n_work = n_tiles * m_tiles * p.splits;
+  const uint32_t spin = spin_budget(p.spin_limit);
 
-  constexpr uint32_t kAccCols = BN < 32 ? 32 : BN;
-  constexpr uint32_t kTmemCols = 2 * kAccCols;
+  constexpr uint32_t kAccCols = BN < 32 ? 32 : BN;   // TMEM columns of one 128-row accumulator
+  constexpr uint32_t kItemCols = MT * kAccCols;      // ... of one work item
+  constexpr uint32_t kBufs = 2 * kItemCols <= 512 ? 2 : 1;
+  constexpr uint32_t kTmemCols = kBufs * kItemCols;
+  static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM allocation");
 
   if (threadIdx.x == 0) {
+    stamp(p, 0);
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
 #pragma unroll
@@ -151,12 +221,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (p.ag_flags != nullptr) ok = wait_sources(p, 0, p.ag_n_src - 1, gridDim.x) ? 1 : 0;
       int acc = 0;
       for (int e = 0; e < p.n_groups; ++e) {
-        s_counts[1 + e] = acc;  // first m tile of group e
+        s_counts[e] = acc;  // first m tile of group e
         acc += (static_cast<int>(__ldcg(p.group_counts + e)) + BM - 1) / BM;
       }
-      s_counts[1 + p.n_groups] = acc;
+      s_counts[p.n_groups] = acc;
     }
-    s_counts[0] = ok;
+    s_misc[0] = ok;
+    s_misc[1] = 1;
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -166,7 +237,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const bool all_ok = s_counts[0] != 0;
+  const bool all_ok = s_misc[0] != 0;
 
   // work item w -> tile coordinates; consecutive items share the weight tile (m fastest)
   auto decode = [&](int w) -> WorkItem {
@@ -174,21 +245,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int mt = w % m_tiles;
     const int rest = w / m_tiles;
     const int nt = rest % n_tiles;
-    const int z = rest / n_tiles;
+    it.z = rest / n_tiles;
+    it.tile = nt * m_tiles + mt;
     it.n0 = nt * BN;
-    it.kb0 = z * p.kb_per_split;
+    it.kb0 = it.z * p.kb_per_split;
     it.nkb = total_kb - it.kb0;
     if (it.nkb > p.kb_per_split) it.nkb = p.kb_per_split;
     it.group = 0;
-    it.m0 = mt * BM;
+    it.m0 = mt * BM * MT;
     it.rows = p.M;
     it.valid = all_ok && it.nkb > 0;
     if (grouped) {
       it.valid = false;
       for (int e = 0; e < p.n_groups; ++e) {
-        if (mt >= s_counts[1 + e] && mt < s_counts[2 + e]) {
+        if (mt >= s_counts[e] && mt < s_counts[e + 1]) {
           it.group = e;
-          it.m0 = (mt - s_counts[1 + e]) * BM;
+          it.m0 = (mt - s_counts[e]) * BM;
           it.rows = static_cast<int>(__ldcg(p.group_counts + e));
           it.valid = all_ok && it.nkb > 0;
           break;
@@ -200,54 +272,64 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
-      uint32_t iter = 0;  // k-block counter across all items of this CTA
-      bool ok = true;
-      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
-        const WorkItem it = decode(w);
-        bool need_wait = p.ag_flags != nullptr && !grouped;
-        if (!it.valid) {
-          // keep the waiter count of the grid exact: an empty item still passes the gate
-          if (need_wait) wait_sources(p, 0, -1, static_cast<uint32_t>(n_work));
-          continue;
+    // The whole warp runs this loop. TMA copies issued by one thread complete about one per memory
+    // round trip (measured: the rate of a single issuing thread does not grow with the number of
+    // stages in flight, it grows with the number of issuing threads), so every copy of a stage
+    // has its own lane, and consecutive stages use different lanes: lane = stage * 4 + copy.
+    constexpr int kBOps = (BN + 127) / 128;  // tile-major weights: one box per 128 weight rows
+    uint32_t iter = 0;  // k-block counter across all items of this CTA
+    bool ok = true;
+    for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+      const WorkItem it = decode(w);
+      bool need_wait = p.ag_flags != nullptr && !grouped;
+      if (!it.valid) {
+        // keep the waiter count of the grid exact: an empty item still passes the gate
+        if (need_wait && lane == 0) wait_sources(p, 0, -1, static_cast<uint32_t>(n_work));
+        continue;
+      }
+      for (int kb = 0; kb < it.nkb && ok; ++kb, ++iter) {
+        const int s = iter % STAGES;
+        const uint32_t ph = (iter / STAGES) & 1;
+        if (iter >= STAGES && !mbar_wait(&empty[s], ph ^ 1, spin)) ok = false;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) set_status_once(p.status, kStatusMbarTimeoutProducer);
+          break;
         }
-        for (int kb = 0; kb < it.nkb && ok; ++kb, ++iter) {
-          const int s = iter % STAGES;
-          const uint32_t ph = (iter / STAGES) & 1;
-          if (iter >= STAGES && !mbar_wait(&empty[s], ph ^ 1)) {
-            atomicExch(p.status, kStatusMbarTimeoutProducer);
-            ok = false;
-            break;
-          }
-          mbar_arrive_expect_tx(&full[s], L::kABytes + L::kBBytes);
-          // weights first: they do not depend on any peer
-          if (p.b_tiled) {
-            // tile-major weights: tile index = (n / 128) * total_kb + kb, box = 128 x 64 (or the
-            // 64-row half of a tile for BN = 64)
-            constexpr int kRowsPerLoad = BN < 128 ? BN : 128;
-#pragma unroll
-            for (int j = 0; j < (BN + 127) / 128; ++j)
-              tma_load_3d(sB + s * L::kBBytes + j * 16384, &tmB, &full[s], 0, BN < 128 ? (it.n0 & 127) : 0,
-                          ((it.n0 >> 7) + j) * total_kb + it.kb0 + kb);
-            (void)kRowsPerLoad;
-          } else {
-            tma_load_3d(sB + s * L::kBBytes, &tmB, &full[s], (it.kb0 + kb) * BK, it.n0, it.group);
-          }
-          if (need_wait) {
+        if (lane == 0) mbar_arrive_expect_tx(&full[s], L::kABytes + L::kBBytes);
+        __syncwarp();
+        const int op = lane - (s & 7) * 4;  // which copy of this stage this lane issues (0..3), if any
+        // weights first: they do not depend on any peer
+        if (p.b_tiled) {
+          // tile-major weights: tile index = (n / 128) * total_kb + kb, box = 128 x 64 (or the
+          // 64-row half of a tile for BN = 64)
+          if (op >= 0 && op < kBOps)
+            tma_load_3d(sB + s * L::kBBytes + op * 16384, &tmB, &full[s], 0, BN < 128 ? (it.n0 & 127) : 0,
+                        ((it.n0 >> 7) + op) * total_kb + it.kb0 + kb);
+        } else if (op == 0) {
+          tma_load_3d(sB + s * L::kBBytes, &tmB, &full[s], (it.kb0 + kb) * BK, it.n0, it.group);
+        }
+        if (need_wait) {
+          int src_ok = 1;
+          if (lane == 0) {
             int s_lo = 0, s_hi = p.ag_n_src - 1;  // rows_per_src <= 0: rows are not grouped by source
             if (p.ag_rows_per_src > 0) {
-              const int m_end = it.m0 + BM < it.rows ? it.m0 + BM : it.rows;
+              const int m_end = it.m0 + BM * MT < it.rows ? it.m0 + BM * MT : it.rows;
               s_lo = it.m0 / p.ag_rows_per_src;
               s_hi = (m_end - 1) / p.ag_rows_per_src;
               if (s_hi >= p.ag_n_src) s_hi = p.ag_n_src - 1;
               if (s_lo > s_hi) s_lo = s_hi;
             }
-            ok = wait_sources(p, s_lo, s_hi, static_cast<uint32_t>(n_work));
-            need_wait = false;
-            if (!ok) break;
+            src_ok = wait_sources(p, s_lo, s_hi, static_cast<uint32_t>(n_work)) ? 1 : 0;
           }
-          tma_load_3d(sA + s * L::kABytes, &tmA, &full[s], (it.kb0 + kb) * BK, it.m0, it.group);
+          ok = __shfl_sync(0xffffffffu, src_ok, 0) != 0;
+          need_wait = false;
+          if (!ok) break;
         }
+        // rows past M read as zeros (the box is filled in full either way)
+        if (op >= 2 && op < 2 + MT)
+          tma_load_3d(sA + s * L::kABytes + (op - 2) * (BM * BK * 2), &tmA, &full[s], (it.kb0 + kb) * BK,
+                      it.m0 + (op - 2) * BM, it.group);
       }
     }
   } else if (warp == 1) {
@@ -259,20 +341,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
         const WorkItem it = decode(w);
         if (!it.valid) continue;
-        const uint32_t buf = t & 1;
-        // the epilogue must have drained this accumulator buffer (two items ago)
-        if (t >= 2 && !mbar_wait(&tmem_empty[buf], ((t >> 1) & 1) ^ 1)) {
-          atomicExch(p.status, kStatusMbarTimeoutMma);
+        const uint32_t buf = t % kBufs;
+        const uint32_t use = t / kBufs;
+        // the epilogue must have drained this accumulator buffer (kBufs items ago)
+        if (use >= 1 && !mbar_wait(&tmem_empty[buf], (use & 1) ^ 1, spin)) {
+          set_status_once(p.status, kStatusMbarTimeoutMma);
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * kAccCols;
+        const uint32_t d_tmem = tmem_base + buf * kItemCols;
         for (int kb = 0; kb < it.nkb; ++kb, ++iter) {
           const int s = iter % STAGES;
           const uint32_t ph = (iter / STAGES) & 1;
-          if (!mbar_wait(&full[s], ph)) {
-            atomicExch(p.status, kStatusMbarTimeoutMma);
+          if (!mbar_wait(&full[s], ph, spin)) {
+            set_status_once(p.status, kStatusMbarTimeoutMma);
             ok = false;
             break;
           }
@@ -281,8 +364,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t b_addr = smem_u32(sB + s * L::kBBytes);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            tc_mma_f16(d_tmem, make_desc_kmajor_sw128(a_addr + k * 32),
-                       make_desc_kmajor_sw128(b_addr + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
+            const uint64_t db = make_desc_kmajor_sw128(b_addr + k * 32);
+#pragma unroll
+            for (int h = 0; h < MT; ++h)
+              tc_mma_f16(d_tmem + h * kAccCols, make_desc_kmajor_sw128(a_addr + h * (BM * BK * 2) + k * 32),
+                         db, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           tc_commit(&empty[s]);  // frees this smem stage once the MMAs above have read it
         }
@@ -293,160 +379,212 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     // ------------------------------ epilogue ----------------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
-    if (p.prefetch_bytes > 0 && warp == 5) {
-      // this CTA's slice of the range, in 4 KB requests spread over the lanes
-      constexpr long long kChunk = 4096;
-      const long long n_chunks = (p.prefetch_bytes + kChunk - 1) / kChunk;
-      const char* base = static_cast<const char*>(p.prefetch_ptr);
-      for (long long c = static_cast<long long>(blockIdx.x) * 32 + lane; c < n_chunks;
-           c += static_cast<long long>(gridDim.x) * 32) {
-        const long long off = c * kChunk;
-        const long long left = p.prefetch_bytes - off;
-        const uint32_t sz = static_cast<uint32_t>(left < kChunk ? left : kChunk);
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"(sz) : "memory");
-      }
-    }
     uint8_t* stage = sStage + static_cast<size_t>(q) * 32 * kStagePitch;
     uint8_t* my_row = stage + static_cast<size_t>(lane) * kStagePitch;
     const bool vec_ok = (p.N & 7) == 0;
+    const bool fix = p.ws != nullptr && p.splits > 1;  // split-K combined in this kernel
+    const bool swiglu = p.epi == kEpiSwigluBf16;
+    const int n_total = swiglu ? (p.N >> 1) : p.N;  // output row length
+    const int out_cols = swiglu ? BN / 2 : BN;      // output columns of one tile
+    const int units_per_half = (out_cols + kStageCols - 1) / kStageCols;
+    const int n_units = MT * units_per_half;        // 64-output-column x 128-row pieces of a tile
+    const size_t ws_half = static_cast<size_t>(BN) * 128;  // bf16 elements of one row half of a slab
     uint32_t t = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
       const WorkItem it = decode(w);
       if (!it.valid) continue;
-      const uint32_t buf = t & 1;
-      if (ok && !mbar_wait(&tmem_full[buf], (t >> 1) & 1)) {
-        if (lane == 0) atomicExch(p.status, kStatusMbarTimeoutEpilogue);
+      const uint32_t buf = t % kBufs;
+      const uint32_t use = t / kBufs;
+      if (ok && !mbar_wait(&tmem_full[buf], use & 1, spin)) {
+        if (lane == 0) set_status_once(p.status, kStatusMbarTimeoutEpilogue);
         ok = false;
       }
       ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective
       if (!ok) break;
       tc_fence_after_sync();
-      const int row = it.m0 + q * 32 + lane;
-      const bool row_ok = row < it.rows;
+      if (t == 0 && warp == 2 && lane == 0) stamp(p, 1);
       const int n0 = it.n0;
       const int group = it.group;
       const __nv_bfloat16* bias =
           p.bias != nullptr ? p.bias + static_cast<long long>(group) * p.N : nullptr;
-      const uint32_t lane_addr = tmem_base + buf * kAccCols + (static_cast<uint32_t>(q * 32) << 16);
+      const uint32_t lane_addr = tmem_base + buf * kItemCols + (static_cast<uint32_t>(q * 32) << 16);
+      // this thread's row inside a slab of the split-K workspace: [half][col / 8][128 rows][8]
+      const __nv_bfloat16* ws_tile =
+          fix ? p.ws + static_cast<size_t>(it.tile) * p.splits * MT * ws_half + (q * 32 + lane) * 8 : nullptr;
 
-      if (p.epi == kEpiRedF32) {
-        int owner = 0, row_local = row;
-        float wgt = 1.f;
-        if (p.row_meta != nullptr) {
-          if (row_ok) {
-            const RowMeta m = p.row_meta[static_cast<long long>(group) * p.meta_group_stride + row];
-            owner = m.rank;
-            row_local = m.row;
-            wgt = m.weight;
+      if (fix) {
+        // ---- phase A: this split's partial tile -> its slab (bf16; a warp's 32 rows of one
+        // 8-column group are 512 contiguous bytes), then meet the other splits of the tile ----
+        __nv_bfloat16* slab = const_cast<__nv_bfloat16*>(ws_tile) + static_cast<size_t>(it.z) * MT * ws_half;
+#pragma unroll 1
+        for (int h = 0; h < MT; ++h) {
+#pragma unroll 1
+          for (int c = 0; c < BN / 64; ++c) {
+            float a[64];
+            tmem_load_cols<2>(lane_addr + h * kAccCols + c * 64, a);
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              uint4 o4;
+              o4.x = pack_bf16x2(a[g * 8], a[g * 8 + 1]);
+              o4.y = pack_bf16x2(a[g * 8 + 2], a[g * 8 + 3]);
+              o4.z = pack_bf16x2(a[g * 8 + 4], a[g * 8 + 5]);
+              o4.w = pack_bf16x2(a[g * 8 + 6], a[g * 8 + 7]);
+              __stcg(reinterpret_cast<uint4*>(slab + h * ws_half + static_cast<size_t>(c * 8 + g) * 1024), o4);
+            }
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          stamp(p, 2);
+          uint32_t* arrived = p.ws_tickets + 2 * it.tile;
+          atomicAdd(arrived, 1u);
+          int met = 1;
+          uint32_t n = 0;
+          while (ld_acquire_gpu(arrived) < static_cast<uint32_t>(p.splits)) {
+            if (++n > spin) {
+              set_status_once(p.status, kStatusPeerFlagTimeout);
+              met = 0;
+              break;
+            }
+          }
+          s_misc[1] = met;
+          stamp(p, 3);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (s_misc[1] == 0) {
+          ok = false;
+          break;
+        }
+      }
+
+      // 64 accumulator columns [col, col + 64) of row half h for this thread's row: straight from
+      // TMEM, or summed over the slabs of every split
+      auto load_acc = [&](int h, int col, float (&a)[64]) __attribute__((always_inline)) {
+        if (!fix)
+          tmem_load_cols<2>(lane_addr + h * kAccCols + col, a);
+        else
+          ws_load_cols<2>(ws_tile + h * ws_half + static_cast<size_t>(col >> 3) * 1024, p.splits, MT * ws_half, a);
+      };
+
+      // with the fix-up the 64-column units of the tile are dealt out over its splits
+#pragma unroll 1
+      for (int u = fix ? it.z : 0; u < n_units; u += fix ? p.splits : 1) {
+        const int h = u / units_per_half;
+        const int oc = (u - h * units_per_half) * kStageCols;  // first output column inside the tile
+        const int width = out_cols - oc < kStageCols ? out_cols - oc : kStageCols;  // 32 or 64
+        const int row = it.m0 + h * BM + q * 32 + lane;
+        const bool row_ok = row < it.rows;
+
+        if (p.epi == kEpiRedF32) {
+          int owner = 0, row_local = row;
+          float wgt = 1.f;
+          if (p.row_meta != nullptr) {
+            if (row_ok) {
+              const RowMeta m = p.row_meta[static_cast<long long>(group) * p.meta_group_stride + row];
+              owner = m.rank;
+              row_local = m.row;
+              wgt = m.weight;
+            }
+          } else {
+            owner = row / p.rows_per_owner;
+            if (owner >= p.n_owners) owner = p.n_owners - 1;
+            row_local = row - owner * p.rows_per_owner;
+          }
+          float* red_base = nullptr;
+          // avoid a dynamically indexed parameter array (it would be copied to local memory)
+#pragma unroll
+          for (int o = 0; o < kMaxRanks; ++o)
+            if (o == owner) red_base = p.dst[o];
+          float a[64];
+          load_acc(h, oc, a);
+          const int col0 = n0 + oc;
+          if (row_ok && col0 < p.N && red_base != nullptr) {
+            float* d = red_base + static_cast<long long>(row_local) * p.dst_ld + col0;
+#pragma unroll
+            for (int j = 0; j < 64; j += 4) {
+              if (vec_ok && col0 + j + 4 <= p.N) {
+                red_add_v4_f32(d + j, wgt * a[j], wgt * a[j + 1], wgt * a[j + 2], wgt * a[j + 3]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  if (col0 + j + e < p.N) atomicAdd(d + j + e, wgt * a[j + e]);
+              }
+            }
+          }
+        } else if (p.epi == kEpiStoreF32) {
+          float a[64];
+          load_acc(h, oc, a);
+          const int col0 = n0 + oc;
+          if (row_ok && col0 < p.N) {
+            float* d = reinterpret_cast<float*>(p.C) + static_cast<long long>(group) * p.c_group_stride +
+                       static_cast<long long>(row) * p.ldc + col0;
+            const bool vec = (p.ldc & 3) == 0 && vec_ok;
+#pragma unroll
+            for (int j = 0; j < 64; j += 4) {
+              float o[4] = {a[j], a[j + 1], a[j + 2], a[j + 3]};
+              if (bias != nullptr) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  if (col0 + j + e < p.N) o[e] += __bfloat162float(bias[col0 + j + e]);
+              }
+              if (vec && col0 + j + 4 <= p.N) {
+                *reinterpret_cast<float4*>(d + j) = make_float4(o[0], o[1], o[2], o[3]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  if (col0 + j + e < p.N) d[j + e] = o[e];
+              }
+            }
           }
         } else {
-          owner = row / p.rows_per_owner;
-          if (owner >= p.n_owners) owner = p.n_owners - 1;
-          row_local = row - owner * p.rows_per_owner;
-        }
-        float* red_base = nullptr;
-        // avoid a dynamically indexed parameter array (it would be copied to local memory)
-#pragma unroll
-        for (int o = 0; o < kMaxRanks; ++o)
-          if (o == owner) red_base = p.dst[o];
+          // ---- bf16 outputs (plain store, SwiGLU, routed slab store): accumulators -> registers
+          // -> a padded shared-memory tile -> row-contiguous 16-byte stores, 64 output columns per
+          // round, so local HBM and NVLink both see full lines. Each warp stages and writes only
+          // its own 32 rows; __syncwarp is all it needs.
+          const int oc0 = (swiglu ? (n0 >> 1) : n0) + oc;  // first output column of this unit
+          const bool out_vec =
+              (n_total & 7) == 0 && (((p.epi == kEpiSlabBf16) ? p.dst_ld : p.ldc) & 7) == 0;
+          if (swiglu) {
+            // 32 outputs come from 64 accumulator columns: 32 gate | 32 up
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(lane_addr + c * 32, r);
-          tmem_ld_wait();
-          const int col0 = n0 + c * 32;
-          if (!row_ok || col0 >= p.N || red_base == nullptr) continue;
-          float* d = red_base + static_cast<long long>(row_local) * p.dst_ld + col0;
-          if (vec_ok && col0 + 32 <= p.N) {
+            for (int c = 0; c < width; c += 32) {
+              float a[64];
+              load_acc(h, 2 * (oc + c), a);
 #pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              red_add_v4_f32(d + j, wgt * __uint_as_float(r[j]), wgt * __uint_as_float(r[j + 1]),
-                             wgt * __uint_as_float(r[j + 2]), wgt * __uint_as_float(r[j + 3]));
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.N; ++j)
-              atomicAdd(d + j, wgt * __uint_as_float(r[j]));
-          }
-        }
-      } else if (p.epi == kEpiStoreF32) {
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(lane_addr + c * 32, r);
-          tmem_ld_wait();
-          const int col0 = n0 + c * 32;
-          if (!row_ok || col0 >= p.N) continue;
-          float* d = reinterpret_cast<float*>(p.C) + static_cast<long long>(group) * p.c_group_stride +
-                     static_cast<long long>(row) * p.ldc + col0;
-          if ((p.ldc & 3) == 0 && vec_ok && col0 + 32 <= p.N) {
+              for (int j = 0; j < 32; j += 8) {
+                float v[8];
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 o4;
-              o4.x = __uint_as_float(r[j]);
-              o4.y = __uint_as_float(r[j + 1]);
-              o4.z = __uint_as_float(r[j + 2]);
-              o4.w = __uint_as_float(r[j + 3]);
-              if (bias) {
-                o4.x += __bfloat162float(bias[col0 + j]);
-                o4.y += __bfloat162float(bias[col0 + j + 1]);
-                o4.z += __bfloat162float(bias[col0 + j + 2]);
-                o4.w += __bfloat162float(bias[col0 + j + 3]);
-              }
-              *reinterpret_cast<float4*>(d + j) = o4;
-            }
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
-              float v = __uint_as_float(r[j]);
-              if (bias) v += __bfloat162float(bias[col0 + j]);
-              d[j] = v;
-            }
-          }
-        }
-      } else {
-        // ---- bf16 outputs (plain store, SwiGLU, routed slab store): TMEM -> registers -> a
-        // padded shared-memory tile -> row-contiguous 16-byte stores, 64 output columns per
-        // round, so local HBM and NVLink both see full lines. Each warp stages and writes only
-        // its own 32 rows; __syncwarp is all it needs.
-        const bool swiglu = p.epi == kEpiSwigluBf16;
-        const int n_total = swiglu ? (p.N >> 1) : p.N;  // output row length
-        const int oc0 = swiglu ? (n0 >> 1) : n0;        // first output column of this tile
-        const int out_cols = swiglu ? BN / 2 : BN;
-        const bool out_vec =
-            (n_total & 7) == 0 && (((p.epi == kEpiSlabBf16) ? p.dst_ld : p.ldc) & 7) == 0;
-#pragma unroll 1
-        for (int oc = 0; oc < out_cols; oc += kStageCols) {
-          const int width = out_cols - oc < kStageCols ? out_cols - oc : kStageCols;  // 32 or 64
-#pragma unroll 1
-          for (int h = 0; h < width; h += 32) {
-            float v[32];
-            if (swiglu) {
-              uint32_t gt[32], up[32];
-              const int c = (oc + h) / 32;  // 32 outputs come from accumulator columns [64c, 64c+64)
-              tmem_ld_32x32b_x32(lane_addr + c * 64, gt);
-              tmem_ld_32x32b_x32(lane_addr + c * 64 + 32, up);
-              tmem_ld_wait();
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                v[j] = act_fn(__uint_as_float(gt[j]), p.act) * __uint_as_float(up[j]);
-            } else {
-              uint32_t r[32];
-              tmem_ld_32x32b_x32(lane_addr + oc + h, r);
-              tmem_ld_wait();
-              const int col0 = n0 + oc + h;
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                v[j] = __uint_as_float(r[j]);
-                if (bias != nullptr && col0 + j < p.N) v[j] += __bfloat162float(bias[col0 + j]);
+                for (int e = 0; e < 8; ++e) v[e] = act_fn(a[j + e], p.act) * a[32 + j + e];
+                uint4 o4;
+                o4.x = pack_bf16x2(v[0], v[1]);
+                o4.y = pack_bf16x2(v[2], v[3]);
+                o4.z = pack_bf16x2(v[4], v[5]);
+                o4.w = pack_bf16x2(v[6], v[7]);
+                *reinterpret_cast<uint4*>(my_row + (c + j) * 2) = o4;
               }
             }
+          } else {
+            float a[64];
+            load_acc(h, oc, a);
+            const int col0 = n0 + oc;
+            if (bias != nullptr) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
+              for (int j = 0; j < 64; ++j)
+                if (col0 + j < p.N) a[j] += __bfloat162float(bias[col0 + j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 64; j += 8) {
               uint4 o4;
-              o4.x = pack_bf16x2(v[j], v[j + 1]);
-              o4.y = pack_bf16x2(v[j + 2], v[j + 3]);
-              o4.z = pack_bf16x2(v[j + 4], v[j + 5]);
-              o4.w = pack_bf16x2(v[j + 6], v[j + 7]);
-              *reinterpret_cast<uint4*>(my_row + (h + j) * 2) = o4;
+              o4.x = pack_bf16x2(a[j], a[j + 1]);
+              o4.y = pack_bf16x2(a[j + 2], a[j + 3]);
+              o4.z = pack_bf16x2(a[j + 4], a[j + 5]);
+              o4.w = pack_bf16x2(a[j + 6], a[j + 7]);
+              *reinterpret_cast<uint4*>(my_row + j * 2) = o4;
             }
           }
           __syncwarp();
@@ -455,8 +593,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int r0 = 0; r0 < 32; r0 += rows_per_it) {
             const int rr = r0 + lane / chunks;
             const int ch = lane % chunks;
-            const int grow = it.m0 + q * 32 + rr;
-            const int gcol = oc0 + oc + ch * 8;
+            const int grow = it.m0 + h * BM + q * 32 + rr;
+            const int gcol = oc0 + ch * 8;
             if (grow >= it.rows || gcol >= n_total) continue;
             __nv_bfloat16* drow;
             if (p.epi == kEpiSlabBf16) {
@@ -485,12 +623,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           __syncwarp();
         }
       }
-      // hand the accumulator buffer back to the MMA warp
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+
+      if (fix) {
+        // the last split to leave the tile re-arms its two counters for the next launch
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          uint32_t* tk = p.ws_tickets + 2 * it.tile;
+          const uint32_t old = atomicAdd(tk + 1, 1u);
+          if (old == static_cast<uint32_t>(p.splits) - 1) {
+            tk[0] = 0;
+            tk[1] = 0;
+          }
+        }
+      } else {
+        // hand the accumulator buffer back to the MMA warp
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+      }
       ++t;
     }
+    if (warp == 2 && lane == 0) stamp(p, 4);
     tc_fence_before_sync();
     // When the whole grid has landed its contributions, tell every owner once.
     if (p.done_ticket != nullptr) {
@@ -517,40 +670,70 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 0) stamp(p, 5);
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MT>
 void launch_impl(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                  cudaStream_t stream) {
-  using L = SmemLayout<BN, STAGES>;
-  static bool configured = false;
-  static int sm_count = 148;
-  auto kern = gemm_bf16_kernel<BN, STAGES>;
-  if (!configured) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    configured = true;
-  }
+  using L = SmemLayout<BN, STAGES, MT>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, MT>;
+  ensure_dynamic_smem(kern, L::kTotal);
+  const int sms = sm_count();
   const int n_work = ((p.N + BN - 1) / BN) * p.m_tiles * p.splits;
-  const int grid = n_work < sm_count ? n_work : sm_count;
-  kern<<<grid, kThreads, L::kTotal, stream>>>(tmA, tmB, p);
+  const int grid = n_work < sms ? n_work : sms;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = L::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (p.ws != nullptr && p.splits > 1) {
+    // the splits of a tile wait for each other: ask for a launch that is resident as a whole
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p);
+}
+
+int tiles_of(int M, int N, int bn, int mt) {
+  return ((N + bn - 1) / bn) * ((M + 128 * mt - 1) / (128 * mt));
 }
 
 }  // namespace
 
+size_t gemm_ws_bytes(int M, int N, int bn, int mt, int splits) {
+  return static_cast<size_t>(tiles_of(M, N, bn, mt)) * splits * mt * bn * 128 * sizeof(__nv_bfloat16);
+}
+int gemm_ws_tickets(int M, int N, int bn, int mt) { return 2 * tiles_of(M, N, bn, mt); }
+
 void launch_gemm_bf16(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int bn,
-                      cudaStream_t stream) {
+                      int mt, cudaStream_t stream) {
+  if (mt == 2) {
+    switch (bn) {
+      case 64:
+        launch_impl<64, 5, 2>(tmA, tmB, p, stream);
+        break;
+      case 256:
+        launch_impl<256, 3, 2>(tmA, tmB, p, stream);
+        break;
+      default:
+        launch_impl<128, 4, 2>(tmA, tmB, p, stream);
+        break;
+    }
+    return;
+  }
   switch (bn) {
     case 64:
-      launch_impl<64, 8>(tmA, tmB, p, stream);
+      launch_impl<64, 8, 1>(tmA, tmB, p, stream);
       break;
     case 256:
-      launch_impl<256, 4>(tmA, tmB, p, stream);
+      launch_impl<256, 4, 1>(tmA, tmB, p, stream);
       break;
     default:
-      launch_impl<128, 6>(tmA, tmB, p, stream);
+      launch_impl<128, 6, 1>(tmA, tmB, p, stream);
       break;
   }
 }

@@ -31,13 +31,9 @@ struct GemmParams {
   int M, N, K;        // M = rows per group when group_counts == nullptr
   int kb_per_split;   // 64-wide k blocks per split
   int splits;         // number of K slices
-  int m_tiles;        // 128-row tiles along M (grouped mode: upper bound over all groups)
+  int m_tiles;        // M tiles of 128 * mt rows (grouped mode: upper bound over all groups, mt = 1)
   int epi;
   int act;            // kEpiSwigluBf16: 0 = SiLU, 1 = tanh-GELU
-  // L2 prefetch of the NEXT kernel's weights, issued by an otherwise idle epilogue warp while this
-  // GEMM streams its own (decode GEMMs are latency bound and leave HBM bandwidth unused).
-  const void* prefetch_ptr;
-  long long prefetch_bytes;  // multiple of 16; 0 = none
   int b_tiled;        // 1: B is stored tile-major [N/128][K/64][128][64]: every TMA box is one contiguous 16 KB
   void* C;            // kEpiStoreBf16 / kEpiStoreF32 / kEpiSwigluBf16
   long long ldc;
@@ -65,9 +61,25 @@ struct GemmParams {
   int ag_n_src;
   uint32_t* ag_ticket;       // local ticket used to re-arm the counters after the last CTA passed
   int* status;               // error word (0 = ok)
+  uint32_t spin_limit;       // iterations of every bounded wait (0 = OXB_SPIN_LIMIT)
+  // --- split-K with an in-kernel fix-up (store / SwiGLU / slab epilogues with splits > 1) ---
+  // Every split stores its partial tile as bf16 into its own slab of `ws`, the splits of a tile
+  // meet at a ticket (bounded wait; the launch is cooperative so they are co-resident), and each
+  // of them then sums a share of the tile's columns over all slabs and runs the epilogue on it.
+  __nv_bfloat16* ws;         // [tiles * splits][mt][BN / 8][128][8] partial tiles; nullptr = off
+  uint32_t* ws_tickets;      // [2 * tiles] arrival / departure counters, zero between launches
+  // Optional timeline of every CTA (bench_gemm --trace): 8 x uint64 nanosecond stamps per CTA
+  // [entry, first accumulator ready, partial stored, splits met, epilogue done, exit, 0, 0].
+  unsigned long long* trace;
 };
 
+// Bytes of partial-tile workspace and number of ticket words a split-K launch with fix-up needs.
+size_t gemm_ws_bytes(int M, int N, int bn, int mt, int splits);
+int gemm_ws_tickets(int M, int N, int bn, int mt);
+
+// bn: 64 / 128 / 256 output columns per tile; mt: 1 or 2 row halves of 128 per tile (mt = 2 keeps
+// all 256 rows of a decode batch with the CTA that streams a weight tile).
 void launch_gemm_bf16(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int bn,
-                      cudaStream_t stream);
+                      int mt, cudaStream_t stream);
 
 }  // namespace oxb

@@ -15,6 +15,7 @@
 
 #include <cuda_fp8.h>
 
+#include "../common/device_info.h"
 #include "../common/sm100.cuh"
 
 namespace oxb {
@@ -73,7 +74,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       for (int kb = 0; kb < n_kb; ++kb) {
         const int s = kb % STAGES;
         if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1)) {
-          atomicExch(p.status, kStatusMbarTimeoutProducer);
+          set_status_once(p.status, kStatusMbarTimeoutProducer);
           break;
         }
         mbar_arrive_expect_tx(&full[s], 2 * kTileBytes);
@@ -88,11 +89,11 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         const int s = kb % STAGES;
         const uint32_t buf = kb & 1;
         if (kb >= 2 && !mbar_wait(&tmem_empty[buf], ((kb >> 1) & 1) ^ 1)) {
-          atomicExch(p.status, kStatusMbarTimeoutMma);
+          set_status_once(p.status, kStatusMbarTimeoutMma);
           break;
         }
         if (!mbar_wait(&full[s], (kb / STAGES) & 1)) {
-          atomicExch(p.status, kStatusMbarTimeoutMma);
+          set_status_once(p.status, kStatusMbarTimeoutMma);
           break;
         }
         tc_fence_after_sync();
@@ -119,7 +120,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     for (int kb = 0; kb < n_kb; ++kb) {
       const uint32_t buf = kb & 1;
       if (ok && !mbar_wait(&tmem_full[buf], (kb >> 1) & 1)) {
-        if (lane == 0) atomicExch(p.status, kStatusMbarTimeoutEpilogue);
+        if (lane == 0) set_status_once(p.status, kStatusMbarTimeoutEpilogue);
         ok = false;
       }
       ok = __all_sync(0xffffffffu, ok);
@@ -284,11 +285,7 @@ __global__ void quant_act_fp8_kernel(const __nv_bfloat16* x, long long x_ld, uin
 
 void launch_gemm_fp8_block(const CUtensorMap& tmA, const CUtensorMap& tmB, const Fp8GemmParams& p,
                            cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(gemm_fp8_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
-    configured = true;
-  }
+  ensure_dynamic_smem(gemm_fp8_block_kernel, kSmemTotal);
   dim3 grid((p.M + BM - 1) / BM, (p.N + BN - 1) / BN);
   gemm_fp8_block_kernel<<<grid, kThreads, kSmemTotal, stream>>>(tmA, tmB, p);
 }

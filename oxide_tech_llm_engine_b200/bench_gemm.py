@@ -26,6 +26,10 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--tiled", default="0", help="comma list of 0/1: weights stored tile-major")
+    ap.add_argument("--mt", default="1", help="comma list of 1/2: 128-row halves per tile (2 = all 256 rows with one CTA)")
+    ap.add_argument("--graph", action="store_true", help="time a CUDA-graph replay of the launch (no host launch path in the number)")
+    ap.add_argument("--trace", action="store_true", help="print the per-CTA timeline (medians over CTAs, microseconds from kernel entry)")
+    ap.add_argument("--auto", action="store_true", help="time the (bn, mt, splits) that ops.pick_decode_cfg chooses")
     ap.add_argument("--fp8", action="store_true", help="time the block-scaled fp8 GEMM (and its activation quantiser)")
     args = ap.parse_args()
     from . import ops
@@ -73,13 +77,19 @@ def main() -> None:
                           "x_bf16_peak_of_measured": round(flops / us / 1e6 / peaks["bf16_tflops"], 3),
                           "quant_act_us": round(uq, 2)}), flush=True)
         return
-    for bn, sp, stag in itertools.product([int(x) for x in args.bn.split(",")], [int(x) for x in args.splits.split(",")],
-                                           [int(x) for x in args.tiled.split(",")]):
-        if sp > 1 and args.epi != ops.EPI_RED_F32:
-            continue
+    combos = list(itertools.product([int(x) for x in args.bn.split(",")], [int(x) for x in args.splits.split(",")],
+                                    [int(x) for x in args.tiled.split(",")], [int(x) for x in args.mt.split(",")]))
+    if args.auto:
+        bn, mt, sp = ops.pick_decode_cfg(args.m, args.n, args.k, swiglu=args.epi == ops.EPI_SWIGLU_BF16,
+                                         sms=ops.sm_count(dev))
+        combos = [(bn, sp, int(args.tiled.split(",")[0]), mt)]
+    for bn, sp, stag, mt in combos:
         if args.epi == ops.EPI_SWIGLU_BF16 and args.n % bn:
             continue
-        kw = dict(bn=bn, splits=sp)
+        tiles = -(-args.n // bn) * -(-args.m // (128 * mt))
+        if sp > 1 and args.epi != ops.EPI_RED_F32 and tiles * sp > ops.sm_count(dev):
+            continue
+        kw = dict(bn=bn, splits=sp, mt=mt)
         ww = w_tiled if stag else w
         if args.epi == ops.EPI_RED_F32:
             kw.update(epi=ops.EPI_RED_F32, dst_ptrs=[out_f32.data_ptr()])
@@ -87,23 +97,42 @@ def main() -> None:
             kw.update(epi=ops.EPI_STORE_F32, out=out_f32)
         else:
             kw.update(epi=args.epi, out=out_bf)
+        trace = torch.zeros(8 * ops.sm_count(dev), dtype=torch.int64, device=dev) if args.trace else None
+        if trace is not None:
+            kw["trace"] = trace
         for _ in range(3):
             ops.gemm(a, ww, **kw)
         torch.cuda.synchronize()
+        launch = lambda: ops.gemm(a, ww, **kw)
+        if args.graph:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                ops.gemm(a, ww, **kw)
+            launch = g.replay
         ts = []
         for _ in range(args.iters):
             if not args.no_flush:
                 flush.fill_(1)
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
-            ops.gemm(a, ww, **kw)
+            launch()
             e.record()
             torch.cuda.synchronize()
             ts.append(s.elapsed_time(e) * 1e3)
         ops.check_status()
         ts.sort()
         us = ts[len(ts) // 2]
-        print(json.dumps({"m": args.m, "n": args.n, "k": args.k, "epi": args.epi, "bn": bn, "splits": sp,
+        if trace is not None:
+            t = trace.view(-1, 8).cpu().numpy().astype("int64")
+            t = t[t[:, 0] > 0]
+            t0 = t[:, 0].min()
+            names = ["entry", "acc_ready", "partial_stored", "splits_met", "epilogue_done", "exit"]
+            med = {n: round(float(__import__("numpy").median(t[:, i][t[:, i] > 0] - t0)) / 1e3, 2) if (t[:, i] > 0).any() else None
+                   for i, n in enumerate(names)}
+            mx = {n: round(float((t[:, i][t[:, i] > 0] - t0).max()) / 1e3, 2) if (t[:, i] > 0).any() else None
+                  for i, n in enumerate(names)}
+            print(json.dumps({"trace_us_median": med, "trace_us_max": mx, "ctas": int(t.shape[0])}), flush=True)
+        print(json.dumps({"m": args.m, "n": args.n, "k": args.k, "epi": args.epi, "bn": bn, "mt": mt, "splits": sp,
                           "tiled": stag, "us": round(us, 2), "weights_gb_s": round(wbytes / us / 1e3, 1),
                           "tflops": round(flops / us / 1e6, 1),
                           "frac_hbm_of_measured": round(wbytes / us / 1e3 / peaks["hbm_gbs"], 3),

@@ -109,7 +109,7 @@ def main() -> None:
         slots = np.concatenate([bt[i, np.arange(q) // 16] * 16 + np.arange(q) % 16 for i, q in enumerate(q_lens)])
         tile_seq, tile_q0 = [], []
         for s, q in enumerate(q_lens):
-            for q0 in range(0, q, 64):
+            for q0 in range(0, q, 128):
                 tile_seq.append(s)
                 tile_q0.append(q0)
         lmap = np.full(M, -1, dtype=np.int32)

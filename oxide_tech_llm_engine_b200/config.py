@@ -44,6 +44,7 @@ class EngineConfig:
     gemm: str = "tcgen05"               # tcgen05 | library
     speculative: str = "off"            # off | ngram | auto
     draft_tokens: int = 5
+    jump_forward: bool = True           # grammar-forced bytes are appended without sampling
     quant_dense_copy: str = "auto"    # auto | on | off: keep a bf16 copy of packed weights for steps with > 8 rows
     h2o_pruning: bool = False
     h2o_budget_blocks: int = 128        # blocks a sequence may keep (sink + rolling window + heavy hitters)

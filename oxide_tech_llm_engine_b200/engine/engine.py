@@ -47,6 +47,15 @@ class RequestState:
     finish_reason: str = ""
 
 
+@dataclass
+class _Event:
+    """Engine-made token event (same fields as the scheduler's TokenEvent)."""
+    req_id: int
+    token: int
+    finished: bool
+    reason: str
+
+
 class _Staging:
     """One pinned host buffer and its device mirror holding every per-step array; a step is
     described to the GPU with a single H2D copy."""
@@ -298,6 +307,11 @@ class LLMEngine:
         """Gives grammars the byte strings of the vocabulary and the engine the stop ids."""
         self.vocab_bytes = tokenizer.vocab_bytes()
         self.stop_ids_default = tokenizer.stop_ids()
+        self._bytes_to_token = {}
+        for i, b in enumerate(self.vocab_bytes):
+            if b and b not in self._bytes_to_token:
+                self._bytes_to_token[bytes(b)] = i
+        self._max_token_bytes = max((len(b) for b in self._bytes_to_token), default=1)
 
     def cancel(self, req_id: int) -> bool:
         ok, events = self.sched.cancel(req_id)
@@ -502,10 +516,24 @@ class LLMEngine:
                 self.fail_all(f"rank_failure: {e}")
                 raise
         plan = self.sched.schedule()
+        # requests the scheduler had to end while planning (they can never fit the KV pool)
+        early = list(self.sched.take_events())
+        for e in early:
+            self._deliver(e)
         if plan.n_tokens == 0:
-            return []
-        if self._drafter is not None:
-            pass  # drafts are attached after update(), see below
+            if early or not self.sched.has_work():
+                self._idle_plans = 0
+                return early
+            # work is queued and nothing was scheduled: one such step can happen around a
+            # preemption, a run of them means the loop would spin for ever
+            self._idle_plans = getattr(self, "_idle_plans", 0) + 1
+            if self._idle_plans >= 4:
+                raise EngineError(
+                    f"scheduler made no progress for {self._idle_plans} steps with "
+                    f"{self.sched.num_running()} running / {self.sched.num_waiting()} waiting requests "
+                    f"and {self.sched.num_free_blocks()} free KV blocks")
+            return early
+        self._idle_plans = 0
         if self.cpu:
             tokens = self._step_cpu(plan)
         else:
@@ -516,12 +544,13 @@ class LLMEngine:
             else:
                 logits = self._forward(s, bucket)
                 tokens = self._sample(plan, logits, n_rows)
-        events = self.sched.update(plan, tokens)
+        events = early + list(self.sched.update(plan, tokens))
         self.stats["steps"] += 1
         self.stats["decode_tokens"] += plan.n_decode
         self.stats["prefill_tokens"] += plan.prefill_tokens
-        for e in events:
+        for e in events[len(early):]:
             self._deliver(e)
+        events += self._grammar_follow_up(events[len(early):])
         if self.cfg.h2o_pruning and plan.n_decode:
             self._h2o_prune(plan)
         if self._drafter is not None:
@@ -620,6 +649,49 @@ class LLMEngine:
             r.finish_reason = e.reason
         if r.on_token is not None:
             r.on_token(r, e)
+
+    def _grammar_follow_up(self, events: list) -> list:
+        """After the tokens of this step: a grammar that reached an accepting state ends its request
+        with "stop"; a grammar whose next bytes are forced has them appended without sampling
+        (jump-forward, continuous_batching.rs:475,807,1328): the scheduler computes them as one
+        prefill chunk in the next step."""
+        extra: list = []
+        for e in events:
+            r = self.requests.get(int(e.req_id))
+            if r is None or r.grammar is None or r.finished or e.token < 0:
+                continue
+            if r.grammar.done():
+                ok, _ = self.sched.cancel(r.req_id)
+                if ok:
+                    ev = _Event(r.req_id, -1, True, "stop")
+                    self._deliver(ev)
+                    extra.append(ev)
+                continue
+            forced = self._forced_tokens(r)
+            if forced:
+                self.stats["jump_forward_tokens"] = self.stats.get("jump_forward_tokens", 0) + len(forced)
+                for ev in self.sched.append_forced(r.req_id, forced):
+                    self._deliver(ev)
+                    extra.append(ev)
+        return extra
+
+    def _forced_tokens(self, r: RequestState) -> list:
+        """Greedy longest-match tokenisation of the bytes the grammar forces next."""
+        lookup = getattr(self, "_bytes_to_token", None)
+        if not lookup or not self.cfg.jump_forward:
+            return []
+        data = r.grammar.jump_forward()
+        out = []
+        while data:
+            for n in range(min(len(data), self._max_token_bytes), 0, -1):
+                t = lookup.get(data[:n])
+                if t is not None:
+                    out.append(t)
+                    data = data[n:]
+                    break
+            else:
+                break
+        return out
 
     def _attach_drafts(self) -> None:
         for rid in self.sched.running_ids():

@@ -152,8 +152,8 @@ class DeviceModel:
         # GEMM has to read them
         self.gemv_small = os.environ.get("OXB_GEMV", "1") != "0"
         self.gemv_max_rows = int(os.environ.get("OXB_GEMV_MAX", "2"))
-        self.prefetch_mask = int(os.environ.get("OXB_PREFETCH", "0"))
-        self.prefetch_head = int(os.environ.get("OXB_PREFETCH_HEAD_MB", "48")) << 19  # bf16 elements
+        self._sms = torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 148
+        self._gemm_cfg: dict = {}
         self.tile_weights = (os.environ.get("OXB_TILE_WEIGHTS", "1") != "0") if tile_weights is None else tile_weights
         self.D = cfg.head_dim
         self.hq = cfg.n_heads // tp
@@ -429,11 +429,37 @@ class DeviceModel:
         return dict(ag_flags=self.ws.local("flags")[flag_base:flag_base + self.tp], ag_expected=expected,
                     ag_rows_per_src=rows_per_src, ag_ticket=self.tickets[ticket:ticket + 1])
 
-    def _red_kwargs(self, acc: int, ticket: int, rpr: int, splits: int = 1) -> dict:
-        """Epilogue routing of a row-parallel GEMM. Across GPUs without split-K the partial tiles
-        travel as bf16 row-contiguous stores into the owner's receive slab (half the NVLink bytes
-        of fp32 and full-line packets); otherwise they are added into the fp32 accumulator."""
-        self._rs_slab[acc] = self.tp > 1 and splits == 1
+    def _gemm_shape(self, m: int, n: int, k: int, *, swiglu: bool = False, routed: bool = False) -> dict:
+        """Tile width, rows per tile, split-K factor and split-K mode of one projection. Steps of
+        at most 256 rows (decode batches) keep every row with the CTA that streams a weight tile and
+        split K to fill the SMs, combined inside the kernel; a routed projection on one GPU adds its
+        splits straight into the fp32 accumulator instead. Larger steps use 128-row tiles."""
+        key = (m, n, k, swiglu, routed)
+        c = self._gemm_cfg.get(key)
+        if c is not None:
+            return c
+        if m <= 256 and os.environ.get("OXB_DECODE_GEMM", "1") != "0":
+            bn, mt, sp = ops.pick_decode_cfg(m, n, k, swiglu=swiglu, sms=self._sms)
+            fixup = sp > 1 and not (routed and self.tp == 1)
+        else:
+            m_tiles = (m + 127) // 128
+            bn = ops.pick_bn(n, m_tiles, can_split=not swiglu)
+            mt = 1
+            sp = 1 if swiglu else ops.pick_splits(m, n, k, bn, self._sms)
+            fixup = sp > 1 and routed and self.tp > 1 and ((n + bn - 1) // bn) * m_tiles * sp <= self._sms
+            if sp > 1 and routed and self.tp > 1 and not fixup:
+                sp = 1
+        c = dict(bn=bn, mt=mt, splits=sp, fixup=fixup)
+        self._gemm_cfg[key] = c
+        return c
+
+    def _red_kwargs(self, acc: int, ticket: int, rpr: int, gc: Optional[dict] = None) -> dict:
+        """Epilogue routing of a row-parallel GEMM. Across GPUs the partial tiles travel as bf16
+        row-contiguous stores into the owner's receive slab (half the NVLink bytes of fp32 and
+        full-line packets; split-K is combined locally first, so every row crosses NVLink once);
+        on one GPU they are added into the fp32 accumulator."""
+        splits = gc["splits"] if gc is not None else 1
+        self._rs_slab[acc] = self.tp > 1 and (splits == 1 or bool(gc and gc["fixup"]))
         if self._rs_slab[acc]:
             kw = dict(epi=ops.EPI_SLAB_BF16, dst_ptrs=self.ws.ptrs(f"slab{acc}"), rows_per_owner=rpr,
                       my_rank=self.rank, dst_ld=self.cfg.d_model)
@@ -517,10 +543,6 @@ class DeviceModel:
                        first=True)
         g0 = self.ws.local("gather0")[:M]
         g1 = self.ws.local("gather1")[:M]
-        # Decode-sized GEMMs are latency bound and leave HBM bandwidth idle: each one pulls the next
-        # kernel's weights into L2 meanwhile (bit 0: gate/up -> down, 1: down -> next QKV,
-        # 2: QKV -> O, 3: O -> head of gate/up).
-        pf = self.prefetch_mask if M <= 512 and not cfg.is_moe else 0
         # single GPU, a handful of rows (latency-mode decoding): weight-streaming GEMVs instead of
         # 128-row MMA tiles
         gemv = (tp == 1 and M <= self.gemv_max_rows and not cfg.is_moe and self.gemv_small and d % 64 == 0
@@ -546,15 +568,13 @@ class DeviceModel:
                                    r0=r0)
                 continue
             # ---- attention block ----
-            bn = ops.pick_bn(self.wqkv, (M + 127) // 128, can_split=True)
-            splits = ops.pick_splits(M, self.wqkv, d, bn)
             ag = self._ag_kwargs(F_AG0, T_AG0, rpr, rpr)
-            if splits > 1:
-                ops.gemm(g0, L["w_qkv"], epi=ops.EPI_RED_F32, dst_ptrs=[self.qkv_acc.data_ptr()], bn=bn,
-                         splits=splits, prefetch=L["w_o"] if pf & 4 else None, **ag)
+            gc = self._gemm_shape(M, self.wqkv, d)
+            if gc["splits"] > 1 and not gc["fixup"]:
+                ops.gemm(g0, L["w_qkv"], epi=ops.EPI_RED_F32, dst_ptrs=[self.qkv_acc.data_ptr()], **gc, **ag)
                 qkv_kw = dict(acc_f32=self.qkv_acc)
             else:
-                ops.gemm(g0, L["w_qkv"], out=self.qkv_bf16[:M], bn=bn, prefetch=L["w_o"] if pf & 4 else None, **ag)
+                ops.gemm(g0, L["w_qkv"], out=self.qkv_bf16[:M], **gc, **ag)
                 qkv_kw = dict(qkv_bf16=self.qkv_bf16)
             ops.qkv_rope_append(bias=L["b_qkv"], q_norm_w=L["q_norm"], k_norm_w=L["k_norm"], norm_eps=1e-6,
                                 norm_w_offset=cfg.norm_weight_offset, positions=s.positions,
@@ -562,26 +582,19 @@ class DeviceModel:
                                 rope_mscale=self.rope_mscale, q_out=self.q_buf, k_cache=self.k_cache[li],
                                 v_cache=self.v_cache[li], m=M, hq=self.hq, hkv=self.hkv, d=self.D, **qkv_kw)
             self._attention(s, li)
-            bn = ops.pick_bn(d, (M + 127) // 128, can_split=True)
-            sp = ops.pick_splits(M, d, self.hq * self.D, bn)
-            ops.gemm(self.attn_out[:M], L["w_o"], bn=bn, splits=sp,
-                     prefetch=L["w_gu"].view(-1)[:self.prefetch_head] if pf & 8 else None,
-                     **self._red_kwargs(0, T_DONE_O, rpr, sp))
+            gc = self._gemm_shape(M, d, self.hq * self.D, routed=True)
+            ops.gemm(self.attn_out[:M], L["w_o"], **gc, **self._red_kwargs(0, T_DONE_O, rpr, gc))
             # ---- feed-forward block ----
             if cfg.is_moe:
                 self._finalize(rpr, L["ffn_norm"], acc=0, gather="", flag_base=F_MOE, r0=r0, layer=L, moe=True)
                 self._moe(L, M, rpr)
             else:
                 self._finalize(rpr, L["ffn_norm"], acc=0, gather="gather1", flag_base=F_AG1, r0=r0)
-                n_gu = 2 * self.i_l
                 ops.gemm(g1, L["w_gu"], out=self.act[:M], epi=ops.EPI_SWIGLU_BF16, act=self._act_code,
-                         bn=ops.pick_bn(n_gu, (M + 127) // 128), prefetch=L["w_down"] if pf & 1 else None,
+                         **self._gemm_shape(M, 2 * self.i_l, d, swiglu=True),
                          **self._ag_kwargs(F_AG1, T_AG1, rpr, rpr))
-                bn = ops.pick_bn(d, (M + 127) // 128, can_split=True)
-                sp = ops.pick_splits(M, d, self.i_l, bn)
-                nxt = self.layers[li + 1]["w_qkv"] if li + 1 < len(self.layers) else None
-                ops.gemm(self.act[:M], L["w_down"], bn=bn, splits=sp, prefetch=nxt if pf & 2 else None,
-                         **self._red_kwargs(1, T_DONE_D, rpr, sp))
+                gc = self._gemm_shape(M, d, self.i_l, routed=True)
+                ops.gemm(self.act[:M], L["w_down"], **gc, **self._red_kwargs(1, T_DONE_D, rpr, gc))
             last = li == len(self.layers) - 1
             if not last:
                 self._finalize(rpr, self.layers[li + 1]["attn_norm"], acc=1, gather="gather0", flag_base=F_AG0,
@@ -600,7 +613,7 @@ class DeviceModel:
             ops.gemv(lmg, self.lm_head, self.logits[:n_log])
         else:
             ops.gemm(lmg, self.lm_head, out=self.logits[:n_log], epi=ops.EPI_STORE_F32,
-                     bn=ops.pick_bn(self.v_l, (n_log + 127) // 128), **self._ag_kwargs(F_LMG, T_LMG, 0, rpr))
+                     **self._gemm_shape(n_log, self.v_l, d), **self._ag_kwargs(F_LMG, T_LMG, 0, rpr))
         if cfg.logit_softcap > 0:
             ops.softcap(self.logits[:n_log], cfg.logit_softcap)
         return self.logits[:n_log]

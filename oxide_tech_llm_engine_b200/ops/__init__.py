@@ -67,6 +67,21 @@ def check_status(device=None) -> None:
         raise EngineError(f"kernel reported: {msg}")
 
 
+# Iterations of every bounded device-side wait (0 = the compile-time default of about a second).
+# Tests of the time-out path set a few thousand.
+SPIN_LIMIT = 0
+
+_sm_count: dict[int, int] = {}
+
+
+def sm_count(device=None) -> int:
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _sm_count:
+        _sm_count[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    return _sm_count[key]
+
+
 def pick_bn(n: int, m_tiles: int = 1, can_split: bool = False) -> int:
     """Output-tile width. Wide tiles move fewer operand bytes per FLOP through the 64 B/clk
     SM<->L2 port, so take the widest tile that still gives about one CTA per SM; GEMMs that can
@@ -79,13 +94,66 @@ def pick_bn(n: int, m_tiles: int = 1, can_split: bool = False) -> int:
     return 64
 
 
-def pick_splits(m: int, n: int, k: int, bn: int) -> int:
+def pick_splits(m: int, n: int, k: int, bn: int, sms: int = 148) -> int:
     """Split-K factor so that small GEMMs still occupy most SMs (needs the fp32 red epilogue)."""
     tiles = ((m + 127) // 128) * ((n + bn - 1) // bn)
     kb = (k + 63) // 64
     if tiles >= 100 or kb < 8:
         return 1
-    return min(max(1, 148 // tiles), max(1, kb // 4), 16)
+    return min(max(1, sms // tiles), max(1, kb // 4), 16)
+
+
+def pick_decode_cfg(m: int, n: int, k: int, *, swiglu: bool = False, sms: int = 148) -> tuple[int, int, int]:
+    """(bn, mt, splits) for a GEMM with at most 256 rows against a large weight matrix.
+
+    Such a GEMM is bound by the bytes every SM pulls through its L2 port: a CTA that owns a
+    bn-wide weight tile over a K slice streams (rows + bn) * K_slice * 2 bytes, of which only the
+    bn share is distinct weight data. All rows stay with the CTA that loads the weight tile
+    (mt = 2 above 128 rows) and K is split so that tiles * splits fills the SMs; the splits are
+    combined inside the kernel. The estimate below is time = the slower of the per-SM stream and
+    the HBM stream, plus what the split costs (its partial tiles cross L2 twice).
+    """
+    mt = 2 if m > 128 else 1
+    rows = 128 * mt
+    kb = (k + 63) // 64
+    best = None
+    for bn in (256, 128, 64):
+        if n % bn and (swiglu or n < bn):
+            continue
+        tiles = (n + bn - 1) // bn
+        if tiles > sms:
+            cands = [1]
+        else:
+            cands = sorted({1, *(s for s in range(2, min(sms // tiles, kb // 2, 32) + 1))})
+        for s in cands:
+            per = -(-kb // s)
+            s_eff = -(-kb // per)
+            waves = -(-tiles * s_eff // sms)
+            stream_us = waves * per * 64 * (rows + bn) * 2 / 100e3      # ~100 GB/s per SM
+            hbm_us = n * k * 2 / 6.0e6
+            fix_us = 0.0 if s_eff == 1 else 3.0 + tiles * s_eff * rows * bn * 2 * 2 / (sms * 100e3)
+            t = max(stream_us, hbm_us) + fix_us
+            if best is None or t < best[0] - 1e-9:
+                best = (t, bn, s_eff)
+    if best is None:
+        return pick_bn(n, mt), 1, 1
+    return best[1], mt, best[2]
+
+
+_gemm_ws: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+GEMM_WS_BYTES = 48 << 20
+GEMM_WS_TICKETS = 4096
+
+
+def gemm_workspace(device) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-device scratch of the split-K fix-up: bf16 partial tiles and their tickets (allocated
+    once, so CUDA graphs can capture launches that use it)."""
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _gemm_ws:
+        _gemm_ws[key] = (torch.empty(GEMM_WS_BYTES // 2, dtype=torch.bfloat16, device=dev),
+                         torch.zeros(GEMM_WS_TICKETS, dtype=torch.int32, device=dev))
+    return _gemm_ws[key]
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
@@ -96,9 +164,11 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
          row_meta: Optional[torch.Tensor] = None, ag_flags: Optional[torch.Tensor] = None,
          ag_expected: int = 0, ag_rows_per_src: int = 0, ag_ticket: Optional[torch.Tensor] = None,
          bn: int = 0, splits: int = 1, act: int = 0, m_tiles: int = 0,
-         dst_ld: int = 0, my_rank: int = 0, prefetch: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+         dst_ld: int = 0, my_rank: int = 0, mt: int = 1, fixup: Optional[bool] = None,
+         trace: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """tcgen05 GEMM  out = a @ w^T  (bf16 in, fp32 accumulate). See csrc/kernels/gemm_bf16.cu.
-    `prefetch`: a contiguous tensor (the next kernel's weights) pulled into L2 while this GEMM runs."""
+    `mt` = 2 keeps 256 rows with one CTA per weight tile; `splits` > 1 with a store / SwiGLU / slab
+    epilogue combines the split partial tiles inside the kernel (`fixup`, default on for those)."""
     M = a.shape[-2]
     tiled = w.dim() == 4  # tile-major weight from tile_weight()
     N = w.shape[0] * 128 if tiled else w.shape[-2]
@@ -108,10 +178,13 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
         n_out = N // 2 if epi == EPI_SWIGLU_BF16 else N
         dt = torch.float32 if epi == EPI_STORE_F32 else torch.bfloat16
         out = torch.empty(*a.shape[:-1], n_out, dtype=dt, device=a.device)
+    if fixup is None:
+        fixup = splits > 1 and epi != EPI_RED_F32
+    ws, tk = gemm_workspace(a.device) if fixup and splits > 1 else (None, None)
     _ext().gemm_bf16(a, w, epi, out, bias, list(dst_ptrs), list(arrive_ptrs), done_ticket,
                      reset_on_done, rows_per_owner, group_counts, row_meta, ag_flags, ag_expected,
                      ag_rows_per_src, ag_ticket, status_word(a.device), bn, splits, act, m_tiles, dst_ld,
-                     my_rank, 1 if tiled else 0, prefetch)
+                     my_rank, 1 if tiled else 0, mt, ws, tk, SPIN_LIMIT, trace)
     _bump()
     return out
 
@@ -187,19 +260,14 @@ def paged_decode(q, k_cache, v_cache, block_tables, seq_lens, pages_per_split, p
 # OXB_CHECKS=1: the attention kernels verify every block-table id against the pool size (a bad id is
 # recorded in the status word and page 0 is read instead); costs ~4 % of the decode attention kernel.
 CHECK_BOUNDS = os.environ.get("OXB_CHECKS", "0") != "0"
-PREFILL_IMPL = os.environ.get("OXB_PREFILL", "tc")  # tc = tcgen05 kernel, mma = mma.sync kernel
 
 
 def paged_prefill(q, k_cache, v_cache, block_tables, tile_seq, tile_q0, q_start, q_lens, ctx_lens, out,
-                  *, n_tiles: int, window: int = 0, scale: float, impl: Optional[str] = None) -> None:
-    """Causal paged attention over ragged prefill chunks. `tc`: tcgen05 / TMEM kernel on 128-row
-    query tiles (attn_prefill_tc.cu); `mma`: the mma.sync kernel on 64-row tiles (attn_prefill.cu)."""
-    if (impl or PREFILL_IMPL) == "tc":
-        _ext().paged_prefill_tc(q, k_cache, v_cache, block_tables, tile_seq, tile_q0, q_start, q_lens,
-                                ctx_lens, out, n_tiles, window, scale, status_word(q.device))
-    else:
-        _ext().paged_prefill(q, k_cache, v_cache, block_tables, tile_seq, tile_q0, q_start, q_lens,
-                             ctx_lens, out, n_tiles, window, scale, status_word(q.device) if CHECK_BOUNDS else None)
+                  *, n_tiles: int, window: int = 0, scale: float) -> None:
+    """Causal paged attention over ragged prefill chunks on 128-row query tiles (tcgen05 / TMEM,
+    attn_prefill_tc.cu); `tile_q0` entries are multiples of 128."""
+    _ext().paged_prefill_tc(q, k_cache, v_cache, block_tables, tile_seq, tile_q0, q_start, q_lens,
+                            ctx_lens, out, n_tiles, window, scale, status_word(q.device))
     _bump()
 
 
@@ -213,7 +281,7 @@ def finalize_norm(*, rows: int, n: int, acc=None, rs_slab=None, n_slabs: int = 0
     _ext().finalize_norm(acc, rs_slab, n_slabs, slab_stride, arrive, expected, ticket, residual_in, residual_out, bias, norm_w, eps,
                          w_offset, list(out_ptrs), list(out_flag_ptrs), out_row_off, out_row_map, rows, n,
                          status_word(device), router_w, top_k, experts_per_rank, routed_scale,
-                         list(slab_ptrs), list(meta_ptrs), list(cnt_ptrs), cap, my_rank)
+                         list(slab_ptrs), list(meta_ptrs), list(cnt_ptrs), cap, my_rank, SPIN_LIMIT)
     _bump()
 
 

@@ -173,6 +173,66 @@ def test_grammar_constrained_json_is_valid():
         json.loads(text)
 
 
+def test_grammar_jump_forward_skips_sampling_and_ends_on_accept():
+    """Bytes the grammar forces are appended without a forward pass each (the fixed prefix takes
+    one prefill chunk instead of one decode step per token); an accepting state ends the request
+    with "stop"; the text is the same as with jump-forward off."""
+    import json
+
+    from oxide_tech_llm_engine_b200.tokenizer import Tokenizer
+
+    outs, steps = [], []
+    for jf in (True, False):
+        eng, mc, src = mk(jump_forward=jf)
+        tok = Tokenizer.ascii_fallback(mc.vocab_size)
+        eng.set_tokenizer(tok)
+        sp = SamplingParams(greedy=True, max_tokens=80, grammar='json_prefix:{"answer": "', ignore_eos=True)
+        rid = eng.add_request(tok.encode("q"), sp)
+        n = 0
+        while eng.has_work() and n < 200:
+            eng.step()
+            n += 1
+        r = eng.requests[rid]
+        outs.append(tok.decode(r.output))
+        steps.append(eng.stats["steps"])
+        assert r.finished and eng.sched.num_free_blocks() + eng.sched.radix_stats()["cached_blocks"] == 96
+        if jf:
+            assert eng.stats.get("jump_forward_tokens", 0) >= 8
+        if r.finish_reason == "stop":
+            json.loads(outs[-1])
+    assert outs[0].startswith('{"answer": "') and outs[0] == outs[1]
+    assert steps[0] < steps[1]
+
+
+def test_engine_fails_loudly_when_the_scheduler_cannot_progress():
+    from oxide_tech_llm_engine_b200.errors import EngineError
+
+    eng, mc, src = mk(num_kv_blocks=8)
+    rid = eng.add_request(list(range(1, 300)), GREEDY)     # 19 blocks needed, 8 exist
+    rid2 = eng.add_request(list(range(1, 20)), GREEDY)
+    outs = eng.generate([], GREEDY, max_steps=100)
+    assert outs == [] and not eng.has_work()
+    assert eng.requests[rid].finished and eng.requests[rid].finish_reason.startswith("prefill_error")
+    assert eng.requests[rid2].finish_reason == "length" and len(eng.requests[rid2].output) == 8
+    # an empty plan with queued work is reported, not spun on
+    class Stuck:
+        def __getattr__(self, k):
+            return getattr(eng_sched, k)
+        def schedule(self):
+            return empty_plan
+        def take_events(self):
+            return []
+        def has_work(self):
+            return True
+    eng_sched = eng.sched
+    empty_plan = eng.sched.schedule()
+    assert empty_plan.n_tokens == 0
+    eng.sched = Stuck()
+    with pytest.raises(EngineError, match="no progress"):
+        for _ in range(10):
+            eng.step()
+
+
 def test_monitor_failure_fails_requests_and_returns_blocks():
     """A peer that stops answering is found before the step: requests end with a typed reason and
     every KV block goes back to the pool."""

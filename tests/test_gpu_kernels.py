@@ -130,6 +130,73 @@ def test_gemm_swiglu_epilogue(ops):
     assert _rel_err(out, ref) < 2e-2
 
 
+@pytest.mark.parametrize("m,n,k,bn,splits,tiled", [
+    (256, 1024, 1024, 256, 1, False), (256, 768, 2048, 128, 1, True), (200, 512, 512, 64, 1, False),
+    (256, 1024, 2048, 256, 4, False), (130, 640, 4096, 128, 5, False), (256, 1280, 8192, 128, 13, True),
+    (255, 1000, 1024, 256, 3, False), (600, 512, 1024, 256, 2, False), (64, 1024, 4096, 256, 6, False),
+])
+def test_gemm_full_m_tiles_and_in_kernel_splitk(ops, m, n, k, bn, splits, tiled):
+    """mt = 2 (both 128-row halves with the CTA that owns the weight tile) and split-K combined
+    inside the kernel through bf16 partial slabs, against fp32 matmul; run twice so that the
+    tickets are seen re-armed."""
+    torch.manual_seed(21)
+    a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(n, device=DEV, dtype=torch.bfloat16)
+    ww = ops.tile_weight(w) if tiled else w
+    ref = a.float() @ w.float().T + bias.float()
+    mt = 2 if m > 128 else 1
+    for _ in range(2):
+        out = ops.gemm(a, ww, bias=bias, bn=bn, mt=mt, splits=splits)
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert _rel_err(out, ref) < 1.5e-2 and _cos(out, ref) > 0.9999, (m, n, k, bn, splits, _rel_err(out, ref))
+    out32 = ops.gemm(a, ww, bias=bias, bn=bn, mt=mt, splits=splits, epi=ops.EPI_STORE_F32)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert _rel_err(out32, ref) < (2e-3 if splits == 1 else 8e-3)
+    assert int(ops.gemm_workspace(DEV)[1].abs().max().item()) == 0  # tickets re-armed
+
+
+@pytest.mark.parametrize("m,i,k,bn,splits", [(256, 1792, 2048, 256, 5), (256, 512, 1024, 128, 1),
+                                              (192, 3584, 1024, 256, 5), (96, 1024, 2048, 64, 4)])
+def test_gemm_swiglu_full_m_splitk(ops, m, i, k, bn, splits):
+    torch.manual_seed(22)
+    a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16) * 0.5
+    wg = torch.randn(i, k, device=DEV, dtype=torch.bfloat16) * 0.05
+    wu = torch.randn(i, k, device=DEV, dtype=torch.bfloat16) * 0.05
+    w = torch.stack([wg.view(i // 32, 32, k), wu.view(i // 32, 32, k)], 1).reshape(2 * i, k).contiguous()
+    out = ops.gemm(a, w, epi=ops.EPI_SWIGLU_BF16, bn=bn, mt=2 if m > 128 else 1, splits=splits)
+    torch.cuda.synchronize()
+    ops.check_status()
+    ref = torch.nn.functional.silu(a.float() @ wg.float().T) * (a.float() @ wu.float().T)
+    assert out.shape == (m, i) and _rel_err(out, ref) < 2e-2
+
+
+def test_gemm_slab_full_m_splitk_reduce_scatter_emulated(ops):
+    """Row-parallel projection at decode size: 256 rows, 8 owners emulated on one GPU, split-K
+    combined locally before ONE bf16 push per row."""
+    torch.manual_seed(23)
+    tp, rpo, n, k = 8, 32, 1024, 3584
+    m = tp * rpo
+    a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=DEV, dtype=torch.bfloat16)
+    slabs = [torch.zeros(tp, rpo, n, device=DEV, dtype=torch.bfloat16) for _ in range(tp)]
+    arrive = torch.zeros(tp, dtype=torch.int32, device=DEV)
+    ticket = torch.zeros(1, dtype=torch.int32, device=DEV)
+    my = 5
+    ops.gemm(a, ops.tile_weight(w), epi=ops.EPI_SLAB_BF16, dst_ptrs=[s.data_ptr() for s in slabs],
+             rows_per_owner=rpo, my_rank=my, dst_ld=n, bn=256, mt=2, splits=7,
+             arrive_ptrs=[arrive[o:o + 1].data_ptr() for o in range(tp)], done_ticket=ticket)
+    torch.cuda.synchronize()
+    ops.check_status()
+    ref = a.float() @ w.float().T
+    for o in range(tp):
+        assert _rel_err(slabs[o][my], ref[o * rpo:(o + 1) * rpo]) < 1.5e-2
+        assert slabs[o][(my + 1) % tp].abs().max().item() == 0
+    assert arrive.tolist() == [1] * tp and int(ticket.item()) == 0
+
+
 def test_gemm_grouped_combine(ops):
     torch.manual_seed(4)
     G, cap, k, n = 4, 256, 512, 384
@@ -252,8 +319,7 @@ def test_paged_decode(ops, hq, hkv, d, seq_lens, pps, window):
     (2, 1, 128, [(300, 700), (128, 128), (257, 257)], 0),
     (4, 2, 64, [(200, 500)], 100),
 ])
-@pytest.mark.parametrize("impl", ["tc", "mma"])
-def test_paged_prefill(ops, hq, hkv, d, chunks, window, impl):
+def test_paged_prefill(ops, hq, hkv, d, chunks, window):
     torch.manual_seed(6)
     q_lens = [c[0] for c in chunks]
     ctx_lens = [c[1] for c in chunks]
@@ -265,14 +331,14 @@ def test_paged_prefill(ops, hq, hkv, d, chunks, window, impl):
     for s, ql in enumerate(q_lens):
         q_start.append(off)
         off += ql
-        for q0 in range(0, ql, 64):
+        for q0 in range(0, ql, 128):
             tile_seq.append(s)
             tile_q0.append(q0)
     ti = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
     out = torch.zeros(T, hq * d, device=DEV, dtype=torch.bfloat16)
     scale = 1.0 / math.sqrt(d)
     ops.paged_prefill(q, k_cache, v_cache, bt, ti(tile_seq), ti(tile_q0), ti(q_start), ti(q_lens),
-                      ti(ctx_lens), out, n_tiles=len(tile_seq), window=window, scale=scale, impl=impl)
+                      ti(ctx_lens), out, n_tiles=len(tile_seq), window=window, scale=scale)
     torch.cuda.synchronize()
     ops.check_status()
     for s, (ql, cl) in enumerate(chunks):

@@ -122,7 +122,11 @@ def _drain(s, H, answer=lambda rid, row: 7):
         if not s.has_work():
             break
         plan = s.schedule()
+        early = s.take_events()
+        events += early
         if plan.n_tokens == 0:
+            if early:
+                continue
             break
         toks = np.array([answer(int(r), i) for i, r in enumerate(plan.logit_req)], dtype=np.int32)
         events += s.update(plan, toks)
@@ -175,6 +179,62 @@ def test_scheduler_preempts_youngest_when_kv_runs_out(H):
     counts = {rid: sum(1 for e in ev if e.req_id == rid and e.token >= 0) for rid in (1, 2, 3)}
     assert counts == {1: 40, 2: 40, 3: 40}
     assert s.num_free_blocks() == 6
+
+
+def test_two_long_prefills_that_fill_the_pool_both_finish(H):
+    """Two prompts that each fit the pool alone but not together: the younger one is preempted when
+    the older one's next chunk finds no block, instead of both waiting on each other."""
+    c = H.SchedulerConfig()
+    c.num_blocks, c.enable_radix = 100, False
+    s = H.Scheduler(c)
+    for rid in (1, 2):
+        s.add_request(rid, np.arange(1500, dtype=np.int32), 4, [], True)
+    ev = _drain(s, H)
+    assert {e.req_id for e in ev if e.finished} == {1, 2} and not s.has_work()
+    assert all(e.reason == "length" for e in ev if e.finished)
+    assert s.preemptions() > 0 and s.num_free_blocks() == 100
+
+
+def test_request_that_can_never_fit_is_ended_not_spun_on(H):
+    c = H.SchedulerConfig()
+    c.num_blocks, c.enable_radix, c.chunk_max = 4, False, 32
+    s = H.Scheduler(c)
+    s.add_request(1, np.arange(200, dtype=np.int32), 4, [], True)   # 13 blocks needed, 4 exist
+    s.add_request(2, np.arange(20, dtype=np.int32), 3, [], True)
+    ev = _drain(s, H)
+    by = {e.req_id: e for e in ev if e.finished}
+    assert by[1].reason.startswith("prefill_error") and by[2].reason == "length"
+    assert not s.has_work() and s.num_free_blocks() == 4
+    # a decoding request that outgrows a pool it has to itself ends with "length"
+    s.add_request(3, np.arange(40, dtype=np.int32), 500, [], True)
+    ev = _drain(s, H)
+    fin = [e for e in ev if e.finished]
+    assert len(fin) == 1 and fin[0].req_id == 3 and fin[0].reason == "length"
+    assert sum(1 for e in ev if e.token >= 0) == 4 * 16 - 40 + 1 and s.num_free_blocks() == 4
+
+
+def test_forced_tokens_are_prefilled_as_one_chunk(H):
+    c = H.SchedulerConfig()
+    c.num_blocks, c.enable_radix = 32, False
+    s = H.Scheduler(c)
+    s.add_request(1, np.arange(10, dtype=np.int32), 20, [99], False)
+    plan = s.schedule()
+    s.update(plan, np.array([100], dtype=np.int32))
+    ev = s.append_forced(1, [201, 202, 203])
+    assert [e.token for e in ev] == [201, 202, 203] and not any(e.finished for e in ev)
+    plan = s.schedule()
+    assert plan.n_decode == 0 and plan.n_prefill == 1 and plan.q_lens[0] == 4 and plan.logit_rows.size == 1
+    assert list(plan.token_ids) == [100, 201, 202, 203] and list(plan.positions) == [10, 11, 12, 13]
+    ev = s.update(plan, np.array([300], dtype=np.int32))
+    assert [e.token for e in ev] == [300]
+    info = s.request_info(1)
+    assert info["computed"] == 14 and info["generated"] == 5 and info["phase"] == 2
+    plan = s.schedule()
+    assert plan.n_decode == 1 and list(plan.token_ids) == [300]
+    s.update(plan, np.array([7], dtype=np.int32))
+    ev = s.append_forced(1, [5, 99, 6])   # a forced stop id ends the request
+    assert [e.token for e in ev] == [5, 99] and ev[-1].finished and ev[-1].reason == "stop"
+    assert not s.has_work() and s.num_free_blocks() == 32
 
 
 def test_scheduler_speculative_accept_and_rollback(H):
