@@ -57,7 +57,7 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
                int64_t splits, int64_t act, int64_t m_tiles_override, int64_t dst_ld,
                int64_t my_rank, int64_t b_tiled, int64_t mt, const c10::optional<Tensor>& ws,
                const c10::optional<Tensor>& ws_tickets, int64_t spin_limit,
-               const c10::optional<Tensor>& trace) {
+               const c10::optional<Tensor>& trace, int64_t wide_boxes) {
   TORCH_CHECK(a.is_cuda() && w.is_cuda(), "gemm_bf16: CUDA tensors required");
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16,
               "gemm_bf16: bf16 operands required");
@@ -87,10 +87,17 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
   const uint64_t a_grp = grouped3d ? static_cast<uint64_t>(a.stride(0)) * 2 : a_row * M;
   const uint64_t w_grp = tiled ? 16384 : (grouped3d ? static_cast<uint64_t>(w.stride(0)) * 2 : w_row * N);
   const int bn_i = bn == 64 ? 64 : (bn == 256 ? 256 : 128);
+  // decode tiles (mt = 2): one copy per operand and stage instead of two 16 KB boxes each
+  const bool wide = mt == 2 && !grouped3d && wide_boxes != 0;
   CUtensorMap tmA = oxb::make_tma_map(a.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, K, M, G,
-                                      a_row, a_grp, 64, 128, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+                                      a_row, a_grp, 64, wide ? 256 : 128, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+  const uint64_t total_kb_u = static_cast<uint64_t>((K + 63) / 64);
   CUtensorMap tmB =
-      tiled ? oxb::make_tma_map(w.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, 64, 128,
+      (tiled && wide && bn_i == 256)
+          ? oxb::make_tma_map(w.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 4, 64, 128, total_kb_u, 128,
+                              16384, 64, 128, 1, CU_TENSOR_MAP_SWIZZLE_128B, static_cast<uint64_t>(w.size(0)),
+                              16384 * total_kb_u, 2)
+      : tiled ? oxb::make_tma_map(w.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, 64, 128,
                                 static_cast<uint64_t>(w.size(0) * w.size(1)), 128, 16384, 64,
                                 bn_i < 128 ? bn_i : 128, 1, CU_TENSOR_MAP_SWIZZLE_128B)
             : oxb::make_tma_map(w.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, K, N, G, w_row,
@@ -108,6 +115,7 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
   p.epi = static_cast<int>(epi);
   p.act = static_cast<int>(act);
   p.b_tiled = static_cast<int>(b_tiled);
+  p.wide_boxes = wide ? 1 : 0;
   p.spin_limit = static_cast<uint32_t>(spin_limit > 0 ? spin_limit : 0);
   if (trace.has_value() && trace->defined()) {
     TORCH_CHECK(trace->scalar_type() == torch::kInt64 && trace->numel() >= 8 * oxb::sm_count(),
@@ -180,6 +188,8 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
     const int n_work = static_cast<int>((N + bn_i - 1) / bn_i) * m_tiles * s;
     TORCH_CHECK(n_work <= oxb::sm_count(),
                 "gemm_bf16: split-K with the in-kernel fix-up needs one work item per SM at most (", n_work, ")");
+    TORCH_CHECK(s <= oxb::gemm_max_fixup_splits(bn_i, mt_i, epi == oxb::kEpiSwigluBf16),
+                "gemm_bf16: too many splits for the in-kernel fix-up of this tile shape (", s, ")");
     TORCH_CHECK(ws->is_cuda() && ws->is_contiguous() &&
                     static_cast<size_t>(ws->numel() * ws->element_size()) >=
                         oxb::gemm_ws_bytes(static_cast<int>(M), static_cast<int>(N), bn_i, mt_i, s),
@@ -735,6 +745,7 @@ Tensor tensor_from_ptr(int64_t ptr, const std::vector<int64_t>& shape, const std
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "sm_100a kernels of the B200-native Oxide engine";
   m.def("gemm_bf16", &gemm_bf16);
+  m.def("gemm_max_fixup_splits", &oxb::gemm_max_fixup_splits);
   m.def("gemm_fp8_block", &gemm_fp8_block);
   m.def("quant_act_fp8", &quant_act_fp8);
   m.def("paged_decode", &paged_decode);

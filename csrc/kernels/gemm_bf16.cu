@@ -106,27 +106,6 @@ __device__ __forceinline__ void tmem_load_cols(uint32_t taddr, float (&a)[NG * 3
 #pragma unroll
     for (int j = 0; j < 32; ++j) a[g * 32 + j] = __uint_as_float(r[g][j]);
 }
-// The same columns summed over the bf16 slabs of every split: `src` = this thread's row in the
-// first 8-column group of the first split ([col / 8][128 rows][8] layout, 1024 elements per group).
-template <int NG>
-__device__ __forceinline__ void ws_load_cols(const __nv_bfloat16* src, int splits, size_t split_stride,
-                                             float (&a)[NG * 32]) {
-#pragma unroll
-  for (int j = 0; j < NG * 32; ++j) a[j] = 0.f;
-#pragma unroll 2
-  for (int s = 0; s < splits; ++s, src += split_stride) {
-    uint4 x[NG * 4];
-#pragma unroll
-    for (int g = 0; g < NG * 4; ++g) x[g] = __ldcg(reinterpret_cast<const uint4*>(src + g * 1024));
-#pragma unroll
-    for (int g = 0; g < NG * 4; ++g) {
-      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&x[g]);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) a[g * 8 + j] += __bfloat162float(e[j]);
-    }
-  }
-}
-
 // Waits until the source counters [s_lo, s_hi] reach the expected value; `waiters` is the number
 // of such waits the whole grid performs, the last of them re-arms the counters.
 __device__ bool wait_sources(const GemmParams& p, int s_lo, int s_hi, uint32_t waiters) {
@@ -151,6 +130,33 @@ __device__ bool wait_sources(const GemmParams& p, int s_lo, int s_hi, uint32_t w
     *p.ag_ticket = 0;
   }
   return ok;
+}
+
+// Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completion on `bar`.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+// 64 columns of this thread's row summed over the partial slabs that were landed in shared memory:
+// `src` = this thread's 16 bytes in the first 8-column group of the first split, groups are 2 KB
+// apart, splits `split_bytes` apart. Consecutive lanes read consecutive 16-byte words.
+__device__ __forceinline__ void smem_sum_cols(const uint8_t* src, int splits, uint32_t split_bytes,
+                                              float (&a)[64]) {
+#pragma unroll
+  for (int j = 0; j < 64; ++j) a[j] = 0.f;
+#pragma unroll 1
+  for (int s = 0; s < splits; ++s, src += split_bytes) {
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      const uint4 x = *reinterpret_cast<const uint4*>(src + g * 2048);
+      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[g * 8 + j] += __bfloat162float(e[j]);
+    }
+  }
 }
 
 template <int BN, int STAGES, int MT>
@@ -182,7 +188,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* empty = full + STAGES;
   uint64_t* tmem_full = empty + STAGES;  // [2]
   uint64_t* tmem_empty = tmem_full + 2;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* fix_bar = tmem_empty + 2;    // landing of the partial slabs in the split-K fix-up
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fix_bar + 1);
   int* s_misc = reinterpret_cast<int*>(tmem_slot + 2);  // [0] start-up ok, [1] tile barrier ok
   int* s_counts = s_misc + 2;                           // first m tile per group, grouped mode
 
@@ -214,6 +221,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     mbar_init(&tmem_full[1], 1);
     mbar_init(&tmem_empty[0], 4);
     mbar_init(&tmem_empty[1], 4);
+    mbar_init(fix_bar, 1);
     fence_mbar_init();
     int ok = 1;
     if (grouped) {
@@ -300,7 +308,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         __syncwarp();
         const int op = lane - (s & 7) * 4;  // which copy of this stage this lane issues (0..3), if any
         // weights first: they do not depend on any peer
-        if (p.b_tiled) {
+        if (p.b_tiled && p.wide_boxes && BN == 256) {
+          // both 128-row weight tiles of this k block in one 32 KB copy: [64][128][k block][n tile]
+          if (op == 0) tma_load_4d(sB + s * L::kBBytes, &tmB, &full[s], 0, 0, it.kb0 + kb, it.n0 >> 7);
+        } else if (p.b_tiled) {
           // tile-major weights: tile index = (n / 128) * total_kb + kb, box = 128 x 64 (or the
           // 64-row half of a tile for BN = 64)
           if (op >= 0 && op < kBOps)
@@ -327,7 +338,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (!ok) break;
         }
         // rows past M read as zeros (the box is filled in full either way)
-        if (op >= 2 && op < 2 + MT)
+        if (p.wide_boxes && MT == 2) {
+          if (op == 2) tma_load_3d(sA + s * L::kABytes, &tmA, &full[s], (it.kb0 + kb) * BK, it.m0, it.group);
+        } else if (op >= 2 && op < 2 + MT)
           tma_load_3d(sA + s * L::kABytes + (op - 2) * (BM * BK * 2), &tmA, &full[s], (it.kb0 + kb) * BK,
                       it.m0 + (op - 2) * BM, it.group);
       }
@@ -389,7 +402,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int units_per_half = (out_cols + kStageCols - 1) / kStageCols;
     const int n_units = MT * units_per_half;        // 64-output-column x 128-row pieces of a tile
     const size_t ws_half = static_cast<size_t>(BN) * 128;  // bf16 elements of one row half of a slab
-    uint32_t t = 0;
+    uint32_t t = 0, fix_phase = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
       const WorkItem it = decode(w);
@@ -417,21 +430,38 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // ---- phase A: this split's partial tile -> its slab (bf16; a warp's 32 rows of one
         // 8-column group are 512 contiguous bytes), then meet the other splits of the tile ----
         __nv_bfloat16* slab = const_cast<__nv_bfloat16*>(ws_tile) + static_cast<size_t>(it.z) * MT * ws_half;
-#pragma unroll 1
-        for (int h = 0; h < MT; ++h) {
-#pragma unroll 1
-          for (int c = 0; c < BN / 64; ++c) {
-            float a[64];
-            tmem_load_cols<2>(lane_addr + h * kAccCols + c * 64, a);
+        // software pipelined: the TMEM load of chunk i + 1 is in flight while chunk i is packed
+        // and stored (64 columns per chunk, two register sets)
+        constexpr int kChunks = MT * (BN / 64);
+        auto issue = [&](int i, uint32_t (&r)[2][32]) __attribute__((always_inline)) {
+          const uint32_t addr = lane_addr + (i / (BN / 64)) * kAccCols + (i % (BN / 64)) * 64;
+          tmem_ld_32x32b_x32(addr, r[0]);
+          tmem_ld_32x32b_x32(addr + 32, r[1]);
+        };
+        auto store = [&](int i, const uint32_t (&r)[2][32]) __attribute__((always_inline)) {
+          __nv_bfloat16* dst = slab + (i / (BN / 64)) * ws_half + static_cast<size_t>((i % (BN / 64)) * 8) * 1024;
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              uint4 o4;
-              o4.x = pack_bf16x2(a[g * 8], a[g * 8 + 1]);
-              o4.y = pack_bf16x2(a[g * 8 + 2], a[g * 8 + 3]);
-              o4.z = pack_bf16x2(a[g * 8 + 4], a[g * 8 + 5]);
-              o4.w = pack_bf16x2(a[g * 8 + 6], a[g * 8 + 7]);
-              __stcg(reinterpret_cast<uint4*>(slab + h * ws_half + static_cast<size_t>(c * 8 + g) * 1024), o4);
-            }
+          for (int g = 0; g < 8; ++g) {
+            const uint32_t* v = &r[g >> 2][(g & 3) * 8];
+            uint4 o4;
+            o4.x = pack_bf16x2(__uint_as_float(v[0]), __uint_as_float(v[1]));
+            o4.y = pack_bf16x2(__uint_as_float(v[2]), __uint_as_float(v[3]));
+            o4.z = pack_bf16x2(__uint_as_float(v[4]), __uint_as_float(v[5]));
+            o4.w = pack_bf16x2(__uint_as_float(v[6]), __uint_as_float(v[7]));
+            __stcg(reinterpret_cast<uint4*>(dst + static_cast<size_t>(g) * 1024), o4);
+          }
+        };
+        uint32_t ra[2][32], rb[2][32];
+        issue(0, ra);
+#pragma unroll 1
+        for (int i = 0; i < kChunks; i += 2) {
+          tmem_ld_wait();
+          if (i + 1 < kChunks) issue(i + 1, rb);
+          store(i, ra);
+          if (i + 1 < kChunks) {
+            tmem_ld_wait();
+            if (i + 2 < kChunks) issue(i + 2, ra);
+            store(i + 1, rb);
           }
         }
         tc_fence_before_sync();
@@ -463,12 +493,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
 
       // 64 accumulator columns [col, col + 64) of row half h for this thread's row: straight from
-      // TMEM, or summed over the slabs of every split
+      // TMEM, or summed over the slabs of every split (landed in shared memory, see below)
+      int unit_acc0 = 0;          // first accumulator column of the unit whose slabs are in shared memory
+      uint32_t unit_bytes = 0;    // bytes of one split's share of that unit
       auto load_acc = [&](int h, int col, float (&a)[64]) __attribute__((always_inline)) {
         if (!fix)
           tmem_load_cols<2>(lane_addr + h * kAccCols + col, a);
         else
-          ws_load_cols<2>(ws_tile + h * ws_half + static_cast<size_t>(col >> 3) * 1024, p.splits, MT * ws_half, a);
+          smem_sum_cols(smem + ((col - unit_acc0) >> 3) * 2048 + (q * 32 + lane) * 16, p.splits, unit_bytes, a);
       };
 
       // with the fix-up the 64-column units of the tile are dealt out over its splits
@@ -477,6 +509,37 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int h = u / units_per_half;
         const int oc = (u - h * units_per_half) * kStageCols;  // first output column inside the tile
         const int width = out_cols - oc < kStageCols ? out_cols - oc : kStageCols;  // 32 or 64
+        if (fix) {
+          // Land every split's share of this unit in the operand ring (idle now: the one work item
+          // of this CTA has been multiplied) with one bulk copy per split, each issued by its own
+          // lane, instead of chains of dependent global loads. A unit of n accumulator columns is
+          // n / 8 column groups of 2 KB, contiguous inside a slab.
+          unit_acc0 = swiglu ? 2 * oc : oc;
+          unit_bytes = static_cast<uint32_t>(swiglu ? 2 * width : width) * 256u;
+          asm volatile("bar.sync 1, 128;" ::: "memory");  // the previous unit has been read out of the ring
+          if (warp == 2) {
+            if (lane == 0) {
+              asm volatile("fence.proxy.async;" ::: "memory");  // slabs and ring were touched by plain stores / loads
+              mbar_arrive_expect_tx(fix_bar, static_cast<uint32_t>(p.splits) * unit_bytes);
+            }
+            __syncwarp();
+            if (lane < p.splits)
+              bulk_load(smem + static_cast<size_t>(lane) * unit_bytes,
+                        p.ws + (static_cast<size_t>(it.tile) * p.splits + lane) * MT * ws_half + h * ws_half +
+                            static_cast<size_t>(unit_acc0 >> 3) * 1024,
+                        unit_bytes, fix_bar);
+          }
+          if (!mbar_wait(fix_bar, fix_phase, spin)) {
+            set_status_once(p.status, kStatusMbarTimeoutEpilogue);
+            s_misc[1] = 0;
+          }
+          fix_phase ^= 1;
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (s_misc[1] == 0) {
+            ok = false;
+            break;
+          }
+        }
         const int row = it.m0 + h * BM + q * 32 + lane;
         const bool row_ok = row < it.rows;
 
@@ -703,6 +766,15 @@ int tiles_of(int M, int N, int bn, int mt) {
 }
 
 }  // namespace
+
+int gemm_max_fixup_splits(int bn, int mt, bool swiglu) {
+  // every split's share of one 64-output-column unit is landed in the operand ring at once
+  const int stages = mt == 2 ? (bn == 64 ? 5 : (bn == 256 ? 3 : 4)) : (bn == 64 ? 8 : (bn == 256 ? 4 : 6));
+  const int ring = stages * (mt * BM * BK * 2 + bn * BK * 2);
+  const int acc_cols = swiglu ? (bn >= 128 ? 128 : bn) : 64;
+  const int s = ring / (acc_cols * 256);
+  return s > 32 ? 32 : s;
+}
 
 size_t gemm_ws_bytes(int M, int N, int bn, int mt, int splits) {
   return static_cast<size_t>(tiles_of(M, N, bn, mt)) * splits * mt * bn * 128 * sizeof(__nv_bfloat16);

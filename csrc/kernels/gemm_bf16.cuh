@@ -34,6 +34,8 @@ struct GemmParams {
   int m_tiles;        // M tiles of 128 * mt rows (grouped mode: upper bound over all groups, mt = 1)
   int epi;
   int act;            // kEpiSwigluBf16: 0 = SiLU, 1 = tanh-GELU
+  int wide_boxes;     // 1: one TMA copy per operand and stage (A box of 256 rows; tile-major B through a
+                      //    4-D map that spans both 128-row weight tiles of a 256-wide tile)
   int b_tiled;        // 1: B is stored tile-major [N/128][K/64][128][64]: every TMA box is one contiguous 16 KB
   void* C;            // kEpiStoreBf16 / kEpiStoreF32 / kEpiSwigluBf16
   long long ldc;
@@ -76,6 +78,9 @@ struct GemmParams {
 // Bytes of partial-tile workspace and number of ticket words a split-K launch with fix-up needs.
 size_t gemm_ws_bytes(int M, int N, int bn, int mt, int splits);
 int gemm_ws_tickets(int M, int N, int bn, int mt);
+// Largest split-K factor the in-kernel fix-up takes for a tile shape (the partial slabs of one
+// output unit are landed in the operand ring together).
+int gemm_max_fixup_splits(int bn, int mt, bool swiglu);
 
 // bn: 64 / 128 / 256 output columns per tile; mt: 1 or 2 row halves of 128 per tile (mt = 2 keeps
 // all 256 rows of a decode batch with the CTA that streams a weight tile).

@@ -29,6 +29,7 @@ def main() -> None:
     ap.add_argument("--mt", default="1", help="comma list of 1/2: 128-row halves per tile (2 = all 256 rows with one CTA)")
     ap.add_argument("--graph", action="store_true", help="time a CUDA-graph replay of the launch (no host launch path in the number)")
     ap.add_argument("--trace", action="store_true", help="print the per-CTA timeline (medians over CTAs, microseconds from kernel entry)")
+    ap.add_argument("--narrow-boxes", action="store_true", help="mt = 2: two 16 KB TMA boxes per operand and stage instead of one 32 KB box")
     ap.add_argument("--auto", action="store_true", help="time the (bn, mt, splits) that ops.pick_decode_cfg chooses")
     ap.add_argument("--fp8", action="store_true", help="time the block-scaled fp8 GEMM (and its activation quantiser)")
     args = ap.parse_args()
@@ -89,7 +90,7 @@ def main() -> None:
         tiles = -(-args.n // bn) * -(-args.m // (128 * mt))
         if sp > 1 and args.epi != ops.EPI_RED_F32 and tiles * sp > ops.sm_count(dev):
             continue
-        kw = dict(bn=bn, splits=sp, mt=mt)
+        kw = dict(bn=bn, splits=sp, mt=mt, wide_boxes=not args.narrow_boxes)
         ww = w_tiled if stag else w
         if args.epi == ops.EPI_RED_F32:
             kw.update(epi=ops.EPI_RED_F32, dst_ptrs=[out_f32.data_ptr()])

@@ -431,14 +431,14 @@ class DeviceModel:
 
     def _gemm_shape(self, m: int, n: int, k: int, *, swiglu: bool = False, routed: bool = False) -> dict:
         """Tile width, rows per tile, split-K factor and split-K mode of one projection. Steps of
-        at most 256 rows (decode batches) keep every row with the CTA that streams a weight tile and
-        split K to fill the SMs, combined inside the kernel; a routed projection on one GPU adds its
-        splits straight into the fp32 accumulator instead. Larger steps use 128-row tiles."""
+        129 to 256 rows (large decode batches) keep every row with the CTA that streams a weight
+        tile and split K to fill the SMs, combined inside the kernel; a routed projection on one GPU
+        adds its splits straight into the fp32 accumulator instead. Other steps use 128-row tiles."""
         key = (m, n, k, swiglu, routed)
         c = self._gemm_cfg.get(key)
         if c is not None:
             return c
-        if m <= 256 and os.environ.get("OXB_DECODE_GEMM", "1") != "0":
+        if 128 < m <= 256 and os.environ.get("OXB_DECODE_GEMM", "1") != "0":
             bn, mt, sp = ops.pick_decode_cfg(m, n, k, swiglu=swiglu, sms=self._sms)
             fixup = sp > 1 and not (routed and self.tp == 1)
         else:

@@ -106,12 +106,15 @@ def pick_splits(m: int, n: int, k: int, bn: int, sms: int = 148) -> int:
 def pick_decode_cfg(m: int, n: int, k: int, *, swiglu: bool = False, sms: int = 148) -> tuple[int, int, int]:
     """(bn, mt, splits) for a GEMM with at most 256 rows against a large weight matrix.
 
-    Such a GEMM is bound by the bytes every SM pulls through its L2 port: a CTA that owns a
-    bn-wide weight tile over a K slice streams (rows + bn) * K_slice * 2 bytes, of which only the
-    bn share is distinct weight data. All rows stay with the CTA that loads the weight tile
-    (mt = 2 above 128 rows) and K is split so that tiles * splits fills the SMs; the splits are
-    combined inside the kernel. The estimate below is time = the slower of the per-SM stream and
-    the HBM stream, plus what the split costs (its partial tiles cross L2 twice).
+    All rows stay with the CTA that loads a weight tile (mt = 2 above 128 rows) and K is split so
+    that tiles * splits fills the SMs; the splits are combined inside the kernel. The choice
+    minimises a cost model fitted to per-CTA timelines measured on a B200 (bench_gemm --trace):
+    a 64-wide k block costs the slower of the CTA's shared-memory traffic (TMA fills plus the
+    operand reads of the MMAs at 128 B/clk), its share of an HBM stream of about 4.5 TB/s and its
+    share of about 10 TB/s between L2 and the SMs; a
+    split costs the store of the partial tile (3 us for 256 x 256), about 1 us at the ticket and
+    3 us (6 us with SwiGLU) per 128 x 64 output unit that the CTA then combines; a direct epilogue
+    costs 1.4 us (2.2 us with SwiGLU) per unit.
     """
     mt = 2 if m > 128 else 1
     rows = 128 * mt
@@ -124,20 +127,38 @@ def pick_decode_cfg(m: int, n: int, k: int, *, swiglu: bool = False, sms: int = 
         if tiles > sms:
             cands = [1]
         else:
-            cands = sorted({1, *(s for s in range(2, min(sms // tiles, kb // 2, 32) + 1))})
+            cap = max_fixup_splits(bn, mt, swiglu)
+            cands = sorted({1, *(s for s in range(2, min(sms // tiles, kb // 2, cap) + 1))})
         for s in cands:
             per = -(-kb // s)
             s_eff = -(-kb // per)
-            waves = -(-tiles * s_eff // sms)
-            stream_us = waves * per * 64 * (rows + bn) * 2 / 100e3      # ~100 GB/s per SM
-            hbm_us = n * k * 2 / 6.0e6
-            fix_us = 0.0 if s_eff == 1 else 3.0 + tiles * s_eff * rows * bn * 2 * 2 / (sms * 100e3)
-            t = max(stream_us, hbm_us) + fix_us
+            n_cta = tiles * s_eff
+            waves = -(-n_cta // sms)
+            smem_us = ((rows + bn) * 128 + 4 * mt * (128 + bn) * 32) / (128 * 1.9e3)
+            hbm_us = min(n_cta, sms) * bn * 128 / 4.5e6
+            l2_us = min(n_cta, sms) * (rows + bn) * 128 / 10e6   # both operands cross the L2 -> SM fabric
+            main_us = waves * per * 1.1 * max(smem_us, hbm_us, l2_us)
+            units = mt * (((bn // 2 if swiglu else bn) + 63) // 64)
+            if s_eff > 1:
+                tail_us = 0.6 + rows * bn * 2 / 55e3 + 1.0 + -(-units // s_eff) * (6.0 if swiglu else 3.0)
+            else:
+                tail_us = waves * units * (2.2 if swiglu else 1.4)
+            t = main_us + tail_us
             if best is None or t < best[0] - 1e-9:
                 best = (t, bn, s_eff)
     if best is None:
         return pick_bn(n, mt), 1, 1
     return best[1], mt, best[2]
+
+
+def max_fixup_splits(bn: int, mt: int, swiglu: bool) -> int:
+    """Largest split-K factor the in-kernel fix-up takes (mirrors gemm_max_fixup_splits in
+    csrc/kernels/gemm_bf16.cu): one split's share of an output unit is 16 KB (32 KB with the SwiGLU
+    epilogue at bn >= 128) and all of them are landed in the operand ring together."""
+    stages = {(2, 64): 5, (2, 128): 4, (2, 256): 3, (1, 64): 8, (1, 128): 6, (1, 256): 4}[(mt, bn)]
+    ring = stages * (mt * 128 * 64 * 2 + bn * 64 * 2)
+    acc_cols = (128 if bn >= 128 else bn) if swiglu else 64
+    return min(32, ring // (acc_cols * 256))
 
 
 _gemm_ws: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
@@ -165,7 +186,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
          ag_expected: int = 0, ag_rows_per_src: int = 0, ag_ticket: Optional[torch.Tensor] = None,
          bn: int = 0, splits: int = 1, act: int = 0, m_tiles: int = 0,
          dst_ld: int = 0, my_rank: int = 0, mt: int = 1, fixup: Optional[bool] = None,
-         trace: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+         trace: Optional[torch.Tensor] = None, wide_boxes: bool = True) -> Optional[torch.Tensor]:
     """tcgen05 GEMM  out = a @ w^T  (bf16 in, fp32 accumulate). See csrc/kernels/gemm_bf16.cu.
     `mt` = 2 keeps 256 rows with one CTA per weight tile; `splits` > 1 with a store / SwiGLU / slab
     epilogue combines the split partial tiles inside the kernel (`fixup`, default on for those)."""
@@ -180,11 +201,23 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
         out = torch.empty(*a.shape[:-1], n_out, dtype=dt, device=a.device)
     if fixup is None:
         fixup = splits > 1 and epi != EPI_RED_F32
+    if fixup and splits > 1:
+        # the launch must be one wave (the splits of a tile wait for each other) and the partial
+        # slabs of one output unit must fit the operand ring
+        K = a.shape[-1]
+        kb = (K + 63) // 64
+        per = -(-kb // min(splits, kb))
+        s_eff = -(-kb // per)
+        tiles = -(-N // bn) * -(-M // (128 * mt))
+        cap = max_fixup_splits(bn, mt, epi == EPI_SWIGLU_BF16)
+        if tiles * s_eff > sm_count(a.device) or s_eff > cap:
+            raise ValueError(f"gemm: {tiles} tiles x {s_eff} splits do not fit one wave of {sm_count(a.device)} SMs "
+                             f"or exceed the fix-up limit of {cap} splits")
     ws, tk = gemm_workspace(a.device) if fixup and splits > 1 else (None, None)
     _ext().gemm_bf16(a, w, epi, out, bias, list(dst_ptrs), list(arrive_ptrs), done_ticket,
                      reset_on_done, rows_per_owner, group_counts, row_meta, ag_flags, ag_expected,
                      ag_rows_per_src, ag_ticket, status_word(a.device), bn, splits, act, m_tiles, dst_ld,
-                     my_rank, 1 if tiled else 0, mt, ws, tk, SPIN_LIMIT, trace)
+                     my_rank, 1 if tiled else 0, mt, ws, tk, SPIN_LIMIT, trace, 1 if wide_boxes else 0)
     _bump()
     return out
 

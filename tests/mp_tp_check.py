@@ -25,26 +25,31 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     ok = True
-    for name in sys.argv[1:] or ["tiny", "tiny-moe", "tiny-fp8", "tiny-h2o"]:
+    for name in sys.argv[1:] or ["tiny", "tiny-moe", "tiny-fp8", "tiny-h2o", "tiny-b160"]:
         fp8 = name.endswith("-fp8")
         h2o = name.endswith("-h2o")
-        base = name[:-4] if (fp8 or h2o) else name
-        if world > 2:
+        big = name.endswith("-b160")   # 160 sequences decode together: the 256-row GEMM tiles with in-kernel split-K
+        base = name[:-4] if (fp8 or h2o) else (name[:-5] if big else name)
+        if big:
+            mc = preset(base, n_heads=8, n_kv_heads=8, d_model=512, ffn_dim=1024, head_dim=64)
+        elif world > 2:
             mc = preset(base, n_heads=8, n_kv_heads=8, d_model=256, ffn_dim=512, head_dim=64)
         elif fp8:
             mc = preset(base, d_model=256, ffn_dim=512, head_dim=64)
         else:
             mc = preset(base)
         src = SyntheticSource(mc, seed=3, std=0.08)
-        cfg = EngineConfig(tp=world, max_num_seqs=8, max_num_batched_tokens=256, num_kv_blocks=256,
-                           ctx_size=1024, graph_buckets=(8,), cuda_graph=True,
+        cfg = EngineConfig(tp=world, max_num_seqs=192 if big else 8, max_num_batched_tokens=2048 if big else 256,
+                           num_kv_blocks=1024 if big else 256, sla_budget=not big,
+                           ctx_size=1024, graph_buckets=(192,) if big else (8,), cuda_graph=True,
                            weight_mode="fp8" if fp8 else "auto",
                            **(dict(h2o_pruning=True, h2o_budget_blocks=5, h2o_sink_blocks=1, h2o_rolling_blocks=2,
                                    enable_radix=False) if h2o else {}))
         eng = LLMEngine(cfg, mc, weights=src, rank=rank, world=world, device=dev)
         rng = np.random.default_rng(1)
-        prompts = [rng.integers(3, mc.vocab_size, size=n).tolist() for n in (4, 33, 100, 17)]
-        outs = eng.generate(prompts, SamplingParams(greedy=True, max_tokens=12, ignore_eos=True))
+        lens = rng.integers(3, 24, size=160).tolist() if big else (4, 33, 100, 17)
+        prompts = [rng.integers(3, mc.vocab_size, size=n).tolist() for n in lens]
+        outs = eng.generate(prompts, SamplingParams(greedy=True, max_tokens=6 if big else 12, ignore_eos=True))
         torch.cuda.synchronize()
         eng.check_device_status()
         gathered = [None] * world
@@ -57,6 +62,8 @@ def main():
                     assert all(len(o) == 12 for o in outs) and eng.stats.get("h2o_pruned_blocks", 0) > 0
                 else:
                     assert_consistent(mc, src, prompts, outs, **(dict(tol=0.6, min_exact=0.5) if fp8 else {}))
+                if big:
+                    assert eng.stats["graph_replays"] >= 3, "the 160-row decode steps did not run as graph replays"
                 print(f"TP_CHECK {name} world={world} OK replays={eng.stats['graph_replays']}", flush=True)
             except AssertionError as e:
                 ok = False

@@ -132,7 +132,7 @@ def test_gemm_swiglu_epilogue(ops):
 
 @pytest.mark.parametrize("m,n,k,bn,splits,tiled", [
     (256, 1024, 1024, 256, 1, False), (256, 768, 2048, 128, 1, True), (200, 512, 512, 64, 1, False),
-    (256, 1024, 2048, 256, 4, False), (130, 640, 4096, 128, 5, False), (256, 1280, 8192, 128, 13, True),
+    (256, 1024, 2048, 256, 4, False), (130, 640, 4096, 128, 5, False), (256, 1280, 8192, 128, 12, True), (256, 1280, 8192, 64, 7, True),
     (255, 1000, 1024, 256, 3, False), (600, 512, 1024, 256, 2, False), (64, 1024, 4096, 256, 6, False),
 ])
 def test_gemm_full_m_tiles_and_in_kernel_splitk(ops, m, n, k, bn, splits, tiled):
@@ -159,7 +159,7 @@ def test_gemm_full_m_tiles_and_in_kernel_splitk(ops, m, n, k, bn, splits, tiled)
 
 
 @pytest.mark.parametrize("m,i,k,bn,splits", [(256, 1792, 2048, 256, 5), (256, 512, 1024, 128, 1),
-                                              (192, 3584, 1024, 256, 5), (96, 1024, 2048, 64, 4)])
+                                              (192, 3584, 1024, 256, 5), (96, 1024, 2048, 64, 4), (256, 3584, 8192, 256, 5)])
 def test_gemm_swiglu_full_m_splitk(ops, m, i, k, bn, splits):
     torch.manual_seed(22)
     a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16) * 0.5
@@ -171,6 +171,15 @@ def test_gemm_swiglu_full_m_splitk(ops, m, i, k, bn, splits):
     ops.check_status()
     ref = torch.nn.functional.silu(a.float() @ wg.float().T) * (a.float() @ wu.float().T)
     assert out.shape == (m, i) and _rel_err(out, ref) < 2e-2
+
+
+def test_gemm_rejects_splits_that_do_not_fit_one_wave(ops):
+    a = torch.randn(256, 1024, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(7168, 1024, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="one wave"):
+        ops.gemm(a, w, epi=ops.EPI_SWIGLU_BF16, bn=256, mt=2, splits=6)   # 28 tiles x 6 > 148 SMs
+    with pytest.raises(RuntimeError, match="K mismatch"):
+        ops.gemm(a, w[:, :512].contiguous(), bn=128)
 
 
 def test_gemm_slab_full_m_splitk_reduce_scatter_emulated(ops):
