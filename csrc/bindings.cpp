@@ -329,7 +329,7 @@ void paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
   p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
   p.status = opt_ptr<int>(status);  // given only when bounds checking is on
   p.num_blocks = p.status != nullptr ? static_cast<int>(k_cache.size(0)) : 0;
-  oxb::launch_paged_decode(p, static_cast<int>(batch), D, cur_stream());
+  (void)oxb::launch_paged_decode(p, static_cast<int>(batch), D, cur_stream());
   check_launch("paged_decode");
 }
 

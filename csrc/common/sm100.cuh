@@ -95,6 +95,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
 __device__ __forceinline__ void set_status_once(int* status, int code) {
   if (status != nullptr) atomicCAS(status, 0, code);
 }
+// A peer-flag time-out is a root cause: it replaces the mbarrier time-outs (codes 1..3) that the
+// warps waiting on the stalled producer may have recorded first, but not an index error.
+__device__ __forceinline__ void set_status_peer_timeout(int* status) {
+  if (status == nullptr) return;
+  int seen = *reinterpret_cast<volatile int*>(status);
+  while (seen >= 0 && seen < kStatusPeerFlagTimeout) {
+    const int old = atomicCAS(status, seen, static_cast<int>(kStatusPeerFlagTimeout));
+    if (old == seen) break;
+    seen = old;
+  }
+}
 // The spin budget a kernel uses: the value in its parameter block, or the compile-time default
 // when that is 0.
 __device__ __forceinline__ uint32_t spin_budget(uint32_t from_params) {

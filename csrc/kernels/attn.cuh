@@ -28,7 +28,10 @@ struct DecodeAttnParams {
   int* status;
 };
 
-void launch_paged_decode(const DecodeAttnParams& p, int batch, int head_dim, cudaStream_t stream);
+// Launches the split kernel and then the merge; the merge is skipped when the first launch failed.
+// Coverage rule: pages_per_split * max_splits pages must cover the longest attended window, a
+// split beyond max_splits does not exist and its tokens would be left out.
+cudaError_t launch_paged_decode(const DecodeAttnParams& p, int batch, int head_dim, cudaStream_t stream);
 
 struct PrefillAttnParams {
   const __nv_bfloat16* q;  // [T, Hq, D] ragged over sequences, row stride q_stride

@@ -72,7 +72,12 @@ paged_decode_kernel(const DecodeAttnParams p) {
 
   const int seq_len = p.seq_lens[seq];
   const int win_start = (p.window > 0 && seq_len > p.window) ? seq_len - p.window : 0;
-  const int n_pages = (seq_len + kPage - 1) / kPage;
+  int n_pages = (seq_len + kPage - 1) / kPage;
+  if (n_pages > p.max_blocks) {
+    // a length beyond the block-table row: recorded, and the walk stops at the end of the row
+    if (p.status != nullptr && threadIdx.x == 0) atomicCAS(p.status, 0, 5 /* kStatusBadIndex */);
+    n_pages = p.max_blocks;
+  }
   const int pps = *p.pages_per_split;
   const int first_page = win_start / kPage;
   const int pg_lo = first_page + split * pps;
@@ -130,7 +135,7 @@ paged_decode_kernel(const DecodeAttnParams p) {
   // a block id outside the pool is recorded and replaced by block 0 (never dereferenced)
   auto checked = [&](int b) -> int {
     if (p.num_blocks > 0 && static_cast<unsigned>(b) >= static_cast<unsigned>(p.num_blocks)) {
-      if (p.status != nullptr && lane == 0) atomicExch(p.status, 5 /* kStatusBadIndex */);
+      if (p.status != nullptr && lane == 0) atomicCAS(p.status, 0, 5 /* kStatusBadIndex */);
       return 0;
     }
     return b;
@@ -306,7 +311,7 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const DecodeAttnParams 
 
 }  // namespace
 
-void launch_paged_decode(const DecodeAttnParams& p, int batch, int head_dim, cudaStream_t stream) {
+cudaError_t launch_paged_decode(const DecodeAttnParams& p, int batch, int head_dim, cudaStream_t stream) {
   const int G = p.Hq / p.Hkv;
   dim3 grid(batch, p.Hkv, p.max_splits);
   dim3 mgrid(batch, p.Hq);
@@ -315,14 +320,20 @@ void launch_paged_decode(const DecodeAttnParams& p, int batch, int head_dim, cud
       paged_decode_kernel<128, 1><<<grid, kWarps * 32, 0, stream>>>(p);
     else
       paged_decode_kernel<128, 2><<<grid, kWarps * 32, 0, stream>>>(p);
-    decode_merge_kernel<128><<<mgrid, 128, 0, stream>>>(p);
   } else {
     if (G <= 8)
       paged_decode_kernel<64, 1><<<grid, kWarps * 32, 0, stream>>>(p);
     else
       paged_decode_kernel<64, 2><<<grid, kWarps * 32, 0, stream>>>(p);
-    decode_merge_kernel<64><<<mgrid, 64, 0, stream>>>(p);
   }
+  // a failed first launch leaves the partials stale: do not merge them into `out`
+  const cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return e;
+  if (head_dim == 128)
+    decode_merge_kernel<128><<<mgrid, 128, 0, stream>>>(p);
+  else
+    decode_merge_kernel<64><<<mgrid, 64, 0, stream>>>(p);
+  return cudaPeekAtLastError();
 }
 
 }  // namespace oxb

@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const Fi
       const uint32_t limit = spin_budget(p.spin_limit);
       while (ld_acquire_sys_u32(p.arrive) < p.expected) {
         if (++it > limit) {
-          set_status_once(p.status, kStatusPeerFlagTimeout);
+          set_status_peer_timeout(p.status);
           ok = 0;
           break;
         }

@@ -115,7 +115,7 @@ __device__ bool wait_sources(const GemmParams& p, int s_lo, int s_hi, uint32_t w
     uint32_t it = 0;
     while (ld_acquire_sys(p.ag_flags + s) < p.ag_expected) {
       if (++it > limit) {
-        set_status_once(p.status, kStatusPeerFlagTimeout);
+        set_status_peer_timeout(p.status);
         ok = false;
         break;
       }
@@ -477,7 +477,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint32_t n = 0;
           while (ld_acquire_gpu(arrived) < static_cast<uint32_t>(p.splits)) {
             if (++n > spin) {
-              set_status_once(p.status, kStatusPeerFlagTimeout);
+              set_status_peer_timeout(p.status);
               met = 0;
               break;
             }

@@ -236,7 +236,7 @@ __global__ void quant_act_fp8_kernel(const __nv_bfloat16* x, long long x_ld, uin
           if (v >= w.expected) break;
         } while (++it <= OXB_SPIN_LIMIT);
         if (v < w.expected) {
-          atomicExch(w.status, kStatusPeerFlagTimeout);
+          set_status_peer_timeout(w.status);
           ok = 0;
         }
       }

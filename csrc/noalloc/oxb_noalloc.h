@@ -17,7 +17,22 @@
  * any stream capture.
  *
  * Limits: batch * hq * max_splits * (head_dim + 2) + 64 floats must fit into the scratch; a larger
- * request is rejected with OXB_NOALLOC_TOO_LARGE before anything is launched.
+ * request is rejected with OXB_NOALLOC_TOO_LARGE before anything is launched. hkv and max_splits
+ * are grid dimensions and may not exceed 65535.
+ *
+ * What is checked on the host, before any launch: null pointers, the shape rules below, 16-byte
+ * alignment of q, k_cache, v_cache and out (the kernels use 16-byte loads and stores), q_stride and
+ * out_stride a multiple of 8 elements and at least hq * head_dim, the size limit above (computed
+ * without overflow). What is checked on the device: every block id read from a block table is
+ * compared with num_blocks and a sequence length is cut at max_blocks * 16 tokens; a violation
+ * reads block 0 / stops at the end of the table row instead of touching memory outside the pool,
+ * and is reported through `status` when that pointer is given (the word is set to 5 once and is
+ * otherwise left alone; the caller zeroes it).
+ *
+ * Coverage: split z of a sequence attends pages [first + z * pages_per_split, + pages_per_split),
+ * so pages_per_split * max_splits * 16 must be at least the longest attended window (the longest
+ * sequence, or `window` + 15 tokens with a sliding window). Tokens beyond that are left out of the
+ * result without any error: the lengths live in device memory and are not known to this call.
  *
  * Sharing: all calls on a device use the same scratch, which keeps the previous call's
  * contents. The kernels overwrite every entry they later read, so nothing has to be cleared
@@ -43,16 +58,19 @@ extern "C" {
  * v_cache     [num_blocks, hkv, 16, head_dim] bf16
  * block_tables[batch, max_blocks] int32, seq_lens [batch] int32 (device memory)
  * out         [batch, hq * head_dim] bf16, rows out_stride elements apart
- * pages_per_split >= 1 pages of 16 tokens per KV split, max_splits = grid depth
+ * num_blocks  blocks in the cache pool: bound for the ids in block_tables
+ * pages_per_split >= 1 pages of 16 tokens per KV split, max_splits = grid depth (see Coverage)
  * scale       softmax scale (1/sqrt(head_dim)); window = sliding window in tokens, 0 = none
  * stream      a cudaStream_t (NULL = default stream)
+ * status      optional device int32 that receives 5 when a block id or a length was out of range
  * err/err_len optional buffer that receives a message when the return value is not OXB_NOALLOC_OK
  */
 int oxb_paged_decode_noalloc(const void* q, long long q_stride, const void* k_cache,
                              const void* v_cache, const int* block_tables, const int* seq_lens,
                              void* out, long long out_stride, int batch, int hq, int hkv,
-                             int head_dim, int max_blocks, int pages_per_split, int max_splits,
-                             int window, float scale, void* stream, char* err, int err_len);
+                             int head_dim, int num_blocks, int max_blocks, int pages_per_split,
+                             int max_splits, int window, float scale, void* stream, int* status,
+                             char* err, int err_len);
 
 #ifdef __cplusplus
 }

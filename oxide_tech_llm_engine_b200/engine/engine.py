@@ -184,6 +184,8 @@ class LLMEngine:
         self.sampled_val = torch.zeros(self.model.max_logits, dtype=torch.float32, device=self.device)
         self.sampled_host = torch.zeros(self.model.max_logits, dtype=torch.int32,
                                         pin_memory=torch.cuda.is_available())
+        # the kernels' status word rides home with the sampled ids of every step
+        self.status_host = torch.zeros(1, dtype=torch.int32, pin_memory=torch.cuda.is_available())
         self.requests: dict[int, RequestState] = {}
         self._next_id = 0
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
@@ -500,7 +502,7 @@ class LLMEngine:
         for rid in list(self.requests.keys()):
             ok, ev = self.sched.cancel(rid)
             for e in ev:
-                self._deliver(e)
+                self._deliver(_Event(int(e.req_id), -1, True, reason))
                 events.append(e)
         self.degraded = reason
         return events
@@ -626,9 +628,30 @@ class LLMEngine:
 
     def _fetch(self, n_rows: int) -> np.ndarray:
         self.sampled_host[:n_rows].copy_(self.sampled[:n_rows], non_blocking=True)
+        self.status_host.copy_(ops.status_word(self.device), non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
-        self.stats["d2h_bytes"] += 4 * n_rows
+        self.stats["d2h_bytes"] += 4 * n_rows + 4
+        if int(self.status_host[0]) != 0:
+            self._device_fault(int(self.status_host[0]))
         return self.sampled_host[:n_rows].numpy().copy()
+
+    def _device_fault(self, code: int) -> None:
+        """A kernel's bounded wait ran out (a peer never arrived) or an index check failed: the
+        step's tokens cannot be trusted. Every request ends with a typed reason, all KV blocks go
+        back to the pool, the hand-off counters are re-armed and the engine is marked degraded; the
+        error is raised to the caller (the context stays usable, new requests may be served)."""
+        from ..errors import CollectiveTimeout
+
+        ops.status_word(self.device).zero_()
+        reason = "collective_timeout" if code == 4 else f"device_error_{code}"
+        self.fail_all(reason)
+        self.model.reset_sync_state()
+        self.stats["degraded"] = True
+        self.stats["device_faults"] = self.stats.get("device_faults", 0) + 1
+        msg = ops.STATUS_NAMES.get(code, f"code {code}")
+        if code == 4:
+            raise CollectiveTimeout(f"device wait expired during a step: {msg}")
+        raise EngineError(f"kernel reported during a step: {msg}")
 
     # ------------------------------------------------------------------ events
     def _deliver(self, e) -> None:

@@ -822,5 +822,21 @@ class DeviceModel:
         self.logits[:logits.shape[0]] = logits
         return self.logits[:n_log]
 
+    def reset_sync_state(self) -> None:
+        """Re-arms every counter of the hand-off protocol on this rank (arrival / all-gather flags,
+        tickets, split-K tickets, MoE slot counters). Used after a device wait ran out: waiters that
+        gave up leave tickets part-way and a late peer may still bump a flag. Every rank of the group
+        calls it between steps, with none of its kernels in flight."""
+        torch.cuda.synchronize(self.device)
+        self.ws.local("flags").zero_()
+        self.tickets.zero_()
+        if self.cfg.is_moe:
+            self.ws.local("cnt").zero_()
+        ops.gemm_workspace(self.device)[1].zero_()
+        for name in ("acc0", "acc1"):
+            self.ws.local(name).zero_()
+        self.qkv_acc.zero_()
+        torch.cuda.synchronize(self.device)
+
     def close(self) -> None:
         self.ws.close()

@@ -239,3 +239,30 @@ def test_h2o_pruning_on_device_scores():
     assert len(out) == 48 and out[:first_pruned_at] == ref[:first_pruned_at]
     assert eng.sched.num_free_blocks() == free0
     eng.close()
+
+
+def test_a_device_wait_that_ran_out_degrades_the_engine_and_returns_every_block():
+    """The status word that a kernel sets when a bounded wait expires is read with the sampled ids
+    of the step: requests end with a typed reason, blocks go back to the pool, the hand-off
+    counters are re-armed, and the engine serves again afterwards."""
+    from oxide_tech_llm_engine_b200 import ops
+    from oxide_tech_llm_engine_b200.errors import CollectiveTimeout
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    eng, mc, src = _mk("tiny", enable_radix=False)
+    free0 = eng.sched.num_free_blocks()
+    sp = SamplingParams(greedy=True, max_tokens=8, ignore_eos=True)
+    want = eng.generate([[5, 6, 7, 8, 9]], sp)[0]
+    rids = [eng.add_request(list(range(3, 3 + n)), sp) for n in (20, 7)]
+    eng.step()
+    ops.status_word(eng.device).fill_(4)      # what a kernel writes when its peer never arrived
+    with pytest.raises(CollectiveTimeout):
+        eng.step()
+    assert all(eng.requests[r].finished and eng.requests[r].finish_reason == "collective_timeout" for r in rids)
+    assert eng.sched.num_free_blocks() == free0 and not eng.has_work()
+    assert eng.stats["degraded"] and eng.stats["device_faults"] == 1
+    assert int(ops.status_word(eng.device).item()) == 0
+    assert int(eng.model.tickets.abs().max().item()) == 0
+    again = eng.generate([[5, 6, 7, 8, 9]], sp)[0]
+    assert again == want
+    eng.close()

@@ -388,6 +388,68 @@ def test_finalize_norm(ops, rows, n):
     assert _rel_err(y, _rms(res, w, 1e-6, 1.0)) < 1.5e-2
 
 
+def test_device_waits_that_run_out_return_a_status_and_leave_the_context_usable(ops):
+    """A wait on a counter that nothing bumps (the stand-in for a peer that never arrives) gives
+    up after its spin budget: the kernel returns, the status word says 'peer flag', check_status
+    raises CollectiveTimeout exactly once, and the same call works once the counters are re-armed."""
+    from oxide_tech_llm_engine_b200.errors import CollectiveTimeout
+
+    torch.manual_seed(31)
+    old = ops.SPIN_LIMIT
+    ops.SPIN_LIMIT = 3000
+    try:
+        # --- reduce-scatter tail: finalize_norm waits for arrivals that never come ---
+        rows, n = 8, 1024
+        acc = torch.randn(rows, n, device=DEV)
+        acc0 = acc.clone()
+        res = torch.randn(rows, n, device=DEV, dtype=torch.bfloat16)
+        w = torch.rand(n, device=DEV, dtype=torch.bfloat16) + 0.5
+        out = torch.zeros_like(res)
+        arrive = torch.zeros(1, dtype=torch.int32, device=DEV)
+        ticket = torch.zeros(1, dtype=torch.int32, device=DEV)
+        kw = dict(rows=rows, n=n, acc=acc, arrive=arrive, expected=1, ticket=ticket, residual_in=res, norm_w=w,
+                  eps=1e-5, out_ptrs=[out.data_ptr()])
+        ops.finalize_norm(**kw)
+        torch.cuda.synchronize()
+        with pytest.raises(CollectiveTimeout):
+            ops.check_status()
+        ops.check_status()                                   # reported once, then clean
+        assert out.abs().max().item() == 0.0                 # nothing was produced from missing data
+        assert torch.equal(acc, acc0)                        # and the accumulator was not consumed
+        assert int(arrive.item()) == 0 and int(ticket.item()) == 0   # this wait leaves nothing to re-arm
+        arrive.fill_(1)                                      # the arrival comes after all
+        ops.finalize_norm(**kw)
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert _rel_err(out, _rms(acc0 + res.float(), w, 1e-5)) < 1.5e-2
+        assert int(arrive.item()) == 0                       # consumed and re-armed by the kernel
+
+        # --- all-gather -> GEMM: the producer waits for source rows that never arrive; the MMA and
+        # epilogue warps then run out of their own waits and the kernel frees its TMEM and returns ---
+        m, nn, k = 256, 512, 1024
+        a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+        wt = torch.randn(nn, k, device=DEV, dtype=torch.bfloat16)
+        o = torch.zeros(m, nn, device=DEV, dtype=torch.bfloat16)
+        flags = torch.zeros(2, dtype=torch.int32, device=DEV)
+        agt = torch.zeros(1, dtype=torch.int32, device=DEV)
+        gkw = dict(out=o, bn=128, ag_flags=flags, ag_expected=128, ag_rows_per_src=128, ag_ticket=agt)
+        ops.gemm(a, wt, **gkw)
+        torch.cuda.synchronize()
+        with pytest.raises(CollectiveTimeout):
+            ops.check_status()
+        ops.check_status()
+        # re-arm: the waiters that gave up left the ticket part-way; the owner zeroes flags and ticket
+        agt.zero_()
+        flags.fill_(128)
+        ops.gemm(a, wt, **gkw)
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert _rel_err(o, a.float() @ wt.float().T) < 1.5e-2
+        assert flags.tolist() == [0, 0] and int(agt.item()) == 0
+    finally:
+        ops.SPIN_LIMIT = old
+
+
 def test_finalize_norm_moe_dispatch(ops):
     torch.manual_seed(8)
     rows, n, E, top_k, cap = 50, 1024, 8, 2, 64
