@@ -11,6 +11,11 @@ pinned-host H2D of the step descriptor -> forward -> device sampler -> D2H of th
 `value` is tokens/s from CUDA-event device time of the K steps (max over ranks); `e2e.value` is the
 same K steps by wall clock through the public API. Weights (>= 17 GB per GPU) are far larger than
 L2, so nothing is served from cache between steps.
+
+Around the timed region, untimed: an open-loop phase (a few requests arriving as a Poisson process
+at a stated rate on the idle engine: p50 / p99 time to first token without queueing behind 255
+other prompts), and a check of the fused path against the library-GEMM + NCCL all-reduce path on
+the same state (`tokens_match_baseline`).
 """
 from __future__ import annotations
 
@@ -108,6 +113,8 @@ def main() -> None:
                          "the headline number is bf16")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
                     help="nccl: comparison path with library GEMMs and NCCL all-reduces")
+    ap.add_argument("--open-loop", type=int, default=12, help="requests of the open-loop TTFT phase (0 = skip)")
+    ap.add_argument("--check-steps", type=int, default=2, help="decode steps compared against the baseline path (0 = skip)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
@@ -151,6 +158,49 @@ def main() -> None:
     torch.cuda.synchronize()
     rng = np.random.default_rng(1234)  # same request stream on every rank
     sp = SamplingParams(greedy=True, max_tokens=args.output_len, ignore_eos=True)
+
+    # ---- untimed: open-loop time to first token on the idle engine ----
+    # Poisson arrivals at `rate` requests/s (same seeded schedule on every rank; arrival times are
+    # compared with rank 0's clock, broadcast each iteration, so every rank admits the same requests
+    # before the same step). Each request decodes 4 tokens and leaves.
+    open_loop = None
+    if args.open_loop > 0:
+        rate = min(4.0, 0.5 * world)
+        gaps = rng.exponential(1.0 / rate, size=args.open_loop)
+        arrivals = np.cumsum(gaps)
+        prompts = [rng.integers(0, mc.vocab_size, size=int(rng.integers(args.prompt_min, args.prompt_max + 1)),
+                                dtype=np.int64).tolist() for _ in range(args.open_loop)]
+        sp_ol = SamplingParams(greedy=True, max_tokens=4, ignore_eos=True)
+        clock = torch.zeros(1, dtype=torch.float64, device=dev)
+        t_start = time.perf_counter()
+        nxt, ids, sched_at = 0, [], {}
+        while nxt < args.open_loop or eng.has_work():
+            now = time.perf_counter() - t_start
+            if world > 1:
+                clock[0] = now
+                dist.broadcast(clock, src=0)
+                now = float(clock[0])
+            while nxt < args.open_loop and arrivals[nxt] <= now:
+                rid = eng.add_request(prompts[nxt], sp_ol)
+                sched_at[rid] = arrivals[nxt]
+                ids.append(rid)
+                nxt += 1
+            if eng.has_work():
+                eng.step()
+            else:
+                time.sleep(min(0.002, max(0.0, arrivals[nxt] - now)))
+        # TTFT against the scheduled arrival time (includes the wait for the step in flight)
+        ol = sorted((eng.requests[r].t_first_token - t_start - sched_at[r]) * 1e3 for r in ids
+                    if eng.requests[r].t_first_token is not None)
+        open_loop = {"requests": len(ol), "rate_req_per_s": rate,
+                     "ttft_p50_ms": round(ol[len(ol) // 2], 1) if ol else None,
+                     "ttft_p99_ms": round(ol[min(len(ol) - 1, int(len(ol) * 0.99))], 1) if ol else None}
+        for r in ids:
+            eng.requests.pop(r, None)
+        eng.stats["prefill_tokens"] = 0
+        eng.stats["decode_tokens"] = 0
+
+    t_submit = time.perf_counter()
     for _ in range(args.requests):
         n = int(rng.integers(args.prompt_min, args.prompt_max + 1))
         eng.add_request(rng.integers(0, mc.vocab_size, size=n, dtype=np.int64).tolist(), sp)
@@ -171,6 +221,11 @@ def main() -> None:
     for _ in range(args.warmup):
         eng.step()
     eng.check_device_status()
+    # ---- untimed: the fused path against library GEMMs + NCCL all-reduces on the same state ----
+    check = eng.compare_with_baseline(args.check_steps) if (args.check_steps > 0 and args.comm == "fused") else {"steps": 0}
+    torch.cuda.empty_cache()
+    for _ in range(2):
+        eng.step()  # back to steady state (the comparison ran its steps outside the graphs)
 
     def barrier():
         if world > 1:
@@ -192,6 +247,7 @@ def main() -> None:
         batch_sizes.append(len(events))
     barrier()
     wall = time.perf_counter() - t0
+    whole_wall = time.perf_counter() - t_submit
     clocks = sampler.stop() if sampler else {}
     eng.check_device_status()
     # latency view of the same run: time to first token of every admitted request (all arrive at
@@ -233,6 +289,14 @@ def main() -> None:
                 "ttft_p50_ms": round(ttft[len(ttft) // 2], 1) if ttft else None,
                 "ttft_p99_ms": round(ttft[min(len(ttft) - 1, int(len(ttft) * 0.99))], 1) if ttft else None,
                 "tpot_p50_ms": round(statistics.median(a.elapsed_time(b) for a, b in ev), 3),
+                "ttft_note": "ttft_p50/p99 above are closed-loop: all requests arrive at t=0 and queue behind each other",
+                "open_loop": open_loop,
+                # from the first submission to the end of the timed steps: prefill, warm-up, the baseline check and decode
+                "whole_run": {"wall_s": round(whole_wall, 2), "prompt_tokens": int(prefill_tokens),
+                              "generated_tokens": int(sum(r.n_generated for r in eng.requests.values())),
+                              "generated_tok_per_s": round(sum(r.n_generated for r in eng.requests.values()) / whole_wall, 1)},
+                "tokens_match_baseline": (f"{check['tokens_equal']}/{check['tokens']}" if check.get("tokens") else None),
+                "baseline_check": check,
             },
             "clocks": clocks,
             "e2e": {"value": round(e2e, 2), "unit": "tokens/s", "ms_per_step": round(wall_ms / args.steps, 4),
@@ -240,6 +304,11 @@ def main() -> None:
                     "d2h_bytes_per_step": int((eng.stats["d2h_bytes"] - d2h0) / args.steps)},
             "gpu_launches": int(launches),
         }
+        conc = out["config"]["concurrent_decoding"]
+        if conc < args.requests:
+            out["n1_note"] = (f"the KV pool beside the weights holds {conc} of the {args.requests} requests at once on "
+                              f"{world} GPU(s); runs on more GPUs decode all {args.requests} together, so throughput ratios "
+                              f"against this run compare different batch sizes")
         print(json.dumps(out), flush=True)
     eng.close()
     if world > 1:

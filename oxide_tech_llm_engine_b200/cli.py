@@ -78,7 +78,8 @@ def add_common(p: argparse.ArgumentParser) -> None:
     p.add_argument("--system")
     p.add_argument("--chat-format", default="auto")
     p.add_argument("--continuous-batching", action="store_true")
-    p.add_argument("--tp", type=int, default=1)
+    p.add_argument("--tp", type=int, default=1, help="tensor / expert parallel ranks (one process per GPU, started through torch.distributed.run)")
+    p.add_argument("--dp", type=int, default=1, help="data-parallel engine replicas behind one front (tp = 1: one GPU each, in this process)")
     p.add_argument("--max-batched-tokens", type=int, default=2048)
     p.add_argument("--no-cuda-graph", action="store_true")
     p.add_argument("--no-radix", action="store_true")
@@ -141,7 +142,7 @@ def engine_config_from_args(args) -> EngineConfig:
     return EngineConfig.from_env(
         model=args.model, alias=args.alias, models_dir=args.models_dir, ctx_size=args.ctx_size,
         max_num_seqs=args.max_slots, num_kv_blocks=args.kv_device_blocks, seed=args.seed, backend=be,
-        weight_mode=args.weights, speculative=spec, draft_tokens=args.draft_tokens, tp=args.tp,
+        weight_mode=args.weights, speculative=spec, draft_tokens=args.draft_tokens, tp=args.tp, dp=args.dp,
         max_num_batched_tokens=args.max_batched_tokens, cuda_graph=not args.no_cuda_graph,
         enable_radix=not args.no_radix)
 
@@ -154,8 +155,49 @@ def sampling_from_args(args):
                           seed=args.seed, max_tokens=args.max_tokens, greedy=args.greedy)
 
 
+class Job:
+    """What this process is in a multi-rank serving job (`--tp N` under torch.distributed.run):
+    rank, world, the NCCL (or gloo, CPU backend) group of the engine ranks, the gloo control group
+    that carries the commands, the job store and this rank's heartbeat."""
+
+    def __init__(self, backend: str):
+        import torch
+        import torch.distributed as dist
+
+        from .parallel import front
+        from .parallel.watchdog import Heartbeat
+
+        self.rank, self.world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if backend == "cuda":
+            torch.cuda.set_device(self.local)
+            self.device = torch.device("cuda", self.local)
+            dist.init_process_group("nccl", device_id=self.device)
+        else:
+            self.device = torch.device("cpu")
+            dist.init_process_group("gloo")
+        self.group = dist.group.WORLD
+        self.ctl = front.make_control_group()
+        self.store = front.job_store()
+        self.heartbeat = Heartbeat(self.store, self.rank, period_s=0.2).start()
+
+    def close(self) -> None:
+        import torch.distributed as dist
+
+        self.heartbeat.stop()
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+_job: Optional[Job] = None
+
+
 def load_model(name: str, path: Optional[str], cfg: EngineConfig):
-    """Builds engine + tokenizer + handle for a checkpoint path or a catalog preset."""
+    """Builds engine + tokenizer + handle for a checkpoint path or a catalog preset. In a
+    multi-rank job (see `Job`) every rank builds its shard; rank 0 gets the handle that broadcasts
+    commands, the others get a plain handle-less record and run `front.follower_loop`. With
+    `dp > 1` (and tp = 1) one engine per GPU is built in this process behind a `DpHandle`."""
     from .engine.engine import LLMEngine
     from .engine.handle import EngineHandle
     from .engine.model_manager import LoadedModel
@@ -175,9 +217,75 @@ def load_model(name: str, path: Optional[str], cfg: EngineConfig):
         tok = None
     if tok is None:
         tok = Tokenizer.ascii_fallback(mc.vocab_size)
+    if _job is not None:
+        from .parallel.front import DistributedEngineHandle
+        from .parallel.watchdog import RankMonitor
+
+        if getattr(_job, "model_loaded", False):
+            raise ConfigError("a multi-rank job serves the model it was started with (no hot swap: the "
+                              "follower ranks only follow rank 0's request stream)")
+        _job.model_loaded = True
+
+        eng = LLMEngine(cfg, mc, weights=src, rank=_job.rank, world=1 if cfg.backend == "cpu" else _job.world,
+                        group=_job.group, device=_job.device if cfg.backend != "cpu" else None)
+        eng.set_tokenizer(tok)
+        if _job.rank != 0:
+            return LoadedModel(name, path, None, tok, mc), eng
+        monitor = RankMonitor(_job.store, 0, _job.world, timeout_s=5.0)
+        handle = DistributedEngineHandle(eng, _job.ctl, _job.world, monitor=monitor, heartbeat=_job.heartbeat,
+                                         store=_job.store)
+        return LoadedModel(name, path, handle, tok, mc)
+    if cfg.dp > 1:
+        import torch
+
+        from .parallel.dp_router import DpHandle
+
+        if cfg.tp != 1:
+            raise ConfigError("--dp replicas are built for tp = 1 (one GPU per replica in this process)")
+        handles = []
+        for i in range(cfg.dp):
+            if cfg.backend == "cpu":
+                eng = LLMEngine(cfg, mc, weights=src)
+            else:
+                if i >= torch.cuda.device_count():
+                    raise ConfigError(f"--dp {cfg.dp} needs {cfg.dp} GPUs, {torch.cuda.device_count()} visible")
+                with torch.cuda.device(i):
+                    eng = LLMEngine(cfg, mc, weights=src, device=torch.device("cuda", i))
+            eng.set_tokenizer(tok)
+            handles.append(EngineHandle(eng))
+        return LoadedModel(name, path, DpHandle(handles), tok, mc)
     eng = LLMEngine(cfg, mc, weights=src)
     eng.set_tokenizer(tok)
     return LoadedModel(name, path, EngineHandle(eng), tok, mc)
+
+
+def run_follower(cfg: EngineConfig) -> int:
+    """A rank other than 0 of a multi-rank job: builds its shard of the default model and follows
+    rank 0's command stream until shut-down."""
+    from .engine.model_manager import ModelManager
+    from .parallel.front import follower_loop
+
+    mgr = ModelManager(lambda n, p: None, cfg.models_dir)
+    path = mgr.resolve_path(cfg.model)
+    _, eng = load_model(cfg.model, path, cfg)
+    try:
+        follower_loop(eng, _job.ctl, heartbeat=_job.heartbeat, store=_job.store, rank=_job.rank)
+    finally:
+        eng.close()
+    return 0
+
+
+def relaunch_under_torchrun(argv: list[str], n: int) -> int:
+    """`--tp N` outside a launcher: start N ranks of this same command line on this node."""
+    import socket
+    import subprocess
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "oxide_tech_llm_engine_b200", *argv]
+    return subprocess.call(cmd)
 
 
 def make_manager(cfg: EngineConfig):
@@ -369,7 +477,24 @@ def main(argv: Optional[list[str]] = None) -> int:
     if args.command == "quantize":
         return run_quantize(args)
     cfg = engine_config_from_args(args)
-    print(cfg.describe(), file=sys.stderr)
+    global _job
+    if cfg.tp > 1:
+        if args.command != "server" and not getattr(args, "serve", False):
+            print("error: --tp > 1 is for the server (chat / bench / verify drive one GPU)", file=sys.stderr)
+            return 2
+        if "RANK" not in os.environ:
+            return relaunch_under_torchrun(normalize_argv(list(sys.argv[1:] if argv is None else argv)), cfg.tp)
+        if int(os.environ["WORLD_SIZE"]) != cfg.tp:
+            print(f"error: --tp {cfg.tp} but the launcher started {os.environ['WORLD_SIZE']} ranks", file=sys.stderr)
+            return 2
+        _job = Job(cfg.backend)
+        if _job.rank != 0:
+            try:
+                return run_follower(cfg)
+            finally:
+                _job.close()
+    if _job is None or _job.rank == 0:
+        print(cfg.describe(), file=sys.stderr)
     try:
         mgr = make_manager(cfg)
     except EngineError as ex:
@@ -386,6 +511,8 @@ def main(argv: Optional[list[str]] = None) -> int:
     finally:
         for m in list(mgr.models.values()):
             m.handle.shutdown(timeout=2.0)
+        if _job is not None:
+            _job.close()
 
 
 if __name__ == "__main__":

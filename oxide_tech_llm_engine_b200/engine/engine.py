@@ -406,20 +406,21 @@ class LLMEngine:
         return s, bucket
 
     def _forward(self, s: StepInputs, bucket: Optional[int]) -> torch.Tensor:
-        if self.cfg.comm == "nccl" or self.cfg.gemm == "library":
-            # baseline path: eager library GEMMs + NCCL collectives (torch allocates, so no graphs)
-            return self.model.forward_baseline(s)
+        baseline = self.cfg.comm == "nccl" or self.cfg.gemm == "library"
+        # baseline path: library GEMMs + NCCL all-reduces; decode buckets are captured in a CUDA graph
+        # like the fused path (torch's graph-private pool serves its temporaries)
+        fwd = self.model.forward_baseline if baseline else self.model.forward
         if bucket is None:
-            return self.model.forward(s)
+            return fwd(s)
         g = self.graphs.get(bucket)
         if g is None:
             # warm-up launches outside capture (lazy module init, TMA descriptor cache), then capture
-            self.model.forward(s)
+            fwd(s)
             torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
             c0 = ops.launch_count
             with torch.cuda.graph(g):
-                self.model.forward(s)
+                fwd(s)
             self.graph_launches[bucket] = ops.launch_count - c0
             self.graphs[bucket] = g
             # the capture did not execute; the warm-up run already produced this step's state
@@ -490,6 +491,40 @@ class LLMEngine:
                                             cfg.h2o_budget_blocks)
             if keep:
                 self.stats["h2o_pruned_blocks"] = self.stats.get("h2o_pruned_blocks", 0) + len(blocks) - len(keep)
+
+    def compare_with_baseline(self, n_steps: int = 2) -> dict:
+        """Runs `n_steps` decode steps twice from the same state: through the fused path and through
+        the library-GEMM + NCCL all-reduce path, and compares the sampled tokens and the logits.
+        The fused result is the one the scheduler advances with. Used by bench.py as evidence that
+        the fused multi-rank path computes what the plain one does."""
+        if self.cpu or self.model.weight_mode != "bf16" or self.model_cfg.is_moe or self.pp is not None:
+            return {"steps": 0}
+        same = total = 0
+        worst = 0.0
+        for _ in range(n_steps):
+            plan = self.sched.schedule()
+            for e in self.sched.take_events():
+                self._deliver(e)
+            if plan.n_tokens == 0:
+                break
+            s, _ = self._fill(plan)
+            n_rows = plan.logit_rows.size
+            logits = self.model.forward(s)
+            ref_fused = logits.clone()
+            tok_fused = self._sample(plan, logits, n_rows).copy()
+            logits_b = self.model.forward_baseline(s)     # same inputs: the KV append rewrites equal values
+            ref_base = logits_b.clone()
+            tok_base = self._sample(plan, logits_b, n_rows)
+            same += int((tok_fused == tok_base).sum())
+            total += int(n_rows)
+            scale_ = float(ref_base[:n_rows].abs().max().clamp_min(1e-6))
+            worst = max(worst, float((ref_fused[:n_rows] - ref_base[:n_rows]).abs().max()) / scale_)
+            for e in self.sched.update(plan, tok_fused):
+                self._deliver(e)
+            self.stats["steps"] += 1
+            self.stats["decode_tokens"] += plan.n_decode
+            self.stats["prefill_tokens"] += plan.prefill_tokens
+        return {"steps": n_steps, "tokens_equal": same, "tokens": total, "max_logit_diff_rel": round(worst, 5)}
 
     def attach_monitor(self, monitor) -> None:
         """`monitor.check()` (parallel.watchdog.RankMonitor) runs before every step: a peer that

@@ -143,7 +143,17 @@ class EngineHandle:
                 self._stop.set()
                 return got
 
+    def _bind_device(self) -> None:
+        """The current CUDA device is per thread: the worker adopts the engine's (a process may hold
+        several engines on different GPUs, e.g. data-parallel replicas)."""
+        dev = getattr(self.engine, "device", None)
+        if dev is not None and getattr(dev, "type", "cpu") == "cuda":
+            import torch
+
+            torch.cuda.set_device(dev)
+
     def _run(self) -> None:
+        self._bind_device()
         idle = 0
         while not self._stop.is_set():
             busy = self._drain()

@@ -783,6 +783,7 @@ class DeviceModel:
             raise ConfigError("the NCCL + library-GEMM baseline covers dense bf16 models")
         M = s.m
         eps, off = cfg.rms_eps, cfg.norm_weight_offset
+        rowmajor = ops.untile_weight  # the fused path keeps weights tile-major; a library GEMM reads rows
 
         def norm(x, w):
             xf = x.float()
@@ -791,32 +792,37 @@ class DeviceModel:
         x = (self.embed[s.token_ids[:M].long()].float() * cfg.emb_scale).to(torch.bfloat16)
         for li, L in enumerate(self.layers):
             h = norm(x, L["attn_norm"])
-            qkv = F.linear(h, L["w_qkv"])
+            qkv = F.linear(h, rowmajor(L["w_qkv"]))
             ops.qkv_rope_append(qkv_bf16=qkv, bias=L["b_qkv"], q_norm_w=L["q_norm"], k_norm_w=L["k_norm"],
                                 norm_eps=1e-6, norm_w_offset=off, positions=s.positions, slot_mapping=s.slot_mapping,
                                 inv_freq=self.inv_freq, rope_mscale=self.rope_mscale, q_out=self.q_buf,
                                 k_cache=self.k_cache[li], v_cache=self.v_cache[li], m=M, hq=self.hq, hkv=self.hkv,
                                 d=self.D)
             self._attention(s, li)
-            o = F.linear(self.attn_out[:M], L["w_o"])
+            o = F.linear(self.attn_out[:M], rowmajor(L["w_o"]))
             if tp > 1:
                 dist.all_reduce(o, group=self.group)
             x = x + o
             h = norm(x, L["ffn_norm"])
-            gu = F.linear(h, L["w_gu"]).view(M, self.i_l // 32, 2, 32)
+            gu = F.linear(h, rowmajor(L["w_gu"])).view(M, self.i_l // 32, 2, 32)
             gate, up = gu[:, :, 0].reshape(M, self.i_l), gu[:, :, 1].reshape(M, self.i_l)
             a = (F.gelu(gate.float(), approximate="tanh") if self._act_code else F.silu(gate.float())) * up.float()
-            dn = F.linear(a.to(torch.bfloat16), L["w_down"])
+            dn = F.linear(a.to(torch.bfloat16), rowmajor(L["w_down"]))
             if tp > 1:
                 dist.all_reduce(dn, group=self.group)
             x = x + dn
         n_log = max(s.n_logits, 1)
-        rows = torch.nonzero(s.logit_map[:M] >= 0).flatten()
-        if rows.numel() == 0:
-            rows = torch.zeros(1, dtype=torch.long, device=self.device)
-        order = torch.argsort(s.logit_map[:M][rows])
-        hl = norm(x[rows[order]], self.out_norm)
-        logits = F.linear(hl, self.lm_head).float()
+        if s.n_logits == M:
+            # decode bucket: every row has a logits row, in order (no host round trip, so the step
+            # can be captured in a CUDA graph)
+            hl = norm(x, self.out_norm)
+        else:
+            rows = torch.nonzero(s.logit_map[:M] >= 0).flatten()
+            if rows.numel() == 0:
+                rows = torch.zeros(1, dtype=torch.long, device=self.device)
+            order = torch.argsort(s.logit_map[:M][rows])
+            hl = norm(x[rows[order]], self.out_norm)
+        logits = F.linear(hl, rowmajor(self.lm_head)).float()
         if cfg.logit_softcap > 0:
             logits = cfg.logit_softcap * torch.tanh(logits / cfg.logit_softcap)
         self.logits[:logits.shape[0]] = logits

@@ -227,6 +227,8 @@ def create_app(manager, *, allow_queueing: bool = True) -> FastAPI:
             stream = submit(m, toks, sp)
         except SlotsExhausted:
             return _busy()
+        except EngineError as ex:  # the engine group is down (a rank left): no request can be served
+            return _error(503, str(ex), "server_error")
         rid = f"chatcmpl-oxide-{next(_req_counter)}"
         name = body.get("model") or m.name
         if body.get("stream"):
@@ -254,6 +256,8 @@ def create_app(manager, *, allow_queueing: bool = True) -> FastAPI:
             stream = submit(m, toks, sp)
         except SlotsExhausted:
             return _busy()
+        except EngineError as ex:  # the engine group is down (a rank left): no request can be served
+            return _error(503, str(ex), "server_error")
         rid = f"cmpl-oxide-{next(_req_counter)}"
         name = body.get("model") or m.name
         if body.get("stream"):
@@ -352,6 +356,8 @@ def create_app(manager, *, allow_queueing: bool = True) -> FastAPI:
             stream = submit(m, toks, sp)
         except SlotsExhausted:
             return JSONResponse(status_code=529, content={"type": "error", "error": {"type": "overloaded_error", "message": "All inference slots busy"}})
+        except EngineError as ex:
+            return JSONResponse(status_code=503, content={"type": "error", "error": {"type": "api_error", "message": str(ex)}})
         mid = f"msg_oxide_{next(_req_counter)}"
         name = body.get("model") or m.name
         if body.get("stream"):

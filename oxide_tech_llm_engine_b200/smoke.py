@@ -27,6 +27,17 @@ def run_smoke() -> None:
     eng.check_device_status()
     assert all(len(o) == 8 for o in outs), outs
     assert ops.launch_count > 0
+    # against the fp32 CPU oracle fed the engine's own tokens: every generated token must be the
+    # oracle's argmax or a near tie (bf16 activations), and most must be the argmax itself
+    from .models.reference import ReferenceModel
+
+    src = SyntheticSource(mc, seed=3, std=0.08)
+    gaps = []
+    for prompt, out in zip(prompts, outs):
+        logits = ReferenceModel(mc, src).forward(list(prompt) + list(out[:-1]), all_logits=True)[len(prompt) - 1:]
+        gaps += [float((logits[i].max() - logits[i][t]) / logits[i].std()) for i, t in enumerate(out)]
+    exact = sum(g == 0.0 for g in gaps) / len(gaps)
+    assert max(gaps) < 0.3 and exact >= 0.6, f"tokens differ from the fp32 oracle: max gap {max(gaps):.3f}, exact {exact:.2f}"
     print(f"smoke ok: {ops.launch_count} kernel launches, graph replays {eng.stats['graph_replays']}, "
-          f"tokens {outs[0]}")
+          f"{exact:.2f} of {len(gaps)} tokens equal the fp32 oracle's argmax (max gap {max(gaps):.3f}), tokens {outs[0]}")
     eng.close()

@@ -46,3 +46,61 @@ def test_context_parallel_attention_over_nccl_matches_full_attention(what, token
            "--master-addr", "127.0.0.1", "--master-port", "29513", os.path.join(here, "mp_cpu_parallel.py"), what]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and token in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_http_server_over_a_tensor_parallel_engine():
+    """`server --tp 2`: the CLI starts two ranks (one per GPU), rank 0 serves HTTP and broadcasts the
+    admitted requests to rank 1 over gloo; a streamed chat completion equals the non-streamed one."""
+    import json
+    import signal
+    import socket
+    import time
+    import urllib.request
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=root)
+    proc = subprocess.Popen([sys.executable, "-m", "oxide_tech_llm_engine_b200", "server", "-m", "tiny", "--tp", "2",
+                             "--port", str(port), "--max-slots", "8", "-c", "512", "--kv-device-blocks", "256"],
+                            env=env, cwd=root, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                            start_new_session=True)
+    base = f"http://127.0.0.1:{port}"
+    try:
+        up = False
+        for _ in range(240):
+            if proc.poll() is not None:
+                break
+            try:
+                up = urllib.request.urlopen(base + "/health", timeout=1).status == 200
+                if up:
+                    break
+            except Exception:
+                time.sleep(0.5)
+        assert up, "server did not come up: " + (proc.stdout.read()[-3000:] if proc.poll() is not None else "")
+        body = {"model": "tiny", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 10, "temperature": 0}
+
+        def post(b):
+            req = urllib.request.Request(base + "/v1/chat/completions", data=json.dumps(b).encode(),
+                                         headers={"Content-Type": "application/json"})
+            return urllib.request.urlopen(req, timeout=120).read().decode()
+        whole = json.loads(post(body))["choices"][0]["message"]["content"]
+        text = ""
+        for line in post(dict(body, stream=True)).splitlines():
+            if line.startswith("data: ") and line != "data: [DONE]":
+                text += json.loads(line[6:])["choices"][0]["delta"].get("content", "")
+        assert text == whole and len(whole) > 0
+        m = urllib.request.urlopen(base + "/metrics", timeout=5).read().decode()
+        assert "oxide_up 1" in m
+    finally:
+        try:
+            os.killpg(proc.pid, signal.SIGTERM)   # the process group this test started, nothing else
+        except ProcessLookupError:
+            pass
+        try:
+            proc.wait(timeout=30)
+        except subprocess.TimeoutExpired:
+            os.killpg(proc.pid, signal.SIGKILL)

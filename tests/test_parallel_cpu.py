@@ -181,3 +181,28 @@ def test_dp_handle_serves_over_two_cpu_replicas():
     finally:
         dp.shutdown()
         single.shutdown()
+
+
+@pytest.mark.parametrize("mode", ["stream", "leave"])
+def test_http_front_over_two_engine_ranks(mode):
+    """`server --tp 2` on CPU ranks: rank 0 serves HTTP and broadcasts the admitted requests over gloo,
+    rank 1 follows; a rank that leaves between steps ends the requests with `rank_failure` and every
+    KV block returns to the pool."""
+    import os
+    import socket
+    import subprocess
+    import sys
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    here = os.path.dirname(os.path.abspath(__file__))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(here, "mp_front_check.py"), mode]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, OMP_NUM_THREADS="2"))
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-4000:]
+    assert f"FRONT {mode} OK" in out and "FRONT done" in out, out[-4000:]
+    assert "FOLLOWER steps=" in out
+    if mode == "stream":
+        assert "running=0" in out
