@@ -6,10 +6,14 @@
 // the M dimension:  S^T[16 tok x 8 heads] = K_page * Q^T,  O^T[dims x 8 heads] +=
 // V_page^T * P^T  (mma.sync m16n8k16 -- 8 query heads against one page cannot fill
 // a 128-row tcgen05 tile, and this kernel is bound by the KV stream from HBM, which
-// every query head of the group shares). K and V are read with 16-byte loads
-// straight from the page into MMA fragments: the head-dim permutation that makes
-// this possible is applied identically to Q, and V is transposed in registers
-// with byte permutes; P is transposed with movmatrix.
+// every query head of the group shares). Every warp keeps a ring of kRing pages in
+// flight with cp.async (16-byte chunks, XOR-swizzled so that the fragment reads are
+// bank-conflict free): the bytes a warp has outstanding are what sets the rate of a
+// latency-bound stream, and registers cannot hold more than one page. The MMA
+// fragments are read from the ring with 16-byte loads in the pattern of the page
+// itself: the head-dim permutation that makes this possible is applied identically
+// to Q, and V is transposed in registers with byte permutes; P is transposed with
+// movmatrix.
 //
 // A second kernel merges the per-split (max, sum, O) partials.
 //
@@ -20,6 +24,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "../common/device_info.h"
 #include "attn.cuh"
 
 namespace oxb {
@@ -27,7 +32,26 @@ namespace oxb {
 namespace {
 
 constexpr int kPage = 16;
-constexpr int kWarps = 4;  // 104 registers -> 4 CTAs per SM; forcing 5 (96 registers, spills) measured 17 % slower
+constexpr int kWarps = 4;
+constexpr int kRing = 3;   // pages per warp in the shared-memory ring (2 in flight while 1 is consumed)
+
+__device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+// 16-byte chunk c of token row r sits at chunk c ^ swz(r) of that row: the K fragment reads (rows
+// 2k, 2k+1 x 4 chunks per quarter warp) and the V fragment reads (4 rows of equal parity x 2 chunks)
+// then touch 8 different 16-byte bank groups.
+__device__ __forceinline__ int swz(int row) { return (((row >> 1) & 3) << 1) ^ ((row & 1) << 2); }
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                                uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -140,28 +164,79 @@ paged_decode_kernel(const DecodeAttnParams p) {
     }
     return b;
   };
+  // ---- per-warp ring of pages in shared memory ----
+  extern __shared__ __align__(128) uint8_t ring_raw[];
+  constexpr int kRowBytes = D * 2;
+  constexpr int kPageBytes = kPage * kRowBytes;             // K or V of one page
+  constexpr int kChunksPerRow = kRowBytes / 16;
+  constexpr int kChunksPerLane = kPage * kChunksPerRow / 32;  // 16-byte chunks each lane copies per tensor
+  const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(ring_raw)) +
+                        static_cast<uint32_t>(warp) * kRing * 2 * kPageBytes;
+  auto issue = [&](int slot, int b) {
+    const __nv_bfloat16* kp = p.k_cache + static_cast<long long>(b) * page_stride + head_off;
+    const __nv_bfloat16* vp = p.v_cache + static_cast<long long>(b) * page_stride + head_off;
+    const uint32_t dk = ring + static_cast<uint32_t>(slot) * 2 * kPageBytes;
+    const uint32_t dv = dk + kPageBytes;
+#pragma unroll
+    for (int j = 0; j < kChunksPerLane; ++j) {
+      const int c = lane + 32 * j;
+      const int row = c / kChunksPerRow, ch = c % kChunksPerRow;
+      const uint32_t off = static_cast<uint32_t>(row * kRowBytes + ((ch ^ swz(row)) << 4));
+      cp_async_16(dk + off, kp + row * D + ch * 8);
+      cp_async_16(dv + off, vp + row * D + ch * 8);
+    }
+  };
+  // block ids run one page ahead of the copies, the copies kRing - 1 pages ahead of the math
   int page = pg_lo + warp;
-  int blk = page < pg_hi ? checked(bt[page]) : 0;
+  int issue_page = page;
+  int blk_next = issue_page < pg_hi ? checked(bt[issue_page]) : 0;
+#pragma unroll
+  for (int i = 0; i < kRing - 1; ++i) {
+    if (issue_page < pg_hi) {
+      const int b = blk_next;
+      const int np = issue_page + kWarps;
+      blk_next = np < pg_hi ? checked(bt[np]) : 0;
+      issue(i, b);
+    }
+    cp_async_commit();
+    issue_page += kWarps;
+  }
+  int slot = 0;
   for (; page < pg_hi; page += kWarps) {
-    const int next_page = page + kWarps;
-    const int next_blk = next_page < pg_hi ? bt[next_page] : 0;  // checked when it is consumed
-    const __nv_bfloat16* kp = p.k_cache + static_cast<long long>(blk) * page_stride + head_off;
-    const __nv_bfloat16* vp = p.v_cache + static_cast<long long>(blk) * page_stride + head_off;
+    // top up the ring, then wait until the oldest page has landed
+    {
+      int s_new = slot + kRing - 1;
+      if (s_new >= kRing) s_new -= kRing;
+      if (issue_page < pg_hi) {
+        const int b = blk_next;
+        const int np = issue_page + kWarps;
+        blk_next = np < pg_hi ? checked(bt[np]) : 0;
+        issue(s_new, b);
+      }
+      cp_async_commit();
+      issue_page += kWarps;
+    }
+    cp_async_wait<kRing - 1>();
+    __syncwarp();
+    const uint32_t sk = ring + static_cast<uint32_t>(slot) * 2 * kPageBytes;
+    const uint32_t sv = sk + kPageBytes;
 
-    // ---- issue all loads of the page up front ----
+    // ---- fragments of the page ----
     uint4 kr[2][CPL];
 #pragma unroll
-    for (int r = 0; r < 2; ++r)
+    for (int r = 0; r < 2; ++r) {
+      const int row = g + 8 * r;
 #pragma unroll
       for (int ci = 0; ci < CPL; ++ci)
-        kr[r][ci] = __ldg(reinterpret_cast<const uint4*>(kp + (g + 8 * r) * D + (t + 4 * ci) * 8));
+        kr[r][ci] = lds128(sk + row * kRowBytes + (((t + 4 * ci) ^ swz(row)) << 4));
+    }
     uint4 vr[4][VCH];
 #pragma unroll
     for (int tk = 0; tk < 4; ++tk) {
       const int tok = 2 * t + (tk & 1) + 8 * (tk >> 1);
 #pragma unroll
       for (int c = 0; c < VCH; ++c)
-        vr[tk][c] = __ldg(reinterpret_cast<const uint4*>(vp + tok * D + (g + 8 * c) * 8));
+        vr[tk][c] = lds128(sv + tok * kRowBytes + (((g + 8 * c) ^ swz(tok)) << 4));
     }
 
     // ---- S^T = K * Q^T ----
@@ -234,13 +309,16 @@ paged_decode_kernel(const DecodeAttnParams p) {
           mma_bf16_16816(o_acc[nt][4 * c + e], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
       }
     }
-    blk = checked(next_blk);
+    __syncwarp();  // every lane is done with this slot before it is refilled
+    if (++slot == kRing) slot = 0;
   }
+  cp_async_wait<0>();
 
-  // ---- merge the 4 warps through shared memory ----
-  __shared__ float s_o[kWarps][8 * NT][D];
-  __shared__ float s_m[kWarps][8 * NT];
-  __shared__ float s_l[kWarps][8 * NT];
+  // ---- merge the 4 warps through shared memory (the ring is free now) ----
+  __syncthreads();
+  float(*s_o)[8 * NT][D] = reinterpret_cast<float(*)[8 * NT][D]>(ring_raw);
+  float(*s_m)[8 * NT] = reinterpret_cast<float(*)[8 * NT]>(ring_raw + sizeof(float) * kWarps * 8 * NT * D);
+  float(*s_l)[8 * NT] = s_m + kWarps;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     float l0 = l_run[nt][0], l1 = l_run[nt][1];
@@ -311,20 +389,31 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const DecodeAttnParams 
 
 }  // namespace
 
+template <int D, int NT>
+void launch_split(const DecodeAttnParams& p, dim3 grid, cudaStream_t stream) {
+  // the ring (kWarps x kRing pages of K and V) is also the scratch of the warp merge at the end
+  constexpr size_t ring = static_cast<size_t>(kWarps) * kRing * 2 * kPage * D * 2;
+  constexpr size_t merge = sizeof(float) * kWarps * 8 * NT * (D + 2);
+  constexpr size_t smem = ring > merge ? ring : merge;
+  auto kern = paged_decode_kernel<D, NT>;
+  ensure_dynamic_smem(kern, smem);
+  kern<<<grid, kWarps * 32, smem, stream>>>(p);
+}
+
 cudaError_t launch_paged_decode(const DecodeAttnParams& p, int batch, int head_dim, cudaStream_t stream) {
   const int G = p.Hq / p.Hkv;
   dim3 grid(batch, p.Hkv, p.max_splits);
   dim3 mgrid(batch, p.Hq);
   if (head_dim == 128) {
     if (G <= 8)
-      paged_decode_kernel<128, 1><<<grid, kWarps * 32, 0, stream>>>(p);
+      launch_split<128, 1>(p, grid, stream);
     else
-      paged_decode_kernel<128, 2><<<grid, kWarps * 32, 0, stream>>>(p);
+      launch_split<128, 2>(p, grid, stream);
   } else {
     if (G <= 8)
-      paged_decode_kernel<64, 1><<<grid, kWarps * 32, 0, stream>>>(p);
+      launch_split<64, 1>(p, grid, stream);
     else
-      paged_decode_kernel<64, 2><<<grid, kWarps * 32, 0, stream>>>(p);
+      launch_split<64, 2>(p, grid, stream);
   }
   // a failed first launch leaves the partials stale: do not merge them into `out`
   const cudaError_t e = cudaPeekAtLastError();

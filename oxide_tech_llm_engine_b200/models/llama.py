@@ -438,7 +438,10 @@ class DeviceModel:
         c = self._gemm_cfg.get(key)
         if c is not None:
             return c
-        if 128 < m <= 256 and os.environ.get("OXB_DECODE_GEMM", "1") != "0":
+        # the in-kernel split-K costs about 10 us of partial-tile traffic and barrier: it pays for the
+        # large weight streams (gate/up, down), not for the small ones (QKV, O), measured in situ
+        big = n * k * 2 >= (48 << 20)
+        if 128 < m <= 256 and big and os.environ.get("OXB_DECODE_GEMM", "1") != "0":
             bn, mt, sp = ops.pick_decode_cfg(m, n, k, swiglu=swiglu, sms=self._sms)
             fixup = sp > 1 and not (routed and self.tp == 1)
         else:

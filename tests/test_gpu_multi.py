@@ -87,12 +87,15 @@ def test_http_server_over_a_tensor_parallel_engine():
             req = urllib.request.Request(base + "/v1/chat/completions", data=json.dumps(b).encode(),
                                          headers={"Content-Type": "application/json"})
             return urllib.request.urlopen(req, timeout=120).read().decode()
-        whole = json.loads(post(body))["choices"][0]["message"]["content"]
-        text = ""
+        first = json.loads(post(body))
+        whole = first["choices"][0]["message"]["content"]
+        assert first["usage"]["completion_tokens"] == 10     # random weights: the text itself may be unprintable
+        text, chunks = "", []
         for line in post(dict(body, stream=True)).splitlines():
             if line.startswith("data: ") and line != "data: [DONE]":
-                text += json.loads(line[6:])["choices"][0]["delta"].get("content", "")
-        assert text == whole and len(whole) > 0
+                chunks.append(json.loads(line[6:]))
+                text += chunks[-1]["choices"][0]["delta"].get("content", "")
+        assert text == whole and chunks and chunks[-1]["choices"][0]["finish_reason"] == "length"
         m = urllib.request.urlopen(base + "/metrics", timeout=5).read().decode()
         assert "oxide_up 1" in m
     finally:
