@@ -57,10 +57,20 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
                int64_t splits, int64_t act, int64_t m_tiles_override, int64_t dst_ld,
                int64_t my_rank, int64_t b_tiled, int64_t mt, const c10::optional<Tensor>& ws,
                const c10::optional<Tensor>& ws_tickets, int64_t spin_limit,
-               const c10::optional<Tensor>& trace, int64_t wide_boxes) {
+               const c10::optional<Tensor>& trace, int64_t wide_boxes, const c10::optional<Tensor>& sfa,
+               const c10::optional<Tensor>& sfb, const c10::optional<Tensor>& a_gscale,
+               const c10::optional<Tensor>& w_gscale) {
   TORCH_CHECK(a.is_cuda() && w.is_cuda(), "gemm_bf16: CUDA tensors required");
-  TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16,
-              "gemm_bf16: bf16 operands required");
+  // NVFP4: a and w hold e2m1 values packed two per byte ([.., K / 2] uint8) with block scales sfa / sfb
+  const bool fp4 = sfa.has_value() && sfa->defined();
+  if (fp4) {
+    TORCH_CHECK(a.scalar_type() == torch::kUInt8 && w.scalar_type() == torch::kUInt8 && sfb.has_value() &&
+                    sfb->defined() && sfa->scalar_type() == torch::kUInt8 && sfb->scalar_type() == torch::kUInt8,
+                "gemm (nvfp4): packed uint8 operands and uint8 scale atoms required");
+  } else {
+    TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16,
+                "gemm_bf16: bf16 operands required");
+  }
   TORCH_CHECK(a.stride(-1) == 1 && w.stride(-1) == 1, "gemm_bf16: K must be contiguous");
   TORCH_CHECK(b_tiled == 0 || !(group_counts.has_value() && group_counts->defined()),
               "gemm_bf16: grouped GEMMs take row-major weights");
@@ -74,23 +84,32 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
   }
   const int64_t G = grouped3d ? a.size(0) : 1;
   const int64_t M = grouped3d ? a.size(1) : a.size(0);
-  const int64_t K = a.size(-1);
+  // K in operand elements of 2 bytes for the tile arithmetic below: a row of the packed fp4 operands
+  // has K / 2 bytes = K / 4 such units, and one 128-byte k block covers 256 fp4 values
+  const int64_t K = fp4 ? a.size(-1) / 2 : a.size(-1);
   const int64_t N = tiled ? w.size(0) * 128 : (grouped3d ? w.size(1) : w.size(0));
-  TORCH_CHECK(tiled ? w.size(1) * 64 == K : w.size(-1) == K, "gemm_bf16: K mismatch");
+  TORCH_CHECK(tiled ? w.size(1) * 64 == K : w.size(-1) == a.size(-1), "gemm_bf16: K mismatch");
   TORCH_CHECK(K % 8 == 0, "gemm_bf16: K must be a multiple of 8 (16-byte TMA rows)");
+  if (fp4) {
+    TORCH_CHECK(!tiled && a.size(-1) % 128 == 0, "gemm (nvfp4): K must be a multiple of 256, row-major weights");
+  }
   if (grouped3d) {
     TORCH_CHECK(w.size(0) == G, "gemm_bf16: group mismatch");
   }
 
-  const uint64_t a_row = static_cast<uint64_t>(a.stride(-2)) * 2;
-  const uint64_t w_row = tiled ? 128 : static_cast<uint64_t>(w.stride(-2)) * 2;
-  const uint64_t a_grp = grouped3d ? static_cast<uint64_t>(a.stride(0)) * 2 : a_row * M;
-  const uint64_t w_grp = tiled ? 16384 : (grouped3d ? static_cast<uint64_t>(w.stride(0)) * 2 : w_row * N);
+  const uint64_t eb = fp4 ? 1 : 2;  // bytes per tensor element
+  const uint64_t a_row = static_cast<uint64_t>(a.stride(-2)) * eb;
+  const uint64_t w_row = tiled ? 128 : static_cast<uint64_t>(w.stride(-2)) * eb;
+  const uint64_t a_grp = grouped3d ? static_cast<uint64_t>(a.stride(0)) * eb : a_row * M;
+  const uint64_t w_grp = tiled ? 16384 : (grouped3d ? static_cast<uint64_t>(w.stride(0)) * eb : w_row * N);
   const int bn_i = bn == 64 ? 64 : (bn == 256 ? 256 : 128);
   // decode tiles (mt = 2): one copy per operand and stage instead of two 16 KB boxes each
   const bool wide = mt == 2 && !grouped3d && wide_boxes != 0;
-  CUtensorMap tmA = oxb::make_tma_map(a.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, K, M, G,
-                                      a_row, a_grp, 64, wide ? 256 : 128, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+  const CUtensorMapDataType dt = fp4 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const uint64_t k_inner = fp4 ? static_cast<uint64_t>(a.size(-1)) : static_cast<uint64_t>(K);  // elements of the map's type
+  const uint32_t box_inner = fp4 ? 128 : 64;
+  CUtensorMap tmA = oxb::make_tma_map(a.data_ptr(), dt, static_cast<int>(eb), 3, k_inner, M, G,
+                                      a_row, a_grp, box_inner, wide ? 256 : 128, 1, CU_TENSOR_MAP_SWIZZLE_128B);
   const uint64_t total_kb_u = static_cast<uint64_t>((K + 63) / 64);
   CUtensorMap tmB =
       (tiled && wide && bn_i == 256)
@@ -100,8 +119,8 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
       : tiled ? oxb::make_tma_map(w.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, 64, 128,
                                 static_cast<uint64_t>(w.size(0) * w.size(1)), 128, 16384, 64,
                                 bn_i < 128 ? bn_i : 128, 1, CU_TENSOR_MAP_SWIZZLE_128B)
-            : oxb::make_tma_map(w.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, K, N, G, w_row,
-                                w_grp, 64, bn_i, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+            : oxb::make_tma_map(w.data_ptr(), dt, static_cast<int>(eb), 3, k_inner, N, G, w_row,
+                                w_grp, box_inner, bn_i, 1, CU_TENSOR_MAP_SWIZZLE_128B);
 
   oxb::GemmParams p{};
   p.M = static_cast<int>(M);
@@ -117,6 +136,27 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
   p.b_tiled = static_cast<int>(b_tiled);
   p.wide_boxes = wide ? 1 : 0;
   p.spin_limit = static_cast<uint32_t>(spin_limit > 0 ? spin_limit : 0);
+  if (fp4) {
+    TORCH_CHECK(bn == 128 && mt != 2, "gemm (nvfp4): 128 x 128 tiles");
+    p.kind = 1;
+    p.kb_total = static_cast<int>(a.size(-1) / 128);
+    const int64_t row_tiles = ((grouped3d ? a.size(1) : M) + 127) / 128;
+    TORCH_CHECK(!grouped3d || a.size(1) % 128 == 0, "gemm (nvfp4): grouped slabs need a multiple of 128 rows per group");
+    TORCH_CHECK(sfa->numel() >= G * row_tiles * p.kb_total * 2048 && sfa->is_contiguous(), "gemm (nvfp4): sfa too small");
+    TORCH_CHECK(sfb->numel() >= G * ((N + 127) / 128) * p.kb_total * 2048 && sfb->is_contiguous(), "gemm (nvfp4): sfb too small");
+    p.sfa = sfa->data_ptr<uint8_t>();
+    p.sfb = sfb->data_ptr<uint8_t>();
+    p.sfa_group_tiles = row_tiles;
+    if (a_gscale.has_value() && a_gscale->defined()) {
+      TORCH_CHECK(a_gscale->scalar_type() == torch::kFloat32 && a_gscale->numel() >= G * M, "gemm (nvfp4): a_gscale");
+      p.a_gscale = a_gscale->data_ptr<float>();
+      p.a_gs_stride = M;
+    }
+    if (w_gscale.has_value() && w_gscale->defined()) {
+      TORCH_CHECK(w_gscale->scalar_type() == torch::kFloat32 && w_gscale->numel() >= G, "gemm (nvfp4): w_gscale");
+      p.w_gscale = w_gscale->data_ptr<float>();
+    }
+  }
   if (trace.has_value() && trace->defined()) {
     TORCH_CHECK(trace->scalar_type() == torch::kInt64 && trace->numel() >= 8 * oxb::sm_count(),
                 "gemm_bf16: trace must hold 8 int64 per SM");
@@ -204,6 +244,27 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
 }
 
 // a8: [M, K] e4m3 bytes; sa_t: [ceil(K/128), >= M] fp32; w8: [N, K] e4m3 bytes; sw: [ceil(N/128), ceil(K/128)].
+// x: [rows, K] or [G, cap, K] bf16 -> q [.., K/2] uint8, sf (scale atoms), gscale [rows] fp32
+void quant_act_nvfp4(const Tensor& x, const Tensor& q, const Tensor& sf, const Tensor& gscale,
+                     const c10::optional<Tensor>& group_counts) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.stride(-1) == 1, "quant_act_nvfp4: bf16 rows");
+  const int64_t K = x.size(-1);
+  TORCH_CHECK(K % 64 == 0, "quant_act_nvfp4: K must be a multiple of 64");
+  const int64_t G = x.dim() == 3 ? x.size(0) : 1;
+  const int64_t R = x.size(-2);
+  TORCH_CHECK(x.dim() == 2 || x.stride(0) == R * x.stride(1), "quant_act_nvfp4: groups must be dense");
+  TORCH_CHECK(G == 1 || R % 128 == 0, "quant_act_nvfp4: grouped rows must be a multiple of 128 per group");
+  const int64_t tiles = (G * R + 127) / 128;
+  TORCH_CHECK(q.scalar_type() == torch::kUInt8 && q.is_contiguous() && q.numel() >= G * R * K / 2, "quant_act_nvfp4: q");
+  TORCH_CHECK(sf.scalar_type() == torch::kUInt8 && sf.is_contiguous() && sf.numel() >= tiles * (K / 64) * 512,
+              "quant_act_nvfp4: sf too small");
+  TORCH_CHECK(gscale.scalar_type() == torch::kFloat32 && gscale.numel() >= G * R, "quant_act_nvfp4: gscale");
+  oxb::launch_quant_act_nvfp4(reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), x.stride(-2), q.data_ptr<uint8_t>(),
+                              sf.data_ptr<uint8_t>(), gscale.data_ptr<float>(), static_cast<int>(G),
+                              static_cast<int>(R), static_cast<int>(K), opt_ptr<uint32_t>(group_counts), cur_stream());
+  check_launch("quant_act_nvfp4");
+}
+
 void gemm_fp8_block(const Tensor& a8, const Tensor& sa_t, const Tensor& w8, const Tensor& sw,
                     const c10::optional<Tensor>& out_opt, const c10::optional<Tensor>& bias,
                     const Tensor& status, const std::vector<int64_t>& slab_ptrs,
@@ -745,6 +806,7 @@ Tensor tensor_from_ptr(int64_t ptr, const std::vector<int64_t>& shape, const std
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "sm_100a kernels of the B200-native Oxide engine";
   m.def("gemm_bf16", &gemm_bf16);
+  m.def("quant_act_nvfp4", &quant_act_nvfp4);
   m.def("gemm_max_fixup_splits", &oxb::gemm_max_fixup_splits);
   m.def("gemm_fp8_block", &gemm_fp8_block);
   m.def("quant_act_fp8", &quant_act_fp8);

@@ -221,6 +221,39 @@ __device__ __forceinline__ void tc_mma_f8(uint32_t tmem_d, uint64_t desc_a, uint
       : "memory");
 }
 
+// Block-scaled fp4: D[tmem] (+)= (A * SFA) * (B * SFB)^T with A, B = e2m1 values packed two per byte
+// (K-major, 64 values = 32 bytes per instruction) and one ue4m3 scale per 16 values of K, read from
+// TMEM (`sfa` / `sfb` = TMEM addresses of 4 scale bytes per row: column c of the 32-lane block holds
+// rows 32c .. 32c+31, replicated over the four lane quarters by tc_cp_scales).
+__device__ __forceinline__ void tc_mma_nvfp4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                             uint32_t idesc, uint32_t accumulate, uint32_t sfa,
+                                             uint32_t sfb) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+      "}\n"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
+// Copies one 512-byte scale atom (32 rows x 16 bytes in shared memory: row r = scales of matrix
+// rows r, r+32, r+64, r+96, four bytes each) into 4 TMEM columns, broadcast to all lane quarters.
+__device__ __forceinline__ void tc_cp_scales(uint32_t tmem_dst, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(smem_desc) : "memory");
+}
+// Shared-memory descriptor of an unswizzled K-major block of 8-row x 16-byte core matrices stacked
+// 128 bytes apart (the scale atom above).
+__device__ __forceinline__ uint64_t make_desc_scales(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;            // leading byte offset (one 16-byte column: unused)
+  d |= static_cast<uint64_t>(128 >> 4) << 32;     // stride between groups of 8 rows
+  d |= static_cast<uint64_t>(1) << 46;            // descriptor version (sm_100)
+  return d;                                        // layout type 0: no swizzle
+}
+
 // 32 lanes x 32 columns of 32-bit accumulators: thread t of the warp gets lane
 // (lane_base + t), columns [col, col+32).
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -311,6 +344,13 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t a_fmt, uint32_t b_fmt
          | (b_major << 16)      // b_major
          | ((n >> 3) << 17)     // n_dim
          | ((m >> 4) << 24);    // m_dim
+}
+
+// Instruction descriptor of the block-scaled fp4 MMA (kind::mxf4nvf4): e2m1 operands (format 1),
+// ue4m3 scales (scale format 0), both K-major, scale ids 0. There is no accumulator-format field
+// in this layout (bits 4..5 hold the scale id of B).
+__host__ __device__ constexpr uint32_t make_idesc_nvfp4(uint32_t m, uint32_t n) {
+  return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 // ---------------------------------------------------------------------------

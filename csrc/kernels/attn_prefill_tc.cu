@@ -127,43 +127,46 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, DH * kHalfBytes);
-      for (int hf = 0; hf < DH; ++hf)
-        tma_load_2d(sQ + hf * kHalfBytes, &tmQ, q_full, head * D + hf * 64, row_base + q0);
+    // The whole warp issues: a KV tile is 8 pages x DH halves x {K, V} = up to 32 boxes of 2 KB,
+    // and copies issued by ONE thread complete about one per memory round trip (their rate grows
+    // with the number of issuing threads, not with the number in flight), which would bound a tile
+    // at several microseconds against half a microsecond of MMA work. Lane = (tensor, page, half).
+    {
+      if (lane == 0) mbar_arrive_expect_tx(q_full, DH * kHalfBytes);
+      __syncwarp();
+      if (lane < DH) tma_load_2d(sQ + lane * kHalfBytes, &tmQ, q_full, head * D + lane * 64, row_base + q0);
       const int* bt = p.block_tables + static_cast<long long>(seq) * p.max_blocks;
+      constexpr int kOps = 2 * (BKV / 16) * DH;  // 32 (D = 128) or 16 (D = 64)
+      const bool issuer = lane < kOps;
+      const int is_v = lane / (kOps / 2);
+      const int pg = (lane % (kOps / 2)) / DH;
+      const int hf = lane % DH;
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j & 1;
-        if (j >= 2 && !mbar_wait(&kv_empty[s], ((j >> 1) - 1) & 1)) {
-          set_status_once(status, kStatusMbarTimeoutProducer);
-          ok = false;
+        if (j >= 2 && !mbar_wait(&kv_empty[s], ((j >> 1) - 1) & 1)) ok = false;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) set_status_once(status, kStatusMbarTimeoutProducer);
           break;
         }
-        const int page0 = (first_tile + j) * (BKV / 16);
-        mbar_arrive_expect_tx(&k_full[s], DH * kHalfBytes);
-        for (int pg = 0; pg < BKV / 16; ++pg) {
-          const int pi = page0 + pg;
-          int blk = pi < p.max_blocks ? bt[pi] : 0;
-          if (p.num_blocks > 0 && static_cast<unsigned>(blk) >= static_cast<unsigned>(p.num_blocks)) {
-            set_status_once(status, kStatusBadIndex);
-            blk = 0;
-          }
-          const int row = (blk * p.Hkv + kvh) * 16;
-          for (int hf = 0; hf < DH; ++hf)
-            tma_load_2d(sK + (s * DH + hf) * kHalfBytes + pg * 2048, &tmK, &k_full[s], hf * 64, row);
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&k_full[s], DH * kHalfBytes);
+          mbar_arrive_expect_tx(&v_full[s], DH * kHalfBytes);
         }
-        mbar_arrive_expect_tx(&v_full[s], DH * kHalfBytes);
-        for (int pg = 0; pg < BKV / 16; ++pg) {
-          const int pi = page0 + pg;
+        __syncwarp();
+        if (issuer) {
+          const int pi = (first_tile + j) * (BKV / 16) + pg;
           int blk = pi < p.max_blocks ? bt[pi] : 0;
           if (p.num_blocks > 0 && static_cast<unsigned>(blk) >= static_cast<unsigned>(p.num_blocks)) {
             set_status_once(status, kStatusBadIndex);
             blk = 0;
           }
           const int row = (blk * p.Hkv + kvh) * 16;
-          for (int hf = 0; hf < DH; ++hf)
+          if (is_v)
             tma_load_2d(sV + (s * DH + hf) * kHalfBytes + pg * 2048, &tmV, &v_full[s], hf * 64, row);
+          else
+            tma_load_2d(sK + (s * DH + hf) * kHalfBytes + pg * 2048, &tmK, &k_full[s], hf * 64, row);
         }
       }
     }

@@ -159,11 +159,16 @@ __device__ __forceinline__ void smem_sum_cols(const uint8_t* src, int splits, ui
   }
 }
 
-template <int BN, int STAGES, int MT>
+template <int BN, int STAGES, int MT, int KIND = 0>
 struct SmemLayout {
   static constexpr int kABytes = MT * BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
-  static constexpr int kStageOffset = STAGES * (kABytes + kBBytes);
+  static constexpr int kRingBytes = STAGES * (kABytes + kBBytes);
+  // NVFP4: the scale atoms of one k block (4 x 512 bytes per 128 rows) ride along with each stage
+  static constexpr int kSFABytes = KIND ? MT * 2048 : 0;
+  static constexpr int kSFBBytes = KIND ? ((BN + 127) / 128) * 2048 : 0;
+  static constexpr int kSFOffset = kRingBytes;
+  static constexpr int kStageOffset = kRingBytes + STAGES * (kSFABytes + kSFBBytes);
   static constexpr int kBarOffset = kStageOffset + kStageBytes;
   static constexpr int kTotal = kBarOffset + 512 + 1024;  // + barriers/scratch + alignment slack
 };
@@ -173,16 +178,19 @@ struct WorkItem {
   bool valid;
 };
 
-template <int BN, int STAGES, int MT>
+template <int BN, int STAGES, int MT, int KIND = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmParams p) {
-  using L = SmemLayout<BN, STAGES, MT>;
+  using L = SmemLayout<BN, STAGES, MT, KIND>;
+  static_assert(KIND == 0 || (MT == 1 && BN == 128), "fp4 tiles are 128 x 128");
+  constexpr int kXStep = KIND ? 128 : BK;  // TMA x coordinate of one k block (bytes for the packed fp4 maps)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem =
       reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * L::kABytes;
+  uint8_t* sSF = smem + L::kSFOffset;  // [stage][SFA | SFB]
   uint8_t* sStage = smem + L::kStageOffset;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
   uint64_t* empty = full + STAGES;
@@ -195,7 +203,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_kb = (p.K + BK - 1) / BK;
+  const int total_kb = KIND ? p.kb_total : (p.K + BK - 1) / BK;
   const bool grouped = p.group_counts != nullptr;
   const int n_tiles = (p.N + BN - 1) / BN;
   const int m_tiles = p.m_tiles;
@@ -205,7 +213,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   constexpr uint32_t kAccCols = BN < 32 ? 32 : BN;   // TMEM columns of one 128-row accumulator
   constexpr uint32_t kItemCols = MT * kAccCols;      // ... of one work item
   constexpr uint32_t kBufs = 2 * kItemCols <= 512 ? 2 : 1;
-  constexpr uint32_t kTmemCols = kBufs * kItemCols;
+  constexpr uint32_t kSFCols = KIND ? 64 : 0;   // two sets of (16 columns of A scales, 16 of B scales)
+  constexpr uint32_t kSFCol0 = kBufs * kItemCols;
+  constexpr uint32_t kTmemCols = KIND ? 512 : kBufs * kItemCols;
+  static_assert(kBufs * kItemCols + kSFCols <= 512, "TMEM budget");
   static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM allocation");
 
   if (threadIdx.x == 0) {
@@ -304,9 +315,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (lane == 0) set_status_once(p.status, kStatusMbarTimeoutProducer);
           break;
         }
-        if (lane == 0) mbar_arrive_expect_tx(&full[s], L::kABytes + L::kBBytes);
+        if (lane == 0) mbar_arrive_expect_tx(&full[s], L::kABytes + L::kBBytes + L::kSFABytes + L::kSFBBytes);
         __syncwarp();
         const int op = lane - (s & 7) * 4;  // which copy of this stage this lane issues (0..3), if any
+        if (KIND) {
+          // the scale atoms of this k block: 2 KB per 128 rows, contiguous in [row tile][k block]
+          uint8_t* sf = sSF + s * (L::kSFABytes + L::kSFBBytes);
+          if (op == 1)
+            bulk_load(sf + L::kSFABytes,
+                      p.sfb + ((static_cast<long long>(it.group) * ((p.N + 127) / 128) + (it.n0 >> 7)) * total_kb +
+                               it.kb0 + kb) * 2048,
+                      L::kSFBBytes, &full[s]);
+          if (op == 3)
+            bulk_load(sf,
+                      p.sfa + ((static_cast<long long>(it.group) * p.sfa_group_tiles + (it.m0 >> 7)) * total_kb +
+                               it.kb0 + kb) * 2048,
+                      L::kSFABytes, &full[s]);
+        }
         // weights first: they do not depend on any peer
         if (p.b_tiled && p.wide_boxes && BN == 256) {
           // both 128-row weight tiles of this k block in one 32 KB copy: [64][128][k block][n tile]
@@ -318,7 +343,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tma_load_3d(sB + s * L::kBBytes + op * 16384, &tmB, &full[s], 0, BN < 128 ? (it.n0 & 127) : 0,
                         ((it.n0 >> 7) + op) * total_kb + it.kb0 + kb);
         } else if (op == 0) {
-          tma_load_3d(sB + s * L::kBBytes, &tmB, &full[s], (it.kb0 + kb) * BK, it.n0, it.group);
+          tma_load_3d(sB + s * L::kBBytes, &tmB, &full[s], (it.kb0 + kb) * kXStep, it.n0, it.group);
         }
         if (need_wait) {
           int src_ok = 1;
@@ -339,9 +364,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         // rows past M read as zeros (the box is filled in full either way)
         if (p.wide_boxes && MT == 2) {
-          if (op == 2) tma_load_3d(sA + s * L::kABytes, &tmA, &full[s], (it.kb0 + kb) * BK, it.m0, it.group);
+          if (op == 2) tma_load_3d(sA + s * L::kABytes, &tmA, &full[s], (it.kb0 + kb) * kXStep, it.m0, it.group);
         } else if (op >= 2 && op < 2 + MT)
-          tma_load_3d(sA + s * L::kABytes + (op - 2) * (BM * BK * 2), &tmA, &full[s], (it.kb0 + kb) * BK,
+          tma_load_3d(sA + s * L::kABytes + (op - 2) * (BM * BK * 2), &tmA, &full[s], (it.kb0 + kb) * kXStep,
                       it.m0 + (op - 2) * BM, it.group);
       }
     }
@@ -375,6 +400,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(sA + s * L::kABytes);
           const uint32_t b_addr = smem_u32(sB + s * L::kBBytes);
+          if (KIND) {
+            // scales of this k block -> TMEM (alternating column sets), then 4 MMAs of 64 values of K
+            constexpr uint32_t idesc4 = make_idesc_nvfp4(BM, BN);
+            const uint32_t sfa_t = tmem_base + kSFCol0 + (iter & 1) * 32;
+            const uint32_t sfb_t = sfa_t + 16;
+            const uint32_t sf_s = smem_u32(sSF + s * (L::kSFABytes + L::kSFBBytes));
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              tc_cp_scales(sfa_t + 4 * j, make_desc_scales(sf_s + j * 512));
+              tc_cp_scales(sfb_t + 4 * j, make_desc_scales(sf_s + L::kSFABytes + j * 512));
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              tc_mma_nvfp4(d_tmem, make_desc_kmajor_sw128(a_addr + k * 32), make_desc_kmajor_sw128(b_addr + k * 32),
+                           idesc4, (kb | k) != 0 ? 1u : 0u, sfa_t + 4 * k, sfb_t + 4 * k);
+            tc_commit(&empty[s]);
+            continue;
+          }
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             const uint64_t db = make_desc_kmajor_sw128(b_addr + k * 32);
@@ -496,10 +539,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // TMEM, or summed over the slabs of every split (landed in shared memory, see below)
       int unit_acc0 = 0;          // first accumulator column of the unit whose slabs are in shared memory
       uint32_t unit_bytes = 0;    // bytes of one split's share of that unit
+      float acc_scale = 1.f;      // NVFP4: second-level scales of this thread's row and of the weights
       auto load_acc = [&](int h, int col, float (&a)[64]) __attribute__((always_inline)) {
-        if (!fix)
+        if (!fix) {
           tmem_load_cols<2>(lane_addr + h * kAccCols + col, a);
-        else
+          if (KIND) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) a[j] *= acc_scale;
+          }
+        } else
           smem_sum_cols(smem + ((col - unit_acc0) >> 3) * 2048 + (q * 32 + lane) * 16, p.splits, unit_bytes, a);
       };
 
@@ -542,6 +590,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         const int row = it.m0 + h * BM + q * 32 + lane;
         const bool row_ok = row < it.rows;
+        if (KIND) {
+          acc_scale = p.w_gscale != nullptr ? p.w_gscale[group] : 1.f;
+          if (p.a_gscale != nullptr && row_ok) acc_scale *= p.a_gscale[static_cast<long long>(group) * p.a_gs_stride + row];
+        }
 
         if (p.epi == kEpiRedF32) {
           int owner = 0, row_local = row;
@@ -736,11 +788,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (threadIdx.x == 0) stamp(p, 5);
 }
 
-template <int BN, int STAGES, int MT>
+template <int BN, int STAGES, int MT, int KIND = 0>
 void launch_impl(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                  cudaStream_t stream) {
-  using L = SmemLayout<BN, STAGES, MT>;
-  auto kern = gemm_bf16_kernel<BN, STAGES, MT>;
+  using L = SmemLayout<BN, STAGES, MT, KIND>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, MT, KIND>;
   ensure_dynamic_smem(kern, L::kTotal);
   const int sms = sm_count();
   const int n_work = ((p.N + BN - 1) / BN) * p.m_tiles * p.splits;
@@ -783,6 +835,10 @@ int gemm_ws_tickets(int M, int N, int bn, int mt) { return 2 * tiles_of(M, N, bn
 
 void launch_gemm_bf16(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int bn,
                       int mt, cudaStream_t stream) {
+  if (p.kind == 1) {
+    launch_impl<128, 5, 1, 1>(tmA, tmB, p, stream);
+    return;
+  }
   if (mt == 2) {
     switch (bn) {
       case 64:

@@ -70,6 +70,18 @@ struct GemmParams {
   // of them then sums a share of the tile's columns over all slabs and runs the epilogue on it.
   __nv_bfloat16* ws;         // [tiles * splits][mt][BN / 8][128][8] partial tiles; nullptr = off
   uint32_t* ws_tickets;      // [2 * tiles] arrival / departure counters, zero between launches
+  // --- block-scaled fp4 operands (kind = 1, NVFP4): a and w are e2m1 values packed two per byte
+  // (row-major, K / 2 bytes per row), one ue4m3 scale per 16 values of K in 512-byte atoms
+  // [row tile of 128][K / 64][(row % 32) * 16 + (row / 32 % 4) * 4 + (k / 16 % 4)], and the
+  // accumulator of row r is multiplied by a_gscale[g * a_gs_stride + r] * w_gscale[g] ---
+  int kind;                   // 0 = bf16 operands, 1 = NVFP4
+  int kb_total;               // k blocks of 128 operand bytes (kind 1: K / 256; kind 0: ceil(K / 64))
+  const uint8_t* sfa;         // scales of A
+  const uint8_t* sfb;         // scales of B
+  long long sfa_group_tiles;  // 128-row tiles per group in sfa
+  const float* a_gscale;      // per-row second-level scale of A (nullable: 1)
+  long long a_gs_stride;
+  const float* w_gscale;      // per-group second-level scale of B (nullable: 1)
   // Optional timeline of every CTA (bench_gemm --trace): 8 x uint64 nanosecond stamps per CTA
   // [entry, first accumulator ready, partial stored, splits met, epilogue done, exit, 0, 0].
   unsigned long long* trace;
@@ -86,5 +98,12 @@ int gemm_max_fixup_splits(int bn, int mt, bool swiglu);
 // all 256 rows of a decode batch with the CTA that streams a weight tile).
 void launch_gemm_bf16(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int bn,
                       int mt, cudaStream_t stream);
+
+// Activation quantiser of the NVFP4 GEMM: bf16 rows -> packed e2m1 + ue4m3 block scales (atom layout
+// above) + one fp32 scale per row (row amax / (448 * 6)). Rows are [groups, rows_per_group, K];
+// with group_counts only the first group_counts[g] rows of a group are converted.
+void launch_quant_act_nvfp4(const __nv_bfloat16* x, long long x_ld, uint8_t* q, uint8_t* sf, float* gscale,
+                            int groups, int rows_per_group, int K, const uint32_t* group_counts,
+                            cudaStream_t stream);
 
 }  // namespace oxb

@@ -186,13 +186,22 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
          ag_expected: int = 0, ag_rows_per_src: int = 0, ag_ticket: Optional[torch.Tensor] = None,
          bn: int = 0, splits: int = 1, act: int = 0, m_tiles: int = 0,
          dst_ld: int = 0, my_rank: int = 0, mt: int = 1, fixup: Optional[bool] = None,
-         trace: Optional[torch.Tensor] = None, wide_boxes: bool = True) -> Optional[torch.Tensor]:
+         trace: Optional[torch.Tensor] = None, wide_boxes: bool = True,
+         sfa: Optional[torch.Tensor] = None, sfb: Optional[torch.Tensor] = None,
+         a_gscale: Optional[torch.Tensor] = None, w_gscale: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """tcgen05 GEMM  out = a @ w^T  (bf16 in, fp32 accumulate). See csrc/kernels/gemm_bf16.cu.
     `mt` = 2 keeps 256 rows with one CTA per weight tile; `splits` > 1 with a store / SwiGLU / slab
-    epilogue combines the split partial tiles inside the kernel (`fixup`, default on for those)."""
+    epilogue combines the split partial tiles inside the kernel (`fixup`, default on for those).
+    With `sfa` / `sfb` the operands are NVFP4: `a` and `w` hold e2m1 values packed two per byte
+    ([.., K / 2] uint8, see quant_act_nvfp4 / Nvfp4Weight) and the product runs on the block-scaled
+    fp4 tensor-core path (128 x 128 tiles); `a_gscale` [rows] and `w_gscale` [groups] multiply the rows."""
     M = a.shape[-2]
     tiled = w.dim() == 4  # tile-major weight from tile_weight()
     N = w.shape[0] * 128 if tiled else w.shape[-2]
+    if sfa is not None:
+        bn, mt, fixup = 128, 1, False
+        if splits > 1 and epi != EPI_RED_F32:
+            splits = 1
     if bn == 0:
         bn = pick_bn(N, (M + 127) // 128)
     if out is None and epi not in (EPI_RED_F32, EPI_SLAB_BF16):
@@ -217,9 +226,117 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     _ext().gemm_bf16(a, w, epi, out, bias, list(dst_ptrs), list(arrive_ptrs), done_ticket,
                      reset_on_done, rows_per_owner, group_counts, row_meta, ag_flags, ag_expected,
                      ag_rows_per_src, ag_ticket, status_word(a.device), bn, splits, act, m_tiles, dst_ld,
-                     my_rank, 1 if tiled else 0, mt, ws, tk, SPIN_LIMIT, trace, 1 if wide_boxes else 0)
+                     my_rank, 1 if tiled else 0, mt, ws, tk, SPIN_LIMIT, trace, 1 if wide_boxes else 0, sfa, sfb, a_gscale, w_gscale)
     _bump()
     return out
+
+
+# ---------------------------------------------------------------------------------------- NVFP4
+E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def _sf_atoms(scales: torch.Tensor) -> torch.Tensor:
+    """[rows, K/16] uint8 block scales -> the 512-byte atom layout the tensor cores read:
+    [row tile of 128][K / 64][(row % 32) * 16 + (row / 32 % 4) * 4 + (k / 16 % 4)]. Rows are padded
+    to a multiple of 128 with zero scales (and K / 16 to a multiple of 4)."""
+    rows, nb = scales.shape
+    rp, nbp = (rows + 127) // 128 * 128, (nb + 3) // 4 * 4
+    s = torch.zeros(rp, nbp, dtype=torch.uint8, device=scales.device)
+    s[:rows, :nb] = scales
+    s = s.view(rp // 128, 4, 32, nbp // 4, 4)          # tile, row / 32, row % 32, chunk, k / 16 % 4
+    return s.permute(0, 3, 2, 1, 4).contiguous().view(-1)
+
+
+class Nvfp4Weight:
+    """A weight matrix (or a stack of expert matrices) in the layout of the block-scaled fp4 GEMM:
+    `q` [.., N, K / 2] uint8 (e2m1, even element in the low nibble), `sf` scale atoms, `gscale`
+    [groups] fp32 second-level scale. Built from GGUF NVFP4 blocks (`from_gguf_blocks`: the file's
+    e4m3 micro-scales and nibbles are kept bit for bit, only re-ordered) or by quantising a float
+    matrix (`from_float`)."""
+
+    def __init__(self, q: torch.Tensor, sf: torch.Tensor, gscale: torch.Tensor, n: int, k: int):
+        self.q, self.sf, self.gscale, self.n, self.k = q, sf, gscale, n, k
+
+    @property
+    def groups(self) -> int:
+        return self.q.shape[0] if self.q.dim() == 3 else 1
+
+    @staticmethod
+    def from_gguf_blocks(raw: torch.Tensor, n: int, k: int, groups: int = 1) -> "Nvfp4Weight":
+        """raw: uint8 GGUF NVFP4 blocks of 16 bytes (byte 0 = e4m3 scale, bytes 1..8 = nibbles with
+        element i in the low and element i + 8 in the high nibble), [groups * n * k / 16, 16]."""
+        b = raw.view(groups * n, k // 16, 16)
+        qs = b[:, :, 1:9]
+        el = torch.cat([qs & 0xF, qs >> 4], dim=-1)                      # elements 0..15 of every block
+        q = (el[..., 0::2] | (el[..., 1::2] << 4)).reshape(groups, n, k // 2).contiguous()
+        sc = b[:, :, 0].reshape(groups, n, k // 16)
+        sf = torch.cat([_sf_atoms(sc[g]) for g in range(groups)])
+        gs = torch.ones(groups, dtype=torch.float32, device=raw.device)
+        return Nvfp4Weight(q if groups > 1 else q[0], sf, gs, n, k)
+
+    @staticmethod
+    def from_float(w: torch.Tensor) -> "Nvfp4Weight":
+        """Quantises [N, K] or [G, N, K] float weights: per 16 values an e4m3 scale = amax / 6 relative
+        to the matrix-wide second-level scale amax_matrix / (448 * 6); values to the nearest e2m1."""
+        w3 = w if w.dim() == 3 else w[None]
+        G, N, K = w3.shape
+        wf = w3.float()
+        gs = (wf.abs().amax(dim=(1, 2)) / (448.0 * 6.0)).clamp_min(1e-30)
+        blk = wf.view(G, N, K // 16, 16)
+        want = (blk.abs().amax(-1) / 6.0 / gs[:, None, None]).clamp_max(448.0)
+        sc8 = want.to(torch.float8_e4m3fn)
+        sd = sc8.float()
+        bump = (sd < want) & (sc8.view(torch.uint8) < 0x7E)              # round the scale up, never down
+        sc8 = torch.where(bump, (sc8.view(torch.uint8) + 1).view(torch.float8_e4m3fn), sc8)
+        sd = sc8.float() * gs[:, None, None]
+        y = blk / sd.clamp_min(1e-30)[..., None]
+        lv = torch.tensor(E2M1_VALUES, device=w.device)
+        code = (y.abs()[..., None] - lv).abs().argmin(-1).to(torch.uint8) | ((y < 0).to(torch.uint8) << 3)
+        code = code.view(G, N, K)
+        q = (code[..., 0::2] | (code[..., 1::2] << 4)).contiguous()
+        sf = torch.cat([_sf_atoms(sc8.view(torch.uint8)[g]) for g in range(G)])
+        return Nvfp4Weight(q if w.dim() == 3 else q[0], sf, gs.float(), N, K)
+
+    def dequant(self) -> torch.Tensor:
+        """fp32 values of the packed matrix (test oracle)."""
+        q3 = self.q if self.q.dim() == 3 else self.q[None]
+        G, N, _ = q3.shape
+        K = self.k
+        lv = torch.tensor(E2M1_VALUES, device=q3.device)
+        code = torch.stack([q3 & 0xF, q3 >> 4], -1).view(G, N, K)
+        val = lv[(code & 7).long()] * torch.where((code & 8) != 0, -1.0, 1.0)
+        rp, ch = (N + 127) // 128 * 128, (K // 16 + 3) // 4
+        sf = self.sf.view(G, rp // 128, ch, 32, 4, 4).permute(0, 1, 4, 3, 2, 5).reshape(G, rp, ch * 4)[:, :N, :K // 16]
+        sc = sf.contiguous().view(torch.float8_e4m3fn).float()
+        out = val.view(G, N, K // 16, 16) * sc[..., None] * self.gscale.view(G, 1, 1, 1)
+        out = out.view(G, N, K)
+        return out if self.q.dim() == 3 else out[0]
+
+
+def quant_act_nvfp4(x: torch.Tensor, bufs=None, group_counts: Optional[torch.Tensor] = None):
+    """bf16 [rows, K] or [G, cap, K] -> (q [.., K / 2] uint8, scale atoms, gscale [rows] fp32) for the
+    NVFP4 GEMM. `bufs` = preallocated (q, sf, gscale) flat buffers (CUDA-graph friendly)."""
+    K = x.shape[-1]
+    rows = x.numel() // K
+    tiles = (rows + 127) // 128
+    if bufs is None:
+        q = torch.empty(*x.shape[:-1], K // 2, dtype=torch.uint8, device=x.device)
+        sf = torch.zeros(tiles * (K // 64) * 512, dtype=torch.uint8, device=x.device)
+        gs = torch.ones(rows, dtype=torch.float32, device=x.device)
+    else:
+        q = bufs[0][:rows * K // 2].view(*x.shape[:-1], K // 2)
+        sf = bufs[1][:tiles * (K // 64) * 512]
+        gs = bufs[2][:rows]
+    _ext().quant_act_nvfp4(x, q, sf, gs, group_counts)
+    _bump()
+    return q, sf, gs
+
+
+def dequant_act_nvfp4(q: torch.Tensor, sf: torch.Tensor, gs: torch.Tensor) -> torch.Tensor:
+    """fp32 values of quantised activation rows (test oracle); q is [rows, K / 2]."""
+    rows, K = q.shape[0], q.shape[1] * 2
+    w = Nvfp4Weight(q, sf, torch.ones(1, device=q.device), rows, K).dequant()
+    return w * gs[:rows, None]
 
 
 def quant_weight_fp8_block(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:

@@ -795,3 +795,98 @@ def test_gemv_bf16_small_batch(ops, m, n, k, tiled):
         ops.gemv(x, wi, y, swiglu=True)
         gr, ur = x.float() @ g.float().t(), x.float() @ u.float().t()
         assert _rel_err(y, torch.nn.functional.silu(gr) * ur) < 1.5e-2
+
+
+# ------------------------------------------------------------------------------------------ NVFP4
+@pytest.mark.gpu
+@pytest.mark.parametrize("m", [1, 17, 128, 300])
+def test_gemm_nvfp4_block_scaled_against_dequantised_operands(ops, m):
+    """The block-scaled fp4 tensor-core GEMM against the fp32 product of the *dequantised* operands
+    (so the only difference is the accumulation order), and the quantiser against its own rules."""
+    torch.manual_seed(40 + m)
+    n, k = 384, 1024
+    x = (torch.randn(m, k, device=DEV) * torch.rand(m, 1, device=DEV) * 4).bfloat16()
+    w = torch.randn(n, k, device=DEV) * 0.05
+    wq = ops.Nvfp4Weight.from_float(w)
+    assert _rel_err(wq.dequant(), w) < 0.3 and _cos(wq.dequant(), w) > 0.99      # 4-bit weights
+    xq, sfa, gs = ops.quant_act_nvfp4(x)
+    xd = ops.dequant_act_nvfp4(xq, sfa, gs)
+    assert _cos(xd, x.float()) > 0.99 and (xd.abs().amax(1) <= x.float().abs().amax(1) * 1.001).all()
+    ref = xd @ wq.dequant().T
+    out = ops.gemm(xq, wq.q, sfa=sfa, sfb=wq.sf, a_gscale=gs, w_gscale=wq.gscale)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert out.shape == (m, n) and _rel_err(out, ref) < 1.5e-2 and _cos(out, ref) > 0.9999, _rel_err(out, ref)
+    out32 = ops.gemm(xq, wq.q, sfa=sfa, sfb=wq.sf, a_gscale=gs, w_gscale=wq.gscale, epi=ops.EPI_STORE_F32)
+    torch.cuda.synchronize()
+    assert _rel_err(out32, ref) < 2e-3
+
+
+@pytest.mark.gpu
+def test_nvfp4_weights_from_gguf_blocks_keep_the_file_bits(ops):
+    from oxide_tech_llm_engine_b200.formats import quants
+
+    rng = np.random.default_rng(3)
+    n, k = 256, 512
+    w = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+    raw = quants.quantize("NVFP4", w)
+    want = torch.from_numpy(quants.dequantize("NVFP4", raw, n * k).reshape(n, k)).to(DEV)
+    wq = ops.Nvfp4Weight.from_gguf_blocks(torch.from_numpy(raw.reshape(-1, 16).copy()).to(DEV), n, k)
+    assert torch.equal(wq.dequant(), want)           # the same values, bit for bit
+    x = torch.randn(40, k, device=DEV).bfloat16()
+    xq, sfa, gs = ops.quant_act_nvfp4(x)
+    out = ops.gemm(xq, wq.q, sfa=sfa, sfb=wq.sf, a_gscale=gs, w_gscale=wq.gscale)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert _rel_err(out, ops.dequant_act_nvfp4(xq, sfa, gs) @ want.T) < 1.5e-2
+
+
+@pytest.mark.gpu
+def test_gemm_nvfp4_grouped_swiglu_and_combine(ops):
+    """Expert GEMMs on packed fp4 weights: grouped gate|up with the SwiGLU epilogue over a slab with
+    per-expert row counts, then the grouped down projection with the weighted combine epilogue."""
+    torch.manual_seed(44)
+    G, cap, d, i = 4, 128, 512, 256
+    counts = torch.tensor([100, 0, 128, 37], dtype=torch.int32, device=DEV)
+    slab = torch.randn(G, cap, d, device=DEV).bfloat16()
+    wg = torch.randn(G, i, d, device=DEV) * 0.05
+    wu = torch.randn(G, i, d, device=DEV) * 0.05
+    w_gu = torch.stack([wg.view(G, i // 32, 32, d), wu.view(G, i // 32, 32, d)], 2).reshape(G, 2 * i, d)
+    wq_gu = ops.Nvfp4Weight.from_float(w_gu)
+    wq_dn = ops.Nvfp4Weight.from_float(torch.randn(G, d, i, device=DEV) * 0.05)
+    sq, ssf, sgs = ops.quant_act_nvfp4(slab, group_counts=counts)
+    act = torch.zeros(G, cap, i, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(sq, wq_gu.q, out=act, epi=ops.EPI_SWIGLU_BF16, group_counts=counts, m_tiles=G * (cap // 128),
+             sfa=ssf, sfb=wq_gu.sf, a_gscale=sgs, w_gscale=wq_gu.gscale)
+    torch.cuda.synchronize()
+    ops.check_status()
+    deq_w = wq_gu.dequant().view(G, i // 32, 2, 32, d)
+    for g in range(G):
+        c = int(counts[g])
+        if c == 0:
+            continue
+        xd = ops.dequant_act_nvfp4(sq[g], ssf.view(G, -1)[g], sgs.view(G, cap)[g])[:c]
+        gate = xd @ deq_w[g, :, 0].reshape(i, d).T
+        up = xd @ deq_w[g, :, 1].reshape(i, d).T
+        assert _rel_err(act[g, :c], torch.nn.functional.silu(gate) * up) < 2e-2, g
+    # down projection + combine: row r of expert g goes home to row meta[g, r].row with its weight
+    meta = torch.zeros(G, cap, 4, dtype=torch.int32, device=DEV)
+    home = torch.randint(0, 64, (G, cap), device=DEV, dtype=torch.int32)
+    wts = torch.rand(G, cap, device=DEV)
+    meta[:, :, 1] = home
+    meta[:, :, 2] = wts.view(torch.int32)
+    acc = torch.zeros(64, d, device=DEV)
+    aq, asf, ags = ops.quant_act_nvfp4(act, group_counts=counts)
+    ops.gemm(aq, wq_dn.q, epi=ops.EPI_RED_F32, dst_ptrs=[acc.data_ptr()], group_counts=counts, row_meta=meta,
+             m_tiles=G * (cap // 128), sfa=asf, sfb=wq_dn.sf, a_gscale=ags, w_gscale=wq_dn.gscale)
+    torch.cuda.synchronize()
+    ops.check_status()
+    ref = torch.zeros(64, d, device=DEV)
+    dn = wq_dn.dequant()
+    for g in range(G):
+        c = int(counts[g])
+        if c == 0:
+            continue
+        ad = ops.dequant_act_nvfp4(aq[g], asf.view(G, -1)[g], ags.view(G, cap)[g])[:c]
+        ref.index_add_(0, home[g, :c].long(), (ad @ dn[g].T) * wts[g, :c, None])
+    assert _rel_err(acc, ref) < 2e-3
