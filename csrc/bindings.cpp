@@ -246,7 +246,9 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
 // a8: [M, K] e4m3 bytes; sa_t: [ceil(K/128), >= M] fp32; w8: [N, K] e4m3 bytes; sw: [ceil(N/128), ceil(K/128)].
 // x: [rows, K] or [G, cap, K] bf16 -> q [.., K/2] uint8, sf (scale atoms), gscale [rows] fp32
 void quant_act_nvfp4(const Tensor& x, const Tensor& q, const Tensor& sf, const Tensor& gscale,
-                     const c10::optional<Tensor>& group_counts) {
+                     const c10::optional<Tensor>& group_counts, const c10::optional<Tensor>& ag_flags,
+                     int64_t ag_expected, const c10::optional<Tensor>& ag_ticket, const Tensor& status,
+                     int64_t spin_limit) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.stride(-1) == 1, "quant_act_nvfp4: bf16 rows");
   const int64_t K = x.size(-1);
   TORCH_CHECK(K % 64 == 0, "quant_act_nvfp4: K must be a multiple of 64");
@@ -259,9 +261,19 @@ void quant_act_nvfp4(const Tensor& x, const Tensor& q, const Tensor& sf, const T
   TORCH_CHECK(sf.scalar_type() == torch::kUInt8 && sf.is_contiguous() && sf.numel() >= tiles * (K / 64) * 512,
               "quant_act_nvfp4: sf too small");
   TORCH_CHECK(gscale.scalar_type() == torch::kFloat32 && gscale.numel() >= G * R, "quant_act_nvfp4: gscale");
+  oxb::QuantActWait wait{};
+  if (ag_flags.has_value() && ag_flags->defined()) {
+    TORCH_CHECK(ag_ticket.has_value() && ag_ticket->defined(), "quant_act_nvfp4: ag_ticket required with ag_flags");
+    wait.flags = reinterpret_cast<const uint32_t*>(ag_flags->data_ptr());
+    wait.n_src = static_cast<int>(ag_flags->numel());
+    wait.expected = static_cast<uint32_t>(ag_expected);
+    wait.ticket = reinterpret_cast<uint32_t*>(ag_ticket->data_ptr());
+    wait.status = reinterpret_cast<int*>(status.data_ptr());
+  }
   oxb::launch_quant_act_nvfp4(reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), x.stride(-2), q.data_ptr<uint8_t>(),
                               sf.data_ptr<uint8_t>(), gscale.data_ptr<float>(), static_cast<int>(G),
-                              static_cast<int>(R), static_cast<int>(K), opt_ptr<uint32_t>(group_counts), cur_stream());
+                              static_cast<int>(R), static_cast<int>(K), opt_ptr<uint32_t>(group_counts), wait,
+                              static_cast<uint32_t>(spin_limit > 0 ? spin_limit : 0), cur_stream());
   check_launch("quant_act_nvfp4");
 }
 

@@ -101,9 +101,11 @@ void launch_gemm_bf16(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm
 
 // Activation quantiser of the NVFP4 GEMM: bf16 rows -> packed e2m1 + ue4m3 block scales (atom layout
 // above) + one fp32 scale per row (row amax / (448 * 6)). Rows are [groups, rows_per_group, K];
-// with group_counts only the first group_counts[g] rows of a group are converted.
+// with group_counts only the first group_counts[g] rows of a group are converted. With wait.flags the
+// kernel is the consumer of an MoE dispatch: it waits (bounded) until every source has signalled.
+struct QuantActWait;  // bounded wait on arrival flags before the rows are read (gemm_fp8_block.cuh)
 void launch_quant_act_nvfp4(const __nv_bfloat16* x, long long x_ld, uint8_t* q, uint8_t* sf, float* gscale,
                             int groups, int rows_per_group, int K, const uint32_t* group_counts,
-                            cudaStream_t stream);
+                            const QuantActWait& wait, uint32_t spin_limit, cudaStream_t stream);
 
 }  // namespace oxb

@@ -15,7 +15,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "../common/sm100.cuh"
 #include "gemm_bf16.cuh"
+#include "gemm_fp8_block.cuh"
 
 namespace oxb {
 
@@ -38,19 +40,49 @@ __device__ __forceinline__ uint32_t e2m1_code(float v) {
 
 __global__ void __launch_bounds__(128) quant_act_nvfp4_kernel(const __nv_bfloat16* x, long long x_ld, uint8_t* q,
                                                               uint8_t* sf, float* gscale, int rows_per_group,
-                                                              int K, const uint32_t* group_counts) {
+                                                              int K, const uint32_t* group_counts,
+                                                              const QuantActWait w, uint32_t spin_limit) {
   __shared__ float s_red[4];
   const int group = blockIdx.y;
   const int row = blockIdx.x;
-  if (group_counts != nullptr && row >= static_cast<int>(group_counts[group])) return;
+  if (w.flags != nullptr) {
+    // The rows were written by peers (MoE dispatch) and the per-group counts are final only once
+    // every source has signalled: wait, bounded; the last CTA through the gate re-arms the flags.
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) {
+      int ok = 1;
+      const uint32_t limit = spin_budget(spin_limit);
+      for (int s = 0; s < w.n_src && ok; ++s) {
+        uint32_t it = 0, v;
+        do {
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(w.flags + s) : "memory");
+          if (v >= w.expected) break;
+        } while (++it <= limit);
+        if (v < w.expected) {
+          set_status_peer_timeout(w.status);
+          ok = 0;
+        }
+      }
+      const uint32_t old = atomicAdd(w.ticket, 1u);
+      if (old == gridDim.x * gridDim.y - 1) {
+        for (int s = 0; s < w.n_src; ++s) const_cast<uint32_t*>(w.flags)[s] = 0;
+        __threadfence();
+        *w.ticket = 0;
+      }
+      s_ok = ok;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+  }
+  if (group_counts != nullptr && row >= static_cast<int>(__ldcg(group_counts + group))) return;
   const long long grow = static_cast<long long>(group) * rows_per_group + row;
   const __nv_bfloat16* xr = x + grow * x_ld;
   const int n_blk = K / 16;
   // pass 1: row amax
   float amax = 0.f;
   for (int b = threadIdx.x; b < n_blk; b += blockDim.x) {
-    const uint4 v0 = *reinterpret_cast<const uint4*>(xr + b * 16);
-    const uint4 v1 = *reinterpret_cast<const uint4*>(xr + b * 16 + 8);
+    const uint4 v0 = __ldcg(reinterpret_cast<const uint4*>(xr + b * 16));   // L2: peers may have written it
+    const uint4 v1 = __ldcg(reinterpret_cast<const uint4*>(xr + b * 16 + 8));
     const __nv_bfloat16* e0 = reinterpret_cast<const __nv_bfloat16*>(&v0);
     const __nv_bfloat16* e1 = reinterpret_cast<const __nv_bfloat16*>(&v1);
 #pragma unroll
@@ -69,8 +101,8 @@ __global__ void __launch_bounds__(128) quant_act_nvfp4_kernel(const __nv_bfloat1
   uint8_t* sf_row = sf + tile * static_cast<long long>(K / 64) * 512 + (r128 & 31) * 16 + (r128 >> 5) * 4;
   uint8_t* qr = q + grow * (K / 2);
   for (int b = threadIdx.x; b < n_blk; b += blockDim.x) {
-    const uint4 v0 = *reinterpret_cast<const uint4*>(xr + b * 16);
-    const uint4 v1 = *reinterpret_cast<const uint4*>(xr + b * 16 + 8);
+    const uint4 v0 = __ldcg(reinterpret_cast<const uint4*>(xr + b * 16));
+    const uint4 v1 = __ldcg(reinterpret_cast<const uint4*>(xr + b * 16 + 8));
     float v[16];
     const __nv_bfloat16* e0 = reinterpret_cast<const __nv_bfloat16*>(&v0);
     const __nv_bfloat16* e1 = reinterpret_cast<const __nv_bfloat16*>(&v1);
@@ -105,10 +137,10 @@ __global__ void __launch_bounds__(128) quant_act_nvfp4_kernel(const __nv_bfloat1
 
 void launch_quant_act_nvfp4(const __nv_bfloat16* x, long long x_ld, uint8_t* q, uint8_t* sf, float* gscale,
                             int groups, int rows_per_group, int K, const uint32_t* group_counts,
-                            cudaStream_t stream) {
+                            const QuantActWait& wait, uint32_t spin_limit, cudaStream_t stream) {
   if (groups <= 0 || rows_per_group <= 0) return;
   quant_act_nvfp4_kernel<<<dim3(rows_per_group, groups), 128, 0, stream>>>(x, x_ld, q, sf, gscale, rows_per_group, K,
-                                                                         group_counts);
+                                                                         group_counts, wait, spin_limit);
 }
 
 }  // namespace oxb

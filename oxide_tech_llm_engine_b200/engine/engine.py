@@ -120,6 +120,10 @@ class LLMEngine:
                 weights.type_name(n) not in ("F32", "F16", "BF16") for n in ("blk.0.attn_q.weight",)
                 if weights.has(n))
             weight_mode = "quant" if packed and world == 1 and not mc.is_moe else "bf16"
+            if (mc.is_moe and weights is not None and weights.has("blk.0.ffn_gate_exps.weight")
+                    and weights.type_name("blk.0.ffn_gate_exps.weight") == "NVFP4"
+                    and mc.d_model % 256 == 0 and mc.ffn_dim % 256 == 0):
+                weight_mode = "nvfp4"   # expert matrices stay packed and run on the fp4 tensor-core path
         self.max_tokens = max(cfg.max_num_batched_tokens, cfg.max_num_seqs)
         self.max_tokens = (self.max_tokens + world - 1) // world * world
         # packed GGUF weights may be doubled by a bf16 copy for batched steps (decided before the KV
@@ -267,7 +271,7 @@ class LLMEngine:
         tp = self.world
         w_bytes = 0
         if has_weights:
-            per = {"bf16": 2.0, "fp8": 1.02}.get(weight_mode, 0.6)
+            per = {"bf16": 2.0, "fp8": 1.02, "nvfp4": 0.7}.get(weight_mode, 0.6)
             n = mc.n_params()
             w_bytes = int((n - mc.vocab_size * mc.d_model) / tp * per + mc.vocab_size * mc.d_model * 2)
         act = self.max_tokens * (mc.d_model * 16 + (mc.q_dim + 2 * mc.kv_dim) // tp * 8 + mc.ffn_dim // tp * 4)

@@ -108,6 +108,17 @@ def random_quant_linear(type_name: str, n: int, k: int, device, gen: torch.Gener
     return lin
 
 
+def random_nvfp4(groups: int, n: int, k: int, device, gen: torch.Generator, std: float = 0.02):
+    """Packed NVFP4 expert matrices with random nibbles generated on the device (benchmarks: no float
+    copy, no quantiser pass). Uniform e2m1 codes have a root mean square of 2.93, so one e4m3 scale of
+    0.4375 for every block and a second-level scale of std / (2.93 * 0.4375) give values of about N(0, std)."""
+    q = torch.randint(0, 256, (groups, n, k // 2), dtype=torch.uint8, device=device, generator=gen)
+    tiles = (n + 127) // 128
+    sf = torch.full((groups * tiles * (k // 64) * 512,), 0x2E, dtype=torch.uint8, device=device)   # e4m3 0.4375
+    gs = torch.full((groups,), std / (2.93 * 0.4375), dtype=torch.float32, device=device)
+    return ops.Nvfp4Weight(q, sf, gs, n, k)
+
+
 def fuse_quant_rows(parts: list) -> Optional[QuantLinear]:
     """Stacks packed weights that share the block type and K into one matrix (rows are independent
     byte ranges, so this is a concatenation): Q|K|V and gate|up then take one GEMV launch instead of
@@ -141,11 +152,14 @@ class DeviceModel:
             raise ConfigError("packed GGUF weights are served at tp=1; use weight_mode='bf16' for tp>1")
         if weight_mode == "fp8" and cfg.is_moe:
             raise ConfigError("block-scaled fp8 weights are served on dense models")
+        if weight_mode == "nvfp4" and (not cfg.is_moe or cfg.d_model % 256 or cfg.ffn_dim % 256):
+            raise ConfigError("NVFP4 serving covers the expert matrices of MoE models with d_model and "
+                              "ffn_dim multiples of 256 (attention projections stay bf16)")
         # pipeline stage: this model owns layers [lo, hi); the first stage embeds, the last one
         # runs the final norm and the LM head, the others hand the residual stream on
         self.layer_lo, self.layer_hi = layer_range if layer_range is not None else (0, cfg.n_layers)
         self.pp_first, self.pp_last = self.layer_lo == 0, self.layer_hi == cfg.n_layers
-        if layer_range is not None and weight_mode != "bf16":
+        if layer_range is not None and weight_mode not in ("bf16",):
             raise ConfigError("pipeline stages are served with bf16 weights")
         self.weight_mode = weight_mode
         # dense bf16 projections are kept tile-major in HBM (see ops.tile_weight) unless a library
@@ -187,7 +201,8 @@ class DeviceModel:
             specs["slab1"] = ((tp, rpr, d), "bf16")
         self._rs_slab = [False, False]
         if cfg.is_moe:
-            self.cap = M
+            # rows per expert slab; the fp4 scale atoms cover 128 rows, so that path rounds up
+            self.cap = (M + 127) // 128 * 128 if weight_mode == "nvfp4" else M
             specs["slab"] = ((self.e_l, self.cap, d), "bf16")
             specs["meta"] = ((self.e_l, self.cap, 4), "i32")
             specs["cnt"] = ((16,), "i32")
@@ -201,6 +216,13 @@ class DeviceModel:
         self.qkv_bf16 = torch.zeros(M, self.wqkv, **bf)
         if cfg.is_moe:
             self.act_slab = torch.zeros(self.e_l, self.cap, self.i_l, **bf)
+            if weight_mode == "nvfp4":
+                # quantised copies of the two expert GEMM inputs: packed e2m1, scale atoms, row scales
+                rows = self.e_l * self.cap
+                u8 = dict(dtype=torch.uint8, device=dev)
+                mk = lambda k: (torch.zeros(rows * k // 2, **u8), torch.zeros(rows // 128 * (k // 64) * 512, **u8),
+                                torch.ones(rows, dtype=torch.float32, device=dev))
+                self._fp4_slab, self._fp4_act = mk(d), mk(self.i_l)
         else:
             self.act = torch.zeros(M, self.i_l, **bf)
         self.logits = torch.zeros(self.max_logits, self.v_l, dtype=torch.float32, device=dev)
@@ -256,7 +278,11 @@ class DeviceModel:
         for _ in range(self.layer_lo, self.layer_hi):
             L = {"attn_norm": ones(d), "ffn_norm": ones(d), "w_qkv": rnd(self.wqkv, d),
                  "w_o": rnd(d, self.hq * self.D), "b_qkv": None, "q_norm": None, "k_norm": None}
-            if cfg.is_moe:
+            if cfg.is_moe and self.weight_mode == "nvfp4":
+                L["router"] = rnd(cfg.n_experts, d, gen=gr, s=1.0 / math.sqrt(d))
+                L["w_gu"] = random_nvfp4(self.e_l, 2 * self.i_l, d, dev, g, std)
+                L["w_down"] = random_nvfp4(self.e_l, d, self.i_l, dev, g, std)
+            elif cfg.is_moe:
                 L["router"] = rnd(cfg.n_experts, d, gen=gr, s=1.0 / math.sqrt(d))
                 L["w_gu"] = rnd(self.e_l, 2 * self.i_l, d)
                 L["w_down"] = rnd(self.e_l, d, self.i_l)
@@ -355,7 +381,11 @@ class DeviceModel:
                 wq, wk, wv = src.f32(p + "attn_q.weight"), src.f32(p + "attn_k.weight"), src.f32(p + "attn_v.weight")
                 L["w_qkv"] = bf(np.concatenate([wq[hq_lo:hq_hi], wk[kv_lo:kv_hi], wv[kv_lo:kv_hi]], 0))
                 L["w_o"] = bf(src.f32(p + "attn_output.weight")[:, hq_lo:hq_hi])
-                if cfg.is_moe:
+                if cfg.is_moe and self.weight_mode == "nvfp4":
+                    e_lo, e_hi = r * self.e_l, (r + 1) * self.e_l
+                    L["router"] = bf(src.f32(p + "ffn_gate_inp.weight"))
+                    L["w_gu"], L["w_down"] = self._load_nvfp4_experts(src, p, e_lo, e_hi)
+                elif cfg.is_moe:
                     e_lo, e_hi = r * self.e_l, (r + 1) * self.e_l
                     L["router"] = bf(src.f32(p + "ffn_gate_inp.weight"))
                     g = bf(src.f32(p + "ffn_gate_exps.weight")[e_lo:e_hi])
@@ -373,6 +403,30 @@ class DeviceModel:
                 self._tile_layer(L)
             self.layers.append(L)
         self._tile_head()
+
+    def _load_nvfp4_experts(self, src: WeightSource, p: str, e_lo: int, e_hi: int):
+        """Expert matrices of one layer for the block-scaled fp4 GEMM. Tensors stored as NVFP4 blocks
+        keep their e4m3 micro-scales and nibbles bit for bit (re-ordered for the tensor cores, never
+        expanded to bf16); other storage types are quantised once at load."""
+        cfg, dev = self.cfg, self.device
+        d, i_l, e_l = cfg.d_model, self.i_l, self.e_l
+        names = [p + f"ffn_{k}_exps.weight" for k in ("gate", "up", "down")]
+        if all(src.type_name(n) == "NVFP4" for n in names):
+            def blocks(name, n, k):   # [experts of this rank, n, k / 16, 16] uint8
+                raw = np.ascontiguousarray(src.raw(name)).reshape(cfg.n_experts, n, k // 16, 16)[e_lo:e_hi]
+                return torch.from_numpy(raw.copy()).to(dev)
+            g, u = blocks(names[0], i_l, d), blocks(names[1], i_l, d)
+            gu = torch.cat([g.view(e_l, i_l // 32, 1, 32, d // 16, 16), u.view(e_l, i_l // 32, 1, 32, d // 16, 16)], 2)
+            w_gu = ops.Nvfp4Weight.from_gguf_blocks(gu.reshape(-1, 16), 2 * i_l, d, groups=e_l)
+            w_dn = ops.Nvfp4Weight.from_gguf_blocks(blocks(names[2], d, i_l).reshape(-1, 16), d, i_l, groups=e_l)
+        else:
+            f = lambda n: torch.from_numpy(np.ascontiguousarray(src.f32(n)[e_lo:e_hi], dtype=np.float32)).to(dev)
+            w_gu = ops.Nvfp4Weight.from_float(interleave32(f(names[0]), f(names[1])))
+            w_dn = ops.Nvfp4Weight.from_float(f(names[2]))
+        for w in (w_gu, w_dn):   # the grouped GEMM takes [experts, N, K / 2] even for one expert
+            if w.q.dim() == 2:
+                w.q = w.q[None]
+        return w_gu, w_dn
 
     def _to_fp8(self, L: dict) -> None:
         """Replaces the bf16 projections of a layer by (e4m3 values, 128 x 128 block scales)."""
@@ -429,12 +483,13 @@ class DeviceModel:
         return dict(ag_flags=self.ws.local("flags")[flag_base:flag_base + self.tp], ag_expected=expected,
                     ag_rows_per_src=rows_per_src, ag_ticket=self.tickets[ticket:ticket + 1])
 
-    def _gemm_shape(self, m: int, n: int, k: int, *, swiglu: bool = False, routed: bool = False) -> dict:
+    def _gemm_shape(self, m: int, n: int, k: int, *, swiglu: bool = False, routed: bool = False,
+                    store: bool = False) -> dict:
         """Tile width, rows per tile, split-K factor and split-K mode of one projection. Steps of
         129 to 256 rows (large decode batches) keep every row with the CTA that streams a weight
         tile and split K to fill the SMs, combined inside the kernel; a routed projection on one GPU
         adds its splits straight into the fp32 accumulator instead. Other steps use 128-row tiles."""
-        key = (m, n, k, swiglu, routed)
+        key = (m, n, k, swiglu, routed, store)
         c = self._gemm_cfg.get(key)
         if c is not None:
             return c
@@ -449,12 +504,24 @@ class DeviceModel:
             bn = ops.pick_bn(n, m_tiles, can_split=not swiglu)
             mt = 1
             sp = 1 if swiglu else ops.pick_splits(m, n, k, bn, self._sms)
-            fixup = sp > 1 and routed and self.tp > 1 and ((n + bn - 1) // bn) * m_tiles * sp <= self._sms
-            if sp > 1 and routed and self.tp > 1 and not fixup:
-                sp = 1
+            fixup = False
+            if sp > 1 and (store or (routed and self.tp > 1)):
+                # these epilogues cannot add into an fp32 accumulator: combine the splits in the kernel
+                # when the launch is one wave, else do not split
+                fits = (((n + bn - 1) // bn) * m_tiles * sp <= self._sms
+                        and sp <= ops.max_fixup_splits(bn, 1, False))
+                fixup = fits
+                if not fits:
+                    sp = 1
         c = dict(bn=bn, mt=mt, splits=sp, fixup=fixup)
         self._gemm_cfg[key] = c
         return c
+
+    def _ag_kwargs_quant(self, flag_base: int, ticket: int, expected: int) -> dict:
+        if self.tp == 1:
+            return {}
+        return dict(ag_flags=self.ws.local("flags")[flag_base:flag_base + self.tp], ag_expected=expected,
+                    ag_ticket=self.tickets[ticket:ticket + 1])
 
     def _red_kwargs(self, acc: int, ticket: int, rpr: int, gc: Optional[dict] = None) -> dict:
         """Epilogue routing of a row-parallel GEMM. Across GPUs the partial tiles travel as bf16
@@ -616,7 +683,7 @@ class DeviceModel:
             ops.gemv(lmg, self.lm_head, self.logits[:n_log])
         else:
             ops.gemm(lmg, self.lm_head, out=self.logits[:n_log], epi=ops.EPI_STORE_F32,
-                     **self._gemm_shape(n_log, self.v_l, d), **self._ag_kwargs(F_LMG, T_LMG, 0, rpr))
+                     **self._gemm_shape(n_log, self.v_l, d, store=True), **self._ag_kwargs(F_LMG, T_LMG, 0, rpr))
         if cfg.logit_softcap > 0:
             ops.softcap(self.logits[:n_log], cfg.logit_softcap)
         return self.logits[:n_log]
@@ -639,6 +706,22 @@ class DeviceModel:
         slab, meta = self.ws.local("slab"), self.ws.local("meta")
         cnt = self.ws.local("cnt")[:self.e_l]
         m_tiles = (M * cfg.n_experts_used + 127) // 128 + self.e_l
+        if self.weight_mode == "nvfp4":
+            # The quantiser is the consumer of the dispatch (it waits for every source's flag, then
+            # converts the rows each expert received); both expert GEMMs run on the block-scaled fp4
+            # tensor-core path with the same SwiGLU and combine epilogues as the bf16 path.
+            wgu, wdn = L["w_gu"], L["w_down"]
+            sq, ssf, sgs = ops.quant_act_nvfp4(slab, self._fp4_slab, cnt, **self._ag_kwargs_quant(F_MOE, T_MOE, rpr))
+            ops.gemm(sq, wgu.q, out=self.act_slab, epi=ops.EPI_SWIGLU_BF16, act=self._act_code, group_counts=cnt,
+                     m_tiles=m_tiles, sfa=ssf, sfb=wgu.sf, a_gscale=sgs, w_gscale=wgu.gscale)
+            aq, asf, ags = ops.quant_act_nvfp4(self.act_slab, self._fp4_act, cnt)
+            kw = dict(epi=ops.EPI_RED_F32, dst_ptrs=self.ws.ptrs("acc1"), group_counts=cnt, row_meta=meta,
+                      m_tiles=m_tiles, done_ticket=self.tickets[T_DONE_D:T_DONE_D + 1], reset_on_done=cnt,
+                      sfa=asf, sfb=wdn.sf, a_gscale=ags, w_gscale=wdn.gscale)
+            if tp > 1:
+                kw["arrive_ptrs"] = self._flag_ptrs(F_ARRIVE1)
+            ops.gemm(aq, wdn.q, **kw)
+            return
         ops.gemm(slab, L["w_gu"], out=self.act_slab, epi=ops.EPI_SWIGLU_BF16, act=self._act_code,
                  group_counts=cnt, m_tiles=m_tiles, bn=128, **self._ag_kwargs(F_MOE, T_MOE, 0, rpr))
         kw = dict(epi=ops.EPI_RED_F32, dst_ptrs=self.ws.ptrs("acc1"), group_counts=cnt, row_meta=meta,

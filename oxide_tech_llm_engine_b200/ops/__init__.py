@@ -313,9 +313,13 @@ class Nvfp4Weight:
         return out if self.q.dim() == 3 else out[0]
 
 
-def quant_act_nvfp4(x: torch.Tensor, bufs=None, group_counts: Optional[torch.Tensor] = None):
+def quant_act_nvfp4(x: torch.Tensor, bufs=None, group_counts: Optional[torch.Tensor] = None, *,
+                    ag_flags: Optional[torch.Tensor] = None, ag_expected: int = 0,
+                    ag_ticket: Optional[torch.Tensor] = None):
     """bf16 [rows, K] or [G, cap, K] -> (q [.., K / 2] uint8, scale atoms, gscale [rows] fp32) for the
-    NVFP4 GEMM. `bufs` = preallocated (q, sf, gscale) flat buffers (CUDA-graph friendly)."""
+    NVFP4 GEMM. `bufs` = preallocated (q, sf, gscale) flat buffers (CUDA-graph friendly). With
+    `ag_flags` the kernel first waits (bounded) until every source rank has signalled that its rows
+    (an MoE dispatch into the slab) and the per-group counts are complete."""
     K = x.shape[-1]
     rows = x.numel() // K
     tiles = (rows + 127) // 128
@@ -327,7 +331,8 @@ def quant_act_nvfp4(x: torch.Tensor, bufs=None, group_counts: Optional[torch.Ten
         q = bufs[0][:rows * K // 2].view(*x.shape[:-1], K // 2)
         sf = bufs[1][:tiles * (K // 64) * 512]
         gs = bufs[2][:rows]
-    _ext().quant_act_nvfp4(x, q, sf, gs, group_counts)
+    _ext().quant_act_nvfp4(x, q, sf, gs, group_counts, ag_flags, ag_expected, ag_ticket, status_word(x.device),
+                           SPIN_LIMIT)
     _bump()
     return q, sf, gs
 

@@ -25,12 +25,17 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     ok = True
-    for name in sys.argv[1:] or ["tiny", "tiny-moe", "tiny-fp8", "tiny-h2o", "tiny-b160"]:
+    for name in sys.argv[1:] or ["tiny", "tiny-moe", "tiny-fp8", "tiny-h2o", "tiny-b160", "tiny-moe-fp4"]:
+        fp4 = name.endswith("-fp4")    # expert matrices on the block-scaled fp4 path, experts sharded over the ranks
+        if fp4:
+            name_base = name[:-4]
         fp8 = name.endswith("-fp8")
         h2o = name.endswith("-h2o")
         big = name.endswith("-b160")   # 160 sequences decode together: the 256-row GEMM tiles with in-kernel split-K
-        base = name[:-4] if (fp8 or h2o) else (name[:-5] if big else name)
-        if big:
+        base = name[:-4] if (fp8 or h2o or fp4) else (name[:-5] if big else name)
+        if fp4:
+            mc = preset(base, n_heads=8, n_kv_heads=8, d_model=256, ffn_dim=512, head_dim=64)
+        elif big:
             mc = preset(base, n_heads=8, n_kv_heads=8, d_model=512, ffn_dim=1024, head_dim=64)
         elif world > 2:
             mc = preset(base, n_heads=8, n_kv_heads=8, d_model=256, ffn_dim=512, head_dim=64)
@@ -42,7 +47,7 @@ def main():
         cfg = EngineConfig(tp=world, max_num_seqs=192 if big else 8, max_num_batched_tokens=2048 if big else 256,
                            num_kv_blocks=1024 if big else 256, sla_budget=not big,
                            ctx_size=1024, graph_buckets=(192,) if big else (8,), cuda_graph=True,
-                           weight_mode="fp8" if fp8 else "auto",
+                           weight_mode="fp8" if fp8 else ("nvfp4" if fp4 else "auto"),
                            **(dict(h2o_pruning=True, h2o_budget_blocks=5, h2o_sink_blocks=1, h2o_rolling_blocks=2,
                                    enable_radix=False) if h2o else {}))
         eng = LLMEngine(cfg, mc, weights=src, rank=rank, world=world, device=dev)
@@ -61,7 +66,8 @@ def main():
                 if h2o:   # pruned KV: only agreement between ranks, completion and the pruning itself are checked
                     assert all(len(o) == 12 for o in outs) and eng.stats.get("h2o_pruned_blocks", 0) > 0
                 else:
-                    assert_consistent(mc, src, prompts, outs, **(dict(tol=0.6, min_exact=0.5) if fp8 else {}))
+                    assert_consistent(mc, src, prompts, outs, **(dict(tol=0.6, min_exact=0.5) if fp8 else
+                                                                 dict(tol=2.0, min_exact=0.4) if fp4 else {}))
                 if big:
                     assert eng.stats["graph_replays"] >= 3, "the 160-row decode steps did not run as graph replays"
                 print(f"TP_CHECK {name} world={world} OK replays={eng.stats['graph_replays']}", flush=True)

@@ -140,6 +140,38 @@ def test_nvfp4_moe_checkpoint_is_served_through_the_fused_expert_path():
         eng.close()
 
 
+def test_nvfp4_moe_checkpoint_is_served_packed_on_the_fp4_tensor_core_path():
+    """A Mixtral-style GGUF with NVFP4 expert matrices whose sizes fit the fp4 tiles: the experts stay
+    packed (no bf16 copy exists), both expert GEMMs run on the block-scaled fp4 path, and the tokens
+    stay close to the fp32 oracle of the same (dequantised) weights; activations are quantised to
+    fp4 as well, so the tolerance is wider than for bf16."""
+    from oxide_tech_llm_engine_b200 import ops
+    from oxide_tech_llm_engine_b200.models.config import preset
+    from oxide_tech_llm_engine_b200.models.weights import open_weights, write_synthetic_gguf
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    mc = preset("tiny-moe", d_model=256, ffn_dim=512, head_dim=64)
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "m.gguf")
+        write_synthetic_gguf(path, mc, seed=5, weight_type="NVFP4", embed_type="Q8_0", std=0.08)
+        src = open_weights(path)
+        eng, mc2, _ = _mk("tiny-moe", weights=src)
+        assert eng.model.weight_mode == "nvfp4"
+        L0 = eng.model.layers[0]
+        assert isinstance(L0["w_gu"], ops.Nvfp4Weight) and L0["w_gu"].q.dtype == torch.uint8
+        assert not any(isinstance(v, torch.Tensor) and v.dtype == torch.bfloat16 and v.dim() == 3 for v in L0.values())
+        # the packed matrices decode to exactly what the file's blocks decode to
+        want = torch.from_numpy(src.f32("blk.0.ffn_down_exps.weight")).to("cuda")
+        assert torch.equal(L0["w_down"].dequant(), want)
+        rng = np.random.default_rng(9)
+        prompts = [rng.integers(3, mc.vocab_size, size=n).tolist() for n in (6, 40)]
+        outs = eng.generate(prompts, SamplingParams(greedy=True, max_tokens=10, ignore_eos=True))
+        eng.check_device_status()
+        assert all(len(o) == 10 for o in outs)
+        assert_consistent(mc2, src, prompts, outs, tol=1.0, min_exact=0.4)
+        eng.close()
+
+
 def test_fp8_block_scaled_serving():
     """Block-scaled fp8 projections: tokens stay consistent with the fp32 oracle's logits."""
     from oxide_tech_llm_engine_b200.sampling_params import SamplingParams

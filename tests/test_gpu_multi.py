@@ -23,6 +23,7 @@ def test_tp_and_ep_match_oracle():
     assert "TP_CHECK tiny-fp8 world=%d OK" % n in r.stdout
     assert "TP_CHECK tiny-h2o world=%d OK" % n in r.stdout
     assert "TP_CHECK tiny-b160 world=%d OK" % n in r.stdout
+    assert "TP_CHECK tiny-moe-fp4 world=%d OK" % n in r.stdout
 
 
 def test_pipeline_parallel_stages_match_oracle():
