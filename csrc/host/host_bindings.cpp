@@ -100,7 +100,10 @@ PYBIND11_MODULE(oxb_host, m) {
       .def_readwrite("enable_radix", &SchedulerConfig::enable_radix)
       .def_readwrite("radix_high", &SchedulerConfig::radix_high)
       .def_readwrite("radix_low", &SchedulerConfig::radix_low)
-      .def_readwrite("sla_budget", &SchedulerConfig::sla_budget);
+      .def_readwrite("sla_budget", &SchedulerConfig::sla_budget)
+      .def_readwrite("context_shift", &SchedulerConfig::context_shift)
+      .def_readwrite("shift_keep_tokens", &SchedulerConfig::shift_keep_tokens)
+      .def_readwrite("shift_step_tokens", &SchedulerConfig::shift_step_tokens);
 
   py::class_<TokenEvent>(m, "TokenEvent")
       .def_readonly("req_id", &TokenEvent::req_id)
@@ -171,6 +174,7 @@ PYBIND11_MODULE(oxb_host, m) {
       .def("num_free_blocks", &Scheduler::num_free_blocks)
       .def("has_work", &Scheduler::has_work)
       .def("preemptions", &Scheduler::preemptions)
+      .def("context_shifts", &Scheduler::context_shifts)
       .def("running_ids", &Scheduler::running_ids)
       .def("request_tokens",
            [](const Scheduler& s, int64_t id) -> py::object {

@@ -133,6 +133,22 @@ bool Scheduler::ensure_blocks(Request* r, int n_tokens, StepPlan* plan) {
   return false;
 }
 
+void Scheduler::shift_context(Request* r, int incoming) {
+  const int limit = cfg_.max_blocks_per_seq * kTokensPerBlock;
+  const int n_blocks = static_cast<int>(r->table->blocks().size());
+  const int sink = std::max(1, (cfg_.shift_keep_tokens + kTokensPerBlock - 1) / kTokensPerBlock);
+  const int overflow = r->computed - r->dropped + incoming - limit;
+  const int drop_tokens = std::max(cfg_.shift_step_tokens, overflow);
+  int drop = (drop_tokens + kTokensPerBlock - 1) / kTokensPerBlock;
+  drop = std::min(drop, n_blocks - sink - 1);  // the block being written always stays
+  if (drop <= 0) return;
+  const int rolling = n_blocks - sink - drop;
+  r->table->prune_heavy_hitters({}, sink, rolling, sink + rolling);
+  r->dropped += drop * kTokensPerBlock;
+  r->drafts.clear();
+  ++context_shifts_;
+}
+
 void Scheduler::preempt(Request* r) {
   // recompute-style preemption: drop the KV, keep the tokens, go back to the head of the queue
   ++preemptions_;
@@ -290,7 +306,8 @@ StepPlan Scheduler::schedule() {
     }
     const int need = 1 + static_cast<int>(r->drafts.size());
     const int limit = cfg_.max_blocks_per_seq * kTokensPerBlock;
-    if (r->computed + need > limit) r->drafts.clear();
+    if (r->computed - r->dropped + need > limit) r->drafts.clear();
+    if (cfg_.context_shift && r->computed - r->dropped + 1 > limit) shift_context(r, 1);
     const int n = 1 + static_cast<int>(r->drafts.size());
     if (!blocks_or_preempt(r, n, "length")) continue;  // running_[i] is now the next request
     if (n == 1)
@@ -460,7 +477,8 @@ std::vector<TokenEvent> Scheduler::update(const StepPlan& plan, const std::vecto
       reason = "stop";
     else if (r->generated() >= r->max_new_tokens)
       reason = "length";
-    else if (static_cast<int>(r->tokens.size()) >= cfg_.max_blocks_per_seq * kTokensPerBlock)
+    else if (!cfg_.context_shift &&
+             static_cast<int>(r->tokens.size()) - r->dropped >= cfg_.max_blocks_per_seq * kTokensPerBlock)
       reason = "length";
     events.push_back({r->id, tok, !reason.empty(), reason});
     return !reason.empty();

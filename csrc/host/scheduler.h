@@ -42,6 +42,12 @@ struct SchedulerConfig {
   double radix_high = 0.90;
   double radix_low = 0.80;
   bool sla_budget = true;            // false: budget = max_num_batched_tokens - decodes
+  // Context shift (oxide-alloc/src/kv_advanced.rs:299-339): a sequence that fills its window keeps
+  // its first `shift_keep_tokens` and drops the oldest max(shift_step_tokens, overflow) after them,
+  // instead of ending with "length". Whole 16-token blocks are dropped; positions stay absolute.
+  bool context_shift = false;
+  int shift_keep_tokens = 4;
+  int shift_step_tokens = 256;
 };
 
 enum class Phase : int { Waiting = 0, Prefill = 1, Decode = 2, Finished = 3 };
@@ -126,10 +132,12 @@ class Scheduler {
   RadixCache& radix() { return radix_; }
   const SchedulerConfig& config() const { return cfg_; }
   uint64_t preemptions() const { return preemptions_; }
+  uint64_t context_shifts() const { return context_shifts_; }
   std::vector<int64_t> running_ids() const;
 
  private:
   bool ensure_blocks(Request* r, int n_tokens, StepPlan* plan);
+  void shift_context(Request* r, int incoming);
   void preempt(Request* r);
   void abort(Request* r, const std::string& reason);
   void finish(Request* r);
@@ -146,6 +154,7 @@ class Scheduler {
   std::vector<int64_t> cow_owner_;  // request id of each copy-on-write pair of the plan being built
   uint64_t arrivals_ = 0;
   uint64_t preemptions_ = 0;
+  uint64_t context_shifts_ = 0;
 };
 
 }  // namespace oxb

@@ -154,7 +154,7 @@ def gpu_config(args) -> dict:
                           [rng.integers(0, mc.vocab_size, size=32768).tolist() for _ in range(n_long)],
                           [256] * n_long))
         ctx, seqs = 32768 + 256 + 16, 256
-    wm = {"bf16": "bf16", "fp8": "fp8", "q4k": "quant"}[args.weights]
+    wm = {"bf16": "bf16", "fp8": "fp8", "q4k": "quant", "nvfp4": "nvfp4"}[args.weights]
     cfg = EngineConfig(model=model, tp=world, ctx_size=ctx, max_num_seqs=min(seqs, 256),
                        max_num_batched_tokens=args.max_batched_tokens, gpu_memory_utilization=0.92,
                        sla_budget=False, chunk_max=args.max_batched_tokens, enable_radix=(c == 5),
@@ -200,7 +200,7 @@ def gpu_config(args) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", type=int, required=True, choices=[1, 2, 3, 4, 5])
-    ap.add_argument("--weights", default="bf16", choices=["bf16", "fp8", "q4k"])
+    ap.add_argument("--weights", default="bf16", choices=["bf16", "fp8", "q4k", "nvfp4"])
     ap.add_argument("--scale", type=float, default=1.0, help="fraction of the request count (quick runs)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (marks the run as reduced)")
     ap.add_argument("--prompt-len", type=int, default=0)

@@ -50,6 +50,11 @@ class EngineConfig:
     h2o_budget_blocks: int = 128        # blocks a sequence may keep (sink + rolling window + heavy hitters)
     h2o_sink_blocks: int = 1
     h2o_rolling_blocks: int = 16
+    context_shift: bool = False         # at the context limit keep the prefix and drop the oldest tokens instead of ending
+    shift_keep_tokens: int = 4
+    shift_step_tokens: int = 256
+    native_worker: bool = False         # run engine steps on the C++ StepWorker thread (core pin: worker_pin_core)
+    worker_pin_core: int = -1
     seed: int = 42
     backend: str = "cuda"               # cuda | cpu
     step_deadline_s: float = 30.0       # watchdog: a step that takes longer marks the engine degraded

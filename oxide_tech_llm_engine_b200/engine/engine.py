@@ -167,6 +167,8 @@ class LLMEngine:
         sc.sla_itl_us, sc.base_us, sc.per_token_us = cfg.sla_itl_us, cfg.base_us, cfg.per_token_us
         sc.enable_radix = cfg.enable_radix
         sc.sla_budget = cfg.sla_budget
+        sc.context_shift, sc.shift_keep_tokens, sc.shift_step_tokens = (cfg.context_shift, cfg.shift_keep_tokens,
+                                                                        cfg.shift_step_tokens)
         self.sched = H.Scheduler(sc)
         self.max_blocks_per_seq = max_blocks_per_seq
         S, M = cfg.max_num_seqs, self.max_tokens
@@ -229,6 +231,8 @@ class LLMEngine:
         sc.sla_itl_us, sc.base_us, sc.per_token_us = cfg.sla_itl_us, cfg.base_us, cfg.per_token_us
         sc.enable_radix = cfg.enable_radix
         sc.sla_budget = cfg.sla_budget
+        sc.context_shift, sc.shift_keep_tokens, sc.shift_step_tokens = (cfg.context_shift, cfg.shift_keep_tokens,
+                                                                        cfg.shift_step_tokens)
         self.sched = H.Scheduler(sc)
         self.requests = {}
         self._next_id = 0

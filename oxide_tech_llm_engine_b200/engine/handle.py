@@ -59,8 +59,18 @@ class RequestStream:
 
 
 class EngineHandle:
-    def __init__(self, engine, max_slots: Optional[int] = None):
+    def __init__(self, engine, max_slots: Optional[int] = None, native_worker: Optional[bool] = None):
         self.engine = engine
+        # With `native_worker` the steps run on the C++ StepWorker (csrc/host/worker.*): a dedicated
+        # host thread fed through a single-producer / single-consumer ring of 64-byte commands, with the
+        # spin -> yield -> park idle policy and an optional core pin, as in the reference's
+        # scheduler-actor / GPU-worker split (continuous_batching.rs:1413-1499, worker.rs:90-138). This
+        # thread then only drains commands and hands out step tickets.
+        if native_worker is None:
+            native_worker = bool(getattr(engine.cfg, "native_worker", False))
+        self.native_worker = native_worker
+        self._worker = None
+        self._worker_error: Optional[str] = None
         self.max_slots = max_slots or engine.cfg.max_num_seqs
         self.cmd: "queue.Queue" = queue.Queue()
         self.streams: dict[int, RequestStream] = {}
@@ -152,6 +162,42 @@ class EngineHandle:
 
             torch.cuda.set_device(dev)
 
+    def _step_on_worker(self, kind: int, a0: int, a1: int):
+        """Handler of the native worker thread: one engine step per command."""
+        try:
+            if not getattr(self, "_worker_bound", False):
+                self._bind_device()
+                self._worker_bound = True
+            self.engine.step()
+            return 0, 0
+        except EngineError as ex:
+            self._worker_error = str(ex)
+        except Exception as ex:
+            self._worker_error = f"{type(ex).__name__}: {ex}"
+        return 1, 0
+
+    def _step(self) -> None:
+        """One engine step, on this thread or through the native worker; raises what the step raised."""
+        if not self.native_worker:
+            self.engine.step()
+            return
+        if self._worker is None:
+            from .._build import host_ext
+
+            pin = int(getattr(self.engine.cfg, "worker_pin_core", -1))
+            self._worker = host_ext().StepWorker(self._step_on_worker, capacity=8, pin_core=pin)
+            self._tickets = 0
+        self._tickets += 1
+        while not self._worker.submit(self._tickets):
+            time.sleep(0)
+        deadline_ms = int(max(1.0, getattr(self.engine.cfg, "step_deadline_s", 30.0)) * 1000)
+        done = self._worker.wait(deadline_ms)
+        if done is None:
+            raise EngineError(f"step worker did not finish a step within {deadline_ms} ms")
+        if done[1] != 0:
+            msg, self._worker_error = self._worker_error or "step failed on the worker thread", None
+            raise EngineError(msg)
+
     def _run(self) -> None:
         self._bind_device()
         idle = 0
@@ -159,7 +205,7 @@ class EngineHandle:
             busy = self._drain()
             if self.engine.has_work():
                 try:
-                    self.engine.step()
+                    self._step()
                     self.last_step_time = time.monotonic()
                     self.healthy = not self.engine.stats.get("degraded", False)
                 except EngineError as ex:
@@ -178,6 +224,9 @@ class EngineHandle:
                 time.sleep(0)
             else:
                 time.sleep(50e-6 if idle < 20000 else 1e-3)
+        if self._worker is not None:
+            self._worker.stop()
+            self._worker = None
         for rid, st in list(self.streams.items()):
             st.push(StreamEvent(rid, -1, True, "cancelled"))
         self.streams.clear()

@@ -315,3 +315,58 @@ def test_nvfp4_moe_gguf_round_trip_on_cpu():
         out = eng.generate([p], SamplingParams(greedy=True, max_tokens=6, ignore_eos=True))[0]
         assert out == ReferenceModel(src.cfg, src).generate_greedy(p, 6)
         eng.close()
+
+
+def test_context_shift_keeps_a_sequence_going_past_its_window():
+    """At the context limit the sequence keeps its first block and drops the oldest ones after it
+    (whole 16-token blocks) instead of ending: it generates far beyond the window with bounded KV."""
+    eng, mc, src = mk(ctx_size=64, num_kv_blocks=32, context_shift=True, shift_keep_tokens=4, shift_step_tokens=16,
+                      enable_radix=False)
+    sp = SamplingParams(greedy=True, max_tokens=150, ignore_eos=True)
+    rid = eng.add_request(list(range(3, 33)), sp)
+    peak = 0
+    while eng.has_work():
+        eng.step()
+        info = eng.sched.request_info(rid)
+        if info is not None:
+            peak = max(peak, len(info["blocks"]))
+            assert info["computed"] - info["dropped"] <= 64
+    r = eng.requests[rid]
+    assert r.finished and r.finish_reason == "length" and len(r.output) == 150
+    assert peak <= 4 and eng.sched.context_shifts() >= 5
+    assert eng.sched.num_free_blocks() == 32
+    # without the shift the same request stops at the window
+    eng2, _, _ = mk(ctx_size=64, num_kv_blocks=32, enable_radix=False)
+    out2 = eng2.generate([list(range(3, 33))], sp)[0]
+    assert len(out2) < 40 and out2 == r.output[:len(out2)]
+
+
+def test_engine_handle_runs_steps_on_the_native_worker_thread():
+    """The C++ StepWorker carries the engine steps (scheduler actor -> SPSC ring -> worker thread):
+    same tokens as stepping on the handle's own thread, failures stay isolated per request."""
+    eng, mc, src = mk()
+    ref_eng, _, _ = mk()
+    want = ref_eng.generate([[5, 6, 7, 8], [9, 10, 11]], GREEDY)
+    h = EngineHandle(eng, native_worker=True)
+    try:
+        a = h.submit([5, 6, 7, 8], GREEDY)
+        b = h.submit([9, 10, 11], GREEDY)
+        outs = []
+        for st in (a, b):
+            toks = []
+            while True:
+                ev = st.get(timeout=60)
+                if ev.token >= 0:
+                    toks.append(ev.token)
+                if ev.finished:
+                    break
+            outs.append(toks)
+        assert outs == want
+        assert h._worker is not None and h._worker.idle_stats()["commands"] >= 8
+        rid = h.submit([1, 2, 3], GREEDY)
+        eng.sched.inject_prefill_error(rid.req_id, "boom")
+        ev = rid.get(timeout=60)
+        assert ev.finished and ev.reason.startswith("prefill_error")
+        assert h.generate([5, 6, 7, 8], GREEDY)[0] == want[0]
+    finally:
+        h.shutdown()
