@@ -108,7 +108,7 @@ def main() -> None:
     ap.add_argument("--mem-util", type=float, default=0.94)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--weights", default="bf16", choices=["bf16", "fp8", "q4k"],
+    ap.add_argument("--weights", default="bf16", choices=["bf16", "fp8", "q4k", "q4km"],
                     help="fp8: block-scaled e4m3 projections (1x128 / 128x128 scales); a separate configuration, "
                          "the headline number is bf16")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
@@ -150,11 +150,11 @@ def main() -> None:
     cfg = EngineConfig(model=args.model, tp=world, ctx_size=ctx, max_num_seqs=args.requests,
                        max_num_batched_tokens=args.max_batched_tokens, gpu_memory_utilization=args.mem_util,
                        sla_budget=False, chunk_max=args.max_batched_tokens, enable_radix=False,
-                       cuda_graph=not args.no_graph, comm=args.comm, weight_mode={"q4k": "quant"}.get(args.weights, args.weights), gemm="library" if args.comm == "nccl" else "tcgen05",
+                       cuda_graph=not args.no_graph, comm=args.comm, weight_mode={"q4k": "quant", "q4km": "quant"}.get(args.weights, args.weights), gemm="library" if args.comm == "nccl" else "tcgen05",
                        graph_buckets=tuple(b for b in (8, 16, 32, 64, 128, 192, 256) if b <= args.requests) or (args.requests,))
     t_build = time.perf_counter()
     eng = LLMEngine(cfg, mc, rank=rank, world=world, device=dev, random_init=True,
-                    random_quant_type="Q4_K" if args.weights == "q4k" else None)
+                    random_quant_type={"q4k": "Q4_K", "q4km": "Q4_K_M"}.get(args.weights))
     torch.cuda.synchronize()
     rng = np.random.default_rng(1234)  # same request stream on every rank
     sp = SamplingParams(greedy=True, max_tokens=args.output_len, ignore_eos=True)
@@ -270,7 +270,8 @@ def main() -> None:
             "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None,
             "dtype": {"bf16": "bf16", "fp8": "fp8 block-scaled weights, bf16 activations/KV",
-                      "q4k": "GGUF Q4_K packed weights, bf16 activations/KV"}[args.weights],
+                      "q4k": "GGUF Q4_K packed weights, bf16 activations/KV",
+                      "q4km": "GGUF Q4_K_M layout (Q4_K + Q6_K) packed weights, bf16 activations/KV"}[args.weights],
             "data": "synthetic random-token prompts, random-init N(0,0.02) weights",
             "impl": "ours" if args.comm == "fused" else "ours-baseline-path", "valid": valid,
             "config": {

@@ -8,6 +8,7 @@
 #include <torch/extension.h>
 
 #include <string>
+#include <cstring>
 #include <vector>
 
 #include "common/device_info.h"
@@ -373,7 +374,8 @@ void paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
                   const Tensor& block_tables, const Tensor& seq_lens, const Tensor& pages_per_split,
                   const Tensor& part_o, const Tensor& part_ml, const Tensor& out, int64_t batch,
                   int64_t max_splits, int64_t window, double scale,
-                  const c10::optional<Tensor>& status) {
+                  const c10::optional<Tensor>& status, const c10::optional<Tensor>& page_ml,
+                  const c10::optional<Tensor>& block_mass) {
   TORCH_CHECK(q.dim() == 3 && k_cache.dim() == 4, "paged_decode: q [B,Hq,D], cache [blk,Hkv,16,D]");
   TORCH_CHECK(k_cache.size(2) == 16, "paged_decode: 16-token pages");
   oxb::DecodeAttnParams p{};
@@ -402,6 +404,17 @@ void paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
   p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
   p.status = opt_ptr<int>(status);  // given only when bounds checking is on
   p.num_blocks = p.status != nullptr ? static_cast<int>(k_cache.size(0)) : 0;
+  TORCH_CHECK(page_ml.has_value() == block_mass.has_value(), "paged_decode: page_ml and block_mass go together");
+  if (page_ml.has_value()) {
+    TORCH_CHECK(p.Hq <= 128, "paged_decode: block mass supports up to 128 query heads per rank");
+    TORCH_CHECK(page_ml->scalar_type() == at::kFloat && block_mass->scalar_type() == at::kFloat &&
+                    page_ml->is_contiguous() && block_mass->is_contiguous(),
+                "paged_decode: page_ml / block_mass must be contiguous fp32");
+    TORCH_CHECK(page_ml->numel() >= batch * p.max_blocks * p.Hq * 2, "paged_decode: page_ml too small");
+    TORCH_CHECK(block_mass->numel() >= batch * p.max_blocks, "paged_decode: block_mass too small");
+    p.page_ml = page_ml->data_ptr<float>();
+    p.block_mass = block_mass->data_ptr<float>();
+  }
   (void)oxb::launch_paged_decode(p, static_cast<int>(batch), D, cur_stream());
   check_launch("paged_decode");
 }
@@ -616,6 +629,57 @@ void softcap(const Tensor& logits, double cap) {
   check_launch("softcap");
 }
 
+// Page-locked host memory that the device can write directly: returns the host view (int64 words)
+// and the device address of the same bytes. Freed with the tensor.
+std::tuple<Tensor, int64_t> alloc_mapped_host(int64_t n_words) {
+  TORCH_CHECK(n_words > 0, "alloc_mapped_host: size");
+  void* host = nullptr;
+  cudaError_t e = cudaHostAlloc(&host, static_cast<size_t>(n_words) * 8, cudaHostAllocMapped);
+  TORCH_CHECK(e == cudaSuccess, "cudaHostAlloc(mapped): ", cudaGetErrorString(e));
+  void* dev = nullptr;
+  e = cudaHostGetDevicePointer(&dev, host, 0);
+  if (e != cudaSuccess) {
+    cudaFreeHost(host);
+    TORCH_CHECK(false, "cudaHostGetDevicePointer: ", cudaGetErrorString(e));
+  }
+  std::memset(host, 0, static_cast<size_t>(n_words) * 8);
+  Tensor t = torch::from_blob(host, {n_words}, [](void* p) { cudaFreeHost(p); },
+                              torch::TensorOptions().dtype(torch::kInt64).device(torch::kCPU));
+  return {t, static_cast<int64_t>(reinterpret_cast<uintptr_t>(dev))};
+}
+
+void advance_decode_step(const Tensor& token_ids, const Tensor& positions, const Tensor& slot_mapping,
+                         const Tensor& seq_lens, const Tensor& block_tables, const Tensor& sampled,
+                         int64_t mailbox_dev, const Tensor& step_counter, int64_t rows, int64_t ring,
+                         const c10::optional<Tensor>& status) {
+  TORCH_CHECK(token_ids.is_cuda() && token_ids.scalar_type() == at::kInt && positions.scalar_type() == at::kInt &&
+                  slot_mapping.scalar_type() == at::kLong && seq_lens.scalar_type() == at::kInt &&
+                  block_tables.scalar_type() == at::kInt && sampled.scalar_type() == at::kInt &&
+                  step_counter.scalar_type() == at::kInt,
+              "advance_decode_step: dtypes");
+  TORCH_CHECK(block_tables.dim() == 2 && block_tables.stride(1) == 1 && block_tables.stride(0) == block_tables.size(1),
+              "advance_decode_step: block_tables [rows, max_blocks] contiguous");
+  TORCH_CHECK(rows > 0 && token_ids.numel() >= rows && positions.numel() >= rows && slot_mapping.numel() >= rows &&
+                  seq_lens.numel() >= rows && sampled.numel() >= rows && block_tables.size(0) >= rows,
+              "advance_decode_step: rows");
+  TORCH_CHECK(mailbox_dev != 0 && ring > 0, "advance_decode_step: mailbox");
+  oxb::AdvanceStepParams p{};
+  p.token_ids = token_ids.data_ptr<int>();
+  p.positions = positions.data_ptr<int>();
+  p.slot_mapping = reinterpret_cast<long long*>(slot_mapping.data_ptr<int64_t>());
+  p.seq_lens = seq_lens.data_ptr<int>();
+  p.block_tables = block_tables.data_ptr<int>();
+  p.sampled = sampled.data_ptr<int>();
+  p.mailbox = reinterpret_cast<unsigned long long*>(static_cast<uintptr_t>(mailbox_dev));
+  p.step_counter = reinterpret_cast<unsigned int*>(step_counter.data_ptr<int>());
+  p.rows = static_cast<int>(rows);
+  p.max_blocks = static_cast<int>(block_tables.size(1));
+  p.ring = static_cast<int>(ring);
+  p.status = opt_ptr<int>(status);
+  oxb::launch_advance_decode_step(p, cur_stream());
+  check_launch("advance_decode_step");
+}
+
 // ---------------------------------------------------------------------------------------------
 // quantized weights
 // ---------------------------------------------------------------------------------------------
@@ -652,6 +716,48 @@ void mmvq(int64_t qtype, const Tensor& w, const Tensor& x, const c10::optional<T
   TORCH_CHECK(oxb::launch_mmvq(static_cast<int>(qtype), p, cur_stream()),
               "mmvq: no device decoder for GGUF type ", qtype);
   check_launch("mmvq");
+}
+
+// Stacked packed matrices of different block types sharing K (one launch): out[:, sum of n_i].
+void mmvq_mixed(const std::vector<int64_t>& qtypes, const std::vector<Tensor>& ws, const std::vector<int64_t>& ns,
+                const Tensor& x, const Tensor& out, int64_t K, const Tensor& xq, const Tensor& xd,
+                const Tensor& xs) {
+  const size_t n_seg = qtypes.size();
+  TORCH_CHECK(n_seg >= 1 && n_seg <= 4 && ws.size() == n_seg && ns.size() == n_seg, "mmvq_mixed: 1..4 segments");
+  TORCH_CHECK(K % 32 == 0, "mmvq_mixed: K must be a multiple of 32");
+  oxb::MmvqParams p{};
+  int64_t rows = 0;
+  for (size_t i = 0; i < n_seg; ++i) {
+    TORCH_CHECK(ws[i].scalar_type() == torch::kUInt8 && ws[i].is_cuda(), "mmvq_mixed: packed uint8 weights");
+    p.seg_type[i] = static_cast<int>(qtypes[i]);
+    p.seg_w[i] = ws[i].data_ptr<uint8_t>();
+    p.seg_row_bytes[i] = oxb::quant_row_bytes(p.seg_type[i], K);
+    TORCH_CHECK(p.seg_row_bytes[i] > 0 && ws[i].numel() >= p.seg_row_bytes[i] * ns[i],
+                "mmvq_mixed: weight buffer ", i, " too small");
+    rows += ns[i];
+    p.seg_row_end[i] = static_cast<int>(rows);
+  }
+  p.n_seg = static_cast<int>(n_seg);
+  p.x = bf16_ptr(x);
+  p.ldx = x.stride(0);
+  if (out.scalar_type() == torch::kFloat32)
+    p.out_f32 = out.data_ptr<float>();
+  else
+    p.out_bf16 = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  TORCH_CHECK(out.size(1) >= rows && out.size(0) >= x.size(0), "mmvq_mixed: out too small");
+  p.ldo = out.stride(0);
+  p.M = static_cast<int>(x.size(0));
+  p.N = static_cast<int>(rows);
+  p.K = static_cast<int>(K);
+  TORCH_CHECK(xq.element_size() == 1 && xq.is_contiguous() && xq.size(0) >= x.size(0) && xq.size(1) == K &&
+                  xd.is_contiguous() && xs.is_contiguous() && xd.size(1) == K / 32 && xs.size(1) == K / 32,
+              "mmvq_mixed: xq [M, K] int8 with xd / xs [M, K/32] fp32 expected");
+  p.xq = reinterpret_cast<const int8_t*>(xq.data_ptr());
+  p.xd = xd.data_ptr<float>();
+  p.xs = xs.data_ptr<float>();
+  TORCH_CHECK(oxb::launch_mmvq_mixed(p, cur_stream()),
+              "mmvq_mixed: a segment's block type has no integer path or an operand is misaligned");
+  check_launch("mmvq_mixed");
 }
 
 // x: [M <= 8, K] bf16; w: [N, K] bf16 or tile-major [N/128, K/64, 128, 64]; out: [M, N] (or [M, N/2] with swiglu).
@@ -820,6 +926,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_bf16", &gemm_bf16);
   m.def("quant_act_nvfp4", &quant_act_nvfp4);
   m.def("gemm_max_fixup_splits", &oxb::gemm_max_fixup_splits);
+  m.def("set_pdl", [](bool on) { oxb::pdl_enabled() = on; },
+        "programmatic dependent launch of the GEMM / finalize / RoPE / decode-attention kernels");
+  m.def("pdl_enabled", []() { return oxb::pdl_enabled(); });
   m.def("gemm_fp8_block", &gemm_fp8_block);
   m.def("quant_act_fp8", &quant_act_fp8);
   m.def("paged_decode", &paged_decode);
@@ -832,6 +941,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fwht128", &fwht128);
   m.def("kv_block_copy", &kv_block_copy);
   m.def("softcap", &softcap);
+  m.def("alloc_mapped_host", &alloc_mapped_host);
+  m.def("advance_decode_step", &advance_decode_step);
+  m.def("mmvq_mixed", &mmvq_mixed);
+  m.def("mmvq_has_int8_path", [](int64_t t) { return oxb::mmvq_has_int8_path(static_cast<int>(t)); });
   m.def("mmvq", &mmvq);
   m.def("gemv_bf16", &gemv_bf16);
   m.def("quant_q8_1", &quant_q8_1);

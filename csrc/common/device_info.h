@@ -46,4 +46,37 @@ inline void ensure_dynamic_smem(K kernel, size_t bytes) {
   }
 }
 
+// Programmatic dependent launch of the kernels that support it (they call pdl_wait() before their
+// first dependent access): process-wide switch, off until the embedding program turns it on.
+inline bool& pdl_enabled() {
+  static bool on = false;
+  return on;
+}
+
+// One launch through cudaLaunchKernelEx. `pdl`: the kernel may become resident before the previous
+// kernel of the stream has finished (only honoured when pdl_enabled()). `cooperative`: all CTAs
+// resident at once; such a launch never takes the programmatic attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, bool pdl, bool cooperative, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (cooperative) {
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  } else if (pdl && pdl_enabled()) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 }  // namespace oxb

@@ -48,6 +48,17 @@ __device__ __forceinline__ uint32_t elect_one_sync() {
   return pred;
 }
 
+// Programmatic dependent launch. `pdl_launch_dependents` lets the next kernel of the stream (if it was
+// launched with the programmatic-serialization attribute) become resident once every CTA of this
+// grid has executed it or exited; `pdl_wait` blocks until the prerequisite grid has completed and
+// its memory operations are visible. A kernel launched with the attribute must execute `pdl_wait`
+// before its first access to anything an earlier kernel wrote or reads (completion is transitive
+// only if every such kernel waits). Both are no-ops for a launch without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------

@@ -125,6 +125,24 @@ class SequenceBlockTable {
     return true;
   }
 
+  // Holds blocks for `n` tokens beyond num_tokens() without changing the length, so that the next
+  // advance() calls up to that point allocate nothing (a burst of decode steps whose block table is
+  // handed to the device once). All or nothing. rewind_to() gives unused reservations back.
+  bool reserve(int n) {
+    const int need_blocks = (num_tokens_ + n + kTokensPerBlock - 1) / kTokensPerBlock;
+    std::vector<int> fresh;
+    for (int i = static_cast<int>(blocks_.size()); i < need_blocks; ++i) {
+      int b = pool_->allocate();
+      if (b < 0) {
+        for (int f : fresh) pool_->release(f);
+        return false;
+      }
+      fresh.push_back(b);
+    }
+    blocks_.insert(blocks_.end(), fresh.begin(), fresh.end());
+    return true;
+  }
+
   // Speculative decoding: everything up to num_tokens() becomes permanent.
   void commit() { committed_ = num_tokens_; }
   // O(blocks dropped) rollback to `tokens` (>= committed prefix is the caller's contract).

@@ -1,5 +1,6 @@
 // Python bindings of the C++ host runtime (extension `oxb_host`): block pool, sequence block
 // tables, radix prefix cache and the continuous-batching scheduler core.
+#include <cstring>
 #include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
 #include <pybind11/functional.h>
@@ -161,6 +162,20 @@ PYBIND11_MODULE(oxb_host, m) {
            py::arg("sink_blocks") = 1, py::arg("rolling_blocks") = 16, py::arg("budget_blocks") = 128)
       .def("inject_prefill_error", &Scheduler::inject_prefill_error)
       .def("append_forced", &Scheduler::append_forced)
+      .def("reserve_ahead", &Scheduler::reserve_ahead)
+      .def("radix_cached_blocks", &Scheduler::radix_cached_blocks)
+      .def("radix_adopt", &Scheduler::radix_adopt)
+      .def("record_evictions", [](Scheduler& s, bool on) { s.radix().record_evictions(on); })
+      .def("take_evicted",
+           [](Scheduler& s) {
+             py::list out;
+             for (auto& e : s.radix().take_evicted()) {
+               py::array_t<int32_t> toks(static_cast<py::ssize_t>(e.tokens.size()));
+               std::memcpy(toks.mutable_data(), e.tokens.data(), e.tokens.size() * sizeof(int32_t));
+               out.append(py::make_tuple(toks, e.first_block, e.blocks));
+             }
+             return out;
+           })
       .def("take_events", &Scheduler::take_events)
       .def("schedule", &Scheduler::schedule)
       .def("update",

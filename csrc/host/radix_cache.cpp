@@ -152,6 +152,16 @@ int RadixCache::evict(int want, bool by_utility) {
     }
     if (victim == nullptr) break;
     freed += static_cast<int>(victim->blocks.size());
+    if (record_evictions_) {
+      Evicted e;
+      std::vector<Node*> path;
+      for (Node* n = victim; n != nullptr && n != root_.get(); n = n->parent) path.push_back(n);
+      for (auto it = path.rbegin(); it != path.rend(); ++it)
+        e.tokens.insert(e.tokens.end(), (*it)->tokens.begin(), (*it)->tokens.end());
+      e.first_block = static_cast<int>((e.tokens.size() - victim->tokens.size()) / kTokensPerBlock);
+      e.blocks = victim->blocks;
+      evicted_.push_back(std::move(e));
+    }
     remove_leaf(victim);
   }
   return freed;

@@ -37,6 +37,21 @@ class RadixCache {
   int evict(int want, bool by_utility = false);
   void clear();
 
+  // Demotion hook: when recording, every leaf that evict() removes is logged with its whole token
+  // prefix (root to the end of the leaf), so the owner of the device pool can copy the blocks'
+  // contents to a slower tier before anything overwrites them.
+  struct Evicted {
+    std::vector<int32_t> tokens;  // the prefix the blocks complete, a multiple of 16 tokens
+    int first_block = 0;          // index (in blocks of that prefix) of blocks[0]
+    std::vector<int> blocks;
+  };
+  void record_evictions(bool on) { record_evictions_ = on; }
+  std::vector<Evicted> take_evicted() {
+    std::vector<Evicted> out;
+    out.swap(evicted_);
+    return out;
+  }
+
   int cached_blocks() const { return cached_blocks_; }
   uint64_t lookups() const { return lookups_; }
   uint64_t hit_tokens() const { return hit_tokens_; }
@@ -62,6 +77,8 @@ class RadixCache {
   int cached_blocks_ = 0;
   int num_nodes_ = 0;
   uint64_t lookups_ = 0, hit_tokens_ = 0, lookup_tokens_ = 0;
+  bool record_evictions_ = false;
+  std::vector<Evicted> evicted_;
 };
 
 }  // namespace oxb

@@ -220,6 +220,49 @@ std::vector<TokenEvent> Scheduler::append_forced(int64_t id, const std::vector<i
   return events;
 }
 
+int Scheduler::reserve_ahead(int64_t id, int n) {
+  for (auto& up : running_) {
+    Request* r = up.get();
+    if (r->id != id) continue;
+    if (r->phase != Phase::Decode || r->dropped != 0) return 0;
+    const int cap = cfg_.max_blocks_per_seq * kTokensPerBlock;
+    n = std::min(n, r->max_new_tokens - r->generated());
+    n = std::min(n, cap - 1 - static_cast<int>(r->tokens.size()));
+    while (n > 0 && !r->table->reserve(n)) n /= 2;
+    return std::max(n, 0);
+  }
+  return 0;
+}
+
+int Scheduler::radix_cached_blocks(const std::vector<int32_t>& tokens) {
+  if (!cfg_.enable_radix) return 0;
+  return radix_.match(tokens.data(), static_cast<int>(tokens.size()), false).tokens / kTokensPerBlock;
+}
+
+std::vector<int> Scheduler::radix_adopt(const std::vector<int32_t>& tokens, int n_blocks) {
+  std::vector<int> fresh;
+  if (!cfg_.enable_radix || n_blocks <= 0 || static_cast<int>(tokens.size()) < n_blocks * kTokensPerBlock)
+    return fresh;
+  RadixCache::Match m = radix_.match(tokens.data(), n_blocks * kTokensPerBlock, false);
+  const int have = m.tokens / kTokensPerBlock;
+  if (have >= n_blocks) return fresh;
+  for (int i = have; i < n_blocks; ++i) {
+    const int b = pool_.allocate();
+    if (b < 0) {
+      for (int f : fresh) pool_.release(f);
+      fresh.clear();
+      return fresh;
+    }
+    fresh.push_back(b);
+  }
+  std::vector<int> ids(m.blocks.begin(), m.blocks.begin() + have);
+  ids.insert(ids.end(), fresh.begin(), fresh.end());
+  const int added = radix_.insert(tokens.data(), ids.data(), n_blocks);  // the cache takes its own reference
+  for (int b : fresh) pool_.release(b);                                  // ... and is now the only holder
+  if (added != static_cast<int>(fresh.size())) fresh.clear();            // nothing was taken (key collision)
+  return fresh;
+}
+
 void Scheduler::offer_to_radix(Request* r) {
   if (!cfg_.enable_radix || r->dropped > 0) return;  // pruned KV is not a reusable prefix
   const int n_full = std::min<int>(r->computed, static_cast<int>(r->tokens.size())) / kTokensPerBlock;

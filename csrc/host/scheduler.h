@@ -113,6 +113,17 @@ class Scheduler {
   // row gives the logits of the next free choice (continuous_batching.rs:475,807,1328). Returns one
   // event per appended token (the request may finish on a stop id or its length limit).
   std::vector<TokenEvent> append_forced(int64_t id, const std::vector<int32_t>& forced);
+  // Decode burst: holds KV blocks for up to `n` further tokens of a decoding request, so that the
+  // next decode plans of that request allocate nothing and the block table of the first plan is
+  // valid for all of them. Returns how many tokens are covered (0..n; fewer when the pool, the
+  // context limit or the request's token budget is short).
+  int reserve_ahead(int64_t id, int n);
+  // KV tiers. Number of whole blocks of `tokens` that the device prefix cache holds right now.
+  int radix_cached_blocks(const std::vector<int32_t>& tokens);
+  // Makes the first `n_blocks` blocks of `tokens` a cached prefix: blocks already cached stay, the
+  // rest are taken from the pool and handed to the cache. Returns the ids of the new blocks, in
+  // order (the caller fills them before the next launch); empty when the pool is short.
+  std::vector<int> radix_adopt(const std::vector<int32_t>& tokens, int n_blocks);
   // Events that schedule() produced (requests it had to end because they can never fit the pool).
   std::vector<TokenEvent> take_events();
   // Fault hook: the next prefill chunk of this request fails (host-side fault injection).

@@ -26,6 +26,13 @@ struct DecodeAttnParams {
   // (kStatusBadIndex) and page 0 is read instead. num_blocks <= 0 or status == nullptr: no check.
   int num_blocks;
   int* status;
+  // Heavy-hitter statistics (optional, both or neither): the split kernel records for every attended
+  // page and query head the pair (reference max in log2 units, sum of 2^(x - max) over the page's 16
+  // tokens) in page_ml [B, max_blocks, Hq, 2]; after the merge a third kernel turns them into
+  // block_mass [B, max_blocks] = sum over heads of the softmax probability that fell into the page
+  // (0 for pages outside the attended range).
+  float* page_ml;
+  float* block_mass;
 };
 
 // Launches the split kernel and then the merge; the merge is skipped when the first launch failed.

@@ -35,6 +35,11 @@ constexpr int kPage = 16;
 constexpr int kWarps = 4;
 constexpr int kRing = 3;   // pages per warp in the shared-memory ring (2 in flight while 1 is consumed)
 
+// see sm100.cuh (this file is also built into the plain C library, without the tensor-core header)
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gsrc) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
 }
@@ -77,7 +82,8 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 // D = head dim (64 or 128); NT = number of 8-head column tiles (group size <= 8*NT).
-template <int D, int NT>
+// MASS: also record the per-page softmax statistics of every head (see DecodeAttnParams::page_ml).
+template <int D, int NT, bool MASS>
 __global__ void __launch_bounds__(kWarps * 32)
 paged_decode_kernel(const DecodeAttnParams p) {
   constexpr int KS = D / 16;   // k-steps of QK^T
@@ -85,6 +91,8 @@ paged_decode_kernel(const DecodeAttnParams p) {
   constexpr int VCH = D / 64;  // 16-byte V chunks per lane per token
   constexpr int MT = D / 16;   // m-tiles of O^T
 
+  pdl_launch_dependents();
+  pdl_wait();  // q and the newest K/V rows come from the kernel before this one
   const int seq = blockIdx.x;
   const int kvh = blockIdx.y;
   const int split = blockIdx.z;
@@ -279,6 +287,21 @@ paged_decode_kernel(const DecodeAttnParams p) {
       const float p10 = ex2(x10 - ms0), p11 = ex2(x11 - ms1);
       l_run[nt][0] = l_run[nt][0] * a0 + p00 + p10;
       l_run[nt][1] = l_run[nt][1] * a1 + p01 + p11;
+      if constexpr (MASS) {
+        float ps0 = p00 + p10, ps1 = p01 + p11;
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+          ps0 += __shfl_xor_sync(0xffffffffu, ps0, o);
+          ps1 += __shfl_xor_sync(0xffffffffu, ps1, o);
+        }
+        const int h0 = nt * 8 + 2 * t;
+        if (g == 0 && h0 < G) {
+          float2* dst = reinterpret_cast<float2*>(p.page_ml) +
+                        (static_cast<long long>(seq) * p.max_blocks + page) * p.Hq + kvh * G + h0;
+          dst[0] = make_float2(ms0, ps0);
+          if (h0 + 1 < G) dst[1] = make_float2(ms1, ps1);
+        }
+      }
 #pragma unroll
       for (int i = 0; i < MT; ++i) {
         o_acc[nt][i][0] *= a0;
@@ -369,6 +392,8 @@ paged_decode_kernel(const DecodeAttnParams p) {
 // out[seq, head, :] = sum_s w_s O_s / sum_s w_s l_s  with  w_s = 2^(m_s - max m)
 template <int D>
 __global__ void __launch_bounds__(D) decode_merge_kernel(const DecodeAttnParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int seq = blockIdx.x;
   const int head = blockIdx.y;
   const int d = threadIdx.x;
@@ -387,6 +412,45 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const DecodeAttnParams 
   p.out[static_cast<long long>(seq) * p.out_stride + head * D + d] = __float2bfloat16(r);
 }
 
+// block_mass[seq, page] = sum_h page_sum[h] * 2^(page_max[h] - M_h) / L_h, with (M_h, L_h) the merged
+// statistics of head h over all splits: the softmax probability mass the step's query put on the page.
+__global__ void __launch_bounds__(128) block_mass_kernel(const DecodeAttnParams p) {
+  __shared__ float s_M[128], s_rL[128];
+  const int seq = blockIdx.x;
+  const int seq_len = p.seq_lens[seq];
+  int n_pages = (seq_len + kPage - 1) / kPage;
+  if (n_pages > p.max_blocks) n_pages = p.max_blocks;
+  const int win_start = (p.window > 0 && seq_len > p.window) ? seq_len - p.window : 0;
+  const int first_page = win_start / kPage;
+  int last_page = first_page + *p.pages_per_split * p.max_splits;  // pages past the last split were not walked
+  if (last_page > n_pages) last_page = n_pages;
+  for (int h = threadIdx.x; h < p.Hq; h += blockDim.x) {
+    const long long base = (static_cast<long long>(seq) * p.Hq + h) * p.max_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < p.max_splits; ++s) M = fmaxf(M, p.part_ml[(base + s) * 2]);
+    float L = 0.f;
+    for (int s = 0; s < p.max_splits; ++s) {
+      const float ms = p.part_ml[(base + s) * 2];
+      if (ms != -INFINITY) L += ex2(ms - M) * p.part_ml[(base + s) * 2 + 1];
+    }
+    s_M[h] = M;
+    s_rL[h] = L > 0.f ? 1.f / L : 0.f;
+  }
+  __syncthreads();
+  for (int page = threadIdx.x; page < p.max_blocks; page += blockDim.x) {
+    float mass = 0.f;
+    if (page >= first_page && page < last_page && seq_len > 0) {
+      const float2* ml =
+          reinterpret_cast<const float2*>(p.page_ml) + (static_cast<long long>(seq) * p.max_blocks + page) * p.Hq;
+      for (int h = 0; h < p.Hq; ++h) {
+        const float2 v = ml[h];
+        if (v.y > 0.f) mass += v.y * ex2(v.x - s_M[h]) * s_rL[h];
+      }
+    }
+    p.block_mass[static_cast<long long>(seq) * p.max_blocks + page] = mass;
+  }
+}
+
 }  // namespace
 
 template <int D, int NT>
@@ -395,9 +459,15 @@ void launch_split(const DecodeAttnParams& p, dim3 grid, cudaStream_t stream) {
   constexpr size_t ring = static_cast<size_t>(kWarps) * kRing * 2 * kPage * D * 2;
   constexpr size_t merge = sizeof(float) * kWarps * 8 * NT * (D + 2);
   constexpr size_t smem = ring > merge ? ring : merge;
-  auto kern = paged_decode_kernel<D, NT>;
-  ensure_dynamic_smem(kern, smem);
-  kern<<<grid, kWarps * 32, smem, stream>>>(p);
+  if (p.page_ml != nullptr) {
+    auto kern = paged_decode_kernel<D, NT, true>;
+    ensure_dynamic_smem(kern, smem);
+    launch_kernel(kern, grid, dim3(kWarps * 32), smem, stream, /*pdl=*/true, false, p);
+  } else {
+    auto kern = paged_decode_kernel<D, NT, false>;
+    ensure_dynamic_smem(kern, smem);
+    launch_kernel(kern, grid, dim3(kWarps * 32), smem, stream, /*pdl=*/true, false, p);
+  }
 }
 
 cudaError_t launch_paged_decode(const DecodeAttnParams& p, int batch, int head_dim, cudaStream_t stream) {
@@ -419,9 +489,10 @@ cudaError_t launch_paged_decode(const DecodeAttnParams& p, int batch, int head_d
   const cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) return e;
   if (head_dim == 128)
-    decode_merge_kernel<128><<<mgrid, 128, 0, stream>>>(p);
+    launch_kernel(decode_merge_kernel<128>, mgrid, dim3(128), 0, stream, /*pdl=*/true, false, p);
   else
-    decode_merge_kernel<64><<<mgrid, 64, 0, stream>>>(p);
+    launch_kernel(decode_merge_kernel<64>, mgrid, dim3(64), 0, stream, /*pdl=*/true, false, p);
+  if (p.page_ml != nullptr && p.block_mass != nullptr) block_mass_kernel<<<batch, 128, 0, stream>>>(p);
   return cudaPeekAtLastError();
 }
 

@@ -59,6 +59,8 @@ __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const Fi
   extern __shared__ float s_h[];  // N floats, used only by the MoE router path
   __shared__ float s_red[32];
   __shared__ int s_ok;
+  pdl_launch_dependents();
+  pdl_wait();  // the accumulators / slabs, the residual and the hand-off counters belong to earlier kernels
   const int N = p.N;
   const int nthr = blockDim.x;
 
@@ -318,6 +320,8 @@ __global__ void __launch_bounds__(256) qkv_rope_append_kernel(const QkvRopeParam
   extern __shared__ float s_row[];  // (Hq + 2 Hkv) * D floats
   __shared__ float s_ssq[160];      // per-head sum of squares (Hq + Hkv <= 160)
   __shared__ float s_sin[128], s_cos[128];  // the token's rotation, shared by every head (D <= 256)
+  pdl_launch_dependents();
+  pdl_wait();  // the QKV rows come from the kernel before this one
   const int tok = blockIdx.x;
   const int D = p.D, half = D >> 1;
   const int W = (p.Hq + 2 * p.Hkv) * D;
@@ -536,7 +540,41 @@ __global__ void softcap_kernel(float* x, long long n, float cap) {
     x[i] = cap * tanhf(x[i] / cap);
 }
 
+// Reference counterpart: advance_decode_step_kernel (oxide-backend-cuda/src/kernels/megakernel_ops.cu:331-357)
+// and the pinned step counter the host spins on (oxide-backend-cuda/src/lib.rs:4150-4247).
+__global__ void advance_decode_step_kernel(const AdvanceStepParams p) {
+  __shared__ unsigned int s_step;
+  if (threadIdx.x == 0) s_step = *p.step_counter + 1;
+  __syncthreads();
+  const unsigned int step = s_step;
+  for (int r = threadIdx.x; r < p.rows; r += blockDim.x) {
+    const int tok = p.sampled[r];
+    if (p.seq_lens[r] > 0) {  // padding rows of the batch bucket stay as they are
+      const int pos = p.positions[r] + 1;
+      const int blk = pos >> 4;
+      if (blk >= p.max_blocks) {
+        if (p.status != nullptr) atomicCAS(p.status, 0, kStatusBadIndex);
+      } else {
+        p.token_ids[r] = tok;
+        p.positions[r] = pos;
+        p.seq_lens[r] += 1;
+        p.slot_mapping[r] = static_cast<long long>(p.block_tables[static_cast<long long>(r) * p.max_blocks + blk]) * 16 + (pos & 15);
+      }
+    }
+    p.mailbox[static_cast<size_t>((step - 1) % p.ring) * p.rows + r] =
+        (static_cast<unsigned long long>(step) << 32) | static_cast<unsigned int>(tok);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) *p.step_counter = step;
+}
+
 }  // namespace
+
+void launch_advance_decode_step(const AdvanceStepParams& p, cudaStream_t stream) {
+  if (p.rows <= 0) return;
+  advance_decode_step_kernel<<<1, 256, 0, stream>>>(p);
+}
 
 void launch_finalize_norm(const FinalizeNormParams& p, cudaStream_t stream) {
   if (p.rows <= 0) return;
@@ -550,14 +588,14 @@ void launch_finalize_norm(const FinalizeNormParams& p, cudaStream_t stream) {
   // flight where registers allow two resident CTAs, and cost nothing where they do not
   const int max_ctas = 2 * sm_count();
   const int grid = p.rows < max_ctas ? p.rows : max_ctas;
-  finalize_norm_kernel<<<grid, threads, smem, stream>>>(p);
+  launch_kernel(finalize_norm_kernel, dim3(grid), dim3(threads), smem, stream, /*pdl=*/true, false, p);
 }
 
 void launch_qkv_rope_append(const QkvRopeParams& p, cudaStream_t stream) {
   if (p.M <= 0) return;
   const size_t smem = static_cast<size_t>(p.Hq + 2 * p.Hkv) * p.D * sizeof(float);
   ensure_dynamic_smem(qkv_rope_append_kernel, smem);
-  qkv_rope_append_kernel<<<p.M, 256, smem, stream>>>(p);
+  launch_kernel(qkv_rope_append_kernel, dim3(p.M), dim3(256), smem, stream, /*pdl=*/true, false, p);
 }
 
 void launch_swiglu(const SwigluParams& p, cudaStream_t stream) {

@@ -92,4 +92,24 @@ void launch_kv_block_copy(__nv_bfloat16* k_cache, __nv_bfloat16* v_cache, const 
                           cudaStream_t stream);
 void launch_softcap(float* logits, long long n, float cap, cudaStream_t stream);
 
+// In-graph step advance of a decode burst: after the step's argmax, row r of the step descriptor is
+// rewritten for the next step (token = the sampled id, position and length + 1, KV slot of the new
+// position from the row's block table), and the sampled ids are posted to a ring in mapped pinned
+// host memory that the host polls, so that several replays of the decode graph run back to back
+// without a host round trip. Mailbox word = (step number << 32) | token; the step counter lives on
+// the device and counts from 1.
+struct AdvanceStepParams {
+  int* token_ids;            // [rows]
+  int* positions;            // [rows]
+  long long* slot_mapping;   // [rows]
+  int* seq_lens;             // [rows]
+  const int* block_tables;   // [rows, max_blocks]
+  const int* sampled;        // [rows] this step's argmax
+  unsigned long long* mailbox;  // device address of mapped host memory, [ring][rows]
+  unsigned int* step_counter;   // device, [1]
+  int rows, max_blocks, ring;
+  int* status;               // a position past the block-table row is recorded (kStatusBadIndex), the row stops advancing
+};
+void launch_advance_decode_step(const AdvanceStepParams& p, cudaStream_t stream);
+
 }  // namespace oxb

@@ -219,6 +219,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   static_assert(kBufs * kItemCols + kSFCols <= 512, "TMEM budget");
   static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM allocation");
 
+  // Programmatic dependent launch: the next kernel of the stream may become resident as soon as
+  // every CTA of this grid has started; nothing below that depends on an earlier kernel runs before
+  // pdl_wait(). Both are no-ops for a launch without the attribute.
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     stamp(p, 0);
     tma_prefetch_desc(&tmA);
@@ -236,6 +240,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     fence_mbar_init();
     int ok = 1;
     if (grouped) {
+      pdl_wait();
       // The per-group row counts are final only once every source has finished dispatching.
       if (p.ag_flags != nullptr) ok = wait_sources(p, 0, p.ag_n_src - 1, gridDim.x) ? 1 : 0;
       int acc = 0;
@@ -248,14 +253,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     s_misc[0] = ok;
     s_misc[1] = 1;
   }
-  if (warp == 1) {
-    tmem_alloc(tmem_slot, kTmemCols);
-    tmem_relinquish();
+  __syncthreads();  // barriers, start-up state
+  // The producer warp goes ahead (its first weight tiles depend on no earlier kernel). The other
+  // warps wait for the prerequisite grid first, and TMEM is allocated only after that wait: a CTA
+  // that held TMEM while it waited could starve a CTA of the prerequisite grid on the same SM.
+  uint32_t tmem_base = 0;
+  if (warp >= 1) {
+    pdl_wait();
+    if (warp == 1) {
+      tmem_alloc(tmem_slot, kTmemCols);
+      tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    asm volatile("bar.sync 2, 160;" ::: "memory");
+    tc_fence_after_sync();
+    tmem_base = *tmem_slot;
   }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
   const bool all_ok = s_misc[0] != 0;
 
   // work item w -> tile coordinates; consecutive items share the weight tile (m fastest)
@@ -298,14 +311,43 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     constexpr int kBOps = (BN + 127) / 128;  // tile-major weights: one box per 128 weight rows
     uint32_t iter = 0;  // k-block counter across all items of this CTA
     bool ok = true;
+    bool pdl_pending = true;  // this warp has not yet waited for the prerequisite grid
+    if (grouped) {            // grouped tiles depend on the dispatch from the start
+      pdl_wait();
+      pdl_pending = false;
+    }
+    // copies of a k block that depend on earlier kernels or on peers: activations (and their scales)
+    auto issue_a = [&](const WorkItem& it, int kb, uint32_t iter_kb) __attribute__((always_inline)) {
+      const int s = iter_kb % STAGES;
+      const int op = lane - (s & 7) * 4;
+      if (KIND && op == 3)
+        bulk_load(sSF + s * (L::kSFABytes + L::kSFBBytes),
+                  p.sfa + ((static_cast<long long>(it.group) * p.sfa_group_tiles + (it.m0 >> 7)) * total_kb +
+                           it.kb0 + kb) * 2048,
+                  L::kSFABytes, &full[s]);
+      // rows past M read as zeros (the box is filled in full either way)
+      if (p.wide_boxes && MT == 2) {
+        if (op == 2) tma_load_3d(sA + s * L::kABytes, &tmA, &full[s], (it.kb0 + kb) * kXStep, it.m0, it.group);
+      } else if (op >= 2 && op < 2 + MT)
+        tma_load_3d(sA + s * L::kABytes + (op - 2) * (BM * BK * 2), &tmA, &full[s], (it.kb0 + kb) * kXStep,
+                    it.m0 + (op - 2) * BM, it.group);
+    };
     for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
       const WorkItem it = decode(w);
       bool need_wait = p.ag_flags != nullptr && !grouped;
       if (!it.valid) {
+        if (pdl_pending) {
+          pdl_wait();
+          pdl_pending = false;
+        }
         // keep the waiter count of the grid exact: an empty item still passes the gate
         if (need_wait && lane == 0) wait_sources(p, 0, -1, static_cast<uint32_t>(n_work));
         continue;
       }
+      // On the first item the weight copies of the whole ring are requested before this warp waits
+      // for the prerequisite grid and for the peers; the activation copies of those k blocks follow
+      // right after the wait. Later items pass the gate at their first k block.
+      const int hold = pdl_pending ? (it.nkb < STAGES ? it.nkb : STAGES) - 1 : 0;
       for (int kb = 0; kb < it.nkb && ok; ++kb, ++iter) {
         const int s = iter % STAGES;
         const uint32_t ph = (iter / STAGES) & 1;
@@ -318,21 +360,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0) mbar_arrive_expect_tx(&full[s], L::kABytes + L::kBBytes + L::kSFABytes + L::kSFBBytes);
         __syncwarp();
         const int op = lane - (s & 7) * 4;  // which copy of this stage this lane issues (0..3), if any
-        if (KIND) {
+        // weights (and their scales) first: they depend on nothing that runs before this kernel
+        if (KIND && op == 1)
           // the scale atoms of this k block: 2 KB per 128 rows, contiguous in [row tile][k block]
-          uint8_t* sf = sSF + s * (L::kSFABytes + L::kSFBBytes);
-          if (op == 1)
-            bulk_load(sf + L::kSFABytes,
-                      p.sfb + ((static_cast<long long>(it.group) * ((p.N + 127) / 128) + (it.n0 >> 7)) * total_kb +
-                               it.kb0 + kb) * 2048,
-                      L::kSFBBytes, &full[s]);
-          if (op == 3)
-            bulk_load(sf,
-                      p.sfa + ((static_cast<long long>(it.group) * p.sfa_group_tiles + (it.m0 >> 7)) * total_kb +
-                               it.kb0 + kb) * 2048,
-                      L::kSFABytes, &full[s]);
-        }
-        // weights first: they do not depend on any peer
+          bulk_load(sSF + s * (L::kSFABytes + L::kSFBBytes) + L::kSFABytes,
+                    p.sfb + ((static_cast<long long>(it.group) * ((p.N + 127) / 128) + (it.n0 >> 7)) * total_kb +
+                             it.kb0 + kb) * 2048,
+                    L::kSFBBytes, &full[s]);
         if (p.b_tiled && p.wide_boxes && BN == 256) {
           // both 128-row weight tiles of this k block in one 32 KB copy: [64][128][k block][n tile]
           if (op == 0) tma_load_4d(sB + s * L::kBBytes, &tmB, &full[s], 0, 0, it.kb0 + kb, it.n0 >> 7);
@@ -345,29 +379,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         } else if (op == 0) {
           tma_load_3d(sB + s * L::kBBytes, &tmB, &full[s], (it.kb0 + kb) * kXStep, it.n0, it.group);
         }
-        if (need_wait) {
-          int src_ok = 1;
-          if (lane == 0) {
-            int s_lo = 0, s_hi = p.ag_n_src - 1;  // rows_per_src <= 0: rows are not grouped by source
-            if (p.ag_rows_per_src > 0) {
-              const int m_end = it.m0 + BM * MT < it.rows ? it.m0 + BM * MT : it.rows;
-              s_lo = it.m0 / p.ag_rows_per_src;
-              s_hi = (m_end - 1) / p.ag_rows_per_src;
-              if (s_hi >= p.ag_n_src) s_hi = p.ag_n_src - 1;
-              if (s_lo > s_hi) s_lo = s_hi;
-            }
-            src_ok = wait_sources(p, s_lo, s_hi, static_cast<uint32_t>(n_work)) ? 1 : 0;
+        if (kb < hold) continue;  // activation copies of this k block are issued at k block `hold`
+        if (kb == hold) {
+          if (pdl_pending) {
+            pdl_wait();
+            pdl_pending = false;
           }
-          ok = __shfl_sync(0xffffffffu, src_ok, 0) != 0;
-          need_wait = false;
-          if (!ok) break;
+          if (need_wait) {
+            int src_ok = 1;
+            if (lane == 0) {
+              int s_lo = 0, s_hi = p.ag_n_src - 1;  // rows_per_src <= 0: rows are not grouped by source
+              if (p.ag_rows_per_src > 0) {
+                const int m_end = it.m0 + BM * MT < it.rows ? it.m0 + BM * MT : it.rows;
+                s_lo = it.m0 / p.ag_rows_per_src;
+                s_hi = (m_end - 1) / p.ag_rows_per_src;
+                if (s_hi >= p.ag_n_src) s_hi = p.ag_n_src - 1;
+                if (s_lo > s_hi) s_lo = s_hi;
+              }
+              src_ok = wait_sources(p, s_lo, s_hi, static_cast<uint32_t>(n_work)) ? 1 : 0;
+            }
+            ok = __shfl_sync(0xffffffffu, src_ok, 0) != 0;
+            need_wait = false;
+            if (!ok) break;
+          }
+          for (int kk = 0; kk < hold; ++kk) issue_a(it, kk, iter - static_cast<uint32_t>(hold - kk));
         }
-        // rows past M read as zeros (the box is filled in full either way)
-        if (p.wide_boxes && MT == 2) {
-          if (op == 2) tma_load_3d(sA + s * L::kABytes, &tmA, &full[s], (it.kb0 + kb) * kXStep, it.m0, it.group);
-        } else if (op >= 2 && op < 2 + MT)
-          tma_load_3d(sA + s * L::kABytes + (op - 2) * (BM * BK * 2), &tmA, &full[s], (it.kb0 + kb) * kXStep,
-                      it.m0 + (op - 2) * BM, it.group);
+        issue_a(it, kb, iter);
       }
     }
   } else if (warp == 1) {
@@ -797,20 +834,9 @@ void launch_impl(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParam
   const int sms = sm_count();
   const int n_work = ((p.N + BN - 1) / BN) * p.m_tiles * p.splits;
   const int grid = n_work < sms ? n_work : sms;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = L::kTotal;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  if (p.ws != nullptr && p.splits > 1) {
-    // the splits of a tile wait for each other: ask for a launch that is resident as a whole
-    attr[0].id = cudaLaunchAttributeCooperative;
-    attr[0].val.cooperative = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-  }
-  cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p);
+  // the splits of a tile wait for each other: ask for a launch that is resident as a whole
+  const bool cooperative = p.ws != nullptr && p.splits > 1;
+  launch_kernel(kern, dim3(grid), dim3(kThreads), L::kTotal, stream, /*pdl=*/true, cooperative, tmA, tmB, p);
 }
 
 int tiles_of(int M, int N, int bn, int mt) {

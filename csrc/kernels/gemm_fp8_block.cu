@@ -9,8 +9,10 @@
 // the scales outside the tensor core), while the MMA warp already fills the other buffer.
 // Warp 0 feeds a TMA ring, warp 1 issues the MMAs; every wait is bounded.
 //
-// Covers the reference's fp8 block-scaled path (oxide-kernels/src/cuda/cutlass_fp8_gemm.cu,
-// fp8_gemm.cu:75-129, and the scale layout of fp8_blockwise.rs:55-77,163-175).
+// Reference counterpart: the e4m3 codec and the scaled fp8 block of crates/oxide-quant/src/fp8.rs
+// (Fp8E4M3 :13-98, BlockFp8E4M3 quantize / dequantize / dot_product :185-245). The reference has no
+// fp8 tensor-core GEMM; the 1x128 activation / 128x128 weight scale grid here is the usual layout of
+// block-scaled fp8 checkpoints.
 #include "gemm_fp8_block.cuh"
 
 #include <cuda_fp8.h>

@@ -357,6 +357,223 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q8_0_dp4a_kernel(const 
   }
 }
 
+// ---- integer path for the other block types ------------------------------------------------------
+// A group of 32 weights is rebuilt as eight words of four signed bytes q_j with
+//   w_j = dl0 * q_j + ml  (j < 16),   w_j = dl1 * q_j + ml  (j >= 16),
+// so a group's share of the dot product is  xd * (dl0 * sum_lo(q x) + dl1 * sum_hi(q x)) + ml * xs
+// with eight `dp4a` per activation row. Blocks are read with the widest loads their alignment allows
+// (Q4_0 / Q5_0 / Q8_0 / Q6_K blocks are only 2-byte aligned).
+__device__ __forceinline__ uint32_t ldg_u16(const uint8_t* p) {
+  return __ldg(reinterpret_cast<const uint16_t*>(p));
+}
+__device__ __forceinline__ uint32_t ldg_u32_a2(const uint8_t* p) { return ldg_u16(p) | (ldg_u16(p + 2) << 16); }
+__device__ __forceinline__ uint32_t ldg_u32(const uint8_t* p) { return __ldg(reinterpret_cast<const uint32_t*>(p)); }
+__device__ __forceinline__ float half_bits(uint32_t v) {
+  return __half2float(__ushort_as_half(static_cast<uint16_t>(v & 0xFFFFu)));
+}
+// bits 0..3 of x -> bit 4 of bytes 0..3
+__device__ __forceinline__ uint32_t spread_bit4(uint32_t x) {
+  return (((x & 0xFu) * 0x00204081u) & 0x01010101u) << 4;
+}
+
+template <int T>
+struct HasInt8Path {
+  static constexpr bool value = T == kQ_Q4_0 || T == kQ_Q4_1 || T == kQ_Q5_0 || T == kQ_Q5_1 || T == kQ_Q8_0 ||
+                                T == kQ_Q4_K || T == kQ_Q5_K || T == kQ_Q6_K;
+};
+
+template <int T>
+__device__ __forceinline__ void expand_q8(const uint8_t* row, int grp, uint32_t (&wq)[8], float& dl0, float& dl1,
+                                          float& ml) {
+  if constexpr (T == kQ_Q4_0) {
+    const uint8_t* b = row + static_cast<long long>(grp) * 18;
+    const float d = half_bits(ldg_u16(b));
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t w = ldg_u32_a2(b + 2 + 4 * u);
+      wq[u] = w & 0x0F0F0F0Fu;
+      wq[4 + u] = (w >> 4) & 0x0F0F0F0Fu;
+    }
+    dl0 = dl1 = d;
+    ml = -8.f * d;
+  } else if constexpr (T == kQ_Q4_1) {
+    const uint8_t* b = row + static_cast<long long>(grp) * 20;
+    const uint32_t hdr = ldg_u32(b);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t w = ldg_u32(b + 4 + 4 * u);
+      wq[u] = w & 0x0F0F0F0Fu;
+      wq[4 + u] = (w >> 4) & 0x0F0F0F0Fu;
+    }
+    dl0 = dl1 = half_bits(hdr);
+    ml = half_bits(hdr >> 16);
+  } else if constexpr (T == kQ_Q5_0) {
+    const uint8_t* b = row + static_cast<long long>(grp) * 22;
+    const float d = half_bits(ldg_u16(b));
+    const uint32_t qh = ldg_u32_a2(b + 2);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t w = ldg_u32_a2(b + 6 + 4 * u);
+      wq[u] = (w & 0x0F0F0F0Fu) | spread_bit4(qh >> (4 * u));
+      wq[4 + u] = ((w >> 4) & 0x0F0F0F0Fu) | spread_bit4(qh >> (16 + 4 * u));
+    }
+    dl0 = dl1 = d;
+    ml = -16.f * d;
+  } else if constexpr (T == kQ_Q5_1) {
+    const uint8_t* b = row + static_cast<long long>(grp) * 24;
+    const uint32_t hdr = ldg_u32(b);
+    const uint32_t qh = ldg_u32(b + 4);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t w = ldg_u32(b + 8 + 4 * u);
+      wq[u] = (w & 0x0F0F0F0Fu) | spread_bit4(qh >> (4 * u));
+      wq[4 + u] = ((w >> 4) & 0x0F0F0F0Fu) | spread_bit4(qh >> (16 + 4 * u));
+    }
+    dl0 = dl1 = half_bits(hdr);
+    ml = half_bits(hdr >> 16);
+  } else if constexpr (T == kQ_Q8_0) {
+    const uint8_t* b = row + static_cast<long long>(grp) * 34;
+    const float d = half_bits(ldg_u16(b));
+#pragma unroll
+    for (int u = 0; u < 8; ++u) wq[u] = ldg_u32_a2(b + 2 + 4 * u);
+    dl0 = dl1 = d;
+    ml = 0.f;
+  } else if constexpr (T == kQ_Q4_K || T == kQ_Q5_K) {
+    // Q4_K: d | dmin | scales[12] | qs[128];  Q5_K: d | dmin | scales[12] | qh[32] | qs[128]
+    constexpr int kBytes = T == kQ_Q4_K ? 144 : 176;
+    constexpr int kQs = T == kQ_Q4_K ? 16 : 48;
+    const uint8_t* b = row + static_cast<long long>(grp >> 3) * kBytes;
+    const int sub = grp & 7;
+    const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(b));
+    int sc, mn;
+    if (sub < 4) {
+      sc = byte_of3(hdr.y, hdr.z, hdr.w, sub) & 63;
+      mn = byte_of3(hdr.y, hdr.z, hdr.w, sub + 4) & 63;
+    } else {
+      sc = (byte_of3(hdr.y, hdr.z, hdr.w, sub + 4) & 0xF) | ((byte_of3(hdr.y, hdr.z, hdr.w, sub - 4) >> 6) << 4);
+      mn = (byte_of3(hdr.y, hdr.z, hdr.w, sub + 4) >> 4) | ((byte_of3(hdr.y, hdr.z, hdr.w, sub) >> 6) << 4);
+    }
+    const uint4* q = reinterpret_cast<const uint4*>(b + kQs + (sub >> 1) * 32);
+    const uint4 qa = __ldg(q), qb = __ldg(q + 1);
+    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    const int shift = (sub & 1) * 4;
+    if constexpr (T == kQ_Q4_K) {
+#pragma unroll
+      for (int u = 0; u < 8; ++u) wq[u] = (w[u] >> shift) & 0x0F0F0F0Fu;
+    } else {
+      const uint4* hp = reinterpret_cast<const uint4*>(b + 16);
+      const uint4 ha = __ldg(hp), hb = __ldg(hp + 1);
+      const uint32_t h[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        wq[u] = ((w[u] >> shift) & 0x0F0F0F0Fu) | (((h[u] >> sub) & 0x01010101u) << 4);
+    }
+    dl0 = dl1 = half_bits(hdr.x) * static_cast<float>(sc);
+    ml = -half_bits(hdr.x >> 16) * static_cast<float>(mn);
+  } else if constexpr (T == kQ_Q6_K) {
+    // ql[128] | qh[64] | scales[16] | d ; 210 bytes, 2-byte aligned
+    const uint8_t* b = row + static_cast<long long>(grp >> 3) * 210;
+    const int sub = grp & 7, half = sub >> 2, quarter = sub & 3;
+    const uint8_t* ql = b + half * 64 + (quarter & 1) * 32;
+    const uint8_t* qh = b + 128 + half * 32;
+    const int nib = (quarter >> 1) * 4, hs = 2 * quarter;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const uint32_t lo = (ldg_u32_a2(ql + 4 * u) >> nib) & 0x0F0F0F0Fu;
+      const uint32_t hi = ((ldg_u32_a2(qh + 4 * u) >> hs) & 0x03030303u) << 4;
+      wq[u] = __vsub4(lo | hi, 0x20202020u);
+    }
+    const uint32_t sc = ldg_u16(b + 192 + half * 8 + quarter * 2);
+    const float d = half_bits(ldg_u16(b + 208));
+    dl0 = d * static_cast<float>(static_cast<int8_t>(sc & 0xFF));
+    dl1 = d * static_cast<float>(static_cast<int8_t>(sc >> 8));
+    ml = 0.f;
+  }
+}
+
+// One weight row against MB int8 activation rows; every lane takes the groups lane, lane + 32, ...
+template <int T, int MB>
+__device__ __forceinline__ void row_dot_int8(const uint8_t* wrow, const MmvqParams& p, int m0, int lane,
+                                             float (&acc)[MB]) {
+  const int groups = p.K >> 5;
+#pragma unroll 2
+  for (int grp = lane; grp < groups; grp += 32) {
+    uint32_t wq[8];
+    float dl0, dl1, ml;
+    expand_q8<T>(wrow, grp, wq, dl0, dl1, ml);
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+      const int mm = m0 + m < p.M ? m0 + m : p.M - 1;  // a clamped duplicate row is not stored
+      const int4* xr = reinterpret_cast<const int4*>(p.xq + static_cast<long long>(mm) * p.K + grp * 32);
+      const int4 a = __ldg(xr), c = __ldg(xr + 1);
+      int lo = __dp4a(static_cast<int>(wq[0]), a.x, 0);
+      lo = __dp4a(static_cast<int>(wq[1]), a.y, lo);
+      lo = __dp4a(static_cast<int>(wq[2]), a.z, lo);
+      lo = __dp4a(static_cast<int>(wq[3]), a.w, lo);
+      int hi = __dp4a(static_cast<int>(wq[4]), c.x, 0);
+      hi = __dp4a(static_cast<int>(wq[5]), c.y, hi);
+      hi = __dp4a(static_cast<int>(wq[6]), c.z, hi);
+      hi = __dp4a(static_cast<int>(wq[7]), c.w, hi);
+      const long long bi = static_cast<long long>(mm) * groups + grp;
+      acc[m] += __ldg(p.xd + bi) * (dl0 * int_to_float(lo) + dl1 * int_to_float(hi)) + ml * __ldg(p.xs + bi);
+    }
+  }
+}
+
+template <int T, int MB>
+__global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_int8_kernel(const MmvqParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * kRowsPerCta + warp;
+  if (n >= p.N) return;
+  const int m0 = blockIdx.y * MB;
+  float acc[MB];
+#pragma unroll
+  for (int m = 0; m < MB; ++m) acc[m] = 0.f;
+  row_dot_int8<T, MB>(p.w + static_cast<long long>(n) * p.row_bytes, p, m0, lane, acc);
+#pragma unroll
+  for (int m = 0; m < MB; ++m) {
+    const float v = warp_sum(acc[m]);
+    if (lane == 0 && m0 + m < p.M) mmvq_store(p, n, m0 + m, v);
+  }
+}
+
+// Stacked matrices of different block types (Q|K|V or gate|up of a mixed-precision file) in one
+// launch: a warp looks up the segment of its output row; the type switch is uniform per warp.
+template <int MB>
+__global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_mixed_kernel(const MmvqParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * kRowsPerCta + warp;
+  if (n >= p.N) return;
+  const int m0 = blockIdx.y * MB;
+  int seg = 0, row0 = 0;
+#pragma unroll
+  for (int i = 0; i < 3; ++i)
+    if (seg == i && i + 1 < p.n_seg && n >= p.seg_row_end[i]) {
+      row0 = p.seg_row_end[i];
+      seg = i + 1;
+    }
+  const uint8_t* wrow = p.seg_w[seg] + static_cast<long long>(n - row0) * p.seg_row_bytes[seg];
+  float acc[MB];
+#pragma unroll
+  for (int m = 0; m < MB; ++m) acc[m] = 0.f;
+  switch (p.seg_type[seg]) {
+    case kQ_Q4_0: row_dot_int8<kQ_Q4_0, MB>(wrow, p, m0, lane, acc); break;
+    case kQ_Q4_1: row_dot_int8<kQ_Q4_1, MB>(wrow, p, m0, lane, acc); break;
+    case kQ_Q5_0: row_dot_int8<kQ_Q5_0, MB>(wrow, p, m0, lane, acc); break;
+    case kQ_Q5_1: row_dot_int8<kQ_Q5_1, MB>(wrow, p, m0, lane, acc); break;
+    case kQ_Q8_0: row_dot_int8<kQ_Q8_0, MB>(wrow, p, m0, lane, acc); break;
+    case kQ_Q4_K: row_dot_int8<kQ_Q4_K, MB>(wrow, p, m0, lane, acc); break;
+    case kQ_Q5_K: row_dot_int8<kQ_Q5_K, MB>(wrow, p, m0, lane, acc); break;
+    case kQ_Q6_K: row_dot_int8<kQ_Q6_K, MB>(wrow, p, m0, lane, acc); break;
+    default: break;
+  }
+#pragma unroll
+  for (int m = 0; m < MB; ++m) {
+    const float v = warp_sum(acc[m]);
+    if (lane == 0 && m0 + m < p.M) mmvq_store(p, n, m0 + m, v);
+  }
+}
+
 // Q8_0: 34-byte blocks (fp16 scale + 32 int8) are only 2-byte aligned: seventeen 16-bit loads.
 template <int MB>
 __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q8_0_kernel(const MmvqParams p) {
@@ -414,6 +631,15 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q8_0_kernel(const MmvqP
     else KERNEL<8><<<dim3(gx, (p.M + 7) / 8), kRowsPerCta * 32, 0, s>>>(p);                    \
   } while (0)
 
+// Alignment that expand_q8 of a type needs: 16 bytes for the K-quants read with uint4 loads, 4 for
+// Q4_1 / Q5_1, 2 for the rest; the int8 activations are read with 16-byte loads.
+bool int8_operands_ok(int type, const uint8_t* w, long long row_bytes, const MmvqParams& p) {
+  const uintptr_t need = (type == kQ_Q4_K || type == kQ_Q5_K) ? 16 : ((type == kQ_Q4_1 || type == kQ_Q5_1) ? 4 : 2);
+  const int qk = (type == kQ_Q4_K || type == kQ_Q5_K || type == kQ_Q6_K) ? 256 : 32;
+  return (reinterpret_cast<uintptr_t>(w) % need) == 0 && (row_bytes % static_cast<long long>(need)) == 0 &&
+         (p.K % qk) == 0 && (reinterpret_cast<uintptr_t>(p.xq) & 15) == 0 && p.xd != nullptr && p.xs != nullptr;
+}
+
 template <int T>
 void mmvq_dispatch(const MmvqParams& p, cudaStream_t s) {
   // vector-load fast paths need 16-byte aligned rows (weights and activations)
@@ -446,6 +672,16 @@ void mmvq_dispatch(const MmvqParams& p, cudaStream_t s) {
     if ((reinterpret_cast<uintptr_t>(p.w) & 1) == 0 && (p.row_bytes & 1) == 0 &&
         (reinterpret_cast<uintptr_t>(p.x) & 15) == 0 && (p.ldx & 7) == 0) {
       OXB_MMVQ_FAST(mmvq_q8_0_kernel);
+      return;
+    }
+  }
+  if constexpr (HasInt8Path<T>::value && T != kQ_Q4_K && T != kQ_Q8_0) {
+    if (p.xq != nullptr && int8_operands_ok(T, p.w, p.row_bytes, p)) {
+      const int gx = (p.N + kRowsPerCta - 1) / kRowsPerCta;
+      if (p.M == 1) mmvq_int8_kernel<T, 1><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);
+      else if (p.M == 2) mmvq_int8_kernel<T, 2><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);
+      else if (p.M <= 4) mmvq_int8_kernel<T, 4><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);
+      else mmvq_int8_kernel<T, 8><<<dim3(gx, (p.M + 7) / 8), kRowsPerCta * 32, 0, s>>>(p);
       return;
     }
   }
@@ -505,6 +741,29 @@ bool launch_mmvq(int qtype, const MmvqParams& p, cudaStream_t stream) {
 #define CALL(T) mmvq_dispatch<T>(p, stream)
   OXB_QDISPATCH(qtype, CALL)
 #undef CALL
+  return true;
+}
+
+bool mmvq_has_int8_path(int qtype) {
+  switch (qtype) {
+    case kQ_Q4_0: case kQ_Q4_1: case kQ_Q5_0: case kQ_Q5_1: case kQ_Q8_0: case kQ_Q4_K: case kQ_Q5_K: case kQ_Q6_K:
+      return true;
+    default:
+      return false;
+  }
+}
+
+bool launch_mmvq_mixed(const MmvqParams& p, cudaStream_t stream) {
+  if (p.M <= 0 || p.N <= 0) return true;
+  if (p.n_seg < 1 || p.n_seg > 4 || p.xq == nullptr) return false;
+  for (int i = 0; i < p.n_seg; ++i)
+    if (!mmvq_has_int8_path(p.seg_type[i]) || !int8_operands_ok(p.seg_type[i], p.seg_w[i], p.seg_row_bytes[i], p))
+      return false;
+  const int gx = (p.N + kRowsPerCta - 1) / kRowsPerCta;
+  if (p.M == 1) mmvq_mixed_kernel<1><<<dim3(gx, 1), kRowsPerCta * 32, 0, stream>>>(p);
+  else if (p.M == 2) mmvq_mixed_kernel<2><<<dim3(gx, 1), kRowsPerCta * 32, 0, stream>>>(p);
+  else if (p.M <= 4) mmvq_mixed_kernel<4><<<dim3(gx, 1), kRowsPerCta * 32, 0, stream>>>(p);
+  else mmvq_mixed_kernel<8><<<dim3(gx, (p.M + 7) / 8), kRowsPerCta * 32, 0, stream>>>(p);
   return true;
 }
 

@@ -21,6 +21,13 @@ struct MmvqParams {
   const int8_t* xq;   // [M, K], row stride K
   const float* xd;    // [M, K / 32] block scales
   const float* xs;    // [M, K / 32] block sums (scale * sum of the int8 values)
+  // Mixed-type stack (launch_mmvq_mixed): output rows [row_begin of segment i, row_end) come from
+  // segment i, whose rows are seg_row_bytes apart and packed as seg_type. n_seg == 0: `w` alone.
+  int n_seg;
+  const uint8_t* seg_w[4];
+  long long seg_row_bytes[4];
+  int seg_type[4];
+  int seg_row_end[4];
 };
 
 // x [M, K] bf16 -> int8 blocks of 32 with an fp32 scale (amax / 127) and the block sum.
@@ -29,6 +36,11 @@ void launch_quant_q8_1(const __nv_bfloat16* x, long long ldx, int8_t* xq, float*
 
 // Return false when the type has no device decoder.
 bool launch_mmvq(int qtype, const MmvqParams& p, cudaStream_t stream);
+// One launch over up to four stacked weight matrices of different block types that share K (the
+// Q | K | V or gate | up projections of a mixed-precision GGUF file). Needs the int8 activations
+// (xq / xd / xs). Returns false when a segment's type has no integer path or an operand is misaligned.
+bool launch_mmvq_mixed(const MmvqParams& p, cudaStream_t stream);
+bool mmvq_has_int8_path(int qtype);
 bool launch_dequant_rows(int qtype, const uint8_t* w, long long row_bytes, const int* row_ids,
                          int n_rows, int K, __nv_bfloat16* out, long long ldo, float scale,
                          int n_src_rows, cudaStream_t stream);

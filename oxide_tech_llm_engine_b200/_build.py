@@ -48,15 +48,17 @@ def _sources(name: str) -> list[Path]:
     raise KeyError(name)
 
 
-def _headers() -> list[Path]:
-    hs = list((_CSRC / "common").glob("*")) + list((_CSRC / "kernels").glob("*.cuh"))
-    hs += list((_CSRC / "host").glob("*.h"))
-    return sorted(hs)
+def _headers(name: str) -> list[Path]:
+    """Headers that the extension's sources include (a change in the other extension's headers must
+    not make this one stale)."""
+    if name == "oxb_host":
+        return sorted((_CSRC / "host").glob("*.h"))
+    return sorted(list((_CSRC / "common").glob("*")) + list((_CSRC / "kernels").glob("*.cuh")))
 
 
 def source_hash(name: str) -> str:
     h = hashlib.sha256()
-    for p in _sources(name) + _headers():
+    for p in _sources(name) + _headers(name):
         h.update(p.name.encode())
         h.update(p.read_bytes())
     return h.hexdigest()
@@ -101,7 +103,7 @@ def build(name: str, verbose: bool = False) -> Path:
     if not built.exists():
         raise RuntimeError(f"build of {name} produced no {built}")
     so = _so_path(name)
-    tmp = so.with_suffix(".so.tmp")
+    tmp = so.with_suffix(f".so.tmp{os.getpid()}")
     tmp.write_bytes(built.read_bytes())
     os.replace(tmp, so)
     _stamp_path(name).write_text(source_hash(name))
@@ -121,29 +123,56 @@ def _import_so(name: str):
     return mod
 
 
+class _BuildLock:
+    """Lock between the processes of one job (one rank per GPU imports the package at the same time):
+    only one of them rebuilds a stale extension, the others wait and then find it fresh."""
+
+    def __enter__(self):
+        import fcntl
+
+        _EXT.mkdir(exist_ok=True)
+        self.f = open(_EXT / ".build.lock", "w")
+        fcntl.flock(self.f, fcntl.LOCK_EX)
+        return self
+
+    def __exit__(self, *exc):
+        import fcntl
+
+        fcntl.flock(self.f, fcntl.LOCK_UN)
+        self.f.close()
+        return False
+
+
 def load(name: str):
     """Return the extension module, building it first if it is missing or stale."""
     with _lock:
         if name in _loaded:
             return _loaded[name]
         if not is_fresh(name):
-            import shutil
+            with _BuildLock():
+                return _load_locked(name)
+        return _load_locked(name)
 
-            have_compiler = shutil.which("g++") is not None and (
-                name != "oxb_cuda" or shutil.which("nvcc") is not None
+
+def _load_locked(name: str):
+    if not is_fresh(name):
+        import shutil
+
+        have_compiler = shutil.which("g++") is not None and (
+            name != "oxb_cuda" or shutil.which("nvcc") is not None
+        )
+        if have_compiler and os.environ.get("OXB_NO_BUILD", "0") != "1":
+            build(name)
+            if name in _loaded:
+                return _loaded[name]
+        elif not _so_path(name).exists():
+            raise ImportError(
+                f"native extension {name} is not built and no compiler is available; "
+                "run `python -c 'import __graft_entry__ as g; g.build()'` in the repo root"
             )
-            if have_compiler and os.environ.get("OXB_NO_BUILD", "0") != "1":
-                build(name)
-                if name in _loaded:
-                    return _loaded[name]
-            elif not _so_path(name).exists():
-                raise ImportError(
-                    f"native extension {name} is not built and no compiler is available; "
-                    "run `python -c 'import __graft_entry__ as g; g.build()'` in the repo root"
-                )
-        mod = _import_so(name)
-        _loaded[name] = mod
-        return mod
+    mod = _import_so(name)
+    _loaded[name] = mod
+    return mod
 
 
 def _noalloc_sources() -> list[Path]:

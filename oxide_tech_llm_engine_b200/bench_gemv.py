@@ -46,7 +46,8 @@ def main() -> None:
         return ts[len(ts) // 2]
 
     cases = [("Q4_K", 6144, 4096), ("Q4_K", 4096, 4096), ("Q4_K", 28672, 4096), ("Q4_K", 4096, 14336),
-             ("Q8_0", 128256, 4096), ("bf16", 6144, 4096), ("bf16", 28672, 4096), ("bf16", 4096, 14336)]
+             ("Q8_0", 128256, 4096), ("Q6_K", 4096, 14336), ("Q6_K", 128256, 4096), ("Q4_0", 4096, 4096),
+             ("mixed Q4_K|Q4_K|Q6_K", 6144, 4096), ("bf16", 6144, 4096), ("bf16", 28672, 4096), ("bf16", 4096, 14336)]
     for typ, N, K in cases:
         name = f"{typ} N={N} K={K}"
         if args.only and args.only not in name:
@@ -60,6 +61,21 @@ def main() -> None:
                 us = timed(lambda: ops.gemv(x, wt, y))
                 wbytes = w.numel() * 2
                 row = {"kernel": "gemv_bf16 (tile-major weights)"}
+            elif typ.startswith("mixed"):
+                # Q | K | V of an 8B model in a Q4_K_M file: one launch over three matrices of two types
+                lins = [random_quant_linear(t, n, K, dev, g) for t, n in (("Q4_K", 4096), ("Q4_K", 1024), ("Q6_K", 1024))]
+                parts = [(l.code, l.w, l.n) for l in lins]
+                xq = ops.quant_q8_1(x)
+                us = timed(lambda: ops.mmvq_mixed(parts, x, y, k=K, xq=xq))
+
+                def three():
+                    o = 0
+                    for l in lins:
+                        ops.mmvq(l.code, l.w, x, y[:, o:o + l.n], n=l.n, k=K, xq=xq)
+                        o += l.n
+                us_f = timed(three)
+                wbytes = sum(l.w.numel() for l in lins)
+                row = {"kernel": "mmvq_mixed (one launch)", "us_three_launches": round(us_f, 2)}
             else:
                 lin = random_quant_linear(typ, N, K, dev, g)
                 xq = ops.quant_q8_1(x)

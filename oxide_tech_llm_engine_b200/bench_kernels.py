@@ -127,7 +127,7 @@ def main() -> None:
             pps = args.pps
         else:
             per_sm = 12 if model.hkv >= 4 else 4   # the engine's rule (engine/engine.py, _fill)
-            want = -(-per_sm * 148 // max(1, B * model.hkv))
+            want = -(-per_sm * model._sms // max(1, B * model.hkv))
             splits = max(1, min(args.max_splits, want))
             pps = (max(4, -(-pages // splits)) + 3) // 4 * 4
         s_in = StepInputs(m=M, n_decode=B, n_prefill=0, n_tiles=0, n_logits=B,

@@ -154,14 +154,15 @@ def gpu_config(args) -> dict:
                           [rng.integers(0, mc.vocab_size, size=32768).tolist() for _ in range(n_long)],
                           [256] * n_long))
         ctx, seqs = 32768 + 256 + 16, 256
-    wm = {"bf16": "bf16", "fp8": "fp8", "q4k": "quant", "nvfp4": "nvfp4"}[args.weights]
+    wm = {"bf16": "bf16", "fp8": "fp8", "q4k": "quant", "q4km": "quant", "nvfp4": "nvfp4"}[args.weights]
     cfg = EngineConfig(model=model, tp=world, ctx_size=ctx, max_num_seqs=min(seqs, 256),
                        max_num_batched_tokens=args.max_batched_tokens, gpu_memory_utilization=0.92,
                        sla_budget=False, chunk_max=args.max_batched_tokens, enable_radix=(c == 5),
-                       weight_mode=wm, cuda_graph=True,
-                       graph_buckets=tuple(b for b in (8, 16, 32, 64, 128, 192, 256) if b <= min(seqs, 256)) or (8,))
+                       weight_mode=wm, cuda_graph=True, decode_burst=args.burst, burst_max_batch=8,
+                       graph_buckets=tuple(b for b in (1, 8, 16, 32, 64, 128, 192, 256) if b <= max(min(seqs, 256), 1)) or (8,))
     eng = LLMEngine(cfg, mc, rank=rank, world=world, device=dev, random_init=True,
-                    **({"random_quant_type": "Q4_K"} if args.weights == "q4k" else {}))
+                    **({"random_quant_type": {"q4k": "Q4_K", "q4km": "Q4_K_M"}[args.weights]}
+                       if args.weights in ("q4k", "q4km") else {}))
     results = []
     for label, prompts, outs in workloads:
         if world > 1:
@@ -200,7 +201,9 @@ def gpu_config(args) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", type=int, required=True, choices=[1, 2, 3, 4, 5])
-    ap.add_argument("--weights", default="bf16", choices=["bf16", "fp8", "q4k", "nvfp4"])
+    ap.add_argument("--burst", type=int, default=0,
+                    help="decode steps per host round trip for small greedy batches (in-graph step advance)")
+    ap.add_argument("--weights", default="bf16", choices=["bf16", "fp8", "q4k", "q4km", "nvfp4"])
     ap.add_argument("--scale", type=float, default=1.0, help="fraction of the request count (quick runs)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (marks the run as reduced)")
     ap.add_argument("--prompt-len", type=int, default=0)

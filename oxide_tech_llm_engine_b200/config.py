@@ -37,6 +37,9 @@ class EngineConfig:
     per_token_us: float = 25.0
     sla_budget: bool = True
     enable_radix: bool = True
+    kv_host_blocks: int = 0             # > 0: blocks the prefix cache evicts are kept in host memory (tier 2) and promoted back on a hit
+    kv_storage_blocks: int = 0          # ... and from there to files under kv_storage_dir (tier 3)
+    kv_storage_dir: Optional[str] = None
     cuda_graph: bool = True
     graph_buckets: tuple = (1, 2, 4, 8, 16, 32, 64, 128, 256)
     max_splits: int = 16
@@ -53,6 +56,8 @@ class EngineConfig:
     context_shift: bool = False         # at the context limit keep the prefix and drop the oldest tokens instead of ending
     shift_keep_tokens: int = 4
     shift_step_tokens: int = 256
+    decode_burst: int = 0               # > 1: greedy decode-only batches run this many steps per host round trip (in-graph step advance + pinned mailbox)
+    burst_max_batch: int = 8            # ... when at most this many sequences are decoding and nothing waits
     native_worker: bool = False         # run engine steps on the C++ StepWorker thread (core pin: worker_pin_core)
     worker_pin_core: int = -1
     seed: int = 42

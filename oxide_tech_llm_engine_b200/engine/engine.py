@@ -144,6 +144,8 @@ class LLMEngine:
                                  max_splits=cfg.max_splits, weight_mode=weight_mode,
                                  tile_weights=False if (cfg.comm == "nccl" or cfg.gemm == "library") else None,
                                  layer_range=pp.layers(mc.n_layers) if pp is not None else None)
+        if cfg.h2o_pruning:
+            self.model.enable_block_mass()
         if pp is not None:
             self.pp_recv = torch.zeros(self.max_tokens // world, mc.d_model, dtype=torch.bfloat16, device=self.device)
             self.pp_tokens = torch.zeros(max(cfg.max_num_seqs * (1 + cfg.draft_tokens), 64), dtype=torch.int32,
@@ -170,6 +172,7 @@ class LLMEngine:
         sc.context_shift, sc.shift_keep_tokens, sc.shift_step_tokens = (cfg.context_shift, cfg.shift_keep_tokens,
                                                                         cfg.shift_step_tokens)
         self.sched = H.Scheduler(sc)
+        self._init_kv_tiers()
         self.max_blocks_per_seq = max_blocks_per_seq
         S, M = cfg.max_num_seqs, self.max_tokens
         n_tiles_max = M // 64 + S + 1
@@ -196,6 +199,18 @@ class LLMEngine:
         self._next_id = 0
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
         self.graph_launches: dict[int, int] = {}
+        # decode bursts: K graph replays per host round trip (in-graph step advance, tokens come home
+        # through a ring in mapped pinned memory)
+        self._burst_k = cfg.decode_burst if (cfg.decode_burst > 1 and world == 1 and pp is None and cfg.cuda_graph
+                                             and cfg.comm != "nccl" and cfg.gemm != "library") else 0
+        self.burst_graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self._burst_steps = 0
+        if self._burst_k:
+            self._burst_ring = 2 * self._burst_k
+            self._burst_rows = self._bucket(max(1, cfg.burst_max_batch)) or cfg.burst_max_batch
+            self._mail, self._mail_dev = ops.alloc_mapped_host(self._burst_ring * self._burst_rows)
+            self._mail_np = self._mail.numpy()
+            self._burst_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.stats = {"steps": 0, "decode_tokens": 0, "prefill_tokens": 0, "graph_replays": 0,
                       "h2d_bytes": 0, "d2h_bytes": 0, "degraded": False}
         self.stop_ids_default = [mc.eos_id]
@@ -234,6 +249,7 @@ class LLMEngine:
         sc.context_shift, sc.shift_keep_tokens, sc.shift_step_tokens = (cfg.context_shift, cfg.shift_keep_tokens,
                                                                         cfg.shift_step_tokens)
         self.sched = H.Scheduler(sc)
+        self._init_kv_tiers()
         self.requests = {}
         self._next_id = 0
         self.graphs, self.graph_launches = {}, {}
@@ -300,6 +316,8 @@ class LLMEngine:
         rid = self._next_id if req_id is None else req_id
         self._next_id = max(self._next_id, rid) + 1
         stop = list(params.stop_token_ids) or list(self.stop_ids_default)
+        if getattr(self, "kv_tier", None) is not None:
+            self._promote_prefix(toks)
         self.sched.add_request(rid, toks, int(params.max_tokens), stop, bool(params.ignore_eos))
         st = RequestState(rid, params, int(toks.size), time.perf_counter(), on_token=on_token)
         if not params.is_greedy() and not params.device_ok():
@@ -339,7 +357,9 @@ class LLMEngine:
                 return b
         return None
 
-    def _fill(self, plan):
+    def _fill(self, plan, extra_len: int = 0):
+        """Writes the step descriptor and uploads it. `extra_len`: tokens the sequences will grow by
+        before the next upload (decode burst); the KV split covers them."""
         st = self.st
         n, nd, npf = plan.n_tokens, plan.n_decode, plan.n_prefill
         world = self.world
@@ -372,13 +392,13 @@ class LLMEngine:
             sl[nd:nd_pad] = 0
             bt = h("block_tables").reshape(-1, W)
             bt[:nd, :w] = plan.decode_block_tables.reshape(nd, w)
-            max_len = int(plan.decode_seq_lens.max())
+            max_len = int(plan.decode_seq_lens.max()) + extra_len
             pages = (max_len + 15) // 16
-            # enough CTAs to fill 148 SMs a few times over, at least one page per warp. With several KV
+            # enough CTAs to fill the SMs a few times over, at least one page per warp. With several KV
             # heads per rank (single GPU, low TP) shorter page chains balance ragged lengths better:
             # measured best near 12 CTAs per SM there, near 4 with one KV head per rank (TP = 8).
             per_sm = self._decode_ctas_per_sm or (12 if self.model.hkv >= 4 else 4)
-            want = -(-per_sm * 148 // max(1, nd * self.model.hkv))
+            want = -(-per_sm * getattr(self.model, "_sms", 148) // max(1, nd * self.model.hkv))
             splits = max(1, min(self.cfg.max_splits, want))
             pps = max(4, -(-pages // splits))
             pps = (pps + 3) // 4 * 4
@@ -462,43 +482,42 @@ class LLMEngine:
         return tok[:n_rows].cpu().numpy()
 
     # ------------------------------------------------------------------ heavy-hitter pruning
-    def _block_scores(self, row: int, blocks: list, kv_tokens: int) -> list:
-        """Attention mass per KV block of one decoding sequence: softmax of the last layer's query of
-        this step against the sequence's keys, summed over heads and the 16 tokens of each block
-        (all-reduced over the tensor-parallel ranks, which hold different heads)."""
-        nb = len(blocks)
-        if self.cpu:
-            return [0.0] * nb
-        m = self.model
-        bt = torch.as_tensor(blocks, dtype=torch.long, device=self.device)
-        k = m.k_cache[-1].index_select(0, bt).float()                      # [nb, hkv, 16, D]
-        q = m.q_buf[row].view(m.hkv, m.hq // m.hkv, m.D).float()
-        s = torch.einsum("hgd,bhtd->hgbt", q, k) * m.scale
-        valid = (torch.arange(nb * 16, device=self.device) < kv_tokens).view(nb, 16)
-        s = s.masked_fill(~valid[None, None], float("-inf"))
-        p = torch.softmax(s.flatten(2), dim=-1).view_as(s)
-        score = p.sum(dim=(0, 1, 3))
-        if self.world > 1:
-            import torch.distributed as dist
-
-            dist.all_reduce(score, group=self.group)
-        return score.cpu().tolist()
-
     def _h2o_prune(self, plan) -> None:
         """Sequences that outgrew `h2o_budget_blocks` give their least attended middle blocks back to
-        the pool (sink and rolling-window blocks always stay). Same decision on every rank: the scores
-        are all-reduced and the scheduler replicas prune identically."""
+        the pool (sink and rolling-window blocks always stay). The score of a block is the softmax
+        probability mass that this step's query of the last layer put on it, summed over heads: the
+        decode attention kernel records it (`DeviceModel.enable_block_mass`), so a step costs one
+        all-reduce over the tensor-parallel ranks (which hold different heads) and one device -> host
+        read, and only in steps where some sequence is over its budget. Same decision on every rank.
+        Reference: the per-block mass accumulated in the decode kernel
+        (oxide-backend-cuda/src/kernels/megakernel_ops.cu:577-617)."""
         cfg = self.cfg
+        over = []
         for row, rid in enumerate(plan.decode_ids):
             info = self.sched.request_info(int(rid))
-            if info is None or info["phase"] != 2 or len(info["blocks"]) <= cfg.h2o_budget_blocks:
-                continue
-            blocks = info["blocks"]
-            scores = self._block_scores(row, blocks, info["computed"] - info["dropped"])
-            keep = self.sched.prune_request(int(rid), scores, cfg.h2o_sink_blocks, cfg.h2o_rolling_blocks,
+            if info is not None and info["phase"] == 2 and len(info["blocks"]) > cfg.h2o_budget_blocks:
+                over.append((row, int(rid), info["blocks"]))
+        if not over:
+            return
+        if self.cpu or self.model.block_mass is None:
+            mass = None
+        else:
+            mass = self.model.block_mass[:len(plan.decode_ids)].clone()
+            if self.world > 1:
+                import torch.distributed as dist
+
+                dist.all_reduce(mass, group=self.group)
+            mass = mass.cpu().numpy()
+        for row, rid, blocks in over:
+            nb = len(blocks)
+            scores = [0.0] * nb
+            if mass is not None:
+                n = min(nb, mass.shape[1])
+                scores[:n] = mass[row, :n].tolist()
+            keep = self.sched.prune_request(rid, scores, cfg.h2o_sink_blocks, cfg.h2o_rolling_blocks,
                                             cfg.h2o_budget_blocks)
             if keep:
-                self.stats["h2o_pruned_blocks"] = self.stats.get("h2o_pruned_blocks", 0) + len(blocks) - len(keep)
+                self.stats["h2o_pruned_blocks"] = self.stats.get("h2o_pruned_blocks", 0) + nb - len(keep)
 
     def compare_with_baseline(self, n_steps: int = 2) -> dict:
         """Runs `n_steps` decode steps twice from the same state: through the fused path and through
@@ -560,7 +579,10 @@ class LLMEngine:
             except Exception as e:
                 self.fail_all(f"rank_failure: {e}")
                 raise
+        burst = self._burst_plan() if self._burst_k_now() else 0
         plan = self.sched.schedule()
+        if getattr(self, "kv_tier", None) is not None:
+            self._demote_evicted()
         # requests the scheduler had to end while planning (they can never fit the KV pool)
         early = list(self.sched.take_events())
         for e in early:
@@ -579,6 +601,12 @@ class LLMEngine:
                     f"and {self.sched.num_free_blocks()} free KV blocks")
             return early
         self._idle_plans = 0
+        if burst > 1 and plan.n_prefill == 0 and plan.n_decode == self.sched.num_running() and not early \
+                and plan.cow_src.size == 0:
+            events = early + self._run_burst(plan, burst)
+            if time.perf_counter() - t0 > self.cfg.step_deadline_s * burst:
+                self.stats["degraded"] = True
+            return events
         if self.cpu:
             tokens = self._step_cpu(plan)
         else:
@@ -602,6 +630,201 @@ class LLMEngine:
             self._attach_drafts()
         if time.perf_counter() - t0 > self.cfg.step_deadline_s:
             self.stats["degraded"] = True
+        return events
+
+    # ------------------------------------------------------------------ KV tiers
+    def _kv_caches(self):
+        m = self.model
+        return (m.pk, m.pv) if self.cpu else (m.k_cache, m.v_cache)
+
+    def _init_kv_tiers(self) -> None:
+        """Tier 2 / 3 behind the device block pool: blocks that the prefix cache evicts are copied to
+        host memory (and from there to files) keyed by the chained hash of the token prefix they
+        complete; a later prompt with that prefix gets them copied back into fresh device blocks
+        instead of being prefilled again. Reference: HierarchicalKvCache
+        (oxide-alloc/src/hierarchical_kv.rs:27-310: demotion T1->T2->T3 :135-173, promote on hit :207-242)."""
+        self.kv_tier = None
+        cfg = self.cfg
+        if cfg.kv_host_blocks > 0 and cfg.enable_radix and self.pp is None:
+            from .kv_tiers import HierarchicalKvCache
+
+            self.kv_tier = HierarchicalKvCache(cfg.kv_host_blocks, cfg.kv_storage_blocks, cfg.kv_storage_dir)
+            self.sched.record_evictions(True)
+
+    def _demote_evicted(self) -> None:
+        """Copies the blocks the prefix cache has just given up to the host tier. Runs right after the
+        scheduler planned a step and before the step's kernels are launched, so the copy is ordered
+        before anything that may overwrite a block that was handed out again."""
+        ev = self.sched.take_evicted()
+        if not ev:
+            return
+        from .kv_tiers import KvBlockPayload, prefix_hashes
+
+        ids = [b for _, _, blocks in ev for b in blocks]
+        kc, vc = self._kv_caches()
+        idx = torch.as_tensor(ids, dtype=torch.long, device=kc[0].device)
+        k = torch.stack([c.index_select(0, idx) for c in kc], dim=1)   # [n, layers, hkv, 16, D]
+        v = torch.stack([c.index_select(0, idx) for c in vc], dim=1)
+        if k.dtype == torch.bfloat16:                                   # carried as 16-bit patterns
+            k, v = k.view(torch.int16), v.view(torch.int16)
+        k, v = k.cpu().numpy(), v.cpu().numpy()
+        self.stats["d2h_bytes"] += k.nbytes + v.nbytes
+        i = 0
+        for toks, first, blocks in ev:
+            hashes = prefix_hashes(toks)
+            for j in range(len(blocks)):
+                b0 = (first + j) * self.block
+                self.kv_tier.demote(KvBlockPayload(hashes[first + j], np.asarray(toks[b0:b0 + self.block], dtype=np.int32),
+                                                   k[i], v[i]))
+                i += 1
+        self.stats["kv_demoted_blocks"] = self.stats.get("kv_demoted_blocks", 0) + len(ids)
+
+    def _promote_prefix(self, toks: np.ndarray) -> None:
+        """Before a request is queued: if the host tiers hold blocks of its prompt beyond what the
+        device prefix cache has, they go back into device blocks that the cache adopts, and the
+        scheduler's own prefix match then finds them."""
+        from .kv_tiers import prefix_hashes
+
+        n_full = (int(toks.size) - 1) // self.block          # the last token is always computed
+        if n_full <= 0:
+            return
+        have = int(self.sched.radix_cached_blocks(toks[:n_full * self.block]))
+        if have >= n_full:
+            return
+        hashes = prefix_hashes(toks[:n_full * self.block], self.block)
+        found = []
+        for i in range(have, n_full):
+            p = self.kv_tier.lookup(hashes[i])
+            if p is None or not np.array_equal(p.tokens, toks[i * self.block:(i + 1) * self.block]):
+                break
+            found.append(p)
+        if not found:
+            return
+        n_blocks = have + len(found)
+        ids = list(self.sched.radix_adopt(toks[:n_blocks * self.block], n_blocks))
+        if len(ids) != len(found):
+            return                                            # the pool is short: the prompt is prefilled as usual
+        kc, vc = self._kv_caches()
+        k = torch.from_numpy(np.stack([p.k for p in found], axis=1))   # [layers, n, hkv, 16, D]
+        v = torch.from_numpy(np.stack([p.v for p in found], axis=1))
+        if kc[0].dtype == torch.bfloat16:
+            k, v = k.view(torch.bfloat16), v.view(torch.bfloat16)
+        k, v = k.to(kc[0].device), v.to(kc[0].device)
+        idx = torch.as_tensor(ids, dtype=torch.long, device=kc[0].device)
+        for li in range(len(kc)):
+            kc[li].index_copy_(0, idx, k[li])
+            vc[li].index_copy_(0, idx, v[li])
+        self.stats["h2d_bytes"] += 2 * k.numel() * k.element_size()
+        self.stats["kv_promoted_blocks"] = self.stats.get("kv_promoted_blocks", 0) + len(ids)
+
+    # ------------------------------------------------------------------ decode bursts
+    def _burst_k_now(self) -> bool:
+        return bool(getattr(self, "_burst_k", 0)) and not self.cpu
+
+    def _burst_plan(self) -> int:
+        """How many decode steps the next plan may run back to back on the device: all running
+        requests decode greedily with nothing that needs the host between tokens (grammar, host-side
+        samplers, drafts, pruning), nothing waits for admission, and the KV blocks of all those steps
+        are held now so that one block table serves them all. 0 or 1: an ordinary step."""
+        n_run = self.sched.num_running()
+        if not 1 <= n_run <= self.cfg.burst_max_batch or self.sched.num_waiting() != 0:
+            return 0
+        if self._drafter is not None or self.cfg.h2o_pruning or len(self.requests) != n_run:
+            return 0
+        k = self._burst_k
+        for rid, r in self.requests.items():
+            if not r.params.is_greedy() or r.grammar is not None or r.host_sampler is not None:
+                return 0
+            info = self.sched.request_info(int(rid))
+            if info is None or info["phase"] != 2:
+                return 0
+        for rid in self.requests:
+            k = min(k, int(self.sched.reserve_ahead(int(rid), k)))
+            if k < 2:
+                return 0
+        return k
+
+    def _burst_body(self, s: StepInputs) -> None:
+        logits = self.model.forward(s)
+        rows = s.m
+        ops.argmax(logits[:rows], self.sampled[:rows], self.sampled_val[:rows])
+        ops.advance_decode_step(s, self.sampled, self._mail_dev, self._burst_counter, rows=rows,
+                                ring=self._burst_ring)
+
+    def _wait_mail(self, step: int, rows: int, nd: int) -> np.ndarray:
+        """Tokens of burst step `step` (device numbering) from the mapped-host ring; bounded wait."""
+        base = ((step - 1) % self._burst_ring) * rows
+        mail = self._mail_np
+        deadline = time.perf_counter() + max(2.0, self.cfg.step_deadline_s)
+        spins = 0
+        while True:
+            words = mail[base:base + nd]
+            if bool(np.all((words >> 32) == step)):
+                return (words & 0xFFFFFFFF).astype(np.int32)
+            spins += 1
+            if spins > 2000:
+                time.sleep(0)
+                if time.perf_counter() > deadline:
+                    torch.cuda.synchronize(self.device)
+                    self.check_device_status()
+                    raise EngineError(f"decode burst: step {step} did not post its tokens in time")
+
+    def _run_burst(self, plan, k: int) -> list:
+        """`k` decode steps with one descriptor upload: the graph of a burst step ends with the argmax
+        and the in-graph step advance, so the replays run back to back; the host consumes the tokens
+        from the mailbox as they land and keeps the scheduler in step (one `schedule()` /
+        `update()` pair per token, with the blocks already held). Requests that end inside the burst
+        leave the scheduler at once; their rows idle on the device until the burst is over, writing
+        only into blocks that nothing else can own before the next launch.
+        Reference: advance_decode_step_kernel + the pinned step counter the host spins on
+        (oxide-backend-cuda/src/kernels/megakernel_ops.cu:331-357, oxide-backend-cuda/src/lib.rs:4150-4247)."""
+        s, bucket = self._fill(plan, extra_len=k)
+        rows = s.m
+        g = self.burst_graphs.get(bucket)
+        done = 0
+        if g is None:
+            self._burst_body(s)      # eager warm-up: this is burst step 1
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            c0 = ops.launch_count
+            with torch.cuda.graph(g):
+                self._burst_body(s)
+            self.graph_launches[("burst", bucket)] = ops.launch_count - c0
+            self.burst_graphs[bucket] = g
+            done = 1
+        for _ in range(k - done):
+            g.replay()
+        ops.launch_count += self.graph_launches[("burst", bucket)] * (k - done)
+        self.stats["graph_replays"] += k - done
+        base = self._burst_steps
+        self._burst_steps += k
+        row_of = {int(r): i for i, r in enumerate(plan.decode_ids)}
+        nd0 = plan.n_decode
+        events, cur = [], plan
+        for i in range(k):
+            toks_all = self._wait_mail(base + i + 1, rows, nd0)
+            toks = np.asarray([toks_all[row_of[int(r)]] for r in cur.decode_ids], dtype=np.int32)
+            ev = list(self.sched.update(cur, toks))
+            self.stats["steps"] += 1
+            self.stats["decode_tokens"] += cur.n_decode
+            self.stats["burst_steps"] = self.stats.get("burst_steps", 0) + 1
+            self.stats["d2h_bytes"] += 8 * cur.n_decode
+            for e in ev:
+                self._deliver(e)
+            events += ev
+            if i == k - 1 or not self.sched.has_work():
+                break
+            cur = self.sched.schedule()
+            extra = list(self.sched.take_events())
+            for e in extra:
+                self._deliver(e)
+            events += extra
+            if cur.n_prefill or cur.n_decode == 0 or any(int(r) not in row_of for r in cur.decode_ids):
+                # cannot happen with nothing waiting; the plan is dropped by ending the burst here
+                raise EngineError("decode burst: the scheduler left the decode-only state")
+        self.status_host.copy_(ops.status_word(self.device), non_blocking=False)
+        if int(self.status_host[0]) != 0:
+            self._device_fault(int(self.status_host[0]))
         return events
 
     # ------------------------------------------------------------------ sampling
@@ -686,6 +909,11 @@ class LLMEngine:
         from ..errors import CollectiveTimeout
 
         ops.status_word(self.device).zero_()
+        if getattr(self, "_burst_k", 0):
+            torch.cuda.synchronize(self.device)
+            self._burst_counter.zero_()
+            self._burst_steps = 0
+            self._mail_np[:] = 0
         reason = "collective_timeout" if code == 4 else f"device_error_{code}"
         self.fail_all(reason)
         self.model.reset_sync_state()
@@ -787,5 +1015,7 @@ class LLMEngine:
 
     def close(self) -> None:
         self.graphs.clear()
+        if getattr(self, "burst_graphs", None):
+            self.burst_graphs.clear()
         if not self.cpu:
             self.model.close()

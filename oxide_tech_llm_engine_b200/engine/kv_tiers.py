@@ -47,7 +47,7 @@ class KvBlockPayload:
     """One KV block in transit between tiers or ranks."""
     prefix_hash: int
     tokens: np.ndarray          # [16] int32
-    k: np.ndarray               # [layers, hkv, 16, D] float16
+    k: np.ndarray               # [layers, hkv, 16, D]; float16, float32, or bf16 bit patterns as int16
     v: np.ndarray
     checksum: int = 0
 
@@ -64,9 +64,10 @@ class KvBlockPayload:
         return self.checksum == self.compute_checksum()
 
     def to_bytes(self) -> bytes:
-        hdr = json.dumps({"hash": self.prefix_hash, "checksum": self.checksum, "kshape": list(self.k.shape)}).encode()
+        hdr = json.dumps({"hash": self.prefix_hash, "checksum": self.checksum, "kshape": list(self.k.shape),
+                          "dtype": str(self.k.dtype)}).encode()
         return len(hdr).to_bytes(4, "little") + hdr + self.tokens.astype(np.int32).tobytes() + \
-            self.k.astype(np.float16).tobytes() + self.v.astype(np.float16).tobytes()
+            np.ascontiguousarray(self.k).tobytes() + np.ascontiguousarray(self.v).tobytes()
 
     @classmethod
     def from_bytes(cls, b: bytes) -> "KvBlockPayload":
@@ -77,8 +78,9 @@ class KvBlockPayload:
         off += 64
         shape = tuple(hdr["kshape"])
         cnt = int(np.prod(shape))
-        k = np.frombuffer(b, dtype=np.float16, count=cnt, offset=off).reshape(shape)
-        v = np.frombuffer(b, dtype=np.float16, count=cnt, offset=off + 2 * cnt).reshape(shape)
+        dt = np.dtype(hdr.get("dtype", "float16"))
+        k = np.frombuffer(b, dtype=dt, count=cnt, offset=off).reshape(shape)
+        v = np.frombuffer(b, dtype=dt, count=cnt, offset=off + dt.itemsize * cnt).reshape(shape)
         p = cls(hdr["hash"], toks.copy(), k.copy(), v.copy(), hdr["checksum"])
         if not p.verify():
             raise EngineError("KV block payload failed its checksum")

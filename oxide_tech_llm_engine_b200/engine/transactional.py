@@ -3,7 +3,7 @@
 `with KvTransaction(table, n_tokens) as tx:` reserves the blocks; leaving the block without
 `tx.commit()` (an exception, an early return) returns them to the pool and restores the committed
 length, like the reference's `TransactionalKvGuard` whose drop rolls back
-(oxide-memory/src/transactional.rs:118-128). `table` is the C++ `SequenceBlockTable`.
+(crates/oxide-alloc/src/transactional.rs:77-128). `table` is the C++ `SequenceBlockTable`.
 """
 from __future__ import annotations
 

@@ -87,21 +87,24 @@ class QuantLinear:
 
 
 _RANDOM_BLOCK_HEADERS = {
-    # type -> fp16 header values that make uniformly random payload bytes decode to roughly N(0, 0.02)
-    "Q8_0": (2.7e-4,), "Q4_0": (4.3e-3,), "Q4_K": (1.4e-4, 1.05e-3),
+    # type -> (byte offset in the block, fp16 values written there) that make uniformly random payload
+    # bytes decode to roughly N(0, 0.02). Q6_K keeps its super-block scale at the end of the block and
+    # multiplies it by a random int8 sub-block scale and a 6-bit code.
+    "Q8_0": (0, (2.7e-4,)), "Q4_0": (0, (4.3e-3,)), "Q4_K": (0, (1.4e-4, 1.05e-3)), "Q6_K": (208, (1.46e-5,)),
 }
 
 
 def random_quant_linear(type_name: str, n: int, k: int, device, gen: torch.Generator) -> QuantLinear:
     """A packed weight with random payload bytes generated on the device (benchmarks: no host copy,
-    no quantiser pass). Supported block types: Q8_0, Q4_0, Q4_K."""
+    no quantiser pass). Supported block types: Q8_0, Q4_0, Q4_K, Q6_K."""
     info = quants.TYPES[type_name]
     if type_name not in _RANDOM_BLOCK_HEADERS or k % info.block:
         raise ConfigError(f"random packed weights: unsupported type {type_name} or K % {info.block} != 0")
     n_blocks = n * k // info.block
     raw = torch.randint(0, 256, (n_blocks, info.nbytes), dtype=torch.uint8, device=device, generator=gen)
-    hdr = torch.tensor(_RANDOM_BLOCK_HEADERS[type_name], dtype=torch.float16).view(torch.uint8).to(device)
-    raw[:, :hdr.numel()] = hdr
+    off, vals = _RANDOM_BLOCK_HEADERS[type_name]
+    hdr = torch.tensor(vals, dtype=torch.float16).view(torch.uint8).to(device)
+    raw[:, off:off + hdr.numel()] = hdr
     lin = QuantLinear.__new__(QuantLinear)
     lin.code, lin.type_name, lin.n, lin.k, lin.packed = info.code, type_name, n, k, True
     lin.w = raw.view(-1)
@@ -164,6 +167,8 @@ class DeviceModel:
         self.weight_mode = weight_mode
         # dense bf16 projections are kept tile-major in HBM (see ops.tile_weight) unless a library
         # GEMM has to read them
+        # kernels of a step overlap their start-up with the tail of the kernel before them (OXB_PDL=0: off)
+        ops.set_pdl(os.environ.get("OXB_PDL", "1") != "0")
         self.gemv_small = os.environ.get("OXB_GEMV", "1") != "0"
         self.gemv_max_rows = int(os.environ.get("OXB_GEMV_MAX", "2"))
         self._sms = torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 148
@@ -228,6 +233,8 @@ class DeviceModel:
         self.logits = torch.zeros(self.max_logits, self.v_l, dtype=torch.float32, device=dev)
         self.part_o = torch.zeros(max_seqs * self.hq * max_splits * self.D, dtype=torch.float32, device=dev)
         self.part_ml = torch.zeros(max_seqs * self.hq * max_splits * 2, dtype=torch.float32, device=dev)
+        self.page_ml = self.block_mass = None   # heavy-hitter statistics, see enable_block_mass()
+        self._max_seqs, self._max_blocks_per_seq = max_seqs, max_blocks_per_seq
         n_local = self.layer_hi - self.layer_lo
         self.k_cache = [torch.zeros(num_blocks, self.hkv, 16, self.D, **bf) for _ in range(n_local)]
         self.v_cache = [torch.zeros(num_blocks, self.hkv, 16, self.D, **bf) for _ in range(n_local)]
@@ -297,14 +304,24 @@ class DeviceModel:
 
     @staticmethod
     def _fuse_quant_layer(L: dict) -> None:
+        """Q|K|V and gate|up as one launch each: one stacked matrix when the block types match, else a
+        mixed-type stack for the integer GEMV (a Q4_K_M file keeps attn_v in Q6_K)."""
+        def mixed(parts):
+            ok = all(q.packed and q.code in ops.INT8_MMVQ_CODES and q.k == parts[0].k for q in parts)
+            return [(q.code, q.w, q.n) for q in parts] if ok else None
+
         qkv = fuse_quant_rows([L["attn_q"], L["attn_k"], L["attn_v"]])
         if qkv is not None:
             L["attn_qkv"] = qkv
             del L["attn_q"], L["attn_k"], L["attn_v"]
+        else:
+            L["qkv_mix"] = mixed([L["attn_q"], L["attn_k"], L["attn_v"]])
         gu = fuse_quant_rows([L["ffn_gate"], L["ffn_up"]])
         if gu is not None:
             L["ffn_gate_up"] = gu
             del L["ffn_gate"], L["ffn_up"]
+        else:
+            L["gu_mix"] = mixed([L["ffn_gate"], L["ffn_up"]])
 
     def _tile_layer(self, L: dict) -> None:
         if self.weight_mode != "bf16" or not self.tile_weights:
@@ -319,8 +336,13 @@ class DeviceModel:
             torch.cuda.empty_cache()  # the row-major originals of the re-laid-out weights
 
     def init_random_quant(self, type_name: str = "Q4_K", seed: int = 0, embed_type: str = "Q8_0") -> None:
-        """Random packed GGUF-format weights generated on the device (weight_mode == 'quant')."""
+        """Random packed GGUF-format weights generated on the device (weight_mode == 'quant').
+        `type_name` "Q4_K_M" lays the types out like a stock file of that name: Q4_K everywhere except
+        attn_v, half of the ffn_down matrices and the output matrix, which are Q6_K."""
         cfg, dev = self.cfg, self.device
+        q4km = type_name == "Q4_K_M"
+        if q4km:
+            type_name = "Q4_K"
         g = torch.Generator(device=dev)
         g.manual_seed(seed * 1000 + 17)
         d = cfg.d_model
@@ -328,14 +350,15 @@ class DeviceModel:
         self.out_norm = ones(d)
         self.embed_q = random_quant_linear(embed_type, cfg.vocab_size, d, dev, g)
         self.embed = None
-        self.lm_head_q = random_quant_linear(embed_type, cfg.vocab_size, d, dev, g)
+        self.lm_head_q = random_quant_linear("Q6_K" if q4km else embed_type, cfg.vocab_size, d, dev, g)
         self.layers = []
-        for _ in range(cfg.n_layers):
+        for li in range(cfg.n_layers):
             L = {"attn_norm": ones(d), "ffn_norm": ones(d), "b_qkv": None, "q_norm": None, "k_norm": None}
             for key, n, k in (("attn_q", cfg.q_dim, d), ("attn_k", cfg.kv_dim, d), ("attn_v", cfg.kv_dim, d),
                               ("attn_output", d, cfg.q_dim), ("ffn_gate", cfg.ffn_dim, d), ("ffn_up", cfg.ffn_dim, d),
                               ("ffn_down", d, cfg.ffn_dim)):
-                L[key] = random_quant_linear(type_name, n, k, dev, g)
+                t = "Q6_K" if q4km and (key == "attn_v" or (key == "ffn_down" and li % 2 == 0)) else type_name
+                L[key] = random_quant_linear(t, n, k, dev, g)
             self._fuse_quant_layer(L)
             self.layers.append(L)
 
@@ -571,14 +594,19 @@ class DeviceModel:
             return None
         return ops.quant_q8_1(x, self._q8_bufs)
 
+    @staticmethod
+    def _mmvq_rows(lin: QuantLinear) -> int:
+        """Most rows that still take the packed GEMV: with a bf16 copy at hand the MMA path wins from 5
+        rows on (8B Q4_K, 8 rows: 5.4 vs 9.4 ms/step)."""
+        return 4 if getattr(lin, "dense", None) is not None else 8
+
     def _qlinear(self, lin: QuantLinear, x: torch.Tensor, out_f32: torch.Tensor, ld_out: Optional[int] = None,
                  xq=None):
         """out_f32[:, :n] = x @ W^T for a packed weight: MMVQ for small batches, else dequant + tcgen05."""
         m = x.shape[0]
-        # with a bf16 copy at hand the MMA path wins from 5 rows on (8B Q4_K, 8 rows: 5.4 vs 9.4 ms/step)
-        if lin.packed and m <= (4 if getattr(lin, "dense", None) is not None else 8):
+        if lin.packed and m <= self._mmvq_rows(lin):
             ops.mmvq(lin.code, lin.w, x, out_f32, n=lin.n, k=lin.k,
-                     xq=xq if lin.type_name in ("Q4_K", "Q8_0") else None)
+                     xq=xq if lin.code in ops.INT8_MMVQ_CODES else None)
             return
         w = lin.w
         if lin.packed and getattr(lin, "dense", None) is not None:
@@ -688,14 +716,26 @@ class DeviceModel:
             ops.softcap(self.logits[:n_log], cfg.logit_softcap)
         return self.logits[:n_log]
 
+    def enable_block_mass(self) -> None:
+        """From now on the decode attention of the last layer also writes `block_mass[seq, page]`, the
+        softmax probability mass that the step's queries (this rank's heads) put on every KV block: the
+        heavy-hitter score of H2O pruning. Call before the decode graphs are captured."""
+        if self.block_mass is None:
+            self.page_ml = torch.zeros(self._max_seqs, self._max_blocks_per_seq, self.hq, 2, dtype=torch.float32,
+                                       device=self.device)
+            self.block_mass = torch.zeros(self._max_seqs, self._max_blocks_per_seq, dtype=torch.float32,
+                                          device=self.device)
+
     def _attention(self, s: StepInputs, li: int) -> None:
         nd = s.n_decode
         win = self.cfg.sliding_window
         if nd > 0:
+            mass = self.block_mass is not None and li == len(self.k_cache) - 1
             ops.paged_decode(self.q_buf[:nd].view(nd, self.hq, self.D), self.k_cache[li], self.v_cache[li],
                              s.block_tables, s.seq_lens, s.pages_per_split, self.part_o, self.part_ml,
                              self.attn_out[:nd], batch=nd, max_splits=self.max_splits, window=win,
-                             scale=self.scale)
+                             scale=self.scale, page_ml=self.page_ml if mass else None,
+                             block_mass=self.block_mass if mass else None)
         if s.n_prefill > 0:
             ops.paged_prefill(self.q_buf.view(-1, self.hq, self.D), self.k_cache[li], self.v_cache[li],
                               s.prefill_block_tables, s.tile_seq, s.tile_q0, s.q_start, s.q_lens, s.ctx_lens,
@@ -747,6 +787,8 @@ class DeviceModel:
             xq = self._q8(g0)
             if "attn_qkv" in L:
                 self._qlinear(L["attn_qkv"], g0, self.qkv_acc[:M], xq=xq)
+            elif xq is not None and L.get("qkv_mix") is not None and M <= self._mmvq_rows(L["attn_q"]):
+                ops.mmvq_mixed(L["qkv_mix"], g0, self.qkv_acc[:M], k=d, xq=xq)
             else:
                 self._qlinear(L["attn_q"], g0, self.qkv_acc[:M, :qd], xq=xq)
                 self._qlinear(L["attn_k"], g0, self.qkv_acc[:M, qd:qd + kd], xq=xq)
@@ -762,6 +804,8 @@ class DeviceModel:
             xq = self._q8(g1)
             if "ffn_gate_up" in L:
                 self._qlinear(L["ffn_gate_up"], g1, self.gu_acc[:M], xq=xq)
+            elif xq is not None and L.get("gu_mix") is not None and M <= self._mmvq_rows(L["ffn_gate"]):
+                ops.mmvq_mixed(L["gu_mix"], g1, self.gu_acc[:M], k=d, xq=xq)
             else:
                 self._qlinear(L["ffn_gate"], g1, self.gu_acc[:M, :self.i_l], xq=xq)
                 self._qlinear(L["ffn_up"], g1, self.gu_acc[:M, self.i_l:], xq=xq)

@@ -71,6 +71,21 @@ def check_status(device=None) -> None:
 # Tests of the time-out path set a few thousand.
 SPIN_LIMIT = 0
 
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch of the step's kernels (GEMM, finalize_norm, QKV RoPE/append,
+    decode attention + merge): a kernel becomes resident while the one before it drains, runs its
+    prologue (and, in the GEMM, requests the first weight tiles of its operand ring) and then waits
+    for the earlier kernel to complete before it touches anything that kernel produced. Also holds
+    inside CUDA graphs captured afterwards."""
+    _ext().set_pdl(bool(on))
+
+
+def pdl_enabled() -> bool:
+    return bool(_ext().pdl_enabled())
+
+
 _sm_count: dict[int, int] = {}
 
 
@@ -406,10 +421,16 @@ def untile_weight(w: torch.Tensor) -> torch.Tensor:
 
 
 def paged_decode(q, k_cache, v_cache, block_tables, seq_lens, pages_per_split, part_o, part_ml, out,
-                 *, batch: int, max_splits: int, window: int = 0, scale: float) -> None:
+                 *, batch: int, max_splits: int, window: int = 0, scale: float,
+                 page_ml: Optional[torch.Tensor] = None, block_mass: Optional[torch.Tensor] = None) -> None:
+    """Paged split-KV decode attention + merge. With `page_ml` [B, max_blocks, Hq, 2] and `block_mass`
+    [B, max_blocks] (fp32) the kernels also produce the softmax probability mass per KV block, summed
+    over heads: the heavy-hitter score of H2O pruning (the reference accumulates it in its decode
+    kernel too, oxide-backend-cuda/src/kernels/megakernel_ops.cu:577-617)."""
     _ext().paged_decode(q, k_cache, v_cache, block_tables, seq_lens, pages_per_split, part_o, part_ml,
-                        out, batch, max_splits, window, scale, status_word(q.device) if CHECK_BOUNDS else None)
-    _bump(2)
+                        out, batch, max_splits, window, scale, status_word(q.device) if CHECK_BOUNDS else None,
+                        page_ml, block_mass)
+    _bump(3 if page_ml is not None else 2)
 
 
 # OXB_CHECKS=1: the attention kernels verify every block-table id against the pool size (a bad id is
@@ -498,11 +519,42 @@ def softcap(logits, cap: float) -> None:
     _bump()
 
 
+def alloc_mapped_host(n_words: int):
+    """Page-locked host memory mapped into the device's address space: (int64 host tensor, device
+    address). Kernels post results there and the host polls them without a stream synchronisation."""
+    return _ext().alloc_mapped_host(int(n_words))
+
+
+def advance_decode_step(s, sampled, mailbox_dev: int, step_counter, *, rows: int, ring: int) -> None:
+    """In-graph step advance (see csrc/kernels/fused_ops.cuh, AdvanceStepParams): rewrites the first
+    `rows` rows of the step descriptor `s` for the next decode step from the sampled ids and posts
+    the ids to the mapped-host ring at `mailbox_dev`."""
+    _ext().advance_decode_step(s.token_ids, s.positions, s.slot_mapping, s.seq_lens, s.block_tables, sampled,
+                               int(mailbox_dev), step_counter, rows, ring, status_word(sampled.device))
+    _bump()
+
+
 def mmvq(qtype: int, w, x, out, *, n: int, k: int, bias=None, add: bool = False, xq=None) -> None:
     """Small-batch quantised GEMV. `xq` = (int8 [M, K], scales [M, K/32], sums [M, K/32]) from
-    `quant_q8_1(x)`: Q4_K and Q8_0 weights then take the integer dot-product (dp4a) path."""
+    `quant_q8_1(x)`: the block types of `INT8_MMVQ_CODES` then take the integer dot-product (dp4a)
+    path, the others expand their weights to fp32."""
     q8, xd, xs = xq if xq is not None else (None, None, None)
     _ext().mmvq(qtype, w, x, bias, out, n, k, add, q8, xd, xs)
+    _bump()
+
+
+# GGUF type codes with an integer (dp4a) GEMV: Q4_0 Q4_1 Q5_0 Q5_1 Q8_0 Q4_K Q5_K Q6_K
+INT8_MMVQ_CODES = frozenset((2, 3, 6, 7, 8, 12, 13, 14))
+
+
+def mmvq_mixed(parts: Sequence, x, out, *, k: int, xq) -> None:
+    """One GEMV launch over stacked packed matrices of different block types that share K:
+    `parts` = [(type code, packed bytes, rows), ...] (at most four), out[:, :sum(rows)]. This is how
+    the Q|K|V and gate|up projections of a mixed-precision GGUF file (Q4_K_M keeps attn_v in Q6_K)
+    stay on one launch (reference: gemv_qkv_mixed_*, quant_gemv_kquants.cu:399-917)."""
+    q8, xd, xs = xq
+    _ext().mmvq_mixed([int(c) for c, _, _ in parts], [w for _, w, _ in parts], [int(n) for _, _, n in parts],
+                      x, out, k, q8, xd, xs)
     _bump()
 
 

@@ -370,3 +370,42 @@ def test_engine_handle_runs_steps_on_the_native_worker_thread():
         assert h.generate([5, 6, 7, 8], GREEDY)[0] == want[0]
     finally:
         h.shutdown()
+
+
+def test_kv_blocks_evicted_from_the_prefix_cache_come_back_from_the_host_tier(tmp_path):
+    """Tier 1 -> 2 -> 3 -> 1: prompts push an older prompt's blocks out of the device prefix cache,
+    the engine copies them to the host tier (and, beyond its capacity, to files); when the old
+    prompt returns its blocks are copied back into fresh device blocks, the prefill shrinks to the
+    uncached tail and the tokens are those of the first run."""
+    from oxide_tech_llm_engine_b200.config import EngineConfig
+    from oxide_tech_llm_engine_b200.engine.engine import LLMEngine
+    from oxide_tech_llm_engine_b200.models.config import preset
+    from oxide_tech_llm_engine_b200.models.weights import SyntheticSource
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    mc = preset("tiny")
+    rng = np.random.default_rng(8)
+    old = rng.integers(3, mc.vocab_size, size=100).tolist()                      # 6 full blocks + 4 tokens
+    others = [rng.integers(3, mc.vocab_size, size=120).tolist() for _ in range(4)]
+    sp = SamplingParams(greedy=True, max_tokens=4, ignore_eos=True)
+
+    def run(**kw):
+        eng = LLMEngine(EngineConfig(model="tiny", backend="cpu", max_num_seqs=1, num_kv_blocks=20, ctx_size=256,
+                                     enable_radix=True, **kw), mc, weights=SyntheticSource(mc, seed=4, std=0.08))
+        first = eng.generate([old], sp)[0]
+        for p in others:
+            eng.generate([p], sp)
+        before = eng.stats["prefill_tokens"]
+        again = eng.generate([old], sp)[0]
+        return eng, first, again, eng.stats["prefill_tokens"] - before
+
+    plain, first, again, cost_plain = run()
+    assert again == first and cost_plain == 100          # evicted and gone: the whole prompt is prefilled again
+    plain.close()
+    eng, first2, again2, cost = run(kv_host_blocks=4, kv_storage_blocks=64, kv_storage_dir=str(tmp_path))
+    assert first2 == first and again2 == first
+    assert eng.stats.get("kv_demoted_blocks", 0) >= 6 and eng.stats.get("kv_promoted_blocks", 0) == 6
+    assert cost == 100 - 6 * 16                           # only the uncached tail was computed
+    t = eng.kv_tier.stats
+    assert t["demoted_to_storage"] > 0 and t["storage_hits"] + t["host_hits"] >= 6
+    eng.close()

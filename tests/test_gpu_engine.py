@@ -298,3 +298,36 @@ def test_a_device_wait_that_ran_out_degrades_the_engine_and_returns_every_block(
     again = eng.generate([[5, 6, 7, 8, 9]], sp)[0]
     assert again == want
     eng.close()
+
+
+def test_decode_burst_matches_step_by_step_decoding():
+    """In-graph step advance + mapped-host mailbox: bursts of graph replays without a host round trip
+    produce exactly the tokens of one-step-at-a-time decoding, including a request that meets a stop
+    token in the middle of a burst, budgets that end inside a burst and blocks that fill up."""
+    from oxide_tech_llm_engine_b200.sampling_params import SamplingParams
+
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(3, 200, size=n).tolist() for n in (9, 30, 47)]
+    plain, mc, _ = _mk("tiny")
+    want = plain.generate(prompts, SamplingParams(greedy=True, max_tokens=45, ignore_eos=True))
+    # a stop token that the second request is known to emit mid-way
+    stop_tok = want[1][20]
+    first_hit = want[1].index(stop_tok)
+    want_stop = plain.generate([prompts[1]], SamplingParams(greedy=True, max_tokens=45, stop_token_ids=[stop_tok]))[0]
+    assert len(want_stop) == first_hit + 1
+    plain.close()
+
+    eng, _, _ = _mk("tiny", decode_burst=8, burst_max_batch=4, enable_radix=False)
+    free0 = eng.sched.num_free_blocks()
+    got = eng.generate(prompts, SamplingParams(greedy=True, max_tokens=45, ignore_eos=True))
+    assert got == want
+    assert eng.stats.get("burst_steps", 0) >= 30, eng.stats
+    got_stop = eng.generate([prompts[1]], SamplingParams(greedy=True, max_tokens=45, stop_token_ids=[stop_tok]))[0]
+    assert got_stop == want_stop
+    # every block is back in the pool afterwards (reservations of ended requests included)
+    assert eng.sched.num_running() == 0
+    eng.check_device_status()
+    assert eng.sched.num_free_blocks() == free0
+    single = eng.generate([prompts[0]], SamplingParams(greedy=True, max_tokens=7, ignore_eos=True))[0]
+    assert single == want[0][:7] and eng.sched.num_free_blocks() == free0
+    eng.close()

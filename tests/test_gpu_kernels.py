@@ -320,6 +320,51 @@ def test_paged_decode(ops, hq, hkv, d, seq_lens, pps, window):
         assert _rel_err(got, ref) < 2e-2, (i, s, _rel_err(got, ref))
 
 
+@pytest.mark.parametrize("hq,hkv,d,seq_lens,pps,window", [
+    (8, 1, 128, [1, 17, 300, 64, 1000], 4, 0),
+    (32, 8, 128, [5, 129, 48], 2, 0),
+    (14, 2, 64, [257, 16, 90], 8, 0),
+    (16, 1, 128, [200, 77], 4, 0),
+    (8, 2, 128, [500, 130, 40], 4, 64),
+])
+def test_paged_decode_block_mass(ops, hq, hkv, d, seq_lens, pps, window):
+    """The heavy-hitter statistic of the decode kernel: softmax probability per 16-token block, summed
+    over heads, against fp32 softmax of the same scores; the attention output itself is unchanged."""
+    torch.manual_seed(15)
+    B = len(seq_lens)
+    k_cache, v_cache, bt = _make_paged(seq_lens, hkv, d)
+    q = torch.randn(B, hq, d, device=DEV, dtype=torch.bfloat16) * 1.5
+    sl = torch.tensor(seq_lens, dtype=torch.int32, device=DEV)
+    W = bt.shape[1]
+    max_pages = max((s + 15) // 16 for s in seq_lens)
+    max_splits = (max_pages + pps - 1) // pps + 1
+    part_o = torch.empty(B, hq, max_splits, d, device=DEV, dtype=torch.float32)
+    part_ml = torch.empty(B, hq, max_splits, 2, device=DEV, dtype=torch.float32)
+    out = torch.empty(B, hq * d, device=DEV, dtype=torch.bfloat16)
+    out_plain = torch.empty_like(out)
+    page_ml = torch.full((B, W, hq, 2), float("nan"), device=DEV, dtype=torch.float32)
+    mass = torch.full((B, W), float("nan"), device=DEV, dtype=torch.float32)
+    pps_t = torch.tensor([pps], dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(d)
+    kw = dict(batch=B, max_splits=max_splits, window=window, scale=scale)
+    ops.paged_decode(q, k_cache, v_cache, bt, sl, pps_t, part_o, part_ml, out_plain, **kw)
+    ops.paged_decode(q, k_cache, v_cache, bt, sl, pps_t, part_o, part_ml, out, page_ml=page_ml, block_mass=mass, **kw)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out_plain)
+    assert torch.isfinite(mass).all()
+    for i, s in enumerate(seq_lens):
+        k = _gather_kv(k_cache, bt[i], s).float().repeat_interleave(hq // hkv, dim=1)   # [s, hq, d]
+        sc = torch.einsum("hd,khd->hk", q[i].float(), k) * scale
+        if window > 0 and s > window:
+            sc[:, :s - window] = float("-inf")
+        p = torch.softmax(sc, -1).sum(0)                                                 # [s]
+        ref = torch.zeros(W * 16, device=DEV)
+        ref[:s] = p
+        ref = ref.view(W, 16).sum(1)
+        assert abs(float(mass[i].sum()) - hq) < 2e-2 * hq, (i, float(mass[i].sum()))
+        assert float((mass[i] - ref).abs().max()) < 2e-2 * max(1.0, float(ref.max())), (i, s)
+
+
 @pytest.mark.parametrize("hq,hkv,d,chunks,window", [
     (8, 2, 128, [(70, 70), (5, 133), (64, 64), (1, 40)], 0),
     (4, 4, 64, [(100, 100), (33, 200)], 0),
@@ -610,7 +655,7 @@ def test_dequant_and_mmvq(ops, qname):
         torch.cuda.synchronize()
         yref = x.float() @ ref.T
         assert _rel_err(y, yref) < 2e-3, (qname, M, _rel_err(y, yref))
-    if qname in ("Q4_K", "Q8_0"):
+    if code in ops.INT8_MMVQ_CODES:
         # integer dot-product path: activations quantised to int8 blocks of 32 (Q8_1 style)
         for M in (1, 2, 3, 8):
             x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
@@ -632,6 +677,34 @@ def test_dequant_and_mmvq(ops, qname):
     y0 = yb.clone()
     ops.mmvq(code, w_dev, x, yb, n=N, k=K, bias=bias, add=True)
     assert _rel_err(yb, x.float() @ ref.T + bias.float() + y0.float()) < 2e-2
+
+
+def test_mmvq_mixed_types_in_one_launch(ops):
+    """Q | K | V of a mixed-precision file (Q4_K, Q4_K, Q6_K) and two more combinations as one GEMV
+    launch each, against the exact product of the int8 activations with the decoded weights."""
+    from oxide_tech_llm_engine_b200.formats import quants
+
+    rng = np.random.default_rng(21)
+    K = 1024
+    for names, rows in ((("Q4_K", "Q4_K", "Q6_K"), (40, 16, 16)), (("Q5_K", "Q8_0"), (24, 9)),
+                        (("Q4_0", "Q5_0", "Q4_1", "Q5_1"), (8, 8, 3, 5))):
+        parts, refs = [], []
+        for nm, n in zip(names, rows):
+            w = (rng.standard_normal((n, K)) * 0.05).astype(np.float32)
+            raw = quants.quantize_2d(nm, w)
+            refs.append(torch.from_numpy(quants.dequantize_2d(nm, raw, n, K)).to(DEV))
+            parts.append((quants.TYPES[nm].code, torch.from_numpy(raw).to(DEV).view(-1), n))
+        ref = torch.cat(refs, 0)
+        N = ref.shape[0]
+        for M in (1, 2, 4, 7):
+            x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+            xq = ops.quant_q8_1(x)
+            deq = (xq[0].float().view(M, K // 32, 32) * xq[1][..., None]).view(M, K)
+            y = torch.full((M, N + 3), float("nan"), device=DEV, dtype=torch.float32)
+            ops.mmvq_mixed(parts, x, y, k=K, xq=xq)
+            torch.cuda.synchronize()
+            assert _rel_err(y[:, :N], deq @ ref.T) < 2e-3, (names, M)
+            assert torch.isnan(y[:, N:]).all()
 
 
 # --------------------------------------------------------------------------------------- sampler

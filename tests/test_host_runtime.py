@@ -255,6 +255,31 @@ def test_scheduler_speculative_accept_and_rollback(H):
     assert len(info["blocks"]) == 1
 
 
+def test_scheduler_reserve_ahead_holds_blocks_for_a_decode_burst(H):
+    """reserve_ahead: the next decode plans allocate nothing, the first plan's table already lists the
+    held blocks, budgets and the pool bound the reservation, and everything returns at the end."""
+    sc = H.SchedulerConfig()
+    sc.num_blocks, sc.max_num_seqs, sc.max_blocks_per_seq, sc.enable_radix = 12, 4, 16, False
+    s = H.Scheduler(sc)
+    rid = 5
+    s.add_request(rid, np.arange(1, 21, dtype=np.int32), 40, [], True)   # 20 prompt tokens, 40 new
+    assert s.reserve_ahead(rid, 8) == 0                              # still in prefill
+    plan = s.schedule()
+    s.update(plan, np.array([7], dtype=np.int32))
+    free = s.num_free_blocks()
+    assert s.reserve_ahead(rid, 30) == 30                            # 21 + 30 tokens -> 4 blocks
+    assert free - s.num_free_blocks() == 2
+    plan = s.schedule()
+    assert plan.n_decode == 1 and plan.max_blocks == 4 and s.num_free_blocks() == free - 2
+    for t in range(29):
+        s.update(plan, np.array([9 + t], dtype=np.int32))
+        plan = s.schedule()
+        assert s.num_free_blocks() == free - 2                       # no allocation inside the burst
+    assert s.reserve_ahead(rid, 100) == 10                           # bounded by the 10 tokens left of the budget
+    ok, _ = s.cancel(rid)
+    assert ok and s.num_free_blocks() == 12
+
+
 def test_scheduler_fault_injection_isolated(H):
     c = H.SchedulerConfig()
     c.num_blocks = 32
