@@ -244,6 +244,67 @@ void gemm_bf16(const Tensor& a, const Tensor& w, int64_t epi, const c10::optiona
   check_launch("gemm_bf16");
 }
 
+// out[M, N] (+)= a[M, K] (bf16) x W^T with W kept as GGUF blocks: [N rows] of packed bytes of block type
+// `qtype`, unpacked tile by tile inside the GEMM (no bf16 copy of the weights, no scratch pass).
+// epi: store bf16 / store fp32 (splits == 1) or fp32 reduction into `out` (any splits; zero it first).
+void gemm_packed(const Tensor& a, const Tensor& qw, int64_t qtype, int64_t N, const Tensor& out, int64_t epi,
+                 int64_t mt, int64_t splits, const c10::optional<Tensor>& bias, const Tensor& status,
+                 int64_t spin_limit) {
+  TORCH_CHECK(a.is_cuda() && a.scalar_type() == torch::kBFloat16 && a.dim() == 2 && a.stride(1) == 1,
+              "gemm_packed: bf16 [M, K] activations");
+  TORCH_CHECK(qw.is_cuda() && qw.scalar_type() == torch::kUInt8 && qw.is_contiguous(), "gemm_packed: packed uint8 weights");
+  TORCH_CHECK(oxb::mmvq_has_int8_path(static_cast<int>(qtype)), "gemm_packed: no in-kernel expansion for GGUF type ", qtype);
+  const int64_t M = a.size(0), K = a.size(1);
+  TORCH_CHECK(K % 256 == 0, "gemm_packed: K must be a multiple of 256");
+  const long long row_bytes = oxb::quant_row_bytes(static_cast<int>(qtype), K);
+  TORCH_CHECK(row_bytes > 0 && qw.numel() >= row_bytes * N, "gemm_packed: weight buffer too small");
+  const bool k16 = qtype == 12 || qtype == 13;  // Q4_K / Q5_K rows are read with 16-byte loads
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(qw.data_ptr()) % 16 == 0 && (!k16 || row_bytes % 16 == 0),
+              "gemm_packed: weight alignment");
+  TORCH_CHECK(epi == oxb::kEpiStoreBf16 || epi == oxb::kEpiStoreF32 || epi == oxb::kEpiRedF32, "gemm_packed: epilogue");
+  TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.stride(1) == 1 && out.size(0) >= M && out.size(1) >= N,
+              "gemm_packed: out [M, N] row-major");
+  const int mt_i = mt == 2 ? 2 : 1;
+  const uint64_t a_row = static_cast<uint64_t>(a.stride(0)) * 2;
+  CUtensorMap tmA = oxb::make_tma_map(a.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, static_cast<uint64_t>(K),
+                                      static_cast<uint64_t>(M), 1, a_row, a_row * M, 64, 128, 1,
+                                      CU_TENSOR_MAP_SWIZZLE_128B);
+  oxb::GemmParams p{};
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(K);
+  p.kind = 2;
+  p.qw = qw.data_ptr<uint8_t>();
+  p.q_row_bytes = row_bytes;
+  p.q_type = static_cast<int>(qtype);
+  const int total_kb = static_cast<int>(K / 64);
+  int s = static_cast<int>(splits < 1 ? 1 : splits);
+  if (s > total_kb) s = total_kb;
+  p.kb_per_split = (total_kb + s - 1) / s;
+  s = (total_kb + p.kb_per_split - 1) / p.kb_per_split;
+  p.splits = s;
+  p.epi = static_cast<int>(epi);
+  p.spin_limit = static_cast<uint32_t>(spin_limit > 0 ? spin_limit : 0);
+  p.bias = bf16_ptr(bias);
+  p.m_tiles = static_cast<int>((M + 128 * mt_i - 1) / (128 * mt_i));
+  p.status = reinterpret_cast<int*>(status.data_ptr());
+  if (epi == oxb::kEpiRedF32) {
+    TORCH_CHECK(out.scalar_type() == torch::kFloat32, "gemm_packed: fp32 out for the reduction epilogue");
+    p.dst[0] = out.data_ptr<float>();
+    p.n_owners = 1;
+    p.rows_per_owner = static_cast<int>(M);
+    p.dst_ld = out.stride(0);
+  } else {
+    TORCH_CHECK(s == 1, "gemm_packed: split-K needs the fp32 reduction epilogue");
+    TORCH_CHECK(out.scalar_type() == (epi == oxb::kEpiStoreF32 ? torch::kFloat32 : torch::kBFloat16),
+                "gemm_packed: out dtype does not match the epilogue");
+    p.C = out.data_ptr();
+    p.ldc = out.stride(0);
+  }
+  oxb::launch_gemm_bf16(tmA, tmA, p, 128, mt_i, cur_stream());
+  check_launch("gemm_packed");
+}
+
 // a8: [M, K] e4m3 bytes; sa_t: [ceil(K/128), >= M] fp32; w8: [N, K] e4m3 bytes; sw: [ceil(N/128), ceil(K/128)].
 // x: [rows, K] or [G, cap, K] bf16 -> q [.., K/2] uint8, sf (scale atoms), gscale [rows] fp32
 void quant_act_nvfp4(const Tensor& x, const Tensor& q, const Tensor& sf, const Tensor& gscale,
@@ -943,6 +1004,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("softcap", &softcap);
   m.def("alloc_mapped_host", &alloc_mapped_host);
   m.def("advance_decode_step", &advance_decode_step);
+  m.def("gemm_packed", &gemm_packed);
   m.def("mmvq_mixed", &mmvq_mixed);
   m.def("mmvq_has_int8_path", [](int64_t t) { return oxb::mmvq_has_int8_path(static_cast<int>(t)); });
   m.def("mmvq", &mmvq);

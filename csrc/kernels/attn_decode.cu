@@ -91,7 +91,6 @@ paged_decode_kernel(const DecodeAttnParams p) {
   constexpr int VCH = D / 64;  // 16-byte V chunks per lane per token
   constexpr int MT = D / 16;   // m-tiles of O^T
 
-  pdl_launch_dependents();
   pdl_wait();  // q and the newest K/V rows come from the kernel before this one
   const int seq = blockIdx.x;
   const int kvh = blockIdx.y;
@@ -336,6 +335,7 @@ paged_decode_kernel(const DecodeAttnParams p) {
     if (++slot == kRing) slot = 0;
   }
   cp_async_wait<0>();
+  pdl_launch_dependents();  // the KV stream of this CTA is done: the next kernel may become resident
 
   // ---- merge the 4 warps through shared memory (the ring is free now) ----
   __syncthreads();

@@ -414,6 +414,8 @@ __global__ void __launch_bounds__(256) qkv_rope_append_kernel(const QkvRopeParam
 }
 
 __global__ void swiglu_kernel(const SwigluParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long total = static_cast<long long>(p.M) * p.I / 4;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -603,7 +605,7 @@ void launch_swiglu(const SwigluParams& p, cudaStream_t stream) {
   if (total <= 0) return;
   int blocks = static_cast<int>((total + 255) / 256);
   if (blocks > sm_count() * 16) blocks = sm_count() * 16;
-  swiglu_kernel<<<blocks, 256, 0, stream>>>(p);
+  launch_kernel(swiglu_kernel, dim3(blocks), dim3(256), 0, stream, /*pdl=*/true, false, p);
 }
 
 void launch_embed_gather(const int* tokens, const __nv_bfloat16* table, __nv_bfloat16* out, int M,

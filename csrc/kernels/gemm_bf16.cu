@@ -40,6 +40,7 @@
 // (oxide-engine/src/moe_gemm.rs:208-345); the reference's all-reduce
 // (oxide-backend-cuda/src/nccl.rs:18-29) is a no-op.
 #include "gemm_bf16.cuh"
+#include "quant_expand.cuh"
 
 #include "../common/device_info.h"
 #include "../common/sm100.cuh"
@@ -51,6 +52,7 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle atom row
 constexpr int kThreads = 192;
+constexpr int kDequantWarps = 4;  // KIND 2 only: warps 6..9
 constexpr int kStageCols = 64;                    // output columns staged per copy-out round
 constexpr int kStagePitch = kStageCols * 2 + 16;  // bytes; 16-byte skew keeps smem stores conflict-free
 constexpr int kStageBytes = 128 * kStagePitch;
@@ -159,14 +161,64 @@ __device__ __forceinline__ void smem_sum_cols(const uint8_t* src, int splits, ui
   }
 }
 
+// One 128-row x 64-value weight tile of block type T -> the bf16, 128-byte-swizzled operand stage at
+// `stage` (what a TMA box of bf16 weights would have written): four rows per lane, two groups of 32
+// weights per row; chunk c (16 bytes) of row r sits at chunk c ^ (r % 8) of that row. The type is a
+// template parameter so that the packed-block loads of all eight groups can be issued together.
+template <int T>
+__device__ __forceinline__ void unpack_kblock(const GemmParams& p, int n0, int kblock, uint8_t* stage, int lane) {
+  const int r7 = lane & 7;
+  uint32_t wq[4][2][8];
+  float dl0[4][2], dl1[4][2], ml[4][2];
+#pragma unroll
+  for (int rr = 0; rr < 4; ++rr) {
+    const int n = n0 + rr * 32 + lane;
+    const uint8_t* wrow = p.qw + static_cast<long long>(n < p.N ? n : p.N - 1) * p.q_row_bytes;
+    expand_q8_pair<T>(wrow, kblock, wq[rr], dl0[rr], dl1[rr], ml[rr]);
+  }
+#pragma unroll
+  for (int rr = 0; rr < 4; ++rr) {
+    const int r = rr * 32 + lane;
+    const bool in = n0 + r < p.N;  // rows past N are written as zeros
+    uint8_t* dst = stage + r * 128;
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float dl = in ? (c < 2 ? dl0[rr][g] : dl1[rr][g]) : 0.f;
+        const float m = in ? ml[rr][g] : 0.f;
+        // signed byte b of a word -> float: (b ^ 0x80) in the mantissa of 2^23, minus (2^23 + 128)
+        const uint32_t w0 = wq[rr][g][2 * c] ^ 0x80808080u, w1 = wq[rr][g][2 * c + 1] ^ 0x80808080u;
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          f[j] = __uint_as_float(__byte_perm(w0, 0x4B000000u, 0x7650 + j)) - 8388736.f;
+          f[4 + j] = __uint_as_float(__byte_perm(w1, 0x4B000000u, 0x7650 + j)) - 8388736.f;
+        }
+        uint4 o;
+        __nv_bfloat162 h;
+        h = __floats2bfloat162_rn(fmaf(dl, f[0], m), fmaf(dl, f[1], m));
+        o.x = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(fmaf(dl, f[2], m), fmaf(dl, f[3], m));
+        o.y = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(fmaf(dl, f[4], m), fmaf(dl, f[5], m));
+        o.z = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(fmaf(dl, f[6], m), fmaf(dl, f[7], m));
+        o.w = *reinterpret_cast<uint32_t*>(&h);
+        *reinterpret_cast<uint4*>(dst + (((g * 4 + c) ^ r7) << 4)) = o;
+      }
+    }
+  }
+}
+
 template <int BN, int STAGES, int MT, int KIND = 0>
 struct SmemLayout {
   static constexpr int kABytes = MT * BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kRingBytes = STAGES * (kABytes + kBBytes);
   // NVFP4: the scale atoms of one k block (4 x 512 bytes per 128 rows) ride along with each stage
-  static constexpr int kSFABytes = KIND ? MT * 2048 : 0;
-  static constexpr int kSFBBytes = KIND ? ((BN + 127) / 128) * 2048 : 0;
+  static constexpr int kSFABytes = KIND == 1 ? MT * 2048 : 0;
+  static constexpr int kSFBBytes = KIND == 1 ? ((BN + 127) / 128) * 2048 : 0;
   static constexpr int kSFOffset = kRingBytes;
   static constexpr int kStageOffset = kRingBytes + STAGES * (kSFABytes + kSFBBytes);
   static constexpr int kBarOffset = kStageOffset + kStageBytes;
@@ -178,13 +230,18 @@ struct WorkItem {
   bool valid;
 };
 
+// KIND: 0 = bf16 x bf16, 1 = NVFP4 x NVFP4 (block scales in TMEM), 2 = bf16 x GGUF-packed weights
+// (four more warps, kDequantWarps, rebuild the weight stage in shared memory).
 template <int BN, int STAGES, int MT, int KIND = 0>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(KIND == 2 ? kThreads + 32 * kDequantWarps : kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmParams p) {
   using L = SmemLayout<BN, STAGES, MT, KIND>;
-  static_assert(KIND == 0 || (MT == 1 && BN == 128), "fp4 tiles are 128 x 128");
-  constexpr int kXStep = KIND ? 128 : BK;  // TMA x coordinate of one k block (bytes for the packed fp4 maps)
+  static_assert(KIND != 1 || (MT == 1 && BN == 128), "fp4 tiles are 128 x 128");
+  static_assert(KIND != 2 || BN == 128, "packed weights are unpacked in 128-row tiles");
+  constexpr bool FP4 = KIND == 1;
+  constexpr bool PACKED = KIND == 2;
+  constexpr int kXStep = FP4 ? 128 : BK;  // TMA x coordinate of one k block (bytes for the packed fp4 maps)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem =
       reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -203,7 +260,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_kb = KIND ? p.kb_total : (p.K + BK - 1) / BK;
+  const int total_kb = FP4 ? p.kb_total : (p.K + BK - 1) / BK;
   const bool grouped = p.group_counts != nullptr;
   const int n_tiles = (p.N + BN - 1) / BN;
   const int m_tiles = p.m_tiles;
@@ -213,23 +270,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   constexpr uint32_t kAccCols = BN < 32 ? 32 : BN;   // TMEM columns of one 128-row accumulator
   constexpr uint32_t kItemCols = MT * kAccCols;      // ... of one work item
   constexpr uint32_t kBufs = 2 * kItemCols <= 512 ? 2 : 1;
-  constexpr uint32_t kSFCols = KIND ? 64 : 0;   // two sets of (16 columns of A scales, 16 of B scales)
+  constexpr uint32_t kSFCols = FP4 ? 64 : 0;   // two sets of (16 columns of A scales, 16 of B scales)
   constexpr uint32_t kSFCol0 = kBufs * kItemCols;
-  constexpr uint32_t kTmemCols = KIND ? 512 : kBufs * kItemCols;
+  constexpr uint32_t kTmemCols = FP4 ? 512 : kBufs * kItemCols;
   static_assert(kBufs * kItemCols + kSFCols <= 512, "TMEM budget");
   static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM allocation");
 
-  // Programmatic dependent launch: the next kernel of the stream may become resident as soon as
-  // every CTA of this grid has started; nothing below that depends on an earlier kernel runs before
-  // pdl_wait(). Both are no-ops for a launch without the attribute.
-  pdl_launch_dependents();
+  // Programmatic dependent launch: nothing below that depends on an earlier kernel runs before
+  // pdl_wait(); the next kernel of the stream may become resident once every CTA has issued its last
+  // MMA (pdl_launch_dependents in the MMA warp). Both are no-ops for a launch without the attribute.
   if (threadIdx.x == 0) {
     stamp(p, 0);
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full[s], 1);
+      mbar_init(&full[s], PACKED ? 2 : 1);  // the TMA producer (+ the warp that unpacks this stage's weights)
       mbar_init(&empty[s], 1);
     }
     mbar_init(&tmem_full[0], 1);
@@ -258,7 +314,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // warps wait for the prerequisite grid first, and TMEM is allocated only after that wait: a CTA
   // that held TMEM while it waited could starve a CTA of the prerequisite grid on the same SM.
   uint32_t tmem_base = 0;
-  if (warp >= 1) {
+  if (warp >= 1 && warp < 6) {
     pdl_wait();
     if (warp == 1) {
       tmem_alloc(tmem_slot, kTmemCols);
@@ -320,7 +376,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     auto issue_a = [&](const WorkItem& it, int kb, uint32_t iter_kb) __attribute__((always_inline)) {
       const int s = iter_kb % STAGES;
       const int op = lane - (s & 7) * 4;
-      if (KIND && op == 3)
+      if (FP4 && op == 3)
         bulk_load(sSF + s * (L::kSFABytes + L::kSFBBytes),
                   p.sfa + ((static_cast<long long>(it.group) * p.sfa_group_tiles + (it.m0 >> 7)) * total_kb +
                            it.kb0 + kb) * 2048,
@@ -357,17 +413,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (lane == 0) set_status_once(p.status, kStatusMbarTimeoutProducer);
           break;
         }
-        if (lane == 0) mbar_arrive_expect_tx(&full[s], L::kABytes + L::kBBytes + L::kSFABytes + L::kSFBBytes);
+        if (lane == 0)
+          mbar_arrive_expect_tx(&full[s], L::kABytes + (PACKED ? 0 : L::kBBytes) + L::kSFABytes + L::kSFBBytes);
         __syncwarp();
         const int op = lane - (s & 7) * 4;  // which copy of this stage this lane issues (0..3), if any
         // weights (and their scales) first: they depend on nothing that runs before this kernel
-        if (KIND && op == 1)
+        if (FP4 && op == 1)
           // the scale atoms of this k block: 2 KB per 128 rows, contiguous in [row tile][k block]
           bulk_load(sSF + s * (L::kSFABytes + L::kSFBBytes) + L::kSFABytes,
                     p.sfb + ((static_cast<long long>(it.group) * ((p.N + 127) / 128) + (it.n0 >> 7)) * total_kb +
                              it.kb0 + kb) * 2048,
                     L::kSFBBytes, &full[s]);
-        if (p.b_tiled && p.wide_boxes && BN == 256) {
+        if (PACKED) {
+          // the weight stage is written by the unpacking warps
+        } else if (p.b_tiled && p.wide_boxes && BN == 256) {
           // both 128-row weight tiles of this k block in one 32 KB copy: [64][128][k block][n tile]
           if (op == 0) tma_load_4d(sB + s * L::kBBytes, &tmB, &full[s], 0, 0, it.kb0 + kb, it.n0 >> 7);
         } else if (p.b_tiled) {
@@ -437,7 +496,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(sA + s * L::kABytes);
           const uint32_t b_addr = smem_u32(sB + s * L::kBBytes);
-          if (KIND) {
+          if (FP4) {
             // scales of this k block -> TMEM (alternating column sets), then 4 MMAs of 64 values of K
             constexpr uint32_t idesc4 = make_idesc_nvfp4(BM, BN);
             const uint32_t sfa_t = tmem_base + kSFCol0 + (iter & 1) * 32;
@@ -467,6 +526,50 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         if (ok) tc_commit(&tmem_full[buf]);
         ++t;
+      }
+      pdl_launch_dependents();  // only epilogues are left in this CTA
+    }
+  } else if (PACKED && warp >= 6) {
+    // ------------------------------ weight unpacking (KIND 2) -----------------
+    // Warp dq takes the k blocks dq, dq + 4, ... of the CTA's sequence and unpacks the whole 128-row
+    // tile of each (four rows per lane), so four stages are being filled at once and every lane has
+    // the loads of four rows in flight: the unpacking is bound by the latency of the packed-block
+    // loads, not by arithmetic. A k block is two groups of 32 weights per row: each is expanded to
+    // int8 codes + scales (quant_expand.cuh), converted to bf16 and stored as four 16-byte chunks at
+    // the position the 128-byte swizzle of the operand descriptors expects: chunk c of row r sits at
+    // chunk c ^ (r % 8) of that row.
+    if constexpr (PACKED) {
+      const int dq = warp - 6;
+      uint32_t iter = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        const WorkItem it = decode(w);
+        if (!it.valid) continue;
+        for (int kb = 0; kb < it.nkb && ok; ++kb, ++iter) {
+          if ((iter & (kDequantWarps - 1)) != static_cast<uint32_t>(dq)) continue;
+          const int s = iter % STAGES;
+          const uint32_t ph = (iter / STAGES) & 1;
+          if (iter >= STAGES && !mbar_wait(&empty[s], ph ^ 1, spin)) ok = false;
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) {
+            if (lane == 0) set_status_once(p.status, kStatusMbarTimeoutProducer);
+            break;
+          }
+          switch (p.q_type) {
+            case kQ_Q4_0: unpack_kblock<kQ_Q4_0>(p, it.n0, it.kb0 + kb, sB + s * L::kBBytes, lane); break;
+            case kQ_Q4_1: unpack_kblock<kQ_Q4_1>(p, it.n0, it.kb0 + kb, sB + s * L::kBBytes, lane); break;
+            case kQ_Q5_0: unpack_kblock<kQ_Q5_0>(p, it.n0, it.kb0 + kb, sB + s * L::kBBytes, lane); break;
+            case kQ_Q5_1: unpack_kblock<kQ_Q5_1>(p, it.n0, it.kb0 + kb, sB + s * L::kBBytes, lane); break;
+            case kQ_Q8_0: unpack_kblock<kQ_Q8_0>(p, it.n0, it.kb0 + kb, sB + s * L::kBBytes, lane); break;
+            case kQ_Q4_K: unpack_kblock<kQ_Q4_K>(p, it.n0, it.kb0 + kb, sB + s * L::kBBytes, lane); break;
+            case kQ_Q5_K: unpack_kblock<kQ_Q5_K>(p, it.n0, it.kb0 + kb, sB + s * L::kBBytes, lane); break;
+            default: unpack_kblock<kQ_Q6_K>(p, it.n0, it.kb0 + kb, sB + s * L::kBBytes, lane); break;
+          }
+          // generic-proxy stores -> visible to the tensor core's reads (async proxy), then this warp's arrival
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full[s]);
+        }
       }
     }
   } else {
@@ -580,7 +683,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       auto load_acc = [&](int h, int col, float (&a)[64]) __attribute__((always_inline)) {
         if (!fix) {
           tmem_load_cols<2>(lane_addr + h * kAccCols + col, a);
-          if (KIND) {
+          if (FP4) {
 #pragma unroll
             for (int j = 0; j < 64; ++j) a[j] *= acc_scale;
           }
@@ -627,7 +730,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         const int row = it.m0 + h * BM + q * 32 + lane;
         const bool row_ok = row < it.rows;
-        if (KIND) {
+        if (FP4) {
           acc_scale = p.w_gscale != nullptr ? p.w_gscale[group] : 1.f;
           if (p.a_gscale != nullptr && row_ok) acc_scale *= p.a_gscale[static_cast<long long>(group) * p.a_gs_stride + row];
         }
@@ -836,7 +939,8 @@ void launch_impl(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParam
   const int grid = n_work < sms ? n_work : sms;
   // the splits of a tile wait for each other: ask for a launch that is resident as a whole
   const bool cooperative = p.ws != nullptr && p.splits > 1;
-  launch_kernel(kern, dim3(grid), dim3(kThreads), L::kTotal, stream, /*pdl=*/true, cooperative, tmA, tmB, p);
+  launch_kernel(kern, dim3(grid), dim3(KIND == 2 ? kThreads + 32 * kDequantWarps : kThreads), L::kTotal, stream,
+                /*pdl=*/true, cooperative, tmA, tmB, p);
 }
 
 int tiles_of(int M, int N, int bn, int mt) {
@@ -863,6 +967,13 @@ void launch_gemm_bf16(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm
                       int mt, cudaStream_t stream) {
   if (p.kind == 1) {
     launch_impl<128, 5, 1, 1>(tmA, tmB, p, stream);
+    return;
+  }
+  if (p.kind == 2) {  // GGUF-packed weights, 128-column tiles
+    if (mt == 2)
+      launch_impl<128, 4, 2, 2>(tmA, tmB, p, stream);
+    else
+      launch_impl<128, 6, 1, 2>(tmA, tmB, p, stream);
     return;
   }
   if (mt == 2) {

@@ -74,7 +74,7 @@ struct GemmParams {
   // (row-major, K / 2 bytes per row), one ue4m3 scale per 16 values of K in 512-byte atoms
   // [row tile of 128][K / 64][(row % 32) * 16 + (row / 32 % 4) * 4 + (k / 16 % 4)], and the
   // accumulator of row r is multiplied by a_gscale[g * a_gs_stride + r] * w_gscale[g] ---
-  int kind;                   // 0 = bf16 operands, 1 = NVFP4
+  int kind;                   // 0 = bf16 operands, 1 = NVFP4, 2 = bf16 A x GGUF-packed B unpacked in the kernel
   int kb_total;               // k blocks of 128 operand bytes (kind 1: K / 256; kind 0: ceil(K / 64))
   const uint8_t* sfa;         // scales of A
   const uint8_t* sfb;         // scales of B
@@ -82,6 +82,13 @@ struct GemmParams {
   const float* a_gscale;      // per-row second-level scale of A (nullable: 1)
   long long a_gs_stride;
   const float* w_gscale;      // per-group second-level scale of B (nullable: 1)
+  // --- GGUF-packed weights (kind = 2): B is [N rows] of packed blocks, q_row_bytes apart, of block
+  // type q_type (one with an integer expansion: Q4_0 Q4_1 Q5_0 Q5_1 Q8_0 Q4_K Q5_K Q6_K). Four extra
+  // warps (one k block each, round robin) unpack the 128 x 64 weight tiles into the bf16, 128-byte-swizzled
+  // operand stage that TMA would have filled; K must be a multiple of 256, 128-column tiles, not grouped. ---
+  const uint8_t* qw;
+  long long q_row_bytes;
+  int q_type;
   // Optional timeline of every CTA (bench_gemm --trace): 8 x uint64 nanosecond stamps per CTA
   // [entry, first accumulator ready, partial stored, splits met, epilogue done, exit, 0, 0].
   unsigned long long* trace;

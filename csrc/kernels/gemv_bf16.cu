@@ -9,6 +9,7 @@
 // launch_wrappers.cu:202-247 dispatches cuBLAS for them).
 #include "gemv_bf16.cuh"
 
+#include "../common/device_info.h"
 #include "../common/sm100.cuh"
 
 namespace oxb {
@@ -24,6 +25,7 @@ __device__ __forceinline__ float gemv_act(float x, int act) {
 
 template <int MB>
 __global__ void __launch_bounds__(kWarpsPerCta * 32) gemv_bf16_kernel(const GemvParams p) {
+  pdl_wait();  // the activation rows come from the kernel before this one
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pair = blockIdx.x * kWarpsPerCta + warp;  // index of this warp's row pair
   const int n_pairs = p.N >> 1;
@@ -75,6 +77,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) gemv_bf16_kernel(const Gemv
       }
     }
   }
+  pdl_launch_dependents();  // the weight stream is done: the next kernel may become resident
 #pragma unroll
   for (int m = 0; m < MB; ++m) {
     float v0 = warp_sum(acc[0][m]), v1 = warp_sum(acc[1][m]);
@@ -107,10 +110,10 @@ void launch_gemv_bf16(const GemvParams& p, cudaStream_t stream) {
   if (p.M <= 0 || p.N <= 0) return;
   const int n_pairs = p.N >> 1;
   const int grid = (n_pairs + kWarpsPerCta - 1) / kWarpsPerCta;
-  if (p.M == 1) gemv_bf16_kernel<1><<<grid, kWarpsPerCta * 32, 0, stream>>>(p);
-  else if (p.M == 2) gemv_bf16_kernel<2><<<grid, kWarpsPerCta * 32, 0, stream>>>(p);
-  else if (p.M <= 4) gemv_bf16_kernel<4><<<grid, kWarpsPerCta * 32, 0, stream>>>(p);
-  else gemv_bf16_kernel<8><<<grid, kWarpsPerCta * 32, 0, stream>>>(p);
+  if (p.M == 1) launch_kernel(gemv_bf16_kernel<1>, dim3(grid), dim3(kWarpsPerCta * 32), 0, stream, /*pdl=*/true, false, p);
+  else if (p.M == 2) launch_kernel(gemv_bf16_kernel<2>, dim3(grid), dim3(kWarpsPerCta * 32), 0, stream, /*pdl=*/true, false, p);
+  else if (p.M <= 4) launch_kernel(gemv_bf16_kernel<4>, dim3(grid), dim3(kWarpsPerCta * 32), 0, stream, /*pdl=*/true, false, p);
+  else launch_kernel(gemv_bf16_kernel<8>, dim3(grid), dim3(kWarpsPerCta * 32), 0, stream, /*pdl=*/true, false, p);
 }
 
 }  // namespace oxb

@@ -10,8 +10,10 @@
 // dequantize_*_to_f16 (cublas_ops.cu:18-217), dequantize_token_embd_* (megakernel_ops.cu:2-116).
 #include "quant_ops.cuh"
 
+#include "../common/device_info.h"
 #include "../common/sm100.cuh"
 #include "quant_blocks.cuh"
+#include "quant_expand.cuh"
 
 namespace oxb {
 
@@ -21,6 +23,7 @@ constexpr int kRowsPerCta = 8;  // one warp per weight row
 
 template <int T, int MB>
 __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_kernel(const MmvqParams p) {
+  pdl_wait();  // the activation rows come from the kernel before this one
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * kRowsPerCta + warp;
   if (n >= p.N) return;
@@ -55,6 +58,7 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_kernel(const MmvqParams
       }
     }
   }
+  pdl_launch_dependents();  // the weight stream is done: the next kernel may become resident
 #pragma unroll
   for (int m = 0; m < MB; ++m) {
     const float v = warp_sum(acc[m]);
@@ -115,11 +119,6 @@ __device__ __forceinline__ void mmvq_store(const MmvqParams& p, int n, int m, fl
   }
 }
 
-__device__ __forceinline__ uint32_t byte_of3(uint32_t s0, uint32_t s1, uint32_t s2, int k) {
-  const uint32_t w = k < 4 ? s0 : (k < 8 ? s1 : s2);
-  return (w >> (8 * (k & 3))) & 0xFFu;
-}
-
 __device__ __forceinline__ float nib_to_float(uint32_t bytes, uint32_t sel) {
   // byte `sel & 3` of `bytes` (a value 0..15) placed in the mantissa of 2^23, minus 2^23: exact, and
   // two full-rate instructions instead of a quarter-rate integer-to-float conversion
@@ -133,6 +132,7 @@ __device__ __forceinline__ float nib_to_float(uint32_t bytes, uint32_t sel) {
 // mapping costs one L1 wavefront per lane and made this kernel L1-bound at 1.5 T weights/s).
 template <int MB>
 __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q4k_kernel(const MmvqParams p) {
+  pdl_wait();  // the activation rows come from the kernel before this one
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * kRowsPerCta + warp;
   if (n >= p.N) return;
@@ -189,6 +189,7 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q4k_kernel(const MmvqPa
       acc[m] += dl0 * ql - ml0 * sl + dl1 * qh - ml1 * sh;
     }
   }
+  pdl_launch_dependents();  // the weight stream is done: the next kernel may become resident
 #pragma unroll
   for (int m = 0; m < MB; ++m) {
     const float v = warp_sum(acc[m]);
@@ -205,6 +206,8 @@ __device__ __forceinline__ float int_to_float(int v) {  // |v| < 2^22, two full-
 
 __global__ void quant_q8_1_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int8_t* __restrict__ xq,
                                   float* __restrict__ xd, float* __restrict__ xs, int M, int K) {
+  pdl_launch_dependents();
+  pdl_wait();  // the activation rows come from the kernel before this one
   const int n_blk = K >> 5;
   const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -230,6 +233,7 @@ __global__ void quant_q8_1_kernel(const __nv_bfloat16* __restrict__ x, long long
 // activation loads are shared).
 template <int MB, int R>
 __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q4k_dp4a_kernel(const MmvqParams p) {
+  pdl_wait();  // the activation rows come from the kernel before this one
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_base = (blockIdx.x * kRowsPerCta + warp) * R;
   if (n_base >= p.N) return;
@@ -304,6 +308,7 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q4k_dp4a_kernel(const M
       }
     }
   }
+  pdl_launch_dependents();  // the weight stream is done: the next kernel may become resident
 #pragma unroll
   for (int t = 0; t < R; ++t)
 #pragma unroll
@@ -316,6 +321,7 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q4k_dp4a_kernel(const M
 // Q8_0 x int8: a lane takes one 34-byte block (2-byte aligned: 16-bit loads, repacked into words).
 template <int MB>
 __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q8_0_dp4a_kernel(const MmvqParams p) {
+  pdl_wait();  // the activation rows come from the kernel before this one
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * kRowsPerCta + warp;
   if (n >= p.N) return;
@@ -350,6 +356,7 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q8_0_dp4a_kernel(const 
       acc[m] += d * __ldg(p.xd + static_cast<long long>(m0 + m) * groups + grp) * int_to_float(s);
     }
   }
+  pdl_launch_dependents();  // the weight stream is done: the next kernel may become resident
 #pragma unroll
   for (int m = 0; m < MB; ++m) {
     const float v = warp_sum(acc[m]);
@@ -363,134 +370,6 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q8_0_dp4a_kernel(const 
 // so a group's share of the dot product is  xd * (dl0 * sum_lo(q x) + dl1 * sum_hi(q x)) + ml * xs
 // with eight `dp4a` per activation row. Blocks are read with the widest loads their alignment allows
 // (Q4_0 / Q5_0 / Q8_0 / Q6_K blocks are only 2-byte aligned).
-__device__ __forceinline__ uint32_t ldg_u16(const uint8_t* p) {
-  return __ldg(reinterpret_cast<const uint16_t*>(p));
-}
-__device__ __forceinline__ uint32_t ldg_u32_a2(const uint8_t* p) { return ldg_u16(p) | (ldg_u16(p + 2) << 16); }
-__device__ __forceinline__ uint32_t ldg_u32(const uint8_t* p) { return __ldg(reinterpret_cast<const uint32_t*>(p)); }
-__device__ __forceinline__ float half_bits(uint32_t v) {
-  return __half2float(__ushort_as_half(static_cast<uint16_t>(v & 0xFFFFu)));
-}
-// bits 0..3 of x -> bit 4 of bytes 0..3
-__device__ __forceinline__ uint32_t spread_bit4(uint32_t x) {
-  return (((x & 0xFu) * 0x00204081u) & 0x01010101u) << 4;
-}
-
-template <int T>
-struct HasInt8Path {
-  static constexpr bool value = T == kQ_Q4_0 || T == kQ_Q4_1 || T == kQ_Q5_0 || T == kQ_Q5_1 || T == kQ_Q8_0 ||
-                                T == kQ_Q4_K || T == kQ_Q5_K || T == kQ_Q6_K;
-};
-
-template <int T>
-__device__ __forceinline__ void expand_q8(const uint8_t* row, int grp, uint32_t (&wq)[8], float& dl0, float& dl1,
-                                          float& ml) {
-  if constexpr (T == kQ_Q4_0) {
-    const uint8_t* b = row + static_cast<long long>(grp) * 18;
-    const float d = half_bits(ldg_u16(b));
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const uint32_t w = ldg_u32_a2(b + 2 + 4 * u);
-      wq[u] = w & 0x0F0F0F0Fu;
-      wq[4 + u] = (w >> 4) & 0x0F0F0F0Fu;
-    }
-    dl0 = dl1 = d;
-    ml = -8.f * d;
-  } else if constexpr (T == kQ_Q4_1) {
-    const uint8_t* b = row + static_cast<long long>(grp) * 20;
-    const uint32_t hdr = ldg_u32(b);
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const uint32_t w = ldg_u32(b + 4 + 4 * u);
-      wq[u] = w & 0x0F0F0F0Fu;
-      wq[4 + u] = (w >> 4) & 0x0F0F0F0Fu;
-    }
-    dl0 = dl1 = half_bits(hdr);
-    ml = half_bits(hdr >> 16);
-  } else if constexpr (T == kQ_Q5_0) {
-    const uint8_t* b = row + static_cast<long long>(grp) * 22;
-    const float d = half_bits(ldg_u16(b));
-    const uint32_t qh = ldg_u32_a2(b + 2);
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const uint32_t w = ldg_u32_a2(b + 6 + 4 * u);
-      wq[u] = (w & 0x0F0F0F0Fu) | spread_bit4(qh >> (4 * u));
-      wq[4 + u] = ((w >> 4) & 0x0F0F0F0Fu) | spread_bit4(qh >> (16 + 4 * u));
-    }
-    dl0 = dl1 = d;
-    ml = -16.f * d;
-  } else if constexpr (T == kQ_Q5_1) {
-    const uint8_t* b = row + static_cast<long long>(grp) * 24;
-    const uint32_t hdr = ldg_u32(b);
-    const uint32_t qh = ldg_u32(b + 4);
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const uint32_t w = ldg_u32(b + 8 + 4 * u);
-      wq[u] = (w & 0x0F0F0F0Fu) | spread_bit4(qh >> (4 * u));
-      wq[4 + u] = ((w >> 4) & 0x0F0F0F0Fu) | spread_bit4(qh >> (16 + 4 * u));
-    }
-    dl0 = dl1 = half_bits(hdr);
-    ml = half_bits(hdr >> 16);
-  } else if constexpr (T == kQ_Q8_0) {
-    const uint8_t* b = row + static_cast<long long>(grp) * 34;
-    const float d = half_bits(ldg_u16(b));
-#pragma unroll
-    for (int u = 0; u < 8; ++u) wq[u] = ldg_u32_a2(b + 2 + 4 * u);
-    dl0 = dl1 = d;
-    ml = 0.f;
-  } else if constexpr (T == kQ_Q4_K || T == kQ_Q5_K) {
-    // Q4_K: d | dmin | scales[12] | qs[128];  Q5_K: d | dmin | scales[12] | qh[32] | qs[128]
-    constexpr int kBytes = T == kQ_Q4_K ? 144 : 176;
-    constexpr int kQs = T == kQ_Q4_K ? 16 : 48;
-    const uint8_t* b = row + static_cast<long long>(grp >> 3) * kBytes;
-    const int sub = grp & 7;
-    const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(b));
-    int sc, mn;
-    if (sub < 4) {
-      sc = byte_of3(hdr.y, hdr.z, hdr.w, sub) & 63;
-      mn = byte_of3(hdr.y, hdr.z, hdr.w, sub + 4) & 63;
-    } else {
-      sc = (byte_of3(hdr.y, hdr.z, hdr.w, sub + 4) & 0xF) | ((byte_of3(hdr.y, hdr.z, hdr.w, sub - 4) >> 6) << 4);
-      mn = (byte_of3(hdr.y, hdr.z, hdr.w, sub + 4) >> 4) | ((byte_of3(hdr.y, hdr.z, hdr.w, sub) >> 6) << 4);
-    }
-    const uint4* q = reinterpret_cast<const uint4*>(b + kQs + (sub >> 1) * 32);
-    const uint4 qa = __ldg(q), qb = __ldg(q + 1);
-    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-    const int shift = (sub & 1) * 4;
-    if constexpr (T == kQ_Q4_K) {
-#pragma unroll
-      for (int u = 0; u < 8; ++u) wq[u] = (w[u] >> shift) & 0x0F0F0F0Fu;
-    } else {
-      const uint4* hp = reinterpret_cast<const uint4*>(b + 16);
-      const uint4 ha = __ldg(hp), hb = __ldg(hp + 1);
-      const uint32_t h[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
-#pragma unroll
-      for (int u = 0; u < 8; ++u)
-        wq[u] = ((w[u] >> shift) & 0x0F0F0F0Fu) | (((h[u] >> sub) & 0x01010101u) << 4);
-    }
-    dl0 = dl1 = half_bits(hdr.x) * static_cast<float>(sc);
-    ml = -half_bits(hdr.x >> 16) * static_cast<float>(mn);
-  } else if constexpr (T == kQ_Q6_K) {
-    // ql[128] | qh[64] | scales[16] | d ; 210 bytes, 2-byte aligned
-    const uint8_t* b = row + static_cast<long long>(grp >> 3) * 210;
-    const int sub = grp & 7, half = sub >> 2, quarter = sub & 3;
-    const uint8_t* ql = b + half * 64 + (quarter & 1) * 32;
-    const uint8_t* qh = b + 128 + half * 32;
-    const int nib = (quarter >> 1) * 4, hs = 2 * quarter;
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const uint32_t lo = (ldg_u32_a2(ql + 4 * u) >> nib) & 0x0F0F0F0Fu;
-      const uint32_t hi = ((ldg_u32_a2(qh + 4 * u) >> hs) & 0x03030303u) << 4;
-      wq[u] = __vsub4(lo | hi, 0x20202020u);
-    }
-    const uint32_t sc = ldg_u16(b + 192 + half * 8 + quarter * 2);
-    const float d = half_bits(ldg_u16(b + 208));
-    dl0 = d * static_cast<float>(static_cast<int8_t>(sc & 0xFF));
-    dl1 = d * static_cast<float>(static_cast<int8_t>(sc >> 8));
-    ml = 0.f;
-  }
-}
-
 // One weight row against MB int8 activation rows; every lane takes the groups lane, lane + 32, ...
 template <int T, int MB>
 __device__ __forceinline__ void row_dot_int8(const uint8_t* wrow, const MmvqParams& p, int m0, int lane,
@@ -522,6 +401,7 @@ __device__ __forceinline__ void row_dot_int8(const uint8_t* wrow, const MmvqPara
 
 template <int T, int MB>
 __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_int8_kernel(const MmvqParams p) {
+  pdl_wait();  // the activation rows come from the kernel before this one
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * kRowsPerCta + warp;
   if (n >= p.N) return;
@@ -530,6 +410,7 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_int8_kernel(const MmvqP
 #pragma unroll
   for (int m = 0; m < MB; ++m) acc[m] = 0.f;
   row_dot_int8<T, MB>(p.w + static_cast<long long>(n) * p.row_bytes, p, m0, lane, acc);
+  pdl_launch_dependents();  // the weight stream is done: the next kernel may become resident
 #pragma unroll
   for (int m = 0; m < MB; ++m) {
     const float v = warp_sum(acc[m]);
@@ -541,6 +422,7 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_int8_kernel(const MmvqP
 // launch: a warp looks up the segment of its output row; the type switch is uniform per warp.
 template <int MB>
 __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_mixed_kernel(const MmvqParams p) {
+  pdl_wait();  // the activation rows come from the kernel before this one
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * kRowsPerCta + warp;
   if (n >= p.N) return;
@@ -567,6 +449,7 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_mixed_kernel(const Mmvq
     case kQ_Q6_K: row_dot_int8<kQ_Q6_K, MB>(wrow, p, m0, lane, acc); break;
     default: break;
   }
+  pdl_launch_dependents();  // the weight stream is done: the next kernel may become resident
 #pragma unroll
   for (int m = 0; m < MB; ++m) {
     const float v = warp_sum(acc[m]);
@@ -577,6 +460,7 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_mixed_kernel(const Mmvq
 // Q8_0: 34-byte blocks (fp16 scale + 32 int8) are only 2-byte aligned: seventeen 16-bit loads.
 template <int MB>
 __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q8_0_kernel(const MmvqParams p) {
+  pdl_wait();  // the activation rows come from the kernel before this one
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * kRowsPerCta + warp;
   if (n >= p.N) return;
@@ -615,6 +499,7 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q8_0_kernel(const MmvqP
       acc[m] += d * s;
     }
   }
+  pdl_launch_dependents();  // the weight stream is done: the next kernel may become resident
 #pragma unroll
   for (int m = 0; m < MB; ++m) {
     const float v = warp_sum(acc[m]);
@@ -625,10 +510,10 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) mmvq_q8_0_kernel(const MmvqP
 #define OXB_MMVQ_FAST(KERNEL)                                                                  \
   do {                                                                                         \
     const int gx = (p.N + kRowsPerCta - 1) / kRowsPerCta;                                      \
-    if (p.M == 1) KERNEL<1><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);                       \
-    else if (p.M == 2) KERNEL<2><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);                  \
-    else if (p.M <= 4) KERNEL<4><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);                  \
-    else KERNEL<8><<<dim3(gx, (p.M + 7) / 8), kRowsPerCta * 32, 0, s>>>(p);                    \
+    if (p.M == 1) launch_kernel(KERNEL<1>, dim3(gx, 1), dim3(kRowsPerCta * 32), 0, s, /*pdl=*/true, false, p);                       \
+    else if (p.M == 2) launch_kernel(KERNEL<2>, dim3(gx, 1), dim3(kRowsPerCta * 32), 0, s, /*pdl=*/true, false, p);                  \
+    else if (p.M <= 4) launch_kernel(KERNEL<4>, dim3(gx, 1), dim3(kRowsPerCta * 32), 0, s, /*pdl=*/true, false, p);                  \
+    else launch_kernel(KERNEL<8>, dim3(gx, (p.M + 7) / 8), dim3(kRowsPerCta * 32), 0, s, /*pdl=*/true, false, p);                    \
   } while (0)
 
 // Alignment that expand_q8 of a type needs: 16 bytes for the K-quants read with uint4 loads, 4 for
@@ -649,12 +534,12 @@ void mmvq_dispatch(const MmvqParams& p, cudaStream_t s) {
     if (p.xq != nullptr && aligned && (p.K & 255) == 0 && (reinterpret_cast<uintptr_t>(p.xq) & 15) == 0) {
       if (p.M == 1) {
         const int gx = (p.N + 2 * kRowsPerCta - 1) / (2 * kRowsPerCta);
-        mmvq_q4k_dp4a_kernel<1, 2><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);
+        launch_kernel(mmvq_q4k_dp4a_kernel<1, 2>, dim3(gx, 1), dim3(kRowsPerCta * 32), 0, s, /*pdl=*/true, false, p);
       } else {
         const int gx = (p.N + kRowsPerCta - 1) / kRowsPerCta;
-        if (p.M == 2) mmvq_q4k_dp4a_kernel<2, 1><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);
-        else if (p.M <= 4) mmvq_q4k_dp4a_kernel<4, 1><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);
-        else mmvq_q4k_dp4a_kernel<8, 1><<<dim3(gx, (p.M + 7) / 8), kRowsPerCta * 32, 0, s>>>(p);
+        if (p.M == 2) launch_kernel(mmvq_q4k_dp4a_kernel<2, 1>, dim3(gx, 1), dim3(kRowsPerCta * 32), 0, s, /*pdl=*/true, false, p);
+        else if (p.M <= 4) launch_kernel(mmvq_q4k_dp4a_kernel<4, 1>, dim3(gx, 1), dim3(kRowsPerCta * 32), 0, s, /*pdl=*/true, false, p);
+        else launch_kernel(mmvq_q4k_dp4a_kernel<8, 1>, dim3(gx, (p.M + 7) / 8), dim3(kRowsPerCta * 32), 0, s, /*pdl=*/true, false, p);
       }
       return;
     }
@@ -678,22 +563,22 @@ void mmvq_dispatch(const MmvqParams& p, cudaStream_t s) {
   if constexpr (HasInt8Path<T>::value && T != kQ_Q4_K && T != kQ_Q8_0) {
     if (p.xq != nullptr && int8_operands_ok(T, p.w, p.row_bytes, p)) {
       const int gx = (p.N + kRowsPerCta - 1) / kRowsPerCta;
-      if (p.M == 1) mmvq_int8_kernel<T, 1><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);
-      else if (p.M == 2) mmvq_int8_kernel<T, 2><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);
-      else if (p.M <= 4) mmvq_int8_kernel<T, 4><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);
-      else mmvq_int8_kernel<T, 8><<<dim3(gx, (p.M + 7) / 8), kRowsPerCta * 32, 0, s>>>(p);
+      if (p.M == 1) launch_kernel(mmvq_int8_kernel<T, 1>, dim3(gx, 1), dim3(kRowsPerCta * 32), 0, s, /*pdl=*/true, false, p);
+      else if (p.M == 2) launch_kernel(mmvq_int8_kernel<T, 2>, dim3(gx, 1), dim3(kRowsPerCta * 32), 0, s, /*pdl=*/true, false, p);
+      else if (p.M <= 4) launch_kernel(mmvq_int8_kernel<T, 4>, dim3(gx, 1), dim3(kRowsPerCta * 32), 0, s, /*pdl=*/true, false, p);
+      else launch_kernel(mmvq_int8_kernel<T, 8>, dim3(gx, (p.M + 7) / 8), dim3(kRowsPerCta * 32), 0, s, /*pdl=*/true, false, p);
       return;
     }
   }
   const int gx = (p.N + kRowsPerCta - 1) / kRowsPerCta;
   if (p.M == 1) {
-    mmvq_kernel<T, 1><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);
+    launch_kernel(mmvq_kernel<T, 1>, dim3(gx, 1), dim3(kRowsPerCta * 32), 0, s, /*pdl=*/true, false, p);
   } else if (p.M == 2) {
-    mmvq_kernel<T, 2><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);
+    launch_kernel(mmvq_kernel<T, 2>, dim3(gx, 1), dim3(kRowsPerCta * 32), 0, s, /*pdl=*/true, false, p);
   } else if (p.M <= 4) {
-    mmvq_kernel<T, 4><<<dim3(gx, 1), kRowsPerCta * 32, 0, s>>>(p);
+    launch_kernel(mmvq_kernel<T, 4>, dim3(gx, 1), dim3(kRowsPerCta * 32), 0, s, /*pdl=*/true, false, p);
   } else {
-    mmvq_kernel<T, 8><<<dim3(gx, (p.M + 7) / 8), kRowsPerCta * 32, 0, s>>>(p);
+    launch_kernel(mmvq_kernel<T, 8>, dim3(gx, (p.M + 7) / 8), dim3(kRowsPerCta * 32), 0, s, /*pdl=*/true, false, p);
   }
 }
 
@@ -732,8 +617,8 @@ void launch_quant_q8_1(const __nv_bfloat16* x, long long ldx, int8_t* xq, float*
   const long long warps = static_cast<long long>(M) * (K >> 5);
   if (warps <= 0) return;
   const int threads = 256;
-  quant_q8_1_kernel<<<static_cast<unsigned>((warps * 32 + threads - 1) / threads), threads, 0, stream>>>(
-      x, ldx, xq, xd, xs, M, K);
+  launch_kernel(quant_q8_1_kernel, dim3(static_cast<unsigned>((warps * 32 + threads - 1) / threads)), dim3(threads), 0,
+                stream, /*pdl=*/true, false, x, ldx, xq, xd, xs, M, K);
 }
 
 bool launch_mmvq(int qtype, const MmvqParams& p, cudaStream_t stream) {
@@ -760,10 +645,10 @@ bool launch_mmvq_mixed(const MmvqParams& p, cudaStream_t stream) {
     if (!mmvq_has_int8_path(p.seg_type[i]) || !int8_operands_ok(p.seg_type[i], p.seg_w[i], p.seg_row_bytes[i], p))
       return false;
   const int gx = (p.N + kRowsPerCta - 1) / kRowsPerCta;
-  if (p.M == 1) mmvq_mixed_kernel<1><<<dim3(gx, 1), kRowsPerCta * 32, 0, stream>>>(p);
-  else if (p.M == 2) mmvq_mixed_kernel<2><<<dim3(gx, 1), kRowsPerCta * 32, 0, stream>>>(p);
-  else if (p.M <= 4) mmvq_mixed_kernel<4><<<dim3(gx, 1), kRowsPerCta * 32, 0, stream>>>(p);
-  else mmvq_mixed_kernel<8><<<dim3(gx, (p.M + 7) / 8), kRowsPerCta * 32, 0, stream>>>(p);
+  if (p.M == 1) launch_kernel(mmvq_mixed_kernel<1>, dim3(gx, 1), dim3(kRowsPerCta * 32), 0, stream, /*pdl=*/true, false, p);
+  else if (p.M == 2) launch_kernel(mmvq_mixed_kernel<2>, dim3(gx, 1), dim3(kRowsPerCta * 32), 0, stream, /*pdl=*/true, false, p);
+  else if (p.M <= 4) launch_kernel(mmvq_mixed_kernel<4>, dim3(gx, 1), dim3(kRowsPerCta * 32), 0, stream, /*pdl=*/true, false, p);
+  else launch_kernel(mmvq_mixed_kernel<8>, dim3(gx, (p.M + 7) / 8), dim3(kRowsPerCta * 32), 0, stream, /*pdl=*/true, false, p);
   return true;
 }
 

@@ -202,6 +202,29 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const SampleParams p) 
     }
   }
 
+  // ---- with top-k off the candidates are only the 1024 largest logits: the softmax denominator
+  // (what top-p and the reported log-probability are measured against) is taken over every allowed
+  // logit, so the thresholds are those of the full distribution ----
+  const bool full_mass = top_k >= V && V > C;
+  if (full_mass && n > 0) {
+    const float inv_t = 1.f / temp;
+    const float mx = s_val[0] * inv_t;
+    float part = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x)
+      if (allowed(mask, i)) part += __expf(logits[i] * inv_t - mx);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    float* s_part = reinterpret_cast<float*>(s_hist);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = part;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int w = 0; w < (blockDim.x >> 5); ++w) t += s_part[w];
+      s_best = t;
+    }
+    __syncthreads();
+  }
+
   // ---- filters and draw (serial over <= 1024 sorted candidates) ----
   if (threadIdx.x == 0) {
     if (n <= 0) {
@@ -216,6 +239,7 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const SampleParams p) 
       s_val[i] = e;
       sum += e;
     }
+    if (full_mass) sum = fmaxf(sum, s_best);
     // min-p: keep probabilities >= min_p * p_max (p_max is candidate 0)
     int keep = n;
     if (min_p > 0.f) {

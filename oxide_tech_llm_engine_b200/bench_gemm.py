@@ -31,6 +31,8 @@ def main() -> None:
     ap.add_argument("--trace", action="store_true", help="print the per-CTA timeline (medians over CTAs, microseconds from kernel entry)")
     ap.add_argument("--narrow-boxes", action="store_true", help="mt = 2: two 16 KB TMA boxes per operand and stage instead of one 32 KB box")
     ap.add_argument("--auto", action="store_true", help="time the (bn, mt, splits) that ops.pick_decode_cfg chooses")
+    ap.add_argument("--nvfp4", action="store_true", help="time the NVFP4 block-scaled GEMM (and its activation quantiser)")
+    ap.add_argument("--packed", default="", help="GGUF block type (Q4_K, Q6_K, Q8_0, Q4_0): time the GEMM that unpacks the weights in the kernel")
     ap.add_argument("--fp8", action="store_true", help="time the block-scaled fp8 GEMM (and its activation quantiser)")
     args = ap.parse_args()
     from . import ops
@@ -47,27 +49,28 @@ def main() -> None:
     flops = 2.0 * args.m * args.n * args.k
     wbytes = 2.0 * args.n * args.k
     w_tiled = ops.tile_weight(w)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(args.iters):
+            if not args.no_flush:
+                flush.fill_(1)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e) * 1e3)
+        ts.sort()
+        return ts[len(ts) // 2]
+
     if args.fp8:
         w8, sw = ops.quant_weight_fp8_block(w)
         a8, sa = ops.quant_act_fp8(a)
         out8 = torch.empty(args.m, args.n, device=dev, dtype=torch.bfloat16)
-
-        def timed(fn):
-            for _ in range(3):
-                fn()
-            torch.cuda.synchronize()
-            ts = []
-            for _ in range(args.iters):
-                if not args.no_flush:
-                    flush.fill_(1)
-                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                s.record()
-                fn()
-                e.record()
-                torch.cuda.synchronize()
-                ts.append(s.elapsed_time(e) * 1e3)
-            ts.sort()
-            return ts[len(ts) // 2]
 
         us = timed(lambda: ops.gemm_fp8_block(a8, sa, w8, sw, out=out8))
         uq = timed(lambda: ops.quant_act_fp8(a, a8, sa))
@@ -77,6 +80,37 @@ def main() -> None:
                           "frac_hbm_of_measured": round(wbytes / 2 / us / 1e3 / peaks["hbm_gbs"], 3),
                           "x_bf16_peak_of_measured": round(flops / us / 1e6 / peaks["bf16_tflops"], 3),
                           "quant_act_us": round(uq, 2)}), flush=True)
+        return
+    if args.nvfp4:
+        # NVFP4 x NVFP4 (block scales of 16, e4m3) on the fp4 tensor-core path; the activation quantiser apart
+        wq = ops.Nvfp4Weight.from_float(w.float())
+        aq, sfa, ags = ops.quant_act_nvfp4(a)
+        out4 = torch.empty(args.m, args.n, device=dev, dtype=torch.bfloat16)
+        us = timed(lambda: ops.gemm(aq, wq.q, out=out4, sfa=sfa, sfb=wq.sf, a_gscale=ags, w_gscale=wq.gscale))
+        uq = timed(lambda: ops.quant_act_nvfp4(a))
+        ops.check_status()
+        print(json.dumps({"kernel": "gemm nvfp4 (kind::mxf4nvf4.block_scale)", "m": args.m, "n": args.n, "k": args.k,
+                          "us": round(us, 2), "tflops": round(flops / us / 1e6, 1),
+                          "weights_gb_s": round(wbytes / 4 / us / 1e3, 1),
+                          "x_bf16_peak_of_measured": round(flops / us / 1e6 / peaks["bf16_tflops"], 3),
+                          "quant_act_us": round(uq, 2)}), flush=True)
+        return
+    if args.packed:
+        # bf16 activations x GGUF-packed weights unpacked inside the GEMM, against the same GEMM on a bf16 copy
+        from .models.llama import random_quant_linear
+
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(0)
+        lin = random_quant_linear(args.packed, args.n, args.k, dev, gen)
+        mt = 2 if args.m > 128 else 1
+        sp = max(1, min(ops.sm_count(dev) // (-(-args.n // 128) * -(-args.m // (128 * mt))), args.k // 256, 16))
+        us = timed(lambda: ops.gemm_packed(a, lin.code, lin.w, args.n, out_f32, epi=ops.EPI_RED_F32, mt=mt, splits=sp))
+        ud = timed(lambda: ops.gemm(a, w, epi=ops.EPI_RED_F32, dst_ptrs=[out_f32.data_ptr()], bn=128, mt=mt, splits=sp))
+        ops.check_status()
+        print(json.dumps({"kernel": f"gemm_packed {args.packed}", "m": args.m, "n": args.n, "k": args.k, "mt": mt,
+                          "splits": sp, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1),
+                          "us_same_gemm_on_bf16_weights": round(ud, 2),
+                          "weights_gb_s": round(lin.w.numel() / us / 1e3, 1)}), flush=True)
         return
     combos = list(itertools.product([int(x) for x in args.bn.split(",")], [int(x) for x in args.splits.split(",")],
                                     [int(x) for x in args.tiled.split(",")], [int(x) for x in args.mt.split(",")]))

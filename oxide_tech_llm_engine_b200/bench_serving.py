@@ -159,6 +159,7 @@ def gpu_config(args) -> dict:
                        max_num_batched_tokens=args.max_batched_tokens, gpu_memory_utilization=0.92,
                        sla_budget=False, chunk_max=args.max_batched_tokens, enable_radix=(c == 5),
                        weight_mode=wm, cuda_graph=True, decode_burst=args.burst, burst_max_batch=8,
+                       quant_dense_copy=args.dense_copy,
                        graph_buckets=tuple(b for b in (1, 8, 16, 32, 64, 128, 192, 256) if b <= max(min(seqs, 256), 1)) or (8,))
     eng = LLMEngine(cfg, mc, rank=rank, world=world, device=dev, random_init=True,
                     **({"random_quant_type": {"q4k": "Q4_K", "q4km": "Q4_K_M"}[args.weights]}
@@ -201,6 +202,8 @@ def gpu_config(args) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", type=int, required=True, choices=[1, 2, 3, 4, 5])
+    ap.add_argument("--dense-copy", default="auto", choices=["auto", "on", "off"],
+                    help="packed GGUF weights: keep a bf16 copy for steps with more than 8 rows (off: the GEMM unpacks the blocks itself)")
     ap.add_argument("--burst", type=int, default=0,
                     help="decode steps per host round trip for small greedy batches (in-graph step advance)")
     ap.add_argument("--weights", default="bf16", choices=["bf16", "fp8", "q4k", "q4km", "nvfp4"])

@@ -169,6 +169,7 @@ class DeviceModel:
         # GEMM has to read them
         # kernels of a step overlap their start-up with the tail of the kernel before them (OXB_PDL=0: off)
         ops.set_pdl(os.environ.get("OXB_PDL", "1") != "0")
+        self.packed_gemm = os.environ.get("OXB_PACKED_GEMM", "1") != "0"   # GGUF blocks unpacked inside the GEMM
         self.gemv_small = os.environ.get("OXB_GEMV", "1") != "0"
         self.gemv_max_rows = int(os.environ.get("OXB_GEMV_MAX", "2"))
         self._sms = torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 148
@@ -611,6 +612,17 @@ class DeviceModel:
         w = lin.w
         if lin.packed and getattr(lin, "dense", None) is not None:
             w = lin.dense
+        elif lin.packed and lin.code in ops.INT8_MMVQ_CODES and lin.k % 256 == 0 and self.packed_gemm and m <= 256:
+            # one row tile: the GEMM unpacks every block exactly once itself (no bf16 copy, no scratch
+            # pass). Above 256 rows each row tile would unpack the weights again, and expanding them
+            # once into the scratch buffer is cheaper.
+            mt = 2 if m > 128 else 1
+            # the unpacking is the bound: spread it over as many SMs as the tiles and K allow
+            tiles = (lin.n + 127) // 128
+            sp = max(1, min(self._sms // tiles, lin.k // 256, 16))
+            out_f32[:m].zero_() if out_f32.is_contiguous() else out_f32[:m].fill_(0)
+            ops.gemm_packed(x, lin.code, lin.w, lin.n, out_f32[:m], epi=ops.EPI_RED_F32, mt=mt, splits=sp)
+            return
         elif lin.packed:
             w = self._scratch_for(lin.n, lin.k)
             ops.dequant_rows(lin.code, lin.w, w, n_src_rows=lin.n, k=lin.k)

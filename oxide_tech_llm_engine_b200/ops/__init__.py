@@ -519,6 +519,17 @@ def softcap(logits, cap: float) -> None:
     _bump()
 
 
+def gemm_packed(a: torch.Tensor, qtype: int, qw: torch.Tensor, n: int, out: torch.Tensor, *, epi: int = EPI_STORE_BF16,
+                mt: int = 1, splits: int = 1, bias: Optional[torch.Tensor] = None) -> None:
+    """out[:M, :n] (+)= a @ W^T for a GGUF-packed weight (`qw` = the block bytes of n rows, block type
+    `qtype` from INT8_MMVQ_CODES): the tcgen05 GEMM with four extra warps that unpack each 128 x 64
+    weight tile into the bf16 operand stage, so the weights stay packed in HBM and no bf16 copy or
+    scratch expansion exists (reference: the MMQ kernels, quant_gemm_mmq.cu:191-409, :624-788).
+    `epi` EPI_RED_F32 adds into a zeroed fp32 `out` and may split K."""
+    _ext().gemm_packed(a, qw, int(qtype), int(n), out, epi, mt, splits, bias, status_word(a.device), SPIN_LIMIT)
+    _bump()
+
+
 def alloc_mapped_host(n_words: int):
     """Page-locked host memory mapped into the device's address space: (int64 host tensor, device
     address). Kernels post results there and the host polls them without a stream synchronisation."""

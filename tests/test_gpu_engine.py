@@ -118,8 +118,9 @@ def test_gguf_quantized_serving(qtype):
 
 
 def test_nvfp4_moe_checkpoint_is_served_through_the_fused_expert_path():
-    """A Mixtral-style GGUF whose matrices are NVFP4 blocks: the expert weights are expanded to bf16 at
-    load (packed serving is for dense models) and run through the router / grouped GEMM / combine."""
+    """A Mixtral-style GGUF whose matrices are NVFP4 blocks but whose sizes do not fit the 128 x 256-value
+    tiles of the fp4 tensor-core path (the tiny preset): the expert weights are expanded to bf16 at load
+    and run through the router / grouped GEMM / combine. (Sizes that fit are served packed, next test.)"""
     from oxide_tech_llm_engine_b200.models.config import preset
     from oxide_tech_llm_engine_b200.models.weights import open_weights, write_synthetic_gguf
     from oxide_tech_llm_engine_b200.sampling_params import SamplingParams

@@ -679,6 +679,35 @@ def test_dequant_and_mmvq(ops, qname):
     assert _rel_err(yb, x.float() @ ref.T + bias.float() + y0.float()) < 2e-2
 
 
+@pytest.mark.parametrize("qname", ["Q4_K", "Q6_K", "Q8_0", "Q5_K", "Q5_0", "Q4_0", "Q4_1", "Q5_1"])
+def test_gemm_with_gguf_weights_unpacked_in_the_kernel(ops, qname):
+    """tcgen05 GEMM whose weight operand stays GGUF-packed in HBM: against fp32 of the activations times
+    the decoded weights (rounded to bf16, as the kernel's operand stage holds them)."""
+    from oxide_tech_llm_engine_b200.formats import quants
+
+    rng = np.random.default_rng(31)
+    N, K = 200, 1024
+    w = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    raw = quants.quantize_2d(qname, w)
+    wd = torch.from_numpy(quants.dequantize_2d(qname, raw, N, K)).to(DEV).to(torch.bfloat16).float()
+    code = quants.TYPES[qname].code
+    w_dev = torch.from_numpy(raw).to(DEV).view(-1)
+    for M, mt, splits in ((17, 1, 1), (128, 1, 2), (300, 2, 1), (300, 1, 4), (513, 2, 2)):
+        x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+        ref = x.float() @ wd.T
+        out = torch.zeros(M, N, device=DEV, dtype=torch.float32)
+        ops.gemm_packed(x, code, w_dev, N, out, epi=ops.EPI_RED_F32, mt=mt, splits=splits)
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert _rel_err(out, ref) < 2e-3, (qname, M, mt, splits, _rel_err(out, ref))
+    x = torch.randn(140, K, device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty(140, N, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_packed(x, code, w_dev, N, out, epi=ops.EPI_STORE_BF16, mt=2, bias=bias)
+    torch.cuda.synchronize()
+    assert _rel_err(out, x.float() @ wd.T + bias.float()) < 1e-2
+
+
 def test_mmvq_mixed_types_in_one_launch(ops):
     """Q | K | V of a mixed-precision file (Q4_K, Q4_K, Q6_K) and two more combinations as one GEMV
     launch each, against the exact product of the int8 activations with the decoded weights."""
@@ -757,6 +786,20 @@ def test_argmax_and_sampling(ops):
     ops.sample(lg, toks, temperature=temp, top_k=torch.zeros_like(tk), top_p=tp, min_p=mp2, seeds=seeds,
                counters=ctr)
     assert (toks == top4.indices[0]).all()
+    # top-k off on a flat, hot distribution: the nucleus is cut where the FULL softmax reaches top_p,
+    # not where the softmax over the 1024 candidates does, and the log-probability is the full one
+    hot = torch.full((n,), 3.0, device=DEV)
+    tp3 = torch.full((n,), 0.10, device=DEV)
+    lp = torch.empty(n, device=DEV)
+    ops.sample(lg, toks, temperature=hot, top_k=torch.zeros_like(tk), top_p=tp3, min_p=mp, seeds=seeds,
+               counters=ctr, out_logit=lp)
+    full = torch.softmax(lg[0] / 3.0, -1)
+    srt = full.sort(descending=True)
+    n_keep = int((srt.values.cumsum(0) < 0.10).sum().item()) + 1
+    nucleus = set(srt.indices[:n_keep].tolist())
+    drawn = set(toks.tolist())
+    assert drawn <= nucleus and len(drawn) > 0.5 * n_keep, (len(drawn), n_keep)
+    torch.testing.assert_close(lp, torch.log(full[toks.long()]), rtol=0, atol=2e-3)
 
 
 @pytest.mark.gpu
