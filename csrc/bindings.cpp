@@ -436,7 +436,8 @@ void paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
                   const Tensor& part_o, const Tensor& part_ml, const Tensor& out, int64_t batch,
                   int64_t max_splits, int64_t window, double scale,
                   const c10::optional<Tensor>& status, const c10::optional<Tensor>& page_ml,
-                  const c10::optional<Tensor>& block_mass) {
+                  const c10::optional<Tensor>& block_mass, const c10::optional<Tensor>& q8,
+                  const c10::optional<Tensor>& q8_d, const c10::optional<Tensor>& q8_s) {
   TORCH_CHECK(q.dim() == 3 && k_cache.dim() == 4, "paged_decode: q [B,Hq,D], cache [blk,Hkv,16,D]");
   TORCH_CHECK(k_cache.size(2) == 16, "paged_decode: 16-token pages");
   oxb::DecodeAttnParams p{};
@@ -475,6 +476,16 @@ void paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
     TORCH_CHECK(block_mass->numel() >= batch * p.max_blocks, "paged_decode: block_mass too small");
     p.page_ml = page_ml->data_ptr<float>();
     p.block_mass = block_mass->data_ptr<float>();
+  }
+  if (q8.has_value() && q8->defined()) {
+    const int64_t kq = static_cast<int64_t>(p.Hq) * D;
+    TORCH_CHECK(q8_d.has_value() && q8_s.has_value() && q8->element_size() == 1 && q8->numel() >= batch * kq &&
+                    q8_d->numel() >= batch * (kq / 32) && q8_s->numel() >= batch * (kq / 32) &&
+                    q8_d->scalar_type() == at::kFloat && q8_s->scalar_type() == at::kFloat,
+                "paged_decode: q8 [B, Hq*D] int8 with q8_d / q8_s [B, Hq*D / 32] fp32 expected");
+    p.q8 = reinterpret_cast<signed char*>(q8->data_ptr());
+    p.q8_d = q8_d->data_ptr<float>();
+    p.q8_s = q8_s->data_ptr<float>();
   }
   (void)oxb::launch_paged_decode(p, static_cast<int>(batch), D, cur_stream());
   check_launch("paged_decode");
@@ -541,7 +552,8 @@ void finalize_norm(const c10::optional<Tensor>& acc, const c10::optional<Tensor>
                    const c10::optional<Tensor>& router_w, int64_t top_k, int64_t experts_per_rank,
                    double routed_scale, const std::vector<int64_t>& slab_ptrs,
                    const std::vector<int64_t>& meta_ptrs, const std::vector<int64_t>& cnt_ptrs,
-                   int64_t cap, int64_t my_rank, int64_t spin_limit) {
+                   int64_t cap, int64_t my_rank, int64_t spin_limit, const c10::optional<Tensor>& q8,
+                   const c10::optional<Tensor>& q8_d, const c10::optional<Tensor>& q8_s) {
   TORCH_CHECK(N % 8 == 0 && N <= 1024 * 8 * 4, "finalize_norm: N must be a multiple of 8 and <= 32768");
   oxb::FinalizeNormParams p{};
   p.acc = opt_ptr<float>(acc);
@@ -591,6 +603,16 @@ void finalize_norm(const c10::optional<Tensor>& acc, const c10::optional<Tensor>
     p.cap = static_cast<int>(cap);
     p.my_rank = static_cast<int>(my_rank);
   }
+  if (q8.has_value() && q8->defined()) {
+    TORCH_CHECK(q8_d.has_value() && q8_s.has_value() && N % 32 == 0 && q8->element_size() == 1 &&
+                    q8->numel() >= rows * N && q8_d->numel() >= rows * (N / 32) && q8_s->numel() >= rows * (N / 32) &&
+                    q8_d->scalar_type() == at::kFloat && q8_s->scalar_type() == at::kFloat &&
+                    reinterpret_cast<uintptr_t>(q8->data_ptr()) % 8 == 0,
+                "finalize_norm: q8 [rows, N] int8 with q8_d / q8_s [rows, N / 32] fp32 expected");
+    p.q8 = reinterpret_cast<int8_t*>(q8->data_ptr());
+    p.q8_d = q8_d->data_ptr<float>();
+    p.q8_s = q8_s->data_ptr<float>();
+  }
   oxb::launch_finalize_norm(p, cur_stream());
   check_launch("finalize_norm");
 }
@@ -634,7 +656,8 @@ void qkv_rope_append(const c10::optional<Tensor>& acc_f32, const c10::optional<T
 }
 
 void swiglu(const c10::optional<Tensor>& acc_f32, const c10::optional<Tensor>& gu_bf16,
-            const Tensor& out, int64_t M, int64_t I, int64_t act) {
+            const Tensor& out, int64_t M, int64_t I, int64_t act, const c10::optional<Tensor>& q8,
+            const c10::optional<Tensor>& q8_d, const c10::optional<Tensor>& q8_s) {
   oxb::SwigluParams p{};
   p.acc_f32 = opt_ptr<float>(acc_f32);
   p.gu_bf16 = bf16_ptr(gu_bf16);
@@ -643,6 +666,16 @@ void swiglu(const c10::optional<Tensor>& acc_f32, const c10::optional<Tensor>& g
   p.M = static_cast<int>(M);
   p.I = static_cast<int>(I);
   p.act = static_cast<int>(act);
+  if (q8.has_value() && q8->defined()) {
+    TORCH_CHECK(q8_d.has_value() && q8_s.has_value() && I % 32 == 0 && q8->element_size() == 1 &&
+                    q8->numel() >= M * I && q8_d->numel() >= M * (I / 32) && q8_s->numel() >= M * (I / 32) &&
+                    q8_d->scalar_type() == at::kFloat && q8_s->scalar_type() == at::kFloat &&
+                    reinterpret_cast<uintptr_t>(q8->data_ptr()) % 4 == 0,
+                "swiglu: q8 [M, I] int8 with q8_d / q8_s [M, I / 32] fp32 expected");
+    p.q8 = reinterpret_cast<int8_t*>(q8->data_ptr());
+    p.q8_d = q8_d->data_ptr<float>();
+    p.q8_s = q8_s->data_ptr<float>();
+  }
   oxb::launch_swiglu(p, cur_stream());
   check_launch("swiglu");
 }

@@ -33,6 +33,12 @@ struct DecodeAttnParams {
   // (0 for pages outside the attended range).
   float* page_ml;
   float* block_mass;
+  // Optional int8 view of `out` for an integer GEMV that consumes it (blocks of 32 values with an
+  // fp32 scale = amax / 127 and scale * sum): q8 [B, Hq*D] int8, q8_d / q8_s [B, Hq*D / 32], written
+  // by the merge kernel.
+  signed char* q8;
+  float* q8_d;
+  float* q8_s;
 };
 
 // Launches the split kernel and then the merge; the merge is skipped when the first launch failed.

@@ -409,7 +409,27 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const DecodeAttnParams 
     L += f * p.part_ml[(base + s) * 2 + 1];
   }
   const float r = L > 0.f ? acc / L : 0.f;
-  p.out[static_cast<long long>(seq) * p.out_stride + head * D + d] = __float2bfloat16(r);
+  const __nv_bfloat16 rb = __float2bfloat16(r);
+  p.out[static_cast<long long>(seq) * p.out_stride + head * D + d] = rb;
+  if (p.q8 != nullptr) {
+    // a warp holds one block of 32 values: scale = amax / 127, codes, scale * sum
+    const float v = __bfloat162float(rb);
+    float amax = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float dq = amax / 127.f;
+    const float inv = amax > 0.f ? 127.f / amax : 0.f;
+    const int q = __float2int_rn(v * inv);
+    int sum = q;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const long long e = (static_cast<long long>(seq) * p.Hq + head) * D + d;
+    p.q8[e] = static_cast<signed char>(q);
+    if ((d & 31) == 0) {
+      p.q8_d[e >> 5] = dq;
+      p.q8_s[e >> 5] = dq * static_cast<float>(sum);
+    }
+  }
 }
 
 // block_mass[seq, page] = sum_h page_sum[h] * 2^(page_max[h] - M_h) / L_h, with (M_h, L_h) the merged

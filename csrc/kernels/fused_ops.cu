@@ -53,6 +53,43 @@ constexpr int kNormMaxChunks = 4;  // 8-element chunks per thread: N <= 1024 * 8
 
 // One CTA per row (looping when there are more rows than resident CTAs); every thread owns up to
 // kNormMaxChunks 8-element chunks, kept in registers.
+// int8 quantisation of V consecutive bf16-rounded values of this thread as part of a block of 32 that
+// 32 / V neighbouring lanes hold together (the numbers of quant_q8_1_kernel): scale = amax / 127.
+template <int V>
+__device__ __forceinline__ void q8_block_store(const float (&y)[V], int8_t* q8, float* d_out, float* s_out,
+                                               bool leader) {
+  const unsigned m = __activemask();
+  float v[V], amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    v[j] = __bfloat162float(__float2bfloat16(y[j]));
+    amax = fmaxf(amax, fabsf(v[j]));
+  }
+#pragma unroll
+  for (int o = 1; o < 32 / V; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(m, amax, o));
+  const float d = amax / 127.f;
+  const float inv = amax > 0.f ? 127.f / amax : 0.f;  // one division per block, not one per value
+  int sum = 0;
+  int8_t q[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    const int qi = __float2int_rn(v[j] * inv);
+    q[j] = static_cast<int8_t>(qi);
+    sum += qi;
+  }
+#pragma unroll
+  for (int o = 1; o < 32 / V; o <<= 1) sum += __shfl_xor_sync(m, sum, o);
+  if constexpr (V == 8) {
+    *reinterpret_cast<uint2*>(q8) = *reinterpret_cast<const uint2*>(q);
+  } else {
+    *reinterpret_cast<uint32_t*>(q8) = *reinterpret_cast<const uint32_t*>(q);
+  }
+  if (leader) {
+    *d_out = d;
+    *s_out = d * static_cast<float>(sum);
+  }
+}
+
 // All global loads of a row are issued before the first dependent instruction, so a row costs
 // about one memory round trip however few rows (CTAs) there are.
 __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const FinalizeNormParams p) {
@@ -190,6 +227,10 @@ __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const Fi
 #pragma unroll
     for (int d = 0; d < kMaxPeers; ++d)
       if (d < p.n_dst && store_out) *reinterpret_cast<uint4*>(p.out[d] + ooff + c) = o;
+    if (p.q8 != nullptr && store_out) {
+      const long long blk = orow * static_cast<long long>(N >> 5) + (c >> 5);
+      q8_block_store<8>(y, p.q8 + ooff + c, p.q8_d + blk, p.q8_s + blk, (c & 31) == 0);
+    }
   }
 
   if (p.router_w != nullptr) {
@@ -459,6 +500,10 @@ __global__ void swiglu_kernel(const SwigluParams p) {
     o.x = pack_bf16x2(y[0], y[1]);
     o.y = pack_bf16x2(y[2], y[3]);
     *reinterpret_cast<uint2*>(p.out + m * p.I + c) = o;
+    if (p.q8 != nullptr) {
+      const long long blk = m * (p.I >> 5) + (c >> 5);
+      q8_block_store<4>(y, p.q8 + m * p.I + c, p.q8_d + blk, p.q8_s + blk, (c & 31) == 0);
+    }
   }
 }
 

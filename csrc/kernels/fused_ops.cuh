@@ -40,6 +40,12 @@ struct FinalizeNormParams {
   int rows, N;
   int* status;
   uint32_t spin_limit;      // iterations of the bounded arrival wait (0 = OXB_SPIN_LIMIT)
+  // Optional int8 view of the output rows for the integer GEMV that consumes them (the same numbers
+  // as launch_quant_q8_1 on the bf16 output): q8 [*, N] int8, q8_d / q8_s [*, N / 32] block scale and
+  // scale * sum, indexed by the destination row. N must be a multiple of 32.
+  int8_t* q8;
+  float* q8_d;
+  float* q8_s;
   // --- MoE dispatch mode (router_w != nullptr): the normed row goes only to the ranks that own
   //     its top-k experts, into that expert's receive slab, instead of to out[] ---
   const __nv_bfloat16* router_w;  // [n_experts, N]
@@ -79,6 +85,10 @@ struct SwigluParams {
   __nv_bfloat16* out;              // [M, I]
   int M, I;
   int act;                         // 0 = SiLU (SwiGLU), 1 = tanh-GELU (GeGLU)
+  // optional int8 view of `out` (see FinalizeNormParams::q8); I must be a multiple of 32
+  int8_t* q8;
+  float* q8_d;
+  float* q8_s;
 };
 void launch_swiglu(const SwigluParams& p, cudaStream_t stream);
 

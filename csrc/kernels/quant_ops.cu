@@ -216,7 +216,8 @@ __global__ void quant_q8_1_kernel(const __nv_bfloat16* __restrict__ x, long long
   const float v = __bfloat162float(x[static_cast<long long>(row) * ldx + blk * 32 + lane]);
   const float amax = warp_max(fabsf(v));
   const float d = amax / 127.f;
-  const int q = amax > 0.f ? __float2int_rn(v / d) : 0;
+  const float inv = amax > 0.f ? 127.f / amax : 0.f;
+  const int q = __float2int_rn(v * inv);
   xq[static_cast<long long>(row) * K + blk * 32 + lane] = static_cast<int8_t>(q);
   const float sum = warp_sum(static_cast<float>(q));
   if (lane == 0) {

@@ -169,6 +169,7 @@ class DeviceModel:
         # GEMM has to read them
         # kernels of a step overlap their start-up with the tail of the kernel before them (OXB_PDL=0: off)
         ops.set_pdl(os.environ.get("OXB_PDL", "1") != "0")
+        self.fold_q8 = os.environ.get("OXB_FOLD_Q8", "1") != "0"
         self.packed_gemm = os.environ.get("OXB_PACKED_GEMM", "1") != "0"   # GGUF blocks unpacked inside the GEMM
         self.gemv_small = os.environ.get("OXB_GEMV", "1") != "0"
         self.gemv_max_rows = int(os.environ.get("OXB_GEMV_MAX", "2"))
@@ -463,7 +464,8 @@ class DeviceModel:
 
     def _finalize(self, rows: int, norm_w, *, acc: Optional[int], gather: str, flag_base: int,
                   r0: int, first: bool = False, row_map=None, layer: Optional[dict] = None,
-                  moe: bool = False, moe_acc: bool = False, out_local: Optional[torch.Tensor] = None) -> None:
+                  moe: bool = False, moe_acc: bool = False, out_local: Optional[torch.Tensor] = None,
+                  q8=None) -> None:
         tp, d = self.tp, self.cfg.d_model
         multi = tp > 1
         kw = {}
@@ -499,7 +501,7 @@ class DeviceModel:
                           residual_out=None if first else self.residual, norm_w=norm_w,
                           eps=self.cfg.rms_eps, w_offset=self.cfg.norm_weight_offset,
                           out_ptrs=self.ws.ptrs(gather), out_flag_ptrs=flag_ptrs, out_row_off=r0,
-                          out_row_map=row_map, device=self.device, **kw)
+                          out_row_map=row_map, device=self.device, q8=q8, **kw)
 
     def _ag_kwargs(self, flag_base: int, ticket: int, rows_per_src: int, expected: int) -> dict:
         if self.tp == 1:
@@ -589,9 +591,19 @@ class DeviceModel:
             self._scratch = torch.empty(need, dtype=torch.bfloat16, device=self.device)
         return self._scratch[:need].view(n, k)
 
+    def _q8_views(self, m: int, k: int, producer: bool = True):
+        """Views of the int8 activation buffers for `m` rows of `k` values, or None when the integer GEMV
+        does not apply (more rows than it takes, K not a multiple of 256). `producer`: asked on behalf of
+        a kernel that would write the int8 view next to its own output (OXB_FOLD_Q8=0 turns that off,
+        the stand-alone quantiser then runs instead)."""
+        if m > (4 if self._has_dense else 8) or k % 256 or (producer and not self.fold_q8):
+            return None
+        b = self._q8_bufs
+        return b[0][:m * k].view(m, k), b[1][:m * (k // 32)].view(m, k // 32), b[2][:m * (k // 32)].view(m, k // 32)
+
     def _q8(self, x: torch.Tensor):
         """int8 view of the activation rows for the integer dot-product GEMV (small batches only)."""
-        if x.shape[0] > (4 if self._has_dense else 8) or x.shape[1] % 256:
+        if self._q8_views(x.shape[0], x.shape[1], producer=False) is None:
             return None
         return ops.quant_q8_1(x, self._q8_bufs)
 
@@ -738,7 +750,7 @@ class DeviceModel:
             self.block_mass = torch.zeros(self._max_seqs, self._max_blocks_per_seq, dtype=torch.float32,
                                           device=self.device)
 
-    def _attention(self, s: StepInputs, li: int) -> None:
+    def _attention(self, s: StepInputs, li: int, q8=None) -> None:
         nd = s.n_decode
         win = self.cfg.sliding_window
         if nd > 0:
@@ -747,7 +759,7 @@ class DeviceModel:
                              s.block_tables, s.seq_lens, s.pages_per_split, self.part_o, self.part_ml,
                              self.attn_out[:nd], batch=nd, max_splits=self.max_splits, window=win,
                              scale=self.scale, page_ml=self.page_ml if mass else None,
-                             block_mass=self.block_mass if mass else None)
+                             block_mass=self.block_mass if mass else None, q8=q8)
         if s.n_prefill > 0:
             ops.paged_prefill(self.q_buf.view(-1, self.hq, self.D), self.k_cache[li], self.v_cache[li],
                               s.prefill_block_tables, s.tile_seq, s.tile_q0, s.q_start, s.q_lens, s.ctx_lens,
@@ -793,10 +805,15 @@ class DeviceModel:
                              k=d, row_ids=s.token_ids[:M], scale=cfg.emb_scale)
         else:
             ops.embed_gather(s.token_ids[:M], self.embed_q.w, self.residual[:M], cfg.emb_scale)
-        self._finalize(M, self.layers[0]["attn_norm"], acc=None, gather="gather0", flag_base=F_AG0, r0=0, first=True)
+        # the kernels that produce an activation row also write its int8 view for the integer GEMV
+        # (finalize_norm for the normed rows, swiglu for the FFN activation): no quantiser launches
+        # except for the attention output
+        xq_d = self._q8_views(M, d)
+        self._finalize(M, self.layers[0]["attn_norm"], acc=None, gather="gather0", flag_base=F_AG0, r0=0, first=True,
+                       q8=xq_d)
         qd, kd = cfg.q_dim, cfg.kv_dim
         for li, L in enumerate(self.layers):
-            xq = self._q8(g0)
+            xq = xq_d if xq_d is not None else self._q8(g0)
             if "attn_qkv" in L:
                 self._qlinear(L["attn_qkv"], g0, self.qkv_acc[:M], xq=xq)
             elif xq is not None and L.get("qkv_mix") is not None and M <= self._mmvq_rows(L["attn_q"]):
@@ -810,10 +827,13 @@ class DeviceModel:
                                 slot_mapping=s.slot_mapping, inv_freq=self.inv_freq, rope_mscale=self.rope_mscale,
                                 q_out=self.q_buf, k_cache=self.k_cache[li], v_cache=self.v_cache[li], m=M,
                                 hq=self.hq, hkv=self.hkv, d=self.D)
-            self._attention(s, li)
-            self._qlinear(L["attn_output"], self.attn_out[:M], acc0[:M], xq=self._q8(self.attn_out[:M]))
-            self._finalize(M, L["ffn_norm"], acc=0, gather="gather1", flag_base=F_AG1, r0=0)
-            xq = self._q8(g1)
+            # decode-only steps: the merge kernel of the attention writes the int8 view of its output
+            xq_o = self._q8_views(M, cfg.q_dim) if (s.n_prefill == 0 and s.n_decode == M) else None
+            self._attention(s, li, q8=xq_o)
+            self._qlinear(L["attn_output"], self.attn_out[:M], acc0[:M],
+                          xq=xq_o if xq_o is not None else self._q8(self.attn_out[:M]))
+            self._finalize(M, L["ffn_norm"], acc=0, gather="gather1", flag_base=F_AG1, r0=0, q8=xq_d)
+            xq = xq_d if xq_d is not None else self._q8(g1)
             if "ffn_gate_up" in L:
                 self._qlinear(L["ffn_gate_up"], g1, self.gu_acc[:M], xq=xq)
             elif xq is not None and L.get("gu_mix") is not None and M <= self._mmvq_rows(L["ffn_gate"]):
@@ -821,14 +841,18 @@ class DeviceModel:
             else:
                 self._qlinear(L["ffn_gate"], g1, self.gu_acc[:M, :self.i_l], xq=xq)
                 self._qlinear(L["ffn_up"], g1, self.gu_acc[:M, self.i_l:], xq=xq)
-            ops.swiglu(acc_f32=self.gu_acc, out=self.act, m=M, i=self.i_l, act=self._act_code)
-            self._qlinear(L["ffn_down"], self.act[:M], acc1[:M], xq=self._q8(self.act[:M]))
+            xq_a = self._q8_views(M, self.i_l)
+            ops.swiglu(acc_f32=self.gu_acc, out=self.act, m=M, i=self.i_l, act=self._act_code, q8=xq_a)
+            self._qlinear(L["ffn_down"], self.act[:M], acc1[:M], xq=xq_a if xq_a is not None else self._q8(self.act[:M]))
             if li != cfg.n_layers - 1:
-                self._finalize(M, self.layers[li + 1]["attn_norm"], acc=1, gather="gather0", flag_base=F_AG0, r0=0)
+                self._finalize(M, self.layers[li + 1]["attn_norm"], acc=1, gather="gather0", flag_base=F_AG0, r0=0,
+                               q8=xq_d)
         n_log = max(s.n_logits, 1)
-        self._finalize(M, self.out_norm, acc=1, gather="lmg", flag_base=F_LMG, r0=0, row_map=s.logit_map[:M])
+        xq_l = self._q8_views(M, d)   # indexed by the destination (logits) row, of which there are at most M
+        self._finalize(M, self.out_norm, acc=1, gather="lmg", flag_base=F_LMG, r0=0, row_map=s.logit_map[:M], q8=xq_l)
         lmg = self.ws.local("lmg")[:n_log]
-        self._qlinear(self.lm_head_q, lmg, self.logits[:n_log], xq=self._q8(lmg) if n_log <= 8 else None)
+        self._qlinear(self.lm_head_q, lmg, self.logits[:n_log],
+                      xq=xq_l if xq_l is not None else (self._q8(lmg) if n_log <= 8 else None))
         if cfg.logit_softcap > 0:
             ops.softcap(self.logits[:n_log], cfg.logit_softcap)
         return self.logits[:n_log]

@@ -422,14 +422,17 @@ def untile_weight(w: torch.Tensor) -> torch.Tensor:
 
 def paged_decode(q, k_cache, v_cache, block_tables, seq_lens, pages_per_split, part_o, part_ml, out,
                  *, batch: int, max_splits: int, window: int = 0, scale: float,
-                 page_ml: Optional[torch.Tensor] = None, block_mass: Optional[torch.Tensor] = None) -> None:
+                 page_ml: Optional[torch.Tensor] = None, block_mass: Optional[torch.Tensor] = None,
+                 q8=None) -> None:
     """Paged split-KV decode attention + merge. With `page_ml` [B, max_blocks, Hq, 2] and `block_mass`
     [B, max_blocks] (fp32) the kernels also produce the softmax probability mass per KV block, summed
     over heads: the heavy-hitter score of H2O pruning (the reference accumulates it in its decode
-    kernel too, oxide-backend-cuda/src/kernels/megakernel_ops.cu:577-617)."""
+    kernel too, oxide-backend-cuda/src/kernels/megakernel_ops.cu:577-617). `q8` = (int8 [B, Hq*D],
+    scales, sums): the merge also writes the int8 view of `out` (see `finalize_norm`)."""
+    q8t, q8d, q8s = q8 if q8 is not None else (None, None, None)
     _ext().paged_decode(q, k_cache, v_cache, block_tables, seq_lens, pages_per_split, part_o, part_ml,
                         out, batch, max_splits, window, scale, status_word(q.device) if CHECK_BOUNDS else None,
-                        page_ml, block_mass)
+                        page_ml, block_mass, q8t, q8d, q8s)
     _bump(3 if page_ml is not None else 2)
 
 
@@ -453,11 +456,15 @@ def finalize_norm(*, rows: int, n: int, acc=None, rs_slab=None, n_slabs: int = 0
                   w_offset: float = 0.0, out_ptrs: Sequence[int] = (), out_flag_ptrs: Sequence[int] = (),
                   out_row_off: int = 0, out_row_map=None, router_w=None, top_k: int = 0, experts_per_rank: int = 0,
                   routed_scale: float = 1.0, slab_ptrs: Sequence[int] = (), meta_ptrs: Sequence[int] = (),
-                  cnt_ptrs: Sequence[int] = (), cap: int = 0, my_rank: int = 0, device=None) -> None:
+                  cnt_ptrs: Sequence[int] = (), cap: int = 0, my_rank: int = 0, device=None, q8=None) -> None:
+    """`q8` = (int8 [rows, n], fp32 scales [rows, n/32], fp32 sums [rows, n/32]): the kernel also writes
+    the int8 view of its output rows (the numbers `quant_q8_1` would produce from them), so the integer
+    GEMV that follows needs no quantiser launch."""
+    q8t, q8d, q8s = q8 if q8 is not None else (None, None, None)
     _ext().finalize_norm(acc, rs_slab, n_slabs, slab_stride, arrive, expected, ticket, residual_in, residual_out, bias, norm_w, eps,
                          w_offset, list(out_ptrs), list(out_flag_ptrs), out_row_off, out_row_map, rows, n,
                          status_word(device), router_w, top_k, experts_per_rank, routed_scale,
-                         list(slab_ptrs), list(meta_ptrs), list(cnt_ptrs), cap, my_rank, SPIN_LIMIT)
+                         list(slab_ptrs), list(meta_ptrs), list(cnt_ptrs), cap, my_rank, SPIN_LIMIT, q8t, q8d, q8s)
     _bump()
 
 
@@ -489,8 +496,10 @@ def qkv_rope_append(*, acc_f32=None, qkv_bf16=None, bias=None, q_norm_w=None, k_
     _bump()
 
 
-def swiglu(*, acc_f32=None, gu_bf16=None, out, m: int, i: int, act: int = 0) -> None:
-    _ext().swiglu(acc_f32, gu_bf16, out, m, i, act)
+def swiglu(*, acc_f32=None, gu_bf16=None, out, m: int, i: int, act: int = 0, q8=None) -> None:
+    """`q8` as in `finalize_norm`: the int8 view of `out` for the integer GEMV that follows."""
+    q8t, q8d, q8s = q8 if q8 is not None else (None, None, None)
+    _ext().swiglu(acc_f32, gu_bf16, out, m, i, act, q8t, q8d, q8s)
     _bump()
 
 

@@ -708,6 +708,51 @@ def test_gemm_with_gguf_weights_unpacked_in_the_kernel(ops, qname):
     assert _rel_err(out, x.float() @ wd.T + bias.float()) < 1e-2
 
 
+def test_norm_and_swiglu_write_the_int8_view_of_their_output(ops):
+    """finalize_norm and swiglu with `q8`: the int8 blocks, scales and sums are exactly what the
+    stand-alone quantiser makes of the bf16 rows those kernels wrote."""
+    torch.manual_seed(41)
+    rows, n = 5, 4096
+    x = torch.randn(rows, n, device=DEV, dtype=torch.bfloat16)
+    w = (torch.rand(n, device=DEV) + 0.5).to(torch.bfloat16)
+    out = torch.empty_like(x)
+    q8 = (torch.zeros(rows, n, dtype=torch.int8, device=DEV), torch.zeros(rows, n // 32, device=DEV),
+          torch.zeros(rows, n // 32, device=DEV))
+    ops.finalize_norm(rows=rows, n=n, residual_in=x, norm_w=w, eps=1e-5, out_ptrs=[out.data_ptr()], device=x.device,
+                      q8=q8)
+    want = ops.quant_q8_1(out)
+    torch.cuda.synchronize()
+    for got, ref in zip(q8, want):
+        assert torch.equal(got, ref)
+    m, i = 3, 1024
+    gu = torch.randn(m, 2 * i, device=DEV, dtype=torch.bfloat16)
+    act = torch.empty(m, i, device=DEV, dtype=torch.bfloat16)
+    q8 = (torch.zeros(m, i, dtype=torch.int8, device=DEV), torch.zeros(m, i // 32, device=DEV),
+          torch.zeros(m, i // 32, device=DEV))
+    ops.swiglu(gu_bf16=gu, out=act, m=m, i=i, q8=q8)
+    want = ops.quant_q8_1(act)
+    torch.cuda.synchronize()
+    for got, ref in zip(q8, want):
+        assert torch.equal(got, ref)
+    # decode attention: the merge kernel writes the int8 view of the attention output
+    seq_lens, hq, hkv, d = [70, 5, 300], 8, 2, 128
+    B = len(seq_lens)
+    k_cache, v_cache, bt = _make_paged(seq_lens, hkv, d)
+    q = torch.randn(B, hq, d, device=DEV, dtype=torch.bfloat16)
+    sl = torch.tensor(seq_lens, dtype=torch.int32, device=DEV)
+    part_o = torch.empty(B, hq, 8, d, device=DEV, dtype=torch.float32)
+    part_ml = torch.empty(B, hq, 8, 2, device=DEV, dtype=torch.float32)
+    out = torch.empty(B, hq * d, device=DEV, dtype=torch.bfloat16)
+    q8 = (torch.zeros(B, hq * d, dtype=torch.int8, device=DEV), torch.zeros(B, hq * d // 32, device=DEV),
+          torch.zeros(B, hq * d // 32, device=DEV))
+    ops.paged_decode(q, k_cache, v_cache, bt, sl, torch.tensor([4], dtype=torch.int32, device=DEV), part_o, part_ml, out,
+                     batch=B, max_splits=8, scale=1.0 / math.sqrt(d), q8=q8)
+    want = ops.quant_q8_1(out)
+    torch.cuda.synchronize()
+    for got, ref in zip(q8, want):
+        assert torch.equal(got, ref)
+
+
 def test_mmvq_mixed_types_in_one_launch(ops):
     """Q | K | V of a mixed-precision file (Q4_K, Q4_K, Q6_K) and two more combinations as one GEMV
     launch each, against the exact product of the int8 activations with the decoded weights."""
