@@ -281,6 +281,8 @@ def main() -> None:
                 "global_batch": int(statistics.median(batch_sizes)) if batch_sizes else 0,
                 "prompt_len": f"uniform[{args.prompt_min},{args.prompt_max}]", "output_len": args.output_len,
                 "seq_len": ctx, "kv_blocks": eng.model.num_blocks, "kv_block_tokens": 16,
+                "mem_free_gb_end": round(torch.cuda.mem_get_info(dev)[0] / 2**30, 2),
+                "mem_peak_reserved_gb": round(torch.cuda.max_memory_reserved(dev) / 2**30, 2),
                 "cache_note": "per-step inputs (weights + KV, >= 17 GB per GPU) exceed the 126 MB L2",
                 "cuda_graph": cfg.cuda_graph, "comm": ("nccl all-reduce + library GEMMs (baseline path)" if args.comm == "nccl" else
                          "fused peer-memory kernels" if world > 1 else "single GPU"),

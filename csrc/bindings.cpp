@@ -972,6 +972,39 @@ void argmax_combine(const Tensor& vals, const Tensor& idxs, const Tensor& out) {
   check_launch("argmax_combine");
 }
 
+// Vocab-parallel greedy sampling through peer memory (see ArgmaxExchangeParams): `tab_ptrs[o]` is the
+// table of rank o ([2, ranks, max_rows] 64-bit words, zero-initialised), one call per step on every rank.
+void argmax_exchange(const Tensor& logits, int64_t vocab_start, const std::vector<int64_t>& tab_ptrs,
+                     int64_t max_rows, int64_t my_rank, int64_t slot, const Tensor& out, const Tensor& status,
+                     int64_t spin_limit) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.stride(1) == 1,
+              "argmax_exchange: fp32 [rows, V_local] logits");
+  TORCH_CHECK(tab_ptrs.size() >= 1 && tab_ptrs.size() <= 8 && my_rank >= 0 &&
+                  my_rank < static_cast<int64_t>(tab_ptrs.size()) && (slot == 0 || slot == 1),
+              "argmax_exchange: 1..8 ranks, slot 0 or 1");
+  TORCH_CHECK(logits.size(0) <= max_rows && out.scalar_type() == at::kInt && out.numel() >= logits.size(0),
+              "argmax_exchange: rows");
+  oxb::ArgmaxExchangeParams p{};
+  p.logits = logits.data_ptr<float>();
+  p.ld = logits.stride(0);
+  p.V_local = static_cast<int>(logits.size(1));
+  p.vocab_start = static_cast<int>(vocab_start);
+  p.rows = static_cast<int>(logits.size(0));
+  p.max_rows = static_cast<int>(max_rows);
+  p.ranks = static_cast<int>(tab_ptrs.size());
+  p.my_rank = static_cast<int>(my_rank);
+  p.slot = static_cast<int>(slot);
+  for (size_t i = 0; i < tab_ptrs.size(); ++i) {
+    TORCH_CHECK(tab_ptrs[i] % 8 == 0, "argmax_exchange: table alignment");
+    p.tab[i] = reinterpret_cast<unsigned long long*>(tab_ptrs[i]);
+  }
+  p.out_tokens = out.data_ptr<int>();
+  p.status = reinterpret_cast<int*>(status.data_ptr());
+  p.spin_limit = static_cast<uint32_t>(spin_limit > 0 ? spin_limit : 0);
+  oxb::launch_argmax_exchange(p, cur_stream());
+  check_launch("argmax_exchange");
+}
+
 // ---------------------------------------------------------------------------------------------
 // peer memory (CUDA IPC): symmetric buffers that kernels address directly over NVLink
 // ---------------------------------------------------------------------------------------------
@@ -1048,6 +1081,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sample", &sample);
   m.def("argmax", &argmax);
   m.def("argmax_combine", &argmax_combine);
+  m.def("argmax_exchange", &argmax_exchange);
   m.def("ipc_alloc", &ipc_alloc);
   m.def("ipc_free", &ipc_free);
   m.def("ipc_get_handle", &ipc_get_handle);

@@ -224,7 +224,8 @@ int Scheduler::reserve_ahead(int64_t id, int n) {
   for (auto& up : running_) {
     Request* r = up.get();
     if (r->id != id) continue;
-    if (r->phase != Phase::Decode || r->dropped != 0) return 0;
+    // context shift and pruning address blocks by position from the end of the table: no spare blocks there
+    if (r->phase != Phase::Decode || r->dropped != 0 || cfg_.context_shift) return 0;
     const int cap = cfg_.max_blocks_per_seq * kTokensPerBlock;
     n = std::min(n, r->max_new_tokens - r->generated());
     n = std::min(n, cap - 1 - static_cast<int>(r->tokens.size()));

@@ -311,7 +311,53 @@ __global__ void argmax_combine_kernel(const float* vals, const int* idxs, int ra
   out[b] = bi;
 }
 
+__global__ void __launch_bounds__(kThreads) argmax_push_kernel(const ArgmaxExchangeParams p) {
+  __shared__ int s_tok;
+  __shared__ float s_best;
+  const int row = blockIdx.x;
+  block_argmax(p.logits + static_cast<long long>(row) * p.ld, nullptr, p.V_local, &s_tok, &s_best);
+  if (threadIdx.x == 0) {
+    const unsigned long long word = (static_cast<unsigned long long>(f2key(s_best)) << 32) |
+                                    (0xFFFFFFFFu - static_cast<uint32_t>(s_tok + p.vocab_start));
+    const size_t off = (static_cast<size_t>(p.slot) * p.ranks + p.my_rank) * p.max_rows + row;
+#pragma unroll
+    for (int o = 0; o < 8; ++o)
+      if (o < p.ranks)
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p.tab[o] + off), "l"(word) : "memory");
+  }
+}
+
+__global__ void argmax_collect_kernel(const ArgmaxExchangeParams p) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= p.rows) return;
+  unsigned long long* mine = p.tab[p.my_rank] + static_cast<size_t>(p.slot) * p.ranks * p.max_rows + row;
+  const uint32_t limit = p.spin_limit != 0 ? p.spin_limit : (1u << 22);
+  unsigned long long best = 0;
+  for (int r = 0; r < p.ranks; ++r) {
+    unsigned long long* w = mine + static_cast<size_t>(r) * p.max_rows;
+    unsigned long long v = 0;
+    uint32_t it = 0;
+    while (true) {
+      asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(w) : "memory");
+      if (v != 0) break;
+      if (++it > limit) {
+        if (p.status != nullptr) atomicCAS(p.status, 0, 4 /* kStatusPeerFlagTimeout */);
+        break;
+      }
+    }
+    if (v > best) best = v;
+    *w = 0;  // empty again for the slot's next use (two steps from now)
+  }
+  p.out_tokens[row] = best != 0 ? static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(best & 0xFFFFFFFFull)) : 0;
+}
+
 }  // namespace
+
+void launch_argmax_exchange(const ArgmaxExchangeParams& p, cudaStream_t stream) {
+  if (p.rows <= 0) return;
+  argmax_push_kernel<<<p.rows, kThreads, 0, stream>>>(p);
+  argmax_collect_kernel<<<(p.rows + 127) / 128, 128, 0, stream>>>(p);
+}
 
 void launch_sample(const SampleParams& p, int rows, cudaStream_t stream) {
   if (rows <= 0) return;

@@ -729,7 +729,7 @@ class LLMEngine:
         n_run = self.sched.num_running()
         if not 1 <= n_run <= self.cfg.burst_max_batch or self.sched.num_waiting() != 0:
             return 0
-        if self._drafter is not None or self.cfg.h2o_pruning or len(self.requests) != n_run:
+        if self._drafter is not None or self.cfg.h2o_pruning or self.cfg.context_shift or len(self.requests) != n_run:
             return 0
         k = self._burst_k
         for rid, r in self.requests.items():
@@ -879,6 +879,15 @@ class LLMEngine:
     def _gather_logits(self, logits, all_greedy: bool, n_log: int):
         import torch.distributed as dist
 
+        if all_greedy and self.pp is None and os.environ.get("OXB_NCCL_ARGMAX", "0") == "0":
+            # every rank pushes its shard's (value, index) into every rank's table over peer memory and
+            # combines locally: no library collective in a decode step
+            m = self.model
+            m.amax_slot ^= 1
+            ops.argmax_exchange(logits, self.sampled[:n_log], vocab_start=self.rank * m.v_l,
+                                tab_ptrs=m.ws.ptrs("amax"), max_rows=m.max_logits, my_rank=self.rank,
+                                slot=m.amax_slot)
+            return None
         if all_greedy:
             ops.argmax(logits, self.sampled[:n_log], self.sampled_val[:n_log])
             idx = self.sampled[:n_log] + self.rank * self.model.v_l

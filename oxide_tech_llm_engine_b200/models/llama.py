@@ -203,10 +203,13 @@ class DeviceModel:
             "flags": ((128,), "i32"),
         }
         if tp > 1:
+            # vocab-parallel argmax: [slot, source rank, row] 64-bit words (value | index), see ops.argmax_exchange
+            specs["amax"] = ((2, tp, self.max_logits, 2), "i32")
             # receive slabs of the bf16 reduce-scatter: [source rank, rows of this rank, d]
             specs["slab0"] = ((tp, rpr, d), "bf16")
             specs["slab1"] = ((tp, rpr, d), "bf16")
         self._rs_slab = [False, False]
+        self.amax_slot = 1   # slot of the last argmax exchange (alternates; re-armed with the other counters)
         if cfg.is_moe:
             # rows per expert slab; the fp4 scale atoms cover 128 rows, so that path rounds up
             self.cap = (M + 127) // 128 * 128 if weight_mode == "nvfp4" else M
@@ -1001,6 +1004,9 @@ class DeviceModel:
         calls it between steps, with none of its kernels in flight."""
         torch.cuda.synchronize(self.device)
         self.ws.local("flags").zero_()
+        if self.tp > 1:
+            self.ws.local("amax").zero_()
+            self.amax_slot = 1
         self.tickets.zero_()
         if self.cfg.is_moe:
             self.ws.local("cnt").zero_()

@@ -622,3 +622,13 @@ def argmax(logits, out, out_val=None) -> None:
 def argmax_combine(vals, idxs, out) -> None:
     _ext().argmax_combine(vals, idxs, out)
     _bump()
+
+
+def argmax_exchange(logits, out, *, vocab_start: int, tab_ptrs: Sequence[int], max_rows: int, my_rank: int,
+                    slot: int) -> None:
+    """Vocab-parallel greedy sampling without a library collective: every rank stores (value, index) of
+    its shard's argmax as one 64-bit word per row into every rank's table over peer memory (the word is
+    its own arrival flag) and then combines the words of all ranks. `slot` alternates 0 / 1 per call."""
+    _ext().argmax_exchange(logits, vocab_start, list(tab_ptrs), max_rows, my_rank, slot, out, status_word(logits.device),
+                           SPIN_LIMIT)
+    _bump(2)

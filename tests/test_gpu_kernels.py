@@ -847,6 +847,39 @@ def test_argmax_and_sampling(ops):
     torch.testing.assert_close(lp, torch.log(full[toks.long()]), rtol=0, atol=2e-3)
 
 
+def test_argmax_exchange_on_one_rank(ops):
+    """The peer-memory argmax exchange with a single rank: the word table is this GPU's own, both slots
+    give the argmax (lowest index on ties) and leave the table empty; a word that never arrives ends
+    the bounded wait with the peer-flag status instead of hanging."""
+    from oxide_tech_llm_engine_b200.errors import CollectiveTimeout
+
+    torch.manual_seed(13)
+    rows, V, max_rows = 7, 5000, 16
+    logits = torch.randn(rows, V, device=DEV)
+    logits[2, 17] = logits[2, 4000] = 50.0                      # a tie: the lower index wins
+    tab = torch.zeros(2, 1, max_rows, dtype=torch.int64, device=DEV)
+    out = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
+    for slot in (0, 1, 0):
+        ops.argmax_exchange(logits, out, vocab_start=100, tab_ptrs=[tab.data_ptr()], max_rows=max_rows, my_rank=0,
+                            slot=slot)
+        torch.cuda.synchronize()
+        assert torch.equal(out.long(), logits.argmax(-1) + 100) and int(out[2]) == 117
+        assert int(tab.abs().sum()) == 0
+    # two ranks declared, the second never writes: rank 0 gives up after the spin budget
+    tab2 = torch.zeros(2, 2, max_rows, dtype=torch.int64, device=DEV)
+    old = ops.SPIN_LIMIT
+    ops.SPIN_LIMIT = 2000
+    try:
+        ops.argmax_exchange(logits, out, vocab_start=0, tab_ptrs=[tab2.data_ptr(), tab2.data_ptr()], max_rows=max_rows,
+                            my_rank=0, slot=0)
+        torch.cuda.synchronize()
+        with pytest.raises(CollectiveTimeout):
+            ops.check_status()
+    finally:
+        ops.SPIN_LIMIT = old
+    ops.check_status()
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("M,N,K", [(128, 256, 512), (200, 384, 1024), (8, 1024, 4096), (640, 1152, 2048), (130, 200, 272)])
 def test_gemm_fp8_block_scaled(ops, M, N, K):
