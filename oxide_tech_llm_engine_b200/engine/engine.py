@@ -528,6 +528,7 @@ class LLMEngine:
             return {"steps": 0}
         same = total = 0
         worst = 0.0
+        worst_rms, min_cos = 0.0, 1.0
         for _ in range(n_steps):
             plan = self.sched.schedule()
             for e in self.sched.take_events():
@@ -546,12 +547,17 @@ class LLMEngine:
             total += int(n_rows)
             scale_ = float(ref_base[:n_rows].abs().max().clamp_min(1e-6))
             worst = max(worst, float((ref_fused[:n_rows] - ref_base[:n_rows]).abs().max()) / scale_)
+            # per row over this rank's vocabulary shard: relative RMS difference and cosine of the two logit vectors
+            a, b = ref_fused[:n_rows].double(), ref_base[:n_rows].double()
+            worst_rms = max(worst_rms, float(((a - b).pow(2).mean(-1).sqrt() / b.pow(2).mean(-1).sqrt().clamp_min(1e-12)).max()))
+            min_cos = min(min_cos, float(torch.nn.functional.cosine_similarity(a, b, dim=-1).min()))
             for e in self.sched.update(plan, tok_fused):
                 self._deliver(e)
             self.stats["steps"] += 1
             self.stats["decode_tokens"] += plan.n_decode
             self.stats["prefill_tokens"] += plan.prefill_tokens
-        return {"steps": n_steps, "tokens_equal": same, "tokens": total, "max_logit_diff_rel": round(worst, 5)}
+        return {"steps": n_steps, "tokens_equal": same, "tokens": total, "max_logit_diff_rel": round(worst, 5),
+                "max_row_rms_diff_rel": round(worst_rms, 5), "min_row_logit_cosine": round(min_cos, 6)}
 
     def attach_monitor(self, monitor) -> None:
         """`monitor.check()` (parallel.watchdog.RankMonitor) runs before every step: a peer that
