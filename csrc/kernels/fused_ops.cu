@@ -92,6 +92,9 @@ __device__ __forceinline__ void q8_block_store(const float (&y)[V], int8_t* q8, 
 
 // All global loads of a row are issued before the first dependent instruction, so a row costs
 // about one memory round trip however few rows (CTAs) there are.
+// Q8: also write the int8 view of the output rows (a separate instantiation: the extra values in
+// flight would push the register-resident rows of the plain kernel into local memory).
+template <bool Q8>
 __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const FinalizeNormParams p) {
   extern __shared__ float s_h[];  // N floats, used only by the MoE router path
   __shared__ float s_red[32];
@@ -227,9 +230,11 @@ __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const Fi
 #pragma unroll
     for (int d = 0; d < kMaxPeers; ++d)
       if (d < p.n_dst && store_out) *reinterpret_cast<uint4*>(p.out[d] + ooff + c) = o;
-    if (p.q8 != nullptr && store_out) {
-      const long long blk = orow * static_cast<long long>(N >> 5) + (c >> 5);
-      q8_block_store<8>(y, p.q8 + ooff + c, p.q8_d + blk, p.q8_s + blk, (c & 31) == 0);
+    if constexpr (Q8) {
+      if (store_out) {
+        const long long blk = orow * static_cast<long long>(N >> 5) + (c >> 5);
+        q8_block_store<8>(y, p.q8 + ooff + c, p.q8_d + blk, p.q8_s + blk, (c & 31) == 0);
+      }
     }
   }
 
@@ -358,25 +363,35 @@ __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const Fi
 
 // One CTA per token. Thread i handles rotation pair (d, d + D/2) of some head.
 __global__ void __launch_bounds__(256) qkv_rope_append_kernel(const QkvRopeParams p) {
-  extern __shared__ float s_row[];  // (Hq + 2 Hkv) * D floats
-  __shared__ float s_ssq[160];      // per-head sum of squares (Hq + Hkv <= 160)
+  extern __shared__ float s_row[];  // this CTA's heads: heads_per_cta * D floats
+  __shared__ float s_ssq[160];      // per-head reciprocal RMS (indexed by the head's position in this CTA)
   __shared__ float s_sin[128], s_cos[128];  // the token's rotation, shared by every head (D <= 256)
   pdl_launch_dependents();
   pdl_wait();  // the QKV rows come from the kernel before this one
   const int tok = blockIdx.x;
   const int D = p.D, half = D >> 1;
-  const int W = (p.Hq + 2 * p.Hkv) * D;
+  const int n_heads = p.Hq + 2 * p.Hkv;  // Q heads, then K heads, then V heads
+  const int W = n_heads * D;
+  // blockIdx.y selects a contiguous range of heads, so that few tokens still fill the SMs
+  const int hpc = (n_heads + gridDim.y - 1) / gridDim.y;
+  const int h_lo = blockIdx.y * hpc;
+  const int h_hi = h_lo + hpc < n_heads ? h_lo + hpc : n_heads;
+  if (h_lo >= h_hi) return;
+  const int c_lo = h_lo * D, c_hi = h_hi * D;
   const long long roff = static_cast<long long>(tok) * W;
   const int pos = p.positions[tok];
-  // one precise sincos per frequency and token instead of one per (head, frequency)
-  for (int d = threadIdx.x; d < half; d += blockDim.x) {
-    float sn, cs;
-    sincosf(static_cast<float>(pos) * p.inv_freq[d], &sn, &cs);
-    s_sin[d] = sn * p.rope_mscale;
-    s_cos[d] = cs * p.rope_mscale;
+  const int n_rot_heads = p.Hq + p.Hkv;
+  if (h_lo < n_rot_heads) {
+    // one precise sincos per frequency and token instead of one per (head, frequency)
+    for (int d = threadIdx.x; d < half; d += blockDim.x) {
+      float sn, cs;
+      sincosf(static_cast<float>(pos) * p.inv_freq[d], &sn, &cs);
+      s_sin[d] = sn * p.rope_mscale;
+      s_cos[d] = cs * p.rope_mscale;
+    }
   }
 
-  for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+  for (int c = c_lo + threadIdx.x * 4; c < c_hi; c += blockDim.x * 4) {
     float v[4];
     if (p.acc_f32 != nullptr) {
       float4* a = reinterpret_cast<float4*>(const_cast<float*>(p.acc_f32) + roff + c);
@@ -394,40 +409,41 @@ __global__ void __launch_bounds__(256) qkv_rope_append_kernel(const QkvRopeParam
       for (int j = 0; j < 4; ++j) v[j] += __bfloat162float(p.bias[c + j]);
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) s_row[c + j] = v[j];
+    for (int j = 0; j < 4; ++j) s_row[c - c_lo + j] = v[j];
   }
   __syncthreads();
 
-  const int n_rot_heads = p.Hq + p.Hkv;
+  const int r_hi = h_hi < n_rot_heads ? h_hi : n_rot_heads;  // rotated heads of this CTA: [h_lo, r_hi)
   const bool qk_norm = p.q_norm_w != nullptr;
   if (qk_norm) {
     // one warp per head computes the head's mean square
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    for (int h = warp; h < n_rot_heads; h += nw) {
+    for (int h = h_lo + warp; h < r_hi; h += nw) {
       float ss = 0.f;
       for (int d = lane; d < D; d += 32) {
-        const float x = s_row[h * D + d];
+        const float x = s_row[(h - h_lo) * D + d];
         ss += x * x;
       }
       ss = warp_sum(ss);
-      if (lane == 0) s_ssq[h] = rsqrtf(ss / static_cast<float>(D) + p.norm_eps);
+      if (lane == 0) s_ssq[h - h_lo] = rsqrtf(ss / static_cast<float>(D) + p.norm_eps);
     }
     __syncthreads();
   }
 
   const long long slot = p.slot_mapping[tok];
   const bool store_kv = slot >= 0 && slot < p.num_slots;
-  if (slot >= p.num_slots && threadIdx.x == 0) set_status_once(p.status, kStatusBadIndex);
+  if (slot >= p.num_slots && threadIdx.x == 0 && blockIdx.y == 0) set_status_once(p.status, kStatusBadIndex);
   const long long blk = slot >> 4;
   const int off = static_cast<int>(slot & 15);
 
   // rotate Q and K heads
-  for (int i = threadIdx.x; i < n_rot_heads * half; i += blockDim.x) {
-    const int h = i / half, d = i - h * half;
-    float x0 = s_row[h * D + d], x1 = s_row[h * D + d + half];
+  for (int i = threadIdx.x; i < (r_hi - h_lo) * half; i += blockDim.x) {
+    const int lh = i / half, d = i - lh * half;
+    const int h = h_lo + lh;
+    float x0 = s_row[lh * D + d], x1 = s_row[lh * D + d + half];
     if (qk_norm) {
       const __nv_bfloat16* w = h < p.Hq ? p.q_norm_w : p.k_norm_w;
-      const float r = s_ssq[h];
+      const float r = s_ssq[lh];
       x0 = x0 * r * (__bfloat162float(w[d]) + p.norm_w_offset);
       x1 = x1 * r * (__bfloat162float(w[d + half]) + p.norm_w_offset);
     }
@@ -445,11 +461,13 @@ __global__ void __launch_bounds__(256) qkv_rope_append_kernel(const QkvRopeParam
       k[d + half] = __float2bfloat16(y1);
     }
   }
-  if (store_kv) {
-    const float* vrow = s_row + (p.Hq + p.Hkv) * D;
-    for (int i = threadIdx.x; i < p.Hkv * D; i += blockDim.x) {
-      const int kh = i / D, d = i - kh * D;
-      p.v_cache[((blk * p.Hkv + kh) * 16 + off) * D + d] = __float2bfloat16(vrow[i]);
+  if (store_kv && h_hi > n_rot_heads) {
+    // V heads of this CTA: [max(h_lo, n_rot_heads), h_hi)
+    const int v_lo = h_lo > n_rot_heads ? h_lo : n_rot_heads;
+    for (int i = threadIdx.x; i < (h_hi - v_lo) * D; i += blockDim.x) {
+      const int lv = i / D, d = i - lv * D;
+      const int kh = v_lo + lv - n_rot_heads;
+      p.v_cache[((blk * p.Hkv + kh) * 16 + off) * D + d] = __float2bfloat16(s_row[(v_lo + lv - h_lo) * D + d]);
     }
   }
 }
@@ -630,19 +648,31 @@ void launch_finalize_norm(const FinalizeNormParams& p, cudaStream_t stream) {
   if (threads > kNormMaxThreads) threads = kNormMaxThreads;
   if (threads < 32) threads = 32;
   const size_t smem = p.router_w != nullptr ? static_cast<size_t>(p.N) * sizeof(float) : 0;
-  ensure_dynamic_smem(finalize_norm_kernel, smem);
+  ensure_dynamic_smem(finalize_norm_kernel<false>, smem);
+  ensure_dynamic_smem(finalize_norm_kernel<true>, smem);
   // a CTA loops over rows, so any grid is correct; two CTAs per SM keep a second row's loads in
   // flight where registers allow two resident CTAs, and cost nothing where they do not
   const int max_ctas = 2 * sm_count();
   const int grid = p.rows < max_ctas ? p.rows : max_ctas;
-  launch_kernel(finalize_norm_kernel, dim3(grid), dim3(threads), smem, stream, /*pdl=*/true, false, p);
+  if (p.q8 != nullptr)
+    launch_kernel(finalize_norm_kernel<true>, dim3(grid), dim3(threads), smem, stream, /*pdl=*/true, false, p);
+  else
+    launch_kernel(finalize_norm_kernel<false>, dim3(grid), dim3(threads), smem, stream, /*pdl=*/true, false, p);
 }
 
 void launch_qkv_rope_append(const QkvRopeParams& p, cudaStream_t stream) {
   if (p.M <= 0) return;
-  const size_t smem = static_cast<size_t>(p.Hq + 2 * p.Hkv) * p.D * sizeof(float);
+  // heads are split over blockIdx.y until about two CTAs per SM exist (a step of 64 tokens would
+  // otherwise leave more than half of the SMs idle); a CTA keeps at least 4 heads
+  const int n_heads = p.Hq + 2 * p.Hkv;
+  int chunks = (2 * sm_count() + p.M - 1) / p.M;
+  if (chunks > n_heads / 4) chunks = n_heads / 4;
+  if (chunks < 1) chunks = 1;
+  const int hpc = (n_heads + chunks - 1) / chunks;
+  chunks = (n_heads + hpc - 1) / hpc;
+  const size_t smem = static_cast<size_t>(hpc) * p.D * sizeof(float);
   ensure_dynamic_smem(qkv_rope_append_kernel, smem);
-  launch_kernel(qkv_rope_append_kernel, dim3(p.M), dim3(256), smem, stream, /*pdl=*/true, false, p);
+  launch_kernel(qkv_rope_append_kernel, dim3(p.M, chunks), dim3(256), smem, stream, /*pdl=*/true, false, p);
 }
 
 void launch_swiglu(const SwigluParams& p, cudaStream_t stream) {
