@@ -94,7 +94,9 @@ __device__ __forceinline__ void q8_block_store(const float (&y)[V], int8_t* q8, 
 // about one memory round trip however few rows (CTAs) there are.
 // Q8: also write the int8 view of the output rows (a separate instantiation: the extra values in
 // flight would push the register-resident rows of the plain kernel into local memory).
-template <bool Q8>
+// CH: 8-element chunks per thread (1 covers rows of up to 8192 values with 1024 threads: eight fp32
+// values per thread instead of 32 leave the kernel free of spills).
+template <bool Q8, int CH>
 __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const FinalizeNormParams p) {
   extern __shared__ float s_h[];  // N floats, used only by the MoE router path
   __shared__ float s_red[32];
@@ -127,11 +129,11 @@ __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const Fi
   uint32_t rows_done = 0;
   for (int row = blockIdx.x; row < p.rows; row += gridDim.x, ++rows_done) {
   const long long roff = static_cast<long long>(row) * N;
-  float h[kNormMaxChunks][8];
-  uint4 res[kNormMaxChunks], bia[kNormMaxChunks];
+  float h[CH][8];
+  uint4 res[CH], bia[CH];
   // ---- phase 1: issue every load ----
 #pragma unroll
-  for (int ci = 0; ci < kNormMaxChunks; ++ci) {
+  for (int ci = 0; ci < CH; ++ci) {
     const int c = (ci * nthr + threadIdx.x) * 8;
 #pragma unroll
     for (int j = 0; j < 8; ++j) h[ci][j] = 0.f;
@@ -150,16 +152,16 @@ __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const Fi
   if (p.rs_slab != nullptr) {
     // bf16 partial tiles from every source rank (written by peers): L2-coherent loads
     for (int sidx = 0; sidx < p.n_slabs; ++sidx) {
-      uint4 v[kNormMaxChunks];
+      uint4 v[CH];
 #pragma unroll
-      for (int ci = 0; ci < kNormMaxChunks; ++ci) {
+      for (int ci = 0; ci < CH; ++ci) {
         const int c = (ci * nthr + threadIdx.x) * 8;
         v[ci] = make_uint4(0, 0, 0, 0);
         if (c < N)
           v[ci] = __ldcg(reinterpret_cast<const uint4*>(p.rs_slab + sidx * p.slab_stride + roff + c));
       }
 #pragma unroll
-      for (int ci = 0; ci < kNormMaxChunks; ++ci) {
+      for (int ci = 0; ci < CH; ++ci) {
         const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v[ci]);
 #pragma unroll
         for (int j = 0; j < 8; ++j) h[ci][j] += __bfloat162float(e[j]);
@@ -169,7 +171,7 @@ __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const Fi
   // ---- phase 2: combine, re-arm the accumulator, residual out, sum of squares ----
   float ss = 0.f;
 #pragma unroll
-  for (int ci = 0; ci < kNormMaxChunks; ++ci) {
+  for (int ci = 0; ci < CH; ++ci) {
     const int c = (ci * nthr + threadIdx.x) * 8;
     if (c >= N) continue;
     if (p.acc != nullptr) {
@@ -204,7 +206,7 @@ __global__ void __launch_bounds__(kNormMaxThreads) finalize_norm_kernel(const Fi
   const bool store_out = orow >= 0;
   const long long ooff = orow * static_cast<long long>(N);
 #pragma unroll
-  for (int ci = 0; ci < kNormMaxChunks; ++ci) {
+  for (int ci = 0; ci < CH; ++ci) {
     const int c = (ci * nthr + threadIdx.x) * 8;
     if (c >= N) continue;
     float y[8];
@@ -648,16 +650,23 @@ void launch_finalize_norm(const FinalizeNormParams& p, cudaStream_t stream) {
   if (threads > kNormMaxThreads) threads = kNormMaxThreads;
   if (threads < 32) threads = 32;
   const size_t smem = p.router_w != nullptr ? static_cast<size_t>(p.N) * sizeof(float) : 0;
-  ensure_dynamic_smem(finalize_norm_kernel<false>, smem);
-  ensure_dynamic_smem(finalize_norm_kernel<true>, smem);
+  const bool one = static_cast<long long>(threads) * 8 >= p.N;  // one chunk per thread covers the row
+  ensure_dynamic_smem(finalize_norm_kernel<false, 1>, smem);
+  ensure_dynamic_smem(finalize_norm_kernel<true, 1>, smem);
+  ensure_dynamic_smem(finalize_norm_kernel<false, kNormMaxChunks>, smem);
+  ensure_dynamic_smem(finalize_norm_kernel<true, kNormMaxChunks>, smem);
   // a CTA loops over rows, so any grid is correct; two CTAs per SM keep a second row's loads in
   // flight where registers allow two resident CTAs, and cost nothing where they do not
   const int max_ctas = 2 * sm_count();
   const int grid = p.rows < max_ctas ? p.rows : max_ctas;
-  if (p.q8 != nullptr)
-    launch_kernel(finalize_norm_kernel<true>, dim3(grid), dim3(threads), smem, stream, /*pdl=*/true, false, p);
+  if (p.q8 != nullptr && one)
+    launch_kernel(finalize_norm_kernel<true, 1>, dim3(grid), dim3(threads), smem, stream, /*pdl=*/true, false, p);
+  else if (p.q8 != nullptr)
+    launch_kernel(finalize_norm_kernel<true, kNormMaxChunks>, dim3(grid), dim3(threads), smem, stream, true, false, p);
+  else if (one)
+    launch_kernel(finalize_norm_kernel<false, 1>, dim3(grid), dim3(threads), smem, stream, /*pdl=*/true, false, p);
   else
-    launch_kernel(finalize_norm_kernel<false>, dim3(grid), dim3(threads), smem, stream, /*pdl=*/true, false, p);
+    launch_kernel(finalize_norm_kernel<false, kNormMaxChunks>, dim3(grid), dim3(threads), smem, stream, true, false, p);
 }
 
 void launch_qkv_rope_append(const QkvRopeParams& p, cudaStream_t stream) {
