@@ -51,11 +51,25 @@ def run_workload(eng, prompts, out_lens, *, greedy=True, label=""):
     tpot = [(r.t_last_token - r.t_first_token) / (r.n_generated - 1) for r in reqs
             if r.n_generated > 1 and r.t_first_token is not None]
     gen = sum(r.n_generated for r in reqs)
-    return {"workload": label, "requests": len(reqs), "generated_tokens": gen, "wall_s": round(wall, 3),
-            "tokens_per_s": round(gen / wall, 1), "steps": steps,
-            "ttft_p50_ms": round(_pct(ttft, 50) * 1e3, 2), "ttft_p99_ms": round(_pct(ttft, 99) * 1e3, 2),
-            "tpot_p50_ms": round(_pct(tpot, 50) * 1e3, 3) if tpot else None,
-            "prefill_tokens": int(eng.stats["prefill_tokens"] - pre0)}
+    out = {"workload": label, "requests": len(reqs), "generated_tokens": gen, "wall_s": round(wall, 3),
+           "tokens_per_s": round(gen / wall, 1), "steps": steps,
+           "ttft_p50_ms": round(_pct(ttft, 50) * 1e3, 2), "ttft_p99_ms": round(_pct(ttft, 99) * 1e3, 2),
+           "tpot_p50_ms": round(_pct(tpot, 50) * 1e3, 3) if tpot else None,
+           "prefill_tokens": int(eng.stats["prefill_tokens"] - pre0)}
+    # Prefill arithmetic of the whole job (all ranks), when every prompt token was computed (no prefix hits):
+    # causal attention 4 * D * Hq * L^2 / 2 per layer and prompt, projections 2 * active parameters per token.
+    # Divided by the time until the last first token, which also contains the decode steps that were
+    # interleaved with the prefill chunks: a lower bound of the sustained prefill rate.
+    mc = getattr(eng, "model_cfg", None)
+    lens = [len(p) for p in prompts]
+    if mc is not None and ttft and out["prefill_tokens"] == sum(lens):
+        attn = sum(2.0 * mc.head_dim * mc.n_heads * mc.n_layers * float(n) * n for n in lens)
+        proj = 2.0 * mc.active_params() * sum(lens)
+        t_pre = max(ttft)
+        out["prompt_attention_tflop"] = round(attn / 1e12, 2)
+        out["prefill_attention_tflops_lower_bound"] = round(attn / 1e12 / t_pre, 1)
+        out["prefill_model_tflops_lower_bound"] = round((attn + proj) / 1e12 / t_pre, 1)
+    return out
 
 
 def config1(args) -> dict:
