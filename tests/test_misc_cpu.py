@@ -220,3 +220,29 @@ def test_fuse_quant_rows_stacks_packed_matrices():
     np.testing.assert_array_equal(got, want)
     other = QuantLinear("Q8_0", quants.quantize_2d("Q8_0", mats[0]), 8, K, torch.device("cpu"))
     assert fuse_quant_rows([lins[0], other]) is None          # different block types are not stacked
+
+
+def test_decode_gemm_configs_respect_the_kernel_limits():
+    """`ops.pick_decode_cfg` for the shapes of the serving configurations (70B at TP 1..8, 8B, Mixtral
+    attention): one wave of work items, no more splits than the in-kernel fix-up can land, tiles that
+    divide N where the SwiGLU epilogue needs it. A violation would only show as a launch error on a GPU."""
+    from oxide_tech_llm_engine_b200 import ops
+
+    sms = 148
+    shapes = []
+    for tp in (1, 2, 4, 8):
+        shapes += [(256, 2 * 28672 // tp, 8192, True), (256, 8192, 28672 // tp, False),
+                   (256, (64 + 16) * 128 // tp, 8192, False), (256, 8192, 8192 // tp, False)]
+    shapes += [(192, 2 * 14336, 4096, True), (136, 4096, 14336, False), (256, 6144, 4096, False), (129, 128256, 4096, False)]
+    for m, n, k, swiglu in shapes:
+        bn, mt, sp = ops.pick_decode_cfg(m, n, k, swiglu=swiglu, sms=sms)
+        assert bn in (64, 128, 256) and mt == 2 and sp >= 1, (m, n, k, bn, mt, sp)
+        tiles = -(-n // bn)
+        kb = -(-k // 64)
+        if sp > 1:
+            assert tiles * sp <= sms, (m, n, k, bn, sp)
+            assert sp <= ops.max_fixup_splits(bn, mt, swiglu), (m, n, k, bn, sp)
+            assert -(-kb // -(-kb // sp)) == sp            # the launcher's rounding keeps this split count
+        if swiglu:
+            assert n % bn == 0
+    assert ops.pick_decode_cfg(100, 4096, 4096)[1] == 1    # up to 128 rows: one 128-row tile per weight tile
