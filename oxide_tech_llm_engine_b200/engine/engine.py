@@ -654,7 +654,11 @@ class LLMEngine:
         if cfg.kv_host_blocks > 0 and cfg.enable_radix and self.pp is None:
             from .kv_tiers import HierarchicalKvCache
 
-            self.kv_tier = HierarchicalKvCache(cfg.kv_host_blocks, cfg.kv_storage_blocks, cfg.kv_storage_dir)
+            # every rank keeps its own shard of the KV heads: its files must not meet another rank's
+            sdir = cfg.kv_storage_dir
+            if sdir and self.world > 1:
+                sdir = os.path.join(sdir, f"rank{self.rank}")
+            self.kv_tier = HierarchicalKvCache(cfg.kv_host_blocks, cfg.kv_storage_blocks, sdir)
             self.sched.record_evictions(True)
 
     def _demote_evicted(self) -> None:
