@@ -280,6 +280,42 @@ def test_scheduler_reserve_ahead_holds_blocks_for_a_decode_burst(H):
     assert ok and s.num_free_blocks() == 12
 
 
+def test_radix_eviction_log_and_adoption(H):
+    """The two hooks of the KV tiers: evictions are logged with the whole token prefix their blocks
+    complete, and `radix_adopt` turns a prefix back into cached blocks that the next admission hits."""
+    sc = H.SchedulerConfig()
+    sc.num_blocks, sc.max_num_seqs, sc.max_blocks_per_seq, sc.enable_radix = 16, 2, 16, True
+    s = H.Scheduler(sc)
+    s.record_evictions(True)
+    a = np.arange(100, 100 + 70, dtype=np.int32)            # 4 full blocks + 6 tokens
+    s.add_request(1, a, 2, [], True)
+    _ = _drain(s, H)
+    assert s.radix_stats()["cached_blocks"] == 4 and s.radix_cached_blocks(a[:64]) == 4
+    assert s.take_evicted() == []
+    # two other prompts need the pool: the cached prefix has to go
+    for rid, base in ((2, 1000), (3, 2000)):
+        s.add_request(rid, np.arange(base, base + 120, dtype=np.int32), 2, [], True)
+        _ = _drain(s, H)
+    ev = s.take_evicted()
+    gone = [(np.asarray(t).tolist(), first, list(blocks)) for t, first, blocks in ev if np.asarray(t)[0] == 100]
+    assert gone, ev
+    covered = set()
+    for toks, first, blocks in gone:
+        assert len(toks) % 16 == 0 and toks == a[:len(toks)].tolist()      # the prefix up to the end of the leaf
+        assert len(toks) // 16 == first + len(blocks)
+        covered.update(range(first, first + len(blocks)))
+    assert covered == {0, 1, 2, 3} and s.radix_cached_blocks(a[:64]) == 0
+    # adoption: three blocks come back (the pool is asked for exactly three)
+    free = s.num_free_blocks()
+    ids = s.radix_adopt(a[:48], 3)
+    assert len(ids) == 3 and len(set(ids)) == 3 and s.num_free_blocks() == free - 3
+    assert s.radix_cached_blocks(a[:64]) == 3 and s.radix_adopt(a[:48], 3) == []   # already there
+    s.add_request(4, a, 1, [], True)
+    plan = s.schedule()
+    assert plan.n_prefill == 1 and int(plan.q_lens[0]) == 70 - 48           # only the uncached tail is computed
+    assert [int(b) for b in plan.prefill_block_tables.reshape(-1)[:3]] == [int(b) for b in ids]
+
+
 def test_scheduler_fault_injection_isolated(H):
     c = H.SchedulerConfig()
     c.num_blocks = 32
