@@ -45,6 +45,8 @@ class RequestState:
     output: list = field(default_factory=list)
     finished: bool = False
     finish_reason: str = ""
+    spec: object = None        # AdaptiveSpeculator of this request (speculative decoding)
+    n_drafted: int = 0         # drafts attached to the step in flight
 
 
 @dataclass
@@ -633,6 +635,7 @@ class LLMEngine:
         if self.cfg.h2o_pruning and plan.n_decode:
             self._h2o_prune(plan)
         if self._drafter is not None:
+            self._record_acceptance(events[len(early):])
             self._attach_drafts()
         if time.perf_counter() - t0 > self.cfg.step_deadline_s:
             self.stats["degraded"] = True
@@ -1014,9 +1017,32 @@ class LLMEngine:
             hist = self.sched.request_tokens(rid)
             if hist is None:
                 continue
-            d = self._drafter.propose(hist)
+            if r.spec is None:
+                from .spec_decode import AdaptiveSpeculator
+
+                r.spec = AdaptiveSpeculator(k_min=1, k_max=max(1, self.cfg.draft_tokens))
+            # the draft length follows the request's own rolling acceptance rate
+            d = self._drafter.propose(hist)[:r.spec.k]
+            r.n_drafted = len(d)
             if d:
                 self.sched.set_drafts(rid, d)
+
+    def _record_acceptance(self, events) -> None:
+        """After a verify step: a request that had n drafts attached and got t tokens back accepted t - 1
+        of them (the last token is the model's own choice after the accepted prefix)."""
+        got: dict = {}
+        for e in events:
+            if int(e.token) >= 0:
+                got[int(e.req_id)] = got.get(int(e.req_id), 0) + 1
+        for rid, n in got.items():
+            r = self.requests.get(rid)
+            if r is None or r.spec is None or r.n_drafted <= 0:
+                continue
+            acc = min(max(n - 1, 0), r.n_drafted)
+            r.spec.record(r.n_drafted, acc)
+            self.stats["spec_proposed"] = self.stats.get("spec_proposed", 0) + r.n_drafted
+            self.stats["spec_accepted"] = self.stats.get("spec_accepted", 0) + acc
+            r.n_drafted = 0
 
     # ------------------------------------------------------------------ convenience
     def generate(self, prompts: list, params: Optional[SamplingParams] = None, max_steps: int = 1 << 30):

@@ -102,6 +102,14 @@ def test_speculative_ngram_equals_plain_greedy():
     spec = eng.generate([rep], sp)[0]
     assert spec == ReferenceModel(mc, src).generate_greedy(rep, 20)
     assert eng.stats["steps"] > 0
+    # the draft length of the request followed its acceptance rate (AdaptiveSpeculator), and the
+    # counters add up: never more accepted than proposed, fewer steps than tokens when drafts hit
+    r = eng.requests[max(eng.requests)]
+    assert r.spec is not None and 1 <= r.spec.k <= 5
+    prop, acc = eng.stats.get("spec_proposed", 0), eng.stats.get("spec_accepted", 0)
+    assert prop > 0 and 0 <= acc <= prop and r.spec.proposed == prop and r.spec.accepted == acc
+    if acc:
+        assert eng.stats["steps"] < 20 + 3
 
 
 def test_sampling_seed_determinism_and_stop_ids():
