@@ -40,6 +40,7 @@ class EngineConfig:
     kv_host_blocks: int = 0             # > 0: blocks the prefix cache evicts are kept in host memory (tier 2) and promoted back on a hit
     kv_storage_blocks: int = 0          # ... and from there to files under kv_storage_dir (tier 3)
     kv_storage_dir: Optional[str] = None
+    kv_host_quant: str = "none"         # none | q8: demoted blocks are kept as int8 codes with one scale per layer and tensor
     cuda_graph: bool = True
     graph_buckets: tuple = (1, 2, 4, 8, 16, 32, 64, 128, 256)
     max_splits: int = 16

@@ -678,7 +678,20 @@ class LLMEngine:
         idx = torch.as_tensor(ids, dtype=torch.long, device=kc[0].device)
         k = torch.stack([c.index_select(0, idx) for c in kc], dim=1)   # [n, layers, hkv, 16, D]
         v = torch.stack([c.index_select(0, idx) for c in vc], dim=1)
-        if k.dtype == torch.bfloat16:                                   # carried as 16-bit patterns
+        scales = None
+        if self.cfg.kv_host_quant == "q8":
+            # int8 codes with one scale per (block, layer, K or V), made where the blocks live: the
+            # transfer and the host copy shrink to half of bf16 (reference: QuantizedKvBlock q8,
+            # oxide-alloc/src/kv_advanced.rs:39-175, there one scale per tensor)
+            def q8(x):
+                xf = x.float()
+                sc = xf.abs().amax(dim=(2, 3, 4)) / 127.0                   # [n, layers]
+                codes = torch.round(xf / sc.clamp_min(1e-30)[:, :, None, None, None]).clamp_(-127, 127).to(torch.int8)
+                return codes, sc
+            k, ks = q8(k)
+            v, vs = q8(v)
+            scales = torch.stack([ks, vs], dim=1).cpu().numpy()              # [n, 2, layers]
+        elif k.dtype == torch.bfloat16:                                 # carried as 16-bit patterns
             k, v = k.view(torch.int16), v.view(torch.int16)
         k, v = k.cpu().numpy(), v.cpu().numpy()
         self.stats["d2h_bytes"] += k.nbytes + v.nbytes
@@ -688,7 +701,7 @@ class LLMEngine:
             for j in range(len(blocks)):
                 b0 = (first + j) * self.block
                 self.kv_tier.demote(KvBlockPayload(hashes[first + j], np.asarray(toks[b0:b0 + self.block], dtype=np.int32),
-                                                   k[i], v[i]))
+                                                   k[i], v[i], 0, None if scales is None else scales[i]))
                 i += 1
         self.stats["kv_demoted_blocks"] = self.stats.get("kv_demoted_blocks", 0) + len(ids)
 
@@ -720,7 +733,11 @@ class LLMEngine:
         kc, vc = self._kv_caches()
         k = torch.from_numpy(np.stack([p.k for p in found], axis=1))   # [layers, n, hkv, 16, D]
         v = torch.from_numpy(np.stack([p.v for p in found], axis=1))
-        if kc[0].dtype == torch.bfloat16:
+        if found[0].scales is not None:                                  # int8 codes: expand where the blocks go
+            sc = torch.from_numpy(np.stack([p.scales for p in found], axis=0)).to(kc[0].device)   # [n, 2, layers]
+            k = (k.to(kc[0].device).float() * sc[:, 0].t()[:, :, None, None, None]).to(kc[0].dtype)
+            v = (v.to(kc[0].device).float() * sc[:, 1].t()[:, :, None, None, None]).to(kc[0].dtype)
+        elif kc[0].dtype == torch.bfloat16:
             k, v = k.view(torch.bfloat16), v.view(torch.bfloat16)
         k, v = k.to(kc[0].device), v.to(kc[0].device)
         idx = torch.as_tensor(ids, dtype=torch.long, device=kc[0].device)

@@ -47,9 +47,10 @@ class KvBlockPayload:
     """One KV block in transit between tiers or ranks."""
     prefix_hash: int
     tokens: np.ndarray          # [16] int32
-    k: np.ndarray               # [layers, hkv, 16, D]; float16, float32, or bf16 bit patterns as int16
+    k: np.ndarray               # [layers, hkv, 16, D]; float16, float32, bf16 bit patterns as int16, or int8 codes
     v: np.ndarray
     checksum: int = 0
+    scales: Optional[np.ndarray] = None   # [2, layers] fp32 (K row, V row) when k / v hold int8 codes: value = code * scale
 
     def compute_checksum(self) -> int:
         s = int(self.tokens.astype(np.int64).sum())
@@ -65,7 +66,8 @@ class KvBlockPayload:
 
     def to_bytes(self) -> bytes:
         hdr = json.dumps({"hash": self.prefix_hash, "checksum": self.checksum, "kshape": list(self.k.shape),
-                          "dtype": str(self.k.dtype)}).encode()
+                          "dtype": str(self.k.dtype),
+                          "scales": None if self.scales is None else np.asarray(self.scales, np.float32).tolist()}).encode()
         return len(hdr).to_bytes(4, "little") + hdr + self.tokens.astype(np.int32).tobytes() + \
             np.ascontiguousarray(self.k).tobytes() + np.ascontiguousarray(self.v).tobytes()
 
@@ -81,7 +83,9 @@ class KvBlockPayload:
         dt = np.dtype(hdr.get("dtype", "float16"))
         k = np.frombuffer(b, dtype=dt, count=cnt, offset=off).reshape(shape)
         v = np.frombuffer(b, dtype=dt, count=cnt, offset=off + dt.itemsize * cnt).reshape(shape)
-        p = cls(hdr["hash"], toks.copy(), k.copy(), v.copy(), hdr["checksum"])
+        sc = hdr.get("scales")
+        p = cls(hdr["hash"], toks.copy(), k.copy(), v.copy(), hdr["checksum"],
+                None if sc is None else np.asarray(sc, dtype=np.float32))
         if not p.verify():
             raise EngineError("KV block payload failed its checksum")
         return p

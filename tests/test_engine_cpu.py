@@ -417,3 +417,11 @@ def test_kv_blocks_evicted_from_the_prefix_cache_come_back_from_the_host_tier(tm
     t = eng.kv_tier.stats
     assert t["demoted_to_storage"] > 0 and t["storage_hits"] + t["host_hits"] >= 6
     eng.close()
+    # the same with int8 codes in the lower tiers (one scale per layer and tensor): same bookkeeping, a quarter
+    # of the fp32 bytes, and KV that is close enough for the continuation to start the same way
+    q, first3, again3, cost3 = run(kv_host_blocks=64, kv_host_quant="q8")
+    assert first3 == first and cost3 == 100 - 6 * 16 and q.stats.get("kv_promoted_blocks", 0) == 6
+    held = next(iter(q.kv_tier.host.values()))
+    assert held.k.dtype == np.int8 and held.scales.shape == (2, mc.n_layers)
+    assert again3[:2] == first[:2]
+    q.close()
