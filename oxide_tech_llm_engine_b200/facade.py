@@ -46,6 +46,18 @@ class EngineBuilder:
         self._kw.update(speculative=mode, draft_tokens=draft_tokens)
         return self
 
+    def kv_tiers(self, host_blocks: int, storage_dir: Optional[str] = None, storage_blocks: int = 0,
+                 quant: str = "none") -> "EngineBuilder":
+        """Blocks the prefix cache evicts go to host memory (and files) and come back on a hit."""
+        self._kw.update(kv_host_blocks=int(host_blocks), kv_storage_dir=storage_dir,
+                        kv_storage_blocks=int(storage_blocks), kv_host_quant=quant)
+        return self
+
+    def decode_burst(self, steps: int, max_batch: int = 8) -> "EngineBuilder":
+        """Small greedy batches decode `steps` tokens per host round trip (in-graph step advance)."""
+        self._kw.update(decode_burst=int(steps), burst_max_batch=int(max_batch))
+        return self
+
     def option(self, **kw) -> "EngineBuilder":
         self._kw.update(kw)
         return self

@@ -177,6 +177,10 @@ def test_facade_builder_transaction_and_ascii_mask():
     eng.close()
     with _pt.raises(ValueError):
         oxb.Engine.builder().backend("rocm")
+    cfg = (oxb.Engine.builder().model("tiny").kv_tiers(64, "/tmp/kv", 128, quant="q8").decode_burst(8, 4)
+           .speculative("ngram", 4).config())
+    assert (cfg.kv_host_blocks, cfg.kv_storage_dir, cfg.kv_storage_blocks, cfg.kv_host_quant) == (64, "/tmp/kv", 128, "q8")
+    assert (cfg.decode_burst, cfg.burst_max_batch, cfg.speculative, cfg.draft_tokens) == (8, 4, "ngram", 4)
 
     H = host_ext()
     pool = H.BlockPool(4)
