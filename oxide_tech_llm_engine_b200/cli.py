@@ -64,6 +64,9 @@ def add_common(p: argparse.ArgumentParser) -> None:
     p.add_argument("--kv-device-blocks", type=int, default=0)
     p.add_argument("--kv-host-blocks", type=int, default=8192)
     p.add_argument("--kv-storage-blocks", type=int, default=32768)
+    p.add_argument("--kv-storage-dir", default=None, help="directory of the file tier behind the host KV tier (none: host tier only)")
+    p.add_argument("--kv-host-quant", default="none", choices=["none", "q8"], help="keep demoted KV blocks as int8 codes")
+    p.add_argument("--decode-burst", type=int, default=0, help="decode steps per host round trip for small greedy batches")
     p.add_argument("--temp", type=float, default=0.7)
     p.add_argument("--top-p", type=float, default=0.95)
     p.add_argument("--min-p", type=float, default=0.05)
@@ -144,7 +147,8 @@ def engine_config_from_args(args) -> EngineConfig:
         max_num_seqs=args.max_slots, num_kv_blocks=args.kv_device_blocks, seed=args.seed, backend=be,
         weight_mode=args.weights, speculative=spec, draft_tokens=args.draft_tokens, tp=args.tp, dp=args.dp,
         max_num_batched_tokens=args.max_batched_tokens, cuda_graph=not args.no_cuda_graph,
-        enable_radix=not args.no_radix)
+        enable_radix=not args.no_radix, kv_host_blocks=args.kv_host_blocks, kv_storage_blocks=args.kv_storage_blocks,
+        kv_storage_dir=args.kv_storage_dir, kv_host_quant=args.kv_host_quant, decode_burst=args.decode_burst)
 
 
 def sampling_from_args(args):

@@ -712,7 +712,7 @@ class LLMEngine:
         from .kv_tiers import prefix_hashes
 
         n_full = (int(toks.size) - 1) // self.block          # the last token is always computed
-        if n_full <= 0:
+        if n_full <= 0 or not (self.kv_tier.host or self.kv_tier.storage):
             return
         have = int(self.sched.radix_cached_blocks(toks[:n_full * self.block]))
         if have >= n_full:

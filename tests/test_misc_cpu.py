@@ -52,6 +52,11 @@ def test_cli_flags_and_normalisation():
     assert a.model == "x.gguf" and a.n_gpu_layers == 20 and a.ctx_size == 4096 and a.greedy and a.max_tokens == 5
     cfg = engine_config_from_args(a)
     assert cfg.backend == "cpu" and cfg.max_num_seqs == 8 and cfg.speculative == "ngram" and cfg.ctx_size == 4096
+    # the KV tier flags reach the engine (defaults of the reference: 8192 host blocks, 32768 storage blocks)
+    assert cfg.kv_host_blocks == 8192 and cfg.kv_storage_blocks == 32768 and cfg.kv_storage_dir is None
+    t = engine_config_from_args(parse_args(["-m", "x.gguf", "-b", "cpu", "--kv-host-blocks", "16", "--kv-storage-dir", "/tmp/kv",
+                                            "--kv-host-quant", "q8", "--decode-burst", "4"]))
+    assert (t.kv_host_blocks, t.kv_storage_dir, t.kv_host_quant, t.decode_burst) == (16, "/tmp/kv", "q8", 4)
     s = parse_args(["server", "--port", "9000", "-m", "tiny", "-b", "cpu"])
     assert s.command == "server" and s.port == 9000
     d = parse_args([])
