@@ -117,8 +117,15 @@ class HierarchicalKvCache:
             self.stats["dropped"] += 1
             return
         path = os.path.join(self.dir, f"{h:016x}.kvb")
-        with open(path, "wb") as f:
-            f.write(p.to_bytes())
+        try:
+            tmp = f"{path}.{os.getpid()}.tmp"
+            with open(tmp, "wb") as f:
+                f.write(p.to_bytes())
+            os.replace(tmp, path)          # never a half-written file under the final name
+        except OSError:
+            self.stats["dropped"] += 1
+            self.stats["storage_errors"] = self.stats.get("storage_errors", 0) + 1
+            return
         self.storage[h] = path
         self.stats["demoted_to_storage"] += 1
         while len(self.storage) > self.storage_cap:
@@ -136,9 +143,16 @@ class HierarchicalKvCache:
             return self.host[h]
         path = self.storage.pop(h, None)
         if path is not None:
-            with open(path, "rb") as f:
-                p = KvBlockPayload.from_bytes(f.read())
-            os.unlink(path)
+            try:
+                with open(path, "rb") as f:
+                    p = KvBlockPayload.from_bytes(f.read())
+                os.unlink(path)
+            except (OSError, EngineError, ValueError):
+                # the file is gone or damaged (another process cleaned the directory, a torn write):
+                # the block is simply not cached any more and the prompt is prefilled
+                self.stats["misses"] += 1
+                self.stats["storage_errors"] = self.stats.get("storage_errors", 0) + 1
+                return None
             self.stats["storage_hits"] += 1
             self.demote(p)  # promoted one tier up
             return p

@@ -89,6 +89,24 @@ def test_hierarchical_tiers_and_payload(tmp_path):
     with pytest.raises(EngineError):
         kv_tiers.KvBlockPayload.from_bytes(bytes(bad))
     assert kv_tiers.KvBlockPayload.from_bytes(blob).verify()
+    # a file of the storage tier that vanished or was damaged is a miss, not an error
+    c2 = kv_tiers.HierarchicalKvCache(host_blocks=1, storage_blocks=4, storage_dir=str(tmp_path / "t3"))
+    for p in (mk(0), mk(1), mk(2)):
+        c2.demote(p)
+    paths = list(c2.storage.values())
+    assert len(paths) == 2
+    os.unlink(paths[0])
+    with open(paths[1], "r+b") as f:
+        f.seek(-1, 2)
+        f.write(b"\x00" if open(paths[1], "rb").read()[-1:] != b"\x00" else b"\x01")
+    assert c2.lookup(hs[0]) is None and c2.lookup(hs[1]) is None
+    assert c2.stats["storage_errors"] == 2 and c2.stats["storage_hits"] == 0
+    # int8 payloads with per-layer scales survive the file round trip
+    q = kv_tiers.KvBlockPayload(hs[3], toks[48:64].copy(), rng.integers(-127, 127, (2, 2, 16, 8)).astype(np.int8),
+                                rng.integers(-127, 127, (2, 2, 16, 8)).astype(np.int8), 0,
+                                np.asarray([[0.5, 0.25], [1.5, 2.0]], np.float32)).seal()
+    back = kv_tiers.KvBlockPayload.from_bytes(q.to_bytes())
+    assert back.k.dtype == np.int8 and np.array_equal(back.k, q.k) and np.array_equal(back.scales, q.scales)
 
 
 def test_quantized_kv_blocks_context_shift_registry(tmp_path):
