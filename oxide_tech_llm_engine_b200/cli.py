@@ -246,15 +246,21 @@ def load_model(name: str, path: Optional[str], cfg: EngineConfig):
 
         if cfg.tp != 1:
             raise ConfigError("--dp replicas are built for tp = 1 (one GPU per replica in this process)")
+        import dataclasses
+        import os
+
         handles = []
         for i in range(cfg.dp):
+            # every replica keeps its own KV file tier (same prefixes, different block pools and lifetimes)
+            rcfg = cfg if not cfg.kv_storage_dir else dataclasses.replace(
+                cfg, kv_storage_dir=os.path.join(cfg.kv_storage_dir, f"replica{i}"))
             if cfg.backend == "cpu":
-                eng = LLMEngine(cfg, mc, weights=src)
+                eng = LLMEngine(rcfg, mc, weights=src)
             else:
                 if i >= torch.cuda.device_count():
                     raise ConfigError(f"--dp {cfg.dp} needs {cfg.dp} GPUs, {torch.cuda.device_count()} visible")
                 with torch.cuda.device(i):
-                    eng = LLMEngine(cfg, mc, weights=src, device=torch.device("cuda", i))
+                    eng = LLMEngine(rcfg, mc, weights=src, device=torch.device("cuda", i))
             eng.set_tokenizer(tok)
             handles.append(EngineHandle(eng))
         return LoadedModel(name, path, DpHandle(handles), tok, mc)
