@@ -181,7 +181,22 @@ def create_app(manager, *, allow_queueing: bool = True) -> FastAPI:
                 f"oxide_prefill_tokens_total{lab} {eng.stats['prefill_tokens']}",
                 f"oxide_engine_steps_total{lab} {eng.stats['steps']}",
                 f"oxide_preemptions_total{lab} {eng.sched.preemptions()}",
+                f"oxide_graph_replays_total{lab} {eng.stats.get('graph_replays', 0)}",
+                f"oxide_burst_steps_total{lab} {eng.stats.get('burst_steps', 0)}",
+                f"oxide_spec_proposed_total{lab} {eng.stats.get('spec_proposed', 0)}",
+                f"oxide_spec_accepted_total{lab} {eng.stats.get('spec_accepted', 0)}",
+                f"oxide_h2o_pruned_blocks_total{lab} {eng.stats.get('h2o_pruned_blocks', 0)}",
+                f"oxide_context_shifts_total{lab} {eng.sched.context_shifts()}",
+                f"oxide_kv_demoted_blocks_total{lab} {eng.stats.get('kv_demoted_blocks', 0)}",
+                f"oxide_kv_promoted_blocks_total{lab} {eng.stats.get('kv_promoted_blocks', 0)}",
+                f"oxide_device_faults_total{lab} {eng.stats.get('device_faults', 0)}",
             ]
+            tier = getattr(eng, "kv_tier", None)
+            if tier is not None:
+                lines += [f"oxide_kv_tier_host_blocks{lab} {len(tier.host)}",
+                          f"oxide_kv_tier_storage_blocks{lab} {len(tier.storage)}",
+                          f"oxide_kv_tier_host_hits_total{lab} {tier.stats['host_hits']}",
+                          f"oxide_kv_tier_storage_hits_total{lab} {tier.stats['storage_hits']}"]
         lines += [
             f"oxide_requests_total {metrics.requests}",
             f"oxide_ttft_seconds_p50 {Metrics.pct(metrics.ttft, 50):.6f}",

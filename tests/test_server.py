@@ -28,7 +28,9 @@ def test_health_metrics_models(client):
     assert r.status_code == 200 and r.text == "Oxide-Tech-LLM-Engine OK"
     m = client.get("/metrics")
     assert m.headers["content-type"].startswith("text/plain")
-    for g in ("oxide_up 1", "oxide_active_inference_slots 0", "oxide_max_inference_slots 4", "oxide_kv_blocks_free"):
+    for g in ("oxide_up 1", "oxide_active_inference_slots 0", "oxide_max_inference_slots 4", "oxide_kv_blocks_free",
+              "oxide_context_shifts_total", "oxide_spec_accepted_total", "oxide_kv_promoted_blocks_total",
+              "oxide_burst_steps_total", "oxide_device_faults_total"):
         assert g in m.text
     ids = [d["id"] for d in client.get("/v1/models").json()["data"]]
     assert "tiny" in ids and "default-model" in ids
