@@ -32,6 +32,28 @@ std::vector<int32_t> from_array(const py::array_t<int32_t, py::array::c_style | 
 PYBIND11_MODULE(oxb_host, m) {
   m.doc() = "C++ host runtime of the B200-native Oxide engine";
   m.attr("TOKENS_PER_BLOCK") = kTokensPerBlock;
+  // Chained FNV-1a hash of every whole block of a token list: hash_i = fnv1a(bytes of block i, seeded
+  // with offset_basis ^ hash_{i-1}); the identity of the prefix that a KV block completes (KV tiers).
+  m.def("prefix_hashes", [](py::array_t<int32_t, py::array::c_style | py::array::forcecast> tokens, int block) {
+    const int32_t* t = tokens.data();
+    const py::ssize_t n = tokens.size();
+    py::list out;
+    if (block <= 0) return out;
+    uint64_t prev = 0;
+    for (py::ssize_t i = 0; i + block <= n; i += block) {
+      uint64_t h = 0xCBF29CE484222325ull ^ prev;
+      for (int j = 0; j < block; ++j) {
+        const uint32_t v = static_cast<uint32_t>(t[i + j]);
+        for (int b = 0; b < 4; ++b) {
+          h ^= (v >> (8 * b)) & 0xFFu;
+          h *= 0x100000001B3ull;
+        }
+      }
+      out.append(py::int_(h));
+      prev = h;
+    }
+    return out;
+  });
 
   py::class_<BlockPool>(m, "BlockPool")
       .def(py::init<int>())

@@ -35,6 +35,13 @@ def fnv1a_chain(prev: int, tokens) -> int:
 
 
 def prefix_hashes(tokens, block: int = 16) -> list[int]:
+    """Chained hash of every whole block of `tokens` (native when the host runtime is built)."""
+    try:
+        from .._build import host_ext
+
+        return [int(h) for h in host_ext().prefix_hashes(np.ascontiguousarray(tokens, dtype=np.int32), int(block))]
+    except (ImportError, AttributeError):
+        pass
     out, prev = [], 0
     for i in range(0, len(tokens) // block * block, block):
         prev = fnv1a_chain(prev, tokens[i:i + block])
